@@ -1,0 +1,118 @@
+"""ctypes binding of the in-tree native libraries.
+
+``kernels()`` returns the CUDA kernel library (``_C/libhmf_b200_kernels.so``) and
+``runtime()`` the host-only C++ runtime (``_C/libhmf_b200_runtime.so``).  Both are built by
+``hybrid_model_factory_b200.build``.  On a machine with a GPU a missing kernel library is an
+error (ops never fall back silently to PyTorch there); on a CPU-only machine the pure
+PyTorch reference implementations in ``ops/reference.py`` are used instead.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from pathlib import Path
+
+import torch
+
+_PKG = Path(__file__).resolve().parent.parent
+_KERNELS_PATH = _PKG / "_C" / "libhmf_b200_kernels.so"
+_RUNTIME_PATH = _PKG / "_C" / "libhmf_b200_runtime.so"
+
+_kernels = None
+_runtime = None
+_launch_count = 0
+
+
+class NativeLibraryMissing(RuntimeError):
+    pass
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def kernels_available() -> bool:
+    return _KERNELS_PATH.exists()
+
+
+def use_cuda_kernels(*tensors: torch.Tensor) -> bool:
+    """True when the op must run on the hand-written CUDA path (all tensors on a GPU).
+
+    ``HMF_FORCE_REFERENCE=1`` routes every op to the PyTorch reference (debugging aid);
+    without it a CUDA tensor always takes the native path and a missing library raises.
+    """
+    if not tensors or not all(t.is_cuda for t in tensors if t is not None):
+        return False
+    if os.environ.get("HMF_FORCE_REFERENCE", "0") == "1":
+        return False
+    if not kernels_available():
+        raise NativeLibraryMissing(
+            f"{_KERNELS_PATH} is missing: run `python -m hybrid_model_factory_b200.build` "
+            "before using CUDA tensors")
+    return True
+
+
+def kernels() -> ctypes.CDLL:
+    global _kernels
+    if _kernels is None:
+        if not _KERNELS_PATH.exists():
+            raise NativeLibraryMissing(
+                f"{_KERNELS_PATH} is missing: run `python -m hybrid_model_factory_b200.build`")
+        lib = ctypes.CDLL(str(_KERNELS_PATH))
+        lib.hmf_last_error.restype = ctypes.c_char_p
+        _kernels = lib
+    return _kernels
+
+
+def runtime() -> ctypes.CDLL:
+    global _runtime
+    if _runtime is None:
+        if not _RUNTIME_PATH.exists():
+            raise NativeLibraryMissing(
+                f"{_RUNTIME_PATH} is missing: run `python -m hybrid_model_factory_b200.build`")
+        _runtime = ctypes.CDLL(str(_RUNTIME_PATH))
+    return _runtime
+
+
+def stream_ptr(device=None) -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def ptr(t: torch.Tensor | None) -> ctypes.c_void_p:
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def check(rc: int, what: str) -> None:
+    """Raises ``KernelError`` with the library's message when a launcher rejected a call."""
+    global _launch_count
+    if rc != 0:
+        msg = kernels().hmf_last_error().decode(errors="replace")
+        raise KernelError(f"{what} failed (code {rc}): {msg}")
+    _launch_count += 1
+
+
+def launch_count() -> int:
+    """Number of native kernel launches issued through this binding so far."""
+    return _launch_count
+
+
+def add_launches(n: int) -> None:
+    global _launch_count
+    _launch_count += n
+
+
+def read_status(reset: bool = True) -> tuple[int, int, int, int]:
+    """Returns the device status block (code, block, detail, count); code 0 means no kernel
+    wait ran out since the last reset."""
+    out = (ctypes.c_uint * 4)()
+    rc = kernels().hmf_read_status(out, ctypes.c_int(1 if reset else 0), stream_ptr())
+    if rc != 0:
+        raise KernelError(kernels().hmf_last_error().decode(errors="replace"))
+    return tuple(int(x) for x in out)
+
+
+def assert_status_ok() -> None:
+    code, block, detail, count = read_status(reset=True)
+    if code != 0:
+        raise KernelError(
+            f"a device-side wait ran out: code={code} block={block} detail={detail:#x} count={count}")
