@@ -1,0 +1,89 @@
+"""Context-parallel softmax attention for zig-zag sequence parallelism.
+
+Each rank holds queries, keys and values of its two zig-zag chunks.  K and V of all ranks
+are gathered (GQA keeps them small: ``Hkv`` heads), put back into global order, and each
+local segment attends causally to the key prefix that precedes it; in backward the key /
+value gradients are reduced back to their owners.  This replaces the reference project's
+ring attention monkey-patch (``model/model_utils/sequence_parallel.py:38-101``).
+
+On GPUs with peer access the gather is not a separate collective: ``ops.cuda_ops`` pulls
+remote K/V tiles over NVLink from inside the attention kernel (see ``parallel/peer.py``);
+this module is the portable path (gloo on CPU, NCCL baseline on GPU) and the numerical
+contract of the fused one.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from ..ops import functional as F_ops
+from .sp import SPContext, zigzag_merge, zigzag_split
+
+Tensor = torch.Tensor
+
+
+def _all_gather_seq(x: Tensor, sp: SPContext) -> Tensor:
+    """Gathers ``[B, L_local, ...]`` shards and returns the sequence in global order."""
+    shards = [torch.empty_like(x) for _ in range(sp.size)]
+    dist.all_gather(shards, x.contiguous(), group=sp.group)
+    return zigzag_merge(shards, dim=1)
+
+
+def _reduce_scatter_seq(x_full: Tensor, sp: SPContext) -> Tensor:
+    """Sums full-sequence tensors over the group and returns this rank's zig-zag shard."""
+    if x_full.is_cuda:
+        parts = [zigzag_split(x_full, r, sp.size, dim=1).contiguous() for r in range(sp.size)]
+        out = torch.empty_like(parts[0])
+        dist.reduce_scatter(out, parts, group=sp.group)
+        return out
+    buf = x_full.contiguous()
+    dist.all_reduce(buf, group=sp.group)  # gloo has no reduce_scatter
+    return zigzag_split(buf, sp.rank, sp.size, dim=1)
+
+
+class _CPAttention(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q: Tensor, k: Tensor, v: Tensor, sp: SPContext, scale: Optional[float], window: Optional[int]):
+        B, Ll = q.shape[0], q.shape[1]
+        c = Ll // 2
+        k_all = _all_gather_seq(k, sp)
+        v_all = _all_gather_seq(v, sp)
+        ca, cb = sp.rank, 2 * sp.size - 1 - sp.rank
+        ctx.sp, ctx.c, ctx.full_len = sp, c, k_all.shape[1]
+        graphs, outs = [], []
+        for seg, cid in ((0, ca), (1, cb)):
+            end = (cid + 1) * c
+            qs = q[:, seg * c:(seg + 1) * c].detach().requires_grad_(True)
+            ks = k_all[:, :end].detach().requires_grad_(True)
+            vs = v_all[:, :end].detach().requires_grad_(True)
+            with torch.enable_grad():
+                o = F_ops.attention(qs, ks, vs, scale=scale, causal=True, window=window)
+            graphs.append((qs, ks, vs, o))
+            outs.append(o.detach())
+        ctx.graphs = graphs
+        return torch.cat(outs, dim=1)
+
+    @staticmethod
+    def backward(ctx, d_o: Tensor):
+        sp, c = ctx.sp, ctx.c
+        dqs = []
+        qs0, ks0, vs0, _ = ctx.graphs[0]
+        dk_full = ks0.new_zeros(ks0.shape[0], ctx.full_len, *ks0.shape[2:], dtype=torch.float32)
+        dv_full = torch.zeros_like(dk_full)
+        for seg, (qs, ks, vs, o) in enumerate(ctx.graphs):
+            dq, dk, dv = torch.autograd.grad(o, (qs, ks, vs), d_o[:, seg * c:(seg + 1) * c].to(o.dtype))
+            dqs.append(dq)
+            dk_full[:, :dk.shape[1]] += dk.float()
+            dv_full[:, :dv.shape[1]] += dv.float()
+        ctx.graphs = None
+        dk = _reduce_scatter_seq(dk_full, sp).to(ks0.dtype)
+        dv = _reduce_scatter_seq(dv_full, sp).to(vs0.dtype)
+        return torch.cat(dqs, dim=1), dk, dv, None, None, None
+
+
+def cp_attention(q: Tensor, k: Tensor, v: Tensor, sp: SPContext, *, scale: Optional[float] = None,
+                 window: Optional[int] = None) -> Tensor:
+    """Causal attention of the local zig-zag queries against the whole (distributed) sequence."""
+    return _CPAttention.apply(q, k, v, sp, scale, window)
