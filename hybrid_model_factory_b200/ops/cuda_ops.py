@@ -1,0 +1,343 @@
+"""Bindings of the sm_100a kernels as autograd functions.
+
+Each public function mirrors the function of the same name in ``ops/reference.py``; inputs
+are bf16 CUDA tensors (fp32 where the contract says so).  Tensors of another dtype are
+evaluated with the reference formulas on the GPU (an explicit numerics-debugging path: the
+training and serving paths are bf16).
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+from . import reference as R
+
+Tensor = torch.Tensor
+c_int, c_ll, c_float = ctypes.c_int, ctypes.c_longlong, ctypes.c_float
+BF16 = torch.bfloat16
+
+
+def _K():
+    return _lib.kernels()
+
+
+def _is_bf16(*ts) -> bool:
+    return all(t is None or t.dtype == BF16 for t in ts)
+
+
+def _st(t: Tensor):
+    return _lib.stream_ptr(t.device)
+
+
+# ----------------------------------------------------------------------------------------
+# RMSNorm
+# ----------------------------------------------------------------------------------------
+class _RMSNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, eps, zero_centered):
+        shape = x.shape
+        D = shape[-1]
+        x2 = x.reshape(-1, D).contiguous()
+        N = x2.shape[0]
+        y = torch.empty_like(x2)
+        rstd = torch.empty(N, device=x.device, dtype=torch.float32)
+        w = None if weight is None else weight.contiguous()
+        _lib.check(_K().hmf_rms_norm_fwd(_lib.ptr(x2), None, _lib.ptr(w), _lib.ptr(y), None, _lib.ptr(rstd), c_ll(N),
+                                         c_int(D), c_float(eps), c_int(int(zero_centered)), _st(x)), "rms_norm_fwd")
+        ctx.save_for_backward(x2, w, rstd)
+        ctx.zero_centered, ctx.shape = zero_centered, shape
+        return y.view(shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w, rstd = ctx.saved_tensors
+        N, D = x2.shape
+        dy2 = dy.reshape(-1, D).contiguous()
+        dx = torch.empty_like(x2)
+        dw = None
+        part = None
+        if w is not None and ctx.needs_input_grad[1]:
+            nb = _K().hmf_rms_norm_bwd_blocks(c_ll(N))
+            part = torch.empty(nb, D, device=x2.device, dtype=torch.float32)
+            dw = torch.empty(D, device=x2.device, dtype=BF16)
+        _lib.check(_K().hmf_rms_norm_bwd(_lib.ptr(x2), _lib.ptr(w), _lib.ptr(dy2), _lib.ptr(rstd), _lib.ptr(dx),
+                                         _lib.ptr(part), _lib.ptr(dw), c_int(1), c_ll(N), c_int(D),
+                                         c_int(int(ctx.zero_centered)), _st(x2)), "rms_norm_bwd")
+        return dx.view(ctx.shape), dw, None, None
+
+
+def rms_norm(x: Tensor, weight: Optional[Tensor], eps: float, zero_centered: bool = False) -> Tensor:
+    if not _is_bf16(x, weight) or x.shape[-1] % 8 != 0:
+        return R.rms_norm(x, weight, eps, zero_centered)
+    return _RMSNorm.apply(x, weight, eps, zero_centered)
+
+
+def fused_add_rms_norm(x: Tensor, residual: Tensor, weight: Tensor, eps: float) -> Tuple[Tensor, Tensor]:
+    """Inference-path fusion (no autograd): residual add + norm in one pass."""
+    if not _is_bf16(x, residual, weight) or torch.is_grad_enabled() and (x.requires_grad or residual.requires_grad):
+        return R.fused_add_rms_norm(x, residual, weight, eps)
+    D = x.shape[-1]
+    x2, r2 = x.reshape(-1, D).contiguous(), residual.reshape(-1, D).contiguous()
+    y, r_out = torch.empty_like(x2), torch.empty_like(x2)
+    _lib.check(_K().hmf_rms_norm_fwd(_lib.ptr(x2), _lib.ptr(r2), _lib.ptr(weight.contiguous()), _lib.ptr(y),
+                                     _lib.ptr(r_out), None, c_ll(x2.shape[0]), c_int(D), c_float(eps), c_int(0), _st(x)),
+               "fused_add_rms_norm")
+    return y.view(x.shape), r_out.view(x.shape)
+
+
+# ----------------------------------------------------------------------------------------
+# gated RMSNorm over the head dimension
+# ----------------------------------------------------------------------------------------
+class _GatedNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, gate, weight, eps, mode):
+        shape = x.shape
+        D = shape[-1]
+        x2, g2 = x.reshape(-1, D).contiguous(), gate.reshape(-1, D).contiguous()
+        w = weight.contiguous()
+        w_rows = 1 if w.dim() == 1 else w.shape[0]
+        N = x2.shape[0]
+        y = torch.empty_like(x2)
+        rstd = torch.empty(N, device=x.device, dtype=torch.float32)
+        _lib.check(_K().hmf_gated_norm_fwd(_lib.ptr(x2), _lib.ptr(g2), _lib.ptr(w), _lib.ptr(y), _lib.ptr(rstd), c_ll(N),
+                                           c_int(D), c_int(w_rows), c_float(eps), c_int(mode), _st(x)), "gated_norm_fwd")
+        ctx.save_for_backward(x2, g2, w, rstd)
+        ctx.mode, ctx.shape, ctx.w_rows, ctx.gshape = mode, shape, w_rows, gate.shape
+        return y.view(shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, g2, w, rstd = ctx.saved_tensors
+        N, D = x2.shape
+        dy2 = dy.reshape(-1, D).contiguous()
+        dx, dg = torch.empty_like(x2), torch.empty_like(g2)
+        dw = torch.zeros(w.shape, device=x2.device, dtype=torch.float32)
+        _lib.check(_K().hmf_gated_norm_bwd(_lib.ptr(x2), _lib.ptr(g2), _lib.ptr(w), _lib.ptr(dy2), _lib.ptr(rstd),
+                                           _lib.ptr(dx), _lib.ptr(dg), _lib.ptr(dw), c_ll(N), c_int(D),
+                                           c_int(ctx.w_rows), c_int(ctx.mode), _st(x2)), "gated_norm_bwd")
+        return dx.view(ctx.shape), dg.view(ctx.gshape), dw.to(w.dtype), None, None
+
+
+def gated_rms_norm(x: Tensor, gate: Tensor, weight: Tensor, eps: float, norm_before_gate: bool = True) -> Tensor:
+    D = x.shape[-1]
+    if not _is_bf16(x, gate, weight) or D not in (64, 128, 256):
+        return R.gated_rms_norm(x, gate, weight, eps, norm_before_gate)
+    if weight.dim() == 2:
+        # per-head weights [H, D]: rows are (token, head) pairs with the head fastest
+        assert x.shape[-2] == weight.shape[0], "per-head weight needs x[..., H, D]"
+    return _GatedNorm.apply(x, gate, weight, eps, 0 if norm_before_gate else 1)
+
+
+# ----------------------------------------------------------------------------------------
+# SwiGLU
+# ----------------------------------------------------------------------------------------
+class _SwiGLU(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, g, u):
+        g, u = g.contiguous(), u.contiguous()
+        y = torch.empty_like(g)
+        _lib.check(_K().hmf_swiglu_fwd(_lib.ptr(g), _lib.ptr(u), _lib.ptr(y), c_ll(g.numel()), _st(g)), "swiglu_fwd")
+        ctx.save_for_backward(g, u)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        g, u = ctx.saved_tensors
+        dy = dy.contiguous()
+        dg, du = torch.empty_like(g), torch.empty_like(u)
+        _lib.check(_K().hmf_swiglu_bwd(_lib.ptr(g), _lib.ptr(u), _lib.ptr(dy), _lib.ptr(dg), _lib.ptr(du),
+                                       c_ll(g.numel()), _st(g)), "swiglu_bwd")
+        return dg, du
+
+
+def swiglu(gate: Tensor, up: Tensor) -> Tensor:
+    if not _is_bf16(gate, up) or gate.numel() % 8 != 0:
+        return R.swiglu(gate, up)
+    return _SwiGLU.apply(gate, up)
+
+
+# ----------------------------------------------------------------------------------------
+# RoPE
+# ----------------------------------------------------------------------------------------
+def _rope_launch(x: Tensor, cos: Tensor, sin: Tensor, backward: bool) -> Tensor:
+    B, T, H, D = x.shape
+    R_ = cos.shape[-1]
+    if x.stride(-1) != 1 or x.stride(2) != D or x.stride(0) != T * x.stride(1):
+        x = x.contiguous()
+    y = torch.empty(B, T, H, D, device=x.device, dtype=x.dtype)
+    _lib.check(_K().hmf_rope(_lib.ptr(x), _lib.ptr(cos), _lib.ptr(sin), _lib.ptr(y), c_ll(B * T), c_int(H), c_int(D),
+                             c_int(R_), c_int(int(backward)), c_ll(x.stride(1)), _st(x)), "rope")
+    return y
+
+
+class _RoPE(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, cos, sin):
+        cos2 = cos.expand(x.shape[0], x.shape[1], cos.shape[-1]).to(BF16).contiguous()
+        sin2 = sin.expand(x.shape[0], x.shape[1], sin.shape[-1]).to(BF16).contiguous()
+        ctx.save_for_backward(cos2, sin2)
+        return _rope_launch(x, cos2, sin2, False)
+
+    @staticmethod
+    def backward(ctx, dy):
+        cos2, sin2 = ctx.saved_tensors
+        return _rope_launch(dy, cos2, sin2, True), None, None
+
+
+def apply_rope(x: Tensor, cos: Tensor, sin: Tensor) -> Tensor:
+    Rr = cos.shape[-1]
+    if not _is_bf16(x) or Rr % 16 != 0 or x.shape[-1] % 8 != 0 or (x.data_ptr() % 16) != 0:
+        return R.apply_rope(x, cos, sin)
+    return _RoPE.apply(x, cos, sin)
+
+
+# ----------------------------------------------------------------------------------------
+# gating (tiny [T, H] tensors: plain PyTorch elementwise math)
+# ----------------------------------------------------------------------------------------
+def gdn_gating(a, b, A_log, dt_bias, beta_scale=1.0):
+    return R.gdn_gating(a, b, A_log, dt_bias, beta_scale)
+
+
+# ----------------------------------------------------------------------------------------
+# causal conv1d
+# ----------------------------------------------------------------------------------------
+class _Conv1d(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, bias, init, act, want_state):
+        B, T, C = x.shape
+        x = x.contiguous()
+        w = weight.contiguous()
+        K = w.shape[-1]
+        init_c = None if init is None else init.to(BF16).contiguous()
+        y = torch.empty_like(x)
+        final = torch.empty(B, K - 1, C, device=x.device, dtype=x.dtype) if want_state else None
+        _lib.check(_K().hmf_conv1d_fwd(_lib.ptr(x), _lib.ptr(w), _lib.ptr(bias), _lib.ptr(init_c), _lib.ptr(y),
+                                       _lib.ptr(final), c_int(B), c_int(T), c_int(C), c_int(K), c_int(act), _st(x)),
+                   "conv1d_fwd")
+        ctx.save_for_backward(x, w, bias, init_c)
+        ctx.act = act
+        ctx.has_init = init is not None
+        if want_state:
+            ctx.mark_non_differentiable(final)
+            return y, final
+        return y, None
+
+    @staticmethod
+    def backward(ctx, dy, _dfinal):
+        x, w, bias, init_c = ctx.saved_tensors
+        B, T, C = x.shape
+        K = w.shape[-1]
+        dy = dy.contiguous()
+        dx = torch.empty_like(x)
+        dw = torch.zeros(C, K, device=x.device, dtype=torch.float32)
+        db = torch.zeros(C, device=x.device, dtype=torch.float32) if bias is not None else None
+        dinit = torch.empty(B, K - 1, C, device=x.device, dtype=torch.float32) if ctx.has_init else None
+        _lib.check(_K().hmf_conv1d_bwd(_lib.ptr(x), _lib.ptr(w), _lib.ptr(bias), _lib.ptr(init_c), _lib.ptr(dy),
+                                       _lib.ptr(dx), _lib.ptr(dinit), _lib.ptr(dw), _lib.ptr(db), c_int(B), c_int(T),
+                                       c_int(C), c_int(K), c_int(ctx.act), _st(x)), "conv1d_bwd")
+        return (dx, dw.to(w.dtype), None if db is None else db.to(bias.dtype),
+                None if dinit is None else dinit.to(x.dtype), None, None)
+
+
+def causal_conv1d(x, weight, bias=None, activation="silu", initial_state=None, return_final_state=False):
+    if not _is_bf16(x, weight, bias) or weight.shape[-1] != 4 or x.shape[-1] % 8 != 0:
+        return R.causal_conv1d(x, weight, bias, activation, initial_state, return_final_state)
+    act = 1 if activation in ("silu", "swish") else 0
+    y, final = _Conv1d.apply(x, weight, bias, initial_state, act, return_final_state)
+    return (y, final) if return_final_state else y
+
+
+def causal_conv1d_update(x, conv_state, weight, bias=None, activation="silu", slots: Optional[Tensor] = None):
+    """Decode step; ``conv_state`` is updated in place (and returned)."""
+    if not _is_bf16(x, weight, bias, conv_state) or weight.shape[-1] != 4 or x.shape[-1] % 8 != 0:
+        return R.causal_conv1d_update(x, conv_state, weight, bias, activation)
+    B, C = x.shape
+    y = torch.empty_like(x)
+    state = conv_state if conv_state.is_contiguous() else conv_state.contiguous()
+    _lib.check(_K().hmf_conv1d_update(_lib.ptr(x.contiguous()), _lib.ptr(state), _lib.ptr(weight.contiguous()),
+                                      _lib.ptr(bias), _lib.ptr(y), _lib.ptr(slots), c_int(B), c_int(C), c_int(4),
+                                      c_int(1 if activation in ("silu", "swish") else 0), _st(x)), "conv1d_update")
+    return y, state
+
+
+# ----------------------------------------------------------------------------------------
+# fused linear + cross entropy
+# ----------------------------------------------------------------------------------------
+class _LinearCE(torch.autograd.Function):
+    """Forward computes the loss *and* the gradients chunk by chunk (logits of one chunk live at a
+    time, in bf16); backward only rescales by the incoming gradient."""
+
+    @staticmethod
+    def forward(ctx, hidden, weight, labels, ignore_index, chunk):
+        from .gemm import gemm
+        N, Dm = hidden.shape
+        V = weight.shape[0]
+        hidden = hidden.contiguous()
+        labels = labels.contiguous().to(torch.int64)
+        loss = torch.zeros(1, device=hidden.device, dtype=torch.float32)
+        nvalid = torch.zeros(1, device=hidden.device, dtype=torch.int32)
+        need_dh = ctx.needs_input_grad[0]
+        need_dw = ctx.needs_input_grad[1]
+        dh = torch.empty_like(hidden) if need_dh else None
+        dw = torch.zeros(V, Dm, device=hidden.device, dtype=torch.float32) if need_dw else None
+        Vp = (V + 7) // 8 * 8
+        buf = torch.empty(min(chunk, N), Vp, device=hidden.device, dtype=BF16)
+        for s in range(0, N, chunk):
+            n = min(chunk, N - s)
+            h = hidden[s:s + n]
+            logits = buf[:n, :V]
+            torch.matmul(h, weight.t(), out=logits) if Vp == V else logits.copy_(h @ weight.t())
+            _lib.check(_K().hmf_ce_fwd_bwd(_lib.ptr(logits), _lib.ptr(labels[s:s + n]), _lib.ptr(loss),
+                                           _lib.ptr(nvalid), c_ll(n), c_int(V), c_ll(Vp), c_ll(ignore_index),
+                                           _st(hidden)), "ce_fwd_bwd")
+            if need_dh:
+                torch.matmul(logits, weight, out=dh[s:s + n])
+            if need_dw:
+                # dW[V, Dm] += dlogits^T[V, n] @ h[n, Dm]: both operands MN-major for the tcgen05 GEMM
+                if V % 8 == 0 and Dm % 8 == 0:
+                    gemm(logits, h, a_mn_major=True, b_mn_major=True, out=dw, out_mode="f32_accumulate")
+                else:
+                    dw.addmm_(logits.t().float(), h.float())
+        ctx.save_for_backward(dh, dw)
+        ctx.wdtype = weight.dtype
+        ctx.mark_non_differentiable(nvalid)
+        return loss[0], nvalid[0]
+
+    @staticmethod
+    def backward(ctx, dloss, _dn):
+        dh, dw = ctx.saved_tensors
+        gh = None if dh is None else dh * dloss.to(dh.dtype)
+        gw = None if dw is None else (dw * dloss).to(ctx.wdtype)
+        return gh, gw, None, None, None
+
+
+def linear_cross_entropy(hidden, weight, labels, ignore_index=-100, chunk=8192):
+    if not _is_bf16(hidden, weight):
+        return R.linear_cross_entropy(hidden, weight, labels, ignore_index, "sum", chunk)
+    return _LinearCE.apply(hidden, weight, labels, ignore_index, chunk)
+
+
+# ----------------------------------------------------------------------------------------
+# optimizer kernels
+# ----------------------------------------------------------------------------------------
+_DT = {torch.bfloat16: 0, torch.float32: 1}
+
+
+def grad_sumsq(flat_grad: Tensor, out: Tensor) -> None:
+    """``out[0] += sum(flat_grad ** 2)`` (fp32 accumulator on the device, no host sync)."""
+    _lib.check(_K().hmf_sumsq(_lib.ptr(flat_grad), c_int(1 if flat_grad.dtype == BF16 else 0), c_ll(flat_grad.numel()),
+                              _lib.ptr(out), _st(flat_grad)), "sumsq")
+
+
+def adamw_step(p: Tensor, g: Tensor, m: Tensor, v: Tensor, *, lr: float, beta1: float, beta2: float, eps: float,
+               weight_decay: float, step: int, master: Optional[Tensor] = None, norm_sq: Optional[Tensor] = None,
+               max_norm: float = 0.0, grad_scale: float = 1.0) -> None:
+    """Fused AdamW over flat buffers, with optional global-norm clipping read from ``norm_sq``."""
+    bc1, bc2 = 1.0 - beta1 ** step, 1.0 - beta2 ** step
+    _lib.check(_K().hmf_adamw(_lib.ptr(p), _lib.ptr(g), _lib.ptr(m), _lib.ptr(v), _lib.ptr(master), c_ll(p.numel()),
+                              c_int(_DT[p.dtype]), c_int(_DT[g.dtype]), c_int(_DT[m.dtype]), c_float(lr), c_float(beta1),
+                              c_float(beta2), c_float(eps), c_float(weight_decay), c_float(bc1), c_float(bc2),
+                              _lib.ptr(norm_sq), c_float(max_norm), c_float(grad_scale), _st(p)), "adamw")
