@@ -341,3 +341,48 @@ def adamw_step(p: Tensor, g: Tensor, m: Tensor, v: Tensor, *, lr: float, beta1: 
                               c_int(_DT[p.dtype]), c_int(_DT[g.dtype]), c_int(_DT[m.dtype]), c_float(lr), c_float(beta1),
                               c_float(beta2), c_float(eps), c_float(weight_decay), c_float(bc1), c_float(bc2),
                               _lib.ptr(norm_sq), c_float(max_norm), c_float(grad_scale), _st(p)), "adamw")
+
+
+# ----------------------------------------------------------------------------------------
+# flash attention (tcgen05)
+# ----------------------------------------------------------------------------------------
+_INT_MAX = 2 ** 31 - 1
+
+
+def _mask_bounds(causal: bool, window: Optional[int], hollow: Optional[int]) -> Tuple[int, int]:
+    """(lo, hi) with key visible iff ``lo <= q_pos - k_pos < hi``."""
+    assert causal, "non-causal attention is not part of this library"
+    lo, hi = 0, _INT_MAX
+    if window is not None:
+        hi = min(hi, int(window))
+    if hollow is not None:
+        lo, hi = max(lo, int(hollow)), min(hi, 2 * int(hollow))
+    return lo, hi
+
+
+def _bthd_strides(t: Tensor):
+    assert t.stride(3) == 1, "head dimension must be contiguous"
+    return c_ll(t.stride(0)), c_ll(t.stride(1)), c_ll(t.stride(2))
+
+
+def _tma_ok(t: Tensor) -> bool:
+    return (t.stride(3) == 1 and t.data_ptr() % 16 == 0 and all(s % 8 == 0 for s in t.stride()[:3]))
+
+
+def attention_fwd_raw(q: Tensor, k: Tensor, v: Tensor, scale: float, lo: int, hi: int, q_off: int,
+                      q_pos: Optional[Tensor] = None) -> Tuple[Tensor, Tensor]:
+    """Launches the forward kernel; returns ``(o [B,Tq,Hq,D] bf16, lse [B,Hq,Tq] fp32)``."""
+    B, Tq, Hq, D = q.shape
+    Tk, Hkv = k.shape[1], k.shape[2]
+    q = q if _tma_ok(q) else q.contiguous()
+    k = k if _tma_ok(k) else k.contiguous()
+    v = v if _tma_ok(v) else v.contiguous()
+    o = torch.empty(B, Tq, Hq, D, device=q.device, dtype=BF16)
+    lse = torch.empty(B, Hq, Tq, device=q.device, dtype=torch.float32)
+    if q_pos is not None:
+        q_pos = q_pos.to(torch.int32).contiguous()
+    _lib.check(_K().hmf_attention_fwd(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(o), _lib.ptr(lse), _lib.ptr(q_pos),
+                                      c_int(B), c_int(Tq), c_int(Tk), c_int(Hq), c_int(Hkv), c_int(D),
+                                      *_bthd_strides(q), *_bthd_strides(k), *_bthd_strides(v), c_int(lo), c_int(hi),
+                                      c_int(q_off), c_float(scale), _st(q)), "attention_fwd")
+    return o, lse
