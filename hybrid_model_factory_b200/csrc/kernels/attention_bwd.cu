@@ -1,0 +1,677 @@
+// Flash attention backward for sm_100a (tcgen05 + TMEM + TMA), as three kernels:
+//
+//   1. delta[b,h,t] = sum_d dO * O                                   (memory bound)
+//   2. dQ kernel   : one CTA per 128-row query tile; loops over key tiles of 64:
+//                      S = Q K^T, dP = dO V^T  ->  dS = P o (dP - delta) * scale  ->  dQ += dS K
+//   3. dK/dV kernel: one CTA per 128-key tile of a KV head; loops over the query heads of the group
+//                    and their query tiles of 64:
+//                      S^T = K Q^T, dP^T = V dO^T  ->  P^T, dS^T  ->  dV += P^T dO, dK += dS^T Q
+//
+// Both kernels keep every accumulator in tensor memory, recompute P from the saved log-sum-exp,
+// write the bf16 probabilities / score gradients back into tensor memory over S / dP
+// (tcgen05.st) and feed them to the next MMA as the TMEM A operand.  No atomics: dQ is owned by
+// the query-tile CTA and dK/dV by the key-tile CTA (the GQA group sum happens in the accumulator).
+// Masks follow the forward kernel: key visible <=> lo <= q_pos - k_pos < hi.
+#include <math.h>
+
+#include "../common/host.h"
+#include "../common/sm100.cuh"
+
+namespace hmf {
+namespace attn_bwd {
+
+using bf16 = __nv_bfloat16;
+constexpr float kLog2e = 1.4426950408889634f;
+
+struct Params {
+  const float* lse;    // [B, Hq, Tq]
+  const float* delta;  // [B, Hq, Tq]
+  const int* q_pos;    // optional [B, Tq]
+  bf16* dq;            // [B, Tq, Hq, D]
+  bf16* dk;            // [B, Tk, Hkv, D]
+  bf16* dv;            // [B, Tk, Hkv, D]
+  int B, Tq, Tk, Hq, Hkv;
+  int lo, hi, q_off;
+  float scale, scale_log2;
+  unsigned int* status;
+};
+
+// ------------------------------------------------------------------------------------
+// delta = rowsum(dO * O); 16 lanes per row of D <= 128 (D % 8 == 0)
+// ------------------------------------------------------------------------------------
+__global__ void delta_kernel(const bf16* __restrict__ o, const bf16* __restrict__ d_o,
+                             float* __restrict__ delta, int B, int T, int H, int D) {
+  const int lanes = D / 8;  // 8 or 16
+  const int rows_per_warp = 32 / lanes;
+  const int lane = threadIdx.x & 31;
+  const long long wid = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const long long row = wid * rows_per_warp + lane / lanes;  // index over (b, t, h)
+  const long long total = (long long)B * T * H;
+  float s = 0.f;
+  if (row < total) {
+    const int c = (lane % lanes) * 8;
+    const uint4 a = *reinterpret_cast<const uint4*>(o + row * D + c);
+    const uint4 g = *reinterpret_cast<const uint4*>(d_o + row * D + c);
+    const __nv_bfloat162* ah = reinterpret_cast<const __nv_bfloat162*>(&a);
+    const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&g);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 x = __bfloat1622float2(ah[i]), y = __bfloat1622float2(gh[i]);
+      s += x.x * y.x + x.y * y.y;
+    }
+  }
+  for (int off = lanes / 2; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+  if (row < total && (lane % lanes) == 0) {
+    const long long h = row % H, bt = row / H;
+    const long long t = bt % T, b = bt / T;
+    delta[(b * H + h) * T + t] = s;
+  }
+}
+
+// ------------------------------------------------------------------------------------
+// dQ kernel
+// ------------------------------------------------------------------------------------
+constexpr int BM = 128;  // query rows per CTA
+constexpr int BN = 64;   // keys per inner tile
+
+template <int D>
+struct SmemDQ {
+  static constexpr int QP = BM * 128;           // one 64-wide panel of Q / dO
+  static constexpr int KP = BN * 128;           // one 64-wide panel of K / V
+  static constexpr int Q_BYTES = BM * D * 2;
+  static constexpr int KV_BYTES = BN * D * 2;
+  static constexpr int OFF_DO = Q_BYTES;
+  static constexpr int OFF_K = 2 * Q_BYTES;      // 2 stages
+  static constexpr int OFF_V = OFF_K + 2 * KV_BYTES;
+  static constexpr int OFF_BAR = OFF_V + KV_BYTES;
+  static constexpr int TOTAL = OFF_BAR + 256;
+};
+
+template <int D>
+__global__ void __launch_bounds__(192, 2)
+attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
+                   const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                   const Params p) {
+  using L = SmemDQ<D>;
+  constexpr int TMEM_COLS = (128 + D) <= 256 ? 256 : 512;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint8_t* sQ = smem;
+  uint8_t* sDO = smem + L::OFF_DO;
+  uint8_t* sK = smem + L::OFF_K;
+  uint8_t* sV = smem + L::OFF_V;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
+  uint64_t* qdo_full = bars + 0;
+  uint64_t* k_full = bars + 1;   // [2]
+  uint64_t* k_empty = bars + 3;  // [2]
+  uint64_t* v_full = bars + 5;
+  uint64_t* v_empty = bars + 6;
+  uint64_t* sdp_full = bars + 7;
+  uint64_t* ds_full = bars + 8;
+  uint64_t* dq_done = bars + 9;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const WaitCtx ctx{abort_flag, p.status};
+  const int h = blockIdx.x;
+  const int qt = (int)gridDim.y - 1 - (int)blockIdx.y;
+  const int b = blockIdx.z;
+  const int hkv = h / (p.Hq / p.Hkv);
+  const int q0 = qt * BM;
+  const int rows_valid = min(BM, p.Tq - q0);
+
+  long long pmin, pmax;
+  if (p.q_pos) {
+    pmin = p.q_pos[(size_t)b * p.Tq + q0];
+    pmax = p.q_pos[(size_t)b * p.Tq + q0 + rows_valid - 1];
+  } else {
+    pmin = (long long)q0 + p.q_off;
+    pmax = (long long)q0 + rows_valid - 1 + p.q_off;
+  }
+  long long kmin = pmin - (long long)p.hi + 1;
+  if (kmin < 0) kmin = 0;
+  long long kmax = pmax - (long long)p.lo;
+  if (kmax > p.Tk - 1) kmax = p.Tk - 1;
+  const int j0 = (int)(kmin / BN);
+  const int n_tiles = (kmax >= kmin) ? (int)(kmax / BN) - j0 + 1 : 0;
+
+  if (threadIdx.x == 0) {
+    if ((smem_u32(smem) & 1023u) != 0) report_error(p.status, kBadArgument, 0xA1);
+    mbar_init(qdo_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&k_full[s], 1);
+      mbar_init(&k_empty[s], 1);
+    }
+    mbar_init(v_full, 1);
+    mbar_init(v_empty, 1);
+    mbar_init(sdp_full, 1);
+    mbar_init(ds_full, 128);
+    mbar_init(dq_done, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tS = tmem_base, tDP = tmem_base + 64, tDQ = tmem_base + 128;
+
+  if (warp == 0) {
+    if (lane == 0 && n_tiles > 0) {
+      mbar_expect_tx(qdo_full, 2 * L::Q_BYTES);
+#pragma unroll
+      for (int pn = 0; pn < D / 64; ++pn) {
+        tma_load_4d(sQ + pn * L::QP, &tmQ, qdo_full, pn * 64, h, q0, b);
+        tma_load_4d(sDO + pn * L::QP, &tmDO, qdo_full, pn * 64, h, q0, b);
+      }
+      for (int j = 0; j < n_tiles; ++j) {
+        const int s = j & 1;
+        const int k0 = (j0 + j) * BN;
+        mbar_wait(&k_empty[s], ((j >> 1) & 1) ^ 1, ctx, 0x110 + s);
+        mbar_expect_tx(&k_full[s], L::KV_BYTES);
+#pragma unroll
+        for (int pn = 0; pn < D / 64; ++pn)
+          tma_load_4d(sK + s * L::KV_BYTES + pn * L::KP, &tmK, &k_full[s], pn * 64, hkv, k0, b);
+        mbar_wait(v_empty, (j & 1) ^ 1, ctx, 0x120);
+        mbar_expect_tx(v_full, L::KV_BYTES);
+#pragma unroll
+        for (int pn = 0; pn < D / 64; ++pn) tma_load_4d(sV + pn * L::KP, &tmV, v_full, pn * 64, hkv, k0, b);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && n_tiles > 0) {
+      constexpr uint32_t idescS = make_idesc_bf16(BM, BN, false, false);
+      constexpr uint32_t idescDQ = make_idesc_bf16(BM, D, false, true);
+      const uint32_t aQ = smem_u32(sQ), aDO = smem_u32(sDO), aV = smem_u32(sV);
+      mbar_wait(qdo_full, 0, ctx, 0x130);
+      for (int j = 0; j < n_tiles; ++j) {
+        const int s = j & 1;
+        const uint32_t aK = smem_u32(sK + s * L::KV_BYTES);
+        mbar_wait(&k_full[s], (j >> 1) & 1, ctx, 0x140 + s);
+        mbar_wait(v_full, j & 1, ctx, 0x150);
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint64_t ad = make_desc_kmajor_sw128(aQ + (kk / 4) * L::QP + (kk % 4) * 32);
+          const uint64_t bd = make_desc_kmajor_sw128(aK + (kk / 4) * L::KP + (kk % 4) * 32);
+          umma_ss(tS, ad, bd, idescS, kk > 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint64_t ad = make_desc_kmajor_sw128(aDO + (kk / 4) * L::QP + (kk % 4) * 32);
+          const uint64_t bd = make_desc_kmajor_sw128(aV + (kk / 4) * L::KP + (kk % 4) * 32);
+          umma_ss(tDP, ad, bd, idescS, kk > 0 ? 1u : 0u);
+        }
+        umma_commit(v_empty);
+        umma_commit(sdp_full);
+        mbar_wait(ds_full, j & 1, ctx, 0x160);
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < BN / 16; ++kk) {
+          const uint64_t bd = make_desc_mnmajor_sw128(aK + kk * 2048, L::KP);
+          umma_ts(tDQ, tS + kk * 8, bd, idescDQ, (j > 0 || kk > 0) ? 1u : 0u);
+        }
+        umma_commit(&k_empty[s]);
+      }
+      umma_commit(dq_done);
+    }
+  } else {
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;
+    const int row = q0 + r;
+    const bool row_ok = row < p.Tq;
+    const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
+    long long prow = 0;
+    float lse2 = INFINITY, delta = 0.f;
+    if (row_ok) {
+      prow = p.q_pos ? (long long)p.q_pos[(size_t)b * p.Tq + row] : (long long)row + p.q_off;
+      const float l = p.lse[((size_t)b * p.Hq + h) * p.Tq + row];
+      lse2 = (l == -INFINITY) ? INFINITY : l * kLog2e;
+      delta = p.delta[((size_t)b * p.Hq + h) * p.Tq + row];
+    }
+    for (int j = 0; j < n_tiles; ++j) {
+      const int k0 = (j0 + j) * BN;
+      mbar_wait(sdp_full, j & 1, ctx, 0x170);
+      tc_fence_after();
+      const bool full_vis = (pmin - (long long)(k0 + BN - 1) >= (long long)p.lo) &&
+                            (pmax - (long long)k0 < (long long)p.hi) && (k0 + BN <= p.Tk) &&
+                            (rows_valid == BM);
+      long long chi = prow - k0 - (long long)p.lo;
+      long long clo = prow - k0 - (long long)p.hi;
+      const long long cend = (long long)p.Tk - k0 - 1;
+      if (chi > cend) chi = cend;
+      if (!row_ok) chi = -1;
+      const int ichi = full_vis ? 1000 : (int)max(-1ll, min(chi, 1000ll));
+      const int iclo = full_vis ? -1 : (int)max(-1ll, min(clo, 1000ll));
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t sv[32], dp[32], pk[16];
+        tmem_ld_x32(tS + lane_off + half * 32, sv);
+        tmem_ld_x32(tDP + lane_off + half * 32, dp);
+        tmem_ld_wait();
+#pragma unroll
+        for (int c = 0; c < 32; c += 2) {
+          float d2[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int cc = half * 32 + c + e;
+            const bool vis = (cc <= ichi) && (cc > iclo);
+            const float pr = vis ? exp2f(fmaf(__uint_as_float(sv[c + e]), p.scale_log2, -lse2)) : 0.f;
+            d2[e] = pr * (__uint_as_float(dp[c + e]) - delta) * p.scale;
+          }
+          pk[c >> 1] = pack_bf16x2(d2[0], d2[1]);
+        }
+        tmem_st_x16(tS + lane_off + half * 16, pk);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(ds_full);
+    }
+    if (n_tiles > 0) {
+      mbar_wait(dq_done, 0, ctx, 0x180);
+      tc_fence_after();
+    }
+    bf16* orow = p.dq + (((size_t)b * p.Tq + row) * p.Hq + h) * D;
+#pragma unroll
+    for (int ch = 0; ch < D / 32; ++ch) {
+      uint32_t o[32];
+      if (n_tiles > 0) {
+        tmem_ld_x32(tDQ + lane_off + ch * 32, o);
+        tmem_ld_wait();
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[i] = 0u;
+      }
+      if (row_ok) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          uint4 w;
+          w.x = pack_bf16x2(__uint_as_float(o[8 * i + 0]), __uint_as_float(o[8 * i + 1]));
+          w.y = pack_bf16x2(__uint_as_float(o[8 * i + 2]), __uint_as_float(o[8 * i + 3]));
+          w.z = pack_bf16x2(__uint_as_float(o[8 * i + 4]), __uint_as_float(o[8 * i + 5]));
+          w.w = pack_bf16x2(__uint_as_float(o[8 * i + 6]), __uint_as_float(o[8 * i + 7]));
+          reinterpret_cast<uint4*>(orow + ch * 32)[i] = w;
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ------------------------------------------------------------------------------------
+// dK / dV kernel
+// ------------------------------------------------------------------------------------
+constexpr int KM = 128;  // keys per CTA
+constexpr int QN = 64;   // query rows per inner tile
+
+template <int D>
+struct SmemDKV {
+  static constexpr int KPANEL = KM * 128;
+  static constexpr int QPANEL = QN * 128;
+  static constexpr int K_BYTES = KM * D * 2;
+  static constexpr int Q_BYTES = QN * D * 2;
+  static constexpr int OFF_V = K_BYTES;
+  static constexpr int OFF_Q = 2 * K_BYTES;            // stages: [Q | dO] x 2
+  static constexpr int STAGE = 2 * Q_BYTES;
+  static constexpr int OFF_ROW = OFF_Q + 2 * STAGE;    // lse2 / delta / qpos staging: 2 x 3 x 64 x 4
+  static constexpr int OFF_BAR = OFF_ROW + 2 * 3 * QN * 4;
+  static constexpr int TOTAL = OFF_BAR + 256;
+};
+
+// Iterates the (query head of the group, query tile) pairs that can see the key tile [k0, k0+KM).
+struct QTileIter {
+  int G, nq_tiles, i_lo, i_hi;  // contiguous positions: tiles [i_lo, i_hi]
+  __device__ int count() const { return (i_hi >= i_lo) ? G * (i_hi - i_lo + 1) : 0; }
+  __device__ void get(int it, int& g, int& i) const {
+    const int per = i_hi - i_lo + 1;
+    g = it / per;
+    i = i_lo + it % per;
+  }
+};
+
+template <int D>
+__global__ void __launch_bounds__(192, 1)
+attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
+                    const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                    const Params p) {
+  using L = SmemDKV<D>;
+  constexpr int TMEM_COLS = 512;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint8_t* sK = smem;
+  uint8_t* sV = smem + L::OFF_V;
+  uint8_t* sQ = smem + L::OFF_Q;
+  float* s_row = reinterpret_cast<float*>(smem + L::OFF_ROW);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
+  uint64_t* kv_full = bars + 0;
+  uint64_t* q_full = bars + 1;    // [2]
+  uint64_t* q_empty = bars + 3;   // [2]
+  uint64_t* st_full = bars + 5;   // [2]
+  uint64_t* pds_full = bars + 7;  // [2]
+  uint64_t* acc_done = bars + 9;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const WaitCtx ctx{abort_flag, p.status};
+  const int kt = blockIdx.x;  // ascending: early key tiles (most work under a causal mask) first
+  const int hkv = blockIdx.y;
+  const int b = blockIdx.z;
+  const int k0 = kt * KM;
+  const int keys_valid = min(KM, p.Tk - k0);
+  const int G = p.Hq / p.Hkv;
+  const int nq_tiles = (p.Tq + QN - 1) / QN;
+
+  // query tiles that may see keys [k0, k0+keys_valid): positions in [k0+lo, k0+keys_valid-1+hi-1]
+  QTileIter iter;
+  iter.G = G;
+  iter.nq_tiles = nq_tiles;
+  if (p.q_pos) {
+    iter.i_lo = 0;  // explicit positions: visit every tile, masks do the rest
+    iter.i_hi = nq_tiles - 1;
+  } else {
+    long long rmin = (long long)k0 + p.lo - p.q_off;
+    long long rmax = (long long)k0 + keys_valid - 1 + (long long)p.hi - 1 - p.q_off;
+    if (rmin < 0) rmin = 0;
+    if (rmax > p.Tq - 1) rmax = p.Tq - 1;
+    iter.i_lo = (int)(rmin / QN);
+    iter.i_hi = (rmax >= rmin) ? (int)(rmax / QN) : iter.i_lo - 1;
+  }
+  const int n_it = iter.count();
+
+  if (threadIdx.x == 0) {
+    if ((smem_u32(smem) & 1023u) != 0) report_error(p.status, kBadArgument, 0xA2);
+    mbar_init(kv_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&q_full[s], 1);
+      mbar_init(&q_empty[s], 1);
+      mbar_init(&st_full[s], 1);
+      mbar_init(&pds_full[s], 128);
+    }
+    mbar_init(acc_done, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  auto tST = [&](int s) -> uint32_t { return tmem_base + (uint32_t)s * 64u; };
+  auto tDPT = [&](int s) -> uint32_t { return tmem_base + 128u + (uint32_t)s * 64u; };
+  const uint32_t tDV = tmem_base + 256, tDK = tmem_base + 256 + D;
+
+  if (warp == 0) {
+    if (lane == 0 && n_it > 0) {
+      mbar_expect_tx(kv_full, 2 * L::K_BYTES);
+#pragma unroll
+      for (int pn = 0; pn < D / 64; ++pn) {
+        tma_load_4d(sK + pn * L::KPANEL, &tmK, kv_full, pn * 64, hkv, k0, b);
+        tma_load_4d(sV + pn * L::KPANEL, &tmV, kv_full, pn * 64, hkv, k0, b);
+      }
+      for (int it = 0; it < n_it; ++it) {
+        const int s = it & 1;
+        int g, i;
+        iter.get(it, g, i);
+        const int h = hkv * G + g;
+        mbar_wait(&q_empty[s], ((it >> 1) & 1) ^ 1, ctx, 0x210 + s);
+        mbar_expect_tx(&q_full[s], L::STAGE);
+        uint8_t* dst = sQ + s * L::STAGE;
+#pragma unroll
+        for (int pn = 0; pn < D / 64; ++pn) {
+          tma_load_4d(dst + pn * L::QPANEL, &tmQ, &q_full[s], pn * 64, h, i * QN, b);
+          tma_load_4d(dst + L::Q_BYTES + pn * L::QPANEL, &tmDO, &q_full[s], pn * 64, h, i * QN, b);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && n_it > 0) {
+      constexpr uint32_t idescST = make_idesc_bf16(KM, QN, false, false);
+      constexpr uint32_t idescAcc = make_idesc_bf16(KM, D, false, true);
+      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV);
+      auto issue_SdP = [&](int it) {
+        const int s = it & 1;
+        mbar_wait(&q_full[s], (it >> 1) & 1, ctx, 0x220 + s);
+        tc_fence_after();
+        const uint32_t aQ = smem_u32(sQ + s * L::STAGE);
+        const uint32_t aDO = aQ + L::Q_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint64_t ad = make_desc_kmajor_sw128(aK + (kk / 4) * L::KPANEL + (kk % 4) * 32);
+          const uint64_t bd = make_desc_kmajor_sw128(aQ + (kk / 4) * L::QPANEL + (kk % 4) * 32);
+          umma_ss(tST(s), ad, bd, idescST, kk > 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint64_t ad = make_desc_kmajor_sw128(aV + (kk / 4) * L::KPANEL + (kk % 4) * 32);
+          const uint64_t bd = make_desc_kmajor_sw128(aDO + (kk / 4) * L::QPANEL + (kk % 4) * 32);
+          umma_ss(tDPT(s), ad, bd, idescST, kk > 0 ? 1u : 0u);
+        }
+        umma_commit(&st_full[s]);
+      };
+      mbar_wait(kv_full, 0, ctx, 0x230);
+      issue_SdP(0);
+      if (n_it > 1) issue_SdP(1);
+      for (int it = 0; it < n_it; ++it) {
+        const int s = it & 1;
+        mbar_wait(&pds_full[s], (it >> 1) & 1, ctx, 0x240 + s);
+        tc_fence_after();
+        const uint32_t aQ = smem_u32(sQ + s * L::STAGE);
+        const uint32_t aDO = aQ + L::Q_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < QN / 16; ++kk) {
+          const uint64_t bd = make_desc_mnmajor_sw128(aDO + kk * 2048, L::QPANEL);
+          umma_ts(tDV, tST(s) + kk * 8, bd, idescAcc, (it > 0 || kk > 0) ? 1u : 0u);
+        }
+#pragma unroll
+        for (int kk = 0; kk < QN / 16; ++kk) {
+          const uint64_t bd = make_desc_mnmajor_sw128(aQ + kk * 2048, L::QPANEL);
+          umma_ts(tDK, tDPT(s) + kk * 8, bd, idescAcc, (it > 0 || kk > 0) ? 1u : 0u);
+        }
+        umma_commit(&q_empty[s]);
+        if (it + 2 < n_it) issue_SdP(it + 2);
+      }
+      umma_commit(acc_done);
+    }
+  } else {
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;  // key row
+    const int tid = threadIdx.x - 64;  // 0..127
+    const long long kpos = (long long)k0 + r;
+    const bool key_ok = r < keys_valid;
+    const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
+    // query position window that sees this key: [kpos + lo, kpos + hi), clamped to int range
+    const int vis_lo = (int)min(kpos + (long long)p.lo, 2147483647ll);
+    const int vis_hi = (int)min(kpos + (long long)p.hi, 2147483647ll);
+    for (int it = 0; it < n_it; ++it) {
+      const int s = it & 1;
+      int g, i;
+      iter.get(it, g, i);
+      const int h = hkv * G + g;
+      const int q0 = i * QN;
+      float* st_lse = s_row + s * 3 * QN;
+      float* st_del = st_lse + QN;
+      int* st_pos = reinterpret_cast<int*>(st_del + QN);
+      if (tid < QN) {
+        const int qi = q0 + tid;
+        float l2 = INFINITY;
+        int pos = -(1 << 30);
+        if (qi < p.Tq) {
+          const float l = p.lse[((size_t)b * p.Hq + h) * p.Tq + qi];
+          l2 = (l == -INFINITY) ? INFINITY : l * kLog2e;
+          pos = p.q_pos ? p.q_pos[(size_t)b * p.Tq + qi] : qi + p.q_off;
+        }
+        st_lse[tid] = l2;
+        st_pos[tid] = pos;
+      } else {
+        const int qi = q0 + tid - QN;
+        st_del[tid - QN] = (qi < p.Tq) ? p.delta[((size_t)b * p.Hq + h) * p.Tq + qi] : 0.f;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      mbar_wait(&st_full[s], (it >> 1) & 1, ctx, 0x250 + s);
+      tc_fence_after();
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t sv[32], dp[32], pp[16], pd[16];
+        tmem_ld_x32(tST(s) + lane_off + half * 32, sv);
+        tmem_ld_x32(tDPT(s) + lane_off + half * 32, dp);
+        tmem_ld_wait();
+#pragma unroll
+        for (int c = 0; c < 32; c += 2) {
+          float pr[2], ds[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int cc = half * 32 + c + e;
+            const int pos = st_pos[cc];
+            const bool vis = key_ok && pos >= vis_lo && pos < vis_hi;
+            pr[e] = vis ? exp2f(fmaf(__uint_as_float(sv[c + e]), p.scale_log2, -st_lse[cc])) : 0.f;
+            ds[e] = pr[e] * (__uint_as_float(dp[c + e]) - st_del[cc]) * p.scale;
+          }
+          pp[c >> 1] = pack_bf16x2(pr[0], pr[1]);
+          pd[c >> 1] = pack_bf16x2(ds[0], ds[1]);
+        }
+        tmem_st_x16(tST(s) + lane_off + half * 16, pp);
+        tmem_st_x16(tDPT(s) + lane_off + half * 16, pd);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(&pds_full[s]);
+    }
+    if (n_it > 0) {
+      mbar_wait(acc_done, 0, ctx, 0x260);
+      tc_fence_after();
+    }
+#pragma unroll
+    for (int which = 0; which < 2; ++which) {
+      bf16* base = which == 0 ? p.dv : p.dk;
+      const uint32_t tacc = which == 0 ? tDV : tDK;
+      bf16* orow = base + (((size_t)b * p.Tk + k0 + r) * p.Hkv + hkv) * D;
+#pragma unroll
+      for (int ch = 0; ch < D / 32; ++ch) {
+        uint32_t o[32];
+        if (n_it > 0) {
+          tmem_ld_x32(tacc + lane_off + ch * 32, o);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = 0u;
+        }
+        if (key_ok) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint4 w;
+            w.x = pack_bf16x2(__uint_as_float(o[8 * i + 0]), __uint_as_float(o[8 * i + 1]));
+            w.y = pack_bf16x2(__uint_as_float(o[8 * i + 2]), __uint_as_float(o[8 * i + 3]));
+            w.z = pack_bf16x2(__uint_as_float(o[8 * i + 4]), __uint_as_float(o[8 * i + 5]));
+            w.w = pack_bf16x2(__uint_as_float(o[8 * i + 6]), __uint_as_float(o[8 * i + 7]));
+            reinterpret_cast<uint4*>(orow + ch * 32)[i] = w;
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+static int make_map_bthd(CUtensorMap* m, const void* base, int B, int T, int H, int D, long long sb,
+                         long long st, long long sh, int box_rows) {
+  uint64_t dims[4] = {(uint64_t)D, (uint64_t)H, (uint64_t)T, (uint64_t)B};
+  uint64_t strides[4] = {2, (uint64_t)sh * 2, (uint64_t)st * 2, (uint64_t)sb * 2};
+  uint32_t box[4] = {64, 1, (uint32_t)box_rows, 1};
+  return make_tensor_map(m, base, 0, 4, dims, strides, box, 3);
+}
+
+template <int D>
+static int launch_all(const void* q, const void* k, const void* v, const void* d_o, const Params& p,
+                      const long long* qs, const long long* ks, const long long* vs, cudaStream_t st) {
+  CUtensorMap tmQ, tmDO, tmK, tmV;
+  int rc;
+  const long long os[3] = {(long long)p.Tq * p.Hq * D, (long long)p.Hq * D, D};
+  // dQ kernel: Q/dO boxes of 128 rows, K/V boxes of 64 rows
+  if ((rc = make_map_bthd(&tmQ, q, p.B, p.Tq, p.Hq, D, qs[0], qs[1], qs[2], BM)) != HMF_OK) return rc;
+  if ((rc = make_map_bthd(&tmDO, d_o, p.B, p.Tq, p.Hq, D, os[0], os[1], os[2], BM)) != HMF_OK) return rc;
+  if ((rc = make_map_bthd(&tmK, k, p.B, p.Tk, p.Hkv, D, ks[0], ks[1], ks[2], BN)) != HMF_OK) return rc;
+  if ((rc = make_map_bthd(&tmV, v, p.B, p.Tk, p.Hkv, D, vs[0], vs[1], vs[2], BN)) != HMF_OK) return rc;
+  {
+    auto kern = attn_bwd_dq_kernel<D>;
+    static bool configured = false;
+    if (!configured) {
+      HMF_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemDQ<D>::TOTAL));
+      configured = true;
+    }
+    dim3 grid(p.Hq, (p.Tq + BM - 1) / BM, p.B);
+    kern<<<grid, 192, SmemDQ<D>::TOTAL, st>>>(tmQ, tmDO, tmK, tmV, p);
+    HMF_CHECK_CUDA(cudaGetLastError());
+  }
+  // dK/dV kernel: K/V boxes of 128 rows, Q/dO boxes of 64 rows
+  if ((rc = make_map_bthd(&tmQ, q, p.B, p.Tq, p.Hq, D, qs[0], qs[1], qs[2], QN)) != HMF_OK) return rc;
+  if ((rc = make_map_bthd(&tmDO, d_o, p.B, p.Tq, p.Hq, D, os[0], os[1], os[2], QN)) != HMF_OK) return rc;
+  if ((rc = make_map_bthd(&tmK, k, p.B, p.Tk, p.Hkv, D, ks[0], ks[1], ks[2], KM)) != HMF_OK) return rc;
+  if ((rc = make_map_bthd(&tmV, v, p.B, p.Tk, p.Hkv, D, vs[0], vs[1], vs[2], KM)) != HMF_OK) return rc;
+  {
+    auto kern = attn_bwd_dkv_kernel<D>;
+    static bool configured = false;
+    if (!configured) {
+      HMF_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemDKV<D>::TOTAL));
+      configured = true;
+    }
+    dim3 grid((p.Tk + KM - 1) / KM, p.Hkv, p.B);
+    kern<<<grid, 192, SmemDKV<D>::TOTAL, st>>>(tmQ, tmDO, tmK, tmV, p);
+    HMF_CHECK_CUDA(cudaGetLastError());
+  }
+  return HMF_OK;
+}
+
+}  // namespace attn_bwd
+}  // namespace hmf
+
+// Gradients of hmf_attention_fwd.  o, d_o, dq: [B,Tq,Hq,D] contiguous; dk, dv: [B,Tk,Hkv,D]
+// contiguous; lse from the forward pass; delta: scratch [B,Hq,Tq] fp32 provided by the caller.
+HMF_API int hmf_attention_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o,
+                              const float* lse, float* delta, void* dq, void* dk, void* dv, const int* q_pos,
+                              int B, int Tq, int Tk, int Hq, int Hkv, int D, long long q_sb, long long q_st,
+                              long long q_sh, long long k_sb, long long k_st, long long k_sh, long long v_sb,
+                              long long v_st, long long v_sh, int lo, int hi, int q_off, float scale,
+                              cudaStream_t stream) {
+  using namespace hmf;
+  using namespace hmf::attn_bwd;
+  HMF_REQUIRE(q && k && v && o && d_o && lse && delta && dq && dk && dv, "attention_bwd: null tensor");
+  HMF_REQUIRE(D == 64 || D == 128, "attention_bwd: head dim %d unsupported (64, 128)", D);
+  HMF_REQUIRE(Hkv > 0 && Hq % Hkv == 0, "attention_bwd: Hq=%d not a multiple of Hkv=%d", Hq, Hkv);
+  HMF_REQUIRE(lo >= 0 && hi > lo, "attention_bwd: bad window lo=%d hi=%d", lo, hi);
+  {
+    const long long rows = (long long)B * Tq * Hq;
+    const int rpw = 32 / (D / 8);
+    const long long warps = (rows + rpw - 1) / rpw;
+    const long long blocks = (warps + 7) / 8;
+    delta_kernel<<<(unsigned)blocks, 256, 0, stream>>>((const bf16*)o, (const bf16*)d_o, delta, B, Tq, Hq, D);
+    HMF_CHECK_CUDA(cudaGetLastError());
+  }
+  Params p;
+  p.lse = lse; p.delta = delta; p.q_pos = q_pos;
+  p.dq = (bf16*)dq; p.dk = (bf16*)dk; p.dv = (bf16*)dv;
+  p.B = B; p.Tq = Tq; p.Tk = Tk; p.Hq = Hq; p.Hkv = Hkv;
+  p.lo = lo; p.hi = hi; p.q_off = q_off;
+  p.scale = scale;
+  p.scale_log2 = scale * kLog2e;
+  p.status = status_ptr();
+  const long long qs[3] = {q_sb, q_st, q_sh}, ks[3] = {k_sb, k_st, k_sh}, vs[3] = {v_sb, v_st, v_sh};
+  if (D == 64) return launch_all<64>(q, k, v, d_o, p, qs, ks, vs, stream);
+  return launch_all<128>(q, k, v, d_o, p, qs, ks, vs, stream);
+}

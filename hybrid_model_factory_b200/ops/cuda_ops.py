@@ -386,3 +386,86 @@ def attention_fwd_raw(q: Tensor, k: Tensor, v: Tensor, scale: float, lo: int, hi
                                       *_bthd_strides(q), *_bthd_strides(k), *_bthd_strides(v), c_int(lo), c_int(hi),
                                       c_int(q_off), c_float(scale), _st(q)), "attention_fwd")
     return o, lse
+
+
+def attention_bwd_raw(q, k, v, o, do, lse, scale, lo, hi, q_off, q_pos=None):
+    """Launches delta + dQ + dK/dV kernels; returns ``(dq, dk, dv)`` (bf16, contiguous)."""
+    B, Tq, Hq, D = q.shape
+    Tk, Hkv = k.shape[1], k.shape[2]
+    q = q if _tma_ok(q) else q.contiguous()
+    k = k if _tma_ok(k) else k.contiguous()
+    v = v if _tma_ok(v) else v.contiguous()
+    o, do = o.contiguous(), do.contiguous()
+    dq = torch.empty(B, Tq, Hq, D, device=q.device, dtype=BF16)
+    dk = torch.empty(B, Tk, Hkv, D, device=q.device, dtype=BF16)
+    dv = torch.empty(B, Tk, Hkv, D, device=q.device, dtype=BF16)
+    delta = torch.empty(B, Hq, Tq, device=q.device, dtype=torch.float32)
+    if q_pos is not None:
+        q_pos = q_pos.to(torch.int32).contiguous()
+    _lib.check(_K().hmf_attention_bwd(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(o), _lib.ptr(do), _lib.ptr(lse),
+                                      _lib.ptr(delta), _lib.ptr(dq), _lib.ptr(dk), _lib.ptr(dv), _lib.ptr(q_pos),
+                                      c_int(B), c_int(Tq), c_int(Tk), c_int(Hq), c_int(Hkv), c_int(D),
+                                      *_bthd_strides(q), *_bthd_strides(k), *_bthd_strides(v), c_int(lo), c_int(hi),
+                                      c_int(q_off), c_float(scale), _st(q)), "attention_bwd")
+    _lib.add_launches(2)
+    return dq, dk, dv
+
+
+class _Attention(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, scale, lo, hi, q_off, q_pos):
+        o, lse = attention_fwd_raw(q, k, v, scale, lo, hi, q_off, q_pos)
+        ctx.save_for_backward(q, k, v, o, lse, q_pos)
+        ctx.cfg = (scale, lo, hi, q_off)
+        ctx.mark_non_differentiable(lse)
+        return o, lse
+
+    @staticmethod
+    def backward(ctx, do, _dlse):
+        q, k, v, o, lse, q_pos = ctx.saved_tensors
+        scale, lo, hi, q_off = ctx.cfg
+        dq, dk, dv = attention_bwd_raw(q, k, v, o, do, lse, scale, lo, hi, q_off, q_pos)
+        return dq, dk, dv, None, None, None, None, None
+
+
+def _contiguous_positions(pos: Optional[Tensor], n: int) -> Optional[int]:
+    """Offset ``c`` if ``pos[b, i] == i + c`` for every row, else ``None`` (host sync: small tensors only)."""
+    if pos is None:
+        return 0
+    first = pos[:, :1]
+    if bool((pos == first + torch.arange(n, device=pos.device)[None]).all()) and bool((first == first[0]).all()):
+        return int(first[0, 0])
+    return None
+
+
+def attention(q, k, v, *, scale=None, causal=True, window=None, hollow=None, q_pos=None, k_pos=None,
+              return_lse=False):
+    """Softmax attention on the tcgen05 kernels.  ``q_pos`` / ``k_pos`` follow the reference contract;
+    keys must sit at contiguous positions, queries either contiguous or ascending (query-sparse)."""
+    D = q.shape[-1]
+    if not _is_bf16(q, k, v) or D not in (64, 128):
+        return R.attention(q, k, v, scale=scale, causal=causal, window=window, hollow=hollow, q_pos=q_pos,
+                           k_pos=k_pos, return_lse=return_lse)
+    Tq, Tk = q.shape[1], k.shape[1]
+    scale = D ** -0.5 if scale is None else scale
+    lo, hi = _mask_bounds(causal, window, hollow)
+    k_off = _contiguous_positions(k_pos, Tk)
+    if k_off is None:
+        # keys at irregular positions (B'MOJO halo with padded negatives): shift is not expressible
+        return R.attention(q, k, v, scale=scale, causal=causal, window=window, hollow=hollow, q_pos=q_pos,
+                           k_pos=k_pos, return_lse=return_lse)
+    qp = None
+    if q_pos is None:
+        q_off = Tk - Tq
+    else:
+        c = _contiguous_positions(q_pos, Tq)
+        if c is not None:
+            q_off = c - k_off
+        else:
+            q_off, qp = 0, (q_pos - k_off)
+    o, lse = _Attention.apply(q, k, v, scale, lo, hi, q_off, qp)
+    return (o, lse) if return_lse else o
+
+
+def qsparse_attention(q, k, v, q_index, scale=None):
+    return attention(q, k, v, scale=scale, causal=True, q_pos=q_index)
