@@ -469,3 +469,38 @@ def attention(q, k, v, *, scale=None, causal=True, window=None, hollow=None, q_p
 
 def qsparse_attention(q, k, v, q_index, scale=None):
     return attention(q, k, v, scale=scale, causal=True, q_pos=q_index)
+
+
+# ----------------------------------------------------------------------------------------
+# scan cores (Gated DeltaNet, GKA, SSD)
+# ----------------------------------------------------------------------------------------
+from .scan import TorchScanCore  # noqa: E402
+
+
+def _gdn_state_shapes(inputs):
+    q, v = inputs[0], inputs[2]
+    return [((q.shape[0], q.shape[2], q.shape[3], v.shape[3]), torch.float32)]
+
+
+def GDNCore(scale=None, chunk_size=64, use_qk_l2norm=True, recurrent=False):
+    """Scan core of the gated delta rule on the GPU."""
+    from . import gdn_cuda
+    if gdn_cuda.available() and not recurrent and chunk_size == 64:
+        return gdn_cuda.GDNChunkCore(scale=scale, use_qk_l2norm=use_qk_l2norm)
+    fn = R.gated_delta_rule_recurrent if recurrent else R.gated_delta_rule_chunk
+    kw = dict(scale=scale, use_qk_l2norm=use_qk_l2norm)
+    if not recurrent:
+        kw["chunk_size"] = chunk_size
+    return TorchScanCore(fn, n_state=1, state_shape_fn=_gdn_state_shapes, **kw)
+
+
+def GKACore(scale=None, ridge_ratio=0.02, num_iter=30, chunk_size=64, recurrent=False):
+    from .mixers import _gka_ref, _gka_state_shapes
+    return TorchScanCore(_gka_ref, n_state=2, state_shape_fn=_gka_state_shapes, scale=scale, ridge_ratio=ridge_ratio,
+                         num_iter=num_iter, chunk_size=chunk_size, recurrent=recurrent)
+
+
+def SSDCore(chunk_size=256, recurrent=False):
+    from .mixers import _ssd_ref, _ssd_state_shapes
+    return TorchScanCore(_ssd_ref, n_state=1, state_shape_fn=_ssd_state_shapes, chunk_size=chunk_size,
+                         recurrent=recurrent)

@@ -1,0 +1,181 @@
+"""Chunked gated delta rule on the GPU.
+
+Pipeline of one segment (forward):
+  1. chunk-parallel preparation (``_prep``): L2 norms, cumulative gates, the WY factors
+     ``u = T (beta v)``, ``w = T (beta e^{G} k)`` with ``T = (I + tril(beta k k^T . decay))^{-1}``, the
+     causal intra-chunk score matrix ``P`` and the decayed keys / queries, packed as the bf16
+     operand tiles of the scan kernel;
+  2. ``hmf_gdn_scan_fwd`` (``csrc/kernels/gdn_scan.cu``): the sequential inter-chunk recurrence
+     *and* the output, on tcgen05 with the state in registers / tensor memory.
+Backward: ``hmf_gdn_scan_bwd`` runs the reverse recurrence for the state gradient; the gradients
+of the per-chunk factors are four batched products of saved tensors, and autograd carries them
+through the preparation graph to ``q, k, v, g, beta``.
+
+The preparation currently runs as batched PyTorch ops on the device.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from . import _lib
+from . import reference as R
+from .scan import ScanCore, TorchScanCore
+
+c_int, c_uint = ctypes.c_int, ctypes.c_uint
+BF16 = torch.bfloat16
+C = 64
+
+
+def available() -> bool:
+    if not _lib.kernels_available():
+        return False
+    return hasattr(_lib.kernels(), "hmf_gdn_scan_fwd")
+
+
+def _chunk(x: torch.Tensor, N: int) -> torch.Tensor:
+    """``[B, T, H, ...] -> [B*H, N, C, ...]`` (zero padded to ``N*C`` tokens)."""
+    B, T, H = x.shape[:3]
+    rest = x.shape[3:]
+    pad = N * C - T
+    if pad:
+        x = torch.cat([x, x.new_zeros(B, pad, H, *rest)], dim=1)
+    x = x.reshape(B, N, C, H, *rest)
+    perm = (0, 3, 1, 2) + tuple(range(4, 4 + len(rest)))
+    return x.permute(*perm).reshape(B * H, N, C, *rest)
+
+
+def _unchunk(x: torch.Tensor, B: int, H: int, T: int) -> torch.Tensor:
+    """Inverse of :func:`_chunk`: ``[B*H, N, C, ...] -> [B, T, H, ...]``."""
+    N = x.shape[1]
+    rest = x.shape[3:]
+    x = x.reshape(B, H, N, C, *rest)
+    perm = (0, 2, 3, 1) + tuple(range(4, 4 + len(rest)))
+    return x.permute(*perm).reshape(B, N * C, H, *rest)[:, :T]
+
+
+class GDNChunkCore(ScanCore):
+    n_state = 1
+
+    def __init__(self, scale: Optional[float] = None, use_qk_l2norm: bool = True):
+        self.scale, self.use_qk_l2norm = scale, use_qk_l2norm
+        self._fallback = TorchScanCore(R.gated_delta_rule_chunk, n_state=1, state_shape_fn=self.state_shapes,
+                                       scale=scale, use_qk_l2norm=use_qk_l2norm, chunk_size=C)
+        # sequence-parallel hooks filled in by parallel.peer.PeerStateTransport
+        self.peer = None
+
+    def state_shapes(self, inputs):
+        q, v = inputs[0], inputs[2]
+        return [((q.shape[0], q.shape[2], q.shape[3], v.shape[3]), torch.float32)]
+
+    @staticmethod
+    def _supported(q, k, v) -> bool:
+        return (q.is_cuda and q.dtype == BF16 and k.dtype == BF16 and v.dtype == BF16 and q.shape[-1] == 128
+                and v.shape[-1] == 128)
+
+    # -- chunk-parallel preparation ------------------------------------------------------
+    def _prep(self, q, k, v, g, beta):
+        B, T, H, Dk = q.shape
+        N = (T + C - 1) // C
+        scale = Dk ** -0.5 if self.scale is None else self.scale
+        qf, kf, vf = _chunk(q, N).float(), _chunk(k, N).float(), _chunk(v, N).float()
+        gc, bc = _chunk(g.float(), N), _chunk(beta.float(), N)
+        if self.use_qk_l2norm:
+            qf = qf * torch.rsqrt(qf.pow(2).sum(-1, keepdim=True) + 1e-6)
+            kf = kf * torch.rsqrt(kf.pow(2).sum(-1, keepdim=True) + 1e-6)
+        qf = qf * scale
+        G = gc.cumsum(-1)
+        glast = G[..., -1]
+        idx = torch.arange(C, device=q.device)
+        lower = idx[:, None] >= idx[None, :]
+        strict = idx[:, None] > idx[None, :]
+        diff = G[..., :, None] - G[..., None, :]
+        decay = torch.exp(diff.masked_fill(~lower, 0.0)) * lower
+        A = (bc[..., None] * (kf @ kf.transpose(-1, -2)) * decay) * strict
+        eye = torch.eye(C, device=q.device, dtype=torch.float32)
+        Tm = torch.linalg.solve_triangular(eye + A, eye.expand_as(A), upper=False)
+        u = Tm @ (vf * bc[..., None])
+        w = Tm @ (kf * (bc * torch.exp(G))[..., None])
+        P = (qf @ kf.transpose(-1, -2)) * decay
+        qt = qf * torch.exp(G)[..., None]
+        kt = kf * torch.exp(glast[..., None] - G)[..., None]
+        return {"w": w, "qt": qt, "kt": kt, "P": P, "u": u, "glast": glast, "N": N}
+
+    @staticmethod
+    def _pack(f):
+        wqT = torch.stack([f["w"].transpose(-1, -2), f["qt"].transpose(-1, -2)], dim=2).to(BF16).contiguous()
+        kPT = torch.cat([f["kt"].transpose(-1, -2), f["P"]], dim=-2).to(BF16).contiguous()
+        uT = f["u"].transpose(-1, -2).to(BF16).contiguous()
+        return wqT, kPT, uT, f["glast"].float().contiguous()
+
+    # -- ScanCore API ---------------------------------------------------------------------
+    def forward(self, inputs, state0):
+        q, k, v, g, beta = inputs
+        if not self._supported(q, k, v):
+            out, sT, saved, meta = self._fallback.forward(inputs, state0)
+            return out, sT, saved, ("fallback", meta)
+        B, T, H, Dk = q.shape
+        Dv = v.shape[-1]
+        need_bwd = any(t is not None and t.requires_grad for t in inputs) or (
+            state0 is not None and state0[0].requires_grad)
+        with torch.no_grad():
+            f = self._prep(q, k, v, g, beta)
+            wqT, kPT, uT, glast = self._pack(f)
+            N = f["N"]
+            del f
+            h0 = None if state0 is None else state0[0].float().contiguous()
+            o = torch.empty(B, T, H, Dv, device=q.device, dtype=BF16)
+            hT = torch.empty(B, H, Dk, Dv, device=q.device, dtype=torch.float32)
+            vnT = torch.empty(B * H, N, Dv, C, device=q.device, dtype=BF16) if need_bwd else None
+            h_all = torch.empty(B * H, N, Dv, Dk, device=q.device, dtype=BF16) if need_bwd else None
+            rc = _lib.kernels().hmf_gdn_scan_fwd(
+                _lib.ptr(wqT), _lib.ptr(kPT), _lib.ptr(uT), _lib.ptr(glast), _lib.ptr(h0), _lib.ptr(hT), _lib.ptr(o),
+                _lib.ptr(vnT), _lib.ptr(h_all), c_int(B), c_int(H), c_int(T), c_int(N), None, None, None, c_uint(0),
+                _lib.stream_ptr(q.device))
+            _lib.check(rc, "hmf_gdn_scan_fwd")
+        saved = [q, k, v, g, beta, h0, vnT, h_all]
+        return o, (hT,), saved, ("cuda", state0 is not None)
+
+    def backward(self, saved, meta, d_out, d_stateT):
+        kind, info = meta
+        if kind == "fallback":
+            return self._fallback.backward(saved, info, d_out, d_stateT)
+        q, k, v, g, beta, h0, vnT, h_all = saved
+        B, T, H, Dk = q.shape
+        Dv = v.shape[-1]
+        leaves = [t.detach().requires_grad_(True) for t in (q, k, v, g, beta)]
+        with torch.enable_grad():
+            f = self._prep(*leaves)
+        N = f["N"]
+        with torch.no_grad():
+            wqT, kPT, _, glast = self._pack(f)
+            do = d_out.to(BF16).contiguous()
+            dhT = None
+            if d_stateT is not None and d_stateT[0] is not None:
+                dhT = d_stateT[0].float().contiguous()
+            dh0 = torch.empty(B, H, Dk, Dv, device=q.device, dtype=torch.float32) if info else None
+            dvnT = torch.empty(B * H, N, Dv, C, device=q.device, dtype=BF16)
+            dS_all = torch.empty(B * H, N, Dv, Dk, device=q.device, dtype=BF16)
+            rc = _lib.kernels().hmf_gdn_scan_bwd(
+                _lib.ptr(wqT), _lib.ptr(kPT), _lib.ptr(do), _lib.ptr(glast), _lib.ptr(dhT), _lib.ptr(dh0),
+                _lib.ptr(dvnT), _lib.ptr(dS_all), c_int(B), c_int(H), c_int(T), c_int(N), None, None, None, c_uint(0),
+                _lib.stream_ptr(q.device))
+            _lib.check(rc, "hmf_gdn_scan_bwd")
+            del wqT, kPT
+            # gradients of the per-chunk factors (batched over all chunks)
+            do_c = _chunk(do, N)                      # [BH, N, C, Dv]
+            dvn = dvnT.transpose(-1, -2)              # [BH, N, C, Dv]
+            vn = vnT.transpose(-1, -2)
+            d_u = dvn.float()
+            d_w = -(dvn @ h_all).float()              # [C, Dv] @ [Dv, Dk]
+            d_qt = (do_c @ h_all).float()
+            d_P = torch.tril((do_c @ vnT).float())
+            d_kt = (vn @ dS_all).float()
+            d_gl = torch.exp(glast) * (dS_all.float() * h_all.float()).sum((-1, -2))
+        torch.autograd.backward([f["w"], f["qt"], f["kt"], f["P"], f["u"], f["glast"]],
+                                [d_w, d_qt, d_kt, d_P, d_u, d_gl])
+        d_inputs = [leaves[0].grad.to(q.dtype), leaves[1].grad.to(k.dtype), leaves[2].grad.to(v.dtype),
+                    leaves[3].grad.to(g.dtype), leaves[4].grad.to(beta.dtype)]
+        return d_inputs, (None if dh0 is None else (dh0,))

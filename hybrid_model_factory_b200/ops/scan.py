@@ -4,8 +4,8 @@ Every SSM-style mixer of the framework (Gated DeltaNet, Gated KalmaNet's two sta
 SSD) is expressed as a *scan core*: a function of per-token inputs and an incoming recurrent
 state that returns per-token outputs and the outgoing state,
 
-    ``core.forward(inputs, state0) -> (out, stateT, saved)``
-    ``core.backward(saved, d_out, d_stateT) -> (d_inputs, d_state0)``
+    ``core.forward(inputs, state0) -> (out, stateT, tensors_to_save, meta)``
+    ``core.backward(saved_tensors, meta, d_out, d_stateT) -> (d_inputs, d_state0)``
 
 :func:`ssm_scan` turns a core into one autograd node.  Without sequence parallelism it is a
 plain call.  With a sequence-parallel context the local tokens are the two zig-zag segments
@@ -37,9 +37,11 @@ class ScanCore:
     n_state: int = 1
 
     def forward(self, inputs: Sequence[Tensor], state0: State):
+        """-> ``(out, stateT, tensors_to_save, meta)``"""
         raise NotImplementedError
 
-    def backward(self, saved, d_out: Tensor, d_stateT: State):
+    def backward(self, saved, meta, d_out: Tensor, d_stateT: State):
+        """-> ``(d_inputs, d_state0)``"""
         raise NotImplementedError
 
     def state_shapes(self, inputs: Sequence[Tensor]):
@@ -48,7 +50,9 @@ class ScanCore:
 
 class TorchScanCore(ScanCore):
     """Wraps a differentiable PyTorch function ``fn(*inputs, initial_state=...) -> (out, state)``.
-    The forward pass keeps the autograd graph of the segment; backward differentiates it."""
+    Forward runs without building a graph and saves only the segment inputs (through
+    ``save_for_backward``, so activation checkpointing can drop them); backward re-evaluates the
+    function with autograd enabled and differentiates it."""
 
     def __init__(self, fn: Callable, n_state: int = 1, state_shape_fn: Optional[Callable] = None, **kwargs):
         self.fn = fn
@@ -60,18 +64,25 @@ class TorchScanCore(ScanCore):
         """``[(shape, dtype), ...]`` of the recurrent state for segment inputs ``inputs``."""
         return self.state_shape_fn(inputs)
 
-    def forward(self, inputs, state0):
-        leaves = [t.detach().requires_grad_(t.is_floating_point()) if t is not None else None for t in inputs]
-        s0 = None if state0 is None else tuple(s.detach().requires_grad_(True) for s in state0)
-        with torch.enable_grad():
-            init = None if s0 is None else (s0[0] if self.n_state == 1 else s0)
-            out, sT = self.fn(*leaves, initial_state=init, **self.kwargs)
-            sT = (sT,) if self.n_state == 1 else tuple(sT)
-        saved = (leaves, s0, out, sT)
-        return out.detach(), tuple(s.detach() if s is not None else None for s in sT), saved
+    def _run(self, inputs, s0):
+        init = None if s0 is None else (s0[0] if self.n_state == 1 else s0)
+        out, sT = self.fn(*inputs, initial_state=init, **self.kwargs)
+        sT = (sT,) if self.n_state == 1 else tuple(sT)
+        return out, sT
 
-    def backward(self, saved, d_out, d_stateT):
-        leaves, s0, out, sT = saved
+    def forward(self, inputs, state0):
+        with torch.no_grad():
+            out, sT = self._run(list(inputs), state0)
+        saved = list(inputs) + (list(state0) if state0 is not None else [])
+        meta = (len(inputs), 0 if state0 is None else len(state0))
+        return out, tuple(sT), saved, meta
+
+    def backward(self, saved, meta, d_out, d_stateT):
+        n_in, n_st = meta
+        leaves = [t.detach().requires_grad_(t.is_floating_point()) if t is not None else None for t in saved[:n_in]]
+        s0 = tuple(s.detach().requires_grad_(True) for s in saved[n_in:n_in + n_st]) if n_st else None
+        with torch.enable_grad():
+            out, sT = self._run(leaves, s0)
         outs, grads = [out], [d_out.to(out.dtype)]
         if d_stateT is not None:
             for s, ds in zip(sT, d_stateT):
@@ -79,8 +90,7 @@ class TorchScanCore(ScanCore):
                     outs.append(s)
                     grads.append(ds.to(s.dtype))
         wrt = [t for t in leaves if t is not None and t.requires_grad] + list(s0 or [])
-        g = torch.autograd.grad(outs, wrt, grads, allow_unused=True)
-        g = list(g)
+        g = list(torch.autograd.grad(outs, wrt, grads, allow_unused=True))
         d_inputs = []
         for t in leaves:
             if t is not None and t.requires_grad:
@@ -101,10 +111,6 @@ def _split_time(t: Optional[Tensor]):
     return t[:, :half], t[:, half:]
 
 
-def _zeros_like_state(state: State) -> State:
-    return None if state is None else tuple(torch.zeros_like(s) for s in state)
-
-
 class _SSMScan(torch.autograd.Function):
     @staticmethod
     def forward(ctx, core: ScanCore, sp, n_inputs: int, want_state: bool, *tensors):
@@ -113,10 +119,10 @@ class _SSMScan(torch.autograd.Function):
         state0 = tuple(state0) if len(state0) else None
         ctx.core, ctx.sp, ctx.n_inputs, ctx.n_state0 = core, sp, n_inputs, 0 if state0 is None else len(state0)
         if sp is None or sp.size == 1:
-            out, sT, saved = core.forward(inputs, state0)
-            ctx.saved = [saved]
-            ctx.mark_non_differentiable(*[])
-            ctx.state_templates = sT
+            out, sT, saved, meta = core.forward(inputs, state0)
+            ctx.save_for_backward(*saved)
+            ctx.counts, ctx.metas = [len(saved)], [meta]
+            ctx.state_templates = tuple((s.shape, s.dtype) if s is not None else None for s in sT)
             return (out, *[s if s is not None else out.new_zeros(()) for s in sT])
         # --- sequence-parallel zig-zag chain -------------------------------------------------
         r, n = sp.rank, sp.size
@@ -127,18 +133,18 @@ class _SSMScan(torch.autograd.Function):
             h0 = tr.recv_state(core, list(seg_a), src=r - 1, tag="fwd_a")
         else:
             h0 = state0
-        out_a, sT_a, saved_a = core.forward(list(seg_a), h0)
+        out_a, sT_a, saved_a, meta_a = core.forward(list(seg_a), h0)
         if r < n - 1:
             tr.send_state(sT_a, dst=r + 1, tag="fwd_a")
             h0b = tr.recv_state(core, list(seg_b), src=r + 1, tag="fwd_b")
         else:
             h0b = sT_a
-        out_b, sT_b, saved_b = core.forward(list(seg_b), h0b)
+        out_b, sT_b, saved_b, meta_b = core.forward(list(seg_b), h0b)
         if r > 0:
             tr.send_state(sT_b, dst=r - 1, tag="fwd_b")
-        ctx.saved = [saved_a, saved_b]
-        ctx.had_h0_a = h0 is not None
-        ctx.state_templates = sT_b
+        ctx.save_for_backward(*saved_a, *saved_b)
+        ctx.counts, ctx.metas = [len(saved_a), len(saved_b)], [meta_a, meta_b]
+        ctx.state_templates = tuple((s.shape, s.dtype) if s is not None else None for s in sT_b)
         out = torch.cat([out_a, out_b], dim=1)
         return (out, *[s if s is not None else out.new_zeros(()) for s in sT_b])
 
@@ -148,27 +154,29 @@ class _SSMScan(torch.autograd.Function):
         d_state = tuple(d_state) if len(d_state) else None
         if d_state is not None and all(ds is None for ds in d_state):
             d_state = None
+        saved_all = list(ctx.saved_tensors)
         if sp is None or sp.size == 1:
-            d_inputs, d_s0 = core.backward(ctx.saved[0], d_out, d_state)
+            d_inputs, d_s0 = core.backward(saved_all, ctx.metas[0], d_out, d_state)
             grads = list(d_inputs) + (list(d_s0) if (d_s0 is not None and ctx.n_state0) else [None] * ctx.n_state0)
             return (None, None, None, None, *grads)
         r, n = sp.rank, sp.size
         tr = sp.transport
         half = d_out.shape[1] // 2
         d_a, d_b = d_out[:, :half], d_out[:, half:]
-        saved_a, saved_b = ctx.saved
+        saved_a, saved_b = saved_all[:ctx.counts[0]], saved_all[ctx.counts[0]:]
+        device = d_out.device
         # second segments first: chain 0 -> n-1 (reverse of the forward chain n-1 -> 0)
         if r > 0:
-            dhT_b = tr.recv_state_like(ctx.state_templates, src=r - 1, tag="bwd_b")
+            dhT_b = tr.recv_state_like(ctx.state_templates, device, src=r - 1, tag="bwd_b")
         else:
             dhT_b = d_state
-        d_in_b, d_h0b = core.backward(saved_b, d_b, dhT_b)
+        d_in_b, d_h0b = core.backward(saved_b, ctx.metas[1], d_b, dhT_b)
         if r < n - 1:
             tr.send_state(d_h0b, dst=r + 1, tag="bwd_b")
-            dhT_a = tr.recv_state_like(ctx.state_templates, src=r + 1, tag="bwd_a")
+            dhT_a = tr.recv_state_like(ctx.state_templates, device, src=r + 1, tag="bwd_a")
         else:
             dhT_a = d_h0b
-        d_in_a, d_h0a = core.backward(saved_a, d_a, dhT_a)
+        d_in_a, d_h0a = core.backward(saved_a, ctx.metas[0], d_a, dhT_a)
         if r > 0:
             tr.send_state(d_h0a, dst=r - 1, tag="bwd_a")
         d_inputs = []

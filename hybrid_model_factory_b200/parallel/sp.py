@@ -102,13 +102,14 @@ class StateTransport:
             out.append(buf)
         return tuple(out)
 
-    def recv_state_like(self, templates, src: int, tag: str = ""):
+    def recv_state_like(self, templates, device, src: int, tag: str = ""):
+        """``templates``: ``(shape, dtype)`` per state tensor (``None`` for absent ones)."""
         out = []
         for t in templates:
-            if t is None or t.dim() == 0:
+            if t is None or len(t[0]) == 0:
                 out.append(None)
                 continue
-            buf = torch.empty_like(t)
+            buf = torch.empty(t[0], dtype=t[1], device=device)
             dist.recv(buf, src=self._global(src), group=self.group)
             out.append(buf)
         return tuple(out)

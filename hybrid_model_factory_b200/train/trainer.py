@@ -1,0 +1,186 @@
+"""Training loop (own loop, no HF Trainer): bf16 parameters in a flat buffer, fused AdamW with
+ZeRO sharding over all ranks, sequence-parallel loss reduction, per-layer activation
+checkpointing, gradient accumulation, LR schedules, jsonl progress log, checkpoint save/resume.
+
+One optimizer step over a batch is ``Trainer.train_step(batch)``: the batch is a dict of CPU
+tensors (ideally pinned) holding this rank's shard (``input_ids``, ``labels``, ``position_ids``);
+the method copies it to the device, runs forward/backward (micro-batches when
+``gradient_accumulation_steps > 1``), steps the optimizer and returns the loss as a device tensor.
+
+Reference behaviour: ``train/pt/trainer.py:46-195`` (SP sampler + loss), ``train/tuner.py:58-99``,
+``train/trainer_utils.py:80-122`` (sharded save), ``train/callbacks.py:267-355`` (progress log).
+"""
+from __future__ import annotations
+
+import json
+import os
+import time
+from dataclasses import asdict, dataclass, field
+from typing import Callable, Dict, Iterable, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..parallel.sp import SPContext, init_sp_group, set_sequence_parallel_group_recursive
+from .optimizer import FlatAdamW, get_lr
+
+
+@dataclass
+class TrainingArguments:
+    output_dir: str = "output"
+    learning_rate: float = 1e-5
+    weight_decay: float = 0.0
+    adam_beta1: float = 0.9
+    adam_beta2: float = 0.999
+    adam_epsilon: float = 1e-8
+    max_grad_norm: float = 1.0
+    lr_scheduler_type: str = "cosine"
+    warmup_steps: int = 0
+    max_steps: int = 100
+    per_device_train_batch_size: int = 1
+    gradient_accumulation_steps: int = 1
+    sequence_parallel_size: int = 1
+    sequence_parallel_mode: str = "zigzag-ring"
+    bf16: bool = True
+    pure_bf16: bool = True
+    disable_gradient_checkpointing: bool = False
+    logging_steps: int = 1
+    save_steps: int = 0
+    save_only_model: bool = False
+    save_max_shard_size: str = "5GB"
+    seed: int = 42
+    resume_from_checkpoint: Optional[str] = None
+    optimizer_state_dtype: str = "auto"   # auto = parameter dtype (bf16 under pure_bf16), or float32
+    master_weights: bool = False
+    ddp_timeout: int = 1800
+
+    def to_dict(self):
+        return asdict(self)
+
+
+class Trainer:
+    def __init__(self, model: torch.nn.Module, args: TrainingArguments, device: Optional[torch.device] = None,
+                 loss_fn: Optional[Callable] = None, trainable: Optional[Iterable[torch.nn.Parameter]] = None,
+                 callbacks: Optional[list] = None):
+        self.model, self.args = model, args
+        self.device = device or next(model.parameters()).device
+        self.loss_fn = loss_fn
+        self.callbacks = callbacks or []
+        self.world = dist.get_world_size() if dist.is_initialized() else 1
+        self.rank = dist.get_rank() if dist.is_initialized() else 0
+        sp_size = max(1, args.sequence_parallel_size)
+        self.sp: Optional[SPContext] = init_sp_group(sp_size) if (sp_size > 1 and dist.is_initialized()) else None
+        set_sequence_parallel_group_recursive(model, self.sp)
+        self.dp_size = self.world // sp_size
+        if not args.disable_gradient_checkpointing and hasattr(model, "gradient_checkpointing_enable"):
+            model.gradient_checkpointing_enable()
+        params = list(trainable) if trainable is not None else [p for p in model.parameters() if p.requires_grad]
+        sdt = None if args.optimizer_state_dtype == "auto" else getattr(torch, args.optimizer_state_dtype)
+        self.optimizer = FlatAdamW(params, lr=args.learning_rate, betas=(args.adam_beta1, args.adam_beta2),
+                                   eps=args.adam_epsilon, weight_decay=args.weight_decay,
+                                   max_grad_norm=args.max_grad_norm, group=None, dp_size=self.dp_size,
+                                   state_dtype=sdt, master_weights=args.master_weights)
+        self.global_step = 0
+        self.tokens_seen = 0
+        self._t0 = time.time()
+        self._log_file = None
+        if self.rank == 0 and args.output_dir:
+            os.makedirs(args.output_dir, exist_ok=True)
+            self._log_file = os.path.join(args.output_dir, "trainer_log.jsonl")
+        if args.resume_from_checkpoint:
+            self.load_checkpoint(args.resume_from_checkpoint)
+
+    # -- one optimizer step -----------------------------------------------------------------
+    def _to_device(self, batch: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
+        return {k: (v.to(self.device, non_blocking=True) if isinstance(v, torch.Tensor) else v) for k, v in batch.items()}
+
+    def compute_loss(self, batch: Dict[str, torch.Tensor]) -> torch.Tensor:
+        if self.loss_fn is not None:
+            return self.loss_fn(self.model, batch)
+        out = self.model(input_ids=batch["input_ids"], labels=batch["labels"], position_ids=batch.get("position_ids"),
+                         labels_shifted=bool(batch.get("labels_shifted", self.sp is not None)))
+        return out.loss
+
+    def train_step(self, batch: Dict[str, torch.Tensor]) -> torch.Tensor:
+        self.model.train()
+        ga = max(1, self.args.gradient_accumulation_steps)
+        self.optimizer.zero_grad()
+        dev = self._to_device(batch)
+        total = None
+        bsz = dev["input_ids"].shape[0]
+        micro = max(1, bsz // ga)
+        for i in range(0, bsz, micro):
+            mb = {k: (v[i:i + micro] if isinstance(v, torch.Tensor) and v.dim() > 0 and v.shape[0] == bsz else v)
+                  for k, v in dev.items()}
+            loss = self.compute_loss(mb) * (micro / bsz)
+            loss.backward()
+            total = loss.detach() if total is None else total + loss.detach()
+        lr = get_lr(self.args.lr_scheduler_type, self.global_step, self.args.learning_rate, self.args.warmup_steps,
+                    self.args.max_steps)
+        self.optimizer.step(lr)
+        self.global_step += 1
+        self.tokens_seen += int(dev["input_ids"].numel()) * self.world
+        self._last_lr = lr
+        return total
+
+    # -- loop ---------------------------------------------------------------------------------
+    def train(self, batches: Iterable[Dict[str, torch.Tensor]]) -> None:
+        for batch in batches:
+            if self.global_step >= self.args.max_steps:
+                break
+            loss = self.train_step(batch)
+            if self.args.logging_steps and self.global_step % self.args.logging_steps == 0:
+                self.log({"loss": float(loss.item()), "lr": self._last_lr})
+            for cb in self.callbacks:
+                cb(self)
+            if self.args.save_steps and self.global_step % self.args.save_steps == 0:
+                self.save_checkpoint(os.path.join(self.args.output_dir, f"checkpoint-{self.global_step}"))
+
+    def log(self, values: dict) -> None:
+        elapsed = time.time() - self._t0
+        rec = {"current_steps": self.global_step, "total_steps": self.args.max_steps, "elapsed_time": round(elapsed, 2),
+               "throughput": round(self.tokens_seen / max(elapsed, 1e-9), 2), **values}
+        if os.environ.get("RECORD_VRAM", "0") == "1" and torch.cuda.is_available():
+            rec["vram_reserved_gb"] = round(torch.cuda.max_memory_reserved() / 2 ** 30, 2)
+        if self.rank == 0 and self._log_file:
+            with open(self._log_file, "a") as f:
+                f.write(json.dumps(rec) + "\n")
+
+    # -- checkpoints --------------------------------------------------------------------------
+    def save_checkpoint(self, path: str) -> None:
+        from ..utils.checkpoint_io import save_pretrained
+        if self.rank == 0:
+            save_pretrained(self.model, path, max_shard_size=self.args.save_max_shard_size)
+            with open(os.path.join(path, "trainer_state.json"), "w") as f:
+                json.dump({"global_step": self.global_step, "tokens_seen": self.tokens_seen,
+                           "args": self.args.to_dict()}, f, indent=2)
+        if not self.args.save_only_model:
+            os.makedirs(path, exist_ok=True)
+            torch.save(self.optimizer.state_dict(), os.path.join(path, f"optimizer_rank{self.rank:05d}.pt"))
+        if dist.is_initialized():
+            dist.barrier()
+
+    def load_checkpoint(self, path: str) -> None:
+        from ..utils.checkpoint_io import load_state_dict_into
+        load_state_dict_into(self.model, path)
+        st = os.path.join(path, "trainer_state.json")
+        if os.path.exists(st):
+            with open(st) as f:
+                s = json.load(f)
+            self.global_step, self.tokens_seen = int(s["global_step"]), int(s["tokens_seen"])
+        opt = os.path.join(path, f"optimizer_rank{self.rank:05d}.pt")
+        if os.path.exists(opt):
+            self.optimizer.load_state_dict(torch.load(opt, map_location=self.device))
+
+
+def get_last_checkpoint(output_dir: str) -> Optional[str]:
+    """Latest ``checkpoint-<step>`` directory (auto-resume, reference: ``hparams/parser.py:383-399``)."""
+    if not os.path.isdir(output_dir):
+        return None
+    best, best_step = None, -1
+    for name in os.listdir(output_dir):
+        if name.startswith("checkpoint-") and name.split("-")[-1].isdigit():
+            s = int(name.split("-")[-1])
+            if s > best_step:
+                best, best_step = os.path.join(output_dir, name), s
+    return best
