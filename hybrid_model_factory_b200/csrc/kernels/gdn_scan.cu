@@ -364,16 +364,17 @@ gdn_scan_bwd_kernel(const __grid_constant__ CUtensorMap tmWQ, const __grid_const
         for (int kk = 0; kk < C / 16; ++kk)
           umma_ss(tDA, make_desc_mnmajor_sw128(aDO + kk * 2048, DO_BYTES / 2),
                   make_desc_mnmajor_sw128(aKP + DK * 128 + kk * 2048, C * 128), idescA, kk > 0 ? 1u : 0u);
-#pragma unroll
-        for (int kk = 0; kk < C / 16; ++kk)
-          umma_ss(tDC, make_desc_mnmajor_sw128(aDO + kk * 2048, DO_BYTES / 2),
-                  make_desc_kmajor_sw128(aWQ + DK * 128 + kk * 32), idescC, kk > 0 ? 1u : 0u);
+        // s_ready also tells that the threads have finished reading the previous dS^T accumulator
         mbar_wait(s_ready, it & 1, ctx, 0x430);
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < DK / 16; ++kk)
           umma_ts(tDA, tAs + kk * 8, make_desc_mnmajor_sw128(aKP + kk * 2048, DK * 128), idescB, 1u);
         umma_commit(da_full);
+#pragma unroll
+        for (int kk = 0; kk < C / 16; ++kk)
+          umma_ss(tDC, make_desc_mnmajor_sw128(aDO + kk * 2048, DO_BYTES / 2),
+                  make_desc_kmajor_sw128(aWQ + DK * 128 + kk * 32), idescC, kk > 0 ? 1u : 0u);
         mbar_wait(dv_ready, it & 1, ctx, 0x440);
         tc_fence_after();
 #pragma unroll
