@@ -36,6 +36,7 @@ static EncodeTiledFn get_encode_fn() {
   std::call_once(once, []() {
     void* p = nullptr;
     cudaDriverEntryPointQueryResult q;
+    cudaFree(0);  // make sure this runtime instance is attached to the device's primary context
     cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q);
     if (e == cudaSuccess && q == cudaDriverEntryPointSuccess) fn = (EncodeTiledFn)p;
   });
@@ -101,9 +102,12 @@ int make_tensor_map(CUtensorMap* out, const void* base, int elem, int rank, cons
                   CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
-    set_last_error("cuTensorMapEncodeTiled failed with %d (rank %d, dims %llu,%llu box %u,%u)",
-                   (int)r, rank, (unsigned long long)dims[0],
-                   (unsigned long long)(rank > 1 ? dims[1] : 0), box[0], rank > 1 ? box[1] : 0);
+    char buf[256];
+    int n = 0;
+    for (int i = 0; i < rank && n < 200; ++i)
+      n += snprintf(buf + n, sizeof(buf) - n, " d%d=%llu/s%llu/b%u", i, (unsigned long long)dims[i],
+                    (unsigned long long)(i > 0 ? strides_bytes[i] : 0), box[i]);
+    set_last_error("cuTensorMapEncodeTiled failed with %d (base %p rank %d:%s)", (int)r, base, rank, buf);
     return HMF_ERR_CUDA;
   }
   return HMF_OK;
@@ -162,6 +166,15 @@ HMF_API int hmf_read_status(unsigned int* out, int reset, cudaStream_t stream) {
   HMF_CHECK_CUDA(cudaStreamSynchronize(stream));
   HMF_CHECK_CUDA(cudaMemcpy(out, p, 4 * sizeof(unsigned int), cudaMemcpyDeviceToHost));
   if (reset) HMF_CHECK_CUDA(cudaMemset(p, 0, 4 * sizeof(unsigned int)));
+  return HMF_OK;
+}
+
+// Binds the calling host thread to a device in this library's runtime instance (and makes that
+// device's primary context current).  Needed once per thread that launches kernels, e.g. the
+// autograd worker threads, which otherwise have no current context.
+HMF_API int hmf_set_device(int index) {
+  HMF_CHECK_CUDA(cudaSetDevice(index));
+  HMF_CHECK_CUDA(cudaFree(0));
   return HMF_OK;
 }
 

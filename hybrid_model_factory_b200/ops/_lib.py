@@ -10,6 +10,7 @@ from __future__ import annotations
 
 import ctypes
 import os
+import threading
 from pathlib import Path
 
 import torch
@@ -74,7 +75,22 @@ def runtime() -> ctypes.CDLL:
     return _runtime
 
 
+_thread_state = threading.local()
+
+
+def bind_thread(device=None) -> None:
+    """Makes ``device`` current for the native library on the calling thread (once per thread and
+    device).  Autograd worker threads start without a current CUDA context."""
+    idx = torch.cuda.current_device() if device is None or device.index is None else device.index
+    if getattr(_thread_state, "device", None) != idx:
+        rc = kernels().hmf_set_device(ctypes.c_int(idx))
+        if rc != 0:
+            raise KernelError(kernels().hmf_last_error().decode(errors="replace"))
+        _thread_state.device = idx
+
+
 def stream_ptr(device=None) -> ctypes.c_void_p:
+    bind_thread(device)
     return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
 
 

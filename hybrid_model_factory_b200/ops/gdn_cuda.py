@@ -25,8 +25,12 @@ from . import reference as R
 from .scan import ScanCore, TorchScanCore
 
 c_int, c_uint = ctypes.c_int, ctypes.c_uint
+import os
+
 BF16 = torch.bfloat16
 C = 64
+# debugging aid: evaluate the chunk preparation with batched PyTorch ops instead of the CUDA kernel
+_FORCE_TORCH_PREP = os.environ.get("HMF_GDN_TORCH_PREP", "0") == "1"
 
 
 def available() -> bool:
@@ -111,6 +115,53 @@ class GDNChunkCore(ScanCore):
         return wqT, kPT, uT, f["glast"].float().contiguous()
 
     # -- ScanCore API ---------------------------------------------------------------------
+    @staticmethod
+    def _head_groups(B, T, H):
+        """Head slices such that one fp32 ``[B, T, hs, 128]`` intermediate stays near 256 MB."""
+        per_head = B * T * 128 * 4
+        g = max(1, min(H, (256 << 20) // max(per_head, 1)))
+        return [slice(i, min(H, i + g)) for i in range(0, H, g)]
+
+    def _packed_buffers(self, B, H, N, Dk, Dv, device):
+        wqT = torch.empty(B, H, N, 2, Dk, C, device=device, dtype=BF16)
+        kPT = torch.empty(B, H, N, Dk + C, C, device=device, dtype=BF16)
+        uT = torch.empty(B, H, N, Dv, C, device=device, dtype=BF16)
+        glast = torch.empty(B, H, N, device=device, dtype=torch.float32)
+        return wqT, kPT, uT, glast
+
+    def _prep_packed(self, q, k, v, g, beta, want_u=True):
+        """Runs the preparation head group by head group and returns the packed operand tiles."""
+        B, T, H, Dk = q.shape
+        Dv = v.shape[-1]
+        N = (T + C - 1) // C
+        wqT, kPT, uT, glast = self._packed_buffers(B, H, N, Dk, Dv, q.device)
+        if hasattr(_lib.kernels(), "hmf_gdn_prep") and not _FORCE_TORCH_PREP:
+            def tma_ok(t):
+                return t.stride(3) == 1 and t.data_ptr() % 16 == 0 and all(s % 8 == 0 for s in t.stride()[:3])
+            q, k, v = (t if tma_ok(t) else t.contiguous() for t in (q, k, v))
+            scale = Dk ** -0.5 if self.scale is None else self.scale
+            ll = ctypes.c_longlong
+            rc = _lib.kernels().hmf_gdn_prep(
+                _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(g.float().contiguous()),
+                _lib.ptr(beta.float().contiguous()), _lib.ptr(wqT), _lib.ptr(kPT), _lib.ptr(uT), _lib.ptr(glast),
+                c_int(B), c_int(T), c_int(H), c_int(k.shape[2]), c_int(v.shape[2]), c_int(N),
+                ll(q.stride(0)), ll(q.stride(1)), ll(q.stride(2)), ll(k.stride(0)), ll(k.stride(1)), ll(k.stride(2)),
+                ll(v.stride(0)), ll(v.stride(1)), ll(v.stride(2)), ctypes.c_float(scale),
+                c_int(int(self.use_qk_l2norm)), _lib.stream_ptr(q.device))
+            _lib.check(rc, "hmf_gdn_prep")
+            return wqT, kPT, uT, glast, N
+        for hs in self._head_groups(B, T, H):
+            f = self._prep(q[:, :, hs], k[:, :, hs], v[:, :, hs], g[:, :, hs], beta[:, :, hs])
+            a, b_, c_, d_ = self._pack(f)
+            nh = hs.stop - hs.start
+            wqT[:, hs] = a.view(B, nh, N, 2, Dk, C)
+            kPT[:, hs] = b_.view(B, nh, N, Dk + C, C)
+            if want_u:
+                uT[:, hs] = c_.view(B, nh, N, Dv, C)
+            glast[:, hs] = d_.view(B, nh, N)
+            del f, a, b_, c_, d_
+        return wqT, kPT, uT, glast, N
+
     def forward(self, inputs, state0):
         q, k, v, g, beta = inputs
         if not self._supported(q, k, v):
@@ -121,10 +172,7 @@ class GDNChunkCore(ScanCore):
         need_bwd = any(t is not None and t.requires_grad for t in inputs) or (
             state0 is not None and state0[0].requires_grad)
         with torch.no_grad():
-            f = self._prep(q, k, v, g, beta)
-            wqT, kPT, uT, glast = self._pack(f)
-            N = f["N"]
-            del f
+            wqT, kPT, uT, glast, N = self._prep_packed(q, k, v, g, beta)
             h0 = None if state0 is None else state0[0].float().contiguous()
             o = torch.empty(B, T, H, Dv, device=q.device, dtype=BF16)
             hT = torch.empty(B, H, Dk, Dv, device=q.device, dtype=torch.float32)
@@ -145,12 +193,8 @@ class GDNChunkCore(ScanCore):
         q, k, v, g, beta, h0, vnT, h_all = saved
         B, T, H, Dk = q.shape
         Dv = v.shape[-1]
-        leaves = [t.detach().requires_grad_(True) for t in (q, k, v, g, beta)]
-        with torch.enable_grad():
-            f = self._prep(*leaves)
-        N = f["N"]
         with torch.no_grad():
-            wqT, kPT, _, glast = self._pack(f)
+            wqT, kPT, _, glast, N = self._prep_packed(q, k, v, g, beta, want_u=False)
             do = d_out.to(BF16).contiguous()
             dhT = None
             if d_stateT is not None and d_stateT[0] is not None:
@@ -164,18 +208,32 @@ class GDNChunkCore(ScanCore):
                 _lib.stream_ptr(q.device))
             _lib.check(rc, "hmf_gdn_scan_bwd")
             del wqT, kPT
-            # gradients of the per-chunk factors (batched over all chunks)
-            do_c = _chunk(do, N)                      # [BH, N, C, Dv]
-            dvn = dvnT.transpose(-1, -2)              # [BH, N, C, Dv]
-            vn = vnT.transpose(-1, -2)
-            d_u = dvn.float()
-            d_w = -(dvn @ h_all).float()              # [C, Dv] @ [Dv, Dk]
-            d_qt = (do_c @ h_all).float()
-            d_P = torch.tril((do_c @ vnT).float())
-            d_kt = (vn @ dS_all).float()
-            d_gl = torch.exp(glast) * (dS_all.float() * h_all.float()).sum((-1, -2))
-        torch.autograd.backward([f["w"], f["qt"], f["kt"], f["P"], f["u"], f["glast"]],
-                                [d_w, d_qt, d_kt, d_P, d_u, d_gl])
-        d_inputs = [leaves[0].grad.to(q.dtype), leaves[1].grad.to(k.dtype), leaves[2].grad.to(v.dtype),
-                    leaves[3].grad.to(g.dtype), leaves[4].grad.to(beta.dtype)]
-        return d_inputs, (None if dh0 is None else (dh0,))
+            dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+            dg, dbeta = torch.empty_like(g), torch.empty_like(beta)
+            vn5, h5 = vnT.view(B, H, N, Dv, C), h_all.view(B, H, N, Dv, Dk)
+            dvn5, dS5 = dvnT.view(B, H, N, Dv, C), dS_all.view(B, H, N, Dv, Dk)
+            gl5 = glast.view(B, H, N)
+        # gradients of the per-chunk factors, then autograd through the preparation, per head group
+        for hs in self._head_groups(B, T, H):
+            nh = hs.stop - hs.start
+            leaves = [t[:, :, hs].detach().requires_grad_(True) for t in (q, k, v, g, beta)]
+            with torch.enable_grad():
+                f = self._prep(*leaves)
+            with torch.no_grad():
+                flat = lambda t: t[:, hs].reshape(B * nh, *t.shape[2:])  # noqa: E731
+                vnT_g, h_g, dvnT_g, dS_g = flat(vn5), flat(h5), flat(dvn5), flat(dS5)
+                do_c = _chunk(do[:, :, hs], N)               # [b*nh, N, C, Dv]
+                dvn = dvnT_g.transpose(-1, -2)
+                d_u = dvn.float()
+                d_w = -(dvn @ h_g).float()                   # [C, Dv] @ [Dv, Dk]
+                d_qt = (do_c @ h_g).float()
+                d_P = torch.tril((do_c @ vnT_g).float())
+                d_kt = (vnT_g.transpose(-1, -2) @ dS_g).float()
+                d_gl = torch.exp(flat(gl5)) * (dS_g.float() * h_g.float()).sum((-1, -2))
+            torch.autograd.backward([f["w"], f["qt"], f["kt"], f["P"], f["u"], f["glast"]],
+                                    [d_w, d_qt, d_kt, d_P, d_u, d_gl])
+            with torch.no_grad():
+                dq[:, :, hs], dk[:, :, hs], dv[:, :, hs] = leaves[0].grad, leaves[1].grad, leaves[2].grad
+                dg[:, :, hs], dbeta[:, :, hs] = leaves[3].grad, leaves[4].grad
+            del f, leaves
+        return [dq, dk, dv, dg, dbeta], (None if dh0 is None else (dh0,))

@@ -54,3 +54,19 @@ def test_gdn_state_split_equals_full():
         ob, sb = mixers.gated_delta_rule(q[:, 256:], k[:, 256:], v[:, 256:], g[:, 256:], beta[:, 256:], initial_state=sa)
     assert _rel(torch.cat([oa, ob], 1), o) < 2e-2
     assert _rel(sb, s) < 2e-2
+
+
+def test_gdn_prep_kernel_matches_torch_prep():
+    """The chunk-preparation kernel reproduces the batched PyTorch formulation of the same factors."""
+    from hybrid_model_factory_b200.ops import gdn_cuda
+    q, k, v, g, beta = _inputs(2, 300, 3)
+    core = gdn_cuda.GDNChunkCore()
+    a = core._prep_packed(q, k, v, g, beta)
+    old = gdn_cuda._FORCE_TORCH_PREP
+    gdn_cuda._FORCE_TORCH_PREP = True
+    try:
+        b = core._prep_packed(q, k, v, g, beta)
+    finally:
+        gdn_cuda._FORCE_TORCH_PREP = old
+    for name, x, y in zip(["wqT", "kPT", "uT", "glast"], a[:4], b[:4]):
+        assert _rel(x, y) < 2e-2, f"{name}: {_rel(x, y)}"
