@@ -964,3 +964,73 @@ HMF_API int hmf_adamw(void* p, const void* g, void* m, void* v, float* master, l
   HMF_CHECK_CUDA(cudaGetLastError());
   return HMF_OK;
 }
+
+// ------------------------------------------------------------------------------------------
+// Allocation-free RMSNorm backward (declared and documented in no_alloc.h).
+// ------------------------------------------------------------------------------------------
+#include <mutex>
+
+#include "no_alloc.h"
+
+// Workspace for the per-slab partial sums of the weight gradient: [MAX_SLABS][MAX_D] floats.
+// In host code this name is only a handle for cudaGetSymbolAddress, never a device pointer.
+static __device__ __align__(256) float g_noalloc_rmsnorm_ws[HMF_NOALLOC_RMSNORM_MAX_SLABS * HMF_NOALLOC_RMSNORM_MAX_D];
+
+static int noalloc_workspace(float** out) {
+  static float* table[64] = {nullptr};
+  static std::mutex mu;
+  int dev = -1;
+  HMF_CHECK_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) {
+    set_last_error("rms_norm_bwd_noalloc: device index %d out of range", dev);
+    return HMF_ERR_BAD_ARG;
+  }
+  std::lock_guard<std::mutex> lock(mu);
+  if (table[dev] == nullptr) {
+    float* p = nullptr;
+    // resolved once per device, with that device current
+    HMF_CHECK_CUDA(cudaGetSymbolAddress((void**)&p, g_noalloc_rmsnorm_ws));
+    table[dev] = p;
+  }
+  *out = table[dev];
+  return HMF_OK;
+}
+
+HMF_API int hmf_rms_norm_bwd_noalloc(const void* x, const void* w, const void* dy, const float* rstd, void* dx,
+                                     void* dw_out, int dw_is_bf16, long long N, int D, int zero_centered,
+                                     cudaStream_t st) {
+  HMF_REQUIRE(x && dy && rstd && dx, "rms_norm_bwd_noalloc: null tensor");
+  HMF_REQUIRE(D > 0 && D % 8 == 0, "rms_norm_bwd_noalloc: D=%d must be a positive multiple of 8", D);
+  if (D > HMF_NOALLOC_RMSNORM_MAX_D) {
+    set_last_error("rms_norm_bwd_noalloc: D=%d exceeds the built-in workspace limit of %d columns; "
+                   "use hmf_rms_norm_bwd with a caller-provided buffer", D, HMF_NOALLOC_RMSNORM_MAX_D);
+    return HMF_ERR_TOO_LARGE;
+  }
+  if (N == 0) return HMF_OK;
+  float* ws = nullptr;
+  int rc = noalloc_workspace(&ws);
+  if (rc != HMF_OK) return rc;
+  const int warps = 8;
+  const long long blocks = (N + warps - 1) / warps;
+  rms_norm_bwd_dx_kernel<<<(unsigned)blocks, warps * 32, 0, st>>>(
+      (const bf16*)x, (const bf16*)w, (const bf16*)dy, rstd, (bf16*)dx, N, D, zero_centered);
+  HMF_CHECK_CUDA(cudaGetLastError());
+  if (w && dw_out) {
+    int slabs = hmf_rms_norm_bwd_blocks(N);
+    if (slabs > HMF_NOALLOC_RMSNORM_MAX_SLABS) slabs = HMF_NOALLOC_RMSNORM_MAX_SLABS;
+    const long long rps = (N + slabs - 1) / slabs;
+    int CT = D / 8;
+    if (CT > 256) CT = 256;
+    int p2 = 1;
+    while (p2 * 2 <= CT) p2 *= 2;
+    CT = p2;
+    dim3 grid((D / 8 + CT - 1) / CT, slabs);
+    // every word of ws[0 .. slabs*D) is written by this launch before colsum reads it
+    rms_norm_bwd_dw_kernel<<<grid, 256, 0, st>>>((const bf16*)x, (const bf16*)dy, rstd, ws, N, D, rps, CT);
+    HMF_CHECK_CUDA(cudaGetLastError());
+    colsum_kernel<<<(D + 255) / 256, 256, 0, st>>>(ws, slabs, D, dw_is_bf16 ? nullptr : (float*)dw_out,
+                                                   dw_is_bf16 ? (bf16*)dw_out : nullptr);
+    HMF_CHECK_CUDA(cudaGetLastError());
+  }
+  return HMF_OK;
+}
