@@ -1,0 +1,153 @@
+"""Run configuration: one flat YAML / JSON (plus ``key=value`` command-line overrides) split into
+five argument groups.  Key names follow the reference project's training YAMLs so existing configs
+keep working (``hparams/model_args.py``, ``data_args.py``, ``training_args.py``,
+``finetuning_args.py``, ``generating_args.py``; surface listed in the reference's
+``examples/priming/**.yaml``)."""
+from __future__ import annotations
+
+import json
+from dataclasses import asdict, dataclass, field, fields
+from typing import Any, Dict, List, Optional
+
+
+@dataclass
+class ModelArguments:
+    model_name_or_path: Optional[str] = None
+    config_overrides_json: Optional[str] = None      # JSON string or path: dotted keys into config.json
+    trust_remote_code: bool = False
+    flash_attn: str = "auto"
+    enable_liger_kernel: bool = False                  # accepted for compatibility: fused kernels are always on
+    sequence_parallel_size: int = 1
+    sequence_parallel_mode: str = "zigzag-ring"       # zigzag-ring | ulysses (attention only)
+    use_deepspeed_mics: bool = False
+    preserve_tokenizer_config: bool = False
+    resize_vocab: bool = False
+    rope_scaling: Optional[str] = None
+    infer_dtype: str = "auto"
+    adapter_name_or_path: Optional[str] = None
+
+    def config_overrides(self) -> Dict[str, Any]:
+        if not self.config_overrides_json:
+            return {}
+        s = self.config_overrides_json
+        if isinstance(s, dict):
+            return s
+        try:
+            return json.loads(s)
+        except json.JSONDecodeError:
+            with open(s) as f:
+                return json.load(f)
+
+
+@dataclass
+class DataArguments:
+    dataset: Optional[str] = None                      # comma separated names from dataset_info.json
+    dataset_dir: str = "data"
+    tokenized_path: Optional[str] = None
+    cutoff_len: int = 2048
+    template: Optional[str] = None
+    mix_strategy: str = "concat"                       # concat | interleave_under | interleave_over | interleave_fast
+    interleave_probs: Optional[str] = None
+    packing: Optional[bool] = None
+    neat_packing: bool = False
+    streaming: bool = False
+    preprocessing_num_workers: Optional[int] = None
+    max_samples: Optional[int] = None
+    val_size: float = 0.0
+    disable_shuffling: bool = False
+    overwrite_cache: bool = False
+    train_on_prompt: bool = False
+    mask_history: bool = False
+    ignore_pad_token_for_loss: bool = True
+    synthetic: bool = False                            # uniform random token ids of cutoff_len (benchmarks, smoke runs)
+    synthetic_vocab: int = 0
+
+
+@dataclass
+class RunArguments:
+    """Training-loop arguments (the HF ``TrainingArguments`` subset the reference configs use)."""
+    output_dir: str = "output"
+    overwrite_output_dir: bool = False
+    do_train: bool = True
+    per_device_train_batch_size: int = 1
+    gradient_accumulation_steps: int = 1
+    learning_rate: float = 1e-5
+    weight_decay: float = 0.0
+    adam_beta1: float = 0.9
+    adam_beta2: float = 0.999
+    adam_epsilon: float = 1e-8
+    max_grad_norm: float = 1.0
+    num_train_epochs: float = 1.0
+    max_steps: int = -1
+    lr_scheduler_type: str = "cosine"
+    warmup_steps: int = 0
+    warmup_ratio: float = 0.0
+    logging_steps: int = 1
+    save_steps: int = 0
+    save_only_model: bool = False
+    save_max_shard_size: str = "5GB"
+    seed: int = 42
+    bf16: bool = True
+    pure_bf16: bool = True
+    fp8: bool = False
+    disable_gradient_checkpointing: bool = False
+    deepspeed: Optional[str] = None                    # accepted; ZeRO stage is read from the JSON ("zero_optimization.stage")
+    ddp_timeout: int = 180000000
+    report_to: str = "none"
+    resume_from_checkpoint: Optional[str] = None
+    plot_loss: bool = False
+    ray: bool = False
+
+
+@dataclass
+class FinetuningArguments:
+    stage: str = "pt"                                  # pt | sft | hkd | rm | ppo | dpo | kto
+    finetuning_type: str = "full"                      # full | freeze | lora
+    hybrid_learnable_params: Optional[str] = None      # comma separated substrings, e.g. "gka,norm,self_attn"
+    hybrid_lw_distill_target: Optional[str] = None     # decoder | mixer | residuals | all
+    hybrid_distill_pre_lm_head: bool = True
+    hybrid_distill_loss: str = "mse"                   # mse (fused two-stream model) | kl (external teacher logits)
+    teacher_model_name_or_path: Optional[str] = None
+    use_muon: bool = False
+    use_adam_mini: bool = False
+    pref_beta: float = 0.1
+    pref_loss: str = "sigmoid"
+    lora_rank: int = 8
+    lora_alpha: Optional[int] = None
+    lora_target: str = "all"
+    freeze_trainable_layers: int = 2
+    include_effective_tokens_per_second: bool = False
+
+
+@dataclass
+class GeneratingArguments:
+    do_sample: bool = True
+    temperature: float = 0.95
+    top_p: float = 0.7
+    top_k: int = 50
+    max_new_tokens: int = 1024
+    repetition_penalty: float = 1.0
+
+
+GROUPS = (ModelArguments, DataArguments, RunArguments, FinetuningArguments, GeneratingArguments)
+
+
+def split_args(flat: Dict[str, Any], allow_extra: bool = False):
+    """Distributes a flat dict over the five dataclasses; unknown keys raise unless allowed."""
+    remaining = dict(flat)
+    out = []
+    for cls in GROUPS:
+        names = {f.name for f in fields(cls)}
+        kwargs = {k: remaining.pop(k) for k in list(remaining) if k in names}
+        out.append(cls(**kwargs))
+    # keys shared by two groups (sequence_parallel_size lives in ModelArguments, also read by the run loop)
+    if remaining and not allow_extra:
+        raise ValueError(f"unknown configuration keys: {sorted(remaining)} (set ALLOW_EXTRA_ARGS=1 to ignore)")
+    return tuple(out)
+
+
+def to_flat_dict(*groups) -> Dict[str, Any]:
+    d: Dict[str, Any] = {}
+    for g in groups:
+        d.update(asdict(g))
+    return d

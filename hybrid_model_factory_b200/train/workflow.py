@@ -1,0 +1,143 @@
+"""Training workflows: ``run_exp`` reads the configuration and dispatches on ``stage``.
+
+  * ``pt``  : next-token pre-training / continued pre-training (stage 2 of priming, long context + SP)
+  * ``sft`` : supervised fine-tuning (prompt tokens masked)
+  * ``hkd`` : stage-1 distillation of a fused model (hidden-state MSE; optional logit KL to a teacher)
+  * ``dpo`` / ``kto`` / ``rm`` : preference objectives on top of the same loop (``train/preference.py``)
+
+Reference: ``train/tuner.py:58-112``, ``train/pt/workflow.py:41-127``, ``train/hkd/workflow.py:47-139``.
+"""
+from __future__ import annotations
+
+import json
+import os
+from typing import Any, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..config.parser import get_train_args
+from ..data.formats import load_tokenizer
+from ..data.loader import batch_iterator, get_dataset
+from ..models.configuration import HybridConfig
+from ..models.modeling_hybrid import build_model
+from ..utils import checkpoint_io
+from ..utils.logging import get_logger, info_rank0
+from .hkd import freeze_params_hybrid, hkd_kl_loss, hkd_mse_loss
+from .trainer import Trainer, TrainingArguments
+
+logger = get_logger(__name__)
+
+
+def _device() -> torch.device:
+    if torch.cuda.is_available():
+        local = int(os.environ.get("LOCAL_RANK", "0"))
+        torch.cuda.set_device(local)
+        return torch.device("cuda", local)
+    return torch.device("cpu")
+
+
+def init_distributed(timeout_s: int = 1800) -> None:
+    if dist.is_initialized() or int(os.environ.get("WORLD_SIZE", "1")) <= 1:
+        return
+    import datetime
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    backend = "nccl" if torch.cuda.is_available() else "gloo"
+    dist.init_process_group(backend, timeout=datetime.timedelta(seconds=min(timeout_s, 7 * 24 * 3600)))
+
+
+def load_model(model_args, run_args, device: torch.device):
+    """Config (+ dotted overrides) -> model -> weights -> dtype/device (reference: ``model/loader.py:194-335``)."""
+    path = model_args.model_name_or_path
+    overrides = model_args.config_overrides()
+    dtype = torch.bfloat16 if run_args.bf16 else torch.float32
+    if path and os.path.isdir(path) and os.path.exists(os.path.join(path, "config.json")):
+        cfg = HybridConfig.from_pretrained(path)
+        cfg.apply_overrides(overrides)
+        model = build_model(cfg).to(dtype)
+        if checkpoint_io.checkpoint_files(path):
+            missing, unexpected = checkpoint_io.load_state_dict_into(model, path)
+            if missing:
+                logger.warning("load_model: %d tensors missing in the checkpoint (e.g. %s)", len(missing), missing[:4])
+    else:
+        raw = json.loads(path) if path and path.strip().startswith("{") else (overrides or {})
+        cfg = HybridConfig.from_dict(dict(raw))
+        model = build_model(cfg).to(dtype)
+    return model.to(device)
+
+
+def to_trainer_args(model_args, data_args, run_args, n_batches: Optional[int]) -> TrainingArguments:
+    max_steps = run_args.max_steps
+    if max_steps is None or max_steps < 0:
+        max_steps = int((n_batches or 0) * run_args.num_train_epochs)
+    warmup = run_args.warmup_steps or int(run_args.warmup_ratio * max_steps)
+    return TrainingArguments(
+        output_dir=run_args.output_dir, learning_rate=run_args.learning_rate, weight_decay=run_args.weight_decay,
+        adam_beta1=run_args.adam_beta1, adam_beta2=run_args.adam_beta2, adam_epsilon=run_args.adam_epsilon,
+        max_grad_norm=run_args.max_grad_norm, lr_scheduler_type=run_args.lr_scheduler_type, warmup_steps=warmup,
+        max_steps=max_steps, per_device_train_batch_size=run_args.per_device_train_batch_size,
+        gradient_accumulation_steps=run_args.gradient_accumulation_steps,
+        sequence_parallel_size=model_args.sequence_parallel_size, sequence_parallel_mode=model_args.sequence_parallel_mode,
+        bf16=run_args.bf16, pure_bf16=run_args.pure_bf16,
+        disable_gradient_checkpointing=run_args.disable_gradient_checkpointing, logging_steps=run_args.logging_steps,
+        save_steps=run_args.save_steps, save_only_model=run_args.save_only_model,
+        save_max_shard_size=run_args.save_max_shard_size, seed=run_args.seed,
+        resume_from_checkpoint=run_args.resume_from_checkpoint, ddp_timeout=run_args.ddp_timeout)
+
+
+def run_exp(args: Optional[Any] = None) -> Trainer:
+    model_args, data_args, run_args, ft_args, _ = get_train_args(args)
+    init_distributed(run_args.ddp_timeout)
+    torch.manual_seed(run_args.seed)
+    device = _device()
+    world = dist.get_world_size() if dist.is_initialized() else 1
+    rank = dist.get_rank() if dist.is_initialized() else 0
+    sp = model_args.sequence_parallel_size
+    tokenizer = load_tokenizer(model_args.model_name_or_path)
+    model = load_model(model_args, run_args, device)
+    stage = ft_args.stage
+    if stage == "hkd" or ft_args.hybrid_learnable_params:
+        n = freeze_params_hybrid(model, ft_args.hybrid_learnable_params)
+        info_rank0(logger, "trainable parameters: %d", n)
+    dataset = get_dataset(data_args, tokenizer, stage="pt" if stage in ("pt", "hkd") else "sft", sp_size=sp,
+                          vocab_size=model.config.vocab_size, seed=run_args.seed)
+    bsz = run_args.per_device_train_batch_size * run_args.gradient_accumulation_steps
+    n_batches = None
+    if hasattr(dataset, "__len__") and len(dataset) < (1 << 29):
+        n_batches = (len(dataset) // sp) // (bsz * max(1, world // sp))
+    targs = to_trainer_args(model_args, data_args, run_args, n_batches)
+    loss_fn = None
+    teacher = None
+    if stage == "hkd":
+        if ft_args.hybrid_distill_loss == "kl":
+            if not ft_args.teacher_model_name_or_path:
+                raise ValueError("hybrid_distill_loss=kl needs teacher_model_name_or_path")
+            teacher = checkpoint_io.from_pretrained(ft_args.teacher_model_name_or_path, device=device).eval()
+            for p in teacher.parameters():
+                p.requires_grad_(False)
+            loss_fn = lambda m, b: hkd_kl_loss(m, teacher, b)  # noqa: E731
+        else:
+            loss_fn = lambda m, b: hkd_mse_loss(m, b, ft_args.hybrid_lw_distill_target,  # noqa: E731
+                                                ft_args.hybrid_distill_pre_lm_head)
+    elif stage in ("dpo", "kto", "rm"):
+        from .preference import make_preference_loss
+        loss_fn = make_preference_loss(stage, ft_args)
+    trainer = Trainer(model, targs, device=device, loss_fn=loss_fn)
+    if teacher is not None:
+        from ..parallel.sp import set_sequence_parallel_group_recursive
+        set_sequence_parallel_group_recursive(teacher, trainer.sp)
+    pad_id = getattr(tokenizer, "pad_token_id", None) or 0
+    batches = batch_iterator(dataset, bsz, rank, world, sp, pad_id, start_step=trainer.global_step,
+                             pin=device.type == "cuda")
+    if run_args.do_train:
+        trainer.train(batches)
+        final = os.path.join(run_args.output_dir, "final")
+        trainer.args.save_only_model = True
+        trainer.save_checkpoint(final)
+        if rank == 0:
+            for fn in ("tokenizer.json", "tokenizer_config.json", "vocab.json", "merges.txt", "special_tokens_map.json"):
+                src = os.path.join(model_args.model_name_or_path or "", fn)
+                if os.path.exists(src):
+                    import shutil
+                    shutil.copy(src, os.path.join(final, fn))
+    return trainer

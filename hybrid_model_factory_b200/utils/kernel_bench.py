@@ -1,0 +1,187 @@
+"""Kernel microbenchmarks with roofline fractions.
+
+    python -m hybrid_model_factory_b200.utils.kernel_bench attention_fwd --seq 16384
+    python -m hybrid_model_factory_b200.utils.kernel_bench all
+
+Each case is timed with CUDA events on the launching stream after warm-up (inputs are larger
+than the 126 MB L2, or an L2-sized buffer is rewritten between iterations), and reported as
+achieved TFLOP/s or GB/s and as a fraction of the measured peaks of this machine
+(``MEASURED_PEAKS.json`` at the repository root when present, else the documented fallback of
+6.65 TB/s and 1.59 PFLOP/s).  The same commands are what the ``profiles/`` summaries were
+captured from under ``ncu``.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm_gbs": d["hbm_gbs"], "tflops": d["bf16_tflops"], "src": "measured"}
+    return {"hbm_gbs": 6650.0, "tflops": 1590.0, "src": "fallback"}
+
+
+_flush = None
+
+
+def flush_l2():
+    global _flush
+    if _flush is None:
+        _flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    _flush.zero_()
+
+
+def time_fn(fn, iters=5, warmup=3, flush=True):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    total = 0.0
+    for _ in range(iters):
+        if flush:
+            flush_l2()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        total += s.elapsed_time(e)
+    return total / iters
+
+
+def report(name, ms, flops=None, bytes_=None):
+    pk = peaks()
+    line = f"{name}: {ms:.3f} ms"
+    if flops:
+        tf = flops / ms / 1e9
+        line += f"  {tf:.0f} TFLOP/s ({tf / pk['tflops']:.2f} of {pk['src']} cuBLAS bf16 peak)"
+    if bytes_:
+        gbs = bytes_ / ms / 1e6
+        line += f"  {gbs:.0f} GB/s ({gbs / pk['hbm_gbs']:.2f} of {pk['src']} copy bandwidth)"
+    print(line, flush=True)
+
+
+def bench_gemm(args):
+    from ..ops.gemm import gemm
+    M = N = K = args.size
+    a = torch.randn(M, K, device="cuda").bfloat16()
+    b = torch.randn(N, K, device="cuda").bfloat16()
+    out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    report(f"gemm_bf16 {M}^3", time_fn(lambda: gemm(a, b, out=out)), flops=2.0 * M * N * K)
+
+
+def _qkv(T, H, Hkv, D):
+    q = torch.randn(1, T, H, D, device="cuda").bfloat16()
+    k = torch.randn(1, T, Hkv, D, device="cuda").bfloat16()
+    v = torch.randn(1, T, Hkv, D, device="cuda").bfloat16()
+    return q, k, v
+
+
+def bench_attention_fwd(args):
+    from ..ops import cuda_ops
+    T, H, Hkv, D = args.seq, args.heads, args.kv_heads, 128
+    q, k, v = _qkv(T, H, Hkv, D)
+    ms = time_fn(lambda: cuda_ops.attention_fwd_raw(q, k, v, D ** -0.5, 0, 2 ** 31 - 1, 0), flush=False)
+    report(f"attention_fwd causal T={T} H={H}/{Hkv} D={D}", ms, flops=4.0 * T * T * H * D / 2)
+
+
+def bench_attention_bwd(args):
+    from ..ops import cuda_ops
+    T, H, Hkv, D = args.seq, args.heads, args.kv_heads, 128
+    q, k, v = _qkv(T, H, Hkv, D)
+    o, lse = cuda_ops.attention_fwd_raw(q, k, v, D ** -0.5, 0, 2 ** 31 - 1, 0)
+    do = torch.randn_like(o)
+    ms = time_fn(lambda: cuda_ops.attention_bwd_raw(q, k, v, o, do, lse, D ** -0.5, 0, 2 ** 31 - 1, 0), flush=False)
+    report(f"attention_bwd causal T={T} H={H}/{Hkv} D={D} (5-GEMM flop count)", ms, flops=10.0 * T * T * H * D / 2)
+
+
+def _gdn_inputs(T, H):
+    q = torch.randn(1, T, H, 128, device="cuda").bfloat16()
+    k = torch.randn(1, T, H, 128, device="cuda").bfloat16()
+    v = torch.randn(1, T, H, 128, device="cuda").bfloat16()
+    g = -torch.rand(1, T, H, device="cuda") * 0.1
+    beta = torch.rand(1, T, H, device="cuda")
+    return q, k, v, g, beta
+
+
+def bench_gdn_fwd(args):
+    from ..ops import mixers
+    T, H = args.seq, args.heads
+    q, k, v, g, beta = _gdn_inputs(T, H)
+    with torch.no_grad():
+        ms = time_fn(lambda: mixers.gated_delta_rule(q, k, v, g, beta), flush=False)
+    io = 4 * T * H * 128 * 2  # q, k, v in; o out
+    report(f"gdn_fwd (prep + scan) T={T} H={H}", ms, bytes_=io)
+
+
+def bench_gdn_fwd_bwd(args):
+    from ..ops import mixers
+    T, H = args.seq, args.heads
+    leaves = [t.requires_grad_(True) for t in _gdn_inputs(T, H)]
+
+    def step():
+        o, _ = mixers.gated_delta_rule(*leaves)
+        o.backward(torch.ones_like(o))
+    report(f"gdn_fwd_bwd T={T} H={H}", time_fn(step, flush=False))
+
+
+def bench_rmsnorm(args):
+    from ..ops import functional as F_ops
+    N, D = args.seq * 8, 4096
+    x = torch.randn(N, D, device="cuda").bfloat16()
+    w = torch.ones(D, device="cuda").bfloat16()
+    with torch.no_grad():
+        ms = time_fn(lambda: F_ops.rms_norm(x, w, 1e-6))
+    report(f"rms_norm [{N}, {D}]", ms, bytes_=2.0 * N * D * 2)
+
+
+def bench_swiglu(args):
+    from ..ops import functional as F_ops
+    N, D = args.seq, 12288
+    g = torch.randn(N, D, device="cuda").bfloat16()
+    u = torch.randn(N, D, device="cuda").bfloat16()
+    with torch.no_grad():
+        ms = time_fn(lambda: F_ops.swiglu(g, u))
+    report(f"swiglu [{N}, {D}]", ms, bytes_=3.0 * N * D * 2)
+
+
+def bench_conv1d(args):
+    from ..ops import functional as F_ops
+    T, Cc = args.seq, 6144
+    x = torch.randn(1, T, Cc, device="cuda").bfloat16()
+    w = torch.randn(Cc, 4, device="cuda").bfloat16()
+    with torch.no_grad():
+        ms = time_fn(lambda: F_ops.causal_conv1d(x, w, None, "silu"))
+    report(f"causal_conv1d+silu [1, {T}, {Cc}]", ms, bytes_=2.0 * T * Cc * 2)
+
+
+CASES = {"gemm": bench_gemm, "attention_fwd": bench_attention_fwd, "attention_bwd": bench_attention_bwd,
+         "gdn_fwd": bench_gdn_fwd, "gdn_fwd_bwd": bench_gdn_fwd_bwd, "rmsnorm": bench_rmsnorm, "swiglu": bench_swiglu,
+         "conv1d": bench_conv1d}
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("case", choices=list(CASES) + ["all"])
+    ap.add_argument("--seq", type=int, default=16384)
+    ap.add_argument("--heads", type=int, default=32)
+    ap.add_argument("--kv-heads", type=int, default=8)
+    ap.add_argument("--size", type=int, default=8192)
+    args = ap.parse_args(argv)
+    names = list(CASES) if args.case == "all" else [args.case]
+    for n in names:
+        CASES[n](args)
+    from ..ops import _lib
+    print("kernel status", _lib.read_status())
+
+
+if __name__ == "__main__":
+    sys.exit(main())
