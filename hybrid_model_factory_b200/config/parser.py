@@ -25,6 +25,30 @@ def _set_dotted(d: Dict[str, Any], key: str, value: Any) -> None:
     d[parts[-1]] = value
 
 
+def _typed(text: str) -> Any:
+    """YAML typing plus plain scientific notation (YAML 1.1 reads ``5e-5`` as a string)."""
+    v = yaml.safe_load(text)
+    if isinstance(v, str):
+        try:
+            return float(v) if any(c in v for c in ".eE") else int(v)
+        except ValueError:
+            return v
+    return v
+
+
+def _fix_numbers(d: Dict[str, Any]) -> Dict[str, Any]:
+    for k, v in list(d.items()):
+        if isinstance(v, dict):
+            _fix_numbers(v)
+        elif isinstance(v, str) and k not in ("model_name_or_path", "dataset", "output_dir", "template"):
+            try:
+                d[k] = float(v) if any(c in v for c in "eE") and v.replace(".", "").replace("-", "").replace(
+                    "e", "").replace("E", "").replace("+", "").isdigit() else v
+            except ValueError:
+                pass
+    return d
+
+
 def parse_overrides(tokens: Sequence[str]) -> Dict[str, Any]:
     out: Dict[str, Any] = {}
     i = 0
@@ -33,7 +57,7 @@ def parse_overrides(tokens: Sequence[str]) -> Dict[str, Any]:
         t = tokens[i]
         if "=" in t and not t.startswith("--"):
             k, v = t.split("=", 1)
-            _set_dotted(out, k, yaml.safe_load(v))
+            _set_dotted(out, k, _typed(v))
         elif t.startswith("--"):
             k = t[2:]
             if "=" in k:
@@ -43,7 +67,7 @@ def parse_overrides(tokens: Sequence[str]) -> Dict[str, Any]:
                 v = tokens[i]
             else:
                 v = "true"
-            _set_dotted(out, k.replace("-", "_"), yaml.safe_load(v))
+            _set_dotted(out, k.replace("-", "_"), _typed(v))
         else:
             raise ValueError(f"cannot parse argument '{t}' (expected key=value)")
         i += 1
@@ -60,7 +84,7 @@ def read_args(args: Optional[Any] = None) -> Dict[str, Any]:
     if tokens and tokens[0].endswith((".yaml", ".yml", ".json")):
         path = tokens.pop(0)
         with open(path) as f:
-            base = (json.load(f) if path.endswith(".json") else yaml.safe_load(f)) or {}
+            base = _fix_numbers((json.load(f) if path.endswith(".json") else yaml.safe_load(f)) or {})
     over = parse_overrides(tokens)
     for k, v in over.items():
         if isinstance(v, dict) and isinstance(base.get(k), dict):
