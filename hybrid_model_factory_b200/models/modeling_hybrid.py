@@ -20,7 +20,9 @@ from typing import List, Optional, Tuple
 import torch
 import torch.nn as nn
 import torch.nn.functional as F
-from torch.utils.checkpoint import checkpoint
+from torch.utils.checkpoint import checkpoint  # noqa: F401
+
+from ..utils.checkpointing import layer_checkpoint
 
 from ..layers.attention import Attention, SlidingWindowAttention
 from ..layers.bmojo import BMojoLayer
@@ -233,6 +235,12 @@ class HybridModel(nn.Module):
         self.gradient_checkpointing = False
         self.sequence_parallel_group = None
 
+    @staticmethod
+    def _ckpt_anchor(h: torch.Tensor) -> torch.Tensor:
+        """Zero-size tensor that requires grad: keeps a checkpointed layer in the autograd graph even when
+        its activations do not require grad (frozen embeddings)."""
+        return torch.empty(0, device=h.device, dtype=h.dtype, requires_grad=True)
+
     @property
     def has_fused_layers(self) -> bool:
         return any(isinstance(l, FusedDecoderLayer) for l in self.layers)
@@ -252,7 +260,13 @@ class HybridModel(nn.Module):
                 h = layer(h, h, position_embeddings=pos_emb, position_ids=position_ids)[0]
                 continue
             if self.gradient_checkpointing and self.training:
-                h, rl = checkpoint(layer, h, pos_emb, position_ids, None, False, use_reentrant=False, **kwargs)
+                if layer.is_moe:
+                    h, rl = layer_checkpoint(lambda a, c, s_, p_, _d, layer=layer: layer(a, (c, s_), p_, None, False),
+                                             h, pos_emb[0], pos_emb[1], position_ids, self._ckpt_anchor(h))
+                else:
+                    (h,) = layer_checkpoint(lambda a, c, s_, p_, _d, layer=layer: layer(a, (c, s_), p_, None, False)[0],
+                                            h, pos_emb[0], pos_emb[1], position_ids, self._ckpt_anchor(h))
+                    rl = None
             else:
                 h, rl = layer(h, position_embeddings=pos_emb, position_ids=position_ids,
                               past_key_values=past_key_values, use_cache=use_cache, **kwargs)

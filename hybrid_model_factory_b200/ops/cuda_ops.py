@@ -428,6 +428,25 @@ class _Attention(torch.autograd.Function):
         return dq, dk, dv, None, None, None, None, None
 
 
+class _AttentionFromSaved(torch.autograd.Function):
+    """Re-registers the backward of an attention call whose forward result was stashed by the first run
+    of a checkpointed layer (``utils/checkpointing.py``): no forward kernel is launched."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, o, lse, scale, lo, hi, q_off, q_pos):
+        ctx.save_for_backward(q, k, v, o, lse, q_pos)
+        ctx.cfg = (scale, lo, hi, q_off)
+        ctx.mark_non_differentiable(lse)
+        return o.view_as(o), lse.view_as(lse)
+
+    @staticmethod
+    def backward(ctx, do, _dlse):
+        q, k, v, o, lse, q_pos = ctx.saved_tensors
+        scale, lo, hi, q_off = ctx.cfg
+        dq, dk, dv = attention_bwd_raw(q, k, v, o, do, lse, scale, lo, hi, q_off, q_pos)
+        return dq, dk, dv, None, None, None, None, None, None, None
+
+
 def _contiguous_positions(pos: Optional[Tensor], n: int) -> Optional[int]:
     """Offset ``c`` if ``pos[b, i] == i + c`` for every row, else ``None`` (host sync: small tensors only)."""
     if pos is None:
@@ -463,7 +482,16 @@ def attention(q, k, v, *, scale=None, causal=True, window=None, hollow=None, q_p
             q_off = c - k_off
         else:
             q_off, qp = 0, (q_pos - k_off)
-    o, lse = _Attention.apply(q, k, v, scale, lo, hi, q_off, qp)
+    from ..utils import checkpointing as _ckpt
+    rd = _ckpt.stash_for_read()
+    if rd is not None and torch.is_grad_enabled() and len(rd) > 0:
+        o_saved, lse_saved = rd.pop(0)
+        o, lse = _AttentionFromSaved.apply(q, k, v, o_saved, lse_saved, scale, lo, hi, q_off, qp)
+    else:
+        o, lse = _Attention.apply(q, k, v, scale, lo, hi, q_off, qp)
+        wr = _ckpt.stash_for_write()
+        if wr is not None:
+            wr.append((o.detach(), lse.detach()))
     return (o, lse) if return_lse else o
 
 

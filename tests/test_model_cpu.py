@@ -81,3 +81,18 @@ def test_fused_layers_streams():
     pe = model.model.rotary_emb(pos)
     outs = model.model.layers[1](h, h, position_embeddings=pe, position_ids=pos)
     assert len(outs) == 6 and not outs[1].requires_grad and outs[0].requires_grad
+
+
+def test_layer_checkpoint_matches_plain_backward():
+    torch.manual_seed(0)
+    cfg = tiny("*-GDN-GKA-M2")
+    m1 = build_model(cfg)
+    import copy
+    m2 = copy.deepcopy(m1)
+    m2.gradient_checkpointing_enable()
+    m1.train(), m2.train()
+    ids = torch.randint(0, 256, (2, 40))
+    m1(ids, labels=ids).loss.backward()
+    m2(ids, labels=ids).loss.backward()
+    for (n, a), (_, b) in zip(m1.named_parameters(), m2.named_parameters()):
+        torch.testing.assert_close(a.grad, b.grad, rtol=1e-5, atol=1e-6, msg=n)
