@@ -49,6 +49,7 @@ struct Params {
   int k_rep, v_rep;   // query heads per key / value head (1 when k, v are already expanded)
   float scale;
   int l2norm;
+  int gla;            // 1: plain gated linear attention (no delta rule): T = I, beta = 1, w = 0
   unsigned int* status;
 };
 
@@ -133,7 +134,7 @@ gdn_prep_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   if (tid < C) {
     const int t = t0 + tid;
     sG[tid] = (t < p.T) ? p.g[((size_t)b * p.T + t) * p.H + h] : 0.f;
-    sBeta[tid] = (t < p.T) ? p.beta[((size_t)b * p.T + t) * p.H + h] : 0.f;
+    sBeta[tid] = p.gla ? 1.f : ((t < p.T) ? p.beta[((size_t)b * p.T + t) * p.H + h] : 0.f);
   }
   // zero the diagonal B tiles and the k~ half of B_wk while the loads are in flight
   for (int i = tid; i < (BQ_BYTES + BWK_BYTES / 2) / 16; i += 128) {
@@ -188,7 +189,7 @@ gdn_prep_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const float bi = sBeta[i] * sKinv[i];
 #pragma unroll
       for (int j = 0; j < C; ++j) {
-        const float a = (j < i) ? bi * __uint_as_float(gr[j]) * sKinv[j] * __expf(Gi - sG[j]) : 0.f;
+        const float a = (j < i && !p.gla) ? bi * __uint_as_float(gr[j]) * sKinv[j] * __expf(Gi - sG[j]) : 0.f;
         sA[i * C + j] = a;
       }
     } else {
@@ -214,7 +215,7 @@ gdn_prep_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       Tc[i] = acc;
     }
     const float bc = sBeta[c];
-    const float bw = bc * __expf(sG[c]) * sKinv[c];
+    const float bw = p.gla ? 0.f : bc * __expf(sG[c]) * sKinv[c];
 #pragma unroll
     for (int i = 0; i < C; ++i) {
       *reinterpret_cast<bf16*>(sBU + sw128_offset(i, c * 2)) = __float2bfloat16(Tc[i] * bc);
@@ -300,11 +301,11 @@ static int make_map_bthd(CUtensorMap* m, const void* base, int B, int T, int H, 
 HMF_API int hmf_gdn_prep(const void* q, const void* k, const void* v, const float* g, const float* beta,
                          void* wqT, void* kPT, void* uT, float* glast, int B, int T, int H, int Hk, int Hv,
                          int N, long long q_sb, long long q_st, long long q_sh, long long k_sb, long long k_st,
-                         long long k_sh, long long v_sb, long long v_st, long long v_sh, float scale, int l2norm,
+                         long long k_sh, long long v_sb, long long v_st, long long v_sh, float scale, int l2norm, int gla,
                          cudaStream_t stream) {
   using namespace hmf;
   using namespace hmf::gdn_prep;
-  HMF_REQUIRE(q && k && v && g && beta && wqT && kPT && uT && glast, "gdn_prep: null tensor");
+  HMF_REQUIRE(q && k && v && g && (beta || gla) && wqT && kPT && uT && glast, "gdn_prep: null tensor");
   HMF_REQUIRE(H % Hk == 0 && H % Hv == 0, "gdn_prep: H=%d must be a multiple of Hk=%d and Hv=%d", H, Hk, Hv);
   HMF_REQUIRE(N * C >= T && N > 0, "gdn_prep: N=%d chunks do not cover T=%d", N, T);
   CUtensorMap tmQ, tmK, tmV;
@@ -320,7 +321,7 @@ HMF_API int hmf_gdn_prep(const void* q, const void* k, const void* v, const floa
   Params p;
   p.g = g; p.beta = beta; p.wqT = (bf16*)wqT; p.kPT = (bf16*)kPT; p.uT = (bf16*)uT; p.glast = glast;
   p.B = B; p.T = T; p.H = H; p.N = N; p.k_rep = H / Hk; p.v_rep = H / Hv;
-  p.scale = scale; p.l2norm = l2norm; p.status = status_ptr();
+  p.scale = scale; p.l2norm = l2norm; p.gla = gla; p.status = status_ptr();
   dim3 grid(N, B * H);
   gdn_prep_kernel<<<grid, 128, SMEM, stream>>>(tmQ, tmK, tmV, p);
   HMF_CHECK_CUDA(cudaGetLastError());

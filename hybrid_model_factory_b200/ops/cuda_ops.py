@@ -520,15 +520,3 @@ def GDNCore(scale=None, chunk_size=64, use_qk_l2norm=True, recurrent=False):
     if not recurrent:
         kw["chunk_size"] = chunk_size
     return TorchScanCore(fn, n_state=1, state_shape_fn=_gdn_state_shapes, **kw)
-
-
-def GKACore(scale=None, ridge_ratio=0.02, num_iter=30, chunk_size=64, recurrent=False):
-    from .mixers import _gka_ref, _gka_state_shapes
-    return TorchScanCore(_gka_ref, n_state=2, state_shape_fn=_gka_state_shapes, scale=scale, ridge_ratio=ridge_ratio,
-                         num_iter=num_iter, chunk_size=chunk_size, recurrent=recurrent)
-
-
-def SSDCore(chunk_size=256, recurrent=False):
-    from .mixers import _ssd_ref, _ssd_state_shapes
-    return TorchScanCore(_ssd_ref, n_state=1, state_shape_fn=_ssd_state_shapes, chunk_size=chunk_size,
-                         recurrent=recurrent)

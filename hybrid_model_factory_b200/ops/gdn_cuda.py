@@ -63,10 +63,17 @@ def _unchunk(x: torch.Tensor, B: int, H: int, T: int) -> torch.Tensor:
 class GDNChunkCore(ScanCore):
     n_state = 1
 
-    def __init__(self, scale: Optional[float] = None, use_qk_l2norm: bool = True):
-        self.scale, self.use_qk_l2norm = scale, use_qk_l2norm
-        self._fallback = TorchScanCore(R.gated_delta_rule_chunk, n_state=1, state_shape_fn=self.state_shapes,
-                                       scale=scale, use_qk_l2norm=use_qk_l2norm, chunk_size=C)
+    def __init__(self, scale: Optional[float] = None, use_qk_l2norm: bool = True, gla: bool = False):
+        """``gla=True``: plain gated linear attention ``S_t = e^{g_t} S_{t-1} + k_t v_t^T`` (no delta rule;
+        ``beta`` is ignored).  Same kernels: the WY factors degenerate to ``w = 0``, ``u = v``."""
+        self.scale, self.use_qk_l2norm, self.gla = scale, use_qk_l2norm, gla
+        if gla:
+            self._fallback = TorchScanCore(lambda q, k, v, g, beta, initial_state=None: R.simple_gla_chunk(
+                q, k, v, g, scale=scale, initial_state=initial_state, chunk_size=C), n_state=1,
+                state_shape_fn=self.state_shapes)
+        else:
+            self._fallback = TorchScanCore(R.gated_delta_rule_chunk, n_state=1, state_shape_fn=self.state_shapes,
+                                           scale=scale, use_qk_l2norm=use_qk_l2norm, chunk_size=C)
         # sequence-parallel hooks filled in by parallel.peer.PeerStateTransport
         self.peer = None
 
@@ -85,7 +92,8 @@ class GDNChunkCore(ScanCore):
         N = (T + C - 1) // C
         scale = Dk ** -0.5 if self.scale is None else self.scale
         qf, kf, vf = _chunk(q, N).float(), _chunk(k, N).float(), _chunk(v, N).float()
-        gc, bc = _chunk(g.float(), N), _chunk(beta.float(), N)
+        gc = _chunk(g.float(), N)
+        bc = torch.ones_like(gc) if self.gla else _chunk(beta.float(), N)
         if self.use_qk_l2norm:
             qf = qf * torch.rsqrt(qf.pow(2).sum(-1, keepdim=True) + 1e-6)
             kf = kf * torch.rsqrt(kf.pow(2).sum(-1, keepdim=True) + 1e-6)
@@ -97,11 +105,14 @@ class GDNChunkCore(ScanCore):
         strict = idx[:, None] > idx[None, :]
         diff = G[..., :, None] - G[..., None, :]
         decay = torch.exp(diff.masked_fill(~lower, 0.0)) * lower
-        A = (bc[..., None] * (kf @ kf.transpose(-1, -2)) * decay) * strict
-        eye = torch.eye(C, device=q.device, dtype=torch.float32)
-        Tm = torch.linalg.solve_triangular(eye + A, eye.expand_as(A), upper=False)
-        u = Tm @ (vf * bc[..., None])
-        w = Tm @ (kf * (bc * torch.exp(G))[..., None])
+        if self.gla:
+            u, w = vf, torch.zeros_like(kf)
+        else:
+            A = (bc[..., None] * (kf @ kf.transpose(-1, -2)) * decay) * strict
+            eye = torch.eye(C, device=q.device, dtype=torch.float32)
+            Tm = torch.linalg.solve_triangular(eye + A, eye.expand_as(A), upper=False)
+            u = Tm @ (vf * bc[..., None])
+            w = Tm @ (kf * (bc * torch.exp(G))[..., None])
         P = (qf @ kf.transpose(-1, -2)) * decay
         qt = qf * torch.exp(G)[..., None]
         kt = kf * torch.exp(glast[..., None] - G)[..., None]
@@ -143,15 +154,16 @@ class GDNChunkCore(ScanCore):
             ll = ctypes.c_longlong
             rc = _lib.kernels().hmf_gdn_prep(
                 _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(g.float().contiguous()),
-                _lib.ptr(beta.float().contiguous()), _lib.ptr(wqT), _lib.ptr(kPT), _lib.ptr(uT), _lib.ptr(glast),
+                _lib.ptr(None if self.gla else beta.float().contiguous()), _lib.ptr(wqT), _lib.ptr(kPT), _lib.ptr(uT), _lib.ptr(glast),
                 c_int(B), c_int(T), c_int(H), c_int(k.shape[2]), c_int(v.shape[2]), c_int(N),
                 ll(q.stride(0)), ll(q.stride(1)), ll(q.stride(2)), ll(k.stride(0)), ll(k.stride(1)), ll(k.stride(2)),
                 ll(v.stride(0)), ll(v.stride(1)), ll(v.stride(2)), ctypes.c_float(scale),
-                c_int(int(self.use_qk_l2norm)), _lib.stream_ptr(q.device))
+                c_int(int(self.use_qk_l2norm)), c_int(int(self.gla)), _lib.stream_ptr(q.device))
             _lib.check(rc, "hmf_gdn_prep")
             return wqT, kPT, uT, glast, N
         for hs in self._head_groups(B, T, H):
-            f = self._prep(q[:, :, hs], k[:, :, hs], v[:, :, hs], g[:, :, hs], beta[:, :, hs])
+            f = self._prep(q[:, :, hs], k[:, :, hs], v[:, :, hs], g[:, :, hs],
+                           None if beta is None else beta[:, :, hs])
             a, b_, c_, d_ = self._pack(f)
             nh = hs.stop - hs.start
             wqT[:, hs] = a.view(B, nh, N, 2, Dk, C)
@@ -209,14 +221,15 @@ class GDNChunkCore(ScanCore):
             _lib.check(rc, "hmf_gdn_scan_bwd")
             del wqT, kPT
             dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
-            dg, dbeta = torch.empty_like(g), torch.empty_like(beta)
+            dg = torch.empty_like(g)
+            dbeta = None if (beta is None or self.gla) else torch.empty_like(beta)
             vn5, h5 = vnT.view(B, H, N, Dv, C), h_all.view(B, H, N, Dv, Dk)
             dvn5, dS5 = dvnT.view(B, H, N, Dv, C), dS_all.view(B, H, N, Dv, Dk)
             gl5 = glast.view(B, H, N)
         # gradients of the per-chunk factors, then autograd through the preparation, per head group
         for hs in self._head_groups(B, T, H):
             nh = hs.stop - hs.start
-            leaves = [t[:, :, hs].detach().requires_grad_(True) for t in (q, k, v, g, beta)]
+            leaves = [t[:, :, hs].detach().requires_grad_(True) if t is not None else None for t in (q, k, v, g, beta)]
             with torch.enable_grad():
                 f = self._prep(*leaves)
             with torch.no_grad():
@@ -234,6 +247,8 @@ class GDNChunkCore(ScanCore):
                                     [d_w, d_qt, d_kt, d_P, d_u, d_gl])
             with torch.no_grad():
                 dq[:, :, hs], dk[:, :, hs], dv[:, :, hs] = leaves[0].grad, leaves[1].grad, leaves[2].grad
-                dg[:, :, hs], dbeta[:, :, hs] = leaves[3].grad, leaves[4].grad
+                dg[:, :, hs] = leaves[3].grad
+                if dbeta is not None:
+                    dbeta[:, :, hs] = leaves[4].grad
             del f, leaves
         return [dq, dk, dv, dg, dbeta], (None if dh0 is None else (dh0,))

@@ -3,7 +3,11 @@
 Each function builds the scan core for the device of its inputs (CUDA kernels or the PyTorch
 reference) and runs it through :func:`ops.scan.ssm_scan`, which also handles the
 sequence-parallel state chain.  Decode steps (``recurrent=True``) use the token-by-token
-kernels / definitions.
+definitions (the serving engine has dedicated slot-indexed decode kernels).
+
+Mamba2's SSD and GKA's output stage are both plain gated linear attention
+(``S_t = e^{g_t} S_{t-1} + k_t v_t^T``), which the GDN kernels evaluate in their ``gla`` mode
+(WY factors degenerate to ``w = 0``, ``u = v``).
 """
 from __future__ import annotations
 
@@ -18,12 +22,12 @@ from .scan import TorchScanCore, ssm_scan
 Tensor = torch.Tensor
 
 
-# -- Gated DeltaNet ------------------------------------------------------------------------
-def _gdn_state_shapes(inputs):
-    q, k, v = inputs[0], inputs[1], inputs[2]
+def _qkv_state_shapes(inputs):
+    q, v = inputs[0], inputs[2]
     return [((q.shape[0], q.shape[2], q.shape[3], v.shape[3]), torch.float32)]
 
 
+# -- Gated DeltaNet ------------------------------------------------------------------------
 def gated_delta_rule(q: Tensor, k: Tensor, v: Tensor, g: Tensor, beta: Tensor, *, scale: Optional[float] = None,
                      initial_state: Optional[Tensor] = None, sp=None, chunk_size: int = 64,
                      use_qk_l2norm: bool = True, recurrent: bool = False) -> Tuple[Tensor, Tensor]:
@@ -37,21 +41,59 @@ def gated_delta_rule(q: Tensor, k: Tensor, v: Tensor, g: Tensor, beta: Tensor, *
         kw = dict(scale=scale, use_qk_l2norm=use_qk_l2norm)
         if not recurrent:
             kw["chunk_size"] = chunk_size
-        core = TorchScanCore(fn, n_state=1, state_shape_fn=_gdn_state_shapes, **kw)
+        core = TorchScanCore(fn, n_state=1, state_shape_fn=_qkv_state_shapes, **kw)
     state = None if initial_state is None else (initial_state,)
     o, (sT,) = ssm_scan(core, [q, k, v, g, beta], state, sp)
     return o, sT
 
 
+# -- plain gated linear attention ------------------------------------------------------------
+def _gla_ref(q, k, v, g, beta=None, initial_state=None, scale=None, chunk_size=64, recurrent=False):
+    if recurrent:
+        return R.simple_gla_recurrent(q, k, v, g, scale=scale, initial_state=initial_state)
+    return R.simple_gla_chunk(q, k, v, g, scale=scale, initial_state=initial_state, chunk_size=chunk_size)
+
+
+def simple_gla(q: Tensor, k: Tensor, v: Tensor, g: Tensor, *, scale: Optional[float] = None,
+               initial_state: Optional[Tensor] = None, sp=None, chunk_size: int = 64, recurrent: bool = False):
+    """``S_t = e^{g_t} S_{t-1} + k_t v_t^T``, ``o_t = S_t^T q_t * scale``.  State ``[B,H,Dk,Dv]`` fp32."""
+    core = None
+    if _lib.use_cuda_kernels(q, k, v) and not recurrent:
+        from . import gdn_cuda
+        if gdn_cuda.available():
+            core = gdn_cuda.GDNChunkCore(scale=scale, use_qk_l2norm=False, gla=True)
+    if core is None:
+        core = TorchScanCore(_gla_ref, n_state=1, state_shape_fn=_qkv_state_shapes, scale=scale,
+                             chunk_size=chunk_size, recurrent=recurrent)
+    state = None if initial_state is None else (initial_state,)
+    o, (sT,) = ssm_scan(core, [q, k, v, g, None], state, sp)
+    return o, sT
+
+
 # -- Gated KalmaNet --------------------------------------------------------------------------
-def _gka_state_shapes(inputs):
-    q, v = inputs[0], inputs[2]
+def _cheb_state_shapes(inputs):
+    q = inputs[0]
     B, H, D = q.shape[0], q.shape[2], q.shape[3]
-    return [((B, H, D, D), torch.float32), ((B, H, D, v.shape[3]), torch.float32)]
+    return [((B, H, D, D), torch.float32)]
 
 
-def _gka_ref(q, k, v, alpha, g, gk, initial_state=None, **kw):
-    return R.gka_forward(q, k, v, alpha, g, gk, initial_state=initial_state, **kw)
+def _cheb_ref(q, k, gk, initial_state=None, ridge_ratio=0.02, num_iter=30, chunk_size=64, recurrent=False):
+    if recurrent:
+        return R.gka_chebyshev_recurrent(q, k, gk, ridge_ratio=ridge_ratio, num_iter=num_iter,
+                                         initial_state=initial_state)
+    return R.gka_chebyshev_chunk(q, k, gk, ridge_ratio=ridge_ratio, num_iter=num_iter, initial_state=initial_state,
+                                 chunk_size=chunk_size)
+
+
+def chebyshev_solve(q: Tensor, k: Tensor, gk: Optional[Tensor], *, ridge_ratio: float = 0.02, num_iter: int = 30,
+                    initial_state: Optional[Tensor] = None, sp=None, chunk_size: int = 64, recurrent: bool = False):
+    """Per-token ridge solve ``(H_t + lambda_t I) x_t = q_t`` (``H_t`` the decayed key covariance).
+    Returns ``(x [B,T,H,D] fp32, H_T [B,H,D,D] fp32)``."""
+    core = TorchScanCore(_cheb_ref, n_state=1, state_shape_fn=_cheb_state_shapes, ridge_ratio=ridge_ratio,
+                         num_iter=num_iter, chunk_size=chunk_size, recurrent=recurrent)
+    state = None if initial_state is None else (initial_state,)
+    x, (hT,) = ssm_scan(core, [q, k, gk], state, sp)
+    return x, hT
 
 
 def gka(q: Tensor, k: Tensor, v: Tensor, alpha: Optional[Tensor], g: Tensor, gk: Optional[Tensor], *,
@@ -60,55 +102,36 @@ def gka(q: Tensor, k: Tensor, v: Tensor, alpha: Optional[Tensor], g: Tensor, gk:
         recurrent: bool = False):
     """GKA core: Chebyshev ridge solve against the running key covariance, alpha-mix, simple GLA.
     Returns ``(o, (h_kk, h_kv))`` with both states ``[B,H,D,D]`` in fp32."""
-    if _lib.use_cuda_kernels(q, k, v):
-        from . import cuda_ops
-        core = cuda_ops.GKACore(scale=scale, ridge_ratio=ridge_ratio, num_iter=num_iter, chunk_size=chunk_size,
-                                recurrent=recurrent)
-    else:
-        core = TorchScanCore(_gka_ref, n_state=2, state_shape_fn=_gka_state_shapes, scale=scale,
-                             ridge_ratio=ridge_ratio, num_iter=num_iter, chunk_size=chunk_size, recurrent=recurrent)
-    state = None
-    if initial_state is not None and initial_state[1] is not None:
-        h_kk0, h_kv0 = initial_state
-        if h_kk0 is None:
-            h_kk0 = torch.zeros(q.shape[0], q.shape[2], q.shape[3], q.shape[3], device=q.device)
-        state = (h_kk0, h_kv0)
-    o, sT = ssm_scan(core, [q, k, v, alpha, g, gk], state, sp)
-    return o, (sT[0] if sT[0].dim() else None, sT[1])
+    h_kk0, h_kv0 = (None, None) if initial_state is None else initial_state
+    h_kk = None
+    qm = q
+    if num_iter > 0:
+        x, h_kk = chebyshev_solve(q, k, gk, ridge_ratio=ridge_ratio, num_iter=num_iter, initial_state=h_kk0, sp=sp,
+                                  chunk_size=chunk_size, recurrent=recurrent)
+        qf = q.float()
+        qm = (qf + alpha.float()[..., None] * (x - qf)) if alpha is not None else x
+        qm = qm.to(q.dtype)
+    o, h_kv = simple_gla(qm, k, v, g, scale=scale, initial_state=h_kv0, sp=sp, chunk_size=chunk_size,
+                         recurrent=recurrent)
+    return o, (h_kk, h_kv)
 
 
 # -- Mamba2 SSD ------------------------------------------------------------------------------
-def _ssd_state_shapes(inputs):
-    x, Bm = inputs[0], inputs[3]
-    return [((x.shape[0], x.shape[2], x.shape[3], Bm.shape[3]), torch.float32)]
-
-
-def _ssd_ref(x, dt, g, Bm, Cm, initial_state=None, chunk_size=256, recurrent=False):
-    H, Gr = x.shape[2], Bm.shape[2]
-    kq = Bm.float().repeat_interleave(H // Gr, dim=2)
-    qq = Cm.float().repeat_interleave(H // Gr, dim=2)
-    v = x.float() * dt.float()[..., None]
-    h0 = None if initial_state is None else initial_state.float().transpose(-1, -2)
-    if recurrent:
-        y, hT = R.simple_gla_recurrent(qq, kq, v, g, scale=1.0, initial_state=h0)
-    else:
-        y, hT = R.simple_gla_chunk(qq, kq, v, g, scale=1.0, initial_state=h0, chunk_size=chunk_size)
-    return y, hT.transpose(-1, -2)
-
-
 def ssd(x: Tensor, dt: Tensor, A: Tensor, Bm: Tensor, Cm: Tensor, D: Optional[Tensor] = None, *,
         initial_state: Optional[Tensor] = None, sp=None, chunk_size: int = 256, recurrent: bool = False):
     """Mamba2 selective state-space scan.  ``x [B,T,H,P]``, ``dt [B,T,H]`` (post-softplus),
-    ``A [H]``, ``Bm,Cm [B,T,G,N]``.  Returns ``(y [B,T,H,P], state [B,H,P,N] fp32)``."""
+    ``A [H]``, ``Bm,Cm [B,T,G,N]``.  Returns ``(y [B,T,H,P], state [B,H,P,N] fp32)``.
+    Evaluated as gated linear attention with ``q=C``, ``k=B``, ``v=dt*x``, ``g=dt*A`` (state transposed)."""
+    H, Gr = x.shape[2], Bm.shape[2]
+    rep = H // Gr
     g = dt.float() * A.float()
-    if _lib.use_cuda_kernels(x, dt, Bm, Cm):
-        from . import cuda_ops
-        core = cuda_ops.SSDCore(chunk_size=chunk_size, recurrent=recurrent)
-    else:
-        core = TorchScanCore(_ssd_ref, n_state=1, state_shape_fn=_ssd_state_shapes, chunk_size=chunk_size,
-                             recurrent=recurrent)
-    state = None if initial_state is None else (initial_state,)
-    y, (sT,) = ssm_scan(core, [x, dt, g, Bm, Cm], state, sp)
+    v = (x.float() * dt.float()[..., None]).to(x.dtype)
+    k = Bm if rep == 1 else Bm.repeat_interleave(rep, dim=2)
+    q = Cm if rep == 1 else Cm.repeat_interleave(rep, dim=2)
+    h0 = None if initial_state is None else initial_state.float().transpose(-1, -2).contiguous()
+    on_cuda = _lib.use_cuda_kernels(x, Bm, Cm)
+    y, hT = simple_gla(q, k, v, g, scale=1.0, initial_state=h0, sp=sp, chunk_size=64 if on_cuda else chunk_size,
+                       recurrent=recurrent)
     if D is not None:
-        y = y + D.float()[None, None, :, None] * x.float()
-    return y, sT
+        y = y.float() + D.float()[None, None, :, None] * x.float()
+    return y, hT.transpose(-1, -2)

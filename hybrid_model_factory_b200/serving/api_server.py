@@ -1,0 +1,150 @@
+"""OpenAI-compatible HTTP front end on the native engine: ``/v1/models``, ``/v1/completions``,
+``/v1/chat/completions`` (optionally SSE streaming) and ``/metrics``.  One background thread drives
+``engine.step()``; handlers enqueue requests and wait on per-request queues.
+Reference surface: ``api/app.py:69-133`` and ``vllm serve`` as used in ``docs/Inference.md``."""
+from __future__ import annotations
+
+import argparse
+import asyncio
+import json
+import threading
+import time
+import uuid
+from typing import Dict, List, Optional
+
+import torch
+
+from ..data.formats import get_template, load_tokenizer
+from ..utils import checkpoint_io
+from .engine import SamplingParams, ServingEngine
+
+
+class EngineLoop:
+    """Runs ``engine.step()`` in a thread and routes new tokens to per-request asyncio queues."""
+
+    def __init__(self, engine: ServingEngine):
+        self.engine = engine
+        self.lock = threading.Lock()
+        self.queues: Dict[int, tuple] = {}
+        self.wake = threading.Event()
+        self.stop = False
+        self.thread = threading.Thread(target=self._run, daemon=True)
+        self.thread.start()
+
+    def submit(self, prompt: List[int], params: SamplingParams, loop) -> tuple:
+        q: asyncio.Queue = asyncio.Queue()
+        with self.lock:
+            rid = self.engine.add_request(prompt, params)
+            self.queues[rid] = (q, loop)
+        self.wake.set()
+        return rid, q
+
+    def _run(self):
+        while not self.stop:
+            with self.lock:
+                busy = self.engine.has_unfinished()
+                results = self.engine.step() if busy else []
+            for rid, tok, done in results:
+                entry = self.queues.get(rid)
+                if entry:
+                    q, loop = entry
+                    loop.call_soon_threadsafe(q.put_nowait, (tok, done))
+                    if done:
+                        self.queues.pop(rid, None)
+            if not busy:
+                self.wake.wait(timeout=0.05)
+                self.wake.clear()
+
+
+def create_app(engine: ServingEngine, tokenizer, model_name: str = "hybrid", template: Optional[str] = None):
+    from fastapi import FastAPI
+    from fastapi.responses import JSONResponse, StreamingResponse
+    app = FastAPI(title="hybrid-model-factory (B200 native) server")
+    loop_runner = EngineLoop(engine)
+    tpl = get_template(template)
+
+    def params_from(body: dict) -> SamplingParams:
+        return SamplingParams(max_new_tokens=int(body.get("max_tokens", 64)), temperature=float(body.get("temperature", 0.0)),
+                              top_k=int(body.get("top_k", 0)), eos_token_id=getattr(tokenizer, "eos_token_id", None),
+                              ignore_eos=bool(body.get("ignore_eos", False)))
+
+    async def run(prompt_ids: List[int], body: dict, chat: bool):
+        rid, q = loop_runner.submit(prompt_ids, params_from(body), asyncio.get_running_loop())
+        created, cid = int(time.time()), f"cmpl-{uuid.uuid4().hex[:12]}"
+        if body.get("stream"):
+            async def gen():
+                while True:
+                    tok, done = await q.get()
+                    text = tokenizer.decode([tok])
+                    delta = {"delta": {"content": text}} if chat else {"text": text}
+                    yield "data: " + json.dumps({"id": cid, "created": created, "model": model_name,
+                                                 "choices": [{"index": 0, **delta, "finish_reason": "length" if done else None}]}) + "\n\n"
+                    if done:
+                        yield "data: [DONE]\n\n"
+                        return
+            return StreamingResponse(gen(), media_type="text/event-stream")
+        toks = []
+        while True:
+            tok, done = await q.get()
+            toks.append(tok)
+            if done:
+                break
+        text = tokenizer.decode(toks)
+        choice = {"index": 0, "finish_reason": "length"}
+        choice.update({"message": {"role": "assistant", "content": text}} if chat else {"text": text})
+        return JSONResponse({"id": cid, "object": "chat.completion" if chat else "text_completion", "created": created,
+                             "model": model_name, "choices": [choice],
+                             "usage": {"prompt_tokens": len(prompt_ids), "completion_tokens": len(toks),
+                                       "total_tokens": len(prompt_ids) + len(toks)}})
+
+    @app.get("/v1/models")
+    async def models():
+        return {"object": "list", "data": [{"id": model_name, "object": "model", "owned_by": "local"}]}
+
+    @app.post("/v1/completions")
+    async def completions(body: dict):
+        prompt = body.get("prompt", "")
+        ids = prompt if isinstance(prompt, list) and prompt and isinstance(prompt[0], int) else tokenizer.encode(
+            prompt if isinstance(prompt, str) else prompt[0], add_special_tokens=False)
+        return await run(list(ids), body, chat=False)
+
+    @app.post("/v1/chat/completions")
+    async def chat(body: dict):
+        msgs = body.get("messages", [])
+        system = next((m["content"] for m in msgs if m["role"] == "system"), "")
+        turns = [m for m in msgs if m["role"] != "system"] + [{"role": "assistant", "content": ""}]
+        pairs = tpl.encode_multiturn(tokenizer, turns, system)
+        ids: List[int] = []
+        for i, (p, r) in enumerate(pairs):
+            ids += p + (r if i < len(pairs) - 1 else [])
+        return await run(ids, body, chat=True)
+
+    @app.get("/metrics")
+    async def metrics():
+        return engine.request_metrics()
+
+    app.state.loop_runner = loop_runner
+    return app
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="hmf serve")
+    ap.add_argument("model")
+    ap.add_argument("--host", default="127.0.0.1")
+    ap.add_argument("--port", type=int, default=8000)
+    ap.add_argument("--max-num-seqs", type=int, default=64)
+    ap.add_argument("--max-num-batched-tokens", type=int, default=8192)
+    ap.add_argument("--max-model-len", type=int, default=32768)
+    ap.add_argument("--enable-prefix-caching", action="store_true")
+    ap.add_argument("--template", default=None)
+    ap.add_argument("--hf-overrides", default=None, help='JSON, e.g. {"gka_overrides": {"num_iter": 10}}')
+    args = ap.parse_args(argv)
+    overrides = json.loads(args.hf_overrides) if args.hf_overrides else {}
+    device = torch.device("cuda", 0) if torch.cuda.is_available() else torch.device("cpu")
+    model = checkpoint_io.from_pretrained(args.model, device=device, **overrides)
+    engine = ServingEngine(model, max_num_seqs=args.max_num_seqs, max_num_batched_tokens=args.max_num_batched_tokens,
+                           max_model_len=args.max_model_len, enable_prefix_caching=args.enable_prefix_caching)
+    import uvicorn
+    uvicorn.run(create_app(engine, load_tokenizer(args.model), model_name=args.model, template=args.template),
+                host=args.host, port=args.port)
+    return 0

@@ -1,0 +1,430 @@
+"""Native serving engine: continuous batching with chunked prefill over paged K/V and slot-indexed
+recurrent state.
+
+Each ``step()`` asks the native scheduler for a batch (decodes first, then prefill chunks), runs
+  * one batched decode forward for all running requests (slot-indexed decode kernels: paged GQA
+    attention, fused GDN recurrent step, Mamba2 state update, conv1d update), and
+  * one forward per scheduled prefill chunk through the training-path kernels with the slot's state
+    as the initial state (``SlotCache``),
+samples one token per request that reached the end of its known tokens, and returns the new tokens.
+
+This replaces what the reference obtains from vLLM (scheduler, hybrid KV-cache manager, model
+runner; ``vllm-inference/src/primed_vllm`` + ``docs/Inference.md``).
+"""
+from __future__ import annotations
+
+import ctypes
+import itertools
+import time
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence
+
+import torch
+import torch.nn.functional as F
+
+from ..layers.attention import Attention
+from ..layers.gdn import GatedDeltaNet
+from ..layers.gka import GatedKalmaNet
+from ..layers.mamba2 import Mamba2
+from ..ops import _lib
+from ..ops import functional as F_ops
+from ..ops import reference as R
+from .cache import ServingState, SlotCache
+from .scheduler import NativeScheduler, ScheduledSeq
+
+c_int, c_ll, c_float = ctypes.c_int, ctypes.c_longlong, ctypes.c_float
+
+
+@dataclass
+class SamplingParams:
+    max_new_tokens: int = 16
+    temperature: float = 0.0
+    top_k: int = 0
+    eos_token_id: Optional[int] = None
+    ignore_eos: bool = True
+
+
+@dataclass
+class RequestState:
+    req_id: int
+    prompt: List[int]
+    params: SamplingParams
+    output: List[int] = field(default_factory=list)
+    arrival: float = 0.0
+    first_token_time: Optional[float] = None
+    finish_time: Optional[float] = None
+    finished: bool = False
+
+
+class ServingEngine:
+    def __init__(self, model, *, block_size: int = 64, num_blocks: Optional[int] = None, max_num_seqs: int = 64,
+                 max_num_batched_tokens: int = 8192, enable_prefix_caching: bool = False, max_model_len: int = 32768,
+                 gpu_memory_utilization: float = 0.85, tp=None):
+        self.model = model.eval()
+        self.cfg = model.config
+        self.device = next(model.parameters()).device
+        self.tp = tp
+        self.block_size = block_size
+        has_ssm = any(not isinstance(l.seq_mixer, Attention) for l in model.model.layers)
+        n_attn = sum(isinstance(l.seq_mixer, Attention) for l in model.model.layers)
+        if num_blocks is None:
+            num_blocks = self._plan_blocks(n_attn, block_size, max_num_seqs, max_model_len, gpu_memory_utilization)
+        snapshots = max_num_seqs if (enable_prefix_caching and has_ssm) else 0
+        self.state = ServingState(model, num_blocks, block_size, max_num_seqs, snapshots, self.device,
+                                  dtype=next(model.parameters()).dtype)
+        self.sched = NativeScheduler(num_blocks, block_size, max_num_seqs, max_num_seqs, max_num_batched_tokens,
+                                     enable_prefix_caching, snapshots, require_snapshot=has_ssm)
+        self.prefix_caching = enable_prefix_caching
+        self.requests: Dict[int, RequestState] = {}
+        self._ids = itertools.count()
+        self._cuda = self.device.type == "cuda" and _lib.kernels_available()
+        self._layer_cache: Dict[int, dict] = {}
+        self.max_blocks_per_seq = (max_model_len + block_size - 1) // block_size
+        self.stats = {"steps": 0, "decode_tokens": 0, "prefill_tokens": 0}
+
+    def _plan_blocks(self, n_attn, block_size, max_seqs, max_len, util) -> int:
+        need = max_seqs * ((max_len + block_size - 1) // block_size)
+        if self.device.type != "cuda" or n_attn == 0:
+            return max(need if n_attn else 8, 8)
+        free, total = torch.cuda.mem_get_info(self.device)
+        a = next(l.seq_mixer for l in self.model.model.layers if isinstance(l.seq_mixer, Attention))
+        per_block = 2 * block_size * a.num_kv_heads * a.head_dim * 2 * n_attn
+        budget = int(free - (1 - util) * total)
+        return int(max(64, min(need, budget // max(per_block, 1))))
+
+    # -- request API -----------------------------------------------------------------------
+    def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None) -> int:
+        params = params or SamplingParams()
+        rid = next(self._ids)
+        self.requests[rid] = RequestState(rid, list(prompt), params, arrival=time.perf_counter())
+        self.sched.add_request(rid, list(prompt), params.max_new_tokens)
+        return rid
+
+    def has_unfinished(self) -> bool:
+        return any(not r.finished for r in self.requests.values())
+
+    def generate(self, prompts: Sequence[Sequence[int]], params: Optional[SamplingParams] = None) -> List[List[int]]:
+        ids = [self.add_request(p, params) for p in prompts]
+        while any(not self.requests[i].finished for i in ids):
+            self.step()
+        return [self.requests[i].output for i in ids]
+
+    # -- one engine step -------------------------------------------------------------------
+    @torch.no_grad()
+    def step(self) -> List[tuple]:
+        batch = self.sched.step()
+        if not batch:
+            return []
+        self.stats["steps"] += 1
+        decodes = [s for s in batch if s.is_decode and self._at_frontier(s)]
+        prefills = [s for s in batch if s not in decodes]
+        results = []
+        if decodes:
+            logits = self._decode_forward(decodes)
+            toks = self._sample(logits, [self.requests[s.req_id].params for s in decodes])
+            for s, t in zip(decodes, toks):
+                self.sched.advance(s.req_id, 1)
+                results.append(self._emit(s.req_id, int(t)))
+            self.stats["decode_tokens"] += len(decodes)
+        for s in prefills:
+            req = self.requests[s.req_id]
+            tokens = (req.prompt + req.output)[s.start_pos:s.start_pos + s.num_tokens]
+            if s.restore_from >= 0:
+                self.state.copy_slot(s.restore_from, s.slot)
+            logits = self._prefill_forward(s, tokens)
+            self.sched.advance(s.req_id, s.num_tokens)
+            self.stats["prefill_tokens"] += s.num_tokens
+            end = s.start_pos + s.num_tokens
+            if self.prefix_caching and self.state.ssm and end % self.block_size == 0 and end < len(req.prompt):
+                snap = self.sched.register_snapshot(s.req_id, end)
+                if snap >= 0:
+                    self.state.copy_slot(s.slot, snap)
+            if end >= len(req.prompt) + len(req.output):
+                tok = self._sample(logits[-1:], [req.params])[0]
+                results.append(self._emit(s.req_id, int(tok)))
+        return results
+
+    def _at_frontier(self, s: ScheduledSeq) -> bool:
+        req = self.requests[s.req_id]
+        return s.start_pos == len(req.prompt) + len(req.output) - 1
+
+    def _emit(self, rid: int, tok: int):
+        req = self.requests[rid]
+        now = time.perf_counter()
+        if req.first_token_time is None:
+            req.first_token_time = now
+        req.output.append(tok)
+        self.sched.append_token(rid, tok)
+        p = req.params
+        done = len(req.output) >= p.max_new_tokens or (not p.ignore_eos and p.eos_token_id is not None
+                                                       and tok == p.eos_token_id)
+        if done:
+            req.finished, req.finish_time = True, now
+            self.sched.finish(rid)
+        return (rid, tok, done)
+
+    # -- sampling ------------------------------------------------------------------------------
+    def _sample(self, logits: torch.Tensor, params: List[SamplingParams]) -> List[int]:
+        if all(p.temperature <= 0 for p in params):
+            if self._cuda and logits.is_cuda:
+                ids = torch.empty(logits.shape[0], dtype=torch.long, device=logits.device)
+                lg = logits.contiguous()
+                _lib.check(_lib.kernels().hmf_argmax(_lib.ptr(lg), c_int(int(lg.dtype == torch.bfloat16)), _lib.ptr(ids),
+                                                     c_int(lg.shape[0]), c_int(lg.shape[1]), c_ll(lg.stride(0)),
+                                                     _lib.stream_ptr(lg.device)), "argmax")
+                if lg.dtype not in (torch.bfloat16, torch.float32):
+                    ids = lg.float().argmax(-1)
+                return ids.tolist()
+            return logits.float().argmax(-1).tolist()
+        out = []
+        for row, p in zip(logits.float(), params):
+            if p.temperature <= 0:
+                out.append(int(row.argmax()))
+                continue
+            row = row / p.temperature
+            if p.top_k:
+                kth = torch.topk(row, p.top_k).values[-1]
+                row = row.masked_fill(row < kth, float("-inf"))
+            out.append(int(torch.multinomial(torch.softmax(row, -1), 1)))
+        return out
+
+    # -- prefill (per request chunk) -------------------------------------------------------------
+    def _prefill_forward(self, s: ScheduledSeq, tokens: List[int]) -> torch.Tensor:
+        ids = torch.tensor([tokens], dtype=torch.long, device=self.device)
+        pos = torch.arange(s.start_pos, s.start_pos + len(tokens), device=self.device)[None]
+        cache = SlotCache(self.state, s.slot, self.sched.block_table(s.req_id), s.start_pos)
+        h, _ = self.model.model(ids, position_ids=pos, past_key_values=cache, use_cache=True)
+        return self._logits(h[0, -1:])
+
+    def _logits(self, h: torch.Tensor) -> torch.Tensor:
+        logits = self.model.lm_head(h)
+        if self.tp is not None:
+            logits = self.tp.gather_logits(logits)
+        return logits
+
+    # -- batched decode ----------------------------------------------------------------------------
+    def _decode_forward(self, seqs: List[ScheduledSeq]) -> torch.Tensor:
+        m = self.model.model
+        dev = self.device
+        Rn = len(seqs)
+        last = [(self.requests[s.req_id].prompt + self.requests[s.req_id].output)[s.start_pos] for s in seqs]
+        ids = torch.tensor(last, dtype=torch.long, device=dev)
+        pos = torch.tensor([s.start_pos for s in seqs], dtype=torch.long, device=dev)
+        slots = torch.tensor([s.slot for s in seqs], dtype=torch.int32, device=dev)
+        x = m.embed_tokens(ids)                                    # [R, Dm]
+        cos, sin = m.rotary_emb(pos[:, None])                        # [R, 1, rot]
+        cos, sin = cos.to(x.dtype), sin.to(x.dtype)
+        meta = None
+        if self.state.kv:
+            bs = self.block_size
+            tables = [self.sched.block_table(s.req_id) for s in seqs]
+            mb = max(len(t) for t in tables)
+            bt = torch.zeros(Rn, mb, dtype=torch.int32)
+            for i, t in enumerate(tables):
+                bt[i, :len(t)] = torch.tensor(t, dtype=torch.int32)
+            bt = bt.to(dev)
+            slot_map = (bt[torch.arange(Rn), (pos // bs).to(torch.long)].to(torch.long) * bs + pos % bs)
+            meta = {"bt": bt, "mb": mb, "slot_map": slot_map.contiguous(), "lens": (pos + 1).to(torch.int32)}
+        for i, layer in enumerate(m.layers):
+            h = layer.input_layernorm(x)
+            mixer = layer.seq_mixer
+            if isinstance(mixer, Attention):
+                y = self._attn_decode(i, mixer, h, cos, sin, meta)
+            elif isinstance(mixer, GatedDeltaNet):
+                y = self._gdn_decode(i, mixer, h, slots)
+            elif isinstance(mixer, Mamba2):
+                y = self._mamba_decode(i, mixer, h, cos, sin, slots)
+            elif isinstance(mixer, GatedKalmaNet):
+                y = self._gka_decode(i, mixer, h, slots)
+            else:
+                raise NotImplementedError(type(mixer).__name__)
+            if self.tp is not None:
+                y = self.tp.all_reduce(y)
+            x = x + y
+            h2 = layer.post_attention_layernorm(x)
+            y2 = layer.mlp(h2)
+            y2 = y2[0] if isinstance(y2, tuple) else y2
+            if self.tp is not None:
+                y2 = self.tp.all_reduce(y2)
+            x = x + y2
+        return self._logits(m.norm(x))
+
+    def _attn_decode(self, i, mx: Attention, h, cos, sin, meta):
+        Rn = h.shape[0]
+        q = mx.q_proj(h)
+        gate = None
+        if mx.gated:
+            q = q.view(Rn, mx.num_heads, 2 * mx.head_dim)
+            q, gate = q[..., :mx.head_dim], q[..., mx.head_dim:].reshape(Rn, -1)
+        q = q.reshape(Rn, 1, mx.num_heads, mx.head_dim)
+        k = mx.k_proj(h).view(Rn, 1, mx.num_kv_heads, mx.head_dim)
+        v = mx.v_proj(h).view(Rn, mx.num_kv_heads, mx.head_dim)
+        if mx.q_norm is not None:
+            q, k = mx.q_norm(q), mx.k_norm(k)
+        q, k = F_ops.apply_rope(q, cos, sin)[:, 0], F_ops.apply_rope(k, cos, sin)[:, 0]
+        kc, vc = self.state.kv[i]
+        window = mx.sliding_window or 0
+        if self._cuda and mx.head_dim == 128 and q.dtype == torch.bfloat16:
+            K = _lib.kernels()
+            k, v, q = k.contiguous(), v.contiguous(), q.contiguous()
+            _lib.check(K.hmf_cache_append(_lib.ptr(k), _lib.ptr(v), _lib.ptr(kc), _lib.ptr(vc), _lib.ptr(meta["slot_map"]),
+                                          c_ll(Rn), c_int(mx.num_kv_heads), c_int(mx.head_dim), c_ll(k.stride(0)),
+                                          c_ll(v.stride(0)), _lib.stream_ptr(h.device)), "cache_append")
+            splits = 8 if int(meta["lens"].max()) > 4096 else (4 if int(meta["lens"].max()) > 1024 else 1)
+            o = torch.empty(Rn, mx.num_heads, mx.head_dim, device=h.device, dtype=h.dtype)
+            po = torch.empty(Rn, mx.num_heads, splits, mx.head_dim, device=h.device, dtype=torch.float32)
+            pml = torch.empty(Rn, mx.num_heads, splits, 2, device=h.device, dtype=torch.float32)
+            _lib.check(K.hmf_paged_attention_decode(_lib.ptr(q), _lib.ptr(kc), _lib.ptr(vc), _lib.ptr(meta["bt"]),
+                                                    _lib.ptr(meta["lens"]), _lib.ptr(o), _lib.ptr(po), _lib.ptr(pml),
+                                                    c_int(Rn), c_int(mx.num_heads), c_int(mx.num_kv_heads),
+                                                    c_int(mx.head_dim), c_int(self.block_size), c_int(meta["mb"]),
+                                                    c_int(splits), c_int(window), c_float(mx.scaling),
+                                                    _lib.stream_ptr(h.device)), "paged_attention_decode")
+        else:
+            kc.view(-1, *kc.shape[2:])[meta["slot_map"]] = k
+            vc.view(-1, *vc.shape[2:])[meta["slot_map"]] = v
+            outs = []
+            bs = self.block_size
+            for r in range(Rn):
+                L = int(meta["lens"][r])
+                p_ = torch.arange(L, device=h.device)
+                flat = meta["bt"][r].long()[p_ // bs] * bs + p_ % bs
+                kk, vv = kc.view(-1, *kc.shape[2:])[flat][None], vc.view(-1, *vc.shape[2:])[flat][None]
+                outs.append(R.attention(q[r][None, None], kk, vv, scale=mx.scaling, window=window or None)[0, 0])
+            o = torch.stack(outs)
+        o = o.reshape(Rn, -1)
+        if gate is not None:
+            o = o * torch.sigmoid(gate)
+        return mx.o_proj(o)
+
+    def _conv_update(self, i, x_cat, weight, bias, slots):
+        e = self.state.ssm[i]
+        if self._cuda and x_cat.dtype == torch.bfloat16:
+            from ..ops import cuda_ops
+            y, _ = cuda_ops.causal_conv1d_update(x_cat, e["conv"], weight, bias, "silu", slots)
+            return y
+        st = e["conv"][slots.long()]
+        y, new = R.causal_conv1d_update(x_cat, st, weight, bias, "silu")
+        e["conv"][slots.long()] = new.to(e["conv"].dtype)
+        return y
+
+    def _layer_consts(self, i, mixer):
+        c = self._layer_cache.get(i)
+        if c is None:
+            if isinstance(mixer, (GatedDeltaNet, GatedKalmaNet)):
+                convs = [mixer.q_conv1d, mixer.k_conv1d] + ([mixer.v_conv1d] if getattr(mixer, "use_v_conv", True) else [])
+                w = torch.cat([cv.weight for cv in convs], dim=0).squeeze(1).contiguous()
+                b = None
+                if convs[0].bias is not None:
+                    b = torch.cat([cv.bias for cv in convs]).contiguous()
+                c = {"w": w, "b": b}
+            else:
+                c = {"w": mixer.conv1d.weight.squeeze(1).contiguous(), "b": mixer.conv1d.bias}
+            self._layer_cache[i] = c
+        return c
+
+    def _gdn_decode(self, i, mx: GatedDeltaNet, h, slots):
+        Rn = h.shape[0]
+        c = self._layer_consts(i, mx)
+        qkv = torch.cat([mx.q_proj(h), mx.k_proj(h), mx.v_proj(h)], dim=-1)
+        qkv = self._conv_update(i, qkv, c["w"], c["b"], slots)
+        q, k, v = torch.split(qkv, [mx.query_dim, mx.key_dim, mx.value_dim], dim=-1)
+        g, beta = R.gdn_gating(mx.gk_proj(h), mx.b_proj(h), mx.A_log, mx.dt_bias, 2.0 if mx.allow_neg_eigval else 1.0)
+        H, D = mx.expanded_num_heads, mx.head_dim
+        st = self.state.ssm[i]["state"]
+        if self._cuda and D == 128 and h.dtype == torch.bfloat16 and mx.kv_proj_rank is None:
+            o = torch.empty(Rn, H, D, device=h.device, dtype=h.dtype)
+            _lib.check(_lib.kernels().hmf_gdn_decode(
+                _lib.ptr(q.contiguous()), _lib.ptr(k.contiguous()), _lib.ptr(v.contiguous()),
+                _lib.ptr(g.float().contiguous()), _lib.ptr(beta.float().contiguous()), _lib.ptr(st), _lib.ptr(slots),
+                _lib.ptr(o), c_int(Rn), c_int(H), c_int(mx.num_q_heads), c_int(mx.num_k_heads), c_int(mx.num_v_heads),
+                c_int(D), c_int(D), c_float(D ** -0.5), c_int(1), _lib.stream_ptr(h.device)), "gdn_decode")
+        else:
+            from ..layers.common import repeat_heads
+            qh = repeat_heads(q.reshape(Rn, 1, mx.num_q_heads, D), mx.num_q_groups)
+            kh, vh = mx._expand_kv(k[:, None], v[:, None])
+            s0 = st[slots.long()]
+            o, sT = R.gated_delta_rule_recurrent(qh, kh, vh, g[:, None], beta[:, None], initial_state=s0)
+            st[slots.long()] = sT
+            o = o[:, 0].to(h.dtype)
+        if mx.use_gate:
+            o = mx.o_norm(o, mx.g_proj(h).view(Rn, H, D))
+        else:
+            o = mx.o_norm(o)
+        return mx.o_proj(o.reshape(Rn, -1))
+
+    def _mamba_decode(self, i, mx: Mamba2, h, cos, sin, slots):
+        Rn = h.shape[0]
+        c = self._layer_consts(i, mx)
+        z, xBC, dt = torch.split(mx.in_proj(h), [mx.d_inner, mx.conv_dim, mx.nheads], dim=-1)
+        xBC = mx._norm_rope(xBC[:, None], (cos, sin))[:, 0]
+        xBC = self._conv_update(i, xBC.contiguous(), c["w"], c["b"], slots)
+        x, Bm, Cm = torch.split(xBC, [mx.d_xb, mx.d_xb, mx.d_inner], dim=-1)
+        A = -torch.exp(mx.A_log.float())
+        dtp = F.softplus(dt.float() + mx.dt_bias.float())
+        st = self.state.ssm[i]["state"]
+        Hx = mx.d_xb // mx.headdim
+        if self._cuda and h.dtype == torch.bfloat16:
+            y = torch.empty(Rn, mx.nheads, mx.headdim, device=h.device, dtype=h.dtype)
+            _lib.check(_lib.kernels().hmf_ssd_decode(
+                _lib.ptr(x.contiguous()), _lib.ptr(dtp.contiguous()), _lib.ptr(A.contiguous()), _lib.ptr(Bm.contiguous()),
+                _lib.ptr(Cm.contiguous()), _lib.ptr(mx.D.float().contiguous()), _lib.ptr(st), _lib.ptr(slots), _lib.ptr(y),
+                c_int(Rn), c_int(mx.nheads), c_int(Hx), c_int(Hx), c_int(mx.headdim), c_int(mx.d_state),
+                _lib.stream_ptr(h.device)), "ssd_decode")
+        else:
+            from ..layers.common import repeat_heads
+            xh = repeat_heads(x.reshape(Rn, 1, Hx, mx.headdim), mx.num_kv_groups)[:, 0]
+            Bh = repeat_heads(Bm.reshape(Rn, 1, Hx, mx.d_state), mx.num_kv_groups)[:, 0]
+            Ch = Cm.reshape(Rn, mx.ngroups, mx.d_state)
+            s0 = st[slots.long()]
+            y, sT = R.selective_state_update(s0, xh, dtp, A, Bh, Ch, mx.D)
+            st[slots.long()] = sT
+            y = y.to(h.dtype)
+        zg = z.reshape(Rn, mx.nheads, mx.headdim)
+        y = F_ops.gated_rms_norm(y, zg, mx.norm.weight.view(mx.nheads, mx.headdim), mx.norm.eps, norm_before_gate=False)
+        return mx.out_proj(y.reshape(Rn, mx.d_inner))
+
+    def _gka_decode(self, i, mx: GatedKalmaNet, h, slots):
+        """GKA decode: conv update + token-level solve and GLA update on the slot states."""
+        from ..layers.common import repeat_heads
+        Rn = h.shape[0]
+        c = self._layer_consts(i, mx)
+        e = self.state.ssm[i]
+        parts = [mx.q_proj(h), mx.k_proj(h)] + ([mx.v_proj(h)] if mx.use_v_conv else [])
+        x = self._conv_update(i, torch.cat(parts, dim=-1), c["w"], c["b"], slots)
+        outs = torch.split(x, [p.shape[-1] for p in parts], dim=-1)
+        q, k = outs[0], outs[1]
+        v = outs[2] if mx.use_v_conv else mx.v_proj(h)
+        D = mx.head_dim
+        q = repeat_heads(q.reshape(Rn, 1, mx.num_q_heads, D), mx.num_q_groups)
+        k, v = mx._expand_kv(k[:, None], v[:, None])
+        eps = 1e-6
+        q = q.float() / (torch.linalg.vector_norm(q.float(), dim=-1, keepdim=True) + eps)
+        k = k.float() / (torch.linalg.vector_norm(k.float(), dim=-1, keepdim=True) + eps)
+        v = v.float()
+        if mx.use_beta_gate:
+            beta = torch.sigmoid(mx.b_proj(h)).float()[:, None]
+            k, v = (beta[..., None] + eps) * k, (beta[..., None] + eps) * v
+        alpha = torch.sigmoid(mx.alpha_proj(h)).float()[:, None] if mx.use_alpha_connection else None
+        g = (-mx.A_log.float().exp() * F.softplus(mx.a_proj(h).float() + mx.dt_bias.float()))[:, None]
+        gk = g if mx.use_forgetting_gate_kk else None
+        sl = slots.long()
+        o, (h_kk, h_kv) = R.gka_forward(q, k, v, alpha, g, gk, scale=mx.gla_scale, ridge_ratio=mx.ridge_strength,
+                                        num_iter=mx.num_iter, initial_state=(e["state_kk"][sl], e["state"][sl]),
+                                        recurrent=True)
+        if h_kk is not None:
+            e["state_kk"][sl] = h_kk
+        e["state"][sl] = h_kv
+        o = o[:, 0].to(h.dtype)
+        H = mx.expanded_num_heads
+        o = mx.o_norm(o, mx.g_proj(h).view(Rn, H, D)) if mx.use_gate else mx.o_norm(o)
+        return mx.o_proj(o.reshape(Rn, -1))
+
+    # -- metrics ---------------------------------------------------------------------------------------
+    def request_metrics(self) -> dict:
+        done = [r for r in self.requests.values() if r.finished]
+        ttft = sorted((r.first_token_time - r.arrival) * 1e3 for r in done if r.first_token_time)
+        out_tokens = sum(len(r.output) for r in done)
+        return {"finished": len(done), "output_tokens": out_tokens,
+                "p50_ttft_ms": ttft[len(ttft) // 2] if ttft else None,
+                "mean_ttft_ms": sum(ttft) / len(ttft) if ttft else None, **self.sched.stats(), **self.stats}

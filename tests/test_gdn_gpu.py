@@ -70,3 +70,34 @@ def test_gdn_prep_kernel_matches_torch_prep():
         gdn_cuda._FORCE_TORCH_PREP = old
     for name, x, y in zip(["wqT", "kPT", "uT", "glast"], a[:4], b[:4]):
         assert _rel(x, y) < 2e-2, f"{name}: {_rel(x, y)}"
+
+
+def test_simple_gla_kernel_mode():
+    q, k, v, g, _ = _inputs(2, 500, 3)
+    q = (q.float() * 0.3).bfloat16()
+    h0 = torch.randn(2, 3, 128, 128, device=DEV) * 0.1
+    leaves = [t.clone().requires_grad_(True) for t in (q, k, v, g)]
+    refs = [t.float().clone().requires_grad_(True) for t in (q, k, v, g)]
+    o, s = mixers.simple_gla(*leaves, scale=0.1, initial_state=h0)
+    orf, sr = R.simple_gla_chunk(*refs, scale=0.1, initial_state=h0)
+    assert _rel(o, orf) < 3e-2 and _rel(s, sr) < 3e-2
+    do = torch.randn_like(orf)
+    torch.autograd.backward([o], [do.to(o.dtype)])
+    torch.autograd.backward([orf], [do])
+    for n, a, b in zip("qkvg", leaves, refs):
+        assert _rel(a.grad, b.grad) < 5e-2, f"d{n}: {_rel(a.grad, b.grad)}"
+
+
+def test_ssd_matches_reference():
+    B, T, H, P, G, N = 1, 700, 4, 128, 4, 128
+    x = torch.randn(B, T, H, P, device=DEV).bfloat16()
+    dt = torch.rand(B, T, H, device=DEV) * 0.3
+    A = -torch.rand(H, device=DEV)
+    Bm = (torch.randn(B, T, G, N, device=DEV) * 0.3).bfloat16()
+    Cm = (torch.randn(B, T, G, N, device=DEV) * 0.3).bfloat16()
+    Dp = torch.randn(H, device=DEV)
+    h0 = torch.randn(B, H, P, N, device=DEV) * 0.1
+    y, s = mixers.ssd(x, dt, A, Bm, Cm, Dp, initial_state=h0)
+    yr, sr = R.ssd_chunk(x.float(), dt, A, Bm.float(), Cm.float(), Dp, initial_state=h0, chunk_size=64)
+    assert _rel(y, yr) < 3e-2, _rel(y, yr)
+    assert _rel(s, sr) < 3e-2, _rel(s, sr)
