@@ -82,7 +82,8 @@ def fused_add_rms_norm(x: Tensor, residual: Tensor, weight: Tensor, eps: float) 
     D = x.shape[-1]
     x2, r2 = x.reshape(-1, D).contiguous(), residual.reshape(-1, D).contiguous()
     y, r_out = torch.empty_like(x2), torch.empty_like(x2)
-    _lib.check(_K().hmf_rms_norm_fwd(_lib.ptr(x2), _lib.ptr(r2), _lib.ptr(weight.contiguous()), _lib.ptr(y),
+    weight = weight.contiguous()
+    _lib.check(_K().hmf_rms_norm_fwd(_lib.ptr(x2), _lib.ptr(r2), _lib.ptr(weight), _lib.ptr(y),
                                      _lib.ptr(r_out), None, c_ll(x2.shape[0]), c_int(D), c_float(eps), c_int(0), _st(x)),
                "fused_add_rms_norm")
     return y.view(x.shape), r_out.view(x.shape)
@@ -257,7 +258,8 @@ def causal_conv1d_update(x, conv_state, weight, bias=None, activation="silu", sl
     B, C = x.shape
     y = torch.empty_like(x)
     state = conv_state if conv_state.is_contiguous() else conv_state.contiguous()
-    _lib.check(_K().hmf_conv1d_update(_lib.ptr(x.contiguous()), _lib.ptr(state), _lib.ptr(weight.contiguous()),
+    x, weight = x.contiguous(), weight.contiguous()
+    _lib.check(_K().hmf_conv1d_update(_lib.ptr(x), _lib.ptr(state), _lib.ptr(weight),
                                       _lib.ptr(bias), _lib.ptr(y), _lib.ptr(slots), c_int(B), c_int(C), c_int(4),
                                       c_int(1 if activation in ("silu", "swish") else 0), _st(x)), "conv1d_update")
     return y, state

@@ -152,9 +152,11 @@ class GDNChunkCore(ScanCore):
             q, k, v = (t if tma_ok(t) else t.contiguous() for t in (q, k, v))
             scale = Dk ** -0.5 if self.scale is None else self.scale
             ll = ctypes.c_longlong
+            g32 = g.float().contiguous()        # held in locals: a temporary's block could be reused before the launch
+            b32 = None if self.gla else beta.float().contiguous()
             rc = _lib.kernels().hmf_gdn_prep(
-                _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(g.float().contiguous()),
-                _lib.ptr(None if self.gla else beta.float().contiguous()), _lib.ptr(wqT), _lib.ptr(kPT), _lib.ptr(uT), _lib.ptr(glast),
+                _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(g32),
+                _lib.ptr(b32), _lib.ptr(wqT), _lib.ptr(kPT), _lib.ptr(uT), _lib.ptr(glast),
                 c_int(B), c_int(T), c_int(H), c_int(k.shape[2]), c_int(v.shape[2]), c_int(N),
                 ll(q.stride(0)), ll(q.stride(1)), ll(q.stride(2)), ll(k.stride(0)), ll(k.stride(1)), ll(k.stride(2)),
                 ll(v.stride(0)), ll(v.stride(1)), ll(v.stride(2)), ctypes.c_float(scale),
@@ -243,8 +245,9 @@ class GDNChunkCore(ScanCore):
                 d_P = torch.tril((do_c @ vnT_g).float())
                 d_kt = (vnT_g.transpose(-1, -2) @ dS_g).float()
                 d_gl = torch.exp(flat(gl5)) * (dS_g.float() * h_g.float()).sum((-1, -2))
-            torch.autograd.backward([f["w"], f["qt"], f["kt"], f["P"], f["u"], f["glast"]],
-                                    [d_w, d_qt, d_kt, d_P, d_u, d_gl])
+            pairs = [(f[n], d) for n, d in (("w", d_w), ("qt", d_qt), ("kt", d_kt), ("P", d_P), ("u", d_u),
+                                            ("glast", d_gl)) if f[n].requires_grad]   # gla mode: w is constant 0
+            torch.autograd.backward([p[0] for p in pairs], [p[1].to(p[0].dtype) for p in pairs])
             with torch.no_grad():
                 dq[:, :, hs], dk[:, :, hs], dv[:, :, hs] = leaves[0].grad, leaves[1].grad, leaves[2].grad
                 dg[:, :, hs] = leaves[3].grad

@@ -148,3 +148,7 @@ def main(argv=None) -> int:
     uvicorn.run(create_app(engine, load_tokenizer(args.model), model_name=args.model, template=args.template),
                 host=args.host, port=args.port)
     return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

@@ -28,6 +28,12 @@ def run(model, num_requests=64, prompt_min=4096, prompt_max=16384, output_len=51
                            max_num_batched_tokens=max_num_batched_tokens, max_model_len=prompt_max + output_len + 64,
                            tp=tp)
     params = SamplingParams(max_new_tokens=output_len, temperature=0.0)
+    # untimed warm-up: graph capture for every decode bucket and one short request through prefill + decode
+    engine.warmup(prompt_max + output_len)
+    engine.generate([prompts[0][:prompt_min]], SamplingParams(max_new_tokens=4))
+    engine.requests.clear()
+    for k in engine.stats:
+        engine.stats[k] = type(engine.stats[k])()
     if torch.cuda.is_available():
         torch.cuda.synchronize()
     t0 = time.perf_counter()
@@ -46,7 +52,8 @@ def run(model, num_requests=64, prompt_min=4096, prompt_max=16384, output_len=51
             "wall_s": dt, "output_tok_per_s": m["output_tokens"] / dt,
             "decode_tok_per_s_after_prefill": decode_tokens / max(dt - first_done, 1e-9),
             "p50_ttft_ms": ttft[len(ttft) // 2], "mean_ttft_ms": sum(ttft) / len(ttft), "p99_ttft_ms": ttft[-1],
-            "engine_steps": m["steps"]}
+            "engine_steps": m["steps"], "decode_ms_per_step": 1e3 * m["decode_s"] / max(m["decode_steps"], 1),
+            "prefill_tok_per_s": m["prefill_tokens"] / max(m["prefill_s"], 1e-9), "graphs": len(engine._graphs)}
 
 
 def main(argv=None) -> int:
@@ -74,3 +81,7 @@ def main(argv=None) -> int:
               max_num_batched_tokens=args.max_num_batched_tokens)
     print(json.dumps(res))
     return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

@@ -44,3 +44,7 @@ def main(argv=None) -> int:
         print("Assistant:", reply)
         history.append({"role": "assistant", "content": reply})
     return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

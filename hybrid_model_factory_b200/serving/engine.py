@@ -59,7 +59,7 @@ class RequestState:
 class ServingEngine:
     def __init__(self, model, *, block_size: int = 64, num_blocks: Optional[int] = None, max_num_seqs: int = 64,
                  max_num_batched_tokens: int = 8192, enable_prefix_caching: bool = False, max_model_len: int = 32768,
-                 gpu_memory_utilization: float = 0.85, tp=None):
+                 gpu_memory_utilization: float = 0.85, tp=None, use_cuda_graphs: bool = True):
         self.model = model.eval()
         self.cfg = model.config
         self.device = next(model.parameters()).device
@@ -70,8 +70,10 @@ class ServingEngine:
         if num_blocks is None:
             num_blocks = self._plan_blocks(n_attn, block_size, max_num_seqs, max_model_len, gpu_memory_utilization)
         snapshots = max_num_seqs if (enable_prefix_caching and has_ssm) else 0
-        self.state = ServingState(model, num_blocks, block_size, max_num_seqs, snapshots, self.device,
+        # one extra block and one extra slot absorb the padding rows of a bucketed (graph-captured) decode batch
+        self.state = ServingState(model, num_blocks + 1, block_size, max_num_seqs, snapshots + 1, self.device,
                                   dtype=next(model.parameters()).dtype)
+        self._pad_block, self._pad_slot = num_blocks, max_num_seqs + snapshots
         self.sched = NativeScheduler(num_blocks, block_size, max_num_seqs, max_num_seqs, max_num_batched_tokens,
                                      enable_prefix_caching, snapshots, require_snapshot=has_ssm)
         self.prefix_caching = enable_prefix_caching
@@ -80,7 +82,12 @@ class ServingEngine:
         self._cuda = self.device.type == "cuda" and _lib.kernels_available()
         self._layer_cache: Dict[int, dict] = {}
         self.max_blocks_per_seq = (max_model_len + block_size - 1) // block_size
-        self.stats = {"steps": 0, "decode_tokens": 0, "prefill_tokens": 0}
+        self.stats = {"steps": 0, "decode_tokens": 0, "prefill_tokens": 0, "graph_replays": 0, "decode_steps": 0,
+                      "decode_s": 0.0, "prefill_s": 0.0}
+        has_moe = any(hasattr(l.mlp, "experts") for l in model.model.layers)
+        self._use_graphs = bool(use_cuda_graphs and self._cuda and not has_moe)
+        self._graphs: Dict[tuple, dict] = {}
+        self._tables: Dict[int, torch.Tensor] = {}
 
     def _plan_blocks(self, n_attn, block_size, max_seqs, max_len, util) -> int:
         need = max_seqs * ((max_len + block_size - 1) // block_size)
@@ -119,6 +126,7 @@ class ServingEngine:
         decodes = [s for s in batch if s.is_decode and self._at_frontier(s)]
         prefills = [s for s in batch if s not in decodes]
         results = []
+        t0 = time.perf_counter()
         if decodes:
             logits = self._decode_forward(decodes)
             toks = self._sample(logits, [self.requests[s.req_id].params for s in decodes])
@@ -126,6 +134,9 @@ class ServingEngine:
                 self.sched.advance(s.req_id, 1)
                 results.append(self._emit(s.req_id, int(t)))
             self.stats["decode_tokens"] += len(decodes)
+            self.stats["decode_steps"] += 1
+            self.stats["decode_s"] += time.perf_counter() - t0
+        t0 = time.perf_counter()
         for s in prefills:
             req = self.requests[s.req_id]
             tokens = (req.prompt + req.output)[s.start_pos:s.start_pos + s.num_tokens]
@@ -142,6 +153,8 @@ class ServingEngine:
             if end >= len(req.prompt) + len(req.output):
                 tok = self._sample(logits[-1:], [req.params])[0]
                 results.append(self._emit(s.req_id, int(tok)))
+        if prefills:
+            self.stats["prefill_s"] += time.perf_counter() - t0
         return results
 
     def _at_frontier(self, s: ScheduledSeq) -> bool:
@@ -161,6 +174,7 @@ class ServingEngine:
         if done:
             req.finished, req.finish_time = True, now
             self.sched.finish(rid)
+            self._tables.pop(rid, None)
         return (rid, tok, done)
 
     # -- sampling ------------------------------------------------------------------------------
@@ -204,27 +218,136 @@ class ServingEngine:
 
     # -- batched decode ----------------------------------------------------------------------------
     def _decode_forward(self, seqs: List[ScheduledSeq]) -> torch.Tensor:
-        m = self.model.model
-        dev = self.device
+        """Batched single-token forward.  On the GPU the whole step (embedding to logits) is captured once per
+        (batch bucket, KV split count) in a CUDA graph and replayed from static input buffers."""
         Rn = len(seqs)
         last = [(self.requests[s.req_id].prompt + self.requests[s.req_id].output)[s.start_pos] for s in seqs]
-        ids = torch.tensor(last, dtype=torch.long, device=dev)
-        pos = torch.tensor([s.start_pos for s in seqs], dtype=torch.long, device=dev)
-        slots = torch.tensor([s.slot for s in seqs], dtype=torch.int32, device=dev)
+        pos = [s.start_pos for s in seqs]
+        slots = [s.slot for s in seqs]
+        tables = [self._table(s.req_id, s.start_pos) for s in seqs] if self.state.kv else None
+        max_len = max(pos) + 1
+        if not self._use_graphs:
+            inp = self._decode_inputs(Rn, max(len(t) for t in tables) if tables else 1)
+            self._fill_inputs(inp, last, pos, slots, tables)
+            return self._decode_body(inp, self._splits_for(Rn, max_len))
+        Rb = 1
+        while Rb < Rn:
+            Rb *= 2
+        Rb = min(Rb, max(self.sched.max_num_seqs, Rn))
+        splits = self._splits_for(Rb, max_len)
+        key = (Rb, splits)
+        g = self._graphs.get(key)
+        if g is None:
+            try:
+                g = self._capture(Rb, splits, last, pos, slots, tables)
+            except Exception as e:      # an op that cannot be captured (host sync in a fallback path): run eagerly
+                import warnings
+                warnings.warn(f"CUDA graph capture of the decode step failed ({e}); continuing without graphs")
+                self._use_graphs = False
+                torch.cuda.synchronize(self.device)
+                self.state.clear_slot(self._pad_slot)
+                return self._decode_forward(seqs)
+            self._graphs[key] = g
+        self._fill_inputs(g["inp"], last, pos, slots, tables)
+        g["graph"].replay()
+        self.stats["graph_replays"] += 1
+        return g["logits"][:Rn]
+
+    def _table(self, rid: int, pos: int):
+        """Block table of a decoding request, re-read from the scheduler only when a new block was appended."""
+        t = self._tables.get(rid)
+        if t is None or pos // self.block_size >= len(t):
+            t = torch.from_numpy(self.sched.block_table_array(rid))
+            self._tables[rid] = t
+        return t
+
+    def warmup(self, max_len: Optional[int] = None) -> int:
+        """Captures the decode graphs of every batch bucket (short- and long-context split counts) up front."""
+        if not self._use_graphs:
+            return 0
+        n, rows = 0, 1
+        while True:
+            rows = min(rows, self.sched.max_num_seqs)
+            for ml in {1, max_len or self.max_blocks_per_seq * self.block_size}:
+                key = (rows, self._splits_for(rows, ml))
+                if key not in self._graphs:
+                    tables = [[self._pad_block]] * rows if self.state.kv else None
+                    self._graphs[key] = self._capture(rows, key[1], [0] * rows, [0] * rows, [self._pad_slot] * rows, tables)
+                    n += 1
+            if rows >= self.sched.max_num_seqs:
+                return n
+            rows *= 2
+
+    def _splits_for(self, rows: int, max_len: int) -> int:
+        """KV splits of the paged attention kernel: enough CTAs for two waves over the SMs on long contexts."""
+        if max_len <= 1024 or not self.state.kv:
+            return 1
+        a = next(l.seq_mixer for l in self.model.model.layers if isinstance(l.seq_mixer, Attention))
+        ctas = rows * a.num_kv_heads
+        sp = 1
+        while sp < 64 and ctas * sp < 148 and sp * 256 < max_len:
+            sp *= 2
+        return sp
+
+    def _decode_inputs(self, rows: int, mb: int) -> dict:
+        dev = self.device
+        pin = dev.type == "cuda"
+        host = {"ids": torch.zeros(rows, dtype=torch.long, pin_memory=pin),
+                "pos": torch.zeros(rows, dtype=torch.long, pin_memory=pin),
+                "slots": torch.zeros(rows, dtype=torch.int32, pin_memory=pin),
+                "bt": torch.zeros(rows, mb, dtype=torch.int32, pin_memory=pin)}
+        d = {k: torch.zeros_like(v, device=dev) for k, v in host.items()}
+        d.update(host=host, rows=rows, mb=mb)
+        return d
+
+    def _fill_inputs(self, inp: dict, last, pos, slots, tables) -> None:
+        h, Rn, rows = inp["host"], len(last), inp["rows"]
+        h["ids"][:Rn] = torch.tensor(last, dtype=torch.long)
+        h["pos"][:Rn] = torch.tensor(pos, dtype=torch.long)
+        h["slots"][:Rn] = torch.tensor(slots, dtype=torch.int32)
+        if Rn < rows:                       # padding rows: token 0 at position 0 of the spare slot / block
+            h["ids"][Rn:] = 0
+            h["pos"][Rn:] = 0
+            h["slots"][Rn:] = self._pad_slot
+        if tables is not None:
+            bt = h["bt"]
+            bt.fill_(self._pad_block)
+            for i, t in enumerate(tables):
+                bt[i, :len(t)] = t if isinstance(t, torch.Tensor) else torch.tensor(t, dtype=torch.int32)
+        for k in ("ids", "pos", "slots", "bt"):
+            inp[k].copy_(h[k], non_blocking=True)
+
+    def _capture(self, rows: int, splits: int, last, pos, slots, tables) -> dict:
+        inp = self._decode_inputs(rows, self.max_blocks_per_seq)
+        # warm-up on the padding slot only (real state must not advance twice): lazy initialisation, workspaces
+        n = len(last)
+        self._fill_inputs(inp, [0] * n, [0] * n, [self._pad_slot] * n, None if tables is None else [[self._pad_block]] * n)
+        side = torch.cuda.Stream(self.device)
+        side.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(side):
+            self._decode_body(inp, splits)
+        torch.cuda.current_stream(self.device).wait_stream(side)
+        torch.cuda.synchronize(self.device)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            logits = self._decode_body(inp, splits)
+        self.state.clear_slot(self._pad_slot)
+        return {"graph": graph, "inp": inp, "logits": logits}
+
+    def _decode_body(self, inp: dict, splits: int) -> torch.Tensor:
+        m = self.model.model
+        ids, pos, slots = inp["ids"], inp["pos"], inp["slots"]
+        Rn = ids.shape[0]
         x = m.embed_tokens(ids)                                    # [R, Dm]
         cos, sin = m.rotary_emb(pos[:, None])                        # [R, 1, rot]
         cos, sin = cos.to(x.dtype), sin.to(x.dtype)
         meta = None
         if self.state.kv:
             bs = self.block_size
-            tables = [self.sched.block_table(s.req_id) for s in seqs]
-            mb = max(len(t) for t in tables)
-            bt = torch.zeros(Rn, mb, dtype=torch.int32)
-            for i, t in enumerate(tables):
-                bt[i, :len(t)] = torch.tensor(t, dtype=torch.int32)
-            bt = bt.to(dev)
-            slot_map = (bt[torch.arange(Rn), (pos // bs).to(torch.long)].to(torch.long) * bs + pos % bs)
-            meta = {"bt": bt, "mb": mb, "slot_map": slot_map.contiguous(), "lens": (pos + 1).to(torch.int32)}
+            bt = inp["bt"]
+            slot_map = (bt[torch.arange(Rn, device=bt.device), pos // bs].to(torch.long) * bs + pos % bs)
+            meta = {"bt": bt, "mb": bt.shape[1], "slot_map": slot_map.contiguous(), "lens": (pos + 1).to(torch.int32),
+                    "splits": splits}
         for i, layer in enumerate(m.layers):
             h = layer.input_layernorm(x)
             mixer = layer.seq_mixer
@@ -243,9 +366,7 @@ class ServingEngine:
             x = x + y
             h2 = layer.post_attention_layernorm(x)
             y2 = layer.mlp(h2)
-            y2 = y2[0] if isinstance(y2, tuple) else y2
-            if self.tp is not None:
-                y2 = self.tp.all_reduce(y2)
+            y2 = y2[0] if isinstance(y2, tuple) else y2      # (under TP the MLP's forward hook has reduced it)
             x = x + y2
         return self._logits(m.norm(x))
 
@@ -270,16 +391,23 @@ class ServingEngine:
             _lib.check(K.hmf_cache_append(_lib.ptr(k), _lib.ptr(v), _lib.ptr(kc), _lib.ptr(vc), _lib.ptr(meta["slot_map"]),
                                           c_ll(Rn), c_int(mx.num_kv_heads), c_int(mx.head_dim), c_ll(k.stride(0)),
                                           c_ll(v.stride(0)), _lib.stream_ptr(h.device)), "cache_append")
-            splits = 8 if int(meta["lens"].max()) > 4096 else (4 if int(meta["lens"].max()) > 1024 else 1)
+            splits = meta["splits"]
             o = torch.empty(Rn, mx.num_heads, mx.head_dim, device=h.device, dtype=h.dtype)
             po = torch.empty(Rn, mx.num_heads, splits, mx.head_dim, device=h.device, dtype=torch.float32)
             pml = torch.empty(Rn, mx.num_heads, splits, 2, device=h.device, dtype=torch.float32)
-            _lib.check(K.hmf_paged_attention_decode(_lib.ptr(q), _lib.ptr(kc), _lib.ptr(vc), _lib.ptr(meta["bt"]),
-                                                    _lib.ptr(meta["lens"]), _lib.ptr(o), _lib.ptr(po), _lib.ptr(pml),
-                                                    c_int(Rn), c_int(mx.num_heads), c_int(mx.num_kv_heads),
-                                                    c_int(mx.head_dim), c_int(self.block_size), c_int(meta["mb"]),
-                                                    c_int(splits), c_int(window), c_float(mx.scaling),
-                                                    _lib.stream_ptr(h.device)), "paged_attention_decode")
+            if self.block_size % 64 == 0 and self.block_size <= 256:
+                # tcgen05 kernel: K/V tiles by TMA straight from the paged cache, accumulators in tensor memory
+                _lib.check(K.hmf_paged_attention_decode_tc(
+                    _lib.ptr(q), _lib.ptr(kc), _lib.ptr(vc), _lib.ptr(meta["bt"]), _lib.ptr(meta["lens"]), _lib.ptr(o),
+                    _lib.ptr(po), _lib.ptr(pml), c_int(Rn), c_int(mx.num_heads), c_int(mx.num_kv_heads),
+                    c_int(mx.head_dim), c_int(self.block_size), c_int(kc.shape[0]), c_int(meta["mb"]), c_int(splits),
+                    c_int(window), c_float(mx.scaling), _lib.stream_ptr(h.device)), "paged_attention_decode_tc")
+            else:
+                _lib.check(K.hmf_paged_attention_decode(
+                    _lib.ptr(q), _lib.ptr(kc), _lib.ptr(vc), _lib.ptr(meta["bt"]), _lib.ptr(meta["lens"]), _lib.ptr(o),
+                    _lib.ptr(po), _lib.ptr(pml), c_int(Rn), c_int(mx.num_heads), c_int(mx.num_kv_heads),
+                    c_int(mx.head_dim), c_int(self.block_size), c_int(meta["mb"]), c_int(splits), c_int(window),
+                    c_float(mx.scaling), _lib.stream_ptr(h.device)), "paged_attention_decode")
         else:
             kc.view(-1, *kc.shape[2:])[meta["slot_map"]] = k
             vc.view(-1, *vc.shape[2:])[meta["slot_map"]] = v
@@ -334,9 +462,10 @@ class ServingEngine:
         st = self.state.ssm[i]["state"]
         if self._cuda and D == 128 and h.dtype == torch.bfloat16 and mx.kv_proj_rank is None:
             o = torch.empty(Rn, H, D, device=h.device, dtype=h.dtype)
+            # keep the contiguous copies alive until the launch (a temporary's block would be reused)
+            q, k, v, g, beta = q.contiguous(), k.contiguous(), v.contiguous(), g.float().contiguous(), beta.float().contiguous()
             _lib.check(_lib.kernels().hmf_gdn_decode(
-                _lib.ptr(q.contiguous()), _lib.ptr(k.contiguous()), _lib.ptr(v.contiguous()),
-                _lib.ptr(g.float().contiguous()), _lib.ptr(beta.float().contiguous()), _lib.ptr(st), _lib.ptr(slots),
+                _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(g), _lib.ptr(beta), _lib.ptr(st), _lib.ptr(slots),
                 _lib.ptr(o), c_int(Rn), c_int(H), c_int(mx.num_q_heads), c_int(mx.num_k_heads), c_int(mx.num_v_heads),
                 c_int(D), c_int(D), c_float(D ** -0.5), c_int(1), _lib.stream_ptr(h.device)), "gdn_decode")
         else:
@@ -366,9 +495,12 @@ class ServingEngine:
         Hx = mx.d_xb // mx.headdim
         if self._cuda and h.dtype == torch.bfloat16:
             y = torch.empty(Rn, mx.nheads, mx.headdim, device=h.device, dtype=h.dtype)
+            # keep the contiguous copies alive until the launch (a temporary's block would be reused)
+            x, dtp, A, Bm, Cm, Dp = (x.contiguous(), dtp.contiguous(), A.contiguous(), Bm.contiguous(), Cm.contiguous(),
+                                     mx.D.float().contiguous())
             _lib.check(_lib.kernels().hmf_ssd_decode(
-                _lib.ptr(x.contiguous()), _lib.ptr(dtp.contiguous()), _lib.ptr(A.contiguous()), _lib.ptr(Bm.contiguous()),
-                _lib.ptr(Cm.contiguous()), _lib.ptr(mx.D.float().contiguous()), _lib.ptr(st), _lib.ptr(slots), _lib.ptr(y),
+                _lib.ptr(x), _lib.ptr(dtp), _lib.ptr(A), _lib.ptr(Bm), _lib.ptr(Cm), _lib.ptr(Dp), _lib.ptr(st),
+                _lib.ptr(slots), _lib.ptr(y),
                 c_int(Rn), c_int(mx.nheads), c_int(Hx), c_int(Hx), c_int(mx.headdim), c_int(mx.d_state),
                 _lib.stream_ptr(h.device)), "ssd_decode")
         else:

@@ -70,13 +70,19 @@ class NativeScheduler:
         return self._lib.hmf_sched_is_finished(self._h, i64(req_id)) == 1
 
     def block_table(self, req_id: int, max_blocks: int = 4096) -> List[int]:
-        buf = (i32 * max_blocks)()
-        n = self._lib.hmf_sched_block_table(self._h, i64(req_id), buf, max_blocks)
+        return self.block_table_array(req_id, max_blocks).tolist()
+
+    def block_table_array(self, req_id: int, max_blocks: int = 4096):
+        """Block ids of a request as an ``int32`` numpy array (a copy)."""
+        import numpy as np
+        if getattr(self, "_bt_buf", None) is None or len(self._bt_buf) < max_blocks:
+            self._bt_buf = (i32 * max_blocks)()
+        n = self._lib.hmf_sched_block_table(self._h, i64(req_id), self._bt_buf, len(self._bt_buf))
         if n < 0:
             raise KeyError(req_id)
-        if n > max_blocks:
-            return self.block_table(req_id, n)
-        return [int(buf[i]) for i in range(n)]
+        if n > len(self._bt_buf):
+            return self.block_table_array(req_id, n)
+        return np.ctypeslib.as_array(self._bt_buf)[:n].copy()
 
     def register_snapshot(self, req_id: int, pos: int) -> int:
         return int(self._lib.hmf_sched_register_snapshot(self._h, i64(req_id), pos))

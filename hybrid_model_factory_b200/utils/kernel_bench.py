@@ -163,7 +163,35 @@ def bench_conv1d(args):
     report(f"causal_conv1d+silu [1, {T}, {Cc}]", ms, bytes_=2.0 * T * Cc * 2)
 
 
-CASES = {"gemm": bench_gemm, "attention_fwd": bench_attention_fwd, "attention_bwd": bench_attention_bwd,
+def bench_paged_decode(args):
+    """Decode-step paged attention: ``--batch`` requests of ``--seq`` cached tokens each, block size 64."""
+    import ctypes as ct
+    from ..ops import _lib
+    K = _lib.kernels()
+    Rn, H, Hkv, D, bs, L = args.batch, args.heads, args.kv_heads, 128, 64, args.seq
+    mb = (L + bs - 1) // bs
+    nb = Rn * mb
+    kc = torch.randn(nb, bs, Hkv, D, device="cuda", dtype=torch.bfloat16)
+    vc = torch.randn(nb, bs, Hkv, D, device="cuda", dtype=torch.bfloat16)
+    bt = torch.randperm(nb, device="cuda").to(torch.int32).view(Rn, mb).contiguous()
+    lens = torch.full((Rn,), L, dtype=torch.int32, device="cuda")
+    q = torch.randn(Rn, H, D, device="cuda", dtype=torch.bfloat16)
+    o = torch.empty_like(q)
+    for splits in (1, 2, 4, 8):
+        po = torch.empty(Rn, H, splits, D, device="cuda", dtype=torch.float32)
+        pml = torch.empty(Rn, H, splits, 2, device="cuda", dtype=torch.float32)
+
+        def run():
+            _lib.check(K.hmf_paged_attention_decode_tc(
+                _lib.ptr(q), _lib.ptr(kc), _lib.ptr(vc), _lib.ptr(bt), _lib.ptr(lens), _lib.ptr(o), _lib.ptr(po),
+                _lib.ptr(pml), ct.c_int(Rn), ct.c_int(H), ct.c_int(Hkv), ct.c_int(D), ct.c_int(bs), ct.c_int(nb),
+                ct.c_int(mb), ct.c_int(splits), ct.c_int(0), ct.c_float(D ** -0.5), _lib.stream_ptr(q.device)), "pa")
+        ms = time_fn(run, flush=(kc.numel() * 4 < (256 << 20)))
+        report(f"paged_attention_decode_tc R={Rn} L={L} Hq={H} Hkv={Hkv} splits={splits}", ms,
+               bytes_=2.0 * Rn * L * Hkv * D * 2)
+
+
+CASES = {"paged_decode": bench_paged_decode, "gemm": bench_gemm, "attention_fwd": bench_attention_fwd, "attention_bwd": bench_attention_bwd,
          "gdn_fwd": bench_gdn_fwd, "gdn_fwd_bwd": bench_gdn_fwd_bwd, "rmsnorm": bench_rmsnorm, "swiglu": bench_swiglu,
          "conv1d": bench_conv1d}
 
@@ -175,6 +203,7 @@ def main(argv=None):
     ap.add_argument("--heads", type=int, default=32)
     ap.add_argument("--kv-heads", type=int, default=8)
     ap.add_argument("--size", type=int, default=8192)
+    ap.add_argument("--batch", type=int, default=64)
     args = ap.parse_args(argv)
     names = list(CASES) if args.case == "all" else [args.case]
     for n in names:

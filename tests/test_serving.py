@@ -83,3 +83,156 @@ def test_engine_prefix_caching_with_state_snapshots():
     out2 = eng.generate([p2], SamplingParams(max_new_tokens=4))[0]
     assert out2 == ref2
     assert eng.sched.stats()["prefix_hits"] >= 1
+
+
+# ---------------------------------------------------------------------------------------------
+# GPU: decode kernels against fp32 PyTorch references, and the engine in bf16 with head_dim 128
+# ---------------------------------------------------------------------------------------------
+def _kernels():
+    import ctypes
+    from hybrid_model_factory_b200.ops import _lib
+    return _lib, _lib.kernels(), ctypes
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("window", [0, 300])
+def test_paged_attention_decode_kernel(window):
+    _lib, K, ct = _kernels()
+    torch.manual_seed(0)
+    dev = "cuda"
+    Rn, H, Hkv, D, bs = 5, 32, 8, 128, 64
+    lens = torch.tensor([1, 63, 700, 5000, 129], dtype=torch.int32, device=dev)
+    mb = int((lens.max() + bs - 1) // bs)
+    nb = Rn * mb + 3
+    kc = torch.randn(nb, bs, Hkv, D, device=dev, dtype=torch.bfloat16)
+    vc = torch.randn(nb, bs, Hkv, D, device=dev, dtype=torch.bfloat16)
+    perm = torch.randperm(nb, device=dev)[:Rn * mb].to(torch.int32).view(Rn, mb).contiguous()
+    q = torch.randn(Rn, H, D, device=dev, dtype=torch.bfloat16)
+    for splits, tc in ((1, False), (4, False), (1, True), (4, True), (8, True)):
+        o = torch.empty(Rn, H, D, device=dev, dtype=torch.bfloat16)
+        po = torch.empty(Rn, H, splits, D, device=dev, dtype=torch.float32)
+        pml = torch.empty(Rn, H, splits, 2, device=dev, dtype=torch.float32)
+        if tc:
+            _lib.check(K.hmf_paged_attention_decode_tc(
+                _lib.ptr(q), _lib.ptr(kc), _lib.ptr(vc), _lib.ptr(perm), _lib.ptr(lens), _lib.ptr(o), _lib.ptr(po),
+                _lib.ptr(pml), ct.c_int(Rn), ct.c_int(H), ct.c_int(Hkv), ct.c_int(D), ct.c_int(bs), ct.c_int(nb),
+                ct.c_int(mb), ct.c_int(splits), ct.c_int(window), ct.c_float(D ** -0.5), _lib.stream_ptr(q.device)), "pa")
+            _lib.assert_status_ok()
+        else:
+            _lib.check(K.hmf_paged_attention_decode(
+                _lib.ptr(q), _lib.ptr(kc), _lib.ptr(vc), _lib.ptr(perm), _lib.ptr(lens), _lib.ptr(o), _lib.ptr(po),
+                _lib.ptr(pml), ct.c_int(Rn), ct.c_int(H), ct.c_int(Hkv), ct.c_int(D), ct.c_int(bs), ct.c_int(mb),
+                ct.c_int(splits), ct.c_int(window), ct.c_float(D ** -0.5), _lib.stream_ptr(q.device)), "pa")
+        for r in range(Rn):
+            L = int(lens[r])
+            p = torch.arange(L, device=dev)
+            flat = perm[r].long()[p // bs] * bs + p % bs
+            kk = kc.view(-1, Hkv, D)[flat].float()
+            vv = vc.view(-1, Hkv, D)[flat].float()
+            if window:
+                kk, vv = kk[max(0, L - window):], vv[max(0, L - window):]
+            kk = kk.repeat_interleave(H // Hkv, dim=1)
+            vv = vv.repeat_interleave(H // Hkv, dim=1)
+            s = torch.einsum("hd,lhd->hl", q[r].float(), kk) * D ** -0.5
+            ref = torch.einsum("hl,lhd->hd", torch.softmax(s, -1), vv)
+            assert (o[r].float() - ref).abs().max() < 2e-2, (splits, tc, r)
+
+
+@pytest.mark.gpu
+def test_gdn_and_ssd_decode_kernels():
+    from hybrid_model_factory_b200.ops import reference as R
+    _lib, K, ct = _kernels()
+    torch.manual_seed(0)
+    dev = "cuda"
+    Rn, H, Hk, D = 6, 8, 4, 128
+    q = torch.randn(Rn, H * D, device=dev, dtype=torch.bfloat16)
+    k = torch.randn(Rn, Hk * D, device=dev, dtype=torch.bfloat16)
+    v = torch.randn(Rn, Hk * D, device=dev, dtype=torch.bfloat16)
+    g = -torch.rand(Rn, H, device=dev)
+    beta = torch.rand(Rn, H, device=dev)
+    slots = torch.tensor([7, 2, 5, 0, 3, 9], dtype=torch.int32, device=dev)
+    st = torch.randn(10, H, D, D, device=dev) * 0.1
+    st0 = st.clone()
+    o = torch.empty(Rn, H, D, device=dev, dtype=torch.bfloat16)
+    _lib.check(K.hmf_gdn_decode(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(g), _lib.ptr(beta), _lib.ptr(st),
+                                _lib.ptr(slots), _lib.ptr(o), ct.c_int(Rn), ct.c_int(H), ct.c_int(H), ct.c_int(Hk),
+                                ct.c_int(Hk), ct.c_int(D), ct.c_int(D), ct.c_float(D ** -0.5), ct.c_int(1),
+                                _lib.stream_ptr(q.device)), "gdn_decode")
+    rep = H // Hk
+    qh = q.view(Rn, 1, H, D)
+    kh = k.view(Rn, 1, Hk, D).repeat_interleave(rep, dim=2)
+    vh = v.view(Rn, 1, Hk, D).repeat_interleave(rep, dim=2)
+    ro, rs = R.gated_delta_rule_recurrent(qh, kh, vh, g[:, None], beta[:, None], initial_state=st0[slots.long()])
+    assert (o.float() - ro[:, 0].float()).abs().max() < 2e-2
+    assert (st[slots.long()] - rs).abs().max() < 2e-3
+    untouched = [i for i in range(10) if i not in slots.tolist()]
+    assert torch.equal(st[untouched], st0[untouched])
+
+    # Mamba2 state update: x [R,Hx*P] B [R,Hx*N] C [R,H*N]
+    Hh, Hx, P, N = 8, 2, 64, 128
+    x = torch.randn(Rn, Hx * P, device=dev, dtype=torch.bfloat16)
+    Bm = torch.randn(Rn, Hx * N, device=dev, dtype=torch.bfloat16)
+    Cm = torch.randn(Rn, Hh * N, device=dev, dtype=torch.bfloat16)
+    dt = torch.rand(Rn, Hh, device=dev)
+    A = -torch.rand(Hh, device=dev)
+    Dp = torch.randn(Hh, device=dev)
+    st = torch.randn(10, Hh, P, N, device=dev) * 0.1
+    st0 = st.clone()
+    y = torch.empty(Rn, Hh, P, device=dev, dtype=torch.bfloat16)
+    _lib.check(K.hmf_ssd_decode(_lib.ptr(x), _lib.ptr(dt), _lib.ptr(A), _lib.ptr(Bm), _lib.ptr(Cm), _lib.ptr(Dp),
+                                _lib.ptr(st), _lib.ptr(slots), _lib.ptr(y), ct.c_int(Rn), ct.c_int(Hh), ct.c_int(Hx),
+                                ct.c_int(Hx), ct.c_int(P), ct.c_int(N), _lib.stream_ptr(x.device)), "ssd_decode")
+    rep = Hh // Hx
+    xh = x.view(Rn, Hx, P).repeat_interleave(rep, dim=1)
+    Bh = Bm.view(Rn, Hx, N).repeat_interleave(rep, dim=1)
+    ry, rs = R.selective_state_update(st0[slots.long()], xh, dt, A, Bh, Cm.view(Rn, Hh, N), Dp)
+    assert ((y.float() - ry.float()).abs() / (ry.float().abs() + 1.0)).max() < 1e-2
+    assert (st[slots.long()] - rs).abs().max() < 2e-3
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("pattern", ["*-GDN", "M2-*"])
+def test_engine_bf16_kernels_match_torch_path(pattern):
+    """The kernel decode path and the PyTorch decode path of the engine agree on (almost) all greedy tokens."""
+    torch.manual_seed(0)
+    cfg = tiny(pattern, hidden_size=512, intermediate_size=1024, num_attention_heads=4, num_key_value_heads=2,
+               head_dim=128, vocab_size=512)
+    model = build_model(cfg).to("cuda", torch.bfloat16).eval()
+    prompts = [torch.randint(0, 512, (n,)).tolist() for n in (70, 200, 33, 129)]
+    outs = []
+    for use_kernels in (True, False):
+        eng = ServingEngine(model, block_size=64, num_blocks=64, max_num_seqs=4, max_num_batched_tokens=128,
+                            max_model_len=512, use_cuda_graphs=use_kernels)
+        assert eng._cuda
+        eng._cuda = use_kernels
+        outs.append(eng.generate(prompts, SamplingParams(max_new_tokens=12)))
+        assert (eng.stats["graph_replays"] > 0) == use_kernels
+    agree = sum(a == b for x, y in zip(*outs) for a, b in zip(x, y))
+    first = sum(x[0] == y[0] for x, y in zip(*outs))
+    assert first == len(prompts) and agree >= 0.75 * 12 * len(prompts), (agree, outs)
+
+
+def _tp_worker(rank, world, pattern):
+    import torch.distributed as dist
+    from hybrid_model_factory_b200.parallel.tp import TPContext, shard_model
+    torch.manual_seed(0)
+    kw = dict(num_experts=4, num_experts_per_tok=2, moe_intermediate_size=32) if pattern == "moe" else {}
+    cfg = tiny("*-GDN-M2-GKA" if pattern != "moe" else "*-GDN", **kw)
+    if pattern == "moe":
+        d = {k: v for k, v in cfg.to_dict().items() if k != "model_type"}
+        cfg = HybridConfig("hybrid_qwen3_moe", **d)
+    model = build_model(cfg).eval()
+    prompts = [torch.randint(0, 128, (n,)).tolist() for n in (5, 19, 11)]
+    ref = [model.generate(torch.tensor([p]), max_new_tokens=5)[0, len(p):].tolist() for p in prompts]
+    tp = TPContext(dist.group.WORLD)
+    shard_model(model, tp)
+    eng = ServingEngine(model, block_size=4, num_blocks=64, max_num_seqs=4, max_num_batched_tokens=8, max_model_len=64,
+                        tp=tp)
+    out = eng.generate(prompts, SamplingParams(max_new_tokens=5))
+    assert out == ref, (rank, out, ref)
+
+
+@pytest.mark.parametrize("pattern", ["dense", "moe"])
+def test_tensor_parallel_engine_gloo(pattern):
+    from dist_utils import run_ranks
+    run_ranks(_tp_worker, 2, pattern)
