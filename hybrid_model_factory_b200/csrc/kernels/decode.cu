@@ -246,6 +246,66 @@ __global__ void ssd_decode_kernel(const bf16* __restrict__ x, const float* __res
   y[((size_t)r * H + h) * P + pidx] = __float2bfloat16(acc + (Dp ? Dp[h] * xv : 0.f));
 }
 
+// Same update with one warp per state row (N a multiple of 128): lane l holds columns 4l..4l+3 of every
+// 128-column group, so a warp reads and writes whole 512-byte rows; 8 warps walk the P rows 4 at a time.
+template <int NG>
+__global__ void __launch_bounds__(256)
+ssd_decode_rows_kernel(const bf16* __restrict__ x, const float* __restrict__ dt, const float* __restrict__ A,
+                       const bf16* __restrict__ Bm, const bf16* __restrict__ Cm, const float* __restrict__ Dp,
+                       float* __restrict__ state, const int* __restrict__ slots, bf16* __restrict__ y, int H, int Hx,
+                       int Hb, int P) {
+  constexpr int N = NG * 128;
+  const int r = blockIdx.x, h = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int hx = h / (H / Hx), hb = h / (H / Hb);
+  float bv[NG][4], cv[NG][4];
+#pragma unroll
+  for (int j = 0; j < NG; ++j) {
+    const uint2 ub = *reinterpret_cast<const uint2*>(Bm + ((size_t)r * Hb + hb) * N + j * 128 + lane * 4);
+    const uint2 uc = *reinterpret_cast<const uint2*>(Cm + ((size_t)r * H + h) * N + j * 128 + lane * 4);
+    const float2 b0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ub.x));
+    const float2 b1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ub.y));
+    const float2 c0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&uc.x));
+    const float2 c1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&uc.y));
+    bv[j][0] = b0.x; bv[j][1] = b0.y; bv[j][2] = b1.x; bv[j][3] = b1.y;
+    cv[j][0] = c0.x; cv[j][1] = c0.y; cv[j][2] = c1.x; cv[j][3] = c1.y;
+  }
+  const float dtv = dt[(size_t)r * H + h];
+  const float a = __expf(dtv * A[h]);
+  const float dcoef = Dp ? Dp[h] : 0.f;
+  float* S = state + ((size_t)slots[r] * H + h) * P * N;
+  constexpr int RU = 4;   // rows in flight per warp
+  for (int p0 = warp * RU; p0 < P; p0 += 8 * RU) {
+    float4 sv[RU][NG];
+    float xv[RU];
+#pragma unroll
+    for (int u = 0; u < RU; ++u) {
+      const int pr = min(p0 + u, P - 1);
+      xv[u] = __bfloat162float(x[((size_t)r * Hx + hx) * P + pr]);
+#pragma unroll
+      for (int j = 0; j < NG; ++j) sv[u][j] = *reinterpret_cast<const float4*>(S + (size_t)pr * N + j * 128 + lane * 4);
+    }
+#pragma unroll
+    for (int u = 0; u < RU; ++u) {
+      if (p0 + u >= P) break;
+      const float dx = dtv * xv[u];
+      float acc = 0.f;
+#pragma unroll
+      for (int j = 0; j < NG; ++j) {
+        float4 s4 = sv[u][j];
+        s4.x = fmaf(s4.x, a, dx * bv[j][0]);
+        s4.y = fmaf(s4.y, a, dx * bv[j][1]);
+        s4.z = fmaf(s4.z, a, dx * bv[j][2]);
+        s4.w = fmaf(s4.w, a, dx * bv[j][3]);
+        acc += s4.x * cv[j][0] + s4.y * cv[j][1] + s4.z * cv[j][2] + s4.w * cv[j][3];
+        *reinterpret_cast<float4*>(S + (size_t)(p0 + u) * N + j * 128 + lane * 4) = s4;
+      }
+      acc = warp_sum(acc);
+      if (lane == 0) y[((size_t)r * H + h) * P + p0 + u] = __float2bfloat16(acc + dcoef * xv[u]);
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------------
 // argmax over the vocabulary (greedy sampling): logits [R, V] bf16 or fp32 -> ids [R]
 // ------------------------------------------------------------------------------------
@@ -330,6 +390,16 @@ HMF_API int hmf_ssd_decode(const void* x, const float* dt, const float* A, const
   HMF_REQUIRE(H % Hx == 0 && H % Hb == 0, "ssd_decode: head counts do not divide H=%d", H);
   if (R == 0) return HMF_OK;
   dim3 grid(R, H);
+  if (N == 128 || N == 256) {
+    if (N == 128)
+      ssd_decode_rows_kernel<1><<<grid, 256, 0, st>>>((const bf16*)x, dt, A, (const bf16*)Bm, (const bf16*)Cm, Dp, state,
+                                                      slots, (bf16*)y, H, Hx, Hb, P);
+    else
+      ssd_decode_rows_kernel<2><<<grid, 256, 0, st>>>((const bf16*)x, dt, A, (const bf16*)Bm, (const bf16*)Cm, Dp, state,
+                                                      slots, (bf16*)y, H, Hx, Hb, P);
+    HMF_CHECK_CUDA(cudaGetLastError());
+    return HMF_OK;
+  }
   ssd_decode_kernel<<<grid, 128, 2 * N * sizeof(float), st>>>((const bf16*)x, dt, A, (const bf16*)Bm,
                                                               (const bf16*)Cm, Dp, state, slots, (bf16*)y, H, Hx, Hb,
                                                               P, N);

@@ -1,0 +1,195 @@
+// Fused glue kernels of the decode step (one token per request).  They remove the small per-head
+// launches between the GEMMs of a layer:
+//   * hmf_qkv_norm_rope_append: packed QKV row -> per-head RMSNorm (q, k) -> RoPE -> q buffer and paged K/V cache
+//   * hmf_swiglu_packed:        [R, 2F] = [gate | up] -> silu(gate) * up
+//   * hmf_ssd_decode_packed:    Mamba2 state update reading x / B / C / dt straight from the packed projection and
+//                               convolution outputs (softplus(dt + bias) and A = -exp(A_log) computed in place)
+#include <math.h>
+
+#include "../common/host.h"
+#include "../common/sm100.cuh"
+
+namespace hmf {
+namespace decode_fused {
+
+using bf16 = __nv_bfloat16;
+
+// grid (R, Hq + 2 Hkv), 128 threads (= head dim): thread t <-> element t of the head.
+__global__ void __launch_bounds__(128)
+qkv_norm_rope_append_kernel(const bf16* __restrict__ qkv, long long ld, const bf16* __restrict__ qw,
+                            const bf16* __restrict__ kw, float eps, int zero_centered, const bf16* __restrict__ cs,
+                            const bf16* __restrict__ sn, int rot, bf16* __restrict__ q_out, bf16* __restrict__ kc,
+                            bf16* __restrict__ vc, const long long* __restrict__ slot_map, int Hq, int Hkv) {
+  constexpr int D = 128;
+  const int r = blockIdx.x, hh = blockIdx.y, t = threadIdx.x;
+  __shared__ float s_x[D];
+  __shared__ float s_red[4];
+  const bool is_q = hh < Hq, is_k = !is_q && hh < Hq + Hkv;
+  float x = __bfloat162float(qkv[(size_t)r * ld + (size_t)hh * D + t]);
+  const long long slot = slot_map[r];
+  if (!is_q && !is_k) {   // V: plain append
+    if (slot >= 0) vc[(size_t)slot * Hkv * D + (size_t)(hh - Hq - Hkv) * D + t] = __float2bfloat16(x);
+    return;
+  }
+  const bf16* w = is_q ? qw : kw;
+  if (w != nullptr) {
+    const float ss = warp_sum(x * x);
+    if ((t & 31) == 0) s_red[t >> 5] = ss;
+    __syncthreads();
+    const float tot = s_red[0] + s_red[1] + s_red[2] + s_red[3];
+    float wv = __bfloat162float(w[t]);
+    if (zero_centered) wv += 1.f;
+    x = x * rsqrtf(tot / D + eps) * wv;
+    x = __bfloat162float(__float2bfloat16(x));   // the unfused path rounds between the norm and the rotation
+  }
+  s_x[t] = x;
+  __syncthreads();
+  float y = x;
+  if (t < rot) {
+    const int half = rot / 2;
+    const float c = __bfloat162float(cs[(size_t)r * rot + t]), s = __bfloat162float(sn[(size_t)r * rot + t]);
+    const float partner = t < half ? -s_x[t + half] : s_x[t - half];
+    y = x * c + partner * s;
+  }
+  if (is_q) {
+    q_out[((size_t)r * Hq + hh) * D + t] = __float2bfloat16(y);
+  } else if (slot >= 0) {
+    kc[(size_t)slot * Hkv * D + (size_t)(hh - Hq) * D + t] = __float2bfloat16(y);
+  }
+}
+
+__global__ void swiglu_packed_kernel(const bf16* __restrict__ gu, bf16* __restrict__ y, long long rows, int F8,
+                                     long long ld) {
+  const long long total = rows * F8;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long row = i / F8;
+    const int c = (int)(i % F8) * 8;
+    const uint4 g4 = *reinterpret_cast<const uint4*>(gu + row * ld + c);
+    const uint4 u4 = *reinterpret_cast<const uint4*>(gu + row * ld + (size_t)F8 * 8 + c);
+    const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&g4);
+    const __nv_bfloat162* up = reinterpret_cast<const __nv_bfloat162*>(&u4);
+    uint4 o4;
+    uint32_t* op = reinterpret_cast<uint32_t*>(&o4);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 g = __bfloat1622float2(gp[j]), u = __bfloat1622float2(up[j]);
+      op[j] = pack_bf16x2(g.x / (1.f + __expf(-g.x)) * u.x, g.y / (1.f + __expf(-g.y)) * u.y);
+    }
+    *reinterpret_cast<uint4*>(y + row * (size_t)F8 * 8 + c) = o4;
+  }
+}
+
+// Mamba2 step, state [slots, H, P, N] fp32, N = 128 * NG.  One warp per state row, 8 warps, 4 rows in flight.
+//   x  = xbc + r * ld_xbc + x_off  [Hx, P]      B = ... + b_off [Hb, N]      C = ... + c_off [H, N]
+//   dt = softplus(dt_raw[r * ld_dt + h] + dt_bias[h]),  A = -exp(A_log[h])
+template <int NG>
+__global__ void __launch_bounds__(256)
+ssd_decode_packed_kernel(const bf16* __restrict__ xbc, long long ld_xbc, int x_off, int b_off, int c_off,
+                         const bf16* __restrict__ dt_raw, long long ld_dt, const float* __restrict__ dt_bias,
+                         const float* __restrict__ A_log, const float* __restrict__ Dp, float* __restrict__ state,
+                         const int* __restrict__ slots, bf16* __restrict__ y, int H, int Hx, int Hb, int P) {
+  constexpr int N = NG * 128;
+  const int r = blockIdx.x, h = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int hx = h / (H / Hx), hb = h / (H / Hb);
+  const bf16* row = xbc + (size_t)r * ld_xbc;
+  float bv[NG][4], cv[NG][4];
+#pragma unroll
+  for (int j = 0; j < NG; ++j) {
+    const uint2 ub = *reinterpret_cast<const uint2*>(row + b_off + (size_t)hb * N + j * 128 + lane * 4);
+    const uint2 uc = *reinterpret_cast<const uint2*>(row + c_off + (size_t)h * N + j * 128 + lane * 4);
+    const float2 b0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ub.x));
+    const float2 b1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ub.y));
+    const float2 c0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&uc.x));
+    const float2 c1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&uc.y));
+    bv[j][0] = b0.x; bv[j][1] = b0.y; bv[j][2] = b1.x; bv[j][3] = b1.y;
+    cv[j][0] = c0.x; cv[j][1] = c0.y; cv[j][2] = c1.x; cv[j][3] = c1.y;
+  }
+  const float z = __bfloat162float(dt_raw[(size_t)r * ld_dt + h]) + dt_bias[h];
+  const float dtv = z > 20.f ? z : log1pf(__expf(z));
+  const float a = __expf(-dtv * __expf(A_log[h]));
+  const float dcoef = Dp ? Dp[h] : 0.f;
+  float* S = state + ((size_t)slots[r] * H + h) * P * N;
+  constexpr int RU = 4;
+  for (int p0 = warp * RU; p0 < P; p0 += 8 * RU) {
+    float4 sv[RU][NG];
+    float xv[RU];
+#pragma unroll
+    for (int u = 0; u < RU; ++u) {
+      const int pr = min(p0 + u, P - 1);
+      xv[u] = __bfloat162float(row[x_off + (size_t)hx * P + pr]);
+#pragma unroll
+      for (int j = 0; j < NG; ++j) sv[u][j] = *reinterpret_cast<const float4*>(S + (size_t)pr * N + j * 128 + lane * 4);
+    }
+#pragma unroll
+    for (int u = 0; u < RU; ++u) {
+      if (p0 + u >= P) break;
+      const float dx = dtv * xv[u];
+      float acc = 0.f;
+#pragma unroll
+      for (int j = 0; j < NG; ++j) {
+        float4 s4 = sv[u][j];
+        s4.x = fmaf(s4.x, a, dx * bv[j][0]);
+        s4.y = fmaf(s4.y, a, dx * bv[j][1]);
+        s4.z = fmaf(s4.z, a, dx * bv[j][2]);
+        s4.w = fmaf(s4.w, a, dx * bv[j][3]);
+        acc += s4.x * cv[j][0] + s4.y * cv[j][1] + s4.z * cv[j][2] + s4.w * cv[j][3];
+        *reinterpret_cast<float4*>(S + (size_t)(p0 + u) * N + j * 128 + lane * 4) = s4;
+      }
+      acc = warp_sum(acc);
+      if (lane == 0) y[((size_t)r * H + h) * P + p0 + u] = __float2bfloat16(acc + dcoef * xv[u]);
+    }
+  }
+}
+
+}  // namespace decode_fused
+}  // namespace hmf
+
+using namespace hmf;
+using namespace hmf::decode_fused;
+
+// qkv [R, ld] = [q (Hq*128) | k (Hkv*128) | v (Hkv*128)] bf16; q_weight / k_weight [128] or null (no QK norm);
+// cos / sin [R, rot] bf16; q_out [R, Hq, 128]; caches [num_blocks * block_size, Hkv, 128]; slot_map [R] int64.
+HMF_API int hmf_qkv_norm_rope_append(const void* qkv, long long ld, const void* q_weight, const void* k_weight,
+                                     float eps, int zero_centered, const void* cos_t, const void* sin_t, int rot,
+                                     void* q_out, void* kc, void* vc, const long long* slot_map, int R, int Hq, int Hkv,
+                                     int D, cudaStream_t st) {
+  HMF_REQUIRE(D == 128, "qkv_norm_rope_append: head dim %d unsupported (128)", D);
+  HMF_REQUIRE(rot % 2 == 0 && rot <= D, "qkv_norm_rope_append: rotary dim %d unsupported", rot);
+  if (R == 0) return HMF_OK;
+  dim3 grid(R, Hq + 2 * Hkv);
+  qkv_norm_rope_append_kernel<<<grid, 128, 0, st>>>((const bf16*)qkv, ld, (const bf16*)q_weight, (const bf16*)k_weight,
+                                                    eps, zero_centered, (const bf16*)cos_t, (const bf16*)sin_t, rot,
+                                                    (bf16*)q_out, (bf16*)kc, (bf16*)vc, slot_map, Hq, Hkv);
+  HMF_CHECK_CUDA(cudaGetLastError());
+  return HMF_OK;
+}
+
+HMF_API int hmf_swiglu_packed(const void* gu, void* y, long long rows, int F, long long ld, cudaStream_t st) {
+  HMF_REQUIRE(F % 8 == 0 && ld % 8 == 0, "swiglu_packed: F=%d ld=%lld must be multiples of 8", F, ld);
+  if (rows == 0) return HMF_OK;
+  const long long items = rows * (F / 8);
+  const int grid = (int)((items + 255) / 256 < 4096 ? (items + 255) / 256 : 4096);
+  swiglu_packed_kernel<<<grid, 256, 0, st>>>((const bf16*)gu, (bf16*)y, rows, F / 8, ld);
+  HMF_CHECK_CUDA(cudaGetLastError());
+  return HMF_OK;
+}
+
+HMF_API int hmf_ssd_decode_packed(const void* xbc, long long ld_xbc, int x_off, int b_off, int c_off,
+                                  const void* dt_raw, long long ld_dt, const float* dt_bias, const float* A_log,
+                                  const float* Dp, float* state, const int* slots, void* y, int R, int H, int Hx,
+                                  int Hb, int P, int N, cudaStream_t st) {
+  HMF_REQUIRE(N == 128 || N == 256, "ssd_decode_packed: N=%d unsupported (128, 256)", N);
+  HMF_REQUIRE(H % Hx == 0 && H % Hb == 0, "ssd_decode_packed: head counts do not divide H=%d", H);
+  HMF_REQUIRE(b_off % 4 == 0 && c_off % 4 == 0 && ld_xbc % 4 == 0, "ssd_decode_packed: offsets must be multiples of 4");
+  if (R == 0) return HMF_OK;
+  dim3 grid(R, H);
+  if (N == 128)
+    ssd_decode_packed_kernel<1><<<grid, 256, 0, st>>>((const bf16*)xbc, ld_xbc, x_off, b_off, c_off, (const bf16*)dt_raw,
+                                                      ld_dt, dt_bias, A_log, Dp, state, slots, (bf16*)y, H, Hx, Hb, P);
+  else
+    ssd_decode_packed_kernel<2><<<grid, 256, 0, st>>>((const bf16*)xbc, ld_xbc, x_off, b_off, c_off, (const bf16*)dt_raw,
+                                                      ld_dt, dt_bias, A_log, Dp, state, slots, (bf16*)y, H, Hx, Hb, P);
+  HMF_CHECK_CUDA(cudaGetLastError());
+  return HMF_OK;
+}

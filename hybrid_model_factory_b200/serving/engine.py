@@ -348,8 +348,9 @@ class ServingEngine:
             slot_map = (bt[torch.arange(Rn, device=bt.device), pos // bs].to(torch.long) * bs + pos % bs)
             meta = {"bt": bt, "mb": bt.shape[1], "slot_map": slot_map.contiguous(), "lens": (pos + 1).to(torch.int32),
                     "splits": splits}
+        res, pending = x, None
         for i, layer in enumerate(m.layers):
-            h = layer.input_layernorm(x)
+            h, res = self._add_norm(pending, res, layer.input_layernorm)
             mixer = layer.seq_mixer
             if isinstance(mixer, Attention):
                 y = self._attn_decode(i, mixer, h, cos, sin, meta)
@@ -363,34 +364,82 @@ class ServingEngine:
                 raise NotImplementedError(type(mixer).__name__)
             if self.tp is not None:
                 y = self.tp.all_reduce(y)
-            x = x + y
-            h2 = layer.post_attention_layernorm(x)
-            y2 = layer.mlp(h2)
-            y2 = y2[0] if isinstance(y2, tuple) else y2      # (under TP the MLP's forward hook has reduced it)
-            x = x + y2
-        return self._logits(m.norm(x))
+            h2, res = self._add_norm(y, res, layer.post_attention_layernorm)
+            pending = self._mlp_decode(i, layer.mlp, h2)
+        h, _ = self._add_norm(pending, res, m.norm)
+        return self._logits(h)
+
+    def _add_norm(self, y, res, norm):
+        """``res + y`` followed by RMSNorm, in one kernel on the GPU.  Returns ``(normed, new residual)``."""
+        if y is None:
+            return norm(res), res
+        if self._cuda and res.dtype == torch.bfloat16 and not getattr(norm, "zero_centered", False):
+            return F_ops.fused_add_rms_norm(y, res, norm.weight, norm.variance_epsilon)
+        res = res + y
+        return norm(res), res
+
+    def _mlp_decode(self, i, mlp, h):
+        from ..layers.common import MLP
+        if not (self._cuda and isinstance(mlp, MLP) and h.dtype == torch.bfloat16 and mlp.gate_proj.bias is None):
+            y = mlp(h)                       # (under TP the MLP's forward hook reduces the partial sums)
+            return y[0] if isinstance(y, tuple) else y
+        c = self._layer_cache.setdefault(("mlp", i), {})
+        if not c:
+            c["w_gu"] = torch.cat([mlp.gate_proj.weight, mlp.up_proj.weight], dim=0).contiguous()
+        gu = F.linear(h, c["w_gu"])
+        Fi = gu.shape[-1] // 2
+        a = torch.empty(h.shape[0], Fi, device=h.device, dtype=h.dtype)
+        _lib.check(_lib.kernels().hmf_swiglu_packed(_lib.ptr(gu), _lib.ptr(a), c_ll(h.shape[0]), c_int(Fi),
+                                                    c_ll(gu.stride(0)), _lib.stream_ptr(h.device)), "swiglu_packed")
+        y = F.linear(a, mlp.down_proj.weight)
+        return self.tp.all_reduce(y) if self.tp is not None else y
 
     def _attn_decode(self, i, mx: Attention, h, cos, sin, meta):
         Rn = h.shape[0]
-        q = mx.q_proj(h)
+        fused = (self._cuda and mx.head_dim == 128 and h.dtype == torch.bfloat16 and not mx.gated
+                 and cos.shape[-1] % 2 == 0)
         gate = None
-        if mx.gated:
-            q = q.view(Rn, mx.num_heads, 2 * mx.head_dim)
-            q, gate = q[..., :mx.head_dim], q[..., mx.head_dim:].reshape(Rn, -1)
-        q = q.reshape(Rn, 1, mx.num_heads, mx.head_dim)
-        k = mx.k_proj(h).view(Rn, 1, mx.num_kv_heads, mx.head_dim)
-        v = mx.v_proj(h).view(Rn, mx.num_kv_heads, mx.head_dim)
-        if mx.q_norm is not None:
-            q, k = mx.q_norm(q), mx.k_norm(k)
-        q, k = F_ops.apply_rope(q, cos, sin)[:, 0], F_ops.apply_rope(k, cos, sin)[:, 0]
+        if fused:
+            c = self._layer_cache.setdefault(("attn", i), {})
+            if not c:
+                c["w"] = torch.cat([mx.q_proj.weight, mx.k_proj.weight, mx.v_proj.weight], dim=0).contiguous()
+                c["b"] = (torch.cat([mx.q_proj.bias, mx.k_proj.bias, mx.v_proj.bias]).contiguous()
+                          if mx.q_proj.bias is not None else None)
+            qkv = F.linear(h, c["w"], c["b"])
+            kc, vc = self.state.kv[i]
+            q = torch.empty(Rn, mx.num_heads, mx.head_dim, device=h.device, dtype=h.dtype)
+            qn = mx.q_norm
+            cs, sn = cos.reshape(Rn, -1).contiguous(), sin.reshape(Rn, -1).contiguous()
+            _lib.check(_lib.kernels().hmf_qkv_norm_rope_append(
+                _lib.ptr(qkv), c_ll(qkv.stride(0)), _lib.ptr(qn.weight if qn is not None else None),
+                _lib.ptr(mx.k_norm.weight if qn is not None else None),
+                c_float(qn.variance_epsilon if qn is not None else 0.0),
+                c_int(int(getattr(qn, "zero_centered", False)) if qn is not None else 0), _lib.ptr(cs), _lib.ptr(sn),
+                c_int(cs.shape[-1]), _lib.ptr(q), _lib.ptr(kc), _lib.ptr(vc), _lib.ptr(meta["slot_map"]), c_int(Rn),
+                c_int(mx.num_heads), c_int(mx.num_kv_heads), c_int(mx.head_dim), _lib.stream_ptr(h.device)),
+                "qkv_norm_rope_append")
+            k = v = None
+        else:
+            q = mx.q_proj(h)
+            if mx.gated:
+                q = q.view(Rn, mx.num_heads, 2 * mx.head_dim)
+                q, gate = q[..., :mx.head_dim], q[..., mx.head_dim:].reshape(Rn, -1)
+            q = q.reshape(Rn, 1, mx.num_heads, mx.head_dim)
+            k = mx.k_proj(h).view(Rn, 1, mx.num_kv_heads, mx.head_dim)
+            v = mx.v_proj(h).view(Rn, mx.num_kv_heads, mx.head_dim)
+            if mx.q_norm is not None:
+                q, k = mx.q_norm(q), mx.k_norm(k)
+            q, k = F_ops.apply_rope(q, cos, sin)[:, 0], F_ops.apply_rope(k, cos, sin)[:, 0]
         kc, vc = self.state.kv[i]
         window = mx.sliding_window or 0
         if self._cuda and mx.head_dim == 128 and q.dtype == torch.bfloat16:
             K = _lib.kernels()
-            k, v, q = k.contiguous(), v.contiguous(), q.contiguous()
-            _lib.check(K.hmf_cache_append(_lib.ptr(k), _lib.ptr(v), _lib.ptr(kc), _lib.ptr(vc), _lib.ptr(meta["slot_map"]),
-                                          c_ll(Rn), c_int(mx.num_kv_heads), c_int(mx.head_dim), c_ll(k.stride(0)),
-                                          c_ll(v.stride(0)), _lib.stream_ptr(h.device)), "cache_append")
+            q = q.contiguous()
+            if k is not None:
+                k, v = k.contiguous(), v.contiguous()
+                _lib.check(K.hmf_cache_append(_lib.ptr(k), _lib.ptr(v), _lib.ptr(kc), _lib.ptr(vc), _lib.ptr(meta["slot_map"]),
+                                              c_ll(Rn), c_int(mx.num_kv_heads), c_int(mx.head_dim), c_ll(k.stride(0)),
+                                              c_ll(v.stride(0)), _lib.stream_ptr(h.device)), "cache_append")
             splits = meta["splits"]
             o = torch.empty(Rn, mx.num_heads, mx.head_dim, device=h.device, dtype=h.dtype)
             po = torch.empty(Rn, mx.num_heads, splits, mx.head_dim, device=h.device, dtype=torch.float32)
@@ -488,21 +537,34 @@ class ServingEngine:
         z, xBC, dt = torch.split(mx.in_proj(h), [mx.d_inner, mx.conv_dim, mx.nheads], dim=-1)
         xBC = mx._norm_rope(xBC[:, None], (cos, sin))[:, 0]
         xBC = self._conv_update(i, xBC.contiguous(), c["w"], c["b"], slots)
-        x, Bm, Cm = torch.split(xBC, [mx.d_xb, mx.d_xb, mx.d_inner], dim=-1)
-        A = -torch.exp(mx.A_log.float())
-        dtp = F.softplus(dt.float() + mx.dt_bias.float())
         st = self.state.ssm[i]["state"]
         Hx = mx.d_xb // mx.headdim
-        if self._cuda and h.dtype == torch.bfloat16:
+        packed = self._cuda and h.dtype == torch.bfloat16 and mx.d_state in (128, 256)
+        if not packed:
+            x, Bm, Cm = torch.split(xBC, [mx.d_xb, mx.d_xb, mx.d_inner], dim=-1)
+            A = -torch.exp(mx.A_log.float())
+            dtp = F.softplus(dt.float() + mx.dt_bias.float())
+        if self._cuda and h.dtype == torch.bfloat16 and mx.d_state in (128, 256):
+            # x / B / C are read straight from the convolution output, dt from the projection output
+            if "A_log" not in c:
+                c["A_log"], c["dt_bias"], c["D"] = (mx.A_log.float().contiguous(), mx.dt_bias.float().contiguous(),
+                                                   mx.D.float().contiguous())
+            y = torch.empty(Rn, mx.nheads, mx.headdim, device=h.device, dtype=h.dtype)
+            xBC = xBC if xBC.is_contiguous() else xBC.contiguous()
+            _lib.check(_lib.kernels().hmf_ssd_decode_packed(
+                _lib.ptr(xBC), c_ll(xBC.stride(0)), c_int(0), c_int(mx.d_xb), c_int(2 * mx.d_xb), _lib.ptr(dt),
+                c_ll(dt.stride(0)), _lib.ptr(c["dt_bias"]), _lib.ptr(c["A_log"]), _lib.ptr(c["D"]), _lib.ptr(st),
+                _lib.ptr(slots), _lib.ptr(y), c_int(Rn), c_int(mx.nheads), c_int(Hx), c_int(Hx), c_int(mx.headdim),
+                c_int(mx.d_state), _lib.stream_ptr(h.device)), "ssd_decode_packed")
+        elif self._cuda and h.dtype == torch.bfloat16:
             y = torch.empty(Rn, mx.nheads, mx.headdim, device=h.device, dtype=h.dtype)
             # keep the contiguous copies alive until the launch (a temporary's block would be reused)
             x, dtp, A, Bm, Cm, Dp = (x.contiguous(), dtp.contiguous(), A.contiguous(), Bm.contiguous(), Cm.contiguous(),
                                      mx.D.float().contiguous())
             _lib.check(_lib.kernels().hmf_ssd_decode(
                 _lib.ptr(x), _lib.ptr(dtp), _lib.ptr(A), _lib.ptr(Bm), _lib.ptr(Cm), _lib.ptr(Dp), _lib.ptr(st),
-                _lib.ptr(slots), _lib.ptr(y),
-                c_int(Rn), c_int(mx.nheads), c_int(Hx), c_int(Hx), c_int(mx.headdim), c_int(mx.d_state),
-                _lib.stream_ptr(h.device)), "ssd_decode")
+                _lib.ptr(slots), _lib.ptr(y), c_int(Rn), c_int(mx.nheads), c_int(Hx), c_int(Hx), c_int(mx.headdim),
+                c_int(mx.d_state), _lib.stream_ptr(h.device)), "ssd_decode")
         else:
             from ..layers.common import repeat_heads
             xh = repeat_heads(x.reshape(Rn, 1, Hx, mx.headdim), mx.num_kv_groups)[:, 0]
