@@ -1,0 +1,230 @@
+// Row-parallel GEMM fused with its tensor-parallel all-reduce over peer memory (decode-sized M).
+//
+//   y[M, N] = sum over ranks r of  x_r[M, Ks] . W_r[N, Ks]^T          (Ks = K / world, M <= 256)
+//
+// One kernel per rank, one CTA per 128 output columns:
+//   1. swap-AB tcgen05 GEMM: D^T[128 cols x Mpad] = W_tile[128 x Ks] . x^T   (A = weight rows and B = activations,
+//      both K-major, TMA -> shared memory ring -> tcgen05.mma, accumulator in tensor memory);
+//   2. the partial tile goes (bf16) to this rank's slot of a symmetric buffer; a release store raises the
+//      tile's flag on every peer;
+//   3. the CTA waits (bounded) for the same tile's flag from every rank, loads the W partials over NVLink with
+//      plain peer loads, adds them in rank order (every rank gets bit-identical results) and stores y.
+// The transfer of a tile overlaps the GEMM of the other tiles; no separate collective kernel is launched.
+//
+// Epochs come from device memory (`sync[0]`, advanced by the last CTA of each launch), so the kernel can be
+// replayed from a CUDA graph.  Partials are double-buffered by epoch parity: a rank can only be one launch
+// ahead of the slowest peer because it needs that peer's flags to finish a launch.
+#include "../common/host.h"
+#include "../common/sm100.cuh"
+
+namespace hmf {
+namespace gar {
+
+using bf16 = __nv_bfloat16;
+
+constexpr int BN = 128;          // output columns (weight rows) per CTA = MMA M
+constexpr int BK = 64;           // K per stage (one 128-byte swizzle atom)
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BN * BK * 2;             // 16 KB
+constexpr int MAX_M = 256;
+constexpr int B_BYTES = MAX_M * BK * 2;          // 32 KB (only Mpad rows are filled)
+constexpr int OFF_A = 0;
+constexpr int OFF_B = STAGES * A_BYTES;
+constexpr int OFF_BAR = OFF_B + STAGES * B_BYTES;
+constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
+constexpr int MAX_WORLD = 8;
+constexpr uint64_t kPeerWaitNs = 2000000000ull;
+
+struct Params {
+  bf16* y;                          // [M, N] local result
+  bf16* part[MAX_WORLD];            // every rank's partial buffers [2][max_m * max_n] as mapped here
+  unsigned int* flags[MAX_WORLD];   // every rank's flag array [max_tiles][MAX_WORLD]
+  unsigned int* sync;               // local: [0] epoch of the last finished launch, [1] CTA ticket
+  unsigned int* status;
+  long long part_stride;            // elements between the two parity buffers
+  int M, N, Ks, Mpad, rank, world, tmem_cols;
+};
+
+__global__ void __launch_bounds__(192, 1)
+gemm_allreduce_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
+  uint64_t* full = bars;                 // [STAGES]
+  uint64_t* empty = bars + STAGES;       // [STAGES]
+  uint64_t* acc_done = bars + 2 * STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const WaitCtx ctx{abort_flag, p.status};
+  const int tile = blockIdx.x;
+  const int n0 = tile * BN;
+  const int k_steps = p.Ks / BK;
+  const unsigned int epoch = *reinterpret_cast<volatile unsigned int*>(p.sync) + 1u;
+  const int parity = (int)(epoch & 1u);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(acc_done, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tmW);
+    tma_prefetch_desc(&tmX);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, p.tmem_cols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      const uint32_t bytes = A_BYTES + (uint32_t)p.Mpad * BK * 2;
+      for (int i = 0; i < k_steps; ++i) {
+        const int s = i % STAGES;
+        if (i >= STAGES) mbar_wait(&empty[s], ((i / STAGES) - 1) & 1, ctx, 0x10 + s);
+        mbar_expect_tx(&full[s], bytes);
+        tma_load_2d(smem + OFF_A + s * A_BYTES, &tmW, &full[s], i * BK, n0);
+        tma_load_2d(smem + OFF_B + s * B_BYTES, &tmX, &full[s], i * BK, 0);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_bf16(BN, p.Mpad, false, false);
+      for (int i = 0; i < k_steps; ++i) {
+        const int s = i % STAGES;
+        mbar_wait(&full[s], (i / STAGES) & 1, ctx, 0x20 + s);
+        tc_fence_after();
+        const uint32_t a = smem_u32(smem + OFF_A + s * A_BYTES), b = smem_u32(smem + OFF_B + s * B_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < BK / 16; ++kk)
+          umma_ss(tmem_base, make_desc_kmajor_sw128(a + kk * 32), make_desc_kmajor_sw128(b + kk * 32), idesc,
+                  (i > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(&empty[s]);
+      }
+      umma_commit(acc_done);
+    }
+  } else {
+    // ---------------- epilogue: partial store, flags, cross-rank reduction ----------------
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;                 // output column n0 + row
+    const int et = threadIdx.x - 64;                  // 0..127
+    const uint32_t lane_bits = (uint32_t)(quad * 32) << 16;
+    bf16* mine = p.part[p.rank] + (size_t)parity * p.part_stride;
+    mbar_wait(acc_done, 0, ctx, 0x30);
+    tc_fence_after();
+    for (int m0 = 0; m0 < p.Mpad; m0 += 16) {
+      uint32_t v[16];
+      tmem_ld_x16(tmem_base + lane_bits + m0, v);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 16; ++j)
+        if (m0 + j < p.M) mine[(size_t)(m0 + j) * p.N + n0 + row] = __float2bfloat16(__uint_as_float(v[j]));
+    }
+    __threadfence_system();
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (et < p.world) st_release_sys(p.flags[et] + (size_t)tile * MAX_WORLD + p.rank, epoch);
+    if (et < p.world)
+      wait_flag_sys(p.flags[p.rank] + (size_t)tile * MAX_WORLD + et, epoch, kPeerWaitNs, p.status, 0x40 + et);
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    // M x 128 tile = M x 16 chunks of 8 columns
+    const int chunks = p.M * (BN / 8);
+    for (int c = et; c < chunks; c += 128) {
+      const int m = c / (BN / 8), cc = (c % (BN / 8)) * 8;
+      const size_t off = (size_t)parity * p.part_stride + (size_t)m * p.N + n0 + cc;
+      float acc[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+      for (int r = 0; r < p.world; ++r) {
+        uint4 u;
+        const bf16* src = p.part[r] + off;
+        asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(u.x), "=r"(u.y), "=r"(u.z), "=r"(u.w)
+                     : "l"(src));
+        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __bfloat1622float2(h2[j]);
+          acc[2 * j] += f.x;
+          acc[2 * j + 1] += f.y;
+        }
+      }
+      uint4 o;
+      o.x = pack_bf16x2(acc[0], acc[1]);
+      o.y = pack_bf16x2(acc[2], acc[3]);
+      o.z = pack_bf16x2(acc[4], acc[5]);
+      o.w = pack_bf16x2(acc[6], acc[7]);
+      *reinterpret_cast<uint4*>(p.y + (size_t)m * p.N + n0 + cc) = o;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, p.tmem_cols);
+  }
+  // the last CTA of the launch publishes the epoch for the next launch
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const unsigned int ticket = atomicAdd(p.sync + 1, 1u);
+    if (ticket == gridDim.x - 1) {
+      p.sync[1] = 0u;
+      __threadfence();
+      *reinterpret_cast<volatile unsigned int*>(p.sync) = epoch;
+    }
+  }
+}
+
+}  // namespace gar
+}  // namespace hmf
+
+using namespace hmf;
+using namespace hmf::gar;
+
+// x [M, Ks] bf16 (row stride ldx), w [N, Ks] bf16 (row stride ldw), y [M, N] bf16.
+// part_ptrs / flag_ptrs: `world` device addresses (this process' mappings of every rank's buffers);
+// sync: two zero-initialised uint32 on this device, shared by every launch that uses the same buffers.
+HMF_API int hmf_gemm_allreduce(const void* x, const void* w, void* y, int M, int N, int Ks, long long ldx,
+                               long long ldw, const unsigned long long* part_ptrs,
+                               const unsigned long long* flag_ptrs, unsigned int* sync, long long part_stride,
+                               int max_tiles, int rank, int world, cudaStream_t st) {
+  HMF_REQUIRE(M >= 1 && M <= MAX_M, "gemm_allreduce: M=%d out of range (1..%d)", M, MAX_M);
+  HMF_REQUIRE(N % BN == 0 && Ks % BK == 0 && Ks > 0, "gemm_allreduce: N=%d must be a multiple of 128, Ks=%d of 64", N, Ks);
+  HMF_REQUIRE(world >= 1 && world <= MAX_WORLD && rank >= 0 && rank < world, "gemm_allreduce: bad rank %d / world %d",
+              rank, world);
+  HMF_REQUIRE(N / BN <= max_tiles, "gemm_allreduce: %d tiles exceed the flag array (%d)", N / BN, max_tiles);
+  HMF_REQUIRE((long long)M * N <= part_stride, "gemm_allreduce: partial buffer too small");
+  CUtensorMap tmW, tmX;
+  int rc;
+  const int Mpad = (M + 15) / 16 * 16;
+  if ((rc = make_map_2d_bf16(&tmW, w, N, Ks, ldw, BN, BK)) != HMF_OK) return rc;
+  if ((rc = make_map_2d_bf16(&tmX, x, M, Ks, ldx, Mpad, BK)) != HMF_OK) return rc;
+  static bool configured = false;
+  if (!configured) {
+    HMF_CHECK_CUDA(cudaFuncSetAttribute(gemm_allreduce_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    configured = true;
+  }
+  Params p;
+  p.y = (bf16*)y;
+  for (int r = 0; r < MAX_WORLD; ++r) {
+    p.part[r] = r < world ? reinterpret_cast<bf16*>(part_ptrs[r]) : nullptr;
+    p.flags[r] = r < world ? reinterpret_cast<unsigned int*>(flag_ptrs[r]) : nullptr;
+  }
+  p.sync = sync;
+  p.status = status_ptr();
+  p.part_stride = part_stride;
+  p.M = M; p.N = N; p.Ks = Ks; p.Mpad = Mpad; p.rank = rank; p.world = world;
+  int cols = 32;
+  while (cols < Mpad) cols *= 2;
+  p.tmem_cols = cols;
+  gemm_allreduce_kernel<<<N / BN, 192, SMEM_BYTES, st>>>(tmW, tmX, p);
+  HMF_CHECK_CUDA(cudaGetLastError());
+  return HMF_OK;
+}

@@ -176,9 +176,15 @@ class GDNChunkCore(ScanCore):
             del f, a, b_, c_, d_
         return wqT, kPT, uT, glast, N
 
-    def forward(self, inputs, state0):
+    def peer_capable(self, inputs) -> bool:
+        """The scan kernels can receive / push the state over peer memory for these inputs."""
+        q, k, v = inputs[:3]
+        return available() and self._supported(q, k, v)
+
+    def forward(self, inputs, state0, peer=None):
         q, k, v, g, beta = inputs
         if not self._supported(q, k, v):
+            assert peer is None
             out, sT, saved, meta = self._fallback.forward(inputs, state0)
             return out, sT, saved, ("fallback", meta)
         B, T, H, Dk = q.shape
@@ -188,21 +194,30 @@ class GDNChunkCore(ScanCore):
         with torch.no_grad():
             wqT, kPT, uT, glast, N = self._prep_packed(q, k, v, g, beta)
             h0 = None if state0 is None else state0[0].float().contiguous()
+            h0_flag, push_ptr, push_flag, epoch = None, None, None, 0
+            if peer is not None:
+                if peer.recv is not None:       # incoming state arrives in the symmetric buffer
+                    h0, h0_flag = peer.recv, peer.recv_flag
+                push_ptr = ctypes.c_void_p(peer.push_ptr) if peer.push_ptr else None
+                push_flag = ctypes.c_void_p(peer.push_flag_ptr) if peer.push_ptr else None
+                epoch = peer.epoch
             o = torch.empty(B, T, H, Dv, device=q.device, dtype=BF16)
             hT = torch.empty(B, H, Dk, Dv, device=q.device, dtype=torch.float32)
             vnT = torch.empty(B * H, N, Dv, C, device=q.device, dtype=BF16) if need_bwd else None
             h_all = torch.empty(B * H, N, Dv, Dk, device=q.device, dtype=BF16) if need_bwd else None
             rc = _lib.kernels().hmf_gdn_scan_fwd(
                 _lib.ptr(wqT), _lib.ptr(kPT), _lib.ptr(uT), _lib.ptr(glast), _lib.ptr(h0), _lib.ptr(hT), _lib.ptr(o),
-                _lib.ptr(vnT), _lib.ptr(h_all), c_int(B), c_int(H), c_int(T), c_int(N), None, None, None, c_uint(0),
-                _lib.stream_ptr(q.device))
+                _lib.ptr(vnT), _lib.ptr(h_all), c_int(B), c_int(H), c_int(T), c_int(N), _lib.ptr(h0_flag), push_ptr,
+                push_flag, c_uint(epoch), _lib.stream_ptr(q.device))
             _lib.check(rc, "hmf_gdn_scan_fwd")
-        saved = [q, k, v, g, beta, h0, vnT, h_all]
-        return o, (hT,), saved, ("cuda", state0 is not None)
+        # the incoming state itself is not needed again: the backward kernel reads the per-chunk states
+        saved = [q, k, v, g, beta, None, vnT, h_all]
+        return o, (hT,), saved, ("cuda", h0 is not None)
 
-    def backward(self, saved, meta, d_out, d_stateT):
+    def backward(self, saved, meta, d_out, d_stateT, peer=None):
         kind, info = meta
         if kind == "fallback":
+            assert peer is None
             return self._fallback.backward(saved, info, d_out, d_stateT)
         q, k, v, g, beta, h0, vnT, h_all = saved
         B, T, H, Dk = q.shape
@@ -213,13 +228,20 @@ class GDNChunkCore(ScanCore):
             dhT = None
             if d_stateT is not None and d_stateT[0] is not None:
                 dhT = d_stateT[0].float().contiguous()
+            dhT_flag, push_ptr, push_flag, epoch = None, None, None, 0
+            if peer is not None:
+                if peer.recv is not None:       # gradient of the outgoing state arrives in the symmetric buffer
+                    dhT, dhT_flag = peer.recv, peer.recv_flag
+                push_ptr = ctypes.c_void_p(peer.push_ptr) if peer.push_ptr else None
+                push_flag = ctypes.c_void_p(peer.push_flag_ptr) if peer.push_ptr else None
+                epoch = peer.epoch
             dh0 = torch.empty(B, H, Dk, Dv, device=q.device, dtype=torch.float32) if info else None
             dvnT = torch.empty(B * H, N, Dv, C, device=q.device, dtype=BF16)
             dS_all = torch.empty(B * H, N, Dv, Dk, device=q.device, dtype=BF16)
             rc = _lib.kernels().hmf_gdn_scan_bwd(
                 _lib.ptr(wqT), _lib.ptr(kPT), _lib.ptr(do), _lib.ptr(glast), _lib.ptr(dhT), _lib.ptr(dh0),
-                _lib.ptr(dvnT), _lib.ptr(dS_all), c_int(B), c_int(H), c_int(T), c_int(N), None, None, None, c_uint(0),
-                _lib.stream_ptr(q.device))
+                _lib.ptr(dvnT), _lib.ptr(dS_all), c_int(B), c_int(H), c_int(T), c_int(N), _lib.ptr(dhT_flag), push_ptr,
+                push_flag, c_uint(epoch), _lib.stream_ptr(q.device))
             _lib.check(rc, "hmf_gdn_scan_bwd")
             del wqT, kPT
             dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)

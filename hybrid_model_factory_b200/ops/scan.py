@@ -111,6 +111,18 @@ def _split_time(t: Optional[Tensor]):
     return t[:, :half], t[:, half:]
 
 
+def _peer_plan(core, transport, seg_inputs):
+    """``(state shape, batch*heads)`` when both the core and the transport can run the state chain inside the
+    scan kernels (peer-memory push / flag wait), else ``None``."""
+    if not hasattr(transport, "peer_io") or not getattr(core, "peer_capable", None):
+        return None
+    if not core.peer_capable(seg_inputs):
+        return None
+    shape, dtype = core.state_shapes(seg_inputs)[0]
+    bh = int(shape[0]) * int(shape[1])
+    return (tuple(shape), bh) if transport.fits(shape, dtype, bh) else None
+
+
 class _SSMScan(torch.autograd.Function):
     @staticmethod
     def forward(ctx, core: ScanCore, sp, n_inputs: int, want_state: bool, *tensors):
@@ -128,20 +140,30 @@ class _SSMScan(torch.autograd.Function):
         r, n = sp.rank, sp.size
         seg_a, seg_b = zip(*[_split_time(t) for t in inputs])
         tr = sp.transport
-        # first segments: chunk r, chain 0 -> n-1
-        if r > 0:
-            h0 = tr.recv_state(core, list(seg_a), src=r - 1, tag="fwd_a")
+        ctx.peer = _peer_plan(core, tr, list(seg_a))
+        if ctx.peer is not None:
+            # in-kernel state chain over peer memory: both launches are queued at once, the kernels wait for
+            # the incoming state themselves and push the outgoing one into the next rank's buffer
+            shape, bh = ctx.peer
+            io_a = tr.peer_io("fwd_a", shape, bh, r - 1 if r > 0 else None, r + 1 if r < n - 1 else None)
+            out_a, sT_a, saved_a, meta_a = core.forward(list(seg_a), state0 if r == 0 else None, peer=io_a)
+            io_b = tr.peer_io("fwd_b", shape, bh, r + 1 if r < n - 1 else None, r - 1 if r > 0 else None)
+            out_b, sT_b, saved_b, meta_b = core.forward(list(seg_b), sT_a if r == n - 1 else None, peer=io_b)
         else:
-            h0 = state0
-        out_a, sT_a, saved_a, meta_a = core.forward(list(seg_a), h0)
-        if r < n - 1:
-            tr.send_state(sT_a, dst=r + 1, tag="fwd_a")
-            h0b = tr.recv_state(core, list(seg_b), src=r + 1, tag="fwd_b")
-        else:
-            h0b = sT_a
-        out_b, sT_b, saved_b, meta_b = core.forward(list(seg_b), h0b)
-        if r > 0:
-            tr.send_state(sT_b, dst=r - 1, tag="fwd_b")
+            # first segments: chunk r, chain 0 -> n-1
+            if r > 0:
+                h0 = tr.recv_state(core, list(seg_a), src=r - 1, tag="fwd_a")
+            else:
+                h0 = state0
+            out_a, sT_a, saved_a, meta_a = core.forward(list(seg_a), h0)
+            if r < n - 1:
+                tr.send_state(sT_a, dst=r + 1, tag="fwd_a")
+                h0b = tr.recv_state(core, list(seg_b), src=r + 1, tag="fwd_b")
+            else:
+                h0b = sT_a
+            out_b, sT_b, saved_b, meta_b = core.forward(list(seg_b), h0b)
+            if r > 0:
+                tr.send_state(sT_b, dst=r - 1, tag="fwd_b")
         ctx.save_for_backward(*saved_a, *saved_b)
         ctx.counts, ctx.metas = [len(saved_a), len(saved_b)], [meta_a, meta_b]
         ctx.state_templates = tuple((s.shape, s.dtype) if s is not None else None for s in sT_b)
@@ -165,20 +187,27 @@ class _SSMScan(torch.autograd.Function):
         d_a, d_b = d_out[:, :half], d_out[:, half:]
         saved_a, saved_b = saved_all[:ctx.counts[0]], saved_all[ctx.counts[0]:]
         device = d_out.device
-        # second segments first: chain 0 -> n-1 (reverse of the forward chain n-1 -> 0)
-        if r > 0:
-            dhT_b = tr.recv_state_like(ctx.state_templates, device, src=r - 1, tag="bwd_b")
+        if ctx.peer is not None:
+            shape, bh = ctx.peer
+            io_b = tr.peer_io("bwd_b", shape, bh, r - 1 if r > 0 else None, r + 1 if r < n - 1 else None)
+            d_in_b, d_h0b = core.backward(saved_b, ctx.metas[1], d_b, d_state if r == 0 else None, peer=io_b)
+            io_a = tr.peer_io("bwd_a", shape, bh, r + 1 if r < n - 1 else None, r - 1 if r > 0 else None)
+            d_in_a, d_h0a = core.backward(saved_a, ctx.metas[0], d_a, d_h0b if r == n - 1 else None, peer=io_a)
         else:
-            dhT_b = d_state
-        d_in_b, d_h0b = core.backward(saved_b, ctx.metas[1], d_b, dhT_b)
-        if r < n - 1:
-            tr.send_state(d_h0b, dst=r + 1, tag="bwd_b")
-            dhT_a = tr.recv_state_like(ctx.state_templates, device, src=r + 1, tag="bwd_a")
-        else:
-            dhT_a = d_h0b
-        d_in_a, d_h0a = core.backward(saved_a, ctx.metas[0], d_a, dhT_a)
-        if r > 0:
-            tr.send_state(d_h0a, dst=r - 1, tag="bwd_a")
+            # second segments first: chain 0 -> n-1 (reverse of the forward chain n-1 -> 0)
+            if r > 0:
+                dhT_b = tr.recv_state_like(ctx.state_templates, device, src=r - 1, tag="bwd_b")
+            else:
+                dhT_b = d_state
+            d_in_b, d_h0b = core.backward(saved_b, ctx.metas[1], d_b, dhT_b)
+            if r < n - 1:
+                tr.send_state(d_h0b, dst=r + 1, tag="bwd_b")
+                dhT_a = tr.recv_state_like(ctx.state_templates, device, src=r + 1, tag="bwd_a")
+            else:
+                dhT_a = d_h0b
+            d_in_a, d_h0a = core.backward(saved_a, ctx.metas[0], d_a, dhT_a)
+            if r > 0:
+                tr.send_state(d_h0a, dst=r - 1, tag="bwd_a")
         d_inputs = []
         for ga, gb in zip(d_in_a, d_in_b):
             d_inputs.append(None if ga is None else torch.cat([ga, gb], dim=1))

@@ -1,0 +1,129 @@
+"""Peer-memory plumbing: symmetric buffers whose address on every rank of a group is known to every other
+rank, so kernels can load / store a neighbour's memory over NVLink directly.
+
+``SymmetricWorkspace`` wraps ``torch.distributed._symmetric_memory`` (CUDA VMM allocation + handle exchange;
+one process per GPU, single node).  Users:
+
+* ``PeerStateTransport`` — sequence-parallel state chain of the SSM scans: the scan kernel of rank ``r``
+  stores its final recurrent state into the *next* rank's buffer and raises a per-(batch, head) flag; the
+  next rank's kernel, already launched, starts its recurrence when the flag arrives
+  (``csrc/kernels/gdn_scan.cu``).  No host synchronisation, no separate send/recv kernels.  The reference
+  passes these states with blocking NCCL send/recv around the kernels
+  (``layers/gated_kalmanet/sequence_parallel/gka_sp_utils.py:113-226``).
+* ``ops/fused_comm.py`` — tensor-parallel GEMM + all-reduce and the peer all-reduce of the decode step.
+* ``parallel/cp_attention.py`` — context-parallel attention reading remote K/V tiles by TMA.
+
+Flags are monotonically increasing epochs, never reset: a reader waits for ``flag >= epoch``.  A buffer is
+reused every epoch; the chain's data dependencies order the reuse (the writer of epoch ``e+1`` has, through the
+opposite chain of epoch ``e``, already waited for the reader of epoch ``e``).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from .sp import StateTransport
+
+
+class SymmetricWorkspace:
+    """``nbytes`` of symmetric memory on every rank of ``group``; ``ptrs[r]`` is rank ``r``'s base address as
+    mapped into this process."""
+
+    def __init__(self, nbytes: int, group, device: Optional[torch.device] = None):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.group = group
+        self.device = device or torch.device("cuda", torch.cuda.current_device())
+        nbytes = (int(nbytes) + 1023) // 1024 * 1024
+        self.buffer = symm_mem.empty(nbytes, dtype=torch.uint8, device=self.device)
+        self.handle = symm_mem.rendezvous(self.buffer, group)
+        self.rank, self.world = self.handle.rank, self.handle.world_size
+        self.ptrs: List[int] = [int(p) for p in self.handle.buffer_ptrs]
+        self.nbytes = nbytes
+        self.buffer.zero_()
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=group)
+
+    def view(self, offset: int, shape, dtype) -> torch.Tensor:
+        n = 1
+        for s in shape:
+            n *= int(s)
+        nbytes = n * torch.empty((), dtype=dtype).element_size()
+        assert offset % 16 == 0 and offset + nbytes <= self.nbytes, "symmetric workspace view out of range"
+        return self.buffer[offset:offset + nbytes].view(dtype).view(*shape)
+
+    def peer_ptr(self, rank: int, offset: int = 0) -> int:
+        return self.ptrs[rank] + offset
+
+    def barrier(self) -> None:
+        """All kernels launched so far on every rank of the group have finished."""
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)
+
+
+@dataclass
+class PeerIO:
+    """What one scan launch needs to take part in the state chain."""
+    recv: Optional[torch.Tensor]        # local symmetric buffer the previous rank writes (None: chain start)
+    recv_flag: Optional[torch.Tensor]   # [BH] uint32 epochs, local
+    push_ptr: int                       # address of the next rank's buffer (0: chain end)
+    push_flag_ptr: int
+    epoch: int
+
+
+class PeerStateTransport(StateTransport):
+    """State chain over peer memory for scan cores that implement the in-kernel push / wait
+    (``core.peer_capable(inputs)``); every other core falls back to the NCCL send/recv of the base class."""
+
+    TAGS = ("fwd_a", "fwd_b", "bwd_a", "bwd_b")
+
+    def __init__(self, group, ranks, sp_rank: int, max_state_bytes: int = 8 << 20, max_bh: int = 4096):
+        super().__init__(group, ranks)
+        self.sp_rank, self.size = sp_rank, len(ranks)
+        self.state_bytes = (max_state_bytes + 1023) // 1024 * 1024
+        self.flag_bytes = (max_bh * 4 + 1023) // 1024 * 1024
+        self.slot = self.state_bytes + self.flag_bytes
+        self.ws = SymmetricWorkspace(self.slot * len(self.TAGS), group)
+        self.epochs: Dict[str, int] = {t: 0 for t in self.TAGS}
+        self.max_bh = max_bh
+        self.fused_messages = 0
+
+    def fits(self, shape, dtype, bh: int) -> bool:
+        n = 1
+        for s in shape:
+            n *= int(s)
+        return n * torch.empty((), dtype=dtype).element_size() <= self.state_bytes and bh <= self.max_bh
+
+    def peer_io(self, tag: str, shape, bh: int, recv_from: Optional[int], send_to: Optional[int]) -> PeerIO:
+        """``recv_from`` / ``send_to`` are SP ranks (or ``None``).  Every rank of the group must call this for
+        the same sequence of tags, whether or not it receives or sends (the epoch counters advance in step)."""
+        i = self.TAGS.index(tag)
+        self.epochs[tag] += 1
+        epoch = self.epochs[tag]
+        base = i * self.slot
+        recv = recv_flag = None
+        if recv_from is not None:
+            recv = self.ws.view(base, shape, torch.float32)
+            recv_flag = self.ws.view(base + self.state_bytes, (bh,), torch.int32)
+        push_ptr = push_flag_ptr = 0
+        if send_to is not None:
+            push_ptr = self.ws.peer_ptr(send_to, base)
+            push_flag_ptr = self.ws.peer_ptr(send_to, base + self.state_bytes)
+            self.fused_messages += 1
+        return PeerIO(recv, recv_flag, push_ptr, push_flag_ptr, epoch)
+
+
+def enable_peer_transport(sp, max_state_bytes: int = 8 << 20) -> bool:
+    """Replaces the NCCL state transport of an ``SPContext`` by the peer-memory one.  Returns False (and leaves
+    the context unchanged) when symmetric memory cannot be set up (CPU ranks, no P2P access)."""
+    if sp is None or sp.size <= 1 or not torch.cuda.is_available():
+        return False
+    try:
+        sp.transport = PeerStateTransport(sp.group, sp.ranks, sp.rank, max_state_bytes)
+        return True
+    except Exception as e:  # pragma: no cover - depends on the machine
+        import warnings
+        warnings.warn(f"peer-memory state transport unavailable ({e}); using NCCL send/recv")
+        return False

@@ -26,13 +26,25 @@ class TPContext:
         self.group = group
         self.rank = dist.get_rank(group) if rank is None else rank
         self.size = dist.get_world_size(group) if size is None else size
-        self.fused = None          # optional peer-memory all-reduce (ops.fused_comm.PeerAllReduce)
+        self.fused_gemm = None     # optional ops.fused_comm.PeerGemmAllReduce (GEMM + all-reduce in one kernel)
+
+    def enable_fused_gemm(self, max_m: int = 256, max_n: int = 8192) -> bool:
+        """Sets up the peer-memory GEMM + all-reduce kernel (collective call; GPU ranks of one node)."""
+        if self.size == 1 or not torch.cuda.is_available():
+            return False
+        from ..ops.fused_comm import PeerGemmAllReduce
+        self.fused_gemm = PeerGemmAllReduce(self.group, max_m, max_n)
+        return True
+
+    def linear_allreduce(self, x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+        """``all_reduce(x @ weight^T)`` for a row-parallel weight shard ``[N, K / size]``."""
+        if self.size > 1 and self.fused_gemm is not None and self.fused_gemm.accepts(x, weight):
+            return self.fused_gemm(x, weight)
+        return self.all_reduce(torch.nn.functional.linear(x, weight))
 
     def all_reduce(self, x: torch.Tensor) -> torch.Tensor:
         if self.size == 1:
             return x
-        if self.fused is not None and self.fused.accepts(x):
-            return self.fused(x)
         x = x.contiguous()
         dist.all_reduce(x, group=self.group)
         return x

@@ -362,8 +362,6 @@ class ServingEngine:
                 y = self._gka_decode(i, mixer, h, slots)
             else:
                 raise NotImplementedError(type(mixer).__name__)
-            if self.tp is not None:
-                y = self.tp.all_reduce(y)
             h2, res = self._add_norm(y, res, layer.post_attention_layernorm)
             pending = self._mlp_decode(i, layer.mlp, h2)
         h, _ = self._add_norm(pending, res, m.norm)
@@ -391,8 +389,16 @@ class ServingEngine:
         a = torch.empty(h.shape[0], Fi, device=h.device, dtype=h.dtype)
         _lib.check(_lib.kernels().hmf_swiglu_packed(_lib.ptr(gu), _lib.ptr(a), c_ll(h.shape[0]), c_int(Fi),
                                                     c_ll(gu.stride(0)), _lib.stream_ptr(h.device)), "swiglu_packed")
-        y = F.linear(a, mlp.down_proj.weight)
-        return self.tp.all_reduce(y) if self.tp is not None else y
+        return self._row_linear(a, mlp.down_proj)
+
+    def _row_linear(self, x, lin):
+        """Output projection of a mixer / MLP: under TP the weight is a row-parallel shard and the partial sums
+        are reduced inside the GEMM kernel (peer memory) or by NCCL."""
+        if self.tp is None or self.tp.size == 1:
+            return lin(x)
+        if lin.bias is None:
+            return self.tp.linear_allreduce(x, lin.weight)
+        return self.tp.all_reduce(lin(x))
 
     def _attn_decode(self, i, mx: Attention, h, cos, sin, meta):
         Rn = h.shape[0]
@@ -472,7 +478,7 @@ class ServingEngine:
         o = o.reshape(Rn, -1)
         if gate is not None:
             o = o * torch.sigmoid(gate)
-        return mx.o_proj(o)
+        return self._row_linear(o, mx.o_proj)
 
     def _conv_update(self, i, x_cat, weight, bias, slots):
         e = self.state.ssm[i]
@@ -529,7 +535,7 @@ class ServingEngine:
             o = mx.o_norm(o, mx.g_proj(h).view(Rn, H, D))
         else:
             o = mx.o_norm(o)
-        return mx.o_proj(o.reshape(Rn, -1))
+        return self._row_linear(o.reshape(Rn, -1), mx.o_proj)
 
     def _mamba_decode(self, i, mx: Mamba2, h, cos, sin, slots):
         Rn = h.shape[0]
@@ -576,7 +582,7 @@ class ServingEngine:
             y = y.to(h.dtype)
         zg = z.reshape(Rn, mx.nheads, mx.headdim)
         y = F_ops.gated_rms_norm(y, zg, mx.norm.weight.view(mx.nheads, mx.headdim), mx.norm.eps, norm_before_gate=False)
-        return mx.out_proj(y.reshape(Rn, mx.d_inner))
+        return self._row_linear(y.reshape(Rn, mx.d_inner), mx.out_proj)
 
     def _gka_decode(self, i, mx: GatedKalmaNet, h, slots):
         """GKA decode: conv update + token-level solve and GLA update on the slot states."""
@@ -612,7 +618,7 @@ class ServingEngine:
         o = o[:, 0].to(h.dtype)
         H = mx.expanded_num_heads
         o = mx.o_norm(o, mx.g_proj(h).view(Rn, H, D)) if mx.use_gate else mx.o_norm(o)
-        return mx.o_proj(o.reshape(Rn, -1))
+        return self._row_linear(o.reshape(Rn, -1), mx.o_proj)
 
     # -- metrics ---------------------------------------------------------------------------------------
     def request_metrics(self) -> dict:

@@ -14,13 +14,18 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
-def _entry(rank, world, port, fn, args, errq):
+def _entry(rank, world, port, fn, args, errq, backend="gloo"):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     os.environ["RANK"], os.environ["WORLD_SIZE"] = str(rank), str(world)
+    os.environ["LOCAL_RANK"] = str(rank)
     torch.set_num_threads(2)
     try:
-        dist.init_process_group("gloo", rank=rank, world_size=world)
+        if backend == "nccl":
+            torch.cuda.set_device(rank)
+            dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+        else:
+            dist.init_process_group("gloo", rank=rank, world_size=world)
         fn(rank, world, *args)
         dist.barrier()
     except Exception:
@@ -30,11 +35,11 @@ def _entry(rank, world, port, fn, args, errq):
             dist.destroy_process_group()
 
 
-def run_ranks(fn, world: int, *args, timeout: float = 300.0):
+def run_ranks(fn, world: int, *args, timeout: float = 300.0, backend: str = "gloo"):
     ctx = mp.get_context("spawn")
     errq = ctx.SimpleQueue()
     port = _free_port()
-    procs = [ctx.Process(target=_entry, args=(r, world, port, fn, args, errq)) for r in range(world)]
+    procs = [ctx.Process(target=_entry, args=(r, world, port, fn, args, errq, backend)) for r in range(world)]
     for p in procs:
         p.start()
     for p in procs:

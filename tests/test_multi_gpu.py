@@ -1,0 +1,115 @@
+"""Multi-GPU paths (one process per GPU, NCCL + peer memory).  Skipped unless at least two GPUs are visible."""
+import pytest
+import torch
+import torch.distributed as dist
+
+from dist_utils import run_ranks
+
+pytestmark = pytest.mark.gpu
+needs2 = pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+
+
+def _rel(a, b):
+    return ((a.float() - b.float()).norm() / (b.float().norm() + 1e-12)).item()
+
+
+def _sp_gdn_worker(rank, world, use_peer):
+    from hybrid_model_factory_b200.ops import _lib, mixers
+    from hybrid_model_factory_b200.parallel.peer import enable_peer_transport
+    from hybrid_model_factory_b200.parallel.sp import init_sp_group, zigzag_split
+    dev = torch.device("cuda", rank)
+    g = torch.Generator(device="cpu").manual_seed(0)
+    B, T, H, D = 1, 4096, 4, 128
+    mk = lambda *s: torch.randn(*s, generator=g)  # noqa: E731
+    q, k, v = (mk(B, T, H, D).bfloat16().to(dev) for _ in range(3))
+    gg = (-torch.rand(B, T, H, generator=g) * 0.1).to(dev)
+    beta = torch.rand(B, T, H, generator=g).to(dev)
+    h0 = (mk(B, H, D, D) * 0.1).to(dev)
+    do = mk(B, T, H, D).bfloat16().to(dev)
+    dsT = (mk(B, H, D, D) * 0.1).to(dev)
+    # single-GPU result
+    full = [t.clone().requires_grad_(True) for t in (q, k, v, gg, beta, h0)]
+    o_ref, s_ref = mixers.gated_delta_rule(*full[:5], initial_state=full[5])
+    torch.autograd.backward([o_ref, s_ref], [do, dsT])
+    # sequence parallel over the ranks
+    sp = init_sp_group(world)
+    if use_peer:
+        assert enable_peer_transport(sp)
+    loc = [zigzag_split(t, sp.rank, sp.size).contiguous().clone().requires_grad_(True) for t in (q, k, v, gg, beta)]
+    h0l = h0.clone().requires_grad_(True)
+    for it in range(3):    # several epochs through the same symmetric buffers
+        for t in loc + [h0l]:
+            t.grad = None
+        o, sT = mixers.gated_delta_rule(*loc, initial_state=h0l if rank == 0 else None, sp=sp)
+        if rank == 0:
+            torch.autograd.backward([o, sT], [zigzag_split(do, rank, world), dsT])
+        else:
+            torch.autograd.backward([o], [zigzag_split(do, rank, world)])
+        torch.cuda.synchronize()
+        _lib.assert_status_ok()
+        assert _rel(o, zigzag_split(o_ref, rank, world)) < 2e-2
+        for a, b in zip(loc, full[:5]):
+            assert _rel(a.grad, zigzag_split(b.grad, rank, world)) < 5e-2
+        if rank == 0:
+            assert _rel(sT, s_ref) < 2e-2 and _rel(h0l.grad, full[5].grad) < 5e-2
+    if use_peer:
+        assert sp.transport.fused_messages > 0 and sp.transport.messages == 0
+    dist.barrier()
+
+
+@needs2
+@pytest.mark.parametrize("use_peer", [False, True])
+def test_sp_gdn_state_chain_two_gpus(use_peer):
+    run_ranks(_sp_gdn_worker, 2, use_peer, backend="nccl", timeout=240)
+
+
+def _tp_worker(rank, world):
+    import torch.nn.functional as F
+    from hybrid_model_factory_b200.models.configuration import HybridConfig
+    from hybrid_model_factory_b200.models.modeling_hybrid import build_model
+    from hybrid_model_factory_b200.ops import _lib
+    from hybrid_model_factory_b200.parallel.tp import TPContext, shard_model
+    from hybrid_model_factory_b200.serving.engine import SamplingParams, ServingEngine
+    dev = torch.device("cuda", rank)
+    tp = TPContext(dist.group.WORLD)
+    assert tp.enable_fused_gemm(max_m=256, max_n=4096)
+    # 1. the fused kernel against NCCL
+    g = torch.Generator().manual_seed(rank)
+    for M, N, K in ((3, 512, 128), (64, 4096, 512), (130, 1024, 320)):
+        for _ in range(3):
+            x = torch.randn(M, K, generator=g).bfloat16().to(dev)
+            w = (torch.randn(N, K, generator=g) * 0.05).bfloat16().to(dev)
+            y = tp.linear_allreduce(x, w)
+            ref = F.linear(x, w).float()
+            dist.all_reduce(ref)
+            assert (y.float() - ref).abs().max() < 3e-2 * ref.abs().max() + 1e-2
+            ys = [torch.empty_like(y) for _ in range(world)]
+            dist.all_gather(ys, y)
+            assert all(torch.equal(ys[0], t) for t in ys)        # bit-identical on every rank
+    assert tp.fused_gemm.calls == 9
+    torch.cuda.synchronize()
+    _lib.assert_status_ok()
+    # 2. the TP engine (CUDA graphs + fused GEMM/all-reduce) against the unsharded engine
+    torch.manual_seed(0)
+    cfg = HybridConfig("hybrid_qwen3", vocab_size=512, hidden_size=512, intermediate_size=1024, num_hidden_layers=4,
+                       num_attention_heads=4, num_key_value_heads=2, head_dim=128, hybrid_override_pattern="*-GDN-M2-*")
+    model = build_model(cfg).to(dev, torch.bfloat16).eval()
+    prompts = [torch.randint(0, 512, (n,)).tolist() for n in (70, 200, 33)]
+    ref_eng = ServingEngine(model, block_size=64, num_blocks=32, max_num_seqs=4, max_num_batched_tokens=128,
+                            max_model_len=512)
+    ref = ref_eng.generate(prompts, SamplingParams(max_new_tokens=8))
+    shard_model(model, tp)
+    eng = ServingEngine(model, block_size=64, num_blocks=32, max_num_seqs=4, max_num_batched_tokens=128,
+                        max_model_len=512, tp=tp)
+    out = eng.generate(prompts, SamplingParams(max_new_tokens=8))
+    torch.cuda.synchronize()
+    _lib.assert_status_ok()
+    agree = sum(a == b for x, y in zip(out, ref) for a, b in zip(x, y))
+    assert agree >= 0.7 * 24 and all(x[0] == y[0] for x, y in zip(out, ref)), (out, ref)
+    assert eng.stats["graph_replays"] > 0 and tp.fused_gemm.calls > 9
+    dist.barrier()
+
+
+@needs2
+def test_tp_fused_gemm_allreduce_and_engine_two_gpus():
+    run_ranks(_tp_worker, 2, backend="nccl", timeout=300)

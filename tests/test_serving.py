@@ -236,3 +236,24 @@ def _tp_worker(rank, world, pattern):
 def test_tensor_parallel_engine_gloo(pattern):
     from dist_utils import run_ranks
     run_ranks(_tp_worker, 2, pattern)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M,N,K", [(1, 256, 64), (7, 4096, 512), (64, 4096, 1536), (200, 1024, 192)])
+def test_gemm_allreduce_single_rank(M, N, K):
+    """World size 1: the fused kernel is a skinny GEMM that reduces over its own partial (twice, to cover both
+    parity buffers and the device-side epoch)."""
+    from hybrid_model_factory_b200.ops.fused_comm import PeerGemmAllReduce
+    from hybrid_model_factory_b200.ops import _lib
+    torch.manual_seed(0)
+    op = PeerGemmAllReduce(None, max_m=256, max_n=4096)
+    for it in range(3):
+        x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+        w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.05
+        assert op.accepts(x, w)
+        y = op(x, w)
+        ref = x.float() @ w.float().t()
+        assert (y.float() - ref).abs().max() < 2e-2 * ref.abs().max() + 1e-2
+    torch.cuda.synchronize()
+    _lib.assert_status_ok()
+    assert int(op.sync[0]) == 3
