@@ -176,7 +176,15 @@ class GatedDeltaNet(nn.Module):
         o, state = mixers.gated_delta_rule(q, k, v, g, beta, initial_state=state0, sp=sp, chunk_size=self.chunk_size,
                                            recurrent=(T == 1 and not self.training))
         if past_key_values is not None:
-            past_key_values.update_ssm(self.layer_idx, recurrent_state=state, conv_state=new_conv, offset=T)
+            transition = None
+            if getattr(past_key_values, "cache_transitions", False):
+                # the recurrence is affine in the state: with v = 0 and S_0 = I the final state is the transition
+                eye = torch.eye(self.head_dim, device=q.device, dtype=torch.float32).expand(
+                    B, self.expanded_num_heads, -1, -1).contiguous()
+                _, transition = mixers.gated_delta_rule(q, k, torch.zeros_like(k), g, beta, initial_state=eye,
+                                                        chunk_size=self.chunk_size, recurrent=(T == 1))
+            past_key_values.update_ssm(self.layer_idx, recurrent_state=state, conv_state=new_conv, offset=T,
+                                       transition=transition)
         if self.use_gate:
             gate = self.g_proj(hidden_states).view(B, T, self.expanded_num_heads, self.head_dim)
             o = self.o_norm(o.to(hidden_states.dtype), gate)

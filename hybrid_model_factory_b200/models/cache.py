@@ -25,6 +25,7 @@ class HybridCache:
         self.bmojo: Dict[int, dict] = {}
         self.seqlen_offset = 0
         self.cache_aprods = cache_aprods
+        self.cache_transitions = False      # Gated DeltaNet layers also store the chunk's transition matrix
 
     # -- attention ------------------------------------------------------------------
     def update_attention(self, layer_idx: int, k: torch.Tensor, v: torch.Tensor, window: Optional[int] = None):
@@ -42,8 +43,11 @@ class HybridCache:
     def get_ssm(self, layer_idx: int) -> Optional[dict]:
         return self.ssm.get(layer_idx)
 
-    def update_ssm(self, layer_idx: int, recurrent_state=None, conv_state=None, offset: int = 0, log_aprod=None):
+    def update_ssm(self, layer_idx: int, recurrent_state=None, conv_state=None, offset: int = 0, log_aprod=None,
+                   transition=None):
         entry = self.ssm.setdefault(layer_idx, {"recurrent_state": None, "conv_state": None, "log_aprod": None})
+        if transition is not None:     # S_out = transition @ S_in + ...; later segments multiply from the left
+            entry["transition"] = transition if entry.get("transition") is None else transition @ entry["transition"]
         if recurrent_state is not None:
             entry["recurrent_state"] = recurrent_state
         if conv_state is not None:

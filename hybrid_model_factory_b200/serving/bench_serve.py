@@ -53,6 +53,7 @@ def run(model, num_requests=64, prompt_min=4096, prompt_max=16384, output_len=51
             "decode_tok_per_s_after_prefill": decode_tokens / max(dt - first_done, 1e-9),
             "p50_ttft_ms": ttft[len(ttft) // 2], "mean_ttft_ms": sum(ttft) / len(ttft), "p99_ttft_ms": ttft[-1],
             "engine_steps": m["steps"], "decode_ms_per_step": 1e3 * m["decode_s"] / max(m["decode_steps"], 1),
+            "decode_gpu_ms_per_step": 1e3 * m["decode_gpu_s"] / max(m["graph_replays"], 1),
             "prefill_tok_per_s": m["prefill_tokens"] / max(m["prefill_s"], 1e-9), "graphs": len(engine._graphs)}
 
 
@@ -67,7 +68,19 @@ def main(argv=None) -> int:
     ap.add_argument("--output-len", type=int, default=512)
     ap.add_argument("--max-num-batched-tokens", type=int, default=8192)
     args = ap.parse_args(argv)
-    dev = torch.device("cuda", 0) if torch.cuda.is_available() else torch.device("cpu")
+    import os
+    import torch.distributed as dist
+    world, rank = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    dev = torch.device("cuda", local) if torch.cuda.is_available() else torch.device("cpu")
+    tp = None
+    if world > 1:       # tensor parallel over all ranks (launch with torchrun)
+        from ..parallel.tp import TPContext, shard_model
+        torch.cuda.set_device(dev)
+        dist.init_process_group("nccl", device_id=dev)
+        tp = TPContext(dist.group.WORLD)
+        if os.environ.get("HMF_TP_FUSED", "1") == "1":
+            tp.enable_fused_gemm(max_m=256, max_n=8192)
     if args.model:
         model = checkpoint_io.from_pretrained(args.model, device=dev)
     else:
@@ -77,9 +90,19 @@ def main(argv=None) -> int:
             model = build_model(cfg)
         torch.set_default_dtype(torch.float32)
         model = model.to(torch.bfloat16)
+    if tp is not None:
+        shard_model(model, tp)
+        torch.cuda.empty_cache()
     res = run(model, args.num_requests, args.prompt_min, args.prompt_max, args.output_len,
-              max_num_batched_tokens=args.max_num_batched_tokens)
-    print(json.dumps(res))
+              max_num_batched_tokens=args.max_num_batched_tokens, tp=tp)
+    res["tp"] = world
+    if tp is not None:
+        res["fused_gemm_allreduce_calls"] = tp.fused_gemm.calls if tp.fused_gemm is not None else 0
+        dist.barrier()
+    if rank == 0:
+        print(json.dumps(res))
+    if tp is not None:
+        dist.destroy_process_group()
     return 0
 
 

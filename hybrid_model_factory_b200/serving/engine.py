@@ -83,11 +83,14 @@ class ServingEngine:
         self._layer_cache: Dict[int, dict] = {}
         self.max_blocks_per_seq = (max_model_len + block_size - 1) // block_size
         self.stats = {"steps": 0, "decode_tokens": 0, "prefill_tokens": 0, "graph_replays": 0, "decode_steps": 0,
-                      "decode_s": 0.0, "prefill_s": 0.0}
+                      "decode_s": 0.0, "prefill_s": 0.0, "decode_gpu_s": 0.0}
         has_moe = any(hasattr(l.mlp, "experts") for l in model.model.layers)
         self._use_graphs = bool(use_cuda_graphs and self._cuda and not has_moe)
         self._graphs: Dict[tuple, dict] = {}
         self._tables: Dict[int, torch.Tensor] = {}
+        self._timed_replay = False
+        self._events = ((torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+                        if self._cuda else None)
 
     def _plan_blocks(self, n_attn, block_size, max_seqs, max_len, util) -> int:
         need = max_seqs * ((max_len + block_size - 1) // block_size)
@@ -130,6 +133,9 @@ class ServingEngine:
         if decodes:
             logits = self._decode_forward(decodes)
             toks = self._sample(logits, [self.requests[s.req_id].params for s in decodes])
+            if self._timed_replay:      # the sampled ids were read back, so the replay has finished
+                self.stats["decode_gpu_s"] += self._events[0].elapsed_time(self._events[1]) * 1e-3
+                self._timed_replay = False
             for s, t in zip(decodes, toks):
                 self.sched.advance(s.req_id, 1)
                 results.append(self._emit(s.req_id, int(t)))
@@ -221,7 +227,11 @@ class ServingEngine:
         """Batched single-token forward.  On the GPU the whole step (embedding to logits) is captured once per
         (batch bucket, KV split count) in a CUDA graph and replayed from static input buffers."""
         Rn = len(seqs)
-        last = [(self.requests[s.req_id].prompt + self.requests[s.req_id].output)[s.start_pos] for s in seqs]
+        last = []
+        for s in seqs:
+            rq = self.requests[s.req_id]
+            n = len(rq.prompt)
+            last.append(rq.prompt[s.start_pos] if s.start_pos < n else rq.output[s.start_pos - n])
         pos = [s.start_pos for s in seqs]
         slots = [s.slot for s in seqs]
         tables = [self._table(s.req_id, s.start_pos) for s in seqs] if self.state.kv else None
@@ -249,7 +259,11 @@ class ServingEngine:
                 return self._decode_forward(seqs)
             self._graphs[key] = g
         self._fill_inputs(g["inp"], last, pos, slots, tables)
+        ev = self._events
+        ev[0].record()
         g["graph"].replay()
+        ev[1].record()
+        self._timed_replay = True
         self.stats["graph_replays"] += 1
         return g["logits"][:Rn]
 

@@ -70,6 +70,10 @@ class Trainer:
         self.rank = dist.get_rank() if dist.is_initialized() else 0
         sp_size = max(1, args.sequence_parallel_size)
         self.sp: Optional[SPContext] = init_sp_group(sp_size) if (sp_size > 1 and dist.is_initialized()) else None
+        if self.sp is not None and torch.cuda.is_available() and os.environ.get("HMF_SP_PEER", "1") == "1":
+            # recurrent states travel from inside the scan kernels over peer memory (NCCL send/recv otherwise)
+            from ..parallel.peer import enable_peer_transport
+            enable_peer_transport(self.sp)
         set_sequence_parallel_group_recursive(model, self.sp)
         self.dp_size = self.world // sp_size
         if not args.disable_gradient_checkpointing and hasattr(model, "gradient_checkpointing_enable"):
