@@ -53,6 +53,7 @@ class TrainingArguments:
     optimizer_state_dtype: str = "auto"   # auto = parameter dtype (bf16 under pure_bf16), or float32
     master_weights: bool = False
     ddp_timeout: int = 1800
+    optimizer: str = "adamw"              # adamw (flat, ZeRO-sharded, fused kernel) | muon
 
     def to_dict(self):
         return asdict(self)
@@ -80,10 +81,17 @@ class Trainer:
             model.gradient_checkpointing_enable()
         params = list(trainable) if trainable is not None else [p for p in model.parameters() if p.requires_grad]
         sdt = None if args.optimizer_state_dtype == "auto" else getattr(torch, args.optimizer_state_dtype)
-        self.optimizer = FlatAdamW(params, lr=args.learning_rate, betas=(args.adam_beta1, args.adam_beta2),
-                                   eps=args.adam_epsilon, weight_decay=args.weight_decay,
-                                   max_grad_norm=args.max_grad_norm, group=None, dp_size=self.dp_size,
-                                   state_dtype=sdt, master_weights=args.master_weights)
+        if args.optimizer == "muon":
+            from .muon import Muon
+            ids = {id(p) for p in params}
+            self.optimizer = Muon([(n, p) for n, p in model.named_parameters() if id(p) in ids], lr=args.learning_rate,
+                                  betas=(args.adam_beta1, args.adam_beta2), eps=args.adam_epsilon,
+                                  weight_decay=args.weight_decay, max_grad_norm=args.max_grad_norm, dp_size=self.dp_size)
+        else:
+            self.optimizer = FlatAdamW(params, lr=args.learning_rate, betas=(args.adam_beta1, args.adam_beta2),
+                                       eps=args.adam_epsilon, weight_decay=args.weight_decay,
+                                       max_grad_norm=args.max_grad_norm, group=None, dp_size=self.dp_size,
+                                       state_dtype=sdt, master_weights=args.master_weights)
         self.global_step = 0
         self.tokens_seen = 0
         self._t0 = time.time()
@@ -134,7 +142,8 @@ class Trainer:
                 break
             loss = self.train_step(batch)
             if self.args.logging_steps and self.global_step % self.args.logging_steps == 0:
-                self.log({"loss": float(loss.item()), "lr": self._last_lr})
+                self._last_loss = float(loss.item())
+                self.log({"loss": self._last_loss, "lr": self._last_lr})
             for cb in self.callbacks:
                 cb(self)
             if self.args.save_steps and self.global_step % self.args.save_steps == 0:

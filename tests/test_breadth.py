@@ -1,0 +1,132 @@
+"""Smaller components: converters, filters, statistics, Muon, callbacks, layer selection, VL wrapper, export."""
+import json
+import os
+
+import torch
+
+from hybrid_model_factory_b200.models.configuration import HybridConfig
+from hybrid_model_factory_b200.models.modeling_hybrid import build_model
+
+
+def _cfg(pattern="*-GDN", **kw):
+    base = dict(vocab_size=128, hidden_size=64, intermediate_size=128, num_hidden_layers=len(pattern.split("-")),
+                num_attention_heads=4, num_key_value_heads=2, head_dim=16, hybrid_override_pattern=pattern)
+    base.update(kw)
+    return HybridConfig("hybrid_qwen3", **base)
+
+
+def test_qwen_gdn_deinterleave_roundtrip_and_semantics():
+    from hybrid_model_factory_b200.priming import convert_qwen_gdn as cv
+    Hk, Hv, dk, dv, hid = 2, 4, 8, 6, 10
+    r = Hv // Hk
+    q, k = torch.randn(Hk * dk, hid), torch.randn(Hk * dk, hid)
+    v, z = torch.randn(Hv * dv, hid), torch.randn(Hv * dv, hid)
+    fused = cv.interleave_qkvz(q, k, v, z, Hk, Hv, dk, dv)
+    q2, k2, v2, z2 = cv.deinterleave_qkvz(fused, Hk, Hv, dk, dv)
+    assert all(torch.equal(a, b) for a, b in ((q, q2), (k, k2), (v, v2), (z, z2)))
+    # per-head block order of the fused layout: head 0 = [q0 | k0 | v0 v1 | z0 z1]
+    x = torch.randn(3, hid)
+    y = (x @ fused.t()).view(3, Hk, 2 * dk + 2 * r * dv)
+    assert torch.allclose(y[:, 1, :dk], (x @ q.t()).view(3, Hk, dk)[:, 1], atol=1e-5)
+    assert torch.allclose(y[:, 0, 2 * dk:2 * dk + r * dv], (x @ v.t()).view(3, Hk, r * dv)[:, 0], atol=1e-5)
+    ba = torch.randn(Hk * 2 * r, hid)
+    b, a = cv.deinterleave_ba(ba, Hk, Hv)
+    assert torch.equal(b.view(Hk, r, hid), ba.view(Hk, 2 * r, hid)[:, :r])
+    assert cv.pattern_from_layer_types(["linear_attention", "full_attention"], {0: "gka"}) == "GKA-*"
+
+
+def test_filters_and_stats():
+    from hybrid_model_factory_b200.data import filters
+    from hybrid_model_factory_b200.utils import stat_utils
+    recs = [{"text": "a b c d " * 50}, {"text": "every word here is different from the others in this line"},
+            {"text": "x" * 200}]
+    kept, dropped = filters.apply_filters(recs)
+    assert len(kept) == 1 and sum(dropped.values()) == 2
+    cfg = _cfg("*-GDN")
+    f_short, f_long = stat_utils.flops_per_token(cfg, 1024), stat_utils.flops_per_token(cfg, 65536)
+    assert f_long > f_short > 0
+    assert 0 < stat_utils.mfu(1000.0, cfg, 1024, 1e15) < 1
+    assert stat_utils.length_cdf([100, 5000, 200000])[8192] == 2 / 3
+
+
+def test_muon_reduces_loss_and_trainer_option(tmp_path):
+    from hybrid_model_factory_b200.train.muon import Muon, newton_schulz
+    torch.manual_seed(0)
+    G = torch.randn(16, 32)
+    O = newton_schulz(G, steps=8)
+    sv = torch.linalg.svdvals(O)
+    assert sv.max() < 1.3 and sv.min() > 0.5        # approximately orthogonal rows
+    from hybrid_model_factory_b200.train.trainer import Trainer, TrainingArguments
+    model = build_model(_cfg("*-GDN"))
+    tr = Trainer(model, TrainingArguments(output_dir=str(tmp_path), optimizer="muon", learning_rate=2e-2, max_steps=6,
+                                          lr_scheduler_type="constant", disable_gradient_checkpointing=True),
+                 device=torch.device("cpu"))
+    assert isinstance(tr.optimizer, Muon)
+    ids = torch.randint(0, 128, (2, 32))
+    batch = {"input_ids": ids, "labels": ids.clone()}
+    losses = [float(tr.train_step(batch)) for _ in range(6)]
+    assert losses[-1] < losses[0]
+
+
+def test_callbacks_and_layer_selection(tmp_path):
+    from hybrid_model_factory_b200.priming import layer_selection
+    from hybrid_model_factory_b200.train import callbacks
+
+    class T:
+        rank, global_step, tokens_seen, _last_lr = 0, 2, 1000, 1e-4
+
+        class args:
+            max_steps, save_steps, output_dir = 10, 2, None
+    T.args.output_dir = str(tmp_path)
+    callbacks.LogCallback(str(tmp_path))(T)
+    rec = json.loads(open(tmp_path / "trainer_log.jsonl").read().splitlines()[-1])
+    assert rec["current_steps"] == 2 and rec["percentage"] == 20.0
+    src = tmp_path / "tok"
+    src.mkdir()
+    (src / "tokenizer_config.json").write_text("{}")
+    ck = tmp_path / "checkpoint-2"
+    ck.mkdir()
+    callbacks.PreserveTokenizerConfigCallback(str(src))(T)
+    assert (ck / "tokenizer_config.json").exists()
+    csv_path = tmp_path / "scores.csv"
+    csv_path.write_text("layer,score\n0,0.1\n1,0.9\n2,0.5\n3,0.2\n")
+    assert layer_selection.rank_layers(str(csv_path), 4, keep=2) == "GDN-*-*-GDN"
+    base = tmp_path / "base"
+    base.mkdir()
+    (base / "config.json").write_text(json.dumps({"hybrid_override_pattern": "*-GDN-*"}))
+    (base / "model.safetensors").write_text("x")
+    variants = layer_selection.create_swa_variants(str(base), str(tmp_path / "variants"), window=128)
+    assert len(variants) == 2
+    cfg = json.load(open(os.path.join(variants[1], "config.json")))
+    assert cfg["hybrid_override_pattern"] == "*-GDN-SWA" and os.path.islink(os.path.join(variants[1], "model.safetensors"))
+
+
+def test_vl_wrapper_merges_image_features_and_collapses_mrope():
+    from hybrid_model_factory_b200.models.vl import HybridVLForConditionalGeneration, collapse_mrope_position_ids
+    torch.manual_seed(0)
+    vl = HybridVLForConditionalGeneration(_cfg("*-GDN"), image_token_id=5).eval()
+    ids = torch.tensor([[1, 5, 5, 2, 3, 4, 6, 7]])
+    feats = torch.randn(2, 64)
+    emb = vl.merge_embeddings(ids, image_embeds=feats)
+    assert torch.allclose(emb[0, 1:3], feats) and torch.equal(emb[0, 0], vl.language_model.model.embed_tokens(ids)[0, 0])
+    pos3 = torch.arange(8).expand(3, 1, 8)
+    assert collapse_mrope_position_ids(pos3).shape == (1, 8)
+    out = vl(ids, labels=ids, position_ids=pos3, image_embeds=feats)
+    assert torch.isfinite(out.loss)
+
+
+def test_export_and_reassemble(tmp_path):
+    from hybrid_model_factory_b200.priming.reassemble_vlm import reassemble_state
+    from hybrid_model_factory_b200.utils import checkpoint_io
+    from hybrid_model_factory_b200.utils.export import export
+    model = build_model(_cfg("*-GDN"))
+    checkpoint_io.save_pretrained(model, str(tmp_path / "a"))
+    export(str(tmp_path / "a"), str(tmp_path / "b"), dtype="bf16", max_shard_size="100KB")
+    st = checkpoint_io.load_state_dict(str(tmp_path / "b"))
+    assert all(v.dtype == torch.bfloat16 for v in st.values() if v.is_floating_point())
+    assert json.load(open(tmp_path / "b" / "config.json"))["torch_dtype"] == "bfloat16"
+    vl_state = {"model.visual.w": torch.ones(2), "model.language_model.layers.0.x": torch.zeros(1), "lm_head.weight": torch.zeros(1)}
+    text_state = {"model.layers.0.y": torch.ones(1), "lm_head.weight": torch.ones(1)}
+    merged = reassemble_state(text_state, vl_state)
+    assert set(merged) == {"model.visual.w", "model.language_model.layers.0.y", "lm_head.weight"}
+    assert float(merged["lm_head.weight"]) == 1.0
