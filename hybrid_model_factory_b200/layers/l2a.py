@@ -1,0 +1,86 @@
+"""L2A ("learn to attend") mixer: sliding-window attention for every token plus *conditional* global attention
+for the tokens a router selects.
+
+    s   = SWA(norm(x))                                    local stream, own q/k/v/o projections
+    x1  = x + s
+    d   = sigmoid(W_r norm_g(x1) / temperature)           router, one scalar per token
+    m   = 1[d > threshold] + d - stopgrad(d)              straight-through hard decision
+    g   = o_g( m * Attn_global(q_g, K_g, V_g) )           only the selected query rows are computed
+    out = s + g                                           (the decoder layer adds the residual)
+
+Global attention uses a second projection set and the query-sparse kernel path
+(``ops.functional.qsparse_attention``: compacted queries with their original positions against the full K/V).
+During training a fraction ``leak_prob`` of the steps runs dense attention for all tokens ("stochastic leakage").
+The sparsity regulariser ``sum d^2`` of the last forward is kept in ``last_soft_sq`` / ``last_tokens`` for the
+trainer.  Reference: ``examples/research/L2A/model/l2a_qwen3/modeling_qwen3.py:226-630``.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.nn as nn
+
+from ..ops import functional as F_ops
+from .attention import Attention
+from .common import RMSNorm
+
+
+class L2AAttention(nn.Module):
+    def __init__(self, config, layer_idx: int):
+        super().__init__()
+        l2a = getattr(config, "l2a_config", None) or {}
+        self.layer_idx = layer_idx
+        self.window = int(l2a.get("sliding_window", getattr(config, "sliding_window", None) or 512))
+        self.threshold = float(l2a.get("sigmoid_threshold", 0.5))
+        self.temperature = float(l2a.get("temperature", 1.0))
+        self.leak_prob = float(l2a.get("leak_prob", 0.1))
+        self.local = Attention(config, layer_idx, sliding_window=self.window)
+        self.global_attn = Attention(config, layer_idx)          # q/k/v/o_proj (+ q/k norms) of the global stream
+        self.global_norm = RMSNorm(config.hidden_size, config.rms_norm_eps)
+        self.router = nn.Linear(config.hidden_size, 1, bias=False)
+        self.sequence_parallel_group = None
+        self.last_soft_sq: Optional[torch.Tensor] = None
+        self.last_tokens = 0
+        self.last_routed_fraction = 0.0
+
+    def forward(self, hidden_states, residual=None, position_embeddings=None, past_key_values=None, position_ids=None,
+                **kwargs):
+        B, T, _ = hidden_states.shape
+        s, _, _ = self.local(hidden_states, position_embeddings=position_embeddings, position_ids=position_ids)
+        base = hidden_states if residual is None else residual
+        h2 = self.global_norm(base + s)
+        soft = torch.sigmoid(self.router(h2).float() / self.temperature)        # [B, T, 1]
+        hard = (soft > self.threshold).float()
+        mask = hard + soft - soft.detach()
+        self.last_soft_sq, self.last_tokens = (soft ** 2).sum(), B * T
+        self.last_routed_fraction = float(hard.mean())
+        ga = self.global_attn
+        q, k, v, _ = ga._qkv(h2, position_embeddings)
+        leak = self.training and self.leak_prob > 0 and float(torch.rand(())) < self.leak_prob
+        if leak:
+            o = F_ops.attention(q, k, v, scale=ga.scaling, causal=True)
+        else:
+            o = torch.zeros_like(q)
+            for b in range(B):                                   # rows differ per sample: compact each one
+                idx = torch.nonzero(hard[b, :, 0], as_tuple=False)[:, 0]
+                if idx.numel() == 0:
+                    continue
+                ob = F_ops.qsparse_attention(q[b:b + 1, idx], k[b:b + 1], v[b:b + 1], idx[None], scale=ga.scaling)
+                o[b, idx] = ob[0].to(o.dtype)
+        o = (o * mask[..., None].to(o.dtype)).reshape(B, T, -1)
+        return s + ga.o_proj(o), None, past_key_values
+
+
+def l2a_regulariser(model: nn.Module) -> torch.Tensor:
+    """Mean over layers of ``sum d^2 / tokens`` from the last forward."""
+    terms = [m.last_soft_sq / max(m.last_tokens, 1) for m in model.modules()
+             if isinstance(m, L2AAttention) and m.last_soft_sq is not None]
+    if not terms:
+        return torch.zeros(())
+    return torch.stack(terms).mean()
+
+
+def router_sparsity(model: nn.Module) -> dict:
+    """Per-layer fraction of tokens routed to global attention (logged by the L2A trainer)."""
+    return {m.layer_idx: m.last_routed_fraction for m in model.modules() if isinstance(m, L2AAttention)}

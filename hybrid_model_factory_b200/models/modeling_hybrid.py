@@ -120,6 +120,9 @@ def _make_mixer(symbol: str, config: HybridConfig, layer_idx: int) -> nn.Module:
         return GatedKalmaNetLayer(config, layer_idx)
     if symbol == "BMF":
         return BMojoLayer(config, layer_idx)
+    if symbol == "L2A":
+        from ..layers.l2a import L2AAttention
+        return L2AAttention(config, layer_idx)
     raise ValueError(f"no mixer for layer symbol '{symbol}'")
 
 
@@ -152,6 +155,8 @@ class DecoderLayer(nn.Module):
                 use_cache=False, **kwargs):
         residual = hidden_states
         h = self.input_layernorm(hidden_states)
+        if self.symbol == "L2A":        # the router reads the residual stream after the local attention
+            kwargs = dict(kwargs, residual=residual)
         h, _, _ = self.seq_mixer(h, position_embeddings=position_embeddings, position_ids=position_ids,
                                  past_key_values=past_key_values, use_cache=use_cache, **kwargs)
         hidden_states = residual + h

@@ -5,6 +5,7 @@
     M2* GDN* GKA* BMF* SWA*   fused stage-1 layers (student mixer + frozen attention teacher)
     *DA    dual-path attention (same weights on student and teacher streams)
     GDN>GKA  fused SSM->SSM layer (GDN teacher, GKA student)
+    L2A    sliding-window attention + routed global attention (research example)
 
 Reference: ``models/utils.py:6-154`` and ``priming/fused_to_standard.py:142-164``.
 """
@@ -12,15 +13,15 @@ from __future__ import annotations
 
 from typing import Dict, List
 
-LAYER_SYMBOLS = ["*", "M2", "BMF", "GDN", "GKA", "SWA", "M2*", "BMF*", "GDN*", "GKA*", "SWA*", "GDN>GKA", "*DA"]
+LAYER_SYMBOLS = ["*", "M2", "BMF", "GDN", "GKA", "SWA", "M2*", "BMF*", "GDN*", "GKA*", "SWA*", "GDN>GKA", "*DA", "L2A"]
 
 FUSED_SYMBOLS = {"M2*": "M2", "BMF*": "BMF", "GDN*": "GDN", "GKA*": "GKA", "SWA*": "SWA", "GDN>GKA": "GKA", "*DA": "*"}
 
 # attribute name of the sequence mixer inside a decoder layer, per (unfused) symbol
-MIXER_ATTR = {"*": "self_attn", "M2": "mamba", "BMF": "bmojo_f", "GDN": "gdn", "GKA": "gka", "SWA": "swa"}
+MIXER_ATTR = {"*": "self_attn", "M2": "mamba", "BMF": "bmojo_f", "GDN": "gdn", "GKA": "gka", "SWA": "swa", "L2A": "l2a"}
 
 LAYER_TYPE_NAMES = {"*": "full_attention", "SWA": "sliding_attention", "M2": "mamba2", "GDN": "linear_attention",
-                    "GKA": "gated_kalmanet", "BMF": "bmojo_f"}
+                    "GKA": "gated_kalmanet", "BMF": "bmojo_f", "L2A": "l2a_attention"}
 
 
 def parse_override_pattern(pattern: str) -> Dict[int, str]:

