@@ -68,7 +68,10 @@ class Attention(nn.Module):
         q, k, v, gate = self._qkv(hidden_states, position_embeddings)
         sp = self.sequence_parallel_group
         if sp is not None and sp.size > 1:
-            if self.sliding_window is None:
+            if getattr(sp, "mode", "zigzag") == "ulysses":
+                from ..parallel.ulysses import ulysses_attention
+                o = ulysses_attention(q, k, v, sp, scale=self.scaling, window=self.sliding_window)
+            elif self.sliding_window is None:
                 o = cp_attention(q, k, v, sp, scale=self.scaling)
             else:
                 o = self._swa_sp(q, k, v, sp)

@@ -71,6 +71,8 @@ class Trainer:
         self.rank = dist.get_rank() if dist.is_initialized() else 0
         sp_size = max(1, args.sequence_parallel_size)
         self.sp: Optional[SPContext] = init_sp_group(sp_size) if (sp_size > 1 and dist.is_initialized()) else None
+        if self.sp is not None and "ulysses" in (args.sequence_parallel_mode or ""):
+            self.sp.mode = "ulysses"        # attention layers exchange heads instead of gathering K/V
         if self.sp is not None and torch.cuda.is_available() and os.environ.get("HMF_SP_PEER", "1") == "1":
             # recurrent states travel from inside the scan kernels over peer memory (NCCL send/recv otherwise)
             from ..parallel.peer import enable_peer_transport

@@ -1,0 +1,95 @@
+"""Expert, Ulysses and pipeline parallelism and the mesh layout on CPU ranks (gloo)."""
+import copy
+
+import torch
+import torch.distributed as dist
+
+from dist_utils import run_ranks
+from hybrid_model_factory_b200.models.configuration import HybridConfig
+from hybrid_model_factory_b200.models.modeling_hybrid import SparseMoeBlock, build_model
+from hybrid_model_factory_b200.parallel import mesh
+
+
+def test_mesh_coordinates_and_groups():
+    dims = mesh.MeshDims(pp=2, dp=2, sp=2, tp=2)
+    assert mesh.coords(13, dims) == {"pp": 1, "dp": 1, "sp": 0, "tp": 1}
+    tp_groups = mesh.group_ranks(dims, "tp")
+    assert [0, 1] in tp_groups and len(tp_groups) == 8
+    assert [0, 2] in mesh.group_ranks(dims, "sp") and [0, 8] in mesh.group_ranks(dims, "pp")
+    all_ranks = sorted(r for g in mesh.group_ranks(dims, "dp") for r in g)
+    assert all_ranks == list(range(16))
+
+
+def _moe_cfg():
+    return HybridConfig("hybrid_qwen3_moe", vocab_size=64, hidden_size=32, intermediate_size=64, num_hidden_layers=1,
+                        num_attention_heads=2, num_key_value_heads=2, head_dim=16, num_experts=4, num_experts_per_tok=2,
+                        moe_intermediate_size=16, hybrid_override_pattern="*")
+
+
+def _ep_worker(rank, world):
+    from hybrid_model_factory_b200.parallel.ep import EPContext, shard_experts
+    torch.manual_seed(0)
+    ref = SparseMoeBlock(_moe_cfg())
+    blk = copy.deepcopy(ref)
+    g = torch.Generator().manual_seed(10 + rank)
+    x = torch.randn(6 + rank, 32, generator=g)          # different token counts per rank
+    xr = x.clone().requires_grad_(True)
+    out_ref, _ = ref(xr)
+    out_ref.sum().backward()
+    shard_experts(blk, EPContext.from_group(None))
+    xe = x.clone().requires_grad_(True)
+    out, _ = blk(xe)
+    out.sum().backward()
+    assert torch.allclose(out, out_ref, atol=1e-5)
+    assert torch.allclose(xe.grad, xr.grad, atol=1e-5)
+    # expert weight gradients: each rank holds the gradient of its experts from all ranks' tokens
+    full = ref.experts.down_proj.grad.clone()
+    dist.all_reduce(full)
+    per = 4 // world
+    assert torch.allclose(blk.experts.down_proj.grad, full[rank * per:(rank + 1) * per], atol=1e-5)
+
+
+def test_expert_parallel_matches_local_experts():
+    run_ranks(_ep_worker, 2)
+
+
+def _ulysses_worker(rank, world):
+    from hybrid_model_factory_b200.ops import reference as R
+    from hybrid_model_factory_b200.parallel.sp import init_sp_group, zigzag_split
+    from hybrid_model_factory_b200.parallel.ulysses import ulysses_attention
+    g = torch.Generator().manual_seed(0)
+    B, T, H, Hkv, D = 2, 32, 4, 2, 8
+    q, k, v = torch.randn(B, T, H, D, generator=g), torch.randn(B, T, Hkv, D, generator=g), torch.randn(B, T, Hkv, D, generator=g)
+    do = torch.randn(B, T, H, D, generator=g)
+    full = [t.clone().requires_grad_(True) for t in (q, k, v)]
+    o_ref = R.attention(*full, causal=True)
+    o_ref.backward(do)
+    sp = init_sp_group(world)
+    loc = [zigzag_split(t, rank, world).clone().requires_grad_(True) for t in (q, k, v)]
+    o = ulysses_attention(*loc, sp)
+    o.backward(zigzag_split(do, rank, world))
+    assert torch.allclose(o, zigzag_split(o_ref, rank, world), atol=1e-5)
+    for a, b in zip(loc, full):
+        assert torch.allclose(a.grad, zigzag_split(b.grad, rank, world), atol=1e-5)
+
+
+def test_ulysses_attention_matches_single_rank():
+    run_ranks(_ulysses_worker, 2)
+
+
+def _pp_worker(rank, world):
+    from hybrid_model_factory_b200.parallel.pp import PipelineStage, partition_layers
+    assert partition_layers(5, 2) == [(0, 3), (3, 5)]
+    torch.manual_seed(0)
+    cfg = HybridConfig("hybrid_qwen3", vocab_size=64, hidden_size=32, intermediate_size=64, num_hidden_layers=4,
+                       num_attention_heads=2, num_key_value_heads=2, head_dim=16, hybrid_override_pattern="*-GDN-M2-*")
+    model = build_model(cfg).eval()
+    ids = torch.randint(0, 64, (1, 9), generator=torch.Generator().manual_seed(3))
+    ref = model.generate(ids, max_new_tokens=5)[:, 9:]
+    stage = PipelineStage(model)
+    out = stage.generate(ids, max_new_tokens=5)
+    assert torch.equal(out, ref), (rank, out, ref)
+
+
+def test_pipeline_parallel_generation_matches_single_rank():
+    run_ranks(_pp_worker, 2)
