@@ -36,7 +36,16 @@ struct FwdParams {
   int lo, hi, q_off;
   float scale_log2;
   unsigned int* status;
+  // context parallelism: keys / values live in 2*SP zig-zag chunks spread over the ranks' symmetric buffers.
+  // src_maps = [K map of chunk 0 .. n_chunks-1 | V map of chunk 0 .. n_chunks-1] in global memory (each over
+  // [B, chunk_len, Hkv, D] of the owner's buffer); src_flags[r] >= epoch once rank r has published its K/V.
+  const CUtensorMap* src_maps;
+  const unsigned int* src_flags;
+  int n_chunks, chunk_len;
+  unsigned int epoch;
 };
+
+constexpr uint64_t kPeerWaitNs = 2000000000ull;
 
 template <int D>
 struct Smem {
@@ -131,20 +140,36 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       mbar_expect_tx(q_full, L::Q_BYTES);
 #pragma unroll
       for (int pn = 0; pn < D / 64; ++pn) tma_load_4d(sQ + pn * L::Q_PANEL, &tmQ, q_full, pn * 64, h, q0, b);
+      unsigned int waited = 0u;   // owners whose publication flag has been seen
       for (int j = 0; j < n_tiles; ++j) {
         const int s = j & 1;
         const uint32_t par = ((j >> 1) & 1) ^ 1;
-        const int k0 = (j0 + j) * BN;
+        int k0 = (j0 + j) * BN;
+        const CUtensorMap* km = &tmK;
+        const CUtensorMap* vm = &tmV;
+        if (p.src_maps != nullptr) {
+          // remote tile: plain (non-multicast) TMA from the owner's memory over NVLink
+          const int c = k0 / p.chunk_len;
+          const int sp = p.n_chunks >> 1;
+          const int owner = c < sp ? c : p.n_chunks - 1 - c;
+          if (!((waited >> owner) & 1u)) {
+            wait_flag_sys(p.src_flags + owner, p.epoch, kPeerWaitNs, p.status, 0xA0 + owner);
+            waited |= 1u << owner;
+          }
+          km = p.src_maps + c;
+          vm = p.src_maps + p.n_chunks + c;
+          k0 -= c * p.chunk_len;
+        }
         mbar_wait(&k_empty[s], par, ctx, 0x10 + s);
         mbar_expect_tx(&k_full[s], L::KV_BYTES);
 #pragma unroll
         for (int pn = 0; pn < D / 64; ++pn)
-          tma_load_4d(sK + s * L::KV_BYTES + pn * L::KV_PANEL, &tmK, &k_full[s], pn * 64, hkv, k0, b);
+          tma_load_4d(sK + s * L::KV_BYTES + pn * L::KV_PANEL, km, &k_full[s], pn * 64, hkv, k0, b);
         mbar_wait(&v_empty[s], par, ctx, 0x20 + s);
         mbar_expect_tx(&v_full[s], L::KV_BYTES);
 #pragma unroll
         for (int pn = 0; pn < D / 64; ++pn)
-          tma_load_4d(sV + s * L::KV_BYTES + pn * L::KV_PANEL, &tmV, &v_full[s], pn * 64, hkv, k0, b);
+          tma_load_4d(sV + s * L::KV_BYTES + pn * L::KV_PANEL, vm, &v_full[s], pn * 64, hkv, k0, b);
       }
     }
   } else if (warp == 1) {
@@ -364,6 +389,74 @@ HMF_API int hmf_attention_fwd(const void* q, const void* k, const void* v, void*
   p.lo = lo; p.hi = hi; p.q_off = q_off;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = status_ptr();
+  p.src_maps = nullptr; p.src_flags = nullptr; p.n_chunks = 0; p.chunk_len = 0; p.epoch = 0;
   if (D == 64) return launch<64>(tmQ, tmK, tmV, p, stream);
   return launch<128>(tmQ, tmK, tmV, p, stream);
+}
+
+namespace hmf {
+namespace attn {
+__global__ void peer_signal_kernel(unsigned int* const* flags, int n, int index, unsigned int value) {
+  if ((int)threadIdx.x < n) {
+    __threadfence_system();
+    st_release_sys(flags[threadIdx.x] + index, value);
+  }
+}
+}  // namespace attn
+}  // namespace hmf
+
+// Raises flag[index] = value on every rank of `flag_ptrs` (device array of n addresses, one per rank, as mapped
+// into this process).  Work queued before on the stream (the copies into the symmetric K/V buffers) is complete
+// and visible to the peers when they see the flag.
+HMF_API int hmf_peer_signal(const void* flag_ptrs_dev, int n, int index, unsigned int value, cudaStream_t stream) {
+  using namespace hmf;
+  HMF_REQUIRE(n >= 1 && n <= 32, "peer_signal: %d ranks unsupported", n);
+  hmf::attn::peer_signal_kernel<<<1, 32, 0, stream>>>((unsigned int* const*)flag_ptrs_dev, n, index, value);
+  HMF_CHECK_CUDA(cudaGetLastError());
+  return HMF_OK;
+}
+
+// Context-parallel forward: queries are local ([B, Tq, Hq, D]); keys / values of global chunk c
+// (c = 0 .. n_vis-1, chunk_len tokens each) are read from kv_ptrs[c] / kv_ptrs[n_chunks + c] (host array of
+// device addresses of [B, chunk_len, Hkv, D] blocks with batch stride kv_sb elements, in the owners' symmetric
+// buffers).  maps_dev: 2 * n_chunks * 128 bytes of device scratch (64-byte aligned) that stays untouched until the
+// kernel has finished.  flags_local[r] >= epoch signals that rank r's buffers are complete.
+HMF_API int hmf_attention_fwd_cp(const void* q, const unsigned long long* kv_ptrs, void* maps_dev,
+                                 const unsigned int* flags_local, unsigned int epoch, void* o, float* lse, int B,
+                                 int Tq, int chunk_len, int n_chunks, int n_vis, int Hq, int Hkv, int D,
+                                 long long q_sb, long long q_st, long long q_sh, long long kv_sb, int lo, int hi,
+                                 int q_off, float scale, cudaStream_t stream) {
+  using namespace hmf;
+  using namespace hmf::attn;
+  HMF_REQUIRE(q && kv_ptrs && maps_dev && flags_local && o, "attention_cp: null argument");
+  HMF_REQUIRE(D == 64 || D == 128, "attention_cp: head dim %d unsupported (64, 128)", D);
+  HMF_REQUIRE(n_chunks >= 2 && n_chunks <= 64 && n_chunks % 2 == 0 && n_vis >= 1 && n_vis <= n_chunks,
+              "attention_cp: bad chunk counts %d / %d", n_vis, n_chunks);
+  HMF_REQUIRE(chunk_len % BN == 0, "attention_cp: chunk length %d must be a multiple of %d", chunk_len, BN);
+  HMF_REQUIRE(((uintptr_t)maps_dev & 63) == 0, "attention_cp: descriptor scratch must be 64-byte aligned");
+  CUtensorMap tmQ;
+  int rc = make_map_bthd(&tmQ, q, B, Tq, Hq, D, q_sb, q_st, q_sh, BM);
+  if (rc != HMF_OK) return rc;
+  CUtensorMap host_maps[128];
+  for (int i = 0; i < 2 * n_chunks; ++i) {
+    const int c = i % n_chunks;
+    const unsigned long long base = kv_ptrs[c < n_vis ? i : (i / n_chunks) * n_chunks];   // unused chunks alias chunk 0
+    rc = make_map_bthd(&host_maps[i], reinterpret_cast<const void*>(base), B, chunk_len, Hkv, D, kv_sb,
+                       (long long)Hkv * D, D, BN);
+    if (rc != HMF_OK) return rc;
+  }
+  HMF_CHECK_CUDA(cudaMemcpyAsync(maps_dev, host_maps, sizeof(CUtensorMap) * 2 * n_chunks, cudaMemcpyHostToDevice, stream));
+  FwdParams p;
+  p.o = (__nv_bfloat16*)o;
+  p.lse = lse;
+  p.q_pos = nullptr;
+  p.B = B; p.Tq = Tq; p.Tk = n_vis * chunk_len; p.Hq = Hq; p.Hkv = Hkv;
+  p.lo = lo; p.hi = hi; p.q_off = q_off;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.status = status_ptr();
+  p.src_maps = reinterpret_cast<const CUtensorMap*>(maps_dev);
+  p.src_flags = flags_local;
+  p.n_chunks = n_chunks; p.chunk_len = chunk_len; p.epoch = epoch;
+  if (D == 64) return launch<64>(tmQ, host_maps[0], host_maps[n_chunks], p, stream);
+  return launch<128>(tmQ, host_maps[0], host_maps[n_chunks], p, stream);
 }

@@ -48,6 +48,24 @@ class _CPAttention(torch.autograd.Function):
     def forward(ctx, q: Tensor, k: Tensor, v: Tensor, sp: SPContext, scale: Optional[float], window: Optional[int]):
         B, Ll = q.shape[0], q.shape[1]
         c = Ll // 2
+        pk = getattr(sp, "peer_kv", None)
+        if (pk is not None and not any(ctx.needs_input_grad[:3]) and q.is_cuda and q.dtype == torch.bfloat16
+                and k.dtype == torch.bfloat16 and q.shape[-1] in (64, 128) and window is None and pk.fits(k)):
+            # no gradient will be asked of this call (inference, or the first pass of a checkpointed layer): the
+            # K/V gather happens inside the attention kernel, tile by tile over peer memory
+            from ..utils import checkpointing as _ckpt
+            D = q.shape[-1]
+            sc = D ** -0.5 if scale is None else scale
+            pk.publish(k.contiguous(), v.contiguous())
+            wr = _ckpt.stash_for_write()
+            outs = []
+            for seg, cid in ((0, sp.rank), (1, 2 * sp.size - 1 - sp.rank)):
+                o, lse = pk.attention(q[:, seg * c:(seg + 1) * c], cid, sc, 0, 2 ** 31 - 1)
+                if wr is not None:
+                    wr.append((o, lse))
+                outs.append(o)
+            ctx.graphs = None
+            return torch.cat(outs, dim=1)
         k_all = _all_gather_seq(k, sp)
         v_all = _all_gather_seq(v, sp)
         ca, cb = sp.rank, 2 * sp.size - 1 - sp.rank

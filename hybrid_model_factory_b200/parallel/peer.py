@@ -127,3 +127,83 @@ def enable_peer_transport(sp, max_state_bytes: int = 8 << 20) -> bool:
         import warnings
         warnings.warn(f"peer-memory state transport unavailable ({e}); using NCCL send/recv")
         return False
+
+
+class PeerKVExchange:
+    """Keys / values of context-parallel attention in symmetric memory.
+
+    ``publish(k, v)`` copies this rank's ``[B, T_local, Hkv, D]`` tensors into its (double-buffered) symmetric slot
+    and raises ``flag[rank] = epoch`` on every peer.  ``attention(q_seg, ...)`` then runs the forward kernel whose
+    TMA producer fetches every K/V tile straight from the owner's memory (non-multicast TMA over NVLink) after
+    seeing that owner's flag: the all-gather of the unfused path disappears into the attention kernel.
+    Double-buffering is enough: finishing the attention of layer ``l+1`` requires every peer's layer ``l+1`` flags,
+    which a peer raises only after its own layer-``l`` attention has finished reading.
+    """
+
+    def __init__(self, group, sp_rank: int, sp_size: int, max_kv_bytes: int):
+        self.rank, self.size = sp_rank, sp_size
+        self.kv_bytes = (int(max_kv_bytes) + 1023) // 1024 * 1024
+        self.flag_off = 4 * self.kv_bytes                       # [parity][k | v]
+        self.ws = SymmetricWorkspace(self.flag_off + 1024, group)
+        dev = self.ws.device
+        self.flags = self.ws.view(self.flag_off, (sp_size,), torch.int32)
+        self.flag_ptrs = torch.tensor([self.ws.peer_ptr(r, self.flag_off) for r in range(sp_size)], dtype=torch.int64,
+                                      device=dev)
+        self.maps = torch.empty(8 * 2 * 2 * sp_size * 128 + 64, dtype=torch.uint8, device=dev)
+        self.calls = 0
+        self.epoch = 0
+        self.shape = None
+
+    def fits(self, k: torch.Tensor) -> bool:
+        return k.numel() * k.element_size() <= self.kv_bytes and k.shape[1] % 2 == 0 and (k.shape[1] // 2) % 64 == 0
+
+    def _slot(self, which: int) -> int:
+        return ((self.epoch & 1) * 2 + which) * self.kv_bytes
+
+    def publish(self, k: torch.Tensor, v: torch.Tensor) -> None:
+        import ctypes
+        from ..ops import _lib
+        self.epoch += 1
+        self.shape = tuple(k.shape)
+        self.ws.view(self._slot(0), k.shape, k.dtype).copy_(k)
+        self.ws.view(self._slot(1), v.shape, v.dtype).copy_(v)
+        _lib.check(_lib.kernels().hmf_peer_signal(_lib.ptr(self.flag_ptrs), ctypes.c_int(self.size),
+                                                  ctypes.c_int(self.rank), ctypes.c_uint(self.epoch),
+                                                  _lib.stream_ptr(k.device)), "peer_signal")
+
+    def attention(self, q_seg: torch.Tensor, chunk_id: int, scale: float, lo: int, hi: int):
+        """Causal attention of the queries of global chunk ``chunk_id`` against chunks ``0 .. chunk_id``."""
+        import ctypes
+        from ..ops import _lib
+        B, T, Hkv, D = self.shape
+        Lc, n = T // 2, self.size
+        n_chunks = 2 * n
+        arr = (ctypes.c_ulonglong * (2 * n_chunks))()
+        for c in range(n_chunks):
+            owner = c if c < n else n_chunks - 1 - c
+            off = (0 if c < n else Lc) * Hkv * D * 2
+            arr[c] = self.ws.peer_ptr(owner, self._slot(0) + off)
+            arr[n_chunks + c] = self.ws.peer_ptr(owner, self._slot(1) + off)
+        Bq, Tq, Hq, _ = q_seg.shape
+        q_seg = q_seg if (q_seg.stride(3) == 1 and q_seg.data_ptr() % 16 == 0) else q_seg.contiguous()
+        o = torch.empty(Bq, Tq, Hq, D, device=q_seg.device, dtype=torch.bfloat16)
+        lse = torch.empty(Bq, Hq, Tq, device=q_seg.device, dtype=torch.float32)
+        base = (self.maps.data_ptr() + 63) // 64 * 64
+        slot = base + (self.calls % 8) * (2 * n_chunks * 128)
+        self.calls += 1
+        ll = ctypes.c_longlong
+        _lib.check(_lib.kernels().hmf_attention_fwd_cp(
+            _lib.ptr(q_seg), arr, ctypes.c_void_p(slot), _lib.ptr(self.flags), ctypes.c_uint(self.epoch), _lib.ptr(o),
+            _lib.ptr(lse), ctypes.c_int(Bq), ctypes.c_int(Tq), ctypes.c_int(Lc), ctypes.c_int(n_chunks),
+            ctypes.c_int(chunk_id + 1), ctypes.c_int(Hq), ctypes.c_int(Hkv), ctypes.c_int(D), ll(q_seg.stride(0)),
+            ll(q_seg.stride(1)), ll(q_seg.stride(2)), ll(T * Hkv * D), ctypes.c_int(lo), ctypes.c_int(hi),
+            ctypes.c_int(chunk_id * Lc), ctypes.c_float(scale), _lib.stream_ptr(q_seg.device)), "attention_fwd_cp")
+        return o, lse
+
+
+def enable_peer_kv(sp, max_kv_bytes: int) -> bool:
+    """Attaches a ``PeerKVExchange`` to the SP context (``sp.peer_kv``); collective call."""
+    if sp is None or sp.size <= 1 or not torch.cuda.is_available():
+        return False
+    sp.peer_kv = PeerKVExchange(sp.group, sp.rank, sp.size, max_kv_bytes)
+    return True

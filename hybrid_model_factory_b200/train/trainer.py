@@ -75,8 +75,11 @@ class Trainer:
             self.sp.mode = "ulysses"        # attention layers exchange heads instead of gathering K/V
         if self.sp is not None and torch.cuda.is_available() and os.environ.get("HMF_SP_PEER", "1") == "1":
             # recurrent states travel from inside the scan kernels over peer memory (NCCL send/recv otherwise)
-            from ..parallel.peer import enable_peer_transport
+            from ..parallel.peer import enable_peer_kv, enable_peer_transport
             enable_peer_transport(self.sp)
+            kv_bytes = int(os.environ.get("HMF_SP_PEER_KV_MB", "256")) << 20
+            if kv_bytes > 0 and self.sp.mode != "ulysses":
+                enable_peer_kv(self.sp, kv_bytes)       # attention pulls remote K/V tiles inside its forward kernel
         set_sequence_parallel_group_recursive(model, self.sp)
         self.dp_size = self.world // sp_size
         if not args.disable_gradient_checkpointing and hasattr(model, "gradient_checkpointing_enable"):

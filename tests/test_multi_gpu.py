@@ -113,3 +113,36 @@ def _tp_worker(rank, world):
 @needs2
 def test_tp_fused_gemm_allreduce_and_engine_two_gpus():
     run_ranks(_tp_worker, 2, backend="nccl", timeout=300)
+
+
+def _cp_worker(rank, world):
+    from hybrid_model_factory_b200.ops import _lib
+    from hybrid_model_factory_b200.parallel.cp_attention import cp_attention
+    from hybrid_model_factory_b200.parallel.peer import enable_peer_kv
+    from hybrid_model_factory_b200.parallel.sp import init_sp_group, zigzag_split
+    from hybrid_model_factory_b200.ops import functional as F_ops
+    dev = torch.device("cuda", rank)
+    g = torch.Generator().manual_seed(0)
+    B, T, H, Hkv, D = 2, 2048, 8, 2, 128
+    q = torch.randn(B, T, H, D, generator=g).bfloat16().to(dev)
+    k = torch.randn(B, T, Hkv, D, generator=g).bfloat16().to(dev)
+    v = torch.randn(B, T, Hkv, D, generator=g).bfloat16().to(dev)
+    ref = F_ops.attention(q, k, v, causal=True)
+    sp = init_sp_group(world)
+    ql, kl, vl = (zigzag_split(t, rank, world).contiguous() for t in (q, k, v))
+    base = cp_attention(ql, kl, vl, sp)                        # NCCL all-gather path
+    assert enable_peer_kv(sp, kl.numel() * 2)
+    for it in range(3):                                        # both parity buffers and epoch reuse
+        with torch.no_grad():
+            fused = cp_attention(ql, kl + it * 0, vl, sp)
+        torch.cuda.synchronize()
+        _lib.assert_status_ok()
+        assert _rel(fused, zigzag_split(ref, rank, world)) < 2e-2
+        assert torch.equal(fused, base)                        # same kernel, same tiles: bit-identical
+    assert sp.peer_kv.calls == 6
+    dist.barrier()
+
+
+@needs2
+def test_cp_attention_peer_kv_two_gpus():
+    run_ranks(_cp_worker, 2, backend="nccl", timeout=240)
