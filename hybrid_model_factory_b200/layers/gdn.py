@@ -183,8 +183,8 @@ class GatedDeltaNet(nn.Module):
                     B, self.expanded_num_heads, -1, -1).contiguous()
                 _, transition = mixers.gated_delta_rule(q, k, torch.zeros_like(k), g, beta, initial_state=eye,
                                                         chunk_size=self.chunk_size, recurrent=(T == 1))
-            past_key_values.update_ssm(self.layer_idx, recurrent_state=state, conv_state=new_conv, offset=T,
-                                       transition=transition)
+            extra = {} if transition is None else {"transition": transition}
+            past_key_values.update_ssm(self.layer_idx, recurrent_state=state, conv_state=new_conv, offset=T, **extra)
         if self.use_gate:
             gate = self.g_proj(hidden_states).view(B, T, self.expanded_num_heads, self.head_dim)
             o = self.o_norm(o.to(hidden_states.dtype), gate)
