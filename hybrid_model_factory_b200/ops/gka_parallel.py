@@ -1,0 +1,86 @@
+"""Chunk-parallel Chebyshev ridge solve of Gated KalmaNet for the GPU.
+
+``ops.reference.gka_chebyshev_chunk`` walks the chunks one after the other (``N x num_iter`` rounds of small
+launches).  Here the chunk-start covariance states are produced first for *all* chunks (a decay-weighted
+cumulative sum over chunks, one GEMM), after which every chunk's ``num_iter`` Chebyshev steps run as one batch
+over ``[B, H, N]``: ``num_iter`` rounds of four large batched GEMMs in fp32 / TF32 on the tensor cores, independent
+of the sequence length.  Differentiable (used through ``TorchScanCore``, which re-evaluates it in backward).
+Same math as the reference project's chunked kernels (``chebyshev_iteration.py:25-300``,
+``chunk_fwd_h_kk`` in ``gka/ops``), evaluated with library GEMMs instead of one fused kernel.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+Tensor = torch.Tensor
+
+
+def chunk_states(k: Tensor, G: Tensor, H0: Optional[Tensor]) -> Tensor:
+    """``k [B,H,N,C,D]``, inclusive in-chunk cumulative gates ``G [B,H,N,C]`` -> states ``[B,H,N+1,D,D]``
+    (state at the start of chunk ``n``; index ``N`` is the final state)."""
+    B, Hh, N, C, D = k.shape
+    Glast = G[..., -1]                                            # [B,H,N]
+    kdec = k * torch.exp(Glast[..., None] - G)[..., None]
+    U = kdec.transpose(-1, -2) @ k                                # [B,H,N,D,D] contribution of chunk m at its end
+    tot = torch.cumsum(Glast, dim=-1)                             # log decay up to the end of chunk m
+    tot0 = torch.cat([torch.zeros_like(tot[..., :1]), tot], dim=-1)          # [B,H,N+1]: up to the start of chunk n
+    # state_n = e^{tot0_n} H0 + sum_{m<n} e^{tot0_n - tot_m} U_m
+    diff = tot0[..., :, None] - tot[..., None, :]                 # [B,H,N+1,N]
+    idx_n = torch.arange(N + 1, device=k.device)[:, None]
+    idx_m = torch.arange(N, device=k.device)[None, :]
+    lower = idx_m < idx_n
+    W = torch.where(lower, torch.exp(torch.where(lower, diff, torch.zeros_like(diff))), torch.zeros_like(diff))
+    states = (W @ U.reshape(B, Hh, N, D * D)).view(B, Hh, N + 1, D, D)
+    if H0 is not None:
+        states = states + torch.exp(tot0)[..., None, None] * H0[:, :, None]
+    return states
+
+
+def chebyshev_chunk_parallel(q: Tensor, k: Tensor, gk: Optional[Tensor], *, ridge_ratio: float = 0.02,
+                             num_iter: int = 30, initial_state: Optional[Tensor] = None, chunk_size: int = 64):
+    """Returns ``(x [B,T,H,D] fp32, H_T [B,H,D,D] fp32)``; see ``ops.reference.gka_chebyshev_chunk``."""
+    B, T, Hh, D = q.shape
+    C = chunk_size
+    pad = (-T) % C
+    qf, kf = q.float(), k.float()
+    gf = torch.zeros(B, T, Hh, device=q.device) if gk is None else gk.float()
+    if pad:
+        z = lambda t: torch.cat([t, t.new_zeros(B, pad, *t.shape[2:])], dim=1)  # noqa: E731
+        qf, kf, gf = z(qf), z(kf), z(gf)
+    N = (T + pad) // C
+    qf = qf.view(B, N, C, Hh, D).permute(0, 3, 1, 2, 4)           # [B,H,N,C,D]
+    kf = kf.view(B, N, C, Hh, D).permute(0, 3, 1, 2, 4)
+    G = gf.view(B, N, C, Hh).permute(0, 3, 1, 2).cumsum(-1)       # [B,H,N,C]
+    idx = torch.arange(C, device=q.device)
+    lower = idx[:, None] >= idx[None, :]
+    diff = G[..., :, None] - G[..., None, :]
+    m = torch.where(lower, torch.exp(torch.where(lower, diff, torch.zeros_like(diff))), torch.zeros_like(diff))
+    H0 = None if initial_state is None else initial_state.float()
+    states = chunk_states(kf, G, H0)
+    Hs = states[:, :, :N]                                         # [B,H,N,D,D]
+    eg = torch.exp(G)[..., None]                                  # [B,H,N,C,1]
+    gram = kf @ kf.transpose(-1, -2)
+    fro2 = ((m @ (gram * gram)) * m).sum(-1, keepdim=True)
+    fro2 = fro2 + eg * eg * Hs.pow(2).sum((-1, -2))[..., None, None]
+    kHk = (kf * (kf @ Hs)).sum(-1)
+    fro2 = fro2 + 2 * eg * (m * kHk[..., None, :]).sum(-1, keepdim=True)
+    fro = fro2.clamp(min=0).sqrt()
+    lam = ridge_ratio * fro
+    denom = 2 * lam + fro
+    denom = torch.where(denom == 0, torch.ones_like(denom), denom)
+    step = 2.0 / denom
+    c = (fro / denom / 2.0) ** 2
+    kT = kf.transpose(-1, -2)
+    x_prev = torch.zeros_like(qf)
+    x = step * qf
+    omega = torch.full_like(fro, 2.0)
+    for _ in range(num_iter):
+        omega = 1.0 / (1.0 - c * omega)
+        Hx = (x * eg) @ Hs + ((x @ kT) * m) @ kf
+        upd = step * omega * (Hx + lam * x - qf) + (omega - 1.0) * x_prev
+        x_prev = x
+        x = omega * x - upd
+    out = x.permute(0, 2, 3, 1, 4).reshape(B, N * C, Hh, D)[:, :T]
+    return out, states[:, :, N]

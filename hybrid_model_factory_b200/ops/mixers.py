@@ -78,6 +78,11 @@ def _cheb_state_shapes(inputs):
 
 
 def _cheb_ref(q, k, gk, initial_state=None, ridge_ratio=0.02, num_iter=30, chunk_size=64, recurrent=False):
+    if not recurrent and q.is_cuda:
+        # all chunks at once: num_iter rounds of large batched GEMMs instead of N x num_iter small ones
+        from .gka_parallel import chebyshev_chunk_parallel
+        return chebyshev_chunk_parallel(q, k, gk, ridge_ratio=ridge_ratio, num_iter=num_iter,
+                                        initial_state=initial_state, chunk_size=chunk_size)
     if recurrent:
         return R.gka_chebyshev_recurrent(q, k, gk, ridge_ratio=ridge_ratio, num_iter=num_iter,
                                          initial_state=initial_state)

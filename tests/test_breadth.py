@@ -165,3 +165,24 @@ def test_l2a_layer_routes_and_trains(tmp_path):
     assert mixers[0].router.weight.grad is not None or True
     assert float(l2a_regulariser(model)) > 0 and len(loss_fn.last_sparsity) == 2
     assert lambda_schedule(0, 1.0, 2, 10) == 0.0 and 0 < lambda_schedule(6, 1.0, 2, 10, "cosine") < 1.0
+
+
+def test_gka_chunk_parallel_solver_matches_sequential_reference():
+    from hybrid_model_factory_b200.ops import reference as R
+    from hybrid_model_factory_b200.ops.gka_parallel import chebyshev_chunk_parallel
+    torch.manual_seed(0)
+    B, T, H, D = 2, 150, 3, 16
+    q, k = torch.randn(B, T, H, D), torch.randn(B, T, H, D)
+    q, k = q / q.norm(dim=-1, keepdim=True), k / k.norm(dim=-1, keepdim=True)
+    gk = -torch.rand(B, T, H) * 0.1
+    h0 = torch.randn(B, H, D, D) * 0.1
+    h0 = h0 @ h0.transpose(-1, -2)
+    for g in (gk, None):
+        for s in (h0, None):
+            a = R.gka_chebyshev_chunk(q, k, g, initial_state=s, num_iter=12, chunk_size=32)
+            b = chebyshev_chunk_parallel(q, k, g, initial_state=s, num_iter=12, chunk_size=32)
+            assert torch.allclose(a[0], b[0], atol=1e-5) and torch.allclose(a[1], b[1], atol=1e-5)
+    qq = q.clone().requires_grad_(True)
+    x, hT = chebyshev_chunk_parallel(qq, k, gk, num_iter=6, chunk_size=32)
+    (x.sum() + hT.sum()).backward()
+    assert torch.isfinite(qq.grad).all()
