@@ -112,10 +112,15 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
       if (mbar_try_wait(bar, parity)) return true;
     return false;
   }
+  // Fast phase: plain polling.  The global timer is a slow register to read (it sits on the critical path of
+  // every wait that does not succeed at once), so it is consulted only after the common short waits are over.
+#pragma unroll 1
+  for (int i = 0; i < 4096; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = globaltimer_ns();
   for (;;) {
 #pragma unroll 1
-    for (int i = 0; i < 256; ++i)
+    for (int i = 0; i < 1024; ++i)
       if (mbar_try_wait(bar, parity)) return true;
     if (*abort) return false;
     if (globaltimer_ns() - t0 > kWaitLimitNs) {

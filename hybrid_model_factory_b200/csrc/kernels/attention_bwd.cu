@@ -76,24 +76,50 @@ constexpr int BN = 64;   // keys per inner tile
 
 template <int D>
 struct SmemDQ {
+  static constexpr int NST = 3;                 // K and V rings
   static constexpr int QP = BM * 128;           // one 64-wide panel of Q / dO
   static constexpr int KP = BN * 128;           // one 64-wide panel of K / V
   static constexpr int Q_BYTES = BM * D * 2;
   static constexpr int KV_BYTES = BN * D * 2;
   static constexpr int OFF_DO = Q_BYTES;
-  static constexpr int OFF_K = 2 * Q_BYTES;      // 2 stages
-  static constexpr int OFF_V = OFF_K + 2 * KV_BYTES;
-  static constexpr int OFF_BAR = OFF_V + KV_BYTES;
+  static constexpr int OFF_K = 2 * Q_BYTES;
+  static constexpr int OFF_V = OFF_K + NST * KV_BYTES;
+  static constexpr int OFF_BAR = OFF_V + NST * KV_BYTES;
   static constexpr int TOTAL = OFF_BAR + 256;
 };
 
+template <int N>
+__device__ __forceinline__ void tmem_ld_n(uint32_t taddr, uint32_t (&r)[N]) {
+  if constexpr (N == 32) tmem_ld_x32(taddr, r);
+  else if constexpr (N == 16) tmem_ld_x16(taddr, r);
+  else tmem_ld_x8(taddr, r);
+}
+template <int N>
+__device__ __forceinline__ void tmem_st_n(uint32_t taddr, const uint32_t (&r)[N]) {
+  if constexpr (N == 32) tmem_st_x32(taddr, r);
+  else if constexpr (N == 16) tmem_st_x16(taddr, r);
+  else tmem_st_x8(taddr, r);
+}
+
+constexpr int NWG = 2;                        // softmax warpgroups per CTA: each takes 64 / NWG columns of a tile
+constexpr int NSOFT = NWG * 128;              // softmax threads
+constexpr int NTHR = 64 + NSOFT;              // + TMA warp + MMA warp
+constexpr int WCOLS = 64 / NWG;               // 16 fp32 columns per thread and tile
+
 template <int D>
-__global__ void __launch_bounds__(192, 2)
+__global__ void __launch_bounds__(NTHR, 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
                    const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                    const Params p) {
+  // One CTA per SM: S / dP double-buffered in tensor memory so the MMAs of tile j+1 overlap the softmax of tile j;
+  // K and V travel through 3-stage rings; NWG softmax warpgroups split the 64 key columns of a tile.
+  // Q and dO (reused by every key tile) are copied once into tensor memory as bf16 A operands, so the S and dP
+  // MMAs read only the 64-row K / V tile from shared memory (the SS form with a 128-row A operand is bound by
+  // shared-memory bandwidth, not by the tensor pipe).
+  // Tensor-memory map (512 columns): Q [0,64) dO [64,128) S0 S1 [128,256) dP0 dP1 [256,384) dQ [384,384+D).
   using L = SmemDQ<D>;
-  constexpr int TMEM_COLS = (128 + D) <= 256 ? 256 : 512;
+  constexpr int NST = L::NST;
+  constexpr int TMEM_COLS = 512;
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* sQ = smem;
   uint8_t* sDO = smem + L::OFF_DO;
@@ -101,14 +127,15 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   uint8_t* sV = smem + L::OFF_V;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
   uint64_t* qdo_full = bars + 0;
-  uint64_t* k_full = bars + 1;   // [2]
-  uint64_t* k_empty = bars + 3;  // [2]
-  uint64_t* v_full = bars + 5;
-  uint64_t* v_empty = bars + 6;
-  uint64_t* sdp_full = bars + 7;
-  uint64_t* ds_full = bars + 8;
-  uint64_t* dq_done = bars + 9;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+  uint64_t* k_full = bars + 1;              // [NST]
+  uint64_t* k_empty = bars + 1 + NST;       // [NST]
+  uint64_t* v_full = bars + 1 + 2 * NST;    // [NST]
+  uint64_t* v_empty = bars + 1 + 3 * NST;   // [NST]
+  uint64_t* sdp_full = bars + 1 + 4 * NST;  // [2]
+  uint64_t* ds_full = bars + 3 + 4 * NST;   // [2]
+  uint64_t* dq_done = bars + 5 + 4 * NST;
+  uint64_t* a_ready = bars + 6 + 4 * NST;   // Q / dO operands are in tensor memory
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 7 + 4 * NST);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -138,15 +165,18 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   if (threadIdx.x == 0) {
     if ((smem_u32(smem) & 1023u) != 0) report_error(p.status, kBadArgument, 0xA1);
     mbar_init(qdo_full, 1);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < NST; ++s) {
       mbar_init(&k_full[s], 1);
       mbar_init(&k_empty[s], 1);
+      mbar_init(&v_full[s], 1);
+      mbar_init(&v_empty[s], 1);
     }
-    mbar_init(v_full, 1);
-    mbar_init(v_empty, 1);
-    mbar_init(sdp_full, 1);
-    mbar_init(ds_full, 128);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&sdp_full[s], 1);
+      mbar_init(&ds_full[s], NSOFT);
+    }
     mbar_init(dq_done, 1);
+    mbar_init(a_ready, NSOFT);
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -158,7 +188,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tS = tmem_base, tDP = tmem_base + 64, tDQ = tmem_base + 128;
+  const uint32_t tQ = tmem_base, tDO = tmem_base + 64;
+  auto tS = [&](int s) -> uint32_t { return tmem_base + 128u + (uint32_t)s * 64u; };
+  auto tDP = [&](int s) -> uint32_t { return tmem_base + 256u + (uint32_t)s * 64u; };
+  const uint32_t tDQ = tmem_base + 384;
 
   if (warp == 0) {
     if (lane == 0 && n_tiles > 0) {
@@ -169,58 +202,66 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         tma_load_4d(sDO + pn * L::QP, &tmDO, qdo_full, pn * 64, h, q0, b);
       }
       for (int j = 0; j < n_tiles; ++j) {
-        const int s = j & 1;
+        const int s = j % NST;
         const int k0 = (j0 + j) * BN;
-        mbar_wait(&k_empty[s], ((j >> 1) & 1) ^ 1, ctx, 0x110 + s);
+        if (j >= NST) mbar_wait(&k_empty[s], ((j / NST) - 1) & 1, ctx, 0x110 + s);
         mbar_expect_tx(&k_full[s], L::KV_BYTES);
 #pragma unroll
         for (int pn = 0; pn < D / 64; ++pn)
           tma_load_4d(sK + s * L::KV_BYTES + pn * L::KP, &tmK, &k_full[s], pn * 64, hkv, k0, b);
-        mbar_wait(v_empty, (j & 1) ^ 1, ctx, 0x120);
-        mbar_expect_tx(v_full, L::KV_BYTES);
+        if (j >= NST) mbar_wait(&v_empty[s], ((j / NST) - 1) & 1, ctx, 0x120 + s);
+        mbar_expect_tx(&v_full[s], L::KV_BYTES);
 #pragma unroll
-        for (int pn = 0; pn < D / 64; ++pn) tma_load_4d(sV + pn * L::KP, &tmV, v_full, pn * 64, hkv, k0, b);
+        for (int pn = 0; pn < D / 64; ++pn)
+          tma_load_4d(sV + s * L::KV_BYTES + pn * L::KP, &tmV, &v_full[s], pn * 64, hkv, k0, b);
       }
     }
   } else if (warp == 1) {
     if (lane == 0 && n_tiles > 0) {
       constexpr uint32_t idescS = make_idesc_bf16(BM, BN, false, false);
       constexpr uint32_t idescDQ = make_idesc_bf16(BM, D, false, true);
-      const uint32_t aQ = smem_u32(sQ), aDO = smem_u32(sDO), aV = smem_u32(sV);
-      mbar_wait(qdo_full, 0, ctx, 0x130);
-      for (int j = 0; j < n_tiles; ++j) {
-        const int s = j & 1;
-        const uint32_t aK = smem_u32(sK + s * L::KV_BYTES);
-        mbar_wait(&k_full[s], (j >> 1) & 1, ctx, 0x140 + s);
-        mbar_wait(v_full, j & 1, ctx, 0x150);
+      auto issue_SdP = [&](int j) {
+        const int s = j & 1, ks = j % NST;
+        const uint32_t aK = smem_u32(sK + ks * L::KV_BYTES), aV = smem_u32(sV + ks * L::KV_BYTES);
+        mbar_wait(&k_full[ks], (j / NST) & 1, ctx, 0x140 + ks);
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint64_t ad = make_desc_kmajor_sw128(aQ + (kk / 4) * L::QP + (kk % 4) * 32);
           const uint64_t bd = make_desc_kmajor_sw128(aK + (kk / 4) * L::KP + (kk % 4) * 32);
-          umma_ss(tS, ad, bd, idescS, kk > 0 ? 1u : 0u);
+          umma_ts(tS(s), tQ + kk * 8, bd, idescS, kk > 0 ? 1u : 0u);
         }
+        mbar_wait(&v_full[ks], (j / NST) & 1, ctx, 0x150 + ks);
+        tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint64_t ad = make_desc_kmajor_sw128(aDO + (kk / 4) * L::QP + (kk % 4) * 32);
           const uint64_t bd = make_desc_kmajor_sw128(aV + (kk / 4) * L::KP + (kk % 4) * 32);
-          umma_ss(tDP, ad, bd, idescS, kk > 0 ? 1u : 0u);
+          umma_ts(tDP(s), tDO + kk * 8, bd, idescS, kk > 0 ? 1u : 0u);
         }
-        umma_commit(v_empty);
-        umma_commit(sdp_full);
-        mbar_wait(ds_full, j & 1, ctx, 0x160);
+        umma_commit(&v_empty[ks]);
+        umma_commit(&sdp_full[s]);
+      };
+      mbar_wait(a_ready, 0, ctx, 0x130);
+      tc_fence_after();
+      issue_SdP(0);
+      if (n_tiles > 1) issue_SdP(1);
+      for (int j = 0; j < n_tiles; ++j) {
+        const int s = j & 1, ks = j % NST;
+        const uint32_t aK = smem_u32(sK + ks * L::KV_BYTES);
+        mbar_wait(&ds_full[s], (j >> 1) & 1, ctx, 0x160 + s);
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < BN / 16; ++kk) {
           const uint64_t bd = make_desc_mnmajor_sw128(aK + kk * 2048, L::KP);
-          umma_ts(tDQ, tS + kk * 8, bd, idescDQ, (j > 0 || kk > 0) ? 1u : 0u);
+          umma_ts(tDQ, tS(s) + kk * 8, bd, idescDQ, (j > 0 || kk > 0) ? 1u : 0u);
         }
-        umma_commit(&k_empty[s]);
+        umma_commit(&k_empty[ks]);
+        if (j + 2 < n_tiles) issue_SdP(j + 2);
       }
       umma_commit(dq_done);
     }
   } else {
     const int quad = warp & 3;
+    const int part = (warp - 2) >> 2;      // warpgroup: key columns [WCOLS part, WCOLS part + WCOLS)
     const int r = quad * 32 + lane;
     const int row = q0 + r;
     const bool row_ok = row < p.Tq;
@@ -233,9 +274,32 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       lse2 = (l == -INFINITY) ? INFINITY : l * kLog2e;
       delta = p.delta[((size_t)b * p.Hq + h) * p.Tq + row];
     }
+    if (n_tiles > 0) {
+      // this thread's slice of its Q and dO rows: swizzled shared memory -> packed bf16 pairs in tensor memory
+      constexpr int EC = D / NWG;                  // elements per thread and operand (32 or 16)
+      mbar_wait(qdo_full, 0, ctx, 0x190);
+#pragma unroll
+      for (int which = 0; which < 2; ++which) {
+        const uint8_t* src = which == 0 ? sQ : sDO;
+        uint32_t regs[EC / 2];
+#pragma unroll
+        for (int c8 = 0; c8 < EC / 8; ++c8) {
+          const int col = part * EC + c8 * 8;      // first element of a 16-byte chunk
+          const uint4 u = *reinterpret_cast<const uint4*>(src + (col >> 6) * L::QP +
+                                                          sw128_offset((uint32_t)r, (uint32_t)(col & 63) * 2));
+          regs[c8 * 4 + 0] = u.x; regs[c8 * 4 + 1] = u.y; regs[c8 * 4 + 2] = u.z; regs[c8 * 4 + 3] = u.w;
+        }
+        const uint32_t dst = (which == 0 ? tQ : tDO) + lane_off + part * (EC / 2);
+        tmem_st_n<EC / 2>(dst, regs);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(a_ready);
+    }
     for (int j = 0; j < n_tiles; ++j) {
+      const int s = j & 1;
       const int k0 = (j0 + j) * BN;
-      mbar_wait(sdp_full, j & 1, ctx, 0x170);
+      mbar_wait(&sdp_full[s], (j >> 1) & 1, ctx, 0x170 + s);
       tc_fence_after();
       const bool full_vis = (pmin - (long long)(k0 + BN - 1) >= (long long)p.lo) &&
                             (pmax - (long long)k0 < (long long)p.hi) && (k0 + BN <= p.Tk) &&
@@ -245,56 +309,71 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       const long long cend = (long long)p.Tk - k0 - 1;
       if (chi > cend) chi = cend;
       if (!row_ok) chi = -1;
-      const int ichi = full_vis ? 1000 : (int)max(-1ll, min(chi, 1000ll));
-      const int iclo = full_vis ? -1 : (int)max(-1ll, min(clo, 1000ll));
+      const int ichi = (int)max(-1ll, min(chi, 1000ll));
+      const int iclo = (int)max(-1ll, min(clo, 1000ll));
+      uint32_t sv[WCOLS], dp[WCOLS], pk[WCOLS / 2];
+      tmem_ld_n<WCOLS>(tS(s) + lane_off + part * WCOLS, sv);
+      tmem_ld_n<WCOLS>(tDP(s) + lane_off + part * WCOLS, dp);
+      tmem_ld_wait();
+      if (full_vis) {
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        uint32_t sv[32], dp[32], pk[16];
-        tmem_ld_x32(tS + lane_off + half * 32, sv);
-        tmem_ld_x32(tDP + lane_off + half * 32, dp);
-        tmem_ld_wait();
+        for (int c = 0; c < WCOLS; c += 2) {
+          const float p0 = exp2f(fmaf(__uint_as_float(sv[c]), p.scale_log2, -lse2));
+          const float p1 = exp2f(fmaf(__uint_as_float(sv[c + 1]), p.scale_log2, -lse2));
+          pk[c >> 1] = pack_bf16x2(p0 * (__uint_as_float(dp[c]) - delta) * p.scale,
+                                   p1 * (__uint_as_float(dp[c + 1]) - delta) * p.scale);
+        }
+      } else {
 #pragma unroll
-        for (int c = 0; c < 32; c += 2) {
+        for (int c = 0; c < WCOLS; c += 2) {
           float d2[2];
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
-            const int cc = half * 32 + c + e;
+            const int cc = part * WCOLS + c + e;
             const bool vis = (cc <= ichi) && (cc > iclo);
             const float pr = vis ? exp2f(fmaf(__uint_as_float(sv[c + e]), p.scale_log2, -lse2)) : 0.f;
             d2[e] = pr * (__uint_as_float(dp[c + e]) - delta) * p.scale;
           }
           pk[c >> 1] = pack_bf16x2(d2[0], d2[1]);
         }
-        tmem_st_x16(tS + lane_off + half * 16, pk);
       }
+      // every warpgroup has read its fp32 columns before the packed dS overwrites columns 0..31
+      asm volatile("bar.sync 2, %0;" ::"n"(NSOFT) : "memory");
+      tmem_st_n<WCOLS / 2>(tS(s) + lane_off + part * (WCOLS / 2), pk);
       tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(ds_full);
+      mbar_arrive(&ds_full[s]);
     }
     if (n_tiles > 0) {
       mbar_wait(dq_done, 0, ctx, 0x180);
       tc_fence_after();
     }
+    // warpgroup `part` writes output columns [part * D / NWG, (part + 1) * D / NWG)
     bf16* orow = p.dq + (((size_t)b * p.Tq + row) * p.Hq + h) * D;
-#pragma unroll
-    for (int ch = 0; ch < D / 32; ++ch) {
-      uint32_t o[32];
+    constexpr int OC = D / NWG;       // 32 (D = 128) or 16 (D = 64) columns
+    {
+      uint32_t o[OC];
       if (n_tiles > 0) {
-        tmem_ld_x32(tDQ + lane_off + ch * 32, o);
+#pragma unroll
+        for (int c32 = 0; c32 < (OC + 31) / 32; ++c32) {
+          constexpr int W = OC < 32 ? OC : 32;
+          uint32_t (&oo)[W] = *reinterpret_cast<uint32_t (*)[W]>(&o[c32 * 32]);
+          tmem_ld_n<W>(tDQ + lane_off + part * OC + c32 * 32, oo);
+        }
         tmem_ld_wait();
       } else {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) o[i] = 0u;
+        for (int i = 0; i < OC; ++i) o[i] = 0u;
       }
       if (row_ok) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
+        for (int i = 0; i < OC / 8; ++i) {
           uint4 w;
           w.x = pack_bf16x2(__uint_as_float(o[8 * i + 0]), __uint_as_float(o[8 * i + 1]));
           w.y = pack_bf16x2(__uint_as_float(o[8 * i + 2]), __uint_as_float(o[8 * i + 3]));
           w.z = pack_bf16x2(__uint_as_float(o[8 * i + 4]), __uint_as_float(o[8 * i + 5]));
           w.w = pack_bf16x2(__uint_as_float(o[8 * i + 6]), __uint_as_float(o[8 * i + 7]));
-          reinterpret_cast<uint4*>(orow + ch * 32)[i] = w;
+          reinterpret_cast<uint4*>(orow + part * OC)[i] = w;
         }
       }
     }
@@ -320,9 +399,10 @@ struct SmemDKV {
   static constexpr int K_BYTES = KM * D * 2;
   static constexpr int Q_BYTES = QN * D * 2;
   static constexpr int OFF_V = K_BYTES;
-  static constexpr int OFF_Q = 2 * K_BYTES;            // stages: [Q | dO] x 2
+  static constexpr int NST = 4;                        // [Q | dO] ring: deep enough to hide the TMA latency
+  static constexpr int OFF_Q = 2 * K_BYTES;
   static constexpr int STAGE = 2 * Q_BYTES;
-  static constexpr int OFF_ROW = OFF_Q + 2 * STAGE;    // lse2 / delta / qpos staging: 2 x 3 x 64 x 4
+  static constexpr int OFF_ROW = OFF_Q + NST * STAGE;  // lse2 / delta / qpos staging: 2 x 3 x 64 x 4
   static constexpr int OFF_BAR = OFF_ROW + 2 * 3 * QN * 4;
   static constexpr int TOTAL = OFF_BAR + 256;
 };
@@ -339,7 +419,7 @@ struct QTileIter {
 };
 
 template <int D>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(NTHR, 1)
 attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
                     const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                     const Params p) {
@@ -351,13 +431,14 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   uint8_t* sQ = smem + L::OFF_Q;
   float* s_row = reinterpret_cast<float*>(smem + L::OFF_ROW);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
+  constexpr int NST = L::NST;
   uint64_t* kv_full = bars + 0;
-  uint64_t* q_full = bars + 1;    // [2]
-  uint64_t* q_empty = bars + 3;   // [2]
-  uint64_t* st_full = bars + 5;   // [2]
-  uint64_t* pds_full = bars + 7;  // [2]
-  uint64_t* acc_done = bars + 9;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+  uint64_t* q_full = bars + 1;              // [NST]
+  uint64_t* q_empty = bars + 1 + NST;       // [NST]
+  uint64_t* st_full = bars + 1 + 2 * NST;   // [2]
+  uint64_t* pds_full = bars + 3 + 2 * NST;  // [2]
+  uint64_t* acc_done = bars + 5 + 2 * NST;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6 + 2 * NST);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -390,11 +471,13 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   if (threadIdx.x == 0) {
     if ((smem_u32(smem) & 1023u) != 0) report_error(p.status, kBadArgument, 0xA2);
     mbar_init(kv_full, 1);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < NST; ++s) {
       mbar_init(&q_full[s], 1);
       mbar_init(&q_empty[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
       mbar_init(&st_full[s], 1);
-      mbar_init(&pds_full[s], 128);
+      mbar_init(&pds_full[s], NSOFT);
     }
     mbar_init(acc_done, 1);
     *abort_flag = 0;
@@ -421,11 +504,11 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         tma_load_4d(sV + pn * L::KPANEL, &tmV, kv_full, pn * 64, hkv, k0, b);
       }
       for (int it = 0; it < n_it; ++it) {
-        const int s = it & 1;
+        const int s = it % NST;
         int g, i;
         iter.get(it, g, i);
         const int h = hkv * G + g;
-        mbar_wait(&q_empty[s], ((it >> 1) & 1) ^ 1, ctx, 0x210 + s);
+        if (it >= NST) mbar_wait(&q_empty[s], ((it / NST) - 1) & 1, ctx, 0x210 + s);
         mbar_expect_tx(&q_full[s], L::STAGE);
         uint8_t* dst = sQ + s * L::STAGE;
 #pragma unroll
@@ -441,10 +524,10 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       constexpr uint32_t idescAcc = make_idesc_bf16(KM, D, false, true);
       const uint32_t aK = smem_u32(sK), aV = smem_u32(sV);
       auto issue_SdP = [&](int it) {
-        const int s = it & 1;
-        mbar_wait(&q_full[s], (it >> 1) & 1, ctx, 0x220 + s);
+        const int s = it & 1, qs = it % NST;
+        mbar_wait(&q_full[qs], (it / NST) & 1, ctx, 0x220 + qs);
         tc_fence_after();
-        const uint32_t aQ = smem_u32(sQ + s * L::STAGE);
+        const uint32_t aQ = smem_u32(sQ + qs * L::STAGE);
         const uint32_t aDO = aQ + L::Q_BYTES;
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
@@ -467,7 +550,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         const int s = it & 1;
         mbar_wait(&pds_full[s], (it >> 1) & 1, ctx, 0x240 + s);
         tc_fence_after();
-        const uint32_t aQ = smem_u32(sQ + s * L::STAGE);
+        const uint32_t aQ = smem_u32(sQ + (it % NST) * L::STAGE);
         const uint32_t aDO = aQ + L::Q_BYTES;
 #pragma unroll
         for (int kk = 0; kk < QN / 16; ++kk) {
@@ -479,15 +562,18 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           const uint64_t bd = make_desc_mnmajor_sw128(aQ + kk * 2048, L::QPANEL);
           umma_ts(tDK, tDPT(s) + kk * 8, bd, idescAcc, (it > 0 || kk > 0) ? 1u : 0u);
         }
-        umma_commit(&q_empty[s]);
+        umma_commit(&q_empty[it % NST]);
         if (it + 2 < n_it) issue_SdP(it + 2);
       }
       umma_commit(acc_done);
     }
   } else {
+    // NWG softmax warpgroups: each covers the 128 key rows (TMEM lane quadrant = warp % 4) and WCOLS of the 64
+    // query columns of a tile.
     const int quad = warp & 3;
+    const int part = (warp - 2) >> 2;
     const int r = quad * 32 + lane;  // key row
-    const int tid = threadIdx.x - 64;  // 0..127
+    const int tid = threadIdx.x - 64;  // 0..NSOFT-1
     const long long kpos = (long long)k0 + r;
     const bool key_ok = r < keys_valid;
     const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
@@ -514,35 +600,59 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         }
         st_lse[tid] = l2;
         st_pos[tid] = pos;
-      } else {
+      } else if (tid < 2 * QN) {
         const int qi = q0 + tid - QN;
         st_del[tid - QN] = (qi < p.Tq) ? p.delta[((size_t)b * p.Hq + h) * p.Tq + qi] : 0.f;
       }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
+      // every (key, query) pair of the tile visible?  (CTA-uniform: contiguous positions, full tile)
+      const long long pmin = (long long)q0 + p.q_off, pmax = pmin + QN - 1;
+      const bool full = p.q_pos == nullptr && keys_valid == KM && q0 + QN <= p.Tq &&
+                        pmin - ((long long)k0 + KM - 1) >= (long long)p.lo && pmax - (long long)k0 < (long long)p.hi;
+      asm volatile("bar.sync 1, %0;" ::"n"(NSOFT) : "memory");
       mbar_wait(&st_full[s], (it >> 1) & 1, ctx, 0x250 + s);
       tc_fence_after();
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        uint32_t sv[32], dp[32], pp[16], pd[16];
-        tmem_ld_x32(tST(s) + lane_off + half * 32, sv);
-        tmem_ld_x32(tDPT(s) + lane_off + half * 32, dp);
+      {
+        uint32_t sv[WCOLS], dp[WCOLS], pp[WCOLS / 2], pd[WCOLS / 2];
+        tmem_ld_n<WCOLS>(tST(s) + lane_off + part * WCOLS, sv);
+        tmem_ld_n<WCOLS>(tDPT(s) + lane_off + part * WCOLS, dp);
         tmem_ld_wait();
+        if (full) {
 #pragma unroll
-        for (int c = 0; c < 32; c += 2) {
-          float pr[2], ds[2];
-#pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int cc = half * 32 + c + e;
-            const int pos = st_pos[cc];
-            const bool vis = key_ok && pos >= vis_lo && pos < vis_hi;
-            pr[e] = vis ? exp2f(fmaf(__uint_as_float(sv[c + e]), p.scale_log2, -st_lse[cc])) : 0.f;
-            ds[e] = pr[e] * (__uint_as_float(dp[c + e]) - st_del[cc]) * p.scale;
+          for (int c = 0; c < WCOLS; c += 4) {
+            const float4 l4 = *reinterpret_cast<const float4*>(st_lse + part * WCOLS + c);
+            const float4 d4 = *reinterpret_cast<const float4*>(st_del + part * WCOLS + c);
+            const float p0 = exp2f(fmaf(__uint_as_float(sv[c + 0]), p.scale_log2, -l4.x));
+            const float p1 = exp2f(fmaf(__uint_as_float(sv[c + 1]), p.scale_log2, -l4.y));
+            const float p2 = exp2f(fmaf(__uint_as_float(sv[c + 2]), p.scale_log2, -l4.z));
+            const float p3 = exp2f(fmaf(__uint_as_float(sv[c + 3]), p.scale_log2, -l4.w));
+            pp[(c >> 1) + 0] = pack_bf16x2(p0, p1);
+            pp[(c >> 1) + 1] = pack_bf16x2(p2, p3);
+            pd[(c >> 1) + 0] = pack_bf16x2(p0 * (__uint_as_float(dp[c + 0]) - d4.x) * p.scale,
+                                           p1 * (__uint_as_float(dp[c + 1]) - d4.y) * p.scale);
+            pd[(c >> 1) + 1] = pack_bf16x2(p2 * (__uint_as_float(dp[c + 2]) - d4.z) * p.scale,
+                                           p3 * (__uint_as_float(dp[c + 3]) - d4.w) * p.scale);
           }
-          pp[c >> 1] = pack_bf16x2(pr[0], pr[1]);
-          pd[c >> 1] = pack_bf16x2(ds[0], ds[1]);
+        } else {
+#pragma unroll
+          for (int c = 0; c < WCOLS; c += 2) {
+            float pr[2], ds[2];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              const int cc = part * WCOLS + c + e;
+              const int pos = st_pos[cc];
+              const bool vis = key_ok && pos >= vis_lo && pos < vis_hi;
+              pr[e] = vis ? exp2f(fmaf(__uint_as_float(sv[c + e]), p.scale_log2, -st_lse[cc])) : 0.f;
+              ds[e] = pr[e] * (__uint_as_float(dp[c + e]) - st_del[cc]) * p.scale;
+            }
+            pp[c >> 1] = pack_bf16x2(pr[0], pr[1]);
+            pd[c >> 1] = pack_bf16x2(ds[0], ds[1]);
+          }
         }
-        tmem_st_x16(tST(s) + lane_off + half * 16, pp);
-        tmem_st_x16(tDPT(s) + lane_off + half * 16, pd);
+        // all 64 S^T / dP^T columns of these rows must have been read (by every warpgroup) before the packed
+        // values overwrite columns 0..31
+        asm volatile("bar.sync 2, %0;" ::"n"(NSOFT) : "memory");
+        tmem_st_n<WCOLS / 2>(tST(s) + lane_off + part * (WCOLS / 2), pp);
+        tmem_st_n<WCOLS / 2>(tDPT(s) + lane_off + part * (WCOLS / 2), pd);
       }
       tmem_st_wait();
       tc_fence_before();
@@ -552,16 +662,19 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       mbar_wait(acc_done, 0, ctx, 0x260);
       tc_fence_after();
     }
-#pragma unroll
-    for (int which = 0; which < 2; ++which) {
+    {
+      // warpgroups 0 .. NWG/2-1 write dV, the others dK; each a contiguous slice of the D columns
+      constexpr int PER = NWG / 2;
+      constexpr int OC = D / PER;          // columns per warpgroup (64 for D = 128)
+      const int which = part / PER, sub = part % PER;
       bf16* base = which == 0 ? p.dv : p.dk;
       const uint32_t tacc = which == 0 ? tDV : tDK;
-      bf16* orow = base + (((size_t)b * p.Tk + k0 + r) * p.Hkv + hkv) * D;
+      bf16* orow = base + (((size_t)b * p.Tk + k0 + r) * p.Hkv + hkv) * D + sub * OC;
 #pragma unroll
-      for (int ch = 0; ch < D / 32; ++ch) {
+      for (int ch = 0; ch < OC / 32; ++ch) {
         uint32_t o[32];
         if (n_it > 0) {
-          tmem_ld_x32(tacc + lane_off + ch * 32, o);
+          tmem_ld_x32(tacc + lane_off + sub * OC + ch * 32, o);
           tmem_ld_wait();
         } else {
 #pragma unroll
@@ -616,7 +729,7 @@ static int launch_all(const void* q, const void* k, const void* v, const void* d
       configured = true;
     }
     dim3 grid(p.Hq, (p.Tq + BM - 1) / BM, p.B);
-    kern<<<grid, 192, SmemDQ<D>::TOTAL, st>>>(tmQ, tmDO, tmK, tmV, p);
+    kern<<<grid, NTHR, SmemDQ<D>::TOTAL, st>>>(tmQ, tmDO, tmK, tmV, p);
     HMF_CHECK_CUDA(cudaGetLastError());
   }
   // dK/dV kernel: K/V boxes of 128 rows, Q/dO boxes of 64 rows
@@ -632,7 +745,7 @@ static int launch_all(const void* q, const void* k, const void* v, const void* d
       configured = true;
     }
     dim3 grid((p.Tk + KM - 1) / KM, p.Hkv, p.B);
-    kern<<<grid, 192, SmemDKV<D>::TOTAL, st>>>(tmQ, tmDO, tmK, tmV, p);
+    kern<<<grid, NTHR, SmemDKV<D>::TOTAL, st>>>(tmQ, tmDO, tmK, tmV, p);
     HMF_CHECK_CUDA(cudaGetLastError());
   }
   return HMF_OK;
