@@ -146,3 +146,35 @@ def _cp_worker(rank, world):
 @needs2
 def test_cp_attention_peer_kv_two_gpus():
     run_ranks(_cp_worker, 2, backend="nccl", timeout=240)
+
+
+def _ep_fused_worker(rank, world):
+    from hybrid_model_factory_b200.ops import _lib
+    from hybrid_model_factory_b200.ops import reference as R
+    from hybrid_model_factory_b200.parallel.ep_fused import FusedExpertParallel
+    dev = torch.device("cuda", rank)
+    E, Dm, Fi, k = 8, 512, 256, 2
+    per = E // world
+    g = torch.Generator().manual_seed(0)
+    wgu = (torch.randn(E, 2 * Fi, Dm, generator=g) * 0.05).bfloat16().to(dev)
+    wd = (torch.randn(E, Dm, Fi, generator=g) * 0.05).bfloat16().to(dev)
+    ep = FusedExpertParallel(dist.group.WORLD, per, Dm, Fi, max_send_rows=2048, capacity_rows=4096)
+    gl = torch.Generator().manual_seed(100 + rank)
+    for it in range(3):
+        T = 300 + 57 * rank + 11 * it                         # different token counts on every rank and round
+        x = (torch.randn(T, Dm, generator=gl) * 0.5).bfloat16().to(dev)
+        w, idx = R.moe_router(torch.randn(T, E, generator=gl).to(dev), k)
+        out = ep.forward(x, w, idx, wgu[rank * per:(rank + 1) * per].contiguous(),
+                         wd[rank * per:(rank + 1) * per].contiguous())
+        torch.cuda.synchronize()
+        _lib.assert_status_ok()
+        ref = R.moe_experts(x.float(), wgu.float(), wd.float(), w, idx)
+        err = (out.float() - ref).abs().max() / ref.abs().max()
+        assert err < 3e-2, (it, err)
+        assert int(ep.counts[2]) == 0
+    dist.barrier()
+
+
+@needs2
+def test_expert_parallel_fused_all_to_all_two_gpus():
+    run_ranks(_ep_fused_worker, 2, backend="nccl", timeout=240)
