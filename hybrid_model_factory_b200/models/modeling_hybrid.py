@@ -77,6 +77,7 @@ class SparseMoeBlock(nn.Module):
         else:
             self.shared_expert = None
         self.expert_parallel_group = None
+        self.fused_ep = None            # parallel.ep_fused.FusedExpertParallel (grouped GEMM kernels, inference)
 
     def forward(self, x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
         shape = x.shape
@@ -84,7 +85,7 @@ class SparseMoeBlock(nn.Module):
         logits = self.gate(flat)
         weights, indices = moe_ops.router(logits, self.top_k, self.norm_topk_prob)
         out = moe_ops.experts_forward(flat, self.experts.gate_up_proj, self.experts.down_proj, weights.to(flat.dtype),
-                                      indices, ep=self.expert_parallel_group)
+                                      indices, ep=self.expert_parallel_group, fused=self.fused_ep)
         if self.shared_expert is not None:
             out = out + torch.sigmoid(self.shared_expert_gate(flat)) * self.shared_expert(flat)
         return out.reshape(shape), logits

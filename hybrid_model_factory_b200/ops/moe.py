@@ -44,8 +44,13 @@ def grouped_swiglu_experts(x_sorted: Tensor, counts: Tensor, w_gate_up: Tensor, 
 
 
 def experts_forward(x: Tensor, w_gate_up: Tensor, w_down: Tensor, weights: Tensor, indices: Tensor,
-                    ep=None) -> Tensor:
-    """``x [T, Dm]``, routing ``weights, indices [T, k]`` -> ``[T, Dm]``."""
+                    ep=None, fused=None) -> Tensor:
+    """``x [T, Dm]``, routing ``weights, indices [T, k]`` -> ``[T, Dm]``.  ``fused`` (a
+    ``parallel.ep_fused.FusedExpertParallel``) runs the tcgen05 grouped GEMMs, with the expert-parallel all-to-all
+    folded into them, whenever no gradient is needed."""
+    if (fused is not None and not torch.is_grad_enabled() and x.is_cuda and x.dtype == torch.bfloat16
+            and indices.numel() <= fused.max_send):
+        return fused.forward(x, weights, indices, w_gate_up, w_down)
     if ep is not None and ep.size > 1:
         from ..parallel.ep import ep_experts_forward
         return ep_experts_forward(x, w_gate_up, w_down, weights, indices, ep)

@@ -144,3 +144,29 @@ def _numel(shape) -> int:
 
 def _esize(dt) -> int:
     return torch.empty((), dtype=dt).element_size()
+
+
+def attach_fused_moe(model, group=None, max_tokens: int = 8192) -> int:
+    """Gives every ``SparseMoeBlock`` of ``model`` the grouped-GEMM inference path.  With ``group`` the experts are
+    sharded over its ranks first (expert parallelism) and the all-to-all runs inside the GEMMs.  One workspace is
+    shared by all layers (they run one after the other).  Returns the number of blocks attached."""
+    from ..models.modeling_hybrid import SparseMoeBlock
+    from .ep import EPContext, shard_experts
+    blocks = [m for m in model.modules() if isinstance(m, SparseMoeBlock)]
+    if not blocks:
+        return 0
+    world = 1
+    if group is not None:
+        ctx = EPContext.from_group(group)
+        world = ctx.size
+        for b in blocks:
+            if b.expert_parallel_group is None:
+                shard_experts(b, ctx)
+    b0 = blocks[0]
+    e_local, two_f, dm = b0.experts.gate_up_proj.shape
+    rows = max_tokens * b0.top_k
+    shared = FusedExpertParallel(group, e_local, dm, two_f // 2, max_send_rows=rows, capacity_rows=rows * min(world, 4),
+                                 device=b0.experts.gate_up_proj.device)
+    for b in blocks:
+        b.fused_ep = shared
+    return len(blocks)

@@ -283,3 +283,20 @@ def test_moe_grouped_gemm_single_rank():
     assert int(ep.counts[1]) == T * k and int(ep.counts[2]) == 0
     err = (out.float() - ref).abs().max() / ref.abs().max()
     assert err < 3e-2, err
+
+
+@pytest.mark.gpu
+def test_moe_model_uses_grouped_gemm_kernels():
+    from hybrid_model_factory_b200.parallel.ep_fused import attach_fused_moe
+    torch.manual_seed(0)
+    cfg = HybridConfig("hybrid_qwen3_moe", vocab_size=256, hidden_size=256, intermediate_size=512, num_hidden_layers=2,
+                       num_attention_heads=2, num_key_value_heads=2, head_dim=128, num_experts=8, num_experts_per_tok=2,
+                       moe_intermediate_size=128, hybrid_override_pattern="*-GDN")
+    model = build_model(cfg).to("cuda", torch.bfloat16).eval()
+    ids = torch.randint(0, 256, (2, 96), device="cuda")
+    with torch.no_grad():
+        ref = model(ids).logits.float()
+        assert attach_fused_moe(model) == 2
+        out = model(ids).logits.float()
+    assert model.model.layers[0].mlp.fused_ep.calls > 0
+    assert (out - ref).abs().max() < 0.05 * ref.abs().max()
