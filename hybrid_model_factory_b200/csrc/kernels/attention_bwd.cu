@@ -107,7 +107,7 @@ constexpr int NTHR = 64 + NSOFT;              // + TMA warp + MMA warp
 constexpr int WCOLS = 64 / NWG;               // 16 fp32 columns per thread and tile
 
 template <int D>
-__global__ void __launch_bounds__(NTHR, 1)
+__global__ void __launch_bounds__(NTHR + 32, 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
                    const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                    const Params p) {
@@ -135,7 +135,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   uint64_t* ds_full = bars + 3 + 4 * NST;   // [2]
   uint64_t* dq_done = bars + 5 + 4 * NST;
   uint64_t* a_ready = bars + 6 + 4 * NST;   // Q / dO operands are in tensor memory
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 7 + 4 * NST);
+  uint64_t* t_free = bars + 7 + 4 * NST;    // [2] dS of a buffer consumed by the dQ MMAs
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9 + 4 * NST);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -173,6 +174,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(&sdp_full[s], 1);
+      mbar_init(&t_free[s], 1);
       mbar_init(&ds_full[s], NSOFT);
     }
     mbar_init(dq_done, 1);
@@ -219,7 +221,6 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   } else if (warp == 1) {
     if (lane == 0 && n_tiles > 0) {
       constexpr uint32_t idescS = make_idesc_bf16(BM, BN, false, false);
-      constexpr uint32_t idescDQ = make_idesc_bf16(BM, D, false, true);
       auto issue_SdP = [&](int j) {
         const int s = j & 1, ks = j % NST;
         const uint32_t aK = smem_u32(sK + ks * L::KV_BYTES), aV = smem_u32(sV + ks * L::KV_BYTES);
@@ -240,13 +241,21 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         umma_commit(&v_empty[ks]);
         umma_commit(&sdp_full[s]);
       };
+      // S / dP issuer; the dQ MMAs are issued by a second thread (warp 2 + 4 NWG)
       mbar_wait(a_ready, 0, ctx, 0x130);
       tc_fence_after();
-      issue_SdP(0);
-      if (n_tiles > 1) issue_SdP(1);
+      for (int j = 0; j < n_tiles; ++j) {
+        if (j >= 2) mbar_wait(&t_free[j & 1], ((j >> 1) - 1) & 1, ctx, 0x1A0 + (j & 1));
+        issue_SdP(j);
+      }
+    }
+  } else if (warp == 2 + 4 * NWG) {
+    if (lane == 0 && n_tiles > 0) {
+      constexpr uint32_t idescDQ = make_idesc_bf16(BM, D, false, true);
       for (int j = 0; j < n_tiles; ++j) {
         const int s = j & 1, ks = j % NST;
         const uint32_t aK = smem_u32(sK + ks * L::KV_BYTES);
+        mbar_wait(&k_full[ks], (j / NST) & 1, ctx, 0x1B0 + ks);
         mbar_wait(&ds_full[s], (j >> 1) & 1, ctx, 0x160 + s);
         tc_fence_after();
 #pragma unroll
@@ -255,7 +264,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           umma_ts(tDQ, tS(s) + kk * 8, bd, idescDQ, (j > 0 || kk > 0) ? 1u : 0u);
         }
         umma_commit(&k_empty[ks]);
-        if (j + 2 < n_tiles) issue_SdP(j + 2);
+        umma_commit(&t_free[s]);
       }
       umma_commit(dq_done);
     }
@@ -419,7 +428,7 @@ struct QTileIter {
 };
 
 template <int D>
-__global__ void __launch_bounds__(NTHR, 1)
+__global__ void __launch_bounds__(NTHR + 32, 1)
 attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
                     const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                     const Params p) {
@@ -438,7 +447,8 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   uint64_t* st_full = bars + 1 + 2 * NST;   // [2]
   uint64_t* pds_full = bars + 3 + 2 * NST;  // [2]
   uint64_t* acc_done = bars + 5 + 2 * NST;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6 + 2 * NST);
+  uint64_t* t_free = bars + 6 + 2 * NST;    // [2] P^T / dS^T of a buffer consumed by the accumulate MMAs
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8 + 2 * NST);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -477,6 +487,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(&st_full[s], 1);
+      mbar_init(&t_free[s], 1);
       mbar_init(&pds_full[s], NSOFT);
     }
     mbar_init(acc_done, 1);
@@ -521,7 +532,6 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   } else if (warp == 1) {
     if (lane == 0 && n_it > 0) {
       constexpr uint32_t idescST = make_idesc_bf16(KM, QN, false, false);
-      constexpr uint32_t idescAcc = make_idesc_bf16(KM, D, false, true);
       const uint32_t aK = smem_u32(sK), aV = smem_u32(sV);
       auto issue_SdP = [&](int it) {
         const int s = it & 1, qs = it % NST;
@@ -543,14 +553,23 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         }
         umma_commit(&st_full[s]);
       };
+      // S^T / dP^T issuer; the accumulate MMAs (dV, dK) are issued by a second thread (warp 2 + 4 NWG) so that the
+      // two instruction streams do not serialise behind one issuing thread
       mbar_wait(kv_full, 0, ctx, 0x230);
-      issue_SdP(0);
-      if (n_it > 1) issue_SdP(1);
       for (int it = 0; it < n_it; ++it) {
-        const int s = it & 1;
+        if (it >= 2) mbar_wait(&t_free[it & 1], ((it >> 1) - 1) & 1, ctx, 0x270 + (it & 1));
+        issue_SdP(it);
+      }
+    }
+  } else if (warp == 2 + 4 * NWG) {
+    if (lane == 0 && n_it > 0) {
+      constexpr uint32_t idescAcc = make_idesc_bf16(KM, D, false, true);
+      for (int it = 0; it < n_it; ++it) {
+        const int s = it & 1, qs = it % NST;
+        mbar_wait(&q_full[qs], (it / NST) & 1, ctx, 0x280 + qs);
         mbar_wait(&pds_full[s], (it >> 1) & 1, ctx, 0x240 + s);
         tc_fence_after();
-        const uint32_t aQ = smem_u32(sQ + (it % NST) * L::STAGE);
+        const uint32_t aQ = smem_u32(sQ + qs * L::STAGE);
         const uint32_t aDO = aQ + L::Q_BYTES;
 #pragma unroll
         for (int kk = 0; kk < QN / 16; ++kk) {
@@ -562,8 +581,8 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           const uint64_t bd = make_desc_mnmajor_sw128(aQ + kk * 2048, L::QPANEL);
           umma_ts(tDK, tDPT(s) + kk * 8, bd, idescAcc, (it > 0 || kk > 0) ? 1u : 0u);
         }
-        umma_commit(&q_empty[it % NST]);
-        if (it + 2 < n_it) issue_SdP(it + 2);
+        umma_commit(&q_empty[qs]);
+        umma_commit(&t_free[s]);
       }
       umma_commit(acc_done);
     }
@@ -580,30 +599,55 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     // query position window that sees this key: [kpos + lo, kpos + hi), clamped to int range
     const int vis_lo = (int)min(kpos + (long long)p.lo, 2147483647ll);
     const int vis_hi = (int)min(kpos + (long long)p.hi, 2147483647ll);
-    for (int it = 0; it < n_it; ++it) {
-      const int s = it & 1;
+    // Per-tile row data (lse, delta, positions of the 64 queries) is staged in shared memory one tile ahead: the
+    // global loads of tile it+1 are issued before the work of tile it and stored after it, so their latency is
+    // off the critical path.
+    auto load_rows = [&](int it, float& v0, int& v1) {
       int g, i;
       iter.get(it, g, i);
       const int h = hkv * G + g;
       const int q0 = i * QN;
+      v0 = 0.f;
+      v1 = -(1 << 30);
+      if (tid < QN) {
+        const int qi = q0 + tid;
+        v0 = INFINITY;
+        if (qi < p.Tq) {
+          const float l = p.lse[((size_t)b * p.Hq + h) * p.Tq + qi];
+          v0 = (l == -INFINITY) ? INFINITY : l * kLog2e;
+          v1 = p.q_pos ? p.q_pos[(size_t)b * p.Tq + qi] : qi + p.q_off;
+        }
+      } else if (tid < 2 * QN) {
+        const int qi = q0 + tid - QN;
+        v0 = (qi < p.Tq) ? p.delta[((size_t)b * p.Hq + h) * p.Tq + qi] : 0.f;
+      }
+    };
+    auto store_rows = [&](int it, float v0, int v1) {
+      float* b_lse = s_row + (it & 1) * 3 * QN;
+      if (tid < QN) {
+        b_lse[tid] = v0;
+        reinterpret_cast<int*>(b_lse + 2 * QN)[tid] = v1;
+      } else if (tid < 2 * QN) {
+        b_lse[QN + tid - QN] = v0;
+      }
+    };
+    if (n_it > 0) {
+      float v0;
+      int v1;
+      load_rows(0, v0, v1);
+      store_rows(0, v0, v1);
+    }
+    for (int it = 0; it < n_it; ++it) {
+      const int s = it & 1;
+      int g, i;
+      iter.get(it, g, i);
+      const int q0 = i * QN;
       float* st_lse = s_row + s * 3 * QN;
       float* st_del = st_lse + QN;
       int* st_pos = reinterpret_cast<int*>(st_del + QN);
-      if (tid < QN) {
-        const int qi = q0 + tid;
-        float l2 = INFINITY;
-        int pos = -(1 << 30);
-        if (qi < p.Tq) {
-          const float l = p.lse[((size_t)b * p.Hq + h) * p.Tq + qi];
-          l2 = (l == -INFINITY) ? INFINITY : l * kLog2e;
-          pos = p.q_pos ? p.q_pos[(size_t)b * p.Tq + qi] : qi + p.q_off;
-        }
-        st_lse[tid] = l2;
-        st_pos[tid] = pos;
-      } else if (tid < 2 * QN) {
-        const int qi = q0 + tid - QN;
-        st_del[tid - QN] = (qi < p.Tq) ? p.delta[((size_t)b * p.Hq + h) * p.Tq + qi] : 0.f;
-      }
+      float nv0 = 0.f;
+      int nv1 = 0;
+      if (it + 1 < n_it) load_rows(it + 1, nv0, nv1);      // in flight during this tile's work
       // every (key, query) pair of the tile visible?  (CTA-uniform: contiguous positions, full tile)
       const long long pmin = (long long)q0 + p.q_off, pmax = pmin + QN - 1;
       const bool full = p.q_pos == nullptr && keys_valid == KM && q0 + QN <= p.Tq &&
@@ -657,6 +701,8 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&pds_full[s]);
+      // the other row buffer was last read before this iteration's second barrier: free to overwrite
+      if (it + 1 < n_it) store_rows(it + 1, nv0, nv1);
     }
     if (n_it > 0) {
       mbar_wait(acc_done, 0, ctx, 0x260);
@@ -729,7 +775,7 @@ static int launch_all(const void* q, const void* k, const void* v, const void* d
       configured = true;
     }
     dim3 grid(p.Hq, (p.Tq + BM - 1) / BM, p.B);
-    kern<<<grid, NTHR, SmemDQ<D>::TOTAL, st>>>(tmQ, tmDO, tmK, tmV, p);
+    kern<<<grid, NTHR + 32, SmemDQ<D>::TOTAL, st>>>(tmQ, tmDO, tmK, tmV, p);
     HMF_CHECK_CUDA(cudaGetLastError());
   }
   // dK/dV kernel: K/V boxes of 128 rows, Q/dO boxes of 64 rows
@@ -745,7 +791,7 @@ static int launch_all(const void* q, const void* k, const void* v, const void* d
       configured = true;
     }
     dim3 grid((p.Tk + KM - 1) / KM, p.Hkv, p.B);
-    kern<<<grid, NTHR, SmemDKV<D>::TOTAL, st>>>(tmQ, tmDO, tmK, tmV, p);
+    kern<<<grid, NTHR + 32, SmemDKV<D>::TOTAL, st>>>(tmQ, tmDO, tmK, tmV, p);
     HMF_CHECK_CUDA(cudaGetLastError());
   }
   return HMF_OK;
