@@ -18,6 +18,7 @@ from typing import Dict, List, Optional, Tuple
 import torch
 
 from ..layers.attention import Attention
+from ..layers.bmojo import BMojoLayer
 from ..layers.gdn import GatedDeltaNet
 from ..layers.gka import GatedKalmaNet
 from ..layers.mamba2 import Mamba2
@@ -30,6 +31,10 @@ class ServingState:
         self.device = device or next(model.parameters()).device
         self.kv: Dict[int, Tuple[torch.Tensor, torch.Tensor]] = {}
         self.ssm: Dict[int, dict] = {}
+        # B'MOJO-F layers keep a bounded per-request state (SSM state + the last 2w-1 keys / values of both
+        # streams); it lives in one small ``HybridCache`` per request instead of the paged pools
+        self.bmojo_layers = set()
+        self.side: Dict[int, object] = {}
         total_slots = num_slots + num_snapshots
         for i, layer in enumerate(model.model.layers):
             mixer = layer.seq_mixer
@@ -56,6 +61,8 @@ class ServingState:
                                                     device=self.device),
                                "conv": torch.zeros(total_slots, mixer.d_conv - 1, mixer.conv_dim, device=self.device,
                                                    dtype=dtype), "split": None}
+            elif isinstance(mixer, BMojoLayer):
+                self.bmojo_layers.add(i)
             else:
                 raise NotImplementedError(f"layer {i} ({type(mixer).__name__}) is not supported by the paged engine")
 
@@ -64,6 +71,13 @@ class ServingState:
         for e in self.ssm.values():
             n += sum(t.numel() * t.element_size() for t in e.values() if isinstance(t, torch.Tensor))
         return n
+
+    def side_cache(self, req_id: int):
+        from ..models.cache import HybridCache
+        c = self.side.get(req_id)
+        if c is None:
+            c = self.side[req_id] = HybridCache()
+        return c
 
     def copy_slot(self, src: int, dst: int) -> None:
         """Snapshot / restore of the recurrent state (align-mode prefix caching)."""
@@ -82,8 +96,9 @@ class ServingState:
 class SlotCache:
     """``past_key_values`` adapter for one request during (chunked) prefill."""
 
-    def __init__(self, state: ServingState, slot: int, block_table: List[int], start_pos: int):
+    def __init__(self, state: ServingState, slot: int, block_table: List[int], start_pos: int, side=None):
         self.s, self.slot, self.start = state, slot, start_pos
+        self.side = side          # per-request HybridCache for B'MOJO-F layers
         self.block_table = torch.tensor(block_table, dtype=torch.long, device=state.device)
         self.seqlen_offset = start_pos
         self.cache_aprods = False
@@ -107,7 +122,12 @@ class SlotCache:
         return k_all, v_all
 
     # -- recurrent layers ----------------------------------------------------------------
+    def update_bmojo(self, layer_idx, *args, **kw):
+        return self.side.update_bmojo(layer_idx, *args, **kw)
+
     def get_ssm(self, layer_idx: int) -> Optional[dict]:
+        if layer_idx in self.s.bmojo_layers:
+            return self.side.get_ssm(layer_idx)
         if self.start == 0:
             return None
         e = self.s.ssm[layer_idx]
@@ -125,7 +145,9 @@ class SlotCache:
             rec = e["state"][self.slot][None]
         return {"recurrent_state": rec, "conv_state": conv_state, "log_aprod": None}
 
-    def update_ssm(self, layer_idx: int, recurrent_state=None, conv_state=None, offset: int = 0, log_aprod=None):
+    def update_ssm(self, layer_idx: int, recurrent_state=None, conv_state=None, offset: int = 0, log_aprod=None, **kw):
+        if layer_idx in self.s.bmojo_layers:
+            return self.side.update_ssm(layer_idx, recurrent_state=recurrent_state, conv_state=conv_state, offset=offset)
         e = self.s.ssm[layer_idx]
         if recurrent_state is not None:
             if e["kind"] == "gka":

@@ -85,7 +85,8 @@ class ServingEngine:
         self.stats = {"steps": 0, "decode_tokens": 0, "prefill_tokens": 0, "graph_replays": 0, "decode_steps": 0,
                       "decode_s": 0.0, "prefill_s": 0.0, "decode_gpu_s": 0.0}
         has_moe = any(hasattr(l.mlp, "experts") for l in model.model.layers)
-        self._use_graphs = bool(use_cuda_graphs and self._cuda and not has_moe)
+        # B'MOJO-F layers decode request by request through the layer itself (bounded window state per request)
+        self._use_graphs = bool(use_cuda_graphs and self._cuda and not has_moe and not self.state.bmojo_layers)
         self._graphs: Dict[tuple, dict] = {}
         self._tables: Dict[int, torch.Tensor] = {}
         self._timed_replay = False
@@ -181,6 +182,7 @@ class ServingEngine:
             req.finished, req.finish_time = True, now
             self.sched.finish(rid)
             self._tables.pop(rid, None)
+            self.state.side.pop(rid, None)
         return (rid, tok, done)
 
     # -- sampling ------------------------------------------------------------------------------
@@ -212,7 +214,10 @@ class ServingEngine:
     def _prefill_forward(self, s: ScheduledSeq, tokens: List[int]) -> torch.Tensor:
         ids = torch.tensor([tokens], dtype=torch.long, device=self.device)
         pos = torch.arange(s.start_pos, s.start_pos + len(tokens), device=self.device)[None]
-        cache = SlotCache(self.state, s.slot, self.sched.block_table(s.req_id), s.start_pos)
+        side = self.state.side_cache(s.req_id) if self.state.bmojo_layers else None
+        if side is not None:
+            side.seqlen_offset = s.start_pos
+        cache = SlotCache(self.state, s.slot, self.sched.block_table(s.req_id), s.start_pos, side)
         h, _ = self.model.model(ids, position_ids=pos, past_key_values=cache, use_cache=True)
         return self._logits(h[0, -1:])
 
@@ -239,6 +244,7 @@ class ServingEngine:
         if not self._use_graphs:
             inp = self._decode_inputs(Rn, max(len(t) for t in tables) if tables else 1)
             self._fill_inputs(inp, last, pos, slots, tables)
+            inp["req_ids"] = [s.req_id for s in seqs]
             return self._decode_body(inp, self._splits_for(Rn, max_len))
         Rb = 1
         while Rb < Rn:
@@ -374,6 +380,8 @@ class ServingEngine:
                 y = self._mamba_decode(i, mixer, h, cos, sin, slots)
             elif isinstance(mixer, GatedKalmaNet):
                 y = self._gka_decode(i, mixer, h, slots)
+            elif i in self.state.bmojo_layers:
+                y = self._bmojo_decode(mixer, h, pos, cos, sin, inp["req_ids"])
             else:
                 raise NotImplementedError(type(mixer).__name__)
             h2, res = self._add_norm(y, res, layer.post_attention_layernorm)
@@ -493,6 +501,19 @@ class ServingEngine:
         if gate is not None:
             o = o * torch.sigmoid(gate)
         return self._row_linear(o, mx.o_proj)
+
+    def _bmojo_decode(self, mixer, h, pos, cos, sin, req_ids):
+        """B'MOJO-F: one call of the layer per request with that request's window cache."""
+        outs = []
+        for r, rid in enumerate(req_ids):
+            side = self.state.side_cache(rid)
+            side.seqlen_offset = int(pos[r])
+            cache = SlotCache(self.state, -1, [], int(pos[r]), side)
+            y, _, _ = mixer(h[r:r + 1, None], position_embeddings=(cos[r:r + 1], sin[r:r + 1]),
+                            position_ids=pos[r:r + 1, None], past_key_values=cache, use_cache=True)
+            outs.append(y[:, 0])
+        out = torch.cat(outs, dim=0)
+        return self.tp.all_reduce(out) if self.tp is not None and self.tp.size > 1 else out
 
     def _conv_update(self, i, x_cat, weight, bias, slots):
         e = self.state.ssm[i]

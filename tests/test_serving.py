@@ -58,10 +58,10 @@ def test_prefix_cache_hit_reuses_blocks():
     assert s.stats()["prefix_hits"] == 1
 
 
-@pytest.mark.parametrize("pattern", ["*-GDN", "M2-*", "GKA-SWA"])
+@pytest.mark.parametrize("pattern", ["*-GDN", "M2-*", "GKA-SWA", "BMF-*"])
 def test_engine_matches_generate(pattern):
     torch.manual_seed(0)
-    model = build_model(tiny(pattern)).eval()
+    model = build_model(tiny(pattern, bmojo_config={"window_size": 4, "ssm_mixer": "gdn", "tie_attn_weights": False})).eval()
     prompts = [torch.randint(0, 128, (n,)).tolist() for n in (5, 19, 11)]
     ref = [model.generate(torch.tensor([p]), max_new_tokens=6)[0, len(p):].tolist() for p in prompts]
     eng = ServingEngine(model, block_size=4, num_blocks=64, max_num_seqs=4, max_num_batched_tokens=8, max_model_len=64)
