@@ -118,6 +118,78 @@ class GDNChunkCore(ScanCore):
         kt = kf * torch.exp(glast[..., None] - G)[..., None]
         return {"w": w, "qt": qt, "kt": kt, "P": P, "u": u, "glast": glast, "N": N}
 
+    def _prep_backward(self, q, k, v, g, beta, d_w, d_qt, d_kt, d_P, d_u, d_gl):
+        """Hand-written backward of :meth:`_prep` (no autograd graph, a third of the memory passes).
+        ``q, k, v [B,T,h,D]``, ``g, beta [B,T,h]``; upstream gradients in chunk layout ``[B*h, N, C, .]`` (``d_P``
+        lower triangular, ``d_gl [B*h, N]``).  Returns ``dq, dk, dv, dg, dbeta`` in the input layouts."""
+        B, T, H, Dk = q.shape
+        N = (T + C - 1) // C
+        scale = Dk ** -0.5 if self.scale is None else self.scale
+        qf, kf, vf = _chunk(q, N).float(), _chunk(k, N).float(), _chunk(v, N).float()
+        gc = _chunk(g.float(), N)
+        if self.use_qk_l2norm:
+            rq = torch.rsqrt(qf.pow(2).sum(-1, keepdim=True) + 1e-6)
+            rk = torch.rsqrt(kf.pow(2).sum(-1, keepdim=True) + 1e-6)
+            qn, kn = qf * (rq * scale), kf * rk
+        else:
+            qn, kn = qf * scale, kf
+        G = gc.cumsum(-1)
+        eG = torch.exp(G)
+        eR = torch.exp(G[..., -1:] - G)
+        idx = torch.arange(C, device=q.device)
+        lower = idx[:, None] >= idx[None, :]
+        strict = idx[:, None] > idx[None, :]
+        Dm = torch.exp((G[..., :, None] - G[..., None, :]).masked_fill(~lower, 0.0)) * lower
+        knT = kn.transpose(-1, -2)
+        # intra-chunk scores P = (qn kn^T) . D
+        Nm = d_P * Dm
+        dqn = Nm @ kn
+        dkn = Nm.transpose(-1, -2) @ qn
+        sP = Nm * (qn @ knT)                        # d_P . P
+        dG = sP.sum(-1) - sP.sum(-2)
+        # decayed queries / keys
+        dqn.addcmul_(d_qt, eG[..., None])
+        dG += (d_qt * qn).sum(-1) * eG
+        dkn.addcmul_(d_kt, eR[..., None])
+        t = (d_kt * kn).sum(-1) * eR
+        dG -= t
+        dG[..., -1] += t.sum(-1) + d_gl
+        dbeta = None
+        if self.gla:
+            dv = d_u
+        else:
+            bc = _chunk(beta.float(), N)
+            KK = kn @ knT
+            KD = KK * Dm * strict
+            A = bc[..., None] * KD
+            eye = torch.eye(C, device=q.device, dtype=torch.float32)
+            Tm = torch.linalg.solve_triangular(eye + A, eye.expand_as(A), upper=False)
+            TmT = Tm.transpose(-1, -2)
+            be = bc * eG
+            dbv, dbk = TmT @ d_u, TmT @ d_w
+            dT = d_u @ (vf * bc[..., None]).transpose(-1, -2) + d_w @ (kn * be[..., None]).transpose(-1, -2)
+            dA = -(TmT @ dT @ TmT) * strict
+            Mm = dA * Dm * bc[..., None]
+            dkn += Mm @ kn
+            dkn += Mm.transpose(-1, -2) @ kn
+            sA = dA * A
+            dG += sA.sum(-1) - sA.sum(-2)
+            dbeta = (dA * KD).sum(-1)
+            dv = dbv * bc[..., None]
+            dbeta += (dbv * vf).sum(-1)
+            dkn.addcmul_(dbk, be[..., None])
+            x = (dbk * kn).sum(-1) * eG
+            dbeta += x
+            dG += x * bc
+        dg = dG.flip(-1).cumsum(-1).flip(-1)
+        if self.use_qk_l2norm:
+            dq = (dqn - qn * ((qn * dqn).sum(-1, keepdim=True) / (scale * scale))) * (rq * scale)
+            dk = (dkn - kn * (kn * dkn).sum(-1, keepdim=True)) * rk
+        else:
+            dq, dk = dqn * scale, dkn
+        un = lambda t: _unchunk(t, B, H, T)  # noqa: E731
+        return un(dq), un(dk), un(dv), un(dg), (None if dbeta is None else un(dbeta))
+
     @staticmethod
     def _pack(f):
         wqT = torch.stack([f["w"].transpose(-1, -2), f["qt"].transpose(-1, -2)], dim=2).to(BF16).contiguous()
@@ -250,30 +322,24 @@ class GDNChunkCore(ScanCore):
             vn5, h5 = vnT.view(B, H, N, Dv, C), h_all.view(B, H, N, Dv, Dk)
             dvn5, dS5 = dvnT.view(B, H, N, Dv, C), dS_all.view(B, H, N, Dv, Dk)
             gl5 = glast.view(B, H, N)
-        # gradients of the per-chunk factors, then autograd through the preparation, per head group
+        # gradients of the per-chunk factors, then the hand-written backward of the preparation, per head group
         for hs in self._head_groups(B, T, H):
             nh = hs.stop - hs.start
-            leaves = [t[:, :, hs].detach().requires_grad_(True) if t is not None else None for t in (q, k, v, g, beta)]
-            with torch.enable_grad():
-                f = self._prep(*leaves)
             with torch.no_grad():
                 flat = lambda t: t[:, hs].reshape(B * nh, *t.shape[2:])  # noqa: E731
                 vnT_g, h_g, dvnT_g, dS_g = flat(vn5), flat(h5), flat(dvn5), flat(dS5)
                 do_c = _chunk(do[:, :, hs], N)               # [b*nh, N, C, Dv]
                 dvn = dvnT_g.transpose(-1, -2)
                 d_u = dvn.float()
-                d_w = -(dvn @ h_g).float()                   # [C, Dv] @ [Dv, Dk]
+                d_w = None if self.gla else -(dvn @ h_g).float()          # [C, Dv] @ [Dv, Dk]
                 d_qt = (do_c @ h_g).float()
                 d_P = torch.tril((do_c @ vnT_g).float())
                 d_kt = (vnT_g.transpose(-1, -2) @ dS_g).float()
                 d_gl = torch.exp(flat(gl5)) * (dS_g.float() * h_g.float()).sum((-1, -2))
-            pairs = [(f[n], d) for n, d in (("w", d_w), ("qt", d_qt), ("kt", d_kt), ("P", d_P), ("u", d_u),
-                                            ("glast", d_gl)) if f[n].requires_grad]   # gla mode: w is constant 0
-            torch.autograd.backward([p[0] for p in pairs], [p[1].to(p[0].dtype) for p in pairs])
-            with torch.no_grad():
-                dq[:, :, hs], dk[:, :, hs], dv[:, :, hs] = leaves[0].grad, leaves[1].grad, leaves[2].grad
-                dg[:, :, hs] = leaves[3].grad
+                sub = [t[:, :, hs] if t is not None else None for t in (q, k, v, g, beta)]
+                gq, gk, gv, gg, gb = self._prep_backward(*sub, d_w, d_qt, d_kt, d_P, d_u, d_gl)
+                dq[:, :, hs], dk[:, :, hs], dv[:, :, hs], dg[:, :, hs] = gq, gk, gv, gg
                 if dbeta is not None:
-                    dbeta[:, :, hs] = leaves[4].grad
-            del f, leaves
+                    dbeta[:, :, hs] = gb
+                del d_u, d_w, d_qt, d_P, d_kt, d_gl, gq, gk, gv, gg, gb
         return [dq, dk, dv, dg, dbeta], (None if dh0 is None else (dh0,))

@@ -186,3 +186,27 @@ def test_gka_chunk_parallel_solver_matches_sequential_reference():
     x, hT = chebyshev_chunk_parallel(qq, k, gk, num_iter=6, chunk_size=32)
     (x.sum() + hT.sum()).backward()
     assert torch.isfinite(qq.grad).all()
+
+
+def test_gdn_prep_manual_backward_matches_autograd():
+    from hybrid_model_factory_b200.ops.gdn_cuda import GDNChunkCore
+    torch.manual_seed(0)
+    for gla in (False, True):
+        for l2 in (True, False):
+            core = GDNChunkCore(scale=None, use_qk_l2norm=l2, gla=gla)
+            B, T, H, D = 2, 150, 3, 16
+            q, k, v = (torch.randn(B, T, H, D, requires_grad=True) for _ in range(3))
+            g = (-torch.rand(B, T, H) * 0.2).requires_grad_(True)
+            beta = torch.rand(B, T, H).requires_grad_(True)
+            f = core._prep(q, k, v, g, beta)
+            ups = {n: torch.randn_like(f[n]) for n in ("w", "qt", "kt", "P", "u", "glast")}
+            ups["P"] = torch.tril(ups["P"])
+            names = [n for n in ups if f[n].requires_grad]
+            ref = torch.autograd.grad([f[n] for n in names], [q, k, v, g, beta], [ups[n] for n in names],
+                                      allow_unused=True)
+            with torch.no_grad():
+                got = core._prep_backward(q, k, v, g, beta, ups["w"], ups["qt"], ups["kt"], ups["P"], ups["u"],
+                                          ups["glast"])
+            for a, b in zip(got, ref):
+                if b is not None:
+                    assert (a - b).abs().max() <= 1e-4 * (b.abs().max() + 1e-6)
