@@ -193,3 +193,122 @@ HMF_API int hmf_ssd_decode_packed(const void* xbc, long long ld_xbc, int x_off, 
   HMF_CHECK_CUDA(cudaGetLastError());
   return HMF_OK;
 }
+
+// ------------------------------------------------------------------------------------
+// Gated KalmaNet decode step, fully fused (one CTA per (request, head), 128 threads, head dim 128):
+//   q, k <- x / (|x| + eps);  k, v <- (beta + eps) k, v  (optional)
+//   H_kk <- e^{gk} H_kk + k k^T            (thread t keeps row t of the symmetric matrix in registers)
+//   lambda = ridge * |H_kk|_F ;  num_iter Chebyshev steps on (H_kk + lambda I) x = q
+//   q' = q + alpha (x - q)  (or x);  H_kv <- e^{g} H_kv + k v^T ;  o = scale * H_kv^T q'
+// States [slots, H, 128, 128] fp32, indexed through slots[r].
+// ------------------------------------------------------------------------------------
+namespace hmf {
+namespace decode_fused {
+
+__device__ __forceinline__ float block_sum_128(float v, float* red) {
+  v = warp_sum(v);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  return red[0] + red[1] + red[2] + red[3];
+}
+
+__global__ void __launch_bounds__(128)
+gka_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const bf16* __restrict__ v,
+                  const float* __restrict__ g, const float* __restrict__ beta, const float* __restrict__ alpha,
+                  float* __restrict__ h_kk, float* __restrict__ h_kv, const int* __restrict__ slots,
+                  bf16* __restrict__ o, int H, int Hq, int Hk, int Hv, float scale, float ridge, int num_iter,
+                  int use_gk) {
+  constexpr int D = 128;
+  const int r = blockIdx.x, h = blockIdx.y, t = threadIdx.x;
+  __shared__ float s_x[D], s_k[D], s_red[4];
+  const int hq = h / (H / Hq), hk = h / (H / Hk), hv = h / (H / Hv);
+  float qv = __bfloat162float(q[((size_t)r * Hq + hq) * D + t]);
+  float kv = __bfloat162float(k[((size_t)r * Hk + hk) * D + t]);
+  float vv = __bfloat162float(v[((size_t)r * Hv + hv) * D + t]);
+  const float eps = 1e-6f;
+  qv = qv / (sqrtf(block_sum_128(qv * qv, s_red)) + eps);
+  kv = kv / (sqrtf(block_sum_128(kv * kv, s_red)) + eps);
+  if (beta != nullptr) {
+    const float b = beta[(size_t)r * H + h] + eps;
+    kv *= b;
+    vv *= b;
+  }
+  const float gv = g[(size_t)r * H + h];
+  const size_t sbase = (((size_t)slots[r] * H + h) * D) * D;
+  // ---- covariance state update, row t in registers ----
+  s_k[t] = kv;
+  __syncthreads();
+  float row[D];
+  const float dkk = use_gk ? __expf(gv) : 1.f;
+  float* Hrow = h_kk + sbase + (size_t)t * D;
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < D; j += 4) {
+    float4 h4 = *reinterpret_cast<const float4*>(Hrow + j);
+    h4.x = fmaf(h4.x, dkk, kv * s_k[j]);
+    h4.y = fmaf(h4.y, dkk, kv * s_k[j + 1]);
+    h4.z = fmaf(h4.z, dkk, kv * s_k[j + 2]);
+    h4.w = fmaf(h4.w, dkk, kv * s_k[j + 3]);
+    *reinterpret_cast<float4*>(Hrow + j) = h4;
+    row[j] = h4.x; row[j + 1] = h4.y; row[j + 2] = h4.z; row[j + 3] = h4.w;
+    ss += h4.x * h4.x + h4.y * h4.y + h4.z * h4.z + h4.w * h4.w;
+  }
+  float xq = qv;     // value of q' for this feature
+  if (num_iter > 0) {
+    const float fro = sqrtf(block_sum_128(ss, s_red));
+    const float lam = ridge * fro;
+    float denom = 2.f * lam + fro;
+    if (denom == 0.f) denom = 1.f;
+    const float step = 2.f / denom;
+    const float c = (fro / denom * 0.5f) * (fro / denom * 0.5f);
+    float x_prev = 0.f, x = step * qv, omega = 2.f;
+    for (int it = 0; it < num_iter; ++it) {
+      __syncthreads();
+      s_x[t] = x;
+      __syncthreads();
+      float hx = 0.f;
+#pragma unroll
+      for (int j = 0; j < D; ++j) hx = fmaf(row[j], s_x[j], hx);
+      omega = 1.f / (1.f - c * omega);
+      const float upd = step * omega * (hx + lam * x - qv) + (omega - 1.f) * x_prev;
+      x_prev = x;
+      x = omega * x - upd;
+    }
+    xq = (alpha != nullptr) ? qv + alpha[(size_t)r * H + h] * (x - qv) : x;
+  }
+  // ---- key-value state update and read-out: thread t owns column t of H_kv [Dk, Dv] ----
+  __syncthreads();
+  s_x[t] = xq * scale;
+  __syncthreads();
+  const float dkv = __expf(gv);
+  float* S = h_kv + sbase;
+  float out = 0.f;
+#pragma unroll 8
+  for (int d = 0; d < D; ++d) {
+    const float sv = fmaf(S[(size_t)d * D + t], dkv, s_k[d] * vv);
+    S[(size_t)d * D + t] = sv;
+    out = fmaf(sv, s_x[d], out);
+  }
+  o[((size_t)r * H + h) * D + t] = __float2bfloat16(out);
+}
+
+}  // namespace decode_fused
+}  // namespace hmf
+
+// q [R, Hq, 128], k [R, Hk, 128], v [R, Hv, 128] bf16 (after the convolution); g [R, H] fp32 log decay;
+// beta / alpha [R, H] fp32 (already through the sigmoid) or null; states [slots, H, 128, 128] fp32.
+HMF_API int hmf_gka_decode(const void* q, const void* k, const void* v, const float* g, const float* beta,
+                           const float* alpha, float* h_kk, float* h_kv, const int* slots, void* o, int R, int H,
+                           int Hq, int Hk, int Hv, int D, float scale, float ridge, int num_iter, int use_gk,
+                           cudaStream_t st) {
+  HMF_REQUIRE(D == 128, "gka_decode: head dim %d unsupported (128)", D);
+  HMF_REQUIRE(H % Hq == 0 && H % Hk == 0 && H % Hv == 0, "gka_decode: head counts do not divide H=%d", H);
+  if (R == 0) return HMF_OK;
+  dim3 grid(R, H);
+  hmf::decode_fused::gka_decode_kernel<<<grid, 128, 0, st>>>(
+      (const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, g, beta, alpha, h_kk, h_kv, slots,
+      (__nv_bfloat16*)o, H, Hq, Hk, Hv, scale, ridge, num_iter, use_gk);
+  HMF_CHECK_CUDA(cudaGetLastError());
+  return HMF_OK;
+}

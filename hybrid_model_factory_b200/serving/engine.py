@@ -631,6 +631,22 @@ class ServingEngine:
         q, k = outs[0], outs[1]
         v = outs[2] if mx.use_v_conv else mx.v_proj(h)
         D = mx.head_dim
+        H = mx.expanded_num_heads
+        if self._cuda and D == 128 and h.dtype == torch.bfloat16 and mx.kv_proj_rank is None:
+            # fused kernel: norms, gates, covariance update, Chebyshev solve, GLA update and read-out
+            beta = torch.sigmoid(mx.b_proj(h)).float().contiguous() if mx.use_beta_gate else None
+            alpha = torch.sigmoid(mx.alpha_proj(h)).float().contiguous() if mx.use_alpha_connection else None
+            g = (-mx.A_log.float().exp() * F.softplus(mx.a_proj(h).float() + mx.dt_bias.float())).contiguous()
+            qc, kc_, vc_ = q.contiguous(), k.contiguous(), v.contiguous()
+            o = torch.empty(Rn, H, D, device=h.device, dtype=h.dtype)
+            _lib.check(_lib.kernels().hmf_gka_decode(
+                _lib.ptr(qc), _lib.ptr(kc_), _lib.ptr(vc_), _lib.ptr(g), _lib.ptr(beta), _lib.ptr(alpha),
+                _lib.ptr(e["state_kk"]), _lib.ptr(e["state"]), _lib.ptr(slots), _lib.ptr(o), c_int(Rn), c_int(H),
+                c_int(mx.num_q_heads), c_int(mx.num_k_heads), c_int(mx.num_v_heads), c_int(D), c_float(mx.gla_scale),
+                c_float(mx.ridge_strength), c_int(mx.num_iter), c_int(int(mx.use_forgetting_gate_kk)),
+                _lib.stream_ptr(h.device)), "gka_decode")
+            o = mx.o_norm(o, mx.g_proj(h).view(Rn, H, D)) if mx.use_gate else mx.o_norm(o)
+            return self._row_linear(o.reshape(Rn, -1), mx.o_proj)
         q = repeat_heads(q.reshape(Rn, 1, mx.num_q_heads, D), mx.num_q_groups)
         k, v = mx._expand_kv(k[:, None], v[:, None])
         eps = 1e-6

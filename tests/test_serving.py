@@ -191,7 +191,7 @@ def test_gdn_and_ssd_decode_kernels():
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("pattern", ["*-GDN", "M2-*"])
+@pytest.mark.parametrize("pattern", ["*-GDN", "M2-*", "GKA-*"])
 def test_engine_bf16_kernels_match_torch_path(pattern):
     """The kernel decode path and the PyTorch decode path of the engine agree on (almost) all greedy tokens."""
     torch.manual_seed(0)
