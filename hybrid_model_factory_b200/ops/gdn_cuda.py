@@ -51,6 +51,28 @@ def _chunk(x: torch.Tensor, N: int) -> torch.Tensor:
     return x.permute(*perm).reshape(B * H, N, C, *rest)
 
 
+def _chunkf(x: torch.Tensor, N: int) -> torch.Tensor:
+    """:func:`_chunk` fused with the conversion to fp32 (one pass over the data instead of two)."""
+    B, T, H = x.shape[:3]
+    if N * C != T:
+        return _chunk(x, N).float()
+    rest = x.shape[3:]
+    perm = (0, 3, 1, 2) + tuple(range(4, 4 + len(rest)))
+    return x.reshape(B, N, C, H, *rest).permute(*perm).float().reshape(B * H, N, C, *rest)
+
+
+def _unchunk_into(dst: torch.Tensor, x: torch.Tensor) -> None:
+    """``dst [B, T, H, ...]`` (any dtype / strides) <- ``x [B*H, N, C, ...]``; one strided pass when ``T = N*C``."""
+    B, T, H = dst.shape[:3]
+    N = x.shape[1]
+    rest = x.shape[3:]
+    if N * C != T:
+        dst.copy_(_unchunk(x, B, H, T))
+        return
+    perm = (0, 3, 1, 2) + tuple(range(4, 4 + len(rest)))
+    dst.unflatten(1, (N, C)).permute(*perm).copy_(x.reshape(B, H, N, C, *rest))
+
+
 def _unchunk(x: torch.Tensor, B: int, H: int, T: int) -> torch.Tensor:
     """Inverse of :func:`_chunk`: ``[B*H, N, C, ...] -> [B, T, H, ...]``."""
     N = x.shape[1]
@@ -58,6 +80,17 @@ def _unchunk(x: torch.Tensor, B: int, H: int, T: int) -> torch.Tensor:
     x = x.reshape(B, H, N, C, *rest)
     perm = (0, 2, 3, 1) + tuple(range(4, 4 + len(rest)))
     return x.permute(*perm).reshape(B, N * C, H, *rest)[:, :T]
+
+
+class _tf32_matmul:
+    """fp32 matmuls of the chunk-local backward on the tensor cores (TF32); restored on exit."""
+
+    def __enter__(self):
+        self.prev = torch.backends.cuda.matmul.allow_tf32
+        torch.backends.cuda.matmul.allow_tf32 = True
+
+    def __exit__(self, *exc):
+        torch.backends.cuda.matmul.allow_tf32 = self.prev
 
 
 class GDNChunkCore(ScanCore):
@@ -125,8 +158,8 @@ class GDNChunkCore(ScanCore):
         B, T, H, Dk = q.shape
         N = (T + C - 1) // C
         scale = Dk ** -0.5 if self.scale is None else self.scale
-        qf, kf, vf = _chunk(q, N).float(), _chunk(k, N).float(), _chunk(v, N).float()
-        gc = _chunk(g.float(), N)
+        qf, kf, vf = _chunkf(q, N), _chunkf(k, N), _chunkf(v, N)
+        gc = _chunkf(g, N)
         if self.use_qk_l2norm:
             rq = torch.rsqrt(qf.pow(2).sum(-1, keepdim=True) + 1e-6)
             rk = torch.rsqrt(kf.pow(2).sum(-1, keepdim=True) + 1e-6)
@@ -158,7 +191,7 @@ class GDNChunkCore(ScanCore):
         if self.gla:
             dv = d_u
         else:
-            bc = _chunk(beta.float(), N)
+            bc = _chunkf(beta, N)
             KK = kn @ knT
             KD = KK * Dm * strict
             A = bc[..., None] * KD
@@ -187,8 +220,7 @@ class GDNChunkCore(ScanCore):
             dk = (dkn - kn * (kn * dkn).sum(-1, keepdim=True)) * rk
         else:
             dq, dk = dqn * scale, dkn
-        un = lambda t: _unchunk(t, B, H, T)  # noqa: E731
-        return un(dq), un(dk), un(dv), un(dg), (None if dbeta is None else un(dbeta))
+        return dq, dk, dv, dg, dbeta          # chunk layout [B*h, N, C, .]; the caller scatters them
 
     @staticmethod
     def _pack(f):
@@ -337,9 +369,10 @@ class GDNChunkCore(ScanCore):
                 d_kt = (vnT_g.transpose(-1, -2) @ dS_g).float()
                 d_gl = torch.exp(flat(gl5)) * (dS_g.float() * h_g.float()).sum((-1, -2))
                 sub = [t[:, :, hs] if t is not None else None for t in (q, k, v, g, beta)]
-                gq, gk, gv, gg, gb = self._prep_backward(*sub, d_w, d_qt, d_kt, d_P, d_u, d_gl)
-                dq[:, :, hs], dk[:, :, hs], dv[:, :, hs], dg[:, :, hs] = gq, gk, gv, gg
-                if dbeta is not None:
-                    dbeta[:, :, hs] = gb
+                with _tf32_matmul():
+                    gq, gk, gv, gg, gb = self._prep_backward(*sub, d_w, d_qt, d_kt, d_P, d_u, d_gl)
+                for dst, src in ((dq, gq), (dk, gk), (dv, gv), (dg, gg), (dbeta, gb)):
+                    if dst is not None:
+                        _unchunk_into(dst[:, :, hs], src)
                 del d_u, d_w, d_qt, d_P, d_kt, d_gl, gq, gk, gv, gg, gb
         return [dq, dk, dv, dg, dbeta], (None if dh0 is None else (dh0,))
