@@ -99,6 +99,13 @@ def run_exp(args: Optional[Any] = None) -> Trainer:
     if stage == "hkd" or ft_args.hybrid_learnable_params:
         n = freeze_params_hybrid(model, ft_args.hybrid_learnable_params)
         info_rank0(logger, "trainable parameters: %d", n)
+    if ft_args.finetuning_type == "lora":
+        from .adapters import apply_lora
+        wrapped = apply_lora(model, ft_args.lora_rank, ft_args.lora_alpha, ft_args.lora_target)
+        info_rank0(logger, "LoRA adapters on %d linear layers", len(wrapped))
+    elif ft_args.finetuning_type == "freeze":
+        from .adapters import freeze_all_but_last
+        info_rank0(logger, "trainable parameters: %d", freeze_all_but_last(model, ft_args.freeze_trainable_layers))
     dataset = get_dataset(data_args, tokenizer, stage="pt" if stage in ("pt", "hkd") else "sft", sp_size=sp,
                           vocab_size=model.config.vocab_size, seed=run_args.seed)
     bsz = run_args.per_device_train_batch_size * run_args.gradient_accumulation_steps
@@ -106,6 +113,8 @@ def run_exp(args: Optional[Any] = None) -> Trainer:
     if hasattr(dataset, "__len__") and len(dataset) < (1 << 29):
         n_batches = (len(dataset) // sp) // (bsz * max(1, world // sp))
     targs = to_trainer_args(model_args, data_args, run_args, n_batches)
+    if ft_args.use_muon:
+        targs.optimizer = "muon"
     loss_fn = None
     teacher = None
     if stage == "hkd":
@@ -132,6 +141,9 @@ def run_exp(args: Optional[Any] = None) -> Trainer:
     if run_args.do_train:
         trainer.train(batches)
         final = os.path.join(run_args.output_dir, "final")
+        if ft_args.finetuning_type == "lora":
+            from .adapters import merge_lora
+            merge_lora(model)                     # the final checkpoint has the ordinary layout
         trainer.args.save_only_model = True
         trainer.save_checkpoint(final)
         if rank == 0:

@@ -213,3 +213,25 @@ def test_gdn_prep_manual_backward_matches_autograd():
                     dst = torch.empty_like(b)
                     _unchunk_into(dst, a)
                     assert (dst - b).abs().max() <= 1e-4 * (b.abs().max() + 1e-6)
+
+
+def test_lora_and_freeze_adapters():
+    from hybrid_model_factory_b200.train.adapters import apply_lora, freeze_all_but_last, merge_lora
+    torch.manual_seed(0)
+    model = build_model(_cfg("*-GDN"))
+    ids = torch.randint(0, 128, (2, 24))
+    base = model(ids).logits
+    wrapped = apply_lora(model, rank=4, target="q_proj,v_proj,down_proj")
+    assert wrapped and torch.allclose(model(ids).logits, base, atol=1e-6)        # B = 0: identical at start
+    trainable = [n for n, p in model.named_parameters() if p.requires_grad]
+    assert trainable and all("lora_" in n for n in trainable)
+    opt = torch.optim.SGD([p for p in model.parameters() if p.requires_grad], lr=0.5)
+    model(ids, labels=ids).loss.backward()
+    opt.step()
+    tuned = model(ids).logits
+    assert not torch.allclose(tuned, base, atol=1e-4)
+    assert merge_lora(model) == len(wrapped)
+    assert torch.allclose(model(ids).logits, tuned, atol=1e-4)                    # merged weights reproduce the adapter
+    n = freeze_all_but_last(model, 1)
+    assert 0 < n < sum(p.numel() for p in model.parameters())
+    assert all(not p.requires_grad for p in model.model.layers[0].parameters())
