@@ -2,7 +2,8 @@
 //
 //   y[M, N] = sum over ranks r of  x_r[M, Ks] . W_r[N, Ks]^T          (Ks = K / world, M <= 256)
 //
-// One kernel per rank, one CTA per 128 output columns:
+// One kernel per rank, one CTA per (128 output columns, K split); the K splits of a tile exist only to put more SMs
+// on the weight stream (a row-parallel shard has few 128-column tiles) and are summed in the same reduction:
 //   1. swap-AB tcgen05 GEMM: D^T[128 cols x Mpad] = W_tile[128 x Ks] . x^T   (A = weight rows and B = activations,
 //      both K-major, TMA -> shared memory ring -> tcgen05.mma, accumulator in tensor memory);
 //   2. the partial tile goes (bf16) to this rank's slot of a symmetric buffer; a release store raises the
@@ -33,16 +34,18 @@ constexpr int OFF_B = STAGES * A_BYTES;
 constexpr int OFF_BAR = OFF_B + STAGES * B_BYTES;
 constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
 constexpr int MAX_WORLD = 8;
+constexpr int MAX_SPLIT = 4;
+constexpr int FLAGS_PER_TILE = MAX_WORLD * MAX_SPLIT;
 constexpr uint64_t kPeerWaitNs = 2000000000ull;
 
 struct Params {
   bf16* y;                          // [M, N] local result
-  bf16* part[MAX_WORLD];            // every rank's partial buffers [2][max_m * max_n] as mapped here
-  unsigned int* flags[MAX_WORLD];   // every rank's flag array [max_tiles][MAX_WORLD]
+  bf16* part[MAX_WORLD];            // every rank's partial buffers [2][splits][M * N] as mapped here
+  unsigned int* flags[MAX_WORLD];   // every rank's flag array [max_tiles][MAX_WORLD * MAX_SPLIT]
   unsigned int* sync;               // local: [0] epoch of the last finished launch, [1] CTA ticket
   unsigned int* status;
   long long part_stride;            // elements between the two parity buffers
-  int M, N, Ks, Mpad, rank, world, tmem_cols;
+  int M, N, Ks, Mpad, rank, world, tmem_cols, splits;
 };
 
 __global__ void __launch_bounds__(192, 1)
@@ -57,9 +60,10 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const WaitCtx ctx{abort_flag, p.status};
-  const int tile = blockIdx.x;
+  const int tile = blockIdx.x / p.splits, ksp = blockIdx.x % p.splits;
   const int n0 = tile * BN;
-  const int k_steps = p.Ks / BK;
+  const int k_steps = p.Ks / p.splits / BK;
+  const int kb0 = ksp * k_steps;
   const unsigned int epoch = *reinterpret_cast<volatile unsigned int*>(p.sync) + 1u;
   const int parity = (int)(epoch & 1u);
 
@@ -90,8 +94,8 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
         const int s = i % STAGES;
         if (i >= STAGES) mbar_wait(&empty[s], ((i / STAGES) - 1) & 1, ctx, 0x10 + s);
         mbar_expect_tx(&full[s], bytes);
-        tma_load_2d(smem + OFF_A + s * A_BYTES, &tmW, &full[s], i * BK, n0);
-        tma_load_2d(smem + OFF_B + s * B_BYTES, &tmX, &full[s], i * BK, 0);
+        tma_load_2d(smem + OFF_A + s * A_BYTES, &tmW, &full[s], (kb0 + i) * BK, n0);
+        tma_load_2d(smem + OFF_B + s * B_BYTES, &tmX, &full[s], (kb0 + i) * BK, 0);
       }
     }
   } else if (warp == 1) {
@@ -116,7 +120,8 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
     const int row = quad * 32 + lane;                 // output column n0 + row
     const int et = threadIdx.x - 64;                  // 0..127
     const uint32_t lane_bits = (uint32_t)(quad * 32) << 16;
-    bf16* mine = p.part[p.rank] + (size_t)parity * p.part_stride;
+    const size_t split_elems = (size_t)p.M * p.N;
+    bf16* mine = p.part[p.rank] + (size_t)parity * p.part_stride + (size_t)ksp * split_elems;
     mbar_wait(acc_done, 0, ctx, 0x30);
     tc_fence_after();
     for (int m0 = 0; m0 < p.Mpad; m0 += 16) {
@@ -129,21 +134,25 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
     }
     __threadfence_system();
     asm volatile("bar.sync 1, 128;" ::: "memory");
-    if (et < p.world) st_release_sys(p.flags[et] + (size_t)tile * MAX_WORLD + p.rank, epoch);
     if (et < p.world)
-      wait_flag_sys(p.flags[p.rank] + (size_t)tile * MAX_WORLD + et, epoch, kPeerWaitNs, p.status, 0x40 + et);
+      st_release_sys(p.flags[et] + (size_t)tile * FLAGS_PER_TILE + p.rank * p.splits + ksp, epoch);
+    if (et < p.world * p.splits)
+      wait_flag_sys(p.flags[p.rank] + (size_t)tile * FLAGS_PER_TILE + et, epoch, kPeerWaitNs, p.status, 0x40 + et);
     asm volatile("bar.sync 1, 128;" ::: "memory");
-    // M x 128 tile = M x 16 chunks of 8 columns
-    const int chunks = p.M * (BN / 8);
+    // this CTA reduces the rows m = ksp, ksp + splits, ... of the tile: rows x 16 chunks of 8 columns, summed over
+    // every (rank, split) partial in a fixed order
+    const int rows = (p.M - ksp + p.splits - 1) / p.splits;
+    const int chunks = rows * (BN / 8);
     for (int c = et; c < chunks; c += 128) {
-      const int m = c / (BN / 8), cc = (c % (BN / 8)) * 8;
+      const int m = ksp + (c / (BN / 8)) * p.splits, cc = (c % (BN / 8)) * 8;
       const size_t off = (size_t)parity * p.part_stride + (size_t)m * p.N + n0 + cc;
       float acc[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-      for (int r = 0; r < p.world; ++r) {
+      for (int rs = 0; rs < p.world * p.splits; ++rs) {
+        const int r = rs / p.splits;
         uint4 u;
-        const bf16* src = p.part[r] + off;
+        const bf16* src = p.part[r] + off + (size_t)(rs % p.splits) * split_elems;
         asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
                      : "=r"(u.x), "=r"(u.y), "=r"(u.z), "=r"(u.w)
                      : "l"(src));
@@ -191,16 +200,19 @@ using namespace hmf::gar;
 // x [M, Ks] bf16 (row stride ldx), w [N, Ks] bf16 (row stride ldw), y [M, N] bf16.
 // part_ptrs / flag_ptrs: `world` device addresses (this process' mappings of every rank's buffers);
 // sync: two zero-initialised uint32 on this device, shared by every launch that uses the same buffers.
+// flag arrays hold max_tiles * 32 words; partial buffers 2 * part_stride elements with part_stride >= splits * M * N.
 HMF_API int hmf_gemm_allreduce(const void* x, const void* w, void* y, int M, int N, int Ks, long long ldx,
                                long long ldw, const unsigned long long* part_ptrs,
                                const unsigned long long* flag_ptrs, unsigned int* sync, long long part_stride,
-                               int max_tiles, int rank, int world, cudaStream_t st) {
+                               int max_tiles, int rank, int world, int splits, cudaStream_t st) {
+  HMF_REQUIRE(splits >= 1 && splits <= MAX_SPLIT && Ks % (splits * BK) == 0,
+              "gemm_allreduce: %d K splits do not divide Ks=%d into multiples of 64", splits, Ks);
   HMF_REQUIRE(M >= 1 && M <= MAX_M, "gemm_allreduce: M=%d out of range (1..%d)", M, MAX_M);
   HMF_REQUIRE(N % BN == 0 && Ks % BK == 0 && Ks > 0, "gemm_allreduce: N=%d must be a multiple of 128, Ks=%d of 64", N, Ks);
   HMF_REQUIRE(world >= 1 && world <= MAX_WORLD && rank >= 0 && rank < world, "gemm_allreduce: bad rank %d / world %d",
               rank, world);
   HMF_REQUIRE(N / BN <= max_tiles, "gemm_allreduce: %d tiles exceed the flag array (%d)", N / BN, max_tiles);
-  HMF_REQUIRE((long long)M * N <= part_stride, "gemm_allreduce: partial buffer too small");
+  HMF_REQUIRE((long long)M * N * splits <= part_stride, "gemm_allreduce: partial buffer too small");
   CUtensorMap tmW, tmX;
   int rc;
   const int Mpad = (M + 15) / 16 * 16;
@@ -220,11 +232,11 @@ HMF_API int hmf_gemm_allreduce(const void* x, const void* w, void* y, int M, int
   p.sync = sync;
   p.status = status_ptr();
   p.part_stride = part_stride;
-  p.M = M; p.N = N; p.Ks = Ks; p.Mpad = Mpad; p.rank = rank; p.world = world;
+  p.M = M; p.N = N; p.Ks = Ks; p.Mpad = Mpad; p.rank = rank; p.world = world; p.splits = splits;
   int cols = 32;
   while (cols < Mpad) cols *= 2;
   p.tmem_cols = cols;
-  gemm_allreduce_kernel<<<N / BN, 192, SMEM_BYTES, st>>>(tmW, tmX, p);
+  gemm_allreduce_kernel<<<(N / BN) * splits, 192, SMEM_BYTES, st>>>(tmW, tmX, p);
   HMF_CHECK_CUDA(cudaGetLastError());
   return HMF_OK;
 }

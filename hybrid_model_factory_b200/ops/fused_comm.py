@@ -23,10 +23,11 @@ class PeerGemmAllReduce:
     def __init__(self, group, max_m: int = 256, max_n: int = 8192, device=None):
         from ..parallel.peer import SymmetricWorkspace
         self.max_m, self.max_n = max_m, max_n
-        self.part_stride = max_m * max_n                       # elements per parity buffer
+        self.MAX_SPLIT = 4
+        self.part_stride = max_m * max_n * self.MAX_SPLIT      # elements per parity buffer (all K splits)
         part_bytes = 2 * self.part_stride * 2
         self.max_tiles = max_n // 128
-        flag_bytes = self.max_tiles * self.MAX_WORLD * 4
+        flag_bytes = self.max_tiles * self.MAX_WORLD * self.MAX_SPLIT * 4
         arr = ctypes.c_ulonglong * self.MAX_WORLD
         if group is None:       # single rank: ordinary device memory (the kernel then reduces over one partial)
             dev = device or torch.device("cuda", torch.cuda.current_device())
@@ -56,9 +57,15 @@ class PeerGemmAllReduce:
         M, Ks = x.shape
         N = weight.shape[0]
         y = torch.empty(M, N, device=x.device, dtype=torch.bfloat16)
+        # K splits: more CTAs on the weight stream when the shard has few 128-column tiles
+        tiles, splits = N // 128, 1
+        while (splits < self.MAX_SPLIT and tiles * splits * 2 <= 148 and Ks % (splits * 2 * 64) == 0
+               and Ks // (splits * 2) >= 256):
+            splits *= 2
         _lib.check(_lib.kernels().hmf_gemm_allreduce(
             _lib.ptr(x), _lib.ptr(weight), _lib.ptr(y), c_int(M), c_int(N), c_int(Ks), c_ll(x.stride(0)),
             c_ll(weight.stride(0)), self.part_ptrs, self.flag_ptrs, _lib.ptr(self.sync), c_ll(self.part_stride),
-            c_int(self.max_tiles), c_int(self.rank), c_int(self.world), _lib.stream_ptr(x.device)), "gemm_allreduce")
+            c_int(self.max_tiles), c_int(self.rank), c_int(self.world), c_int(splits), _lib.stream_ptr(x.device)),
+            "gemm_allreduce")
         self.calls += 1
         return y

@@ -178,3 +178,53 @@ def _ep_fused_worker(rank, world):
 @needs2
 def test_expert_parallel_fused_all_to_all_two_gpus():
     run_ranks(_ep_fused_worker, 2, backend="nccl", timeout=240)
+
+
+def _sp_model_worker(rank, world, pattern):
+    """A whole hybrid model under SP=2 (peer-memory state chain and K/V exchange) against the single-GPU run."""
+    import copy
+    from hybrid_model_factory_b200.models.configuration import HybridConfig
+    from hybrid_model_factory_b200.models.modeling_hybrid import build_model
+    from hybrid_model_factory_b200.ops import _lib
+    from hybrid_model_factory_b200.parallel.peer import enable_peer_kv, enable_peer_transport
+    from hybrid_model_factory_b200.parallel.sp import (init_sp_group, set_sequence_parallel_group_recursive, zigzag_split)
+    dev = torch.device("cuda", rank)
+    torch.manual_seed(0)
+    cfg = HybridConfig("hybrid_qwen3", vocab_size=1024, hidden_size=512, intermediate_size=1024,
+                       num_hidden_layers=len(pattern.split("-")), num_attention_heads=4, num_key_value_heads=2,
+                       head_dim=128, hybrid_override_pattern=pattern, max_position_embeddings=8192,
+                       swa_config={"window_size": 256},
+                       bmojo_config={"window_size": 128, "ssm_mixer": "gdn", "tie_attn_weights": False})
+    ref = build_model(cfg).to(dev, torch.bfloat16)
+    model = copy.deepcopy(ref)
+    g = torch.Generator().manual_seed(1)
+    T = 2048
+    ids = torch.randint(0, 1024, (1, T), generator=g).to(dev)
+    labels = torch.roll(ids, -1, dims=1)
+    labels[:, -1] = -100
+    out_ref = ref(ids, labels=labels, labels_shifted=True)
+    out_ref.loss.backward()
+    sp = init_sp_group(world)
+    assert enable_peer_transport(sp) and enable_peer_kv(sp, 16 << 20)
+    set_sequence_parallel_group_recursive(model, sp)
+    pos = torch.arange(T, device=dev)[None]
+    l_ids, l_lab, l_pos = (zigzag_split(t, rank, world) for t in (ids, labels, pos))
+    out = model(l_ids, labels=l_lab, position_ids=l_pos, labels_shifted=True)
+    out.loss.backward()
+    torch.cuda.synchronize()
+    _lib.assert_status_ok()
+    assert abs(out.loss.item() - out_ref.loss.item()) < 3.5e-2, (out.loss.item(), out_ref.loss.item())
+    worst = 0.0
+    for (n, p), (_, q) in zip(model.named_parameters(), ref.named_parameters()):
+        gsum = p.grad.float().clone() if p.grad is not None else torch.zeros_like(p, dtype=torch.float32)
+        dist.all_reduce(gsum)
+        denom = q.grad.float().norm() + 1e-6
+        worst = max(worst, float((gsum - q.grad.float()).norm() / denom))
+    assert worst < 0.1, worst
+    dist.barrier()
+
+
+@needs2
+@pytest.mark.parametrize("pattern", ["*-GDN", "M2-GKA", "SWA-BMF"])
+def test_sp_model_two_gpus(pattern):
+    run_ranks(_sp_model_worker, 2, pattern, backend="nccl", timeout=300)
