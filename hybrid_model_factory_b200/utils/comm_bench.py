@@ -1,0 +1,149 @@
+"""Micro-benchmarks of the fused compute + communication kernels against their NCCL formulations.
+
+    torchrun --nproc-per-node N -m hybrid_model_factory_b200.utils.comm_bench [gemm_ar] [cp_attn] [moe]
+
+Every number is a CUDA-event time on the launching stream after warm-up, maximum over ranks, inputs larger than L2
+or an L2 flush between iterations.  Rank 0 prints one line per case with the roofline bound
+``max(FLOPs / measured GEMM peak, NVLink bytes / 770 GB/s)``.
+"""
+from __future__ import annotations
+
+import json
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+import torch.nn.functional as F
+
+LINK_GBS = 770.0     # measured peer copy bandwidth per direction per GPU on this pool
+
+
+def _peaks():
+    here = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    try:
+        with open(os.path.join(here, "MEASURED_PEAKS.json")) as f:
+            p = json.load(f)
+        return p["bf16_tflops"], p["hbm_gbs"], "measured"
+    except Exception:
+        return 1590.0, 6650.0, "fallback"
+
+
+_flush = None
+
+
+def timed(fn, iters=10, warmup=3, flush=True):
+    global _flush
+    if _flush is None:
+        _flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    dist.barrier()
+    total = 0.0
+    for _ in range(iters):
+        if flush:
+            _flush.zero_()
+        dist.barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        total += a.elapsed_time(b)
+    t = torch.tensor([total / iters], device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t)
+
+
+def report(name, ms_fused, ms_nccl, flops, link_bytes):
+    tf, _, src = _peaks()
+    bound_ms = max(flops / (tf * 1e9), link_bytes / (LINK_GBS * 1e6))
+    if dist.get_rank() == 0:
+        print(f"{name}: fused {ms_fused * 1e3:.1f} us, NCCL formulation {ms_nccl * 1e3:.1f} us "
+              f"({ms_nccl / ms_fused:.2f}x), roofline bound {bound_ms * 1e3:.1f} us "
+              f"({bound_ms / ms_fused:.2f} of {src} bound)", flush=True)
+
+
+def bench_gemm_ar():
+    from ..parallel.tp import TPContext
+    tp = TPContext(dist.group.WORLD)
+    tp.enable_fused_gemm(max_m=256, max_n=4096)
+    n = tp.size
+    for M, N, K in ((64, 4096, 4096), (64, 4096, 12288), (16, 4096, 12288), (256, 4096, 4096)):
+        Ks = K // n
+        x = torch.randn(M, Ks, device="cuda").bfloat16()
+        w = (torch.randn(N, Ks, device="cuda") * 0.02).bfloat16()
+
+        def nccl():
+            y = F.linear(x, w)
+            dist.all_reduce(y)
+            return y
+        fused = timed(lambda: tp.linear_allreduce(x, w), flush=False)
+        base = timed(nccl, flush=False)
+        # every rank reads the other ranks' bf16 partials of the whole [M, N] result once
+        report(f"gemm+all-reduce M={M} N={N} K={K}/{n}", fused, base, 2.0 * M * N * Ks, (n - 1) * M * N * 2.0)
+
+
+def bench_cp_attn():
+    from ..parallel.cp_attention import cp_attention
+    from ..parallel.peer import enable_peer_kv
+    from ..parallel.sp import init_sp_group
+    n = dist.get_world_size()
+    sp = init_sp_group(n)
+    T, H, Hkv, D = int(os.environ.get("HMF_CP_TOKENS", 131072)) // n, 32, 8, 128
+    q = torch.randn(1, T, H, D, device="cuda").bfloat16()
+    k = torch.randn(1, T, Hkv, D, device="cuda").bfloat16()
+    v = torch.randn(1, T, Hkv, D, device="cuda").bfloat16()
+    with torch.no_grad():
+        base = timed(lambda: cp_attention(q, k, v, sp), iters=5)
+        enable_peer_kv(sp, k.numel() * 2)
+        fused = timed(lambda: cp_attention(q, k, v, sp), iters=5)
+    Tg = T * n
+    flops = 4.0 * Tg * Tg / 2 * H * D / n                       # causal, this rank's share (zig-zag balanced)
+    link = (n - 1) / n * Tg * Hkv * D * 2 * 2.0                  # remote K and V read once
+    report(f"context-parallel attention fwd, {Tg} tokens over {n} GPUs", fused, base, flops, link)
+
+
+def bench_moe():
+    from ..ops import reference as R
+    from ..parallel.ep import EPContext, ep_experts_forward
+    from ..parallel.ep_fused import FusedExpertParallel
+    n, rank = dist.get_world_size(), dist.get_rank()
+    E, Dm, Fi, T, k = 64, 2048, 768, 8192, 8
+    per = E // n
+    g = torch.Generator().manual_seed(0)
+    wgu = (torch.randn(per, 2 * Fi, Dm, generator=g) * 0.02).bfloat16().cuda()
+    wd = (torch.randn(per, Dm, Fi, generator=g) * 0.02).bfloat16().cuda()
+    x = torch.randn(T, Dm, device="cuda").bfloat16()
+    w, idx = R.moe_router(torch.randn(T, E, device="cuda"), k)
+    ep = EPContext.from_group(dist.group.WORLD)
+    fe = FusedExpertParallel(dist.group.WORLD, per, Dm, Fi, max_send_rows=T * k, capacity_rows=2 * T * k)
+    with torch.no_grad():
+        base = timed(lambda: ep_experts_forward(x, wgu, wd, w.to(x.dtype), idx, ep), iters=5)
+        fused = timed(lambda: fe.forward(x, w, idx, wgu, wd), iters=5)
+    flops = 2.0 * T * k * Dm * Fi * 3
+    link = (n - 1) / n * T * k * Dm * 2 * 2.0                     # dispatch + combine
+    report(f"MoE layer E={E} top-{k} T={T} Dm={Dm} F={Fi}, EP={n}", fused, base, flops, link)
+
+
+CASES = {"gemm_ar": bench_gemm_ar, "cp_attn": bench_cp_attn, "moe": bench_moe}
+
+
+def main(argv=None) -> int:
+    names = [a for a in (argv if argv is not None else sys.argv[1:]) if a in CASES] or list(CASES)
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    for name in names:
+        CASES[name]()
+    from ..ops import _lib
+    torch.cuda.synchronize()
+    if dist.get_rank() == 0:
+        print("kernel status", _lib.read_status())
+    dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())
