@@ -77,9 +77,12 @@ class Trainer:
             # recurrent states travel from inside the scan kernels over peer memory (NCCL send/recv otherwise)
             from ..parallel.peer import enable_peer_kv, enable_peer_transport
             enable_peer_transport(self.sp)
-            kv_bytes = int(os.environ.get("HMF_SP_PEER_KV_MB", "256")) << 20
+            # Opt-in: the attention forward can pull remote K/V tiles itself (no all-gather).  Every query tile then
+            # re-reads its remote tiles over NVLink, which only pays for short contexts; measured 6x slower than the
+            # NCCL gather at 128K tokens over 2 GPUs, so the default stays off.
+            kv_bytes = int(os.environ.get("HMF_SP_PEER_KV_MB", "0")) << 20
             if kv_bytes > 0 and self.sp.mode != "ulysses":
-                enable_peer_kv(self.sp, kv_bytes)       # attention pulls remote K/V tiles inside its forward kernel
+                enable_peer_kv(self.sp, kv_bytes)
         set_sequence_parallel_group_recursive(model, self.sp)
         self.dp_size = self.world // sp_size
         if not args.disable_gradient_checkpointing and hasattr(model, "gradient_checkpointing_enable"):

@@ -32,6 +32,34 @@ def _peaks():
 _flush = None
 
 
+def timed_graph(fn, reps=20, iters=5):
+    """Small ops: ``reps`` calls captured in one CUDA graph, replayed ``iters`` times; returns ms per call (max over
+    ranks).  Removes host launch latency from the measurement."""
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    dist.barrier()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        for _ in range(reps):
+            fn()
+    total = 0.0
+    for _ in range(iters):
+        dist.barrier()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        graph.replay()
+        b.record()
+        torch.cuda.synchronize()
+        total += a.elapsed_time(b)
+    t = torch.tensor([total / iters / reps], device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t)
+
+
 def timed(fn, iters=10, warmup=3, flush=True):
     global _flush
     if _flush is None:
@@ -79,8 +107,8 @@ def bench_gemm_ar():
             y = F.linear(x, w)
             dist.all_reduce(y)
             return y
-        fused = timed(lambda: tp.linear_allreduce(x, w), flush=False)
-        base = timed(nccl, flush=False)
+        fused = timed_graph(lambda: tp.linear_allreduce(x, w))
+        base = timed_graph(nccl)
         # every rank reads the other ranks' bf16 partials of the whole [M, N] result once
         report(f"gemm+all-reduce M={M} N={N} K={K}/{n}", fused, base, 2.0 * M * N * Ks, (n - 1) * M * N * 2.0)
 

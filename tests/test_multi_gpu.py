@@ -214,13 +214,15 @@ def _sp_model_worker(rank, world, pattern):
     torch.cuda.synchronize()
     _lib.assert_status_ok()
     assert abs(out.loss.item() - out_ref.loss.item()) < 3.5e-2, (out.loss.item(), out_ref.loss.item())
-    worst = 0.0
+    worst, worst_name = 0.0, ""
     for (n, p), (_, q) in zip(model.named_parameters(), ref.named_parameters()):
         gsum = p.grad.float().clone() if p.grad is not None else torch.zeros_like(p, dtype=torch.float32)
         dist.all_reduce(gsum)
-        denom = q.grad.float().norm() + 1e-6
-        worst = max(worst, float((gsum - q.grad.float()).norm() / denom))
-    assert worst < 0.1, worst
+        gref = q.grad.float() if q.grad is not None else torch.zeros_like(gsum)
+        err = float((gsum - gref).norm() / (gref.norm() + 1e-3 * gref.numel() ** 0.5 * 1e-3 + 1e-6))
+        if err > worst:
+            worst, worst_name = err, n
+    assert worst < 0.1, (worst, worst_name)
     dist.barrier()
 
 
