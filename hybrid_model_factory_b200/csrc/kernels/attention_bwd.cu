@@ -39,7 +39,9 @@ struct Params {
 // ------------------------------------------------------------------------------------
 // delta = rowsum(dO * O); 16 lanes per row of D <= 128 (D % 8 == 0)
 // ------------------------------------------------------------------------------------
-__global__ void delta_kernel(const bf16* __restrict__ o, const bf16* __restrict__ d_o,
+// With a gradient on the log-sum-exp output (its derivative w.r.t. the scores is P) the score gradient is
+// dS = P o (dP - delta + dlse); it enters here as delta - dlse, so the main kernels are unchanged.
+__global__ void delta_kernel(const bf16* __restrict__ o, const bf16* __restrict__ d_o, const float* __restrict__ dlse,
                              float* __restrict__ delta, int B, int T, int H, int D) {
   const int lanes = D / 8;  // 8 or 16
   const int rows_per_warp = 32 / lanes;
@@ -64,7 +66,8 @@ __global__ void delta_kernel(const bf16* __restrict__ o, const bf16* __restrict_
   if (row < total && (lane % lanes) == 0) {
     const long long h = row % H, bt = row / H;
     const long long t = bt % T, b = bt / T;
-    delta[(b * H + h) * T + t] = s;
+    const long long idx = (b * H + h) * T + t;
+    delta[idx] = dlse != nullptr ? s - dlse[idx] : s;
   }
 }
 
@@ -801,9 +804,11 @@ static int launch_all(const void* q, const void* k, const void* v, const void* d
 }  // namespace hmf
 
 // Gradients of hmf_attention_fwd.  o, d_o, dq: [B,Tq,Hq,D] contiguous; dk, dv: [B,Tk,Hkv,D]
-// contiguous; lse from the forward pass; delta: scratch [B,Hq,Tq] fp32 provided by the caller.
+// contiguous; lse from the forward pass; dlse: optional gradient of the lse output [B,Hq,Tq] fp32 (null = none);
+// delta: scratch [B,Hq,Tq] fp32 provided by the caller.
 HMF_API int hmf_attention_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o,
-                              const float* lse, float* delta, void* dq, void* dk, void* dv, const int* q_pos,
+                              const float* lse, const float* dlse, float* delta, void* dq, void* dk, void* dv,
+                              const int* q_pos,
                               int B, int Tq, int Tk, int Hq, int Hkv, int D, long long q_sb, long long q_st,
                               long long q_sh, long long k_sb, long long k_st, long long k_sh, long long v_sb,
                               long long v_st, long long v_sh, int lo, int hi, int q_off, float scale,
@@ -819,7 +824,7 @@ HMF_API int hmf_attention_bwd(const void* q, const void* k, const void* v, const
     const int rpw = 32 / (D / 8);
     const long long warps = (rows + rpw - 1) / rpw;
     const long long blocks = (warps + 7) / 8;
-    delta_kernel<<<(unsigned)blocks, 256, 0, stream>>>((const bf16*)o, (const bf16*)d_o, delta, B, Tq, Hq, D);
+    delta_kernel<<<(unsigned)blocks, 256, 0, stream>>>((const bf16*)o, (const bf16*)d_o, dlse, delta, B, Tq, Hq, D);
     HMF_CHECK_CUDA(cudaGetLastError());
   }
   Params p;

@@ -390,7 +390,7 @@ def attention_fwd_raw(q: Tensor, k: Tensor, v: Tensor, scale: float, lo: int, hi
     return o, lse
 
 
-def attention_bwd_raw(q, k, v, o, do, lse, scale, lo, hi, q_off, q_pos=None):
+def attention_bwd_raw(q, k, v, o, do, lse, scale, lo, hi, q_off, q_pos=None, dlse=None):
     """Launches delta + dQ + dK/dV kernels; returns ``(dq, dk, dv)`` (bf16, contiguous)."""
     B, Tq, Hq, D = q.shape
     Tk, Hkv = k.shape[1], k.shape[2]
@@ -404,8 +404,10 @@ def attention_bwd_raw(q, k, v, o, do, lse, scale, lo, hi, q_off, q_pos=None):
     delta = torch.empty(B, Hq, Tq, device=q.device, dtype=torch.float32)
     if q_pos is not None:
         q_pos = q_pos.to(torch.int32).contiguous()
+    if dlse is not None:
+        dlse = dlse.float().contiguous()
     _lib.check(_K().hmf_attention_bwd(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(o), _lib.ptr(do), _lib.ptr(lse),
-                                      _lib.ptr(delta), _lib.ptr(dq), _lib.ptr(dk), _lib.ptr(dv), _lib.ptr(q_pos),
+                                      _lib.ptr(dlse), _lib.ptr(delta), _lib.ptr(dq), _lib.ptr(dk), _lib.ptr(dv), _lib.ptr(q_pos),
                                       c_int(B), c_int(Tq), c_int(Tk), c_int(Hq), c_int(Hkv), c_int(D),
                                       *_bthd_strides(q), *_bthd_strides(k), *_bthd_strides(v), c_int(lo), c_int(hi),
                                       c_int(q_off), c_float(scale), _st(q)), "attention_bwd")
@@ -419,14 +421,16 @@ class _Attention(torch.autograd.Function):
         o, lse = attention_fwd_raw(q, k, v, scale, lo, hi, q_off, q_pos)
         ctx.save_for_backward(q, k, v, o, lse, q_pos)
         ctx.cfg = (scale, lo, hi, q_off)
-        ctx.mark_non_differentiable(lse)
+        ctx.set_materialize_grads(False)      # the lse output usually carries no gradient
         return o, lse
 
     @staticmethod
-    def backward(ctx, do, _dlse):
+    def backward(ctx, do, dlse):
         q, k, v, o, lse, q_pos = ctx.saved_tensors
         scale, lo, hi, q_off = ctx.cfg
-        dq, dk, dv = attention_bwd_raw(q, k, v, o, do, lse, scale, lo, hi, q_off, q_pos)
+        if do is None:
+            do = torch.zeros_like(o)
+        dq, dk, dv = attention_bwd_raw(q, k, v, o, do, lse, scale, lo, hi, q_off, q_pos, dlse)
         return dq, dk, dv, None, None, None, None, None
 
 
@@ -438,14 +442,16 @@ class _AttentionFromSaved(torch.autograd.Function):
     def forward(ctx, q, k, v, o, lse, scale, lo, hi, q_off, q_pos):
         ctx.save_for_backward(q, k, v, o, lse, q_pos)
         ctx.cfg = (scale, lo, hi, q_off)
-        ctx.mark_non_differentiable(lse)
+        ctx.set_materialize_grads(False)
         return o.view_as(o), lse.view_as(lse)
 
     @staticmethod
-    def backward(ctx, do, _dlse):
+    def backward(ctx, do, dlse):
         q, k, v, o, lse, q_pos = ctx.saved_tensors
         scale, lo, hi, q_off = ctx.cfg
-        dq, dk, dv = attention_bwd_raw(q, k, v, o, do, lse, scale, lo, hi, q_off, q_pos)
+        if do is None:
+            do = torch.zeros_like(o)
+        dq, dk, dv = attention_bwd_raw(q, k, v, o, do, lse, scale, lo, hi, q_off, q_pos, dlse)
         return dq, dk, dv, None, None, None, None, None, None, None
 
 
