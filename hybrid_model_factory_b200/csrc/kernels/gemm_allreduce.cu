@@ -132,7 +132,7 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
       for (int j = 0; j < 16; ++j)
         if (m0 + j < p.M) mine[(size_t)(m0 + j) * p.N + n0 + row] = __float2bfloat16(__uint_as_float(v[j]));
     }
-    __threadfence_system();
+    // the CTA barrier orders every thread's partial stores before the (cumulative) system-scope release stores
     asm volatile("bar.sync 1, 128;" ::: "memory");
     if (et < p.world)
       st_release_sys(p.flags[et] + (size_t)tile * FLAGS_PER_TILE + p.rank * p.splits + ksp, epoch);
