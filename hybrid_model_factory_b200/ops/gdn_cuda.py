@@ -31,6 +31,7 @@ BF16 = torch.bfloat16
 C = 64
 # debugging aid: evaluate the chunk preparation with batched PyTorch ops instead of the CUDA kernel
 _FORCE_TORCH_PREP = os.environ.get("HMF_GDN_TORCH_PREP", "0") == "1"
+_USE_BWD_KERNEL = os.environ.get("HMF_GDN_BWD_KERNEL", "1") == "1"
 
 
 def available() -> bool:
@@ -354,6 +355,41 @@ class GDNChunkCore(ScanCore):
             vn5, h5 = vnT.view(B, H, N, Dv, C), h_all.view(B, H, N, Dv, Dk)
             dvn5, dS5 = dvnT.view(B, H, N, Dv, C), dS_all.view(B, H, N, Dv, Dk)
             gl5 = glast.view(B, H, N)
+        if hasattr(_lib.kernels(), "hmf_gdn_prep_bwd") and not _FORCE_TORCH_PREP and _USE_BWD_KERNEL:
+            # factor gradients by four batched GEMMs, then one kernel for the whole chunk-local backward
+            with torch.no_grad():
+                vnT_g, h_g = vnT.view(B * H, N, Dv, C), h_all.view(B * H, N, Dv, Dk)
+                dS_g = dS_all.view(B * H, N, Dv, Dk)
+                do_c = _chunk(do, N)                             # [BH, N, C, Dv]
+                dvn = dvnT.transpose(-1, -2)
+                d_w = None if self.gla else (dvn @ h_g).neg_()   # [C, Dv] @ [Dv, Dk]
+                d_qt = do_c @ h_g
+                d_P = (do_c @ vnT_g).float()
+                d_kt = vnT_g.transpose(-1, -2) @ dS_g
+                d_gl = torch.exp(glast.view(B * H, N)) * torch.einsum("bnij,bnij->bn", dS_g, h_g).float()
+                del do_c, dS_g
+                if not (dq.is_contiguous() and dk.is_contiguous() and dv.is_contiguous()):
+                    dq, dk, dv = (torch.empty(t.shape, device=t.device, dtype=t.dtype) for t in (q, k, v))
+                qq, kk, vv = (t if (t.stride(3) == 1 and all(s_ % 4 == 0 for s_ in t.stride()[:3])) else t.contiguous()
+                              for t in (q, k, v))
+                g32 = g.float().contiguous()
+                b32 = None if self.gla else beta.float().contiguous()
+                dg32 = torch.empty(B, T, H, device=q.device, dtype=torch.float32)
+                db32 = None if self.gla else torch.empty(B, T, H, device=q.device, dtype=torch.float32)
+                scale = Dk ** -0.5 if self.scale is None else self.scale
+                ll = ctypes.c_longlong
+                rc = _lib.kernels().hmf_gdn_prep_bwd(
+                    _lib.ptr(qq), _lib.ptr(kk), _lib.ptr(vv), _lib.ptr(g32), _lib.ptr(b32), _lib.ptr(dvnT), _lib.ptr(d_w),
+                    _lib.ptr(d_qt), _lib.ptr(d_kt), _lib.ptr(d_P), _lib.ptr(d_gl), _lib.ptr(dq), _lib.ptr(dk), _lib.ptr(dv),
+                    _lib.ptr(dg32), _lib.ptr(db32), c_int(B), c_int(T), c_int(H), c_int(N),
+                    ll(qq.stride(0)), ll(qq.stride(1)), ll(qq.stride(2)), ll(kk.stride(0)), ll(kk.stride(1)),
+                    ll(kk.stride(2)), ll(vv.stride(0)), ll(vv.stride(1)), ll(vv.stride(2)), ctypes.c_float(scale),
+                    c_int(int(self.use_qk_l2norm)), c_int(int(self.gla)), _lib.stream_ptr(q.device))
+                _lib.check(rc, "hmf_gdn_prep_bwd")
+                dg.copy_(dg32)
+                if dbeta is not None:
+                    dbeta.copy_(db32)
+            return [dq, dk, dv, dg, dbeta], (None if dh0 is None else (dh0,))
         # gradients of the per-chunk factors, then the hand-written backward of the preparation, per head group
         for hs in self._head_groups(B, T, H):
             nh = hs.stop - hs.start
