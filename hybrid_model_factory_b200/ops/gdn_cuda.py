@@ -366,7 +366,7 @@ class GDNChunkCore(ScanCore):
                 d_qt = do_c @ h_g
                 d_P = (do_c @ vnT_g).float()
                 d_kt = vnT_g.transpose(-1, -2) @ dS_g
-                d_gl = torch.exp(glast.view(B * H, N)) * torch.einsum("bnij,bnij->bn", dS_g, h_g).float()
+                d_gl = torch.exp(glast.view(B * H, N)) * (dS_g * h_g).sum((-1, -2), dtype=torch.float32)
                 del do_c, dS_g
                 if not (dq.is_contiguous() and dk.is_contiguous() and dv.is_contiguous()):
                     dq, dk, dv = (torch.empty(t.shape, device=t.device, dtype=t.dtype) for t in (q, k, v))
