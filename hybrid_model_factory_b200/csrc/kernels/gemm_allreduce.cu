@@ -143,33 +143,64 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
     // every (rank, split) partial in a fixed order
     const int rows = (p.M - ksp + p.splits - 1) / p.splits;
     const int chunks = rows * (BN / 8);
-    for (int c = et; c < chunks; c += 128) {
-      const int m = ksp + (c / (BN / 8)) * p.splits, cc = (c % (BN / 8)) * 8;
-      const size_t off = (size_t)parity * p.part_stride + (size_t)m * p.N + n0 + cc;
-      float acc[8];
+    // Remote loads take microseconds, so they go out in batches before the first use: 8 (rank, split) partials of
+    // CU chunks at a time.  The sums are still taken in (rank, split) order, so every rank gets the same bits.
+    constexpr int CU = 2;
+    const int total = p.world * p.splits;
+    for (int c0 = et; c0 < chunks; c0 += 128 * CU) {
+      float acc[CU][8];
+      size_t off[CU];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-      for (int rs = 0; rs < p.world * p.splits; ++rs) {
-        const int r = rs / p.splits;
-        uint4 u;
-        const bf16* src = p.part[r] + off + (size_t)(rs % p.splits) * split_elems;
-        asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
-                     : "=r"(u.x), "=r"(u.y), "=r"(u.z), "=r"(u.w)
-                     : "l"(src));
-        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&u);
+      for (int q = 0; q < CU; ++q) {
+        const int c = c0 + q * 128;
+        const int m = ksp + (c / (BN / 8)) * p.splits, cc = (c % (BN / 8)) * 8;
+        off[q] = (size_t)m * p.N + n0 + cc;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float2 f = __bfloat1622float2(h2[j]);
-          acc[2 * j] += f.x;
-          acc[2 * j + 1] += f.y;
+        for (int j = 0; j < 8; ++j) acc[q][j] = 0.f;
+      }
+      for (int rs0 = 0; rs0 < total; rs0 += 8) {
+        uint4 u[CU][8];
+#pragma unroll
+        for (int q = 0; q < CU; ++q) {
+#pragma unroll
+          for (int b = 0; b < 8; ++b) {
+            const int rs = rs0 + b;
+            if (rs < total && c0 + q * 128 < chunks) {
+              const bf16* src = p.part[rs / p.splits] + (size_t)parity * p.part_stride + off[q] +
+                                (size_t)(rs % p.splits) * split_elems;
+              asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                           : "=r"(u[q][b].x), "=r"(u[q][b].y), "=r"(u[q][b].z), "=r"(u[q][b].w)
+                           : "l"(src));
+            } else {
+              u[q][b] = make_uint4(0u, 0u, 0u, 0u);
+            }
+          }
+        }
+#pragma unroll
+        for (int q = 0; q < CU; ++q) {
+#pragma unroll
+          for (int b = 0; b < 8; ++b) {
+            const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&u[q][b]);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 f = __bfloat1622float2(h2[j]);
+              acc[q][2 * j] += f.x;
+              acc[q][2 * j + 1] += f.y;
+            }
+          }
         }
       }
-      uint4 o;
-      o.x = pack_bf16x2(acc[0], acc[1]);
-      o.y = pack_bf16x2(acc[2], acc[3]);
-      o.z = pack_bf16x2(acc[4], acc[5]);
-      o.w = pack_bf16x2(acc[6], acc[7]);
-      *reinterpret_cast<uint4*>(p.y + (size_t)m * p.N + n0 + cc) = o;
+#pragma unroll
+      for (int q = 0; q < CU; ++q) {
+        if (c0 + q * 128 < chunks) {
+          uint4 o;
+          o.x = pack_bf16x2(acc[q][0], acc[q][1]);
+          o.y = pack_bf16x2(acc[q][2], acc[q][3]);
+          o.z = pack_bf16x2(acc[q][4], acc[q][5]);
+          o.w = pack_bf16x2(acc[q][6], acc[q][7]);
+          *reinterpret_cast<uint4*>(p.y + off[q]) = o;
+        }
+      }
     }
   }
 

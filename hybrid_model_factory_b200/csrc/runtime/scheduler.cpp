@@ -83,6 +83,7 @@ class Scheduler {
       ++n_out; --budget;
     }
     // 2. running prefills continue (chunked)
+    int prefill_used = 0;
     for (int64_t id : running_) {
       Request& r = reqs_[id];
       if (r.finished || r.computed >= r.prompt_len) continue;
@@ -91,14 +92,19 @@ class Scheduler {
       chunk = align_chunk(r, chunk);
       if (chunk <= 0 || !ensure_blocks(r, r.computed + chunk)) continue;
       ids[n_out] = id; ntok[n_out] = chunk; start[n_out] = r.computed; slots[n_out] = r.slot; restore[n_out] = -1;
-      ++n_out; budget -= chunk;
+      ++n_out; budget -= chunk; prefill_used += chunk;
     }
     // 3. admit waiting requests
+    const int prefill_budget = budget + prefill_used;
     while (!waiting_.empty() && (int)running_.size() < max_seqs_ && n_out < max_out && budget > 0) {
       int64_t id = waiting_.front();
       Request& r = reqs_[id];
       if (free_slots_.empty()) break;
       int hit = prefix_cache_ ? lookup_prefix(r) : 0;
+      // whole-prompt policy: a prompt that would fit a step of its own is not split just to fill the rest of this one
+      // (every scheduled piece is a separate forward pass of the engine, so fewer and larger pieces run faster)
+      if (whole_prompts_ && budget < prefill_budget && r.prompt_len - hit > budget && r.prompt_len - hit <= prefill_budget)
+        break;
       int chunk = std::min(budget, r.prompt_len - hit);
       r.computed = hit;
       chunk = align_chunk(r, chunk);
@@ -308,6 +314,7 @@ class Scheduler {
 
  public:
   bool require_snapshot_ = false;
+  bool whole_prompts_ = false;
 
  private:
   int block_size_, max_seqs_, max_tokens_;
@@ -332,6 +339,7 @@ HMF_API void* hmf_sched_create(int num_blocks, int block_size, int num_slots, in
   s->require_snapshot_ = require_snapshot != 0;
   return s;
 }
+HMF_API void hmf_sched_set_whole_prompts(void* s, int on) { static_cast<Scheduler*>(s)->whole_prompts_ = on != 0; }
 HMF_API void hmf_sched_destroy(void* s) { delete static_cast<Scheduler*>(s); }
 HMF_API int hmf_sched_add(void* s, int64_t id, const int32_t* prompt, int n, int max_new) {
   return static_cast<Scheduler*>(s)->add(id, prompt, n, max_new);

@@ -73,6 +73,7 @@ class Mamba2(nn.Module):
         assert d_inner == ngroups * d_state
         d_in_proj = d_inner + d_xb + d_xb + d_inner + self.nheads  # [z, x, B, C, dt]
         self.in_proj = nn.Linear(d_model, d_in_proj, bias=bias)
+        self.in_proj_valid = d_in_proj      # tensor-parallel shards pad the weight with zero rows past this width
         self.conv_dim = d_inner + 2 * d_xb
         self.conv1d = nn.Conv1d(self.conv_dim, self.conv_dim, kernel_size=d_conv, groups=self.conv_dim,
                                 padding=d_conv - 1, bias=conv_bias)
@@ -110,6 +111,8 @@ class Mamba2(nn.Module):
         Bsz, T, _ = hidden_states.shape
         last = past_key_values.get_ssm(self.layer_idx) if past_key_values is not None else None
         zxbcdt = self.in_proj(hidden_states)
+        if zxbcdt.shape[-1] != self.in_proj_valid:
+            zxbcdt = zxbcdt[..., :self.in_proj_valid]
         z, xBC, dt = torch.split(zxbcdt, [self.d_inner, self.conv_dim, self.nheads], dim=-1)
         xBC = self._norm_rope(xBC, position_embeddings)
         w = self.conv1d.weight.squeeze(1)

@@ -160,9 +160,13 @@ class DecoderLayer(nn.Module):
             kwargs = dict(kwargs, residual=residual)
         h, _, _ = self.seq_mixer(h, position_embeddings=position_embeddings, position_ids=position_ids,
                                  past_key_values=past_key_values, use_cache=use_cache, **kwargs)
-        hidden_states = residual + h
-        residual = hidden_states
-        h, router_logits = self._mlp(self.post_attention_layernorm(hidden_states))
+        norm = self.post_attention_layernorm
+        if not torch.is_grad_enabled() and h.is_cuda and h.dtype == torch.bfloat16 and not norm.zero_centered:
+            normed, residual = F_ops.fused_add_rms_norm(h, residual, norm.weight, norm.variance_epsilon)   # one pass
+        else:
+            residual = residual + h
+            normed = norm(residual)
+        h, router_logits = self._mlp(normed)
         return residual + h, router_logits
 
 

@@ -32,8 +32,15 @@ class KernelError(RuntimeError):
     pass
 
 
+_available = None
+_force_reference = os.environ.get("HMF_FORCE_REFERENCE", "0") == "1"     # read once: this is on every op's path
+
+
 def kernels_available() -> bool:
-    return _KERNELS_PATH.exists()
+    global _available
+    if not _available:           # a positive answer is final; a negative one is re-checked (the library may get built)
+        _available = _KERNELS_PATH.exists()
+    return _available
 
 
 def use_cuda_kernels(*tensors: torch.Tensor) -> bool:
@@ -42,11 +49,14 @@ def use_cuda_kernels(*tensors: torch.Tensor) -> bool:
     ``HMF_FORCE_REFERENCE=1`` routes every op to the PyTorch reference (debugging aid);
     without it a CUDA tensor always takes the native path and a missing library raises.
     """
-    if not tensors or not all(t.is_cuda for t in tensors if t is not None):
+    if not tensors:
         return False
-    if os.environ.get("HMF_FORCE_REFERENCE", "0") == "1":
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            return False
+    if _force_reference:
         return False
-    if not kernels_available():
+    if not _available and not kernels_available():
         raise NativeLibraryMissing(
             f"{_KERNELS_PATH} is missing: run `python -m hybrid_model_factory_b200.build` "
             "before using CUDA tensors")
@@ -90,8 +100,11 @@ def bind_thread(device=None) -> None:
 
 
 def stream_ptr(device=None) -> ctypes.c_void_p:
-    bind_thread(device)
-    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+    idx = -1 if device is None or device.index is None else device.index
+    if idx < 0 or getattr(_thread_state, "device", None) != idx:
+        bind_thread(device)
+        idx = _thread_state.device
+    return ctypes.c_void_p(torch._C._cuda_getCurrentRawStream(idx))
 
 
 def ptr(t: torch.Tensor | None) -> ctypes.c_void_p:

@@ -59,8 +59,9 @@ class PeerGemmAllReduce:
         y = torch.empty(M, N, device=x.device, dtype=torch.bfloat16)
         # K splits: more CTAs on the weight stream when the shard has few 128-column tiles
         tiles, splits = N // 128, 1
+        # ... but every (rank, split) partial is read by every rank, so world * splits is kept at 8 or below
         while (splits < self.MAX_SPLIT and tiles * splits * 2 <= 148 and Ks % (splits * 2 * 64) == 0
-               and Ks // (splits * 2) >= 256):
+               and Ks // (splits * 2) >= 256 and self.world * splits * 2 <= 8):
             splits *= 2
         _lib.check(_lib.kernels().hmf_gemm_allreduce(
             _lib.ptr(x), _lib.ptr(weight), _lib.ptr(y), c_int(M), c_int(N), c_int(Ks), c_ll(x.stride(0)),

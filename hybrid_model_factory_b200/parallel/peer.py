@@ -33,10 +33,16 @@ class SymmetricWorkspace:
     mapped into this process."""
 
     def __init__(self, nbytes: int, group, device: Optional[torch.device] = None):
-        import torch.distributed._symmetric_memory as symm_mem
         self.group = group
         self.device = device or torch.device("cuda", torch.cuda.current_device())
         nbytes = (int(nbytes) + 1023) // 1024 * 1024
+        if group is None:       # one rank: ordinary device memory, the only "peer" is this GPU
+            self.buffer = torch.zeros(nbytes, dtype=torch.uint8, device=self.device)
+            self.handle, self.rank, self.world = None, 0, 1
+            self.ptrs = [self.buffer.data_ptr()]
+            self.nbytes = nbytes
+            return
+        import torch.distributed._symmetric_memory as symm_mem
         self.buffer = symm_mem.empty(nbytes, dtype=torch.uint8, device=self.device)
         self.handle = symm_mem.rendezvous(self.buffer, group)
         self.rank, self.world = self.handle.rank, self.handle.world_size
@@ -60,7 +66,8 @@ class SymmetricWorkspace:
     def barrier(self) -> None:
         """All kernels launched so far on every rank of the group have finished."""
         torch.cuda.synchronize(self.device)
-        dist.barrier(group=self.group)
+        if self.group is not None:
+            dist.barrier(group=self.group)
 
 
 @dataclass

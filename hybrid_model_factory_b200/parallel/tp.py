@@ -141,6 +141,18 @@ def shard_mamba2(m, rank, size) -> None:
     hx = m.d_xb // m.headdim
     assert m.nheads % size == 0 and hx % size == 0, "Mamba2 heads must divide by the TP size"
     column_parallel(m.in_proj, rank, size, [m.d_inner, m.d_xb, m.d_xb, m.d_inner, m.nheads])
+    # The shard's output width (d_inner/size * 2 + d_xb/size * 2 + nheads/size) is rarely a multiple of the GEMM tile
+    # granularity, and cuBLAS then falls back to a legacy kernel several times slower: pad with zero rows, which the
+    # layer slices off again (``in_proj_valid``).
+    n = m.in_proj.weight.shape[0]
+    pad = (-n) % 64
+    if pad:
+        w = m.in_proj.weight.data
+        _set(m.in_proj.weight, torch.cat([w, w.new_zeros(pad, w.shape[1])], 0))
+        if m.in_proj.bias is not None:
+            _set(m.in_proj.bias, torch.cat([m.in_proj.bias.data, m.in_proj.bias.data.new_zeros(pad)], 0))
+        m.in_proj.out_features = n + pad
+    m.in_proj_valid = n
     seg = [m.d_xb, m.d_xb, m.d_inner]
     _vec(m.conv1d.weight, rank, size, seg)
     if m.conv1d.bias is not None:

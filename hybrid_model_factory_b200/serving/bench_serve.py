@@ -19,7 +19,7 @@ from ..utils import checkpoint_io
 from .engine import SamplingParams, ServingEngine
 
 
-def run(model, num_requests=64, prompt_min=4096, prompt_max=16384, output_len=512, seed=0, max_num_batched_tokens=8192,
+def run(model, num_requests=64, prompt_min=4096, prompt_max=16384, output_len=512, seed=0, max_num_batched_tokens=16384,
         max_num_seqs=64, block_size=64, tp=None) -> dict:
     rng = random.Random(seed)
     vocab = model.config.vocab_size
@@ -54,7 +54,8 @@ def run(model, num_requests=64, prompt_min=4096, prompt_max=16384, output_len=51
             "p50_ttft_ms": ttft[len(ttft) // 2], "mean_ttft_ms": sum(ttft) / len(ttft), "p99_ttft_ms": ttft[-1],
             "engine_steps": m["steps"], "decode_ms_per_step": 1e3 * m["decode_s"] / max(m["decode_steps"], 1),
             "decode_gpu_ms_per_step": 1e3 * m["decode_gpu_s"] / max(m["graph_replays"], 1),
-            "prefill_tok_per_s": m["prefill_tokens"] / max(m["prefill_s"], 1e-9), "graphs": len(engine._graphs)}
+            "prefill_tok_per_s": m["prefill_tokens"] / max(m["prefill_s"], 1e-9), "graphs": len(engine._graphs),
+            "max_num_batched_tokens": max_num_batched_tokens}
 
 
 def main(argv=None) -> int:
@@ -66,7 +67,7 @@ def main(argv=None) -> int:
     ap.add_argument("--prompt-min", type=int, default=4096)
     ap.add_argument("--prompt-max", type=int, default=16384)
     ap.add_argument("--output-len", type=int, default=512)
-    ap.add_argument("--max-num-batched-tokens", type=int, default=8192)
+    ap.add_argument("--max-num-batched-tokens", type=int, default=16384)
     args = ap.parse_args(argv)
     import os
     import torch.distributed as dist

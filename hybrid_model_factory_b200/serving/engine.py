@@ -59,7 +59,8 @@ class RequestState:
 class ServingEngine:
     def __init__(self, model, *, block_size: int = 64, num_blocks: Optional[int] = None, max_num_seqs: int = 64,
                  max_num_batched_tokens: int = 8192, enable_prefix_caching: bool = False, max_model_len: int = 32768,
-                 gpu_memory_utilization: float = 0.85, tp=None, use_cuda_graphs: bool = True):
+                 gpu_memory_utilization: float = 0.85, tp=None, use_cuda_graphs: bool = True,
+                 whole_prompts: bool = True):
         self.model = model.eval()
         self.cfg = model.config
         self.device = next(model.parameters()).device
@@ -75,7 +76,8 @@ class ServingEngine:
                                   dtype=next(model.parameters()).dtype)
         self._pad_block, self._pad_slot = num_blocks, max_num_seqs + snapshots
         self.sched = NativeScheduler(num_blocks, block_size, max_num_seqs, max_num_seqs, max_num_batched_tokens,
-                                     enable_prefix_caching, snapshots, require_snapshot=has_ssm)
+                                     enable_prefix_caching, snapshots, require_snapshot=has_ssm,
+                                     whole_prompts=whole_prompts)
         self.prefix_caching = enable_prefix_caching
         self.requests: Dict[int, RequestState] = {}
         self._ids = itertools.count()
@@ -575,7 +577,9 @@ class ServingEngine:
     def _mamba_decode(self, i, mx: Mamba2, h, cos, sin, slots):
         Rn = h.shape[0]
         c = self._layer_consts(i, mx)
-        z, xBC, dt = torch.split(mx.in_proj(h), [mx.d_inner, mx.conv_dim, mx.nheads], dim=-1)
+        zx = mx.in_proj(h)
+        z, xBC, dt = torch.split(zx if zx.shape[-1] == mx.in_proj_valid else zx[:, :mx.in_proj_valid],
+                                 [mx.d_inner, mx.conv_dim, mx.nheads], dim=-1)
         xBC = mx._norm_rope(xBC[:, None], (cos, sin))[:, 0]
         xBC = self._conv_update(i, xBC.contiguous(), c["w"], c["b"], slots)
         st = self.state.ssm[i]["state"]

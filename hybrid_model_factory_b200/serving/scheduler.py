@@ -26,7 +26,7 @@ class ScheduledSeq:
 class NativeScheduler:
     def __init__(self, num_blocks: int, block_size: int, num_slots: int, max_num_seqs: int = 64,
                  max_num_batched_tokens: int = 8192, enable_prefix_caching: bool = False,
-                 num_snapshot_slots: int = 0, require_snapshot: bool = False):
+                 num_snapshot_slots: int = 0, require_snapshot: bool = False, whole_prompts: bool = False):
         lib = _lib.runtime()
         lib.hmf_sched_create.restype = ctypes.c_void_p
         lib.hmf_sched_block_table.restype = ctypes.c_int
@@ -34,6 +34,8 @@ class NativeScheduler:
         self._h = ctypes.c_void_p(lib.hmf_sched_create(num_blocks, block_size, num_slots, max_num_seqs,
                                                        max_num_batched_tokens, int(enable_prefix_caching),
                                                        num_snapshot_slots, int(require_snapshot)))
+        if whole_prompts:   # do not split a prompt that fits a step of its own (see Scheduler::step)
+            lib.hmf_sched_set_whole_prompts(self._h, 1)
         self.block_size, self.max_num_seqs = block_size, max_num_seqs
         n = max_num_seqs * 2 + 8
         self._ids, self._ntok = (i64 * n)(), (i32 * n)()

@@ -1,6 +1,10 @@
 """Micro-benchmarks of the fused compute + communication kernels against their NCCL formulations.
 
     torchrun --nproc-per-node N -m hybrid_model_factory_b200.utils.comm_bench [gemm_ar] [cp_attn] [moe]
+    python -m hybrid_model_factory_b200.utils.comm_bench single [gemm_ar] [moe] [sp_scan] [cp_attn]
+
+The ``single`` form runs the same kernels on one GPU with every peer address pointing at that GPU's own buffers
+(profiling and smoke testing).
 
 Every number is a CUDA-event time on the launching stream after warm-up, maximum over ranks, inputs larger than L2
 or an L2 flush between iterations.  Rank 0 prints one line per case with the roofline bound
@@ -158,8 +162,117 @@ def bench_moe():
 CASES = {"gemm_ar": bench_gemm_ar, "cp_attn": bench_cp_attn, "moe": bench_moe}
 
 
+# -- one GPU: every "peer" address is one of this GPU's own buffers ---------------------------------------------------
+# Same kernels, same flag protocol, no NVLink traffic: the mode the kernels are profiled in (a profiler replays each
+# launch many times, which a kernel that waits for another process cannot survive) and a smoke test of each path.
+def _event_ms(fn, iters=5, warmup=2):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(iters):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / iters
+
+
+def single_gemm_ar():
+    from ..ops.fused_comm import PeerGemmAllReduce
+    op = PeerGemmAllReduce(None, max_m=256, max_n=4096)
+    M, N, K = 64, 4096, 12288
+    x = torch.randn(M, K, device="cuda").bfloat16()
+    w = (torch.randn(N, K, device="cuda") * 0.02).bfloat16()
+    ms = _event_ms(lambda: op(x, w))
+    err = float((op(x, w).float() - x.float() @ w.float().t()).abs().max())
+    print(f"single-GPU gemm+all-reduce M={M} N={N} K={K}: {ms * 1e3:.1f} us, max abs err {err:.3g} "
+          f"({N * K * 2 / ms / 1e6:.0f} GB/s of weights)", flush=True)
+
+
+def single_moe():
+    from ..ops import reference as R
+    from ..parallel.ep_fused import FusedExpertParallel
+    E, Dm, Fi, T, k = 64, 2048, 768, 8192, 8
+    g = torch.Generator().manual_seed(0)
+    wgu = (torch.randn(E, 2 * Fi, Dm, generator=g) * 0.02).bfloat16().cuda()
+    wd = (torch.randn(E, Dm, Fi, generator=g) * 0.02).bfloat16().cuda()
+    x = torch.randn(T, Dm, device="cuda").bfloat16()
+    w, idx = R.moe_router(torch.randn(T, E, device="cuda"), k)
+    fe = FusedExpertParallel(None, E, Dm, Fi, max_send_rows=T * k, capacity_rows=T * k)
+    with torch.no_grad():
+        ms = _event_ms(lambda: fe.forward(x, w, idx, wgu, wd))
+    flops = 2.0 * T * k * Dm * Fi * 3
+    print(f"single-GPU MoE layer E={E} top-{k} T={T} Dm={Dm} F={Fi}: {ms:.3f} ms ({flops / ms / 1e9:.0f} TFLOP/s over "
+          f"the whole layer, routing tables included)", flush=True)
+
+
+def single_sp_scan():
+    """Two launches of the GDN scan standing for SP ranks 0 and 1: the first pushes its final state and raises the
+    per-(batch, head) flags in a buffer, the second starts from that buffer after seeing the flags."""
+    from ..ops.gdn_cuda import GDNChunkCore
+    from ..parallel.peer import PeerIO
+    B, T, H, D = 1, 16384, 32, 128
+    q, k, v = (torch.randn(B, T, H, D, device="cuda").bfloat16() for _ in range(3))
+    g = -torch.rand(B, T, H, device="cuda") * 0.1
+    beta = torch.rand(B, T, H, device="cuda")
+    core = GDNChunkCore(scale=D ** -0.5)
+    buf = torch.zeros(B, H, D, D, device="cuda", dtype=torch.float32)
+    flags = torch.zeros(B * H, device="cuda", dtype=torch.int32)
+    epoch = [0]
+
+    def chain():
+        epoch[0] += 1
+        o0, (h_mid,), _, _ = core.forward((q, k, v, g, beta), None,
+                                          PeerIO(None, None, buf.data_ptr(), flags.data_ptr(), epoch[0]))
+        o1, (h_end,), _, _ = core.forward((q, k, v, g, beta), None, PeerIO(buf, flags, 0, 0, epoch[0]))
+        return o0, o1, h_mid, h_end
+    with torch.no_grad():
+        ms = _event_ms(chain)
+        o0, o1, h_mid, h_end = chain()
+        ref1, (ref_end,), _, _ = core.forward((q, k, v, g, beta), (h_mid,), None)
+    err = float((o1.float() - ref1.float()).abs().max())
+    print(f"single-GPU SP scan chain (2 segments of {T} tokens, {H} heads): {ms:.3f} ms for both launches, pushed "
+          f"state vs local state: max abs diff of the outputs {err:.3g}", flush=True)
+
+
+def single_cp_attn():
+    from ..ops import cuda_ops
+    from ..parallel.peer import PeerKVExchange
+    T, H, Hkv, D = 16384, 32, 8, 128
+    q = torch.randn(1, T, H, D, device="cuda").bfloat16()
+    k = torch.randn(1, T, Hkv, D, device="cuda").bfloat16()
+    v = torch.randn(1, T, Hkv, D, device="cuda").bfloat16()
+    kv = PeerKVExchange(None, 0, 1, k.numel() * 2)
+    Lc = T // 2
+
+    def run():
+        kv.publish(k, v)
+        return kv.attention(q[:, Lc:], 1, D ** -0.5, 0, 2 ** 31 - 1)
+    with torch.no_grad():
+        ms = _event_ms(run)
+        o, _ = run()
+        ref = cuda_ops.attention(q, k, v, causal=True)[:, Lc:]
+    err = float((o.float() - ref.float()).abs().max())
+    flops = 4.0 * Lc * (Lc + Lc / 2) * H * D
+    print(f"single-GPU CP attention (second half of {T} tokens, K/V fetched through the exchange buffers): {ms:.3f} ms "
+          f"({flops / ms / 1e9:.0f} TFLOP/s), max abs err vs the plain kernel {err:.3g}", flush=True)
+
+
+SINGLE = {"gemm_ar": single_gemm_ar, "moe": single_moe, "sp_scan": single_sp_scan, "cp_attn": single_cp_attn}
+
+
 def main(argv=None) -> int:
-    names = [a for a in (argv if argv is not None else sys.argv[1:]) if a in CASES] or list(CASES)
+    args = list(argv if argv is not None else sys.argv[1:])
+    if "single" in args:
+        from ..ops import _lib
+        torch.cuda.set_device(0)
+        for name in [a for a in args if a in SINGLE] or list(SINGLE):
+            SINGLE[name]()
+        torch.cuda.synchronize()
+        print("kernel status", _lib.read_status())
+        return 0
+    names = [a for a in args if a in CASES] or list(CASES)
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))

@@ -42,6 +42,27 @@ def test_scheduler_chunked_prefill_and_decode_first():
     assert s.stats()["free_slots"] == 4
 
 
+def test_scheduler_whole_prompt_policy():
+    """A prompt that fits a step of its own is not split to fill the rest of the current step; one that exceeds the
+    step budget still is."""
+    s = NativeScheduler(num_blocks=64, block_size=4, num_slots=4, max_num_seqs=4, max_num_batched_tokens=16,
+                        whole_prompts=True)
+    s.add_request(0, list(range(10)), 1)
+    s.add_request(1, list(range(12)), 1)
+    s.add_request(2, list(range(24)), 1)
+    b = s.step()
+    assert [(x.req_id, x.num_tokens) for x in b] == [(0, 10)]          # request 1 (12 tokens) waits for its own step
+    s.advance(0, 10)
+    s.append_token(0, 7)
+    b = s.step()
+    # request 0 is done (one new token); request 1 runs whole; request 2 exceeds any step and takes what is left
+    assert [(x.req_id, x.num_tokens) for x in b] == [(1, 12), (2, 4)]
+    split = NativeScheduler(num_blocks=64, block_size=4, num_slots=4, max_num_seqs=4, max_num_batched_tokens=16)
+    split.add_request(0, list(range(10)), 1)
+    split.add_request(1, list(range(12)), 1)
+    assert [(x.req_id, x.num_tokens) for x in split.step()] == [(0, 10), (1, 4)]
+
+
 def test_prefix_cache_hit_reuses_blocks():
     s = NativeScheduler(num_blocks=32, block_size=4, num_slots=4, max_num_seqs=4, max_num_batched_tokens=64,
                         enable_prefix_caching=True)
