@@ -110,6 +110,29 @@ class FinetuningArguments:
     teacher_model_name_or_path: Optional[str] = None
     use_muon: bool = False
     use_adam_mini: bool = False
+    use_galore: bool = False
+    galore_target: str = "all"
+    galore_rank: int = 16
+    galore_update_interval: int = 200
+    galore_scale: float = 2.0
+    galore_proj_type: str = "std"                      # std | reverse_std | right | left
+    use_apollo: bool = False
+    apollo_target: str = "all"
+    apollo_rank: int = 16
+    apollo_update_interval: int = 200
+    apollo_scale: float = 32.0
+    apollo_proj: str = "random"                        # svd | random
+    apollo_proj_type: str = "std"
+    apollo_scale_type: str = "channel"                 # channel | tensor
+    use_badam: bool = False
+    badam_mode: str = "layer"                          # layer | ratio
+    badam_start_block: Optional[int] = None
+    badam_switch_mode: str = "ascending"               # ascending | descending | random | fixed
+    badam_switch_interval: int = 50
+    badam_update_ratio: float = 0.05
+    badam_mask_mode: str = "adjacent"                  # adjacent | scatter
+    loraplus_lr_ratio: Optional[float] = None
+    loraplus_lr_embedding: float = 1e-6
     pref_beta: float = 0.1
     pref_loss: str = "sigmoid"
     lora_rank: int = 8

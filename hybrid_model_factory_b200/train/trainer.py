@@ -53,7 +53,9 @@ class TrainingArguments:
     optimizer_state_dtype: str = "auto"   # auto = parameter dtype (bf16 under pure_bf16), or float32
     master_weights: bool = False
     ddp_timeout: int = 1800
-    optimizer: str = "adamw"              # adamw (flat, ZeRO-sharded, fused kernel) | muon
+    optimizer: str = "adamw"              # adamw (flat, ZeRO-sharded, fused kernel) | muon | galore | apollo |
+    #                                       badam | adam_mini | loraplus (train/memory_optimizers.py)
+    optimizer_args: dict = field(default_factory=dict)
 
     def to_dict(self):
         return asdict(self)
@@ -95,6 +97,12 @@ class Trainer:
             self.optimizer = Muon([(n, p) for n, p in model.named_parameters() if id(p) in ids], lr=args.learning_rate,
                                   betas=(args.adam_beta1, args.adam_beta2), eps=args.adam_epsilon,
                                   weight_decay=args.weight_decay, max_grad_norm=args.max_grad_norm, dp_size=self.dp_size)
+        elif args.optimizer in ("galore", "apollo", "badam", "adam_mini", "loraplus"):
+            from .memory_optimizers import build_optimizer
+            self.optimizer = build_optimizer(args.optimizer, model, args.learning_rate, trainable=params,
+                                             betas=(args.adam_beta1, args.adam_beta2), eps=args.adam_epsilon,
+                                             weight_decay=args.weight_decay, max_grad_norm=args.max_grad_norm,
+                                             dp_size=self.dp_size, **args.optimizer_args)
         else:
             self.optimizer = FlatAdamW(params, lr=args.learning_rate, betas=(args.adam_beta1, args.adam_beta2),
                                        eps=args.adam_epsilon, weight_decay=args.weight_decay,

@@ -85,6 +85,36 @@ def to_trainer_args(model_args, data_args, run_args, n_batches: Optional[int]) -
         resume_from_checkpoint=run_args.resume_from_checkpoint, ddp_timeout=run_args.ddp_timeout)
 
 
+def select_optimizer(ft_args, default: str = "adamw"):
+    """Maps the ``use_*`` switches of the fine-tuning arguments to ``(optimizer name, optimizer kwargs)``
+    (reference: ``train/trainer_utils.py:257-605``; at most one of GaLore / APOLLO / BAdam may be set)."""
+    chosen = [k for k in ("galore", "apollo", "badam") if getattr(ft_args, f"use_{k}", False)]
+    if len(chosen) > 1:
+        raise ValueError("use_galore, use_apollo and use_badam exclude one another")
+    if chosen and ft_args.finetuning_type == "lora":
+        raise ValueError("GaLore / APOLLO / BAdam train full weights, not LoRA adapters")
+    if chosen == ["galore"]:
+        return "galore", dict(rank=ft_args.galore_rank, update_interval=ft_args.galore_update_interval,
+                              scale=ft_args.galore_scale, proj_type=ft_args.galore_proj_type,
+                              targets=tuple(t.strip() for t in ft_args.galore_target.split(",")))
+    if chosen == ["apollo"]:
+        return "apollo", dict(rank=ft_args.apollo_rank, update_interval=ft_args.apollo_update_interval,
+                              scale=ft_args.apollo_scale, proj=ft_args.apollo_proj, proj_type=ft_args.apollo_proj_type,
+                              scale_type=ft_args.apollo_scale_type,
+                              targets=tuple(t.strip() for t in ft_args.apollo_target.split(",")))
+    if chosen == ["badam"]:
+        return "badam", dict(mode=ft_args.badam_mode, switch_mode=ft_args.badam_switch_mode,
+                             switch_interval=ft_args.badam_switch_interval, start_block=ft_args.badam_start_block,
+                             update_ratio=ft_args.badam_update_ratio, mask_mode=ft_args.badam_mask_mode)
+    if getattr(ft_args, "use_adam_mini", False):
+        return "adam_mini", {}
+    if getattr(ft_args, "loraplus_lr_ratio", None) is not None:
+        if ft_args.finetuning_type != "lora":
+            raise ValueError("loraplus_lr_ratio is only valid for LoRA training")
+        return "loraplus", dict(lr_ratio=ft_args.loraplus_lr_ratio, lr_embedding=ft_args.loraplus_lr_embedding)
+    return default, {}
+
+
 def run_exp(args: Optional[Any] = None) -> Trainer:
     model_args, data_args, run_args, ft_args, _ = get_train_args(args)
     init_distributed(run_args.ddp_timeout)
@@ -115,6 +145,7 @@ def run_exp(args: Optional[Any] = None) -> Trainer:
     targs = to_trainer_args(model_args, data_args, run_args, n_batches)
     if ft_args.use_muon:
         targs.optimizer = "muon"
+    targs.optimizer, targs.optimizer_args = select_optimizer(ft_args, targs.optimizer)
     loss_fn = None
     teacher = None
     if stage == "hkd":

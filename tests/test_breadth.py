@@ -2,6 +2,7 @@
 import json
 import os
 
+import pytest
 import torch
 
 from hybrid_model_factory_b200.models.configuration import HybridConfig
@@ -235,3 +236,81 @@ def test_lora_and_freeze_adapters():
     n = freeze_all_but_last(model, 1)
     assert 0 < n < sum(p.numel() for p in model.parameters())
     assert all(not p.requires_grad for p in model.model.layers[0].parameters())
+
+
+# -- memory-saving optimizers ---------------------------------------------------------------------------------------
+def _toy_problem(seed=0):
+    import torch
+    torch.manual_seed(seed)
+    model = torch.nn.Sequential()
+    model.add_module("layers", torch.nn.ModuleList([torch.nn.Linear(24, 24, bias=True) for _ in range(3)]))
+    x = torch.randn(64, 24)
+    y = x @ torch.randn(24, 24) * 0.5
+
+    def loss_fn():
+        h = x
+        for lin in model.layers:
+            h = lin(h) + h
+        return ((h - y) ** 2).mean()
+    return model, loss_fn
+
+
+@pytest.mark.parametrize("name,kw", [
+    ("galore", dict(rank=4, update_interval=5, scale=1.0)),
+    ("galore", dict(rank=4, update_interval=5, scale=1.0, proj_type="right")),
+    ("apollo", dict(rank=4, update_interval=5, scale=1.0, proj="random")),
+    ("apollo", dict(rank=4, update_interval=5, scale=1.0, proj="svd", scale_type="tensor")),
+    ("badam", dict(switch_interval=4)),
+    ("badam", dict(mode="ratio", update_ratio=0.25, switch_interval=4, mask_mode="scatter")),
+    ("adam_mini", dict(head_dim=8)),
+    ("loraplus", dict(lr_ratio=4.0)),
+])
+def test_memory_optimizers_reduce_the_loss_and_round_trip_state(name, kw):
+    import torch
+    from hybrid_model_factory_b200.train.memory_optimizers import build_optimizer
+    model, loss_fn = _toy_problem()
+    opt = build_optimizer(name, model, 2e-2, max_grad_norm=1.0, **kw)
+    first = float(loss_fn())
+    for _ in range(40):
+        opt.zero_grad()
+        loss_fn().backward()
+        opt.step()
+    assert float(loss_fn()) < 0.8 * first, (name, first, float(loss_fn()))
+    assert float(opt.grad_norm()) > 0
+    sd = opt.state_dict()
+    opt2 = build_optimizer(name, model, 2e-2, **kw)
+    opt2.load_state_dict(sd)
+    assert opt2.step_count == opt.step_count == 40
+
+
+def test_galore_moments_live_in_the_subspace_and_badam_touches_one_block():
+    import torch
+    from hybrid_model_factory_b200.train.memory_optimizers import build_optimizer
+    model, loss_fn = _toy_problem()
+    opt = build_optimizer("galore", model, 1e-2, rank=4, update_interval=100)
+    opt.zero_grad(); loss_fn().backward(); opt.step()
+    st = opt.state["layers.0.weight"]
+    assert st["m"].shape in ((4, 24), (24, 4)) and st["P"].shape == (24, 4)
+    assert opt.state["layers.0.bias"]["m"].shape == (24,)           # vectors take plain Adam
+    model, loss_fn = _toy_problem()
+    before = [p.detach().clone() for p in model.parameters()]
+    opt = build_optimizer("badam", model, 1e-2, switch_interval=2, start_block=1)
+    for _ in range(2):
+        opt.zero_grad(); loss_fn().backward(); opt.step()
+    changed = [not torch.equal(a, b) for a, b in zip(before, model.parameters())]
+    assert changed == [False, False, True, True, False, False]          # only block 1 (weight, bias) moved
+    assert opt.blocks[opt.active] == 2                                   # and the next block is now active
+
+
+def test_select_optimizer_maps_finetuning_switches():
+    from hybrid_model_factory_b200.config.hparams import FinetuningArguments
+    from hybrid_model_factory_b200.train.workflow import select_optimizer
+    assert select_optimizer(FinetuningArguments())[0] == "adamw"
+    name, kw = select_optimizer(FinetuningArguments(use_galore=True, galore_rank=32, galore_target="q_proj,k_proj"))
+    assert name == "galore" and kw["rank"] == 32 and kw["targets"] == ("q_proj", "k_proj")
+    assert select_optimizer(FinetuningArguments(use_adam_mini=True))[0] == "adam_mini"
+    with pytest.raises(ValueError):
+        select_optimizer(FinetuningArguments(use_galore=True, use_badam=True))
+    with pytest.raises(ValueError):
+        select_optimizer(FinetuningArguments(loraplus_lr_ratio=16.0))
+    assert select_optimizer(FinetuningArguments(finetuning_type="lora", loraplus_lr_ratio=16.0))[0] == "loraplus"
