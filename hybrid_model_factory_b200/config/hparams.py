@@ -131,6 +131,15 @@ class FinetuningArguments:
     badam_switch_interval: int = 50
     badam_update_ratio: float = 0.05
     badam_mask_mode: str = "adjacent"                  # adjacent | scatter
+    reward_model: Optional[str] = None                 # PPO: checkpoint of the `rm` stage
+    ref_model: Optional[str] = None                    # PPO / DPO reference policy (default: the starting policy)
+    ppo_buffer_size: int = 1
+    ppo_epochs: int = 4
+    ppo_score_norm: bool = False
+    ppo_target: float = 6.0
+    ppo_whiten_rewards: bool = False
+    ppo_max_new_tokens: int = 64
+    ppo_prompt_len: int = 32
     loraplus_lr_ratio: Optional[float] = None
     loraplus_lr_embedding: float = 1e-6
     pref_beta: float = 0.1

@@ -115,6 +115,46 @@ def select_optimizer(ft_args, default: str = "adamw"):
     return default, {}
 
 
+def run_ppo(model, ft_args, run_args, dataset, tokenizer, device, bsz):
+    """PPO stage: prompts come from the dataset's ``input_ids`` (truncated to ``cutoff``), scores from the reward model
+    of ``ft_args.reward_model`` (a checkpoint of the ``rm`` stage), the KL reference from ``ft_args.ref_model`` or the
+    policy's own starting point.  Single-process (data-parallel PPO is not wired)."""
+    from .ppo import PPOConfig, PPOTrainer, reward_model_fn
+    if not getattr(ft_args, "reward_model", None):
+        raise ValueError("`reward_model` is necessary for PPO training")
+    rm = checkpoint_io.from_pretrained(ft_args.reward_model, device=device).eval()
+    ref = checkpoint_io.from_pretrained(ft_args.ref_model, device=device).eval() if getattr(ft_args, "ref_model", None) else None
+    cfg = PPOConfig(learning_rate=run_args.learning_rate, ppo_epochs=ft_args.ppo_epochs,
+                    ppo_buffer_size=ft_args.ppo_buffer_size, mini_batch_size=run_args.per_device_train_batch_size,
+                    ppo_score_norm=ft_args.ppo_score_norm, ppo_target=ft_args.ppo_target,
+                    ppo_whiten_rewards=ft_args.ppo_whiten_rewards, max_grad_norm=run_args.max_grad_norm,
+                    eos_token_id=getattr(tokenizer, "eos_token_id", None),
+                    max_new_tokens=getattr(ft_args, "ppo_max_new_tokens", 64))
+    trainer = PPOTrainer(model, reward_model_fn(rm), cfg, ref_model=ref)
+    it = iter(dataset)
+    plen = getattr(ft_args, "ppo_prompt_len", 32)
+    for step in range(run_args.max_steps if run_args.max_steps > 0 else 100):
+        groups = []
+        for _ in range(cfg.ppo_buffer_size):
+            rows = []
+            while len(rows) < bsz:
+                try:
+                    ex = next(it)
+                except StopIteration:
+                    it = iter(dataset)
+                    continue
+                ids = torch.as_tensor(ex["input_ids"]).flatten()[:plen]
+                if ids.numel() == plen:
+                    rows.append(ids)
+            groups.append(torch.stack(rows).to(device))
+        stats = trainer.step(groups)
+        info_rank0(logger, "ppo step %d: %s", step + 1, {k: round(v, 4) for k, v in stats.items()})
+    os.makedirs(run_args.output_dir, exist_ok=True)
+    checkpoint_io.save_pretrained(model, os.path.join(run_args.output_dir, "final"))
+    torch.save(trainer.value_head.state_dict(), os.path.join(run_args.output_dir, "final", "value_head.pt"))
+    return trainer
+
+
 def run_exp(args: Optional[Any] = None) -> Trainer:
     model_args, data_args, run_args, ft_args, _ = get_train_args(args)
     init_distributed(run_args.ddp_timeout)
@@ -162,6 +202,8 @@ def run_exp(args: Optional[Any] = None) -> Trainer:
     elif stage in ("dpo", "kto", "rm"):
         from .preference import make_preference_loss
         loss_fn = make_preference_loss(stage, ft_args)
+    if stage == "ppo":
+        return run_ppo(model, ft_args, run_args, dataset, tokenizer, device, bsz)
     trainer = Trainer(model, targs, device=device, loss_fn=loss_fn)
     if teacher is not None:
         from ..parallel.sp import set_sequence_parallel_group_recursive

@@ -314,3 +314,51 @@ def test_select_optimizer_maps_finetuning_switches():
     with pytest.raises(ValueError):
         select_optimizer(FinetuningArguments(loraplus_lr_ratio=16.0))
     assert select_optimizer(FinetuningArguments(finetuning_type="lora", loraplus_lr_ratio=16.0))[0] == "loraplus"
+
+
+# -- PPO ----------------------------------------------------------------------------------------------------------------
+def test_gae_matches_the_recursive_definition():
+    from hybrid_model_factory_b200.train.ppo import gae
+    torch.manual_seed(0)
+    r, v = torch.randn(2, 5), torch.randn(2, 5)
+    mask = torch.tensor([[1, 1, 1, 1, 1], [1, 1, 1, 0, 0]], dtype=torch.float32)
+    adv, ret = gae(r, v, mask, 0.9, 0.8)
+    for b, n in ((0, 5), (1, 3)):
+        want, last = [0.0] * n, 0.0
+        for t in reversed(range(n)):
+            nxt = float(v[b, t + 1]) if t + 1 < n else 0.0
+            last = float(r[b, t]) + 0.9 * nxt - float(v[b, t]) + 0.9 * 0.8 * last
+            want[t] = last
+        assert torch.allclose(adv[b, :n], torch.tensor(want), atol=1e-5)
+        assert float(adv[b, n:].abs().sum()) == 0.0
+    assert torch.allclose(ret, adv + v * mask)
+
+
+def test_ppo_raises_the_reward_of_a_tiny_policy():
+    """Reward = fraction of response tokens equal to token 7; a few PPO steps must raise it."""
+    from hybrid_model_factory_b200.train.ppo import PPOConfig, PPOTrainer
+    torch.manual_seed(0)
+    model = build_model(_cfg("*-GDN", vocab_size=16))
+    cfg = PPOConfig(learning_rate=3e-3, ppo_epochs=2, mini_batch_size=8, max_new_tokens=6, init_kl_coef=0.0,
+                    ppo_target=None, vf_coef=0.5)
+
+    def reward(ids, mask):
+        resp = ids[:, -mask.shape[1]:]
+        return ((resp == 7).float() * mask).sum(-1) / mask.sum(-1).clamp(min=1)
+    tr = PPOTrainer(model, reward, cfg)
+    prompts = torch.randint(0, 16, (16, 4))
+    scores = [tr.step([prompts])["score"] for _ in range(12)]
+    assert sum(scores[-3:]) / 3 > sum(scores[:3]) / 3 + 0.1, scores
+    assert {"policy_loss", "value_loss", "entropy", "clipfrac", "kl", "kl_coef"} <= set(tr.stats[-1])
+
+
+def test_ppo_adaptive_kl_and_reward_model_fn():
+    from hybrid_model_factory_b200.train.ppo import PPOConfig, PPOTrainer, reward_model_fn
+    torch.manual_seed(0)
+    model, ref, rm = (build_model(_cfg("*-M2", vocab_size=16)) for _ in range(3))
+    cfg = PPOConfig(learning_rate=1e-3, ppo_epochs=1, mini_batch_size=4, max_new_tokens=4, ppo_target=1e-4,
+                    kl_horizon=8, ppo_score_norm=True, ppo_whiten_rewards=True, eos_token_id=3)
+    tr = PPOTrainer(model, reward_model_fn(rm), cfg, ref_model=ref)
+    k0 = tr.kl_coef
+    st = tr.step([torch.randint(4, 16, (4, 3))])
+    assert st["kl"] != 0.0 and tr.kl_coef != k0          # a different reference policy gives a non-zero KL
