@@ -56,6 +56,8 @@ class TrainingArguments:
     optimizer: str = "adamw"              # adamw (flat, ZeRO-sharded, fused kernel) | muon | galore | apollo |
     #                                       badam | adam_mini | loraplus (train/memory_optimizers.py)
     optimizer_args: dict = field(default_factory=dict)
+    zero_stage: int = 2                   # 2: flat AdamW with sharded states / gradients; 3: parameters sharded too
+    offload_optimizer: bool = False       # ZeRO-3 only: moments and master weights in pinned host memory
 
     def to_dict(self):
         return asdict(self)
@@ -91,7 +93,13 @@ class Trainer:
             model.gradient_checkpointing_enable()
         params = list(trainable) if trainable is not None else [p for p in model.parameters() if p.requires_grad]
         sdt = None if args.optimizer_state_dtype == "auto" else getattr(torch, args.optimizer_state_dtype)
-        if args.optimizer == "muon":
+        if args.zero_stage == 3:
+            from .zero3 import Zero3Engine
+            self.optimizer = Zero3Engine(model, lr=args.learning_rate, betas=(args.adam_beta1, args.adam_beta2),
+                                         eps=args.adam_epsilon, weight_decay=args.weight_decay,
+                                         max_grad_norm=args.max_grad_norm, dp_size=self.dp_size,
+                                         offload_optimizer=args.offload_optimizer)
+        elif args.optimizer == "muon":
             from .muon import Muon
             ids = {id(p) for p in params}
             self.optimizer = Muon([(n, p) for n, p in model.named_parameters() if id(p) in ids], lr=args.learning_rate,
@@ -178,11 +186,16 @@ class Trainer:
     # -- checkpoints --------------------------------------------------------------------------
     def save_checkpoint(self, path: str) -> None:
         from ..utils.checkpoint_io import save_pretrained
+        zero3 = hasattr(self.optimizer, "gather_full_state")
+        if zero3:                       # every rank takes part in the all-gathers
+            self.optimizer.gather_full_state()
         if self.rank == 0:
             save_pretrained(self.model, path, max_shard_size=self.args.save_max_shard_size)
             with open(os.path.join(path, "trainer_state.json"), "w") as f:
                 json.dump({"global_step": self.global_step, "tokens_seen": self.tokens_seen,
                            "args": self.args.to_dict()}, f, indent=2)
+        if zero3:
+            self.optimizer.release_all()
         if not self.args.save_only_model:
             os.makedirs(path, exist_ok=True)
             torch.save(self.optimizer.state_dict(), os.path.join(path, f"optimizer_rank{self.rank:05d}.pt"))

@@ -82,7 +82,21 @@ def to_trainer_args(model_args, data_args, run_args, n_batches: Optional[int]) -
         disable_gradient_checkpointing=run_args.disable_gradient_checkpointing, logging_steps=run_args.logging_steps,
         save_steps=run_args.save_steps, save_only_model=run_args.save_only_model,
         save_max_shard_size=run_args.save_max_shard_size, seed=run_args.seed,
-        resume_from_checkpoint=run_args.resume_from_checkpoint, ddp_timeout=run_args.ddp_timeout)
+        resume_from_checkpoint=run_args.resume_from_checkpoint, ddp_timeout=run_args.ddp_timeout,
+        **zero_config(run_args.deepspeed))
+
+
+def zero_config(path: Optional[str]) -> dict:
+    """Reads the ZeRO stage and the optimizer offload switch from a DeepSpeed-style JSON
+    (``zero_optimization.stage``, ``zero_optimization.offload_optimizer.device``); other keys are ignored."""
+    if not path:
+        return {}
+    import json
+    with open(path) as f:
+        z = json.load(f).get("zero_optimization", {})
+    stage = int(z.get("stage", 2))
+    off = str(z.get("offload_optimizer", {}).get("device", "none")).lower() in ("cpu", "nvme")
+    return {"zero_stage": 3 if stage >= 3 else 2, "offload_optimizer": off and stage >= 3}
 
 
 def select_optimizer(ft_args, default: str = "adamw"):

@@ -82,3 +82,14 @@ def test_hkd_stage_only_student_trains(tmp_path):
     assert names and all("gdn" in n for n in names)
     log = [json.loads(l) for l in open(os.path.join(str(tmp_path / "hkd"), "trainer_log.jsonl"))]
     assert log[0]["loss"] > 0
+
+
+def test_zero_config_reads_deepspeed_style_json(tmp_path):
+    import json
+    from hybrid_model_factory_b200.train.workflow import zero_config
+    p = tmp_path / "ds_z3_offload.json"
+    p.write_text(json.dumps({"zero_optimization": {"stage": 3, "offload_optimizer": {"device": "cpu"}}}))
+    assert zero_config(str(p)) == {"zero_stage": 3, "offload_optimizer": True}
+    p.write_text(json.dumps({"zero_optimization": {"stage": 2}}))
+    assert zero_config(str(p)) == {"zero_stage": 2, "offload_optimizer": False}
+    assert zero_config(None) == {}
