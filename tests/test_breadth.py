@@ -362,3 +362,51 @@ def test_ppo_adaptive_kl_and_reward_model_fn():
     k0 = tr.kl_coef
     st = tr.step([torch.randint(4, 16, (4, 3))])
     assert st["kl"] != 0.0 and tr.kl_coef != k0          # a different reference policy gives a non-zero KL
+
+
+# -- multimodal plugin --------------------------------------------------------------------------------------------------
+def test_mm_plugin_qwen2_vl_expands_placeholders_and_patchifies():
+    from PIL import Image
+    from hybrid_model_factory_b200.data.mm_plugin import (VisionProcessorConfig, get_mm_plugin, register_mm_plugin,
+                                                          smart_resize)
+    assert smart_resize(100, 200, 28, 32 * 32, 768 * 768) == (112, 196)
+    h, w = smart_resize(4000, 3000, 28, 32 * 32, 768 * 768)
+    assert h % 28 == 0 and w % 28 == 0 and h * w <= 768 * 768
+    plug = get_mm_plugin("qwen2_vl", image_token="<|image_pad|>", video_token="<|video_pad|>")
+    cfg = VisionProcessorConfig()
+    img = Image.new("RGB", (200, 100), (255, 0, 0))
+    mm = plug.get_mm_inputs([img, torch.rand(3, 60, 60)], processor=cfg)
+    assert mm["image_grid_thw"].tolist() == [[1, 8, 14], [1, 4, 4]]
+    assert mm["pixel_values"].shape == (8 * 14 + 16, 3 * 2 * 14 * 14)
+    # a constant red image: every patch row holds the normalised red / green / blue constants
+    row = mm["pixel_values"][0].view(3, 2, 14, 14)
+    want = [(1.0 - m) / s for m, s in zip(cfg.image_mean[:1], cfg.image_std[:1])][0]
+    assert torch.allclose(row[0], torch.full((2, 14, 14), want), atol=1e-4)
+    msgs = [{"role": "user", "content": "look <image> and <image>"}, {"role": "assistant", "content": "ok"}]
+    out = plug.process_messages(msgs, [img, torch.rand(3, 60, 60)], processor=cfg)
+    assert out[0]["content"].count("<|image_pad|>") == 8 * 14 // 4 + 16 // 4
+    assert out[0]["content"].count("<|vision_start|>") == 2 and msgs[0]["content"].count("<image>") == 2
+    with pytest.raises(ValueError):
+        plug.process_messages(msgs, [img], processor=cfg)                 # placeholder / media count mismatch
+    with pytest.raises(ValueError):
+        get_mm_plugin("base").process_messages(msgs, [img, img])          # text-only model
+    with pytest.raises(ValueError):
+        register_mm_plugin("qwen2_vl", object)
+
+
+def test_mm_plugin_videos_and_qwen3_timestamps():
+    from PIL import Image
+    from hybrid_model_factory_b200.data.mm_plugin import VisionProcessorConfig, get_mm_plugin
+    cfg = VisionProcessorConfig(video_fps=2.0)
+    frames = [Image.new("RGB", (64, 64), (i * 40, 0, 0)) for i in range(5)]       # odd count: last frame repeated
+    p2 = get_mm_plugin("qwen2_vl", image_token="<|image_pad|>", video_token="<|video_pad|>")
+    mm = p2.get_mm_inputs(videos=[frames], processor=cfg)
+    assert mm["video_grid_thw"].tolist() == [[3, 4, 4]] and mm["second_per_grid_ts"] == [1.0]
+    assert mm["pixel_values_videos"].shape == (48, 3 * 2 * 14 * 14)
+    msgs = [{"role": "user", "content": "<video> what happens?"}]
+    assert p2.process_messages(msgs, videos=[frames], processor=cfg)[0]["content"].count("<|video_pad|>") == 12
+    p3 = get_mm_plugin("qwen3_vl", image_token="<|image_pad|>", video_token="<|video_pad|>")
+    text = p3.process_messages(msgs, videos=[frames], processor=cfg)[0]["content"]
+    assert text.count("<|video_pad|>") == 12 and text.count("seconds>") == 3 and text.startswith("<0.5 seconds>")
+    p_noexp = get_mm_plugin("qwen2_vl", image_token="<|image_pad|>", video_token="<|video_pad|>", expand_mm_tokens=False)
+    assert p_noexp.process_messages(msgs, videos=[frames], processor=cfg)[0]["content"].count("<|video_pad|>") == 1
