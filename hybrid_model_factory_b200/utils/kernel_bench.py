@@ -133,6 +133,23 @@ def bench_gdn_fwd_bwd(args):
     report(f"gdn_fwd_bwd T={T} H={H}", time_fn(step, flush=False))
 
 
+def bench_gka_cheb(args):
+    """Chebyshev ridge solve of Gated KalmaNet: the one-kernel solve and the batched fp32 PyTorch formulation."""
+    from ..ops import gka_parallel as GP
+    T, H, D = args.seq, args.heads, 128
+    q = torch.randn(1, T, H, D, device="cuda").bfloat16()
+    k = torch.nn.functional.normalize(torch.randn(1, T, H, D, device="cuda"), dim=-1).bfloat16()
+    gk = -torch.rand(1, T, H, device="cuda") * 0.1
+    iters = 30
+    flops = 2.0 * T * H * iters * (64 * 128 + 64 * 128 + 128 * 128)
+    with torch.no_grad():
+        ms = time_fn(lambda: GP.chebyshev_chunk_parallel(q, k, gk, num_iter=iters), flush=False)
+        report(f"gka_cheb kernel T={T} H={H} iters={iters}", ms, flops=flops)
+        qf, kf = q.float(), k.float()
+        ms = time_fn(lambda: GP.chebyshev_chunk_parallel(qf, kf, gk, num_iter=iters), iters=2, warmup=1, flush=False)
+        report(f"gka_cheb batched PyTorch fp32 T={T} H={H} iters={iters}", ms, flops=flops)
+
+
 def bench_rmsnorm(args):
     from ..ops import functional as F_ops
     N, D = args.seq * 8, 4096
@@ -191,7 +208,7 @@ def bench_paged_decode(args):
                bytes_=2.0 * Rn * L * Hkv * D * 2)
 
 
-CASES = {"paged_decode": bench_paged_decode, "gemm": bench_gemm, "attention_fwd": bench_attention_fwd, "attention_bwd": bench_attention_bwd,
+CASES = {"gka_cheb": bench_gka_cheb, "paged_decode": bench_paged_decode, "gemm": bench_gemm, "attention_fwd": bench_attention_fwd, "attention_bwd": bench_attention_bwd,
          "gdn_fwd": bench_gdn_fwd, "gdn_fwd_bwd": bench_gdn_fwd_bwd, "rmsnorm": bench_rmsnorm, "swiglu": bench_swiglu,
          "conv1d": bench_conv1d}
 

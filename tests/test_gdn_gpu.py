@@ -101,3 +101,32 @@ def test_ssd_matches_reference():
     yr, sr = R.ssd_chunk(x.float(), dt, A, Bm.float(), Cm.float(), Dp, initial_state=h0, chunk_size=64)
     assert _rel(y, yr) < 3e-2, _rel(y, yr)
     assert _rel(s, sr) < 3e-2, _rel(s, sr)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("T,with_state,with_gate", [(256, False, True), (200, True, True), (128, True, False)])
+def test_gka_chebyshev_kernel_matches_fp32_formulation(T, with_state, with_gate):
+    """The one-kernel Chebyshev solve (bf16 operands, fp32 accumulation) against the batched fp32 PyTorch solve."""
+    from hybrid_model_factory_b200.ops import _lib
+    from hybrid_model_factory_b200.ops import gka_parallel as GP
+    torch.manual_seed(0)
+    B, H, D = 2, 3, 128
+    q = torch.randn(B, T, H, D, device="cuda")
+    k = torch.nn.functional.normalize(torch.randn(B, T, H, D, device="cuda"), dim=-1)
+    gk = -torch.rand(B, T, H, device="cuda") * 0.2 if with_gate else None
+    h0 = None
+    if with_state:
+        a = torch.randn(B, H, D, 32, device="cuda") * 0.3
+        h0 = a @ a.transpose(-1, -2)
+    qb, kb = q.bfloat16(), k.bfloat16()
+    with torch.no_grad():
+        x_k, hT_k = GP.chebyshev_chunk_parallel(qb, kb, gk, ridge_ratio=0.02, num_iter=30, initial_state=h0)
+        assert GP._kernel_ok(qb, kb, gk, 64)
+        x_r, hT_r = GP.chebyshev_chunk_parallel(qb.float(), kb.float(), gk, ridge_ratio=0.02, num_iter=30,
+                                                initial_state=h0)
+    torch.cuda.synchronize()
+    _lib.assert_status_ok()
+    assert x_k.shape == x_r.shape and torch.isfinite(x_k).all()
+    err = (x_k - x_r).norm() / x_r.norm()
+    assert err < 2e-2, float(err)
+    assert torch.allclose(hT_k, hT_r, atol=1e-4, rtol=1e-4)
