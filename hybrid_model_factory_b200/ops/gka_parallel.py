@@ -66,38 +66,63 @@ def _solve_kernel(q: Tensor, k: Tensor, gk: Optional[Tensor], states: Tensor, ri
     return x
 
 
-def chebyshev_chunk_parallel(q: Tensor, k: Tensor, gk: Optional[Tensor], *, ridge_ratio: float = 0.02,
-                             num_iter: int = 30, initial_state: Optional[Tensor] = None, chunk_size: int = 64):
-    """Returns ``(x [B,T,H,D] fp32, H_T [B,H,D,D] fp32)``; see ``ops.reference.gka_chebyshev_chunk``."""
-    B, T, Hh, D = q.shape
+def _chunk_layout(q: Optional[Tensor], k: Tensor, gk: Optional[Tensor], initial_state: Optional[Tensor], chunk_size: int):
+    """Pads to whole chunks and returns ``(qf, kf [B,H,N,C,D] fp32, G [B,H,N,C], m [B,H,N,C,C], states, N)``."""
+    B, T, Hh, D = k.shape
     C = chunk_size
     pad = (-T) % C
-    qf, kf = q.float(), k.float()
-    gf = torch.zeros(B, T, Hh, device=q.device) if gk is None else gk.float()
+    kf = k.float()
+    qf = None if q is None else q.float()
+    gf = torch.zeros(B, T, Hh, device=k.device) if gk is None else gk.float()
     if pad:
         z = lambda t: torch.cat([t, t.new_zeros(B, pad, *t.shape[2:])], dim=1)  # noqa: E731
-        qf, kf, gf = z(qf), z(kf), z(gf)
+        kf, gf = z(kf), z(gf)
+        qf = None if qf is None else z(qf)
     N = (T + pad) // C
-    qf = qf.view(B, N, C, Hh, D).permute(0, 3, 1, 2, 4)           # [B,H,N,C,D]
+    if qf is not None:
+        qf = qf.view(B, N, C, Hh, D).permute(0, 3, 1, 2, 4)       # [B,H,N,C,D]
     kf = kf.view(B, N, C, Hh, D).permute(0, 3, 1, 2, 4)
     G = gf.view(B, N, C, Hh).permute(0, 3, 1, 2).cumsum(-1)       # [B,H,N,C]
-    idx = torch.arange(C, device=q.device)
+    idx = torch.arange(C, device=k.device)
     lower = idx[:, None] >= idx[None, :]
     diff = G[..., :, None] - G[..., None, :]
     m = torch.where(lower, torch.exp(torch.where(lower, diff, torch.zeros_like(diff))), torch.zeros_like(diff))
     H0 = None if initial_state is None else initial_state.float()
     states = chunk_states(kf, G, H0)
-    if _kernel_ok(q, k, gk, chunk_size):
-        # inference / first pass of a checkpointed layer: the whole per-chunk solve runs in one kernel
-        return _solve_kernel(q, k, gk, states, ridge_ratio, num_iter, N), states[:, :, N]
-    Hs = states[:, :, :N]                                         # [B,H,N,D,D]
-    eg = torch.exp(G)[..., None]                                  # [B,H,N,C,1]
+    return qf, kf, G, m, states, N
+
+
+def _fro(kf: Tensor, G: Tensor, m: Tensor, Hs: Tensor) -> Tensor:
+    """``|H_i|_F`` for every token, ``[B,H,N,C,1]`` (closed form over the chunk: Gram, state and cross terms)."""
+    eg = torch.exp(G)[..., None]
     gram = kf @ kf.transpose(-1, -2)
     fro2 = ((m @ (gram * gram)) * m).sum(-1, keepdim=True)
     fro2 = fro2 + eg * eg * Hs.pow(2).sum((-1, -2))[..., None, None]
     kHk = (kf * (kf @ Hs)).sum(-1)
     fro2 = fro2 + 2 * eg * (m * kHk[..., None, :]).sum(-1, keepdim=True)
-    fro = fro2.clamp(min=0).sqrt()
+    return fro2.clamp(min=0).sqrt()
+
+
+def chunk_fro(k: Tensor, gk: Optional[Tensor], initial_state: Optional[Tensor], chunk_size: int = 64):
+    """``(|H_t|_F  [B,T,H], H_T [B,H,D,D])``, differentiable in ``k``, ``gk`` and the initial state."""
+    B, T, Hh, D = k.shape
+    _, kf, G, m, states, N = _chunk_layout(None, k, gk, initial_state, chunk_size)
+    fro = _fro(kf, G, m, states[:, :, :N])
+    return fro[..., 0].permute(0, 2, 3, 1).reshape(B, N * chunk_size, Hh)[:, :T], states[:, :, N]
+
+
+def chebyshev_chunk_parallel(q: Tensor, k: Tensor, gk: Optional[Tensor], *, ridge_ratio: float = 0.02,
+                             num_iter: int = 30, initial_state: Optional[Tensor] = None, chunk_size: int = 64):
+    """Returns ``(x [B,T,H,D] fp32, H_T [B,H,D,D] fp32)``; see ``ops.reference.gka_chebyshev_chunk``."""
+    B, T, Hh, D = q.shape
+    C = chunk_size
+    qf, kf, G, m, states, N = _chunk_layout(q, k, gk, initial_state, chunk_size)
+    if _kernel_ok(q, k, gk, chunk_size):
+        # inference / first pass of a checkpointed layer: the whole per-chunk solve runs in one kernel
+        return _solve_kernel(q, k, gk, states, ridge_ratio, num_iter, N), states[:, :, N]
+    Hs = states[:, :, :N]                                         # [B,H,N,D,D]
+    eg = torch.exp(G)[..., None]                                  # [B,H,N,C,1]
+    fro = _fro(kf, G, m, Hs)
     lam = ridge_ratio * fro
     denom = 2 * lam + fro
     denom = torch.where(denom == 0, torch.ones_like(denom), denom)
@@ -115,3 +140,70 @@ def chebyshev_chunk_parallel(q: Tensor, k: Tensor, gk: Optional[Tensor], *, ridg
         x = omega * x - upd
     out = x.permute(0, 2, 3, 1, 4).reshape(B, N * C, Hh, D)[:, :T]
     return out, states[:, :, N]
+
+
+class ChebyshevCore:
+    """Scan core of the ridge solve on the GPU: forward by the one-kernel solve, backward by implicit
+    differentiation of ``(H_t + lam_t I) x_t = q_t`` — the way the reference's backward works
+    (``chebyshev_iteration.py:606-690``):
+
+    * ``dq_t = (H_t + lam_t I)^-1 dx_t``: the same solve with the upstream gradient as right-hand side;
+    * ``dH_t = -x_t dq_t^T`` reaches ``k``, the gates and the incoming state through the gated-linear-attention form
+      ``x_t H_t = GLA(q=x, k=k, v=k)_t`` contracted with ``dq`` (chunked GLA kernels, their own backward);
+    * ``dlam_t = -dq_t . x_t`` reaches them through ``lam_t = ridge |H_t|_F`` and the closed form of ``|H_t|_F``.
+    """
+    n_state = 1
+
+    def __init__(self, ridge_ratio: float, num_iter: int, chunk_size: int = 64, bp_lambda: bool = True):
+        self.ridge_ratio, self.num_iter, self.chunk_size, self.bp_lambda = ridge_ratio, num_iter, chunk_size, bp_lambda
+
+    @staticmethod
+    def supported(q: Tensor, k: Tensor, gk: Optional[Tensor], chunk_size: int) -> bool:
+        with torch.no_grad():
+            return _kernel_ok(q.detach(), k.detach(), None if gk is None else gk.detach(), chunk_size)
+
+    def state_shapes(self, inputs):
+        q = inputs[0]
+        return [((q.shape[0], q.shape[2], q.shape[3], q.shape[3]), torch.float32)]
+
+    def forward(self, inputs, state0):
+        q, k, gk = inputs
+        h0 = None if state0 is None else state0[0]
+        with torch.no_grad():
+            x, hT = chebyshev_chunk_parallel(q, k, gk, ridge_ratio=self.ridge_ratio, num_iter=self.num_iter,
+                                             initial_state=h0, chunk_size=self.chunk_size)
+        saved = [q, k, gk, x] + ([h0] if h0 is not None else [])
+        return x, (hT,), saved, h0 is not None
+
+    def backward(self, saved, meta, d_out, d_stateT):
+        from . import mixers
+        q, k, gk, x = saved[:4]
+        h0 = saved[4] if meta else None
+        with torch.no_grad():
+            dq, _ = chebyshev_chunk_parallel(d_out.to(q.dtype), k, gk, ridge_ratio=self.ridge_ratio,
+                                             num_iter=self.num_iter, initial_state=h0, chunk_size=self.chunk_size)
+            dlam = -(dq * x).sum(-1)                                        # [B,T,H]
+        k1 = k.detach().requires_grad_(True)
+        g1 = None if gk is None else gk.detach().float().requires_grad_(True)
+        h1 = None if h0 is None else h0.detach().float().requires_grad_(True)
+        with torch.enable_grad():
+            gz = torch.zeros(k.shape[:3], device=k.device) if g1 is None else g1
+            # the forward multiplies rows from the left (x_t H_t), so dH_t = -x_t dq_t^T: x takes the query role
+            o, hT = mixers.simple_gla(x.to(k.dtype), k1, k1, gz, scale=1.0, initial_state=h1,
+                                      chunk_size=self.chunk_size)
+            term = -(dq * o.float()).sum()
+            d_hT = None if d_stateT is None else d_stateT[0]
+            if d_hT is not None:
+                term = term + (d_hT.float() * hT.float()).sum()
+            if self.bp_lambda:
+                fro, _ = chunk_fro(k1, g1, h1, self.chunk_size)
+                term = term + (self.ridge_ratio * dlam * fro).sum()
+            wrt = [t for t in (k1, g1, h1) if t is not None]
+            grads = list(torch.autograd.grad(term, wrt, allow_unused=True))
+        dk = grads.pop(0)
+        dgk = grads.pop(0) if g1 is not None else None
+        dh0 = grads.pop(0) if h1 is not None else None
+        d_inputs = [dq.to(q.dtype), torch.zeros_like(k) if dk is None else dk.to(k.dtype),
+                    None if gk is None else (torch.zeros_like(gk) if dgk is None else dgk.to(gk.dtype))]
+        d_s0 = None if h0 is None else ((torch.zeros_like(h0) if dh0 is None else dh0.to(h0.dtype)),)
+        return d_inputs, d_s0

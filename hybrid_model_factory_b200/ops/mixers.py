@@ -11,6 +11,8 @@ Mamba2's SSD and GKA's output stage are both plain gated linear attention
 """
 from __future__ import annotations
 
+import os
+
 from typing import Optional, Tuple
 
 import torch
@@ -94,8 +96,14 @@ def chebyshev_solve(q: Tensor, k: Tensor, gk: Optional[Tensor], *, ridge_ratio: 
                     initial_state: Optional[Tensor] = None, sp=None, chunk_size: int = 64, recurrent: bool = False):
     """Per-token ridge solve ``(H_t + lambda_t I) x_t = q_t`` (``H_t`` the decayed key covariance).
     Returns ``(x [B,T,H,D] fp32, H_T [B,H,D,D] fp32)``."""
-    core = TorchScanCore(_cheb_ref, n_state=1, state_shape_fn=_cheb_state_shapes, ridge_ratio=ridge_ratio,
-                         num_iter=num_iter, chunk_size=chunk_size, recurrent=recurrent)
+    core = None
+    if not recurrent and q.is_cuda and os.environ.get("HMF_GKA_KERNEL", "1") == "1":
+        from .gka_parallel import ChebyshevCore
+        if ChebyshevCore.supported(q, k, gk, chunk_size):       # one-kernel solve, implicit backward
+            core = ChebyshevCore(ridge_ratio, num_iter, chunk_size)
+    if core is None:
+        core = TorchScanCore(_cheb_ref, n_state=1, state_shape_fn=_cheb_state_shapes, ridge_ratio=ridge_ratio,
+                             num_iter=num_iter, chunk_size=chunk_size, recurrent=recurrent)
     state = None if initial_state is None else (initial_state,)
     x, (hT,) = ssm_scan(core, [q, k, gk], state, sp)
     return x, hT

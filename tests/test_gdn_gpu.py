@@ -130,3 +130,43 @@ def test_gka_chebyshev_kernel_matches_fp32_formulation(T, with_state, with_gate)
     err = (x_k - x_r).norm() / x_r.norm()
     assert err < 2e-2, float(err)
     assert torch.allclose(hT_k, hT_r, atol=1e-4, rtol=1e-4)
+
+
+@pytest.mark.gpu
+def test_gka_chebyshev_implicit_backward_matches_autograd_through_the_iteration():
+    """ChebyshevCore's backward (adjoint solve + GLA form + |H|_F closed form) against differentiating the fp32
+    PyTorch iteration; enough iterations that both solves have converged."""
+    from hybrid_model_factory_b200.ops import gka_parallel as GP
+    from hybrid_model_factory_b200.ops.scan import ssm_scan
+    torch.manual_seed(0)
+    B, T, H, D = 1, 192, 2, 128
+    q = torch.randn(B, T, H, D, device="cuda")
+    k = torch.nn.functional.normalize(torch.randn(B, T, H, D, device="cuda"), dim=-1)
+    gk = -torch.rand(B, T, H, device="cuda") * 0.2
+    a = torch.randn(B, H, D, 16, device="cuda") * 0.3
+    h0 = a @ a.transpose(-1, -2)
+    w = torch.randn(B, T, H, D, device="cuda")
+    wh = torch.randn(B, H, D, D, device="cuda") * 0.01
+    wh = wh + wh.transpose(-1, -2)
+    iters = 80
+    # reference: fp32 autograd through the batched iteration
+    qr, kr, gr, hr = (t.clone().requires_grad_(True) for t in (q, k, gk, h0))
+    x_r, hT_r = GP.chebyshev_chunk_parallel(qr, kr, gr, ridge_ratio=0.05, num_iter=iters, initial_state=hr)
+    ((x_r * w).sum() + (hT_r * wh).sum()).backward()
+    # kernel core
+    qk = q.bfloat16().requires_grad_(True)
+    kk = k.bfloat16().requires_grad_(True)
+    gkk = gk.clone().requires_grad_(True)
+    hk = h0.clone().requires_grad_(True)
+    core = GP.ChebyshevCore(0.05, iters)
+    assert core.supported(qk, kk, gkk, 64)
+    x_k, (hT_k,) = ssm_scan(core, [qk, kk, gkk], (hk,), None)
+    ((x_k * w).sum() + (hT_k * wh).sum()).backward()
+
+    def rel(a, b):
+        return float((a.float() - b.float()).norm() / b.float().norm())
+    assert rel(x_k, x_r) < 3e-2
+    assert rel(qk.grad, qr.grad) < 5e-2, rel(qk.grad, qr.grad)
+    assert rel(kk.grad, kr.grad) < 8e-2, rel(kk.grad, kr.grad)
+    assert rel(gkk.grad, gr.grad) < 8e-2, rel(gkk.grad, gr.grad)
+    assert rel(hk.grad, hr.grad) < 8e-2, rel(hk.grad, hr.grad)

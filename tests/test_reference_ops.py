@@ -122,3 +122,33 @@ def test_linear_ce_and_moe():
             g, u = (x[t] @ wgu[e].t()).chunk(2)
             ref[t] += wts[t, j] * ((torch.nn.functional.silu(g) * u) @ wd[e].t())
     torch.testing.assert_close(out, ref, rtol=1e-4, atol=1e-4)
+
+
+def test_gka_implicit_backward_equals_autograd_through_the_converged_iteration():
+    """``ChebyshevCore.backward`` (adjoint solve, GLA form of ``dH``, closed form of ``|H|_F``) against autograd
+    through the iteration itself, on CPU where both use the same PyTorch forward."""
+    import torch
+    from hybrid_model_factory_b200.ops import gka_parallel as GP
+    from hybrid_model_factory_b200.ops.scan import ssm_scan
+    torch.manual_seed(0)
+    B, T, H, D = 1, 40, 2, 8
+    q = torch.randn(B, T, H, D)
+    k = torch.nn.functional.normalize(torch.randn(B, T, H, D), dim=-1)
+    gk = -torch.rand(B, T, H) * 0.2
+    a = torch.randn(B, H, D, 4) * 0.3
+    h0 = a @ a.transpose(-1, -2)
+    w = torch.randn(B, T, H, D)
+    wh = torch.randn(B, H, D, D) * 0.01
+    wh = wh + wh.transpose(-1, -2)
+    ref = [t.clone().requires_grad_(True) for t in (q, k, gk, h0)]
+    x_r, hT_r = GP.chebyshev_chunk_parallel(ref[0], ref[1], ref[2], ridge_ratio=0.05, num_iter=200,
+                                            initial_state=ref[3], chunk_size=16)
+    ((x_r * w).sum() + (hT_r * wh).sum()).backward()
+    mine = [t.clone().requires_grad_(True) for t in (q, k, gk, h0)]
+    core = GP.ChebyshevCore(0.05, 200, chunk_size=16)
+    x_k, (hT_k,) = ssm_scan(core, mine[:3], (mine[3],), None)
+    ((x_k * w).sum() + (hT_k * wh).sum()).backward()
+    assert torch.allclose(x_k, x_r, atol=1e-5)
+    for a_, b_, name in zip(mine, ref, ("dq", "dk", "dgk", "dh0")):
+        err = float((a_.grad - b_.grad).norm() / b_.grad.norm())
+        assert err < 1e-4, (name, err)
