@@ -58,6 +58,46 @@ qkv_norm_rope_append_kernel(const bf16* __restrict__ qkv, long long ld, const bf
   }
 }
 
+// Mamba2 decode glue: one pass over the convolution input row [x | B | C] (heads of 128 channels): x heads are copied,
+// B and C heads get their per-head RMSNorm and the rotary embedding; the result is a contiguous row for the
+// convolution update (replaces split + two norms + two rotations + concatenation + copy).
+__global__ void __launch_bounds__(128)
+heads_norm_rope_kernel(const bf16* __restrict__ in, long long ld_in, bf16* __restrict__ out, long long ld_out, int h_plain,
+                       int h_b, const bf16* __restrict__ wb, const bf16* __restrict__ wc, float eps, int zero_centered,
+                       const bf16* __restrict__ cs, const bf16* __restrict__ sn, int rot) {
+  constexpr int D = 128;
+  const int r = blockIdx.x, hh = blockIdx.y, t = threadIdx.x;
+  __shared__ float s_x[D];
+  __shared__ float s_red[4];
+  float x = __bfloat162float(in[(size_t)r * ld_in + (size_t)hh * D + t]);
+  bf16* dst = out + (size_t)r * ld_out + (size_t)hh * D + t;
+  if (hh < h_plain) {
+    *dst = __float2bfloat16(x);
+    return;
+  }
+  const bf16* w = hh < h_plain + h_b ? wb : wc;
+  if (w != nullptr) {
+    const float ss = warp_sum(x * x);
+    if ((t & 31) == 0) s_red[t >> 5] = ss;
+    __syncthreads();
+    const float tot = s_red[0] + s_red[1] + s_red[2] + s_red[3];
+    float wv = __bfloat162float(w[t]);
+    if (zero_centered) wv += 1.f;
+    x = x * rsqrtf(tot / D + eps) * wv;
+    x = __bfloat162float(__float2bfloat16(x));   // the unfused path rounds between the norm and the rotation
+  }
+  s_x[t] = x;
+  __syncthreads();
+  float y = x;
+  if (t < rot) {
+    const int half = rot / 2;
+    const float c = __bfloat162float(cs[(size_t)r * rot + t]), s = __bfloat162float(sn[(size_t)r * rot + t]);
+    const float partner = t < half ? -s_x[t + half] : s_x[t - half];
+    y = x * c + partner * s;
+  }
+  *dst = __float2bfloat16(y);
+}
+
 __global__ void swiglu_packed_kernel(const bf16* __restrict__ gu, bf16* __restrict__ y, long long rows, int F8,
                                      long long ld) {
   const long long total = rows * F8;
@@ -161,6 +201,22 @@ HMF_API int hmf_qkv_norm_rope_append(const void* qkv, long long ld, const void* 
   qkv_norm_rope_append_kernel<<<grid, 128, 0, st>>>((const bf16*)qkv, ld, (const bf16*)q_weight, (const bf16*)k_weight,
                                                     eps, zero_centered, (const bf16*)cos_t, (const bf16*)sin_t, rot,
                                                     (bf16*)q_out, (bf16*)kc, (bf16*)vc, slot_map, Hq, Hkv);
+  HMF_CHECK_CUDA(cudaGetLastError());
+  return HMF_OK;
+}
+
+// in [R, ld_in] bf16 (h_plain + h_b + h_c heads of 128 channels), out [R, ld_out] bf16; wb / wc [128] or null (no norm);
+// cos / sin [R, rot] bf16 (rot = 0: no rotation).
+HMF_API int hmf_heads_norm_rope(const void* in, long long ld_in, void* out, long long ld_out, int h_plain, int h_b, int h_c,
+                                const void* wb, const void* wc, float eps, int zero_centered, const void* cos_t,
+                                const void* sin_t, int rot, int R, cudaStream_t st) {
+  HMF_REQUIRE(rot % 2 == 0 && rot <= 128 && (rot == 0 || (cos_t && sin_t)), "heads_norm_rope: rotary dim %d unsupported", rot);
+  HMF_REQUIRE((wb == nullptr) == (wc == nullptr), "heads_norm_rope: both norm weights or none");
+  if (R == 0) return HMF_OK;
+  dim3 grid(R, h_plain + h_b + h_c);
+  heads_norm_rope_kernel<<<grid, 128, 0, st>>>((const bf16*)in, ld_in, (bf16*)out, ld_out, h_plain, h_b, (const bf16*)wb,
+                                               (const bf16*)wc, eps, zero_centered, (const bf16*)cos_t,
+                                               (const bf16*)sin_t, rot);
   HMF_CHECK_CUDA(cudaGetLastError());
   return HMF_OK;
 }

@@ -580,8 +580,26 @@ class ServingEngine:
         zx = mx.in_proj(h)
         z, xBC, dt = torch.split(zx if zx.shape[-1] == mx.in_proj_valid else zx[:, :mx.in_proj_valid],
                                  [mx.d_inner, mx.conv_dim, mx.nheads], dim=-1)
-        xBC = mx._norm_rope(xBC[:, None], (cos, sin))[:, 0]
-        xBC = self._conv_update(i, xBC.contiguous(), c["w"], c["b"], slots)
+        rope = mx.use_pos_emb and cos is not None
+        if (self._cuda and h.dtype == torch.bfloat16 and mx.headdim == 128 and mx.d_xb % 128 == 0
+                and (not rope or cos.shape[-1] % 2 == 0)):
+            # split + B/C norms + rotary + concatenation in one pass, written as the contiguous convolution input
+            cs = sn = None
+            if rope:
+                cs, sn = cos.reshape(Rn, -1).contiguous(), sin.reshape(Rn, -1).contiguous()
+            bn = mx.B_norm
+            xin = xBC
+            xBC = torch.empty(Rn, mx.conv_dim, device=h.device, dtype=h.dtype)
+            _lib.check(_lib.kernels().hmf_heads_norm_rope(
+                _lib.ptr(xin), c_ll(xin.stride(0)), _lib.ptr(xBC), c_ll(xBC.stride(0)), c_int(mx.d_xb // 128),
+                c_int(mx.d_xb // 128), c_int(mx.d_inner // 128), _lib.ptr(bn.weight if bn is not None else None),
+                _lib.ptr(mx.C_norm.weight if bn is not None else None),
+                c_float(bn.variance_epsilon if bn is not None else 0.0),
+                c_int(int(getattr(bn, "zero_centered", False)) if bn is not None else 0), _lib.ptr(cs), _lib.ptr(sn),
+                c_int(cs.shape[-1] if rope else 0), c_int(Rn), _lib.stream_ptr(h.device)), "heads_norm_rope")
+        else:
+            xBC = mx._norm_rope(xBC[:, None], (cos, sin))[:, 0].contiguous()
+        xBC = self._conv_update(i, xBC, c["w"], c["b"], slots)
         st = self.state.ssm[i]["state"]
         Hx = mx.d_xb // mx.headdim
         packed = self._cuda and h.dtype == torch.bfloat16 and mx.d_state in (128, 256)
