@@ -24,7 +24,7 @@ namespace gka_cheb {
 
 using bf16 = __nv_bfloat16;
 using namespace nvcuda;
-constexpr int C = 64, D = 128, NT = 256;
+constexpr int C = 64, D = 128, NT = 512, RPT = C * D / NT;   // 16 warps; RPT elements of the iterate per thread
 constexpr int LB = D + 8;      // bf16 rows of D
 constexpr int LY = D + 4;      // fp32 rows of D
 constexpr int LS = C + 4;      // fp32 rows of C
@@ -36,7 +36,7 @@ constexpr int OFF_XE = OFF_X + C * LB * 2;              // bf16 [C][LB]   iterat
 constexpr int OFF_Y = OFF_XE + C * LB * 2;              // fp32 [C][LY]   Hx; its head doubles as S [C][LS]
 constexpr int OFF_P = OFF_Y + C * LY * 4;               // bf16 [C][LP]   (x k^T) o m; before the loop: fp32 m [C][LS] spans P + M
 constexpr int OFF_SMALL = OFF_P + C * LS * 4;
-constexpr int SMEM_BYTES = OFF_SMALL + 10 * C * 4 + 64;
+constexpr int SMEM_BYTES = OFF_SMALL + 10 * C * 4 + 128;
 static_assert(C * LS * 4 >= C * LP * 2, "m scratch must cover P");
 static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
 
@@ -50,54 +50,57 @@ struct Params {
   float ridge_ratio;
 };
 
-// Cs[M, N] = A[M, K] . B   (TB: B stored [N][K], else [K][N]); 16x16 tiles dealt round-robin to the 8 warps.
-template <int M, int N, bool TB>
-__device__ __forceinline__ void mm(float* Cs, int ldc, const bf16* A, int lda, const bf16* Bm, int ldb, int K) {
+// S[C, C] = A[C, D] . B[C, D]^T : 16 tiles, one per warp; two accumulators over alternating k-steps halve the
+// dependent MMA chain.
+__device__ __forceinline__ void mm_abt(float* S, const bf16* A, const bf16* Bm) {
   const int warp = threadIdx.x >> 5;
-  constexpr int TN = N / 16, TILES = (M / 16) * TN;
-  for (int t = warp; t < TILES; t += NT / 32) {
-    const int tm = t / TN, tn = t % TN;
-    wmma::fragment<wmma::accumulator, 16, 16, 16, float> c;
-    wmma::fill_fragment(c, 0.f);
-    for (int k0 = 0; k0 < K; k0 += 16) {
-      wmma::fragment<wmma::matrix_a, 16, 16, 16, bf16, wmma::row_major> a;
-      wmma::load_matrix_sync(a, A + tm * 16 * lda + k0, lda);
-      if constexpr (TB) {
-        wmma::fragment<wmma::matrix_b, 16, 16, 16, bf16, wmma::col_major> b;
-        wmma::load_matrix_sync(b, Bm + tn * 16 * ldb + k0, ldb);
-        wmma::mma_sync(c, a, b, c);
-      } else {
-        wmma::fragment<wmma::matrix_b, 16, 16, 16, bf16, wmma::row_major> b;
-        wmma::load_matrix_sync(b, Bm + k0 * ldb + tn * 16, ldb);
-        wmma::mma_sync(c, a, b, c);
-      }
-    }
-    wmma::store_matrix_sync(Cs + tm * 16 * ldc + tn * 16, c, ldc, wmma::mem_row_major);
+  const int tm = warp >> 2, tn = warp & 3;
+  wmma::fragment<wmma::accumulator, 16, 16, 16, float> c0, c1;
+  wmma::fill_fragment(c0, 0.f);
+  wmma::fill_fragment(c1, 0.f);
+  wmma::fragment<wmma::matrix_a, 16, 16, 16, bf16, wmma::row_major> a0, a1;
+  wmma::fragment<wmma::matrix_b, 16, 16, 16, bf16, wmma::col_major> b0, b1;
+  for (int k0 = 0; k0 < D; k0 += 32) {
+    wmma::load_matrix_sync(a0, A + tm * 16 * LB + k0, LB);
+    wmma::load_matrix_sync(b0, Bm + tn * 16 * LB + k0, LB);
+    wmma::load_matrix_sync(a1, A + tm * 16 * LB + k0 + 16, LB);
+    wmma::load_matrix_sync(b1, Bm + tn * 16 * LB + k0 + 16, LB);
+    wmma::mma_sync(c0, a0, b0, c0);
+    wmma::mma_sync(c1, a1, b1, c1);
   }
+#pragma unroll
+  for (int e = 0; e < c0.num_elements; ++e) c0.x[e] += c1.x[e];
+  wmma::store_matrix_sync(S + tm * 16 * LS + tn * 16, c0, LS, wmma::mem_row_major);
 }
 
-// Y[C, D] = XE[C, D] . Hs[D, D] + P[C, C] . K[C, D]   in one accumulator per tile
+// Y[C, D] = XE[C, D] . Hs[D, D] (+ P[C, C] . K[C, D] when P is given).  Warp w owns the column block w % 8 of the row
+// blocks w / 8 and w / 8 + 2: the B fragments are shared by its two tiles, whose MMA chains are independent.
 __device__ __forceinline__ void mm_hx(float* Y, const bf16* XE, const bf16* Hs, const bf16* P, const bf16* K) {
   const int warp = threadIdx.x >> 5;
-  constexpr int TN = D / 16;
-  for (int t = warp; t < (C / 16) * TN; t += NT / 32) {
-    const int tm = t / TN, tn = t % TN;
-    wmma::fragment<wmma::accumulator, 16, 16, 16, float> c;
-    wmma::fill_fragment(c, 0.f);
-    wmma::fragment<wmma::matrix_a, 16, 16, 16, bf16, wmma::row_major> a;
-    wmma::fragment<wmma::matrix_b, 16, 16, 16, bf16, wmma::row_major> b;
-    for (int k0 = 0; k0 < D; k0 += 16) {
-      wmma::load_matrix_sync(a, XE + tm * 16 * LB + k0, LB);
-      wmma::load_matrix_sync(b, Hs + k0 * LB + tn * 16, LB);
-      wmma::mma_sync(c, a, b, c);
-    }
-    for (int k0 = 0; k0 < C; k0 += 16) {
-      wmma::load_matrix_sync(a, P + tm * 16 * LP + k0, LP);
-      wmma::load_matrix_sync(b, K + k0 * LB + tn * 16, LB);
-      wmma::mma_sync(c, a, b, c);
-    }
-    wmma::store_matrix_sync(Y + tm * 16 * LY + tn * 16, c, LY, wmma::mem_row_major);
+  const int tn = warp & 7, tm0 = warp >> 3, tm1 = tm0 + 2;
+  wmma::fragment<wmma::accumulator, 16, 16, 16, float> c0, c1;
+  wmma::fill_fragment(c0, 0.f);
+  wmma::fill_fragment(c1, 0.f);
+  wmma::fragment<wmma::matrix_a, 16, 16, 16, bf16, wmma::row_major> a0, a1;
+  wmma::fragment<wmma::matrix_b, 16, 16, 16, bf16, wmma::row_major> b;
+  for (int k0 = 0; k0 < D; k0 += 16) {
+    wmma::load_matrix_sync(b, Hs + k0 * LB + tn * 16, LB);
+    wmma::load_matrix_sync(a0, XE + tm0 * 16 * LB + k0, LB);
+    wmma::load_matrix_sync(a1, XE + tm1 * 16 * LB + k0, LB);
+    wmma::mma_sync(c0, a0, b, c0);
+    wmma::mma_sync(c1, a1, b, c1);
   }
+  if (P != nullptr) {
+    for (int k0 = 0; k0 < C; k0 += 16) {
+      wmma::load_matrix_sync(b, K + k0 * LB + tn * 16, LB);
+      wmma::load_matrix_sync(a0, P + tm0 * 16 * LP + k0, LP);
+      wmma::load_matrix_sync(a1, P + tm1 * 16 * LP + k0, LP);
+      wmma::mma_sync(c0, a0, b, c0);
+      wmma::mma_sync(c1, a1, b, c1);
+    }
+  }
+  wmma::store_matrix_sync(Y + tm0 * 16 * LY + tn * 16, c0, LY, wmma::mem_row_major);
+  wmma::store_matrix_sync(Y + tm1 * 16 * LY + tn * 16, c1, LY, wmma::mem_row_major);
 }
 
 __device__ __forceinline__ float warp_sum(float v) {
@@ -105,6 +108,8 @@ __device__ __forceinline__ float warp_sum(float v) {
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
   return v;
 }
+
+static_assert(NT == 512, "tile-to-warp maps assume 16 warps");
 
 __global__ void __launch_bounds__(NT, 1) gka_cheb_fwd_kernel(const Params p) {
   extern __shared__ __align__(128) uint8_t smem[];
@@ -125,16 +130,16 @@ __global__ void __launch_bounds__(NT, 1) gka_cheb_fwd_kernel(const Params p) {
   float* s_om = small + 5 * C;       // [2][C]
   float* s_khk = small + 7 * C;
   float* s_fro = small + 8 * C;
-  float* s_red = small + 9 * C;      // [8] warp partials + result
+  float* s_red = small + 9 * C;      // [16] warp partials + result
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n = blockIdx.x, bh = blockIdx.y, b = bh / p.H, h = bh % p.H;
   const int t0 = n * C;
 
-  // ---- loads: k -> bf16 smem, q -> registers (element e = tid + 256 r <-> (i = e / 128, d = e % 128)) ----
-  float q[32], x[32], xp[32];
+  // ---- loads: k -> bf16 smem, q -> registers (element e = tid + NT r <-> (i = e / 128, d = e % 128)) ----
+  float q[RPT], x[RPT], xp[RPT];
 #pragma unroll
-  for (int r = 0; r < 32; ++r) {
+  for (int r = 0; r < RPT; ++r) {
     const int e = tid + NT * r, i = e >> 7, d = e & 127;
     const bool ok = t0 + i < p.T;
     const bf16 kv = ok ? p.k[(size_t)b * p.k_sb + (size_t)(t0 + i) * p.k_st + (size_t)h * p.k_sh + d] : __float2bfloat16(0.f);
@@ -177,20 +182,20 @@ __global__ void __launch_bounds__(NT, 1) gka_cheb_fwd_kernel(const Params p) {
   if (tid == 0) {
     float t = 0.f;
     for (int w = 0; w < NT / 32; ++w) t += s_red[w];
-    s_red[8] = t;
+    s_red[16] = t;
   }
   // decay mask m_ij (fp32 scratch) and the Gram matrix k k^T
   for (int e = tid; e < C * C; e += NT) {
     const int i = e >> 6, j = e & 63;
     s_m[i * LS + j] = j <= i ? __expf(s_G[i] - s_G[j]) : 0.f;
   }
-  mm<C, C, true>(s_s, LS, s_k, LB, s_k, LB, D);
+  mm_abt(s_s, s_k, s_k);
   __syncthreads();
-  // part 1 of |H_i|_F^2: sum_{j,l<=i} m_ij m_il gram_jl^2  (4 threads per token, j strided over them)
+  // part 1 of |H_i|_F^2: sum_{j,l<=i} m_ij m_il gram_jl^2  (8 threads per token, j strided over them)
   {
-    const int i = tid >> 2, part = tid & 3;
+    const int i = tid >> 3, part = tid & 7;
     float acc = 0.f;
-    for (int j = part; j <= i; j += 4) {
+    for (int j = part; j <= i; j += 8) {
       float inner = 0.f;
       for (int l = 0; l <= i; ++l) {
         const float g = s_s[j * LS + l];
@@ -200,11 +205,12 @@ __global__ void __launch_bounds__(NT, 1) gka_cheb_fwd_kernel(const Params p) {
     }
     acc += __shfl_xor_sync(0xffffffffu, acc, 1);
     acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+    acc += __shfl_xor_sync(0xffffffffu, acc, 4);
     if (part == 0) s_fro[i] = acc;
   }
   __syncthreads();
   // k Hs -> y ; kHk_j = (k Hs)_j . k_j
-  mm<C, D, false>(s_y, LY, s_k, LB, s_hs, LB, D);
+  mm_hx(s_y, s_k, s_hs, nullptr, nullptr);
   __syncthreads();
   for (int j = warp; j < C; j += NT / 32) {
     float acc = 0.f;
@@ -218,7 +224,7 @@ __global__ void __launch_bounds__(NT, 1) gka_cheb_fwd_kernel(const Params p) {
     float cross = 0.f;
     for (int j = 0; j <= i; ++j) cross += s_m[i * LS + j] * s_khk[j];
     const float eg = s_eg[i];
-    const float fro2 = s_fro[i] + eg * eg * s_red[8] + 2.f * eg * cross;
+    const float fro2 = s_fro[i] + eg * eg * s_red[16] + 2.f * eg * cross;
     const float fro = sqrtf(fmaxf(fro2, 0.f));
     const float lam = p.ridge_ratio * fro;
     float denom = 2.f * lam + fro;
@@ -232,7 +238,7 @@ __global__ void __launch_bounds__(NT, 1) gka_cheb_fwd_kernel(const Params p) {
   __syncthreads();
   // ---- x0 = step q ----
 #pragma unroll
-  for (int r = 0; r < 32; ++r) {
+  for (int r = 0; r < RPT; ++r) {
     const int e = tid + NT * r, i = e >> 7, d = e & 127;
     xp[r] = 0.f;
     x[r] = s_step[i] * q[r];
@@ -244,7 +250,7 @@ __global__ void __launch_bounds__(NT, 1) gka_cheb_fwd_kernel(const Params p) {
     const float* om_old = s_om + (it & 1) * C;
     float* om_new = s_om + ((it + 1) & 1) * C;
     // S = x k^T
-    mm<C, C, true>(s_s, LS, s_x, LB, s_k, LB, D);
+    mm_abt(s_s, s_x, s_k);
     __syncthreads();
     // P = S o m (bf16 operand)
     for (int e = tid; e < C * C; e += NT) {
@@ -256,7 +262,7 @@ __global__ void __launch_bounds__(NT, 1) gka_cheb_fwd_kernel(const Params p) {
     mm_hx(s_y, s_xe, s_hs, s_p, s_k);
     __syncthreads();
 #pragma unroll
-    for (int r = 0; r < 32; ++r) {
+    for (int r = 0; r < RPT; ++r) {
       const int e = tid + NT * r, i = e >> 7, d = e & 127;
       const float om = 1.f / (1.f - s_c[i] * om_old[i]);
       const float upd = s_step[i] * om * (s_y[i * LY + d] + s_lam[i] * x[r] - q[r]) + (om - 1.f) * xp[r];
@@ -269,7 +275,7 @@ __global__ void __launch_bounds__(NT, 1) gka_cheb_fwd_kernel(const Params p) {
     __syncthreads();
   }
 #pragma unroll
-  for (int r = 0; r < 32; ++r) {
+  for (int r = 0; r < RPT; ++r) {
     const int e = tid + NT * r, i = e >> 7, d = e & 127;
     if (t0 + i < p.T) p.x[(((size_t)b * p.T + t0 + i) * p.H + h) * D + d] = x[r];
   }
