@@ -22,7 +22,10 @@ class ModelArguments:
     use_deepspeed_mics: bool = False
     preserve_tokenizer_config: bool = False
     resize_vocab: bool = False
-    rope_scaling: Optional[str] = None
+    rope_scaling: Optional[str] = None                 # linear | dynamic | yarn | llama3
+    model_max_length: Optional[int] = None             # target context for the RoPE scaling factor
+    upcast_layernorm: bool = False
+    upcast_lmhead_output: bool = False
     infer_dtype: str = "auto"
     adapter_name_or_path: Optional[str] = None
 
@@ -102,7 +105,8 @@ class RunArguments:
 @dataclass
 class FinetuningArguments:
     stage: str = "pt"                                  # pt | sft | hkd | rm | ppo | dpo | kto
-    finetuning_type: str = "full"                      # full | freeze | lora
+    finetuning_type: str = "full"                      # full | freeze | lora | oft
+    oft_block_size: int = 32
     hybrid_learnable_params: Optional[str] = None      # comma separated substrings, e.g. "gka,norm,self_attn"
     hybrid_lw_distill_target: Optional[str] = None     # decoder | mixer | residuals | all
     hybrid_distill_pre_lm_head: bool = True

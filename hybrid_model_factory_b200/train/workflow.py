@@ -54,6 +54,9 @@ def load_model(model_args, run_args, device: torch.device):
     if path and os.path.isdir(path) and os.path.exists(os.path.join(path, "config.json")):
         cfg = HybridConfig.from_pretrained(path)
         cfg.apply_overrides(overrides)
+        if getattr(model_args, "rope_scaling", None):
+            from .patcher import configure_rope_scaling
+            configure_rope_scaling(cfg, model_args.rope_scaling, getattr(model_args, "model_max_length", None))
         model = build_model(cfg).to(dtype)
         if checkpoint_io.checkpoint_files(path):
             missing, unexpected = checkpoint_io.load_state_dict_into(model, path)
@@ -179,6 +182,11 @@ def run_exp(args: Optional[Any] = None) -> Trainer:
     sp = model_args.sequence_parallel_size
     tokenizer = load_tokenizer(model_args.model_name_or_path)
     model = load_model(model_args, run_args, device)
+    from .patcher import patch_model
+    tok_size = len(tokenizer) if (tokenizer is not None and hasattr(tokenizer, "__len__")) else None
+    patch_model(model, vocab_size=tok_size, resize_vocab=model_args.resize_vocab,
+                upcast_norms=getattr(model_args, "upcast_layernorm", False),
+                upcast_logits=getattr(model_args, "upcast_lmhead_output", False), gradient_checkpointing=False)
     stage = ft_args.stage
     if stage == "hkd" or ft_args.hybrid_learnable_params:
         n = freeze_params_hybrid(model, ft_args.hybrid_learnable_params)
@@ -187,6 +195,10 @@ def run_exp(args: Optional[Any] = None) -> Trainer:
         from .adapters import apply_lora
         wrapped = apply_lora(model, ft_args.lora_rank, ft_args.lora_alpha, ft_args.lora_target)
         info_rank0(logger, "LoRA adapters on %d linear layers", len(wrapped))
+    elif ft_args.finetuning_type == "oft":
+        from .patcher import add_oft
+        wrapped = add_oft(model, tuple(t.strip() for t in ft_args.lora_target.split(",")), ft_args.oft_block_size)
+        info_rank0(logger, "OFT rotations on %d linear layers", len(wrapped))
     elif ft_args.finetuning_type == "freeze":
         from .adapters import freeze_all_but_last
         info_rank0(logger, "trainable parameters: %d", freeze_all_but_last(model, ft_args.freeze_trainable_layers))
@@ -231,6 +243,9 @@ def run_exp(args: Optional[Any] = None) -> Trainer:
         if ft_args.finetuning_type == "lora":
             from .adapters import merge_lora
             merge_lora(model)                     # the final checkpoint has the ordinary layout
+        elif ft_args.finetuning_type == "oft":
+            from .patcher import merge_oft
+            merge_oft(model)
         trainer.args.save_only_model = True
         trainer.save_checkpoint(final)
         if rank == 0:

@@ -410,3 +410,43 @@ def test_mm_plugin_videos_and_qwen3_timestamps():
     assert text.count("<|video_pad|>") == 12 and text.count("seconds>") == 3 and text.startswith("<0.5 seconds>")
     p_noexp = get_mm_plugin("qwen2_vl", image_token="<|image_pad|>", video_token="<|video_pad|>", expand_mm_tokens=False)
     assert p_noexp.process_messages(msgs, videos=[frames], processor=cfg)[0]["content"].count("<|video_pad|>") == 1
+
+
+# -- patchers -----------------------------------------------------------------------------------------------------------
+def test_patchers_resize_upcast_rope_and_oft():
+    from hybrid_model_factory_b200.train import patcher
+    torch.manual_seed(0)
+    model = build_model(_cfg("*-GDN"))
+    ids = torch.randint(0, 128, (2, 10))
+    before = model(ids).logits
+    assert patcher.resize_embedding_layer(model, 130) == 192 and model.config.vocab_size == 192
+    after = model(ids).logits
+    assert after.shape[-1] == 192 and torch.allclose(after[..., :128], before, atol=1e-5)     # old tokens unchanged
+    new_rows = model.model.embed_tokens.weight[128:]
+    assert (new_rows.mean(0) - model.model.embed_tokens.weight[:128].mean(0)).abs().max() < 0.5
+    m16 = build_model(_cfg("*-GDN")).to(torch.bfloat16)
+    assert patcher.upcast_layernorm(m16) > 0
+    assert all(p.dtype == torch.float32 for n, p in m16.named_parameters() if p.dim() == 1 and "norm" in n)
+    patcher.upcast_lmhead_output(m16)
+    cfg = _cfg("*-GDN", max_position_embeddings=4096)
+    rs = patcher.configure_rope_scaling(cfg, "dynamic", 16384)
+    assert rs["factor"] == 4.0 and cfg.max_position_embeddings == 16384 and cfg.rope_scaling["rope_type"] == "dynamic"
+    assert patcher.configure_rope_scaling(cfg, None, 1 << 20) is None
+    # OFT: identity at the start, orthogonal rotation, only S trains, merge reproduces the wrapped model
+    model = build_model(_cfg("*-GDN"))
+    ref = model(ids).logits
+    wrapped = patcher.add_oft(model, targets=("q_proj", "o_proj", "down_proj"), block_size=16)
+    assert wrapped and torch.allclose(model(ids).logits, ref, atol=1e-5)
+    train = [n for n, p in model.named_parameters() if p.requires_grad]
+    assert train and all(n.endswith("oft_s") for n in train)
+    opt = torch.optim.SGD([p for p in model.parameters() if p.requires_grad], lr=0.5)
+    model(ids, labels=ids).loss.backward()
+    opt.step()
+    lin = next(m for m in model.modules() if isinstance(m, patcher.OFTLinear))
+    R = lin.rotation()
+    assert torch.allclose(R @ R.transpose(-1, -2), torch.eye(16).expand_as(R), atol=1e-4) and (R - torch.eye(16)).abs().max() > 0
+    tuned = model(ids).logits
+    assert patcher.merge_oft(model) == len(wrapped)
+    assert not any(isinstance(m, patcher.OFTLinear) for m in model.modules())
+    assert torch.allclose(model(ids).logits, tuned, atol=1e-4)
+    assert patcher.patch_model(model, vocab_size=200, resize_vocab=True)["vocab_size"] == 256
