@@ -58,6 +58,7 @@ class TrainingArguments:
     optimizer_args: dict = field(default_factory=dict)
     zero_stage: int = 2                   # 2: flat AdamW with sharded states / gradients; 3: parameters sharded too
     offload_optimizer: bool = False       # ZeRO-3 only: moments and master weights in pinned host memory
+    mics_shard_size: int = 0              # ZeRO-3 only: shard inside groups of this many ranks, replicate across them
 
     def to_dict(self):
         return asdict(self)
@@ -94,8 +95,12 @@ class Trainer:
         params = list(trainable) if trainable is not None else [p for p in model.parameters() if p.requires_grad]
         sdt = None if args.optimizer_state_dtype == "auto" else getattr(torch, args.optimizer_state_dtype)
         if args.zero_stage == 3:
-            from .zero3 import Zero3Engine
-            self.optimizer = Zero3Engine(model, lr=args.learning_rate, betas=(args.adam_beta1, args.adam_beta2),
+            from .zero3 import Zero3Engine, mics_groups
+            groups = {}
+            if args.mics_shard_size and dist.is_initialized() and args.mics_shard_size < self.world:
+                shard_group, replica_group = mics_groups(args.mics_shard_size)
+                groups = dict(group=shard_group, replica_group=replica_group)
+            self.optimizer = Zero3Engine(model, **groups, lr=args.learning_rate, betas=(args.adam_beta1, args.adam_beta2),
                                          eps=args.adam_epsilon, weight_decay=args.weight_decay,
                                          max_grad_norm=args.max_grad_norm, dp_size=self.dp_size,
                                          offload_optimizer=args.offload_optimizer)

@@ -99,7 +99,10 @@ def zero_config(path: Optional[str]) -> dict:
         z = json.load(f).get("zero_optimization", {})
     stage = int(z.get("stage", 2))
     off = str(z.get("offload_optimizer", {}).get("device", "none")).lower() in ("cpu", "nvme")
-    return {"zero_stage": 3 if stage >= 3 else 2, "offload_optimizer": off and stage >= 3}
+    out = {"zero_stage": 3 if stage >= 3 else 2, "offload_optimizer": off and stage >= 3}
+    if stage >= 3 and int(z.get("mics_shard_size", 0) or 0) > 0:
+        out["mics_shard_size"] = int(z["mics_shard_size"])
+    return out
 
 
 def select_optimizer(ft_args, default: str = "adamw"):

@@ -44,8 +44,9 @@ def _reduce_scatter_flat(out: torch.Tensor, full: torch.Tensor, rank: int, group
 
 
 class _Unit:
-    def __init__(self, name: str, module_or_params, world: int, rank: int, group, align: int = 128):
+    def __init__(self, name: str, module_or_params, world: int, rank: int, group, align: int = 128, replica_group=None):
         self.name, self.world, self.rank, self.group = name, world, rank, group
+        self.replica_group = replica_group
         if isinstance(module_or_params, torch.nn.Module):
             self.params = [p for p in module_or_params.parameters() if p.requires_grad]
         else:
@@ -123,8 +124,30 @@ class _Unit:
             _reduce_scatter_flat(out, flat, self.rank, self.group)
         else:
             out = flat
+        if self.replica_group is not None:      # MiCS: the same shard lives in every replica group
+            dist.all_reduce(out, group=self.replica_group)
         self.grad_shard = out if self.grad_shard is None else self.grad_shard.add_(out)
         self.release()
+
+
+def mics_groups(shard_size: int):
+    """MiCS layout: parameters are sharded inside groups of ``shard_size`` consecutive ranks and replicated across the
+    groups.  Returns ``(shard_group, replica_group)`` of the calling rank (collective: every rank creates every
+    group).  The reference forces this layout through DeepSpeed's ``mics_shard_size`` (``model/loader.py:185-208``)."""
+    world, rank = dist.get_world_size(), dist.get_rank()
+    assert world % shard_size == 0, "mics_shard_size must divide the world size"
+    shard = replica = None
+    for g in range(world // shard_size):
+        ranks = list(range(g * shard_size, (g + 1) * shard_size))
+        grp = dist.new_group(ranks)
+        if rank in ranks:
+            shard = grp
+    for i in range(shard_size):
+        ranks = list(range(i, world, shard_size))
+        grp = dist.new_group(ranks)
+        if rank in ranks:
+            replica = grp
+    return shard, (replica if world > shard_size else None)
 
 
 class Zero3Engine:
@@ -133,13 +156,14 @@ class Zero3Engine:
     def __init__(self, model: torch.nn.Module, units: Optional[Sequence[torch.nn.Module]] = None, group=None,
                  lr: float = 1e-4, betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 0.0,
                  max_grad_norm: float = 0.0, dp_size: Optional[int] = None, offload_optimizer: bool = False,
-                 state_dtype: torch.dtype = torch.float32):
-        self.model, self.group = model, group
+                 state_dtype: torch.dtype = torch.float32, replica_group=None):
+        self.model, self.group, self.replica_group = model, group, replica_group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        n_rep = dist.get_world_size(replica_group) if replica_group is not None else 1
         self.lr, self.betas, self.eps, self.weight_decay = lr, betas, eps, weight_decay
         self.max_grad_norm = max_grad_norm
-        self.dp_size = self.world if dp_size is None else max(1, dp_size)
+        self.dp_size = self.world * n_rep if dp_size is None else max(1, dp_size)
         self.offload = offload_optimizer
         if units is None:
             units = list(model.model.layers)
@@ -147,7 +171,7 @@ class Zero3Engine:
         inside = set()
         for i, m in enumerate(units):
             if any(p.requires_grad for p in m.parameters()):
-                u = _Unit(f"unit{i}", m, self.world, self.rank, group)
+                u = _Unit(f"unit{i}", m, self.world, self.rank, group, replica_group=replica_group)
                 self.units.append(u)
                 inside.update(id(p) for p in u.params)
                 m.register_forward_pre_hook(self._pre(u))
@@ -155,7 +179,7 @@ class Zero3Engine:
         rest = [p for p in model.parameters() if p.requires_grad and id(p) not in inside]
         self.outer: Optional[_Unit] = None
         if rest:
-            self.outer = _Unit("outer", rest, self.world, self.rank, group)
+            self.outer = _Unit("outer", rest, self.world, self.rank, group, replica_group=replica_group)
             self.units.append(self.outer)
             model.register_forward_pre_hook(self._pre(self.outer))
             model.register_forward_hook(self._post(self.outer))

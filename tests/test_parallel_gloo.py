@@ -97,11 +97,11 @@ def test_pipeline_parallel_generation_matches_single_rank():
 
 
 # -- ZeRO-3 ---------------------------------------------------------------------------------------------------------
-def _zero3_worker(rank, world, offload, checkpointing):
+def _zero3_worker(rank, world, offload, checkpointing, mics=0):
     import copy
     from hybrid_model_factory_b200.models.configuration import HybridConfig
     from hybrid_model_factory_b200.models.modeling_hybrid import build_model
-    from hybrid_model_factory_b200.train.zero3 import Zero3Engine
+    from hybrid_model_factory_b200.train.zero3 import Zero3Engine, mics_groups
     torch.manual_seed(0)
     cfg = HybridConfig("hybrid_qwen3", vocab_size=64, hidden_size=32, intermediate_size=64, num_hidden_layers=3,
                        num_attention_heads=2, num_key_value_heads=1, head_dim=16, hybrid_override_pattern="*-GDN-M2")
@@ -110,7 +110,13 @@ def _zero3_worker(rank, world, offload, checkpointing):
     if checkpointing:
         model.gradient_checkpointing_enable()
     total = sum(p.numel() for p in model.parameters())
-    eng = Zero3Engine(model, lr=1e-2, weight_decay=0.1, max_grad_norm=1.0, offload_optimizer=offload)
+    groups = {}
+    if mics:
+        shard_group, replica_group = mics_groups(mics)
+        groups = dict(group=shard_group, replica_group=replica_group)
+    eng = Zero3Engine(model, lr=1e-2, weight_decay=0.1, max_grad_norm=1.0, offload_optimizer=offload, **groups)
+    if mics:
+        assert eng.world == mics and eng.dp_size == world
     assert eng.parameter_bytes_resident() == 0 and all(p.numel() == 0 for p in model.parameters())
     decay = [p for p in ref.parameters() if p.dim() >= 2 and not getattr(p, "_no_weight_decay", False)]
     rest = [p for p in ref.parameters() if not (p.dim() >= 2 and not getattr(p, "_no_weight_decay", False))]
@@ -148,3 +154,8 @@ def _zero3_worker(rank, world, offload, checkpointing):
 @pytest.mark.parametrize("offload,checkpointing", [(False, True), (True, True), (False, False)])
 def test_zero3_matches_single_process_adamw(offload, checkpointing):
     run_ranks(_zero3_worker, 2, offload, checkpointing)
+
+
+def test_zero3_mics_shards_inside_groups_of_two():
+    """Four ranks, parameters sharded over pairs and replicated across the two pairs (MiCS)."""
+    run_ranks(_zero3_worker, 4, False, True, 2)
