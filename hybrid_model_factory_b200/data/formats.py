@@ -28,6 +28,7 @@ class DatasetAttr:
     tags: Dict[str, str] = field(default_factory=dict)
     split: str = "train"
     num_samples: Optional[int] = None
+    ranking: bool = False              # preference data: ``chosen`` / ``rejected`` answers
 
 
 def load_dataset_info(dataset_dir: str) -> Dict[str, dict]:
@@ -48,7 +49,7 @@ def get_dataset_list(names: Optional[str], dataset_dir: str) -> List[DatasetAttr
             e = info[name]
             out.append(DatasetAttr(name, e.get("file_name", name), e.get("formatting", "alpaca"),
                                    e.get("columns", {}), e.get("tags", {}), e.get("split", "train"),
-                                   e.get("num_samples")))
+                                   e.get("num_samples"), bool(e.get("ranking", False))))
         elif os.path.exists(os.path.join(dataset_dir, name)) or os.path.exists(name):
             fmt = "text" if name.endswith(".txt") else "alpaca"
             out.append(DatasetAttr(os.path.basename(name), name, fmt))
@@ -95,8 +96,19 @@ def convert_alpaca(rec: dict, attr: DatasetAttr) -> dict:
     if rec.get(c["query"]):
         prompt = f"{prompt}\n{rec[c['query']]}" if prompt else rec[c["query"]]
     messages.append({"role": "user", "content": prompt})
+    out = {"system": rec.get(c["system"], "") or ""}
+    chosen_col, rejected_col = c.get("chosen", "chosen"), c.get("rejected", "rejected")
+    if (attr.ranking or chosen_col in rec) and rejected_col in rec:       # preference pair: two answers to one prompt
+        out["messages"] = messages
+        out["chosen"] = {"role": "assistant", "content": rec.get(chosen_col, "") or ""}
+        out["rejected"] = {"role": "assistant", "content": rec.get(rejected_col, "") or ""}
+        return out
     messages.append({"role": "assistant", "content": rec.get(c["response"], "") or ""})
-    return {"messages": messages, "system": rec.get(c["system"], "") or ""}
+    out["messages"] = messages
+    kto_col = c.get("kto_tag", "kto_tag")
+    if kto_col in rec:                                                    # KTO feedback: desirable / undesirable
+        out["kto_tag"] = bool(rec[kto_col])
+    return out
 
 
 def convert_sharegpt(rec: dict, attr: DatasetAttr) -> dict:
@@ -115,9 +127,25 @@ def convert_sharegpt(rec: dict, attr: DatasetAttr) -> dict:
             messages.append({"role": "user", "content": content})
         elif role in (t["assistant_tag"], "assistant"):
             messages.append({"role": "assistant", "content": content})
+        elif role in (t.get("function_tag", "function_call"), "function_call", "tool_calls"):
+            messages.append({"role": "function", "content": content})
+        elif role in (t.get("observation_tag", "observation"), "observation", "tool"):
+            messages.append({"role": "observation", "content": content})
         else:
             messages.append({"role": str(role), "content": content})
-    return {"messages": messages, "system": system}
+    out = {"messages": messages, "system": system, "tools": rec.get(c.get("tools", "tools"), "") or ""}
+    chosen_col, rejected_col = c.get("chosen", "chosen"), c.get("rejected", "rejected")
+    if (attr.ranking or chosen_col in rec) and rejected_col in rec:
+
+        def one(m):
+            if isinstance(m, dict):
+                return {"role": "assistant", "content": m.get(t["content_tag"], m.get("content", ""))}
+            return {"role": "assistant", "content": str(m)}
+        out["chosen"], out["rejected"] = one(rec[chosen_col]), one(rec[rejected_col])
+    kto_col = c.get("kto_tag", "kto_tag")
+    if kto_col in rec:
+        out["kto_tag"] = bool(rec[kto_col])
+    return out
 
 
 def convert_text(rec: dict, attr: DatasetAttr) -> dict:
@@ -150,11 +178,44 @@ class Template:
     default_system: str = ""
     add_bos: bool = False
     efficient_eos: bool = True   # append the tokenizer's EOS after each assistant turn
+    function_fmt: str = "<tool_call>\n{content}\n</tool_call>"            # assistant turn that calls tools
+    observation_fmt: str = "<tool_response>\n{content}\n</tool_response>"  # tool results, shown as a user turn
+    tools_fmt: str = ("\n\n# Tools\n\nYou may call one or more functions to assist with the user query.\n"
+                      "<tools>\n{content}\n</tools>\nFor each function call, return a json object with function "
+                      "name and arguments within <tool_call></tool_call> XML tags.")
+
+    def normalise(self, messages: Sequence[dict], system: str = "", tools: str = ""):
+        """Tool turns become ordinary ones: a ``function`` turn is an assistant turn wrapped in ``function_fmt``, an
+        ``observation`` a user turn wrapped in ``observation_fmt``; a tool list is appended to the system prompt."""
+        out = []
+        for m in messages:
+            if m["role"] == "function":
+                content = m["content"]
+                try:                                   # a JSON list of calls: one block per call
+                    import json as _json
+                    calls = _json.loads(content)
+                    calls = calls if isinstance(calls, list) else [calls]
+                    content = "\n".join(self.function_fmt.format(content=_json.dumps(c_, ensure_ascii=False)) for c_ in calls)
+                    out.append({"role": "assistant", "content": content})
+                    continue
+                except (ValueError, TypeError):
+                    pass
+                out.append({"role": "assistant", "content": self.function_fmt.format(content=content)})
+            elif m["role"] == "observation":
+                out.append({"role": "user", "content": self.observation_fmt.format(content=m["content"])})
+            else:
+                out.append(m)
+        if tools:
+            system = (system or self.default_system) + self.tools_fmt.format(content=tools if isinstance(tools, str)
+                                                                             else __import__("json").dumps(tools))
+        return out, system
 
     def encode_multiturn(self, tokenizer, messages: Sequence[dict], system: str = "") -> List[Tuple[List[int], List[int]]]:
         """Returns ``[(prompt_ids, response_ids), ...]`` per user/assistant exchange."""
         pairs = []
         prefix = ""
+        if any(m["role"] in ("function", "observation") for m in messages):
+            messages, system = self.normalise(messages, system)
         sys_text = system or self.default_system
         if sys_text:
             prefix = self.system_fmt.format(content=sys_text)

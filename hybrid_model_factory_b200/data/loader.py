@@ -180,6 +180,57 @@ def mix_datasets(parts: List[List[dict]], strategy: str = "concat", probs: Optio
     return out
 
 
+def _encode_prompt_and_answers(ex: dict, tokenizer, template, cutoff_len: int, answers: Sequence[dict]):
+    """Token ids of the conversation up to the last user turn, and of each candidate answer."""
+    msgs, system = template.normalise(ex["messages"], ex.get("system", ""), ex.get("tools", ""))
+    outs = []
+    for ans in answers:
+        pairs = template.encode_multiturn(tokenizer, list(msgs) + [ans], system)
+        prompt = [t for p, r in pairs[:-1] for t in p + r] + pairs[-1][0]
+        outs.append((prompt, pairs[-1][1]))
+    return outs
+
+
+def process_pairwise(examples: Sequence[dict], tokenizer, template, cutoff_len: int) -> List[Dict[str, List[int]]]:
+    """Preference pairs (``rm`` / ``dpo``): one prompt, a chosen and a rejected answer; labels cover the answers."""
+    rows = []
+    for ex in examples:
+        if "chosen" not in ex or "rejected" not in ex:
+            continue
+        (pc, rc), (pr, rr) = _encode_prompt_and_answers(ex, tokenizer, template, cutoff_len, [ex["chosen"], ex["rejected"]])
+        keep = max(cutoff_len - max(len(rc), len(rr)), cutoff_len // 2)
+        pc, pr = pc[-keep:], pr[-keep:]                      # keep the end of a long prompt
+        row = {}
+        for name, p_ids, r_ids in (("chosen", pc, rc), ("rejected", pr, rr)):
+            ids = (p_ids + r_ids)[:cutoff_len]
+            lab = ([IGNORE_INDEX] * len(p_ids) + r_ids)[:cutoff_len]
+            row[f"{name}_input_ids"], row[f"{name}_labels"] = ids, lab
+        rows.append(row)
+    return rows
+
+
+def process_feedback(examples: Sequence[dict], tokenizer, template, cutoff_len: int) -> List[Dict[str, List[int]]]:
+    """KTO: single answers tagged desirable / undesirable."""
+    rows = []
+    for ex, row in zip(examples, process_supervised(examples, tokenizer, template, cutoff_len)):
+        row = dict(row)
+        row["kto_tags"] = int(bool(ex.get("kto_tag", True)))
+        rows.append(row)
+    return rows
+
+
+def process_unsupervised(examples: Sequence[dict], tokenizer, template, cutoff_len: int) -> List[Dict[str, List[int]]]:
+    """Generation / evaluation: the prompt (up to the last user turn) as ``input_ids``, the reference answer as
+    ``labels``."""
+    rows = []
+    for ex in examples:
+        msgs = list(ex["messages"])
+        answer = msgs.pop() if msgs and msgs[-1]["role"] == "assistant" else {"role": "assistant", "content": ""}
+        (prompt, resp), = _encode_prompt_and_answers(dict(ex, messages=msgs), tokenizer, template, cutoff_len, [answer])
+        rows.append({"input_ids": prompt[-cutoff_len:], "labels": resp[:cutoff_len]})
+    return rows
+
+
 def get_dataset(data_args: DataArguments, tokenizer, stage: str = "pt", sp_size: int = 1, vocab_size: int = 0,
                 seed: int = 42) -> torch.utils.data.Dataset:
     """Builds (or loads from ``tokenized_path``) the training dataset for this configuration."""
@@ -200,6 +251,12 @@ def get_dataset(data_args: DataArguments, tokenizer, stage: str = "pt", sp_size:
         examples = align_dataset(attr, data_args.dataset_dir, data_args.max_samples)
         if stage == "pt":
             rows = process_pretrain(examples, tokenizer, data_args.cutoff_len)
+        elif stage in ("rm", "dpo"):
+            rows = process_pairwise(examples, tokenizer, template, data_args.cutoff_len)
+        elif stage == "kto":
+            rows = process_feedback(examples, tokenizer, template, data_args.cutoff_len)
+        elif stage == "unsupervised":
+            rows = process_unsupervised(examples, tokenizer, template, data_args.cutoff_len)
         else:
             rows = process_supervised(examples, tokenizer, template, data_args.cutoff_len, data_args.train_on_prompt,
                                       data_args.mask_history)
@@ -234,13 +291,17 @@ class _SPSynthetic(torch.utils.data.Dataset):
 
 # -- batching ------------------------------------------------------------------------------------
 def collate(rows: Sequence[Dict[str, List[int]]], pad_id: int = 0, pin: bool = False) -> Dict[str, torch.Tensor]:
-    L = max(len(r["input_ids"]) for r in rows)
-
-    def pad(v, fill):
-        return v + [fill] * (L - len(v))
-    batch = {"input_ids": torch.tensor([pad(r["input_ids"], pad_id) for r in rows], dtype=torch.long),
-             "labels": torch.tensor([pad(r["labels"], IGNORE_INDEX) for r in rows], dtype=torch.long),
-             "position_ids": torch.tensor([pad(r["position_ids"], 0) for r in rows], dtype=torch.long)}
+    """Pads every list-valued column to the batch maximum (``*labels`` with the ignore index, ``*input_ids`` with the
+    pad id, the rest with 0); scalar columns (``kto_tags``) become 1-D tensors."""
+    batch = {}
+    for key in rows[0]:
+        vals = [r[key] for r in rows]
+        if isinstance(vals[0], (list, tuple)):
+            L = max(len(v) for v in vals)
+            fill = IGNORE_INDEX if key.endswith("labels") else (pad_id if key.endswith("input_ids") else 0)
+            batch[key] = torch.tensor([list(v) + [fill] * (L - len(v)) for v in vals], dtype=torch.long)
+        else:
+            batch[key] = torch.tensor(vals, dtype=torch.long)
     if pin and torch.cuda.is_available():
         batch = {k: v.pin_memory() for k, v in batch.items()}
     return batch

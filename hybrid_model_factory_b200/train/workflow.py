@@ -205,7 +205,7 @@ def run_exp(args: Optional[Any] = None) -> Trainer:
     elif ft_args.finetuning_type == "freeze":
         from .adapters import freeze_all_but_last
         info_rank0(logger, "trainable parameters: %d", freeze_all_but_last(model, ft_args.freeze_trainable_layers))
-    dataset = get_dataset(data_args, tokenizer, stage="pt" if stage in ("pt", "hkd") else "sft", sp_size=sp,
+    dataset = get_dataset(data_args, tokenizer, stage=("pt" if stage in ("pt", "hkd") else stage if stage in ("rm", "dpo", "kto") else "sft"), sp_size=sp,
                           vocab_size=model.config.vocab_size, seed=run_args.seed)
     bsz = run_args.per_device_train_batch_size * run_args.gradient_accumulation_steps
     n_batches = None

@@ -93,3 +93,48 @@ def test_zero_config_reads_deepspeed_style_json(tmp_path):
     p.write_text(json.dumps({"zero_optimization": {"stage": 2}}))
     assert zero_config(str(p)) == {"zero_stage": 2, "offload_optimizer": False}
     assert zero_config(None) == {}
+
+
+def test_preference_feedback_and_tool_data_processing(tmp_path):
+    import json
+    import torch
+    from hybrid_model_factory_b200.config.hparams import DataArguments
+    from hybrid_model_factory_b200.data.formats import ByteTokenizer, DatasetAttr, convert_alpaca, convert_sharegpt, get_template
+    from hybrid_model_factory_b200.data.loader import (IGNORE_INDEX, collate, get_dataset, process_feedback,
+                                                       process_pairwise, process_unsupervised)
+    tok, tpl = ByteTokenizer(), get_template("qwen3")
+    pair = convert_alpaca({"instruction": "2+2?", "chosen": "4", "rejected": "five"}, DatasetAttr("p", "p", ranking=True))
+    assert pair["chosen"]["content"] == "4" and pair["messages"][-1]["role"] == "user"
+    rows = process_pairwise([pair], tok, tpl, 256)
+    r = rows[0]
+    assert r["chosen_input_ids"][:10] == r["rejected_input_ids"][:10]                       # the shared prompt
+    n_prompt = sum(l == IGNORE_INDEX for l in r["chosen_labels"])
+    assert bytes(r["chosen_labels"][n_prompt:n_prompt + 1]) == b"4"
+    assert sum(l != IGNORE_INDEX for l in r["rejected_labels"]) > sum(l != IGNORE_INDEX for l in r["chosen_labels"])
+    b = collate(rows * 2, pad_id=0)
+    assert set(b) == {"chosen_input_ids", "chosen_labels", "rejected_input_ids", "rejected_labels"}
+    assert b["chosen_input_ids"].shape[0] == 2 and b["rejected_labels"].dtype == torch.long
+    fb = convert_alpaca({"instruction": "hi", "output": "yo", "kto_tag": False}, DatasetAttr("k", "k"))
+    rows = process_feedback([fb], tok, tpl, 128)
+    assert rows[0]["kto_tags"] == 0 and collate(rows)["kto_tags"].tolist() == [0]
+    # tool calls: function / observation turns, tool list in the system prompt
+    conv = convert_sharegpt({"conversations": [
+        {"from": "human", "value": "weather in Paris?"},
+        {"from": "function_call", "value": json.dumps({"name": "get_weather", "arguments": {"city": "Paris"}})},
+        {"from": "observation", "value": json.dumps({"temp": 21})},
+        {"from": "gpt", "value": "21 degrees."}], "tools": json.dumps([{"name": "get_weather"}])}, DatasetAttr("t", "t", "sharegpt"))
+    assert [m["role"] for m in conv["messages"]] == ["user", "function", "observation", "assistant"]
+    msgs, system = tpl.normalise(conv["messages"], "", conv["tools"])
+    assert [m["role"] for m in msgs] == ["user", "assistant", "user", "assistant"]
+    assert "<tool_call>" in msgs[1]["content"] and "<tool_response>" in msgs[2]["content"] and "<tools>" in system
+    text = bytes(t for p, r_ in tpl.encode_multiturn(tok, conv["messages"]) for t in p + r_).decode()
+    assert "<tool_call>" in text and "get_weather" in text
+    un = process_unsupervised([conv], tok, tpl, 512)[0]
+    assert bytes(un["labels"]).decode().startswith("21 degrees.")
+    # end to end through get_dataset with a ranking dataset from dataset_info.json
+    (tmp_path / "dataset_info.json").write_text(json.dumps({"prefs": {"file_name": "prefs.json", "ranking": True}}))
+    (tmp_path / "prefs.json").write_text(json.dumps([{"instruction": f"q{i}", "chosen": "good", "rejected": "bad"}
+                                                     for i in range(4)]))
+    ds = get_dataset(DataArguments(dataset="prefs", dataset_dir=str(tmp_path), template="qwen3", cutoff_len=128), tok,
+                     stage="dpo")
+    assert len(ds) == 4 and "rejected_labels" in ds[0]
