@@ -144,8 +144,8 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
     const int rows = (p.M - ksp + p.splits - 1) / p.splits;
     const int chunks = rows * (BN / 8);
     // Remote loads take microseconds, so they go out in batches before the first use: 8 (rank, split) partials of
-    // CU chunks at a time.  The sums are still taken in (rank, split) order, so every rank gets the same bits.
-    constexpr int CU = 2;
+    // CU chunks at a time (CU = 4: a 64-row tile at 8 ranks takes two rounds of remote latency).  The sums are still taken in (rank, split) order, so every rank gets the same bits.
+    constexpr int CU = 4;
     const int total = p.world * p.splits;
     for (int c0 = et; c0 < chunks; c0 += 128 * CU) {
       float acc[CU][8];
