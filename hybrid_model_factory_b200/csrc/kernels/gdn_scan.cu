@@ -469,6 +469,26 @@ gdn_scan_bwd_kernel(const __grid_constant__ CUtensorMap tmWQ, const __grid_const
   }
 }
 
+// Gated linear attention only (no delta rule): a sequence cut into P segments can be scanned segment-parallel, because
+// the state transition of a segment is a scalar decay per head.  Given every segment's final state from a zero start
+// (`seg_state` [P, H, E]) and its per-chunk log-decays (`glast` [P, H, n_seg]), this writes the true incoming state of
+// every segment (`s_in` [P, H, E]) and the state after the last one (`s_out` [H, E]).
+__global__ void gla_segment_prefix_kernel(const float* __restrict__ seg_state, const float* __restrict__ glast,
+                                          const float* __restrict__ h0, float* __restrict__ s_in,
+                                          float* __restrict__ s_out, int P, int H, int n_seg, int E) {
+  const int h = blockIdx.y;
+  const int e = blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= E) return;
+  float s = h0 != nullptr ? h0[(size_t)h * E + e] : 0.f;
+  for (int p = 0; p < P; ++p) {
+    s_in[((size_t)p * H + h) * E + e] = s;
+    float ld = 0.f;
+    for (int n = 0; n < n_seg; ++n) ld += glast[((size_t)p * H + h) * n_seg + n];
+    s = __expf(ld) * s + seg_state[((size_t)p * H + h) * E + e];
+  }
+  s_out[(size_t)h * E + e] = s;
+}
+
 }  // namespace gdn
 }  // namespace hmf
 
@@ -538,6 +558,16 @@ HMF_API int hmf_gdn_scan_bwd(const void* wqT, const void* kPT, const void* d_o, 
   p.dhT_flag = dhT_flag; p.peer_dh0 = peer_dh0; p.peer_flag = peer_flag; p.epoch = epoch;
   p.status = status_ptr();
   gdn_scan_bwd_kernel<<<(unsigned)BH, 192, SMEM_BWD, stream>>>(tmWQ, tmKP, tmDO, p);
+  HMF_CHECK_CUDA(cudaGetLastError());
+  return HMF_OK;
+}
+
+// seg_state [P, H, E], glast [P, H, n_seg], h0 [H, E] or null -> s_in [P, H, E], s_out [H, E]   (all fp32, batch 1)
+HMF_API int hmf_gla_segment_prefix(const float* seg_state, const float* glast, const float* h0, float* s_in, float* s_out,
+                                   int P, int H, int n_seg, int E, cudaStream_t stream) {
+  HMF_REQUIRE(seg_state && glast && s_in && s_out && P > 0 && H > 0 && n_seg > 0 && E > 0, "gla_segment_prefix: bad arguments");
+  dim3 grid((E + 255) / 256, H);
+  gla_segment_prefix_kernel<<<grid, 256, 0, stream>>>(seg_state, glast, h0, s_in, s_out, P, H, n_seg, E);
   HMF_CHECK_CUDA(cudaGetLastError());
   return HMF_OK;
 }

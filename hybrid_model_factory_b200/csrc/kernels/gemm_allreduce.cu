@@ -48,6 +48,70 @@ struct Params {
   int M, N, Ks, Mpad, rank, world, tmem_cols, splits;
 };
 
+// Rank-ordered sum of every (rank, split) partial of one tile.  Remote loads take microseconds, so they go out in
+// batches before the first use: 8 partials of CU chunks at a time.  The sums are still taken in (rank, split) order,
+// so every rank gets the same bits.
+template <int CU>
+__device__ __forceinline__ void reduce_tile(const Params& p, int et, int chunks, int ksp, int n0, unsigned parity,
+                                            size_t split_elems) {
+  const int total = p.world * p.splits;
+  for (int c0 = et; c0 < chunks; c0 += 128 * CU) {
+    float acc[CU][8];
+    size_t off[CU];
+#pragma unroll
+    for (int q = 0; q < CU; ++q) {
+      const int c = c0 + q * 128;
+      const int m = ksp + (c / (BN / 8)) * p.splits, cc = (c % (BN / 8)) * 8;
+      off[q] = (size_t)m * p.N + n0 + cc;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[q][j] = 0.f;
+    }
+    for (int rs0 = 0; rs0 < total; rs0 += 8) {
+      uint4 u[CU][8];
+#pragma unroll
+      for (int q = 0; q < CU; ++q) {
+#pragma unroll
+        for (int b = 0; b < 8; ++b) {
+          const int rs = rs0 + b;
+          if (rs < total && c0 + q * 128 < chunks) {
+            const bf16* src = p.part[rs / p.splits] + (size_t)parity * p.part_stride + off[q] +
+                              (size_t)(rs % p.splits) * split_elems;
+            asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(u[q][b].x), "=r"(u[q][b].y), "=r"(u[q][b].z), "=r"(u[q][b].w)
+                         : "l"(src));
+          } else {
+            u[q][b] = make_uint4(0u, 0u, 0u, 0u);
+          }
+        }
+      }
+#pragma unroll
+      for (int q = 0; q < CU; ++q) {
+#pragma unroll
+        for (int b = 0; b < 8; ++b) {
+          const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&u[q][b]);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 f = __bfloat1622float2(h2[j]);
+            acc[q][2 * j] += f.x;
+            acc[q][2 * j + 1] += f.y;
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int q = 0; q < CU; ++q) {
+      if (c0 + q * 128 < chunks) {
+        uint4 o;
+        o.x = pack_bf16x2(acc[q][0], acc[q][1]);
+        o.y = pack_bf16x2(acc[q][2], acc[q][3]);
+        o.z = pack_bf16x2(acc[q][4], acc[q][5]);
+        o.w = pack_bf16x2(acc[q][6], acc[q][7]);
+        *reinterpret_cast<uint4*>(p.y + off[q]) = o;
+      }
+    }
+  }
+}
+
 __global__ void __launch_bounds__(192, 1)
 gemm_allreduce_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const Params p) {
   extern __shared__ uint8_t smem_raw[];
@@ -143,65 +207,10 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
     // every (rank, split) partial in a fixed order
     const int rows = (p.M - ksp + p.splits - 1) / p.splits;
     const int chunks = rows * (BN / 8);
-    // Remote loads take microseconds, so they go out in batches before the first use: 8 (rank, split) partials of
-    // CU chunks at a time (CU = 4: a 64-row tile at 8 ranks takes two rounds of remote latency).  The sums are still taken in (rank, split) order, so every rank gets the same bits.
-    constexpr int CU = 4;
-    const int total = p.world * p.splits;
-    for (int c0 = et; c0 < chunks; c0 += 128 * CU) {
-      float acc[CU][8];
-      size_t off[CU];
-#pragma unroll
-      for (int q = 0; q < CU; ++q) {
-        const int c = c0 + q * 128;
-        const int m = ksp + (c / (BN / 8)) * p.splits, cc = (c % (BN / 8)) * 8;
-        off[q] = (size_t)m * p.N + n0 + cc;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) acc[q][j] = 0.f;
-      }
-      for (int rs0 = 0; rs0 < total; rs0 += 8) {
-        uint4 u[CU][8];
-#pragma unroll
-        for (int q = 0; q < CU; ++q) {
-#pragma unroll
-          for (int b = 0; b < 8; ++b) {
-            const int rs = rs0 + b;
-            if (rs < total && c0 + q * 128 < chunks) {
-              const bf16* src = p.part[rs / p.splits] + (size_t)parity * p.part_stride + off[q] +
-                                (size_t)(rs % p.splits) * split_elems;
-              asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
-                           : "=r"(u[q][b].x), "=r"(u[q][b].y), "=r"(u[q][b].z), "=r"(u[q][b].w)
-                           : "l"(src));
-            } else {
-              u[q][b] = make_uint4(0u, 0u, 0u, 0u);
-            }
-          }
-        }
-#pragma unroll
-        for (int q = 0; q < CU; ++q) {
-#pragma unroll
-          for (int b = 0; b < 8; ++b) {
-            const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&u[q][b]);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const float2 f = __bfloat1622float2(h2[j]);
-              acc[q][2 * j] += f.x;
-              acc[q][2 * j + 1] += f.y;
-            }
-          }
-        }
-      }
-#pragma unroll
-      for (int q = 0; q < CU; ++q) {
-        if (c0 + q * 128 < chunks) {
-          uint4 o;
-          o.x = pack_bf16x2(acc[q][0], acc[q][1]);
-          o.y = pack_bf16x2(acc[q][2], acc[q][3]);
-          o.z = pack_bf16x2(acc[q][4], acc[q][5]);
-          o.w = pack_bf16x2(acc[q][6], acc[q][7]);
-          *reinterpret_cast<uint4*>(p.y + off[q]) = o;
-        }
-      }
-    }
+    // few chunks per thread (many K splits): two at a time; a whole 64-row tile per CTA (8 ranks, no splits): four, so
+    // the tile takes two rounds of remote latency instead of four
+    if (chunks > 256) reduce_tile<4>(p, et, chunks, ksp, n0, parity, split_elems);
+    else reduce_tile<2>(p, et, chunks, ksp, n0, parity, split_elems);
   }
 
   tc_fence_before();

@@ -32,6 +32,7 @@ C = 64
 # debugging aid: evaluate the chunk preparation with batched PyTorch ops instead of the CUDA kernel
 _FORCE_TORCH_PREP = os.environ.get("HMF_GDN_TORCH_PREP", "0") == "1"
 _USE_BWD_KERNEL = os.environ.get("HMF_GDN_BWD_KERNEL", "1") == "1"
+_GLA_SEGMENTS = os.environ.get("HMF_GLA_SEGMENTS", "1") == "1"      # segment-parallel inference scan (gla mode)
 
 
 def available() -> bool:
@@ -296,6 +297,11 @@ class GDNChunkCore(ScanCore):
         Dv = v.shape[-1]
         need_bwd = any(t is not None and t.requires_grad for t in inputs) or (
             state0 is not None and state0[0].requires_grad)
+        if (self.gla and not need_bwd and peer is None and B == 1 and T >= 2048 and 2 * H <= 148 and _GLA_SEGMENTS
+                and q.stride(3) == 1 and k.stride(3) == 1 and v.stride(3) == 1):
+            P = min(8, 148 // H, T // 512)
+            if P >= 2:
+                return self._forward_segmented(q, k, v, g, state0, P)
         with torch.no_grad():
             wqT, kPT, uT, glast, N = self._prep_packed(q, k, v, g, beta)
             h0 = None if state0 is None else state0[0].float().contiguous()
@@ -318,6 +324,46 @@ class GDNChunkCore(ScanCore):
         # the incoming state itself is not needed again: the backward kernel reads the per-chunk states
         saved = [q, k, v, g, beta, None, vnT, h_all]
         return o, (hT,), saved, ("cuda", h0 is not None)
+
+    def _scan(self, wqT, kPT, uT, glast, h0, hT, o, B, H, T, N, device):
+        _lib.check(_lib.kernels().hmf_gdn_scan_fwd(
+            _lib.ptr(wqT), _lib.ptr(kPT), _lib.ptr(uT), _lib.ptr(glast), _lib.ptr(h0), _lib.ptr(hT), _lib.ptr(o), None,
+            None, c_int(B), c_int(H), c_int(T), c_int(N), None, None, None, c_uint(0), _lib.stream_ptr(device)),
+            "hmf_gdn_scan_fwd")
+
+    def _forward_segmented(self, q, k, v, g, state0, P):
+        """Inference forward of plain gated linear attention (Mamba2 SSD, GLA) for one long sequence and few heads:
+        the scan kernel runs one CTA per (batch, head), so 4 heads of a tensor-parallel shard would use 4 of 148 SMs.
+        The sequence is cut into ``P`` equal segments scanned as a batch from a zero state, a prefix kernel turns the
+        segment states into every segment's true incoming state, and the batch is scanned again from those; a tail
+        shorter than a segment follows on its own."""
+        _, T, H, Dk = q.shape
+        Dv = v.shape[-1]
+        L = (T // P) // C * C
+        main, dev = P * L, q.device
+        with torch.no_grad():
+            def seg(t):         # [1, T, ...] -> [P, L, ...] without copying
+                return t.as_strided((P, L) + tuple(t.shape[2:]), (L * t.stride(1),) + tuple(t.stride()[1:]),
+                                    t.storage_offset())
+            g32 = g.float()
+            wqT, kPT, uT, glast, N = self._prep_packed(seg(q), seg(k), seg(v), seg(g32), None)
+            o = torch.empty(1, T, H, Dv, device=dev, dtype=BF16)
+            seg_state = torch.empty(P, H, Dk, Dv, device=dev, dtype=torch.float32)
+            self._scan(wqT, kPT, uT, glast, None, seg_state, o, P, H, L, N, dev)           # pass 1: zero start
+            h0 = None if state0 is None else state0[0].float().contiguous()
+            s_in = torch.empty_like(seg_state)
+            hT = torch.empty(1, H, Dk, Dv, device=dev, dtype=torch.float32)
+            _lib.check(_lib.kernels().hmf_gla_segment_prefix(
+                _lib.ptr(seg_state), _lib.ptr(glast), _lib.ptr(h0), _lib.ptr(s_in), _lib.ptr(hT), c_int(P), c_int(H),
+                c_int(N), c_int(Dk * Dv), _lib.stream_ptr(dev)), "gla_segment_prefix")
+            self._scan(wqT, kPT, uT, glast, s_in, seg_state, o, P, H, L, N, dev)          # pass 2: true states
+            if main < T:
+                tail = slice(main, T)
+                wq2, kP2, u2, gl2, N2 = self._prep_packed(q[:, tail], k[:, tail], v[:, tail], g32[:, tail], None)
+                hT2 = torch.empty_like(hT)
+                self._scan(wq2, kP2, u2, gl2, hT, hT2, o[:, tail], 1, H, T - main, N2, dev)
+                hT = hT2
+        return o, (hT,), [q, k, v, g, None, None, None, None], ("cuda", state0 is not None)
 
     def backward(self, saved, meta, d_out, d_stateT, peer=None):
         kind, info = meta

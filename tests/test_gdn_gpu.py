@@ -170,3 +170,28 @@ def test_gka_chebyshev_implicit_backward_matches_autograd_through_the_iteration(
     assert rel(kk.grad, kr.grad) < 8e-2, rel(kk.grad, kr.grad)
     assert rel(gkk.grad, gr.grad) < 8e-2, rel(gkk.grad, gr.grad)
     assert rel(hk.grad, hr.grad) < 8e-2, rel(hk.grad, hr.grad)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("T,H,with_state", [(5000, 4, True), (4096, 8, False), (2500, 2, True)])
+def test_gla_segment_parallel_inference_scan_matches_sequential(T, H, with_state):
+    """Few heads, one long sequence: the segment-parallel forward (two batched scans + state prefix + tail) against
+    the one-CTA-per-head scan of the same kernels."""
+    from hybrid_model_factory_b200.ops import gdn_cuda
+    torch.manual_seed(0)
+    D = 128
+    q, k, v = (torch.randn(1, T, H, D, device="cuda").bfloat16() * 0.5 for _ in range(3))
+    g = -torch.rand(1, T, H, device="cuda") * 0.05
+    s0 = (torch.randn(1, H, D, D, device="cuda") * 0.1,) if with_state else None
+    core = gdn_cuda.GDNChunkCore(scale=D ** -0.5, use_qk_l2norm=False, gla=True)
+    with torch.no_grad():
+        o_seg, (h_seg,), _, _ = core.forward((q, k, v, g, None), s0)
+        old = gdn_cuda._GLA_SEGMENTS
+        gdn_cuda._GLA_SEGMENTS = False
+        try:
+            o_ref, (h_ref,), _, _ = core.forward((q, k, v, g, None), s0)
+        finally:
+            gdn_cuda._GLA_SEGMENTS = old
+    torch.cuda.synchronize()
+    assert (o_seg.float() - o_ref.float()).abs().max() < 2e-2 * o_ref.float().abs().max() + 1e-2
+    assert (h_seg - h_ref).abs().max() < 2e-2 * h_ref.abs().max() + 1e-2
