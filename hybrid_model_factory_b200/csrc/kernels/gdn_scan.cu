@@ -475,18 +475,20 @@ gdn_scan_bwd_kernel(const __grid_constant__ CUtensorMap tmWQ, const __grid_const
 // every segment (`s_in` [P, H, E]) and the state after the last one (`s_out` [H, E]).
 __global__ void gla_segment_prefix_kernel(const float* __restrict__ seg_state, const float* __restrict__ glast,
                                           const float* __restrict__ h0, float* __restrict__ s_in,
-                                          float* __restrict__ s_out, int P, int H, int n_seg, int E) {
+                                          float* __restrict__ s_out, int P, int n_seg, int E, long long st_p,
+                                          long long st_h, long long gl_p, long long gl_h, long long in_p, long long in_h,
+                                          long long out_h) {
   const int h = blockIdx.y;
   const int e = blockIdx.x * blockDim.x + threadIdx.x;
   if (e >= E) return;
   float s = h0 != nullptr ? h0[(size_t)h * E + e] : 0.f;
   for (int p = 0; p < P; ++p) {
-    s_in[((size_t)p * H + h) * E + e] = s;
+    s_in[(size_t)p * in_p + (size_t)h * in_h + e] = s;
     float ld = 0.f;
-    for (int n = 0; n < n_seg; ++n) ld += glast[((size_t)p * H + h) * n_seg + n];
-    s = __expf(ld) * s + seg_state[((size_t)p * H + h) * E + e];
+    for (int n = 0; n < n_seg; ++n) ld += glast[(size_t)p * gl_p + (size_t)h * gl_h + n];
+    s = __expf(ld) * s + seg_state[(size_t)p * st_p + (size_t)h * st_h + e];
   }
-  s_out[(size_t)h * E + e] = s;
+  s_out[(size_t)h * out_h + e] = s;
 }
 
 }  // namespace gdn
@@ -562,12 +564,17 @@ HMF_API int hmf_gdn_scan_bwd(const void* wqT, const void* kPT, const void* d_o, 
   return HMF_OK;
 }
 
-// seg_state [P, H, E], glast [P, H, n_seg], h0 [H, E] or null -> s_in [P, H, E], s_out [H, E]   (all fp32, batch 1)
+// Segment s of head h: state contribution seg_state[s * st_p + h * st_h + e] (e < E), log-decays
+// glast[s * gl_p + h * gl_h + n] (n < n_seg); h0 [H, E] or null.  Writes the incoming state of every segment to
+// s_in[s * in_p + h * in_h + e] and the state after the last one to s_out[h * out_h + e].  All fp32.
 HMF_API int hmf_gla_segment_prefix(const float* seg_state, const float* glast, const float* h0, float* s_in, float* s_out,
-                                   int P, int H, int n_seg, int E, cudaStream_t stream) {
+                                   int P, int H, int n_seg, int E, long long st_p, long long st_h, long long gl_p,
+                                   long long gl_h, long long in_p, long long in_h, long long out_h, cudaStream_t stream) {
   HMF_REQUIRE(seg_state && glast && s_in && s_out && P > 0 && H > 0 && n_seg > 0 && E > 0, "gla_segment_prefix: bad arguments");
+  HMF_REQUIRE(H <= 65535, "gla_segment_prefix: too many heads");
   dim3 grid((E + 255) / 256, H);
-  gla_segment_prefix_kernel<<<grid, 256, 0, stream>>>(seg_state, glast, h0, s_in, s_out, P, H, n_seg, E);
+  gla_segment_prefix_kernel<<<grid, 256, 0, stream>>>(seg_state, glast, h0, s_in, s_out, P, n_seg, E, st_p, st_h, gl_p, gl_h,
+                                                      in_p, in_h, out_h);
   HMF_CHECK_CUDA(cudaGetLastError());
   return HMF_OK;
 }

@@ -353,9 +353,11 @@ class GDNChunkCore(ScanCore):
             h0 = None if state0 is None else state0[0].float().contiguous()
             s_in = torch.empty_like(seg_state)
             hT = torch.empty(1, H, Dk, Dv, device=dev, dtype=torch.float32)
+            E, ll = Dk * Dv, ctypes.c_longlong
             _lib.check(_lib.kernels().hmf_gla_segment_prefix(
                 _lib.ptr(seg_state), _lib.ptr(glast), _lib.ptr(h0), _lib.ptr(s_in), _lib.ptr(hT), c_int(P), c_int(H),
-                c_int(N), c_int(Dk * Dv), _lib.stream_ptr(dev)), "gla_segment_prefix")
+                c_int(N), c_int(E), ll(H * E), ll(E), ll(H * N), ll(N), ll(H * E), ll(E), ll(E),
+                _lib.stream_ptr(dev)), "gla_segment_prefix")
             self._scan(wqT, kPT, uT, glast, s_in, seg_state, o, P, H, L, N, dev)          # pass 2: true states
             if main < T:
                 tail = slice(main, T)

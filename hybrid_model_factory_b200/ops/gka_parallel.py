@@ -24,6 +24,21 @@ def chunk_states(k: Tensor, G: Tensor, H0: Optional[Tensor]) -> Tensor:
     Glast = G[..., -1]                                            # [B,H,N]
     kdec = k * torch.exp(Glast[..., None] - G)[..., None]
     U = kdec.transpose(-1, -2) @ k                                # [B,H,N,D,D] contribution of chunk m at its end
+    if k.is_cuda and not torch.is_grad_enabled() and B * Hh <= 65535:
+        # no graph to record: one pass of the decayed prefix-sum kernel instead of the [N+1, N] weight product
+        import ctypes
+        from . import _lib
+        if _lib.use_cuda_kernels(k):
+            U = U.contiguous()
+            gl = Glast.float().contiguous()
+            h0 = None if H0 is None else H0.float().contiguous()
+            states = torch.empty(B, Hh, N + 1, D, D, device=k.device, dtype=torch.float32)
+            E, ll = D * D, ctypes.c_longlong
+            _lib.check(_lib.kernels().hmf_gla_segment_prefix(
+                _lib.ptr(U), _lib.ptr(gl), _lib.ptr(h0), _lib.ptr(states), ctypes.c_void_p(states.data_ptr() + N * E * 4),
+                ctypes.c_int(N), ctypes.c_int(B * Hh), ctypes.c_int(1), ctypes.c_int(E), ll(E), ll(N * E), ll(1), ll(N),
+                ll(E), ll((N + 1) * E), ll((N + 1) * E), _lib.stream_ptr(k.device)), "gla_segment_prefix")
+            return states
     tot = torch.cumsum(Glast, dim=-1)                             # log decay up to the end of chunk m
     tot0 = torch.cat([torch.zeros_like(tot[..., :1]), tot], dim=-1)          # [B,H,N+1]: up to the start of chunk n
     # state_n = e^{tot0_n} H0 + sum_{m<n} e^{tot0_n - tot_m} U_m
