@@ -55,6 +55,19 @@ class Attention(nn.Module):
             q = q.view(B, T, self.num_heads, self.head_dim)
         k = self.k_proj(hidden_states).view(B, T, self.num_kv_heads, self.head_dim)
         v = self.v_proj(hidden_states).view(B, T, self.num_kv_heads, self.head_dim)
+        if not self.gated and q.is_cuda and (self.q_norm is not None or position_embeddings is not None):
+            from ..ops import cuda_ops
+            if cuda_ops.heads_norm_rope_ok(q, self.head_dim, position_embeddings):
+                # inference: per-head norm + rotary of q and of k in one launch each
+                qn, kn = self.q_norm, self.k_norm
+                eps = 0.0 if qn is None else qn.variance_epsilon
+                zc = False if qn is None else qn.zero_centered
+                q = cuda_ops.heads_norm_rope(q.reshape(B, T, -1), 0, self.num_heads, 0, None if qn is None else qn.weight,
+                                             None, eps, zc, position_embeddings).view(B, T, self.num_heads, self.head_dim)
+                k = cuda_ops.heads_norm_rope(k.reshape(B, T, -1), 0, self.num_kv_heads, 0,
+                                             None if kn is None else kn.weight, None, eps, zc,
+                                             position_embeddings).view(B, T, self.num_kv_heads, self.head_dim)
+                return q, k, v, gate
         if self.q_norm is not None:
             q, k = self.q_norm(q), self.k_norm(k)
         if position_embeddings is not None:

@@ -95,6 +95,15 @@ class Mamba2(nn.Module):
 
     def _norm_rope(self, xBC, position_embeddings):
         Bsz, T, _ = xBC.shape
+        pe = position_embeddings if self.use_pos_emb else None
+        if xBC.is_cuda and self.headdim == 128 and self.d_xb % 128 == 0 and self.d_state == 128:
+            from ..ops import cuda_ops
+            if cuda_ops.heads_norm_rope_ok(xBC, self.headdim, pe):       # inference: one kernel for the whole method
+                bn = self.B_norm
+                return cuda_ops.heads_norm_rope(
+                    xBC, self.d_xb // 128, self.d_xb // 128, self.d_inner // 128, None if bn is None else bn.weight,
+                    None if bn is None else self.C_norm.weight, 0.0 if bn is None else bn.variance_epsilon,
+                    False if bn is None else bn.zero_centered, pe)
         x, Bm, Cm = torch.split(xBC, [self.d_xb, self.d_xb, self.d_inner], dim=-1)
         Bm = Bm.reshape(Bsz, T, -1, self.headdim)
         Cm = Cm.reshape(Bsz, T, -1, self.headdim)

@@ -219,6 +219,64 @@ def apply_rope(x: Tensor, cos: Tensor, sin: Tensor) -> Tensor:
     return _apply(_RoPE, x, cos, sin)
 
 
+def rope_tables_bf16(position_embeddings, lead_shape):
+    """``(cos, sin)`` as contiguous bf16 ``[rows, rot]`` tables for ``rows = prod(lead_shape)`` tokens; converted once
+    per forward pass (the result is cached on the ``cos`` tensor, which every layer of the pass receives)."""
+    cos, sin = position_embeddings
+    rows = 1
+    for d in lead_shape:
+        rows *= int(d)
+    cached = getattr(cos, "_hmf_bf16_tables", None)
+    if cached is not None and cached[0].shape[0] == rows:
+        return cached
+    rot = cos.shape[-1]
+    cs = cos.expand(*lead_shape, rot).to(BF16).reshape(rows, rot).contiguous()
+    sn = sin.expand(*lead_shape, rot).to(BF16).reshape(rows, rot).contiguous()
+    cos._hmf_bf16_tables = (cs, sn)
+    return cs, sn
+
+
+def heads_norm_rope_ok(x: Tensor, head_dim: int, position_embeddings) -> bool:
+    """The fused inference kernel applies: no autograd graph, bf16 on the GPU, heads of 128 channels, even rotary
+    width."""
+    if torch.is_grad_enabled() or not x.is_cuda or x.dtype != BF16 or head_dim != 128 or x.stride(-1) != 1:
+        return False
+    if position_embeddings is not None and position_embeddings[0].shape[-1] % 2 != 0:
+        return False
+    return _lib.use_cuda_kernels(x)
+
+
+def heads_norm_rope(x: Tensor, n_plain: int, n_b: int, n_c: int, wb: Optional[Tensor], wc: Optional[Tensor], eps: float,
+                    zero_centered: bool, position_embeddings) -> Tensor:
+    """``x [..., (n_plain + n_b + n_c) * 128]`` (the last dimension may be a column slice of a wider tensor): the first
+    ``n_plain`` heads are copied, the next ``n_b`` / ``n_c`` heads get RMSNorm with ``wb`` / ``wc`` (or none) and the
+    rotary embedding; returns a contiguous tensor of the same shape.  One launch instead of split, two norms, two
+    rotations and a concatenation (``csrc/kernels/decode_fused.cu::heads_norm_rope_kernel``)."""
+    lead, cols = x.shape[:-1], x.shape[-1]
+    assert cols == (n_plain + n_b + n_c) * 128
+    rows = 1
+    for d in lead:
+        rows *= int(d)
+    x2 = x.reshape(rows, cols)
+    if x2.stride(1) != 1 or x2.stride(0) % 8 != 0:
+        x2 = x2.contiguous()
+    out = torch.empty(rows, cols, device=x.device, dtype=BF16)
+    cs = sn = None
+    rot = 0
+    if position_embeddings is not None:
+        cs, sn = rope_tables_bf16(position_embeddings, lead)
+        rot = cs.shape[-1]
+    if wb is not None and wc is None:
+        wc = wb
+    if wc is not None and wb is None:
+        wb = wc
+    _lib.check(_K().hmf_heads_norm_rope(_lib.ptr(x2), c_ll(x2.stride(0)), _lib.ptr(out), c_ll(cols), c_int(n_plain),
+                                        c_int(n_b), c_int(n_c), _lib.ptr(wb), _lib.ptr(wc), c_float(eps),
+                                        c_int(int(zero_centered)), _lib.ptr(cs), _lib.ptr(sn), c_int(rot), c_int(rows),
+                                        _st(x)), "heads_norm_rope")
+    return out.view(*lead, cols)
+
+
 # ----------------------------------------------------------------------------------------
 # gating (tiny [T, H] tensors: plain PyTorch elementwise math)
 # ----------------------------------------------------------------------------------------

@@ -245,10 +245,23 @@ class Zero3Engine:
         self.step_count += 1
         b1, b2 = self.betas
         bc1, bc2 = 1 - b1 ** self.step_count, 1 - b2 ** self.step_count
+        fused = (not self.offload) and dev.type == "cuda" and _lib.kernels_available()
         for u in self.units:
             if u.grad_shard is None:
                 continue
             st = self.state[u.name]
+            if fused:       # the flat fused AdamW kernel of the ZeRO-2 optimizer, one launch per decay class
+                from ..ops import cuda_ops
+                lo = u.rank * u.shard_len
+                cut = min(max(u.n_decay - lo, 0), u.shard_len)
+                for a, b_, wd in ((0, cut, self.weight_decay), (cut, u.shard_len, 0.0)):
+                    if b_ > a:
+                        cuda_ops.adamw_step(u.shard[a:b_], u.grad_shard[a:b_], st["m"][a:b_], st["v"][a:b_], lr=lr,
+                                            beta1=b1, beta2=b2, eps=self.eps, weight_decay=wd, step=self.step_count,
+                                            master=st["master"][a:b_], norm_sq=sq, max_norm=self.max_grad_norm,
+                                            grad_scale=gscale)
+                u.grad_shard = None
+                continue
             m, v, master = (st[k].to(u.device, non_blocking=True) if self.offload else st[k] for k in ("m", "v", "master"))
             g = u.grad_shard.float() * scale
             mf = m.float().mul_(b1).add_(g, alpha=1 - b1)
