@@ -65,15 +65,20 @@ def _kernel_ok(q: Tensor, k: Tensor, gk: Optional[Tensor], chunk_size: int) -> b
 
 def _solve_kernel(q: Tensor, k: Tensor, gk: Optional[Tensor], states: Tensor, ridge_ratio: float, num_iter: int,
                   N: int) -> Tensor:
-    """``csrc/kernels/gka_cheb.cu``: one CTA per (chunk, head); ``states [B,H,N+1,D,D]`` fp32 contiguous."""
+    """One CTA per (chunk, head); ``states [B,H,N+1,D,D]`` fp32 contiguous.  ``csrc/kernels/gka_cheb_tc.cu`` (tcgen05,
+    operands read from shared memory by the tensor core, accumulators in tensor memory) unless ``HMF_GKA_TC=0``
+    selects the warp-level MMA version ``csrc/kernels/gka_cheb.cu``."""
     import ctypes
+    import os
     from . import _lib
+    fn = (_lib.kernels().hmf_gka_cheb_fwd_tc if os.environ.get("HMF_GKA_TC", "1") == "1"
+          else _lib.kernels().hmf_gka_cheb_fwd)
     B, T, Hh, D = q.shape
     g = None if gk is None else gk.float().contiguous()
     states = states.contiguous()
     x = torch.empty(B, T, Hh, D, device=q.device, dtype=torch.float32)
     ll = ctypes.c_longlong
-    _lib.check(_lib.kernels().hmf_gka_cheb_fwd(
+    _lib.check(fn(
         _lib.ptr(q), _lib.ptr(k), _lib.ptr(g), _lib.ptr(states), _lib.ptr(x), ctypes.c_int(B), ctypes.c_int(T),
         ctypes.c_int(Hh), ctypes.c_int(N), ctypes.c_int(states.shape[2]), ll(q.stride(0)), ll(q.stride(1)),
         ll(q.stride(2)), ll(k.stride(0)), ll(k.stride(1)), ll(k.stride(2)), ctypes.c_float(ridge_ratio),
