@@ -30,7 +30,7 @@ constexpr int OFF_P = OFF_X + 2 * X_BLK;            //  8 KB  [j][i] bf16, one 1
 constexpr int OFF_Q = OFF_P + C * 128;              // 16 KB  q as bf16 [i][d] (plain)
 constexpr int OFF_SMALL = OFF_Q + C * D * 2;
 constexpr int GR_LD = C + 1;                        // fp32 Gram scratch [64][65] lives in X + P before the loop
-constexpr int SMEM_BYTES = OFF_SMALL + 12 * C * 4 + 128;
+constexpr int SMEM_BYTES = OFF_SMALL + 15 * C * 4 + 128;
 static_assert(C * GR_LD * 4 <= 2 * X_BLK + C * 128, "Gram scratch must fit into the x and P tiles");
 static_assert(SMEM_BYTES <= 113 * 1024, "two CTAs per SM");
 
@@ -64,11 +64,12 @@ __global__ void __launch_bounds__(NT, 2) gka_cheb_tc_kernel(const Params p) {
   float* s_lam = small + 2 * C;
   float* s_step = small + 3 * C;
   float* s_c = small + 4 * C;
-  float* s_om = small + 5 * C;       // [2][C]
-  float* s_khk = small + 7 * C;
-  float* s_fro = small + 8 * C;
-  float* s_red = small + 9 * C;      // [8] warp partials, [8] total
-  uint64_t* bar = reinterpret_cast<uint64_t*>(small + 10 * C);
+  float* s_om = small + 5 * C;       // Chebyshev weight of the previous step
+  float* s_coef = small + 6 * C;     // [2][3][C]
+  float* s_khk = small + 12 * C;
+  float* s_fro = small + 13 * C;
+  float* s_red = small + 14 * C;     // [8] warp partials, [8] total
+  uint64_t* bar = reinterpret_cast<uint64_t*>(small + 15 * C);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -233,8 +234,16 @@ __global__ void __launch_bounds__(NT, 2) gka_cheb_tc_kernel(const Params p) {
     *reinterpret_cast<bf16*>(sX + kmajor_off(i, d, X_BLK)) = __float2bfloat16(x[c]);
   }
   for (int it = 0; it < p.num_iter; ++it) {
-    const float* om_old = s_om + (it & 1) * C;
-    float* om_new = s_om + ((it + 1) & 1) * C;
+    // per-token coefficients of this step, double-buffered by parity (the other buffer may still be read by threads
+    // that have not left the previous step): om, step * om, om - 1
+    float* coef = s_coef + (it & 1) * 3 * C;
+    if (tid < C) {
+      const float om = 1.f / (1.f - s_c[tid] * s_om[tid]);
+      s_om[tid] = om;
+      coef[tid] = om;
+      coef[C + tid] = s_step[tid] * om;
+      coef[2 * C + tid] = om - 1.f;
+    }
     fence_async_smem();
     tc_fence_before();
     __syncthreads();
@@ -245,23 +254,25 @@ __global__ void __launch_bounds__(NT, 2) gka_cheb_tc_kernel(const Params p) {
     ok = mbar_wait(bar, phase, ctx, 0xC20);
     phase ^= 1u;
     tc_fence_after();
-    uint32_t r[32];
-    if (ok && d < C) {       // P row j = d: 32 columns = four 16-byte chunks of the row
-      tmem_ld_x32(tS + lane_bits + i0, r);
-      tmem_ld_wait();
+    if (ok && d < C) {       // P row j = d: 32 columns = four 16-byte chunks of the row, 16 columns at a time
       const float gj = s_G[d];
-      uint32_t w[16];
 #pragma unroll
-      for (int c = 0; c < 32; c += 2) {
-        const int i = i0 + c;
-        const float m0 = d <= i ? __expf(s_G[i] - gj) : 0.f;
-        const float m1 = d <= i + 1 ? __expf(s_G[i + 1] - gj) : 0.f;
-        w[c >> 1] = pack_bf16x2(__uint_as_float(r[c]) * m0, __uint_as_float(r[c + 1]) * m1);
+      for (int half = 0; half < 2; ++half) {
+        uint32_t r[16], w[8];
+        tmem_ld_x16(tS + lane_bits + i0 + 16 * half, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int c = 0; c < 16; c += 2) {
+          const int i = i0 + 16 * half + c;
+          const float m0 = d <= i ? __expf(s_G[i] - gj) : 0.f;
+          const float m1 = d <= i + 1 ? __expf(s_G[i + 1] - gj) : 0.f;
+          w[c >> 1] = pack_bf16x2(__uint_as_float(r[c]) * m0, __uint_as_float(r[c + 1]) * m1);
+        }
+#pragma unroll
+        for (int q4 = 0; q4 < 2; ++q4)
+          *reinterpret_cast<uint4*>(sP + sw128_offset((uint32_t)d, (uint32_t)(i0 * 2 + half * 32 + q4 * 16))) =
+              make_uint4(w[q4 * 4], w[q4 * 4 + 1], w[q4 * 4 + 2], w[q4 * 4 + 3]);
       }
-#pragma unroll
-      for (int q4 = 0; q4 < 4; ++q4)
-        *reinterpret_cast<uint4*>(sP + sw128_offset((uint32_t)d, (uint32_t)(i0 * 2 + q4 * 16))) =
-            make_uint4(w[q4 * 4], w[q4 * 4 + 1], w[q4 * 4 + 2], w[q4 * 4 + 3]);
     }
     fence_async_smem();
     tc_fence_before();
@@ -278,23 +289,21 @@ __global__ void __launch_bounds__(NT, 2) gka_cheb_tc_kernel(const Params p) {
     phase ^= 1u;
     tc_fence_after();
 #pragma unroll
-    for (int half = 0; half < 2; ++half) {       // 16 token columns at a time keeps the register count under 128
-      uint32_t r1[16], r2[16];
+    for (int part = 0; part < 4; ++part) {       // 8 token columns at a time keeps the register count under 128
+      uint32_t r1[8], r2[8];
       if (ok) {
-        tmem_ld_x16(tT1 + lane_bits + i0 + 16 * half, r1);
-        tmem_ld_x16(tT2 + lane_bits + i0 + 16 * half, r2);
+        tmem_ld_x8(tT1 + lane_bits + i0 + 8 * part, r1);
+        tmem_ld_x8(tT2 + lane_bits + i0 + 8 * part, r2);
         tmem_ld_wait();
       }
 #pragma unroll
-      for (int cc = 0; cc < 16; ++cc) {
-        const int c = 16 * half + cc, i = i0 + c;
+      for (int cc = 0; cc < 8; ++cc) {
+        const int c = 8 * part + cc, i = i0 + c;
         const float hx = s_eg[i] * __uint_as_float(r1[cc]) + __uint_as_float(r2[cc]);
-        const float om = 1.f / (1.f - s_c[i] * om_old[i]);
-        const float upd = s_step[i] * om * (hx + s_lam[i] * x[c] - __bfloat162float(sQ[i * D + d])) + (om - 1.f) * xp[c];
+        const float upd = coef[C + i] * (hx + s_lam[i] * x[c] - __bfloat162float(sQ[i * D + d])) + coef[2 * C + i] * xp[c];
         xp[c] = x[c];
-        x[c] = om * x[c] - upd;
+        x[c] = coef[i] * x[c] - upd;
         *reinterpret_cast<bf16*>(sX + kmajor_off(i, d, X_BLK)) = __float2bfloat16(x[c]);
-        if (d == 0) om_new[i] = om;
       }
     }
   }
