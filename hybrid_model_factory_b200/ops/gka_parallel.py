@@ -86,7 +86,8 @@ def _solve_kernel(q: Tensor, k: Tensor, gk: Optional[Tensor], states: Tensor, ri
     return x
 
 
-def _chunk_layout(q: Optional[Tensor], k: Tensor, gk: Optional[Tensor], initial_state: Optional[Tensor], chunk_size: int):
+def _chunk_layout(q: Optional[Tensor], k: Tensor, gk: Optional[Tensor], initial_state: Optional[Tensor], chunk_size: int,
+                  need_mask: bool = True):
     """Pads to whole chunks and returns ``(qf, kf [B,H,N,C,D] fp32, G [B,H,N,C], m [B,H,N,C,C], states, N)``."""
     B, T, Hh, D = k.shape
     C = chunk_size
@@ -103,10 +104,12 @@ def _chunk_layout(q: Optional[Tensor], k: Tensor, gk: Optional[Tensor], initial_
         qf = qf.view(B, N, C, Hh, D).permute(0, 3, 1, 2, 4)       # [B,H,N,C,D]
     kf = kf.view(B, N, C, Hh, D).permute(0, 3, 1, 2, 4)
     G = gf.view(B, N, C, Hh).permute(0, 3, 1, 2).cumsum(-1)       # [B,H,N,C]
-    idx = torch.arange(C, device=k.device)
-    lower = idx[:, None] >= idx[None, :]
-    diff = G[..., :, None] - G[..., None, :]
-    m = torch.where(lower, torch.exp(torch.where(lower, diff, torch.zeros_like(diff))), torch.zeros_like(diff))
+    m = None
+    if need_mask:
+        idx = torch.arange(C, device=k.device)
+        lower = idx[:, None] >= idx[None, :]
+        diff = G[..., :, None] - G[..., None, :]
+        m = torch.where(lower, torch.exp(torch.where(lower, diff, torch.zeros_like(diff))), torch.zeros_like(diff))
     H0 = None if initial_state is None else initial_state.float()
     states = chunk_states(kf, G, H0)
     return qf, kf, G, m, states, N
@@ -136,10 +139,12 @@ def chebyshev_chunk_parallel(q: Tensor, k: Tensor, gk: Optional[Tensor], *, ridg
     """Returns ``(x [B,T,H,D] fp32, H_T [B,H,D,D] fp32)``; see ``ops.reference.gka_chebyshev_chunk``."""
     B, T, Hh, D = q.shape
     C = chunk_size
-    qf, kf, G, m, states, N = _chunk_layout(q, k, gk, initial_state, chunk_size)
     if _kernel_ok(q, k, gk, chunk_size):
-        # inference / first pass of a checkpointed layer: the whole per-chunk solve runs in one kernel
+        # no graph to record (inference, forward of the scan core): the whole per-chunk solve runs in one kernel,
+        # which builds the decay mask and reads q itself; only the chunk-start states are prepared here
+        _, _, _, _, states, N = _chunk_layout(None, k, gk, initial_state, chunk_size, need_mask=False)
         return _solve_kernel(q, k, gk, states, ridge_ratio, num_iter, N), states[:, :, N]
+    qf, kf, G, m, states, N = _chunk_layout(q, k, gk, initial_state, chunk_size)
     Hs = states[:, :, :N]                                         # [B,H,N,D,D]
     eg = torch.exp(G)[..., None]                                  # [B,H,N,C,1]
     fro = _fro(kf, G, m, Hs)
