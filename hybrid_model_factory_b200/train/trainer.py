@@ -148,7 +148,10 @@ class Trainer:
         self.optimizer.zero_grad()
         dev = self._to_device(batch)
         total = None
-        bsz = dev["input_ids"].shape[0]
+        # preference batches carry chosen_* / rejected_* tensors instead of input_ids
+        first = dev["input_ids"] if "input_ids" in dev else next(v for v in dev.values() if isinstance(v, torch.Tensor)
+                                                                   and v.dim() > 0)
+        bsz = first.shape[0]
         micro = max(1, bsz // ga)
         for i in range(0, bsz, micro):
             mb = {k: (v[i:i + micro] if isinstance(v, torch.Tensor) and v.dim() > 0 and v.shape[0] == bsz else v)
@@ -160,7 +163,8 @@ class Trainer:
                     self.args.max_steps)
         self.optimizer.step(lr)
         self.global_step += 1
-        self.tokens_seen += int(dev["input_ids"].numel()) * self.world
+        self.tokens_seen += sum(int(v.numel()) for k, v in dev.items()
+                                if isinstance(v, torch.Tensor) and k.endswith("input_ids")) * self.world
         self._last_lr = lr
         return total
 

@@ -138,3 +138,68 @@ def test_preference_feedback_and_tool_data_processing(tmp_path):
     ds = get_dataset(DataArguments(dataset="prefs", dataset_dir=str(tmp_path), template="qwen3", cutoff_len=128), tok,
                      stage="dpo")
     assert len(ds) == 4 and "rejected_labels" in ds[0]
+
+
+@pytest.mark.parametrize("extra", [
+    {"use_galore": True, "galore_rank": 4, "galore_update_interval": 2},
+    {"use_adam_mini": True},
+    {"finetuning_type": "oft", "lora_target": "q_proj,o_proj", "oft_block_size": 16},
+    {"deepspeed": "z3"},
+])
+def test_training_options_run_end_to_end(tmp_path, extra):
+    """`hmf train` configurations beyond the default optimizer: each runs a few steps, lowers the loss and saves a
+    loadable final checkpoint."""
+    from hybrid_model_factory_b200.utils import checkpoint_io
+    out = str(tmp_path / "run")
+    extra = dict(extra)
+    if extra.get("deepspeed") == "z3":
+        js = tmp_path / "ds_z3.json"
+        js.write_text(json.dumps({"zero_optimization": {"stage": 3}}))
+        extra["deepspeed"] = str(js)
+    cfg = {"model_name_or_path": json.dumps(TINY), "stage": "pt", "synthetic": True, "cutoff_len": 32,
+           "max_steps": 6, "output_dir": out, "bf16": False, "pure_bf16": False, "learning_rate": 3e-3,
+           "lr_scheduler_type": "constant", "per_device_train_batch_size": 2, **extra}
+    tr = run_exp(cfg)
+    assert tr.global_step == 6
+    log = [json.loads(l) for l in open(os.path.join(out, "trainer_log.jsonl"))]
+    assert log[-1]["loss"] < log[0]["loss"] + 0.2, [r["loss"] for r in log]
+    model = checkpoint_io.from_pretrained(os.path.join(out, "final"))
+    assert all(p.numel() > 0 and torch.isfinite(p).all() for p in model.parameters())
+    assert not any("oft" in n or "lora" in n for n, _ in model.named_parameters())
+
+
+def test_dpo_stage_on_a_ranking_dataset(tmp_path):
+    (tmp_path / "dataset_info.json").write_text(json.dumps({"prefs": {"file_name": "prefs.json", "ranking": True}}))
+    (tmp_path / "prefs.json").write_text(json.dumps(
+        [{"instruction": f"question {i}", "chosen": "a good answer", "rejected": "bad"} for i in range(8)]))
+    out = str(tmp_path / "run")
+    cfg = {"model_name_or_path": json.dumps(TINY), "stage": "dpo", "dataset": "prefs", "dataset_dir": str(tmp_path),
+           "template": "qwen3", "cutoff_len": 96, "max_steps": 3, "output_dir": out, "bf16": False, "pure_bf16": False,
+           "learning_rate": 1e-3, "lr_scheduler_type": "constant", "per_device_train_batch_size": 2}
+    tr = run_exp(cfg)
+    assert tr.global_step == 3
+    log = [json.loads(l) for l in open(os.path.join(out, "trainer_log.jsonl"))]
+    assert all(torch.isfinite(torch.tensor(r["loss"])) for r in log)
+
+
+@pytest.mark.parametrize("stage", ["rm", "kto"])
+def test_rm_and_kto_stages(tmp_path, stage):
+    rows = ([{"instruction": f"q{i}", "chosen": "good answer", "rejected": "bad"} for i in range(8)] if stage == "rm" else
+            [{"instruction": f"q{i}", "output": "answer", "kto_tag": i % 2 == 0} for i in range(8)])
+    (tmp_path / "dataset_info.json").write_text(json.dumps({"d": {"file_name": "d.json", "ranking": stage == "rm"}}))
+    (tmp_path / "d.json").write_text(json.dumps(rows))
+    cfg = {"model_name_or_path": json.dumps(TINY), "stage": stage, "dataset": "d", "dataset_dir": str(tmp_path),
+           "template": "qwen3", "cutoff_len": 96, "max_steps": 2, "output_dir": str(tmp_path / "run"), "bf16": False,
+           "pure_bf16": False, "learning_rate": 1e-3, "lr_scheduler_type": "constant", "per_device_train_batch_size": 2}
+    assert run_exp(cfg).global_step == 2
+
+
+def test_ppo_stage_with_a_reward_model_checkpoint(tmp_path):
+    rm_out, ppo_out = str(tmp_path / "rm"), str(tmp_path / "ppo")
+    base = {"model_name_or_path": json.dumps(TINY), "synthetic": True, "cutoff_len": 24, "bf16": False, "pure_bf16": False,
+            "learning_rate": 1e-3, "lr_scheduler_type": "constant", "per_device_train_batch_size": 2}
+    run_exp(dict(base, stage="pt", max_steps=1, output_dir=rm_out))          # any checkpoint serves as the scorer here
+    tr = run_exp(dict(base, stage="ppo", max_steps=2, output_dir=ppo_out, reward_model=os.path.join(rm_out, "final"),
+                      ppo_epochs=1, ppo_max_new_tokens=4, ppo_prompt_len=8))
+    assert len(tr.stats) == 2 and {"score", "kl", "policy_loss"} <= set(tr.stats[-1])
+    assert os.path.exists(os.path.join(ppo_out, "final", "value_head.pt"))
