@@ -321,3 +321,45 @@ def test_moe_model_uses_grouped_gemm_kernels():
         out = model(ids).logits.float()
     assert model.model.layers[0].mlp.fused_ep.calls > 0
     assert (out - ref).abs().max() < 0.05 * ref.abs().max()
+
+
+def test_openai_compatible_server_routes():
+    """The completion, chat, streaming and metrics routes of the API server, called in-process (no HTTP client in the
+    test environment): the generated tokens equal the model's own greedy generation."""
+    import asyncio
+    import json
+    from hybrid_model_factory_b200.data.formats import ByteTokenizer
+    from hybrid_model_factory_b200.serving.api_server import create_app
+    torch.manual_seed(0)
+    cfg = tiny("*-GDN", vocab_size=259)
+    model = build_model(cfg).eval()
+    eng = ServingEngine(model, block_size=4, num_blocks=128, max_num_seqs=4, max_num_batched_tokens=32, max_model_len=128)
+    tok = ByteTokenizer()
+    app = create_app(eng, tok, model_name="tiny", template="qwen3")
+    routes = {r.path: r.endpoint for r in app.routes if hasattr(r, "endpoint")}
+
+    async def scenario():
+        models = await routes["/v1/models"]()
+        assert models["data"][0]["id"] == "tiny"
+        prompt = "hello"
+        resp = await routes["/v1/completions"]({"prompt": prompt, "max_tokens": 5, "ignore_eos": True})
+        body = json.loads(resp.body)
+        ids = tok.encode(prompt, add_special_tokens=False)
+        want = model.generate(torch.tensor([ids]), max_new_tokens=5)[0, len(ids):].tolist()
+        assert body["usage"] == {"prompt_tokens": len(ids), "completion_tokens": 5, "total_tokens": len(ids) + 5}
+        assert body["choices"][0]["text"] == tok.decode(want)
+        chat = await routes["/v1/chat/completions"]({"messages": [{"role": "system", "content": "be brief"},
+                                                                  {"role": "user", "content": "hi"}],
+                                                     "max_tokens": 3, "ignore_eos": True})
+        cbody = json.loads(chat.body)
+        assert cbody["object"] == "chat.completion" and cbody["choices"][0]["message"]["role"] == "assistant"
+        stream = await routes["/v1/completions"]({"prompt": prompt, "max_tokens": 3, "stream": True, "ignore_eos": True})
+        chunks = [c async for c in stream.body_iterator]
+        assert chunks[-1].strip() == "data: [DONE]" and len(chunks) == 4
+        assert "".join(json.loads(c[6:])["choices"][0]["text"] for c in chunks[:-1]) == tok.decode(want[:3])
+        m = await routes["/metrics"]()
+        assert m["output_tokens"] >= 11
+    try:
+        asyncio.run(scenario())
+    finally:
+        app.state.loop_runner.stop = True          # ends the engine thread
