@@ -73,9 +73,14 @@ def create_app(engine: ServingEngine, tokenizer, model_name: str = "hybrid", tem
         created, cid = int(time.time()), f"cmpl-{uuid.uuid4().hex[:12]}"
         if body.get("stream"):
             async def gen():
+                toks, sent = [], 0          # incremental detokenisation: a character may span several tokens
                 while True:
                     tok, done = await q.get()
-                    text = tokenizer.decode([tok])
+                    toks.append(tok)
+                    full = tokenizer.decode(toks)
+                    if not done and full.endswith("\ufffd"):
+                        continue            # incomplete multi-byte character: wait for the rest
+                    text, sent = full[sent:], len(full)
                     delta = {"delta": {"content": text}} if chat else {"text": text}
                     yield "data: " + json.dumps({"id": cid, "created": created, "model": model_name,
                                                  "choices": [{"index": 0, **delta, "finish_reason": "length" if done else None}]}) + "\n\n"

@@ -355,7 +355,7 @@ def test_openai_compatible_server_routes():
         assert cbody["object"] == "chat.completion" and cbody["choices"][0]["message"]["role"] == "assistant"
         stream = await routes["/v1/completions"]({"prompt": prompt, "max_tokens": 3, "stream": True, "ignore_eos": True})
         chunks = [c async for c in stream.body_iterator]
-        assert chunks[-1].strip() == "data: [DONE]" and len(chunks) == 4
+        assert chunks[-1].strip() == "data: [DONE]" and 2 <= len(chunks) <= 4      # partial characters are held back
         assert "".join(json.loads(c[6:])["choices"][0]["text"] for c in chunks[:-1]) == tok.decode(want[:3])
         m = await routes["/metrics"]()
         assert m["output_tokens"] >= 11
