@@ -363,3 +363,15 @@ def test_openai_compatible_server_routes():
         asyncio.run(scenario())
     finally:
         app.state.loop_runner.stop = True          # ends the engine thread
+
+
+def test_plugin_registry_targets_resolve_to_the_native_models():
+    import importlib
+    from hybrid_model_factory_b200.serving import vllm_plugin
+    reg = vllm_plugin.registry()
+    assert set(reg) == set(vllm_plugin.ARCHITECTURES)
+    for name, target in vllm_plugin.ARCHITECTURES.items():
+        mod, cls = target.split(":")
+        assert getattr(importlib.import_module(mod), cls) is reg[name]
+    model = reg["HybridQwen3ForCausalLM"](tiny("*-GDN"))
+    assert model(torch.randint(0, 128, (1, 8))).logits.shape == (1, 8, 128)
