@@ -203,3 +203,29 @@ def test_ppo_stage_with_a_reward_model_checkpoint(tmp_path):
                       ppo_epochs=1, ppo_max_new_tokens=4, ppo_prompt_len=8))
     assert len(tr.stats) == 2 and {"score", "kl", "policy_loss"} <= set(tr.stats[-1])
     assert os.path.exists(os.path.join(ppo_out, "final", "value_head.pt"))
+
+
+def test_launcher_commands_and_torchrun_command(tmp_path, monkeypatch, capsys):
+    from hybrid_model_factory_b200 import launcher
+    assert launcher.launch(["version"]) == 0 and "B200" in capsys.readouterr().out
+    assert launcher.launch(["env"]) == 0 and "torch" in capsys.readouterr().out.lower()
+    assert launcher.launch(["no-such-command"]) == 2
+    monkeypatch.setenv("NPROC_PER_NODE", "4")
+    monkeypatch.setenv("MASTER_PORT", "29611")
+    cmd = launcher.torchrun_command(["cfg.yaml"])
+    assert cmd[1:3] == ["-m", "torch.distributed.run"] and "--master-port" in cmd and cmd[-1] == "cfg.yaml"
+    assert cmd[cmd.index("--nproc-per-node") + 1] == "4" and cmd[cmd.index("--master-addr") + 1] == "127.0.0.1"
+    monkeypatch.setenv("RDZV_ID", "job7")
+    monkeypatch.setenv("MIN_NNODES", "1")
+    monkeypatch.setenv("MAX_NNODES", "2")
+    monkeypatch.setenv("MAX_RESTARTS", "3")
+    el = launcher.torchrun_command(["cfg.yaml"])
+    assert el[el.index("--nnodes") + 1] == "1:2" and el[el.index("--rdzv-id") + 1] == "job7"
+    assert el[el.index("--max-restarts") + 1] == "3" and el[el.index("--rdzv-endpoint") + 1] == "127.0.0.1:29611"
+    monkeypatch.delenv("RDZV_ID")
+    # single-process training through the command line entry
+    y = tmp_path / "c.yaml"
+    y.write_text("model_name_or_path: '%s'\nstage: pt\nsynthetic: true\ncutoff_len: 16\nmax_steps: 1\noutput_dir: %s\n"
+                 "bf16: false\npure_bf16: false\n" % (json.dumps(TINY), tmp_path / "out"))
+    assert launcher.launch(["train", str(y)]) == 0
+    assert os.path.exists(tmp_path / "out" / "final" / "config.json")
