@@ -375,3 +375,17 @@ def test_plugin_registry_targets_resolve_to_the_native_models():
         assert getattr(importlib.import_module(mod), cls) is reg[name]
     model = reg["HybridQwen3ForCausalLM"](tiny("*-GDN"))
     assert model(torch.randint(0, 128, (1, 8))).logits.shape == (1, 8, 128)
+
+
+def test_chat_cli_round_trip(tmp_path, monkeypatch, capsys):
+    """`hmf chat` on a saved tiny checkpoint: two user turns, `clear`, `exit`."""
+    from hybrid_model_factory_b200.serving import chat
+    from hybrid_model_factory_b200.utils import checkpoint_io
+    torch.manual_seed(0)
+    model = build_model(tiny("*-GDN", vocab_size=259))
+    checkpoint_io.save_pretrained(model, str(tmp_path / "ckpt"))
+    lines = iter(["hello", "clear", "again", "exit"])
+    monkeypatch.setattr("builtins.input", lambda _prompt="": next(lines))
+    assert chat.main([str(tmp_path / "ckpt"), "--max-new-tokens", "4", "--template", "qwen3"]) == 0
+    out = capsys.readouterr().out
+    assert out.count("Assistant:") == 2
