@@ -131,8 +131,12 @@ def main(argv=None) -> int:
     ap.add_argument("--num-shards", type=int, default=8)
     ap.add_argument("--workers", type=int, default=4)
     a = ap.parse_args(argv)
-    model_args, data_args, run_args = get_train_args(a.config)[:3]
-    out = run(data_args, model_args.model_name_or_path, run_args.stage, model_args.sequence_parallel_size,
-              a.num_shards, a.workers, getattr(run_args, "seed", 42))
+    model_args, data_args, run_args, ft_args = get_train_args([a.config])[:4]
+    stage = "pt" if ft_args.stage in ("pt", "hkd") else "sft"
+    tok_path = model_args.model_name_or_path
+    if tok_path and tok_path.strip().startswith("{"):      # inline JSON config: no tokenizer files, byte tokenizer
+        tok_path = None
+    out = run(data_args, tok_path, stage, model_args.sequence_parallel_size, a.num_shards, a.workers,
+              getattr(run_args, "seed", 42))
     print(out)
     return 0

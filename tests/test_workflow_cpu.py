@@ -229,3 +229,32 @@ def test_launcher_commands_and_torchrun_command(tmp_path, monkeypatch, capsys):
                  "bf16: false\npure_bf16: false\n" % (json.dumps(TINY), tmp_path / "out"))
     assert launcher.launch(["train", str(y)]) == 0
     assert os.path.exists(tmp_path / "out" / "final" / "config.json")
+
+
+def test_sharded_preprocess_four_phases(tmp_path):
+    from hybrid_model_factory_b200.config.hparams import DataArguments
+    from hybrid_model_factory_b200.data import sharded_preprocess as SPP
+    from hybrid_model_factory_b200.data.loader import ListDataset, get_dataset
+    (tmp_path / "dataset_info.json").write_text(json.dumps({"docs": {"file_name": "docs.json", "formatting": "text",
+                                                                     "columns": {"prompt": "text"}}}))
+    (tmp_path / "docs.json").write_text(json.dumps([{"text": f"document number {i} " * 12} for i in range(40)]))
+    out = str(tmp_path / "tok")
+    da = DataArguments(dataset="docs", dataset_dir=str(tmp_path), cutoff_len=64, tokenized_path=out)
+    path = SPP.run(da, None, stage="pt", sp_size=1, num_shards=3, workers=2)
+    ds = ListDataset.load(path)
+    assert len(ds) > 10 and all(len(ds[i]["input_ids"]) == 64 for i in range(len(ds)))
+    # the same corpus through the single-process path holds the same number of tokens (up to one block per shard)
+    single = get_dataset(DataArguments(dataset="docs", dataset_dir=str(tmp_path), cutoff_len=64), ByteTokenizer(), "pt")
+    assert abs(len(single) - len(ds)) <= 3
+    # sequence-parallel layout: rows come in groups of sp_size, labels pre-shifted
+    out2 = str(tmp_path / "tok_sp")
+    da2 = DataArguments(dataset="docs", dataset_dir=str(tmp_path), cutoff_len=64, tokenized_path=out2)
+    ds2 = ListDataset.load(SPP.run(da2, None, stage="pt", sp_size=2, num_shards=2, workers=2))
+    assert ds2.labels_shifted and len(ds2) % 2 == 0 and len(ds2[0]["input_ids"]) == 32
+    # command line entry
+    y = tmp_path / "c.yaml"
+    y.write_text("model_name_or_path: '%s'\nstage: pt\ndataset: docs\ndataset_dir: %s\ncutoff_len: 64\n"
+                 "tokenized_path: %s\nmax_steps: 1\noutput_dir: %s\n" % (json.dumps(TINY), tmp_path, tmp_path / "tok_cli",
+                                                                         tmp_path / "o"))
+    assert SPP.main(["--config", str(y), "--num-shards", "2", "--workers", "2"]) == 0
+    assert os.path.exists(tmp_path / "tok_cli" / "dataset.pt")
