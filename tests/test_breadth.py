@@ -450,3 +450,22 @@ def test_patchers_resize_upcast_rope_and_oft():
     assert not any(isinstance(m, patcher.OFTLinear) for m in model.modules())
     assert torch.allclose(model(ids).logits, tuned, atol=1e-4)
     assert patcher.patch_model(model, vocab_size=200, resize_vocab=True)["vocab_size"] == 256
+
+
+def test_profiling_helpers_are_inert_without_a_gpu():
+    from hybrid_model_factory_b200.utils import profiling
+    t = profiling.DeviceTimer()
+    with t.time("x"):
+        pass
+    if not torch.cuda.is_available():
+        assert t.summary() == {}
+
+    @profiling.nvtx("f")
+    def f(a):
+        return a + 1
+    assert f(1) == 2
+    model = build_model(_cfg("*-GDN"))
+    sb = profiling.StepBreakdown(model)
+    model(torch.randint(0, 128, (1, 8)))
+    sb.remove()
+    assert isinstance(sb.summary(), dict)

@@ -230,3 +230,22 @@ def test_inference_fusions_match_the_autograd_path(pattern):
     err = (fused - plain).abs().max() / plain.abs().max()
     assert err < 3e-2, float(err)
     assert (fused.argmax(-1) == plain.argmax(-1)).float().mean() > 0.97
+
+
+@pytest.mark.gpu
+def test_device_timer_and_step_breakdown_on_gpu():
+    from hybrid_model_factory_b200.models.configuration import HybridConfig
+    from hybrid_model_factory_b200.models.modeling_hybrid import build_model
+    from hybrid_model_factory_b200.utils import profiling
+    cfg = HybridConfig("hybrid_qwen3", vocab_size=256, hidden_size=256, intermediate_size=512, num_hidden_layers=2,
+                       num_attention_heads=2, num_key_value_heads=2, head_dim=128, hybrid_override_pattern="*-GDN")
+    model = build_model(cfg).to("cuda", torch.bfloat16)
+    sb = profiling.StepBreakdown(model)
+    t = profiling.DeviceTimer()
+    with t.time("forward"), profiling.nvtx_range("forward"):
+        model(torch.randint(0, 256, (1, 256), device="cuda"))
+    s = sb.summary()
+    sb.remove()
+    assert {"Attention", "GatedDeltaNetLayer", "MLP"} <= set(s) and s["MLP"]["calls"] == 2
+    total = t.summary()["forward"]["total_ms"]
+    assert total > 0 and sum(v["total_ms"] for v in s.values()) <= total * 1.05
