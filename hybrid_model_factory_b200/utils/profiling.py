@@ -92,10 +92,12 @@ class StepBreakdown:
     def __init__(self, model: torch.nn.Module, classes=None):
         self.timer = DeviceTimer()
         self.handles = []
+        from ..models.patterns import MIXER_ATTR
+        leaves = tuple("." + a for a in set(MIXER_ATTR.values())) + (".mlp",)      # model.layers.N.{self_attn,gdn,...}
         for name, mod in model.named_modules():
             if classes is not None and not isinstance(mod, tuple(classes)):
                 continue
-            if classes is None and not name.endswith(("seq_mixer", "mlp")):
+            if classes is None and not name.endswith(leaves):
                 continue
             key = type(mod).__name__
             self.handles.append(mod.register_forward_pre_hook(lambda m, a, k=key: self.timer.start(k)))

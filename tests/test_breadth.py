@@ -466,6 +466,7 @@ def test_profiling_helpers_are_inert_without_a_gpu():
     assert f(1) == 2
     model = build_model(_cfg("*-GDN"))
     sb = profiling.StepBreakdown(model)
+    assert len(sb.handles) == 8                       # pre + post hook on two mixers and two MLPs
     model(torch.randint(0, 128, (1, 8)))
     sb.remove()
     assert isinstance(sb.summary(), dict)
