@@ -67,6 +67,7 @@ def simple_gla(q: Tensor, k: Tensor, v: Tensor, g: Tensor, *, scale: Optional[fl
     if core is None:
         core = TorchScanCore(_gla_ref, n_state=1, state_shape_fn=_qkv_state_shapes, scale=scale,
                              chunk_size=chunk_size, recurrent=recurrent)
+    core.scalar_transition, core.decay_input = True, 3       # S_out = e^{sum g} S_in + S_local: chain-free SP possible
     state = None if initial_state is None else (initial_state,)
     o, (sT,) = ssm_scan(core, [q, k, v, g, None], state, sp)
     return o, sT
@@ -104,6 +105,7 @@ def chebyshev_solve(q: Tensor, k: Tensor, gk: Optional[Tensor], *, ridge_ratio: 
     if core is None:
         core = TorchScanCore(_cheb_ref, n_state=1, state_shape_fn=_cheb_state_shapes, ridge_ratio=ridge_ratio,
                              num_iter=num_iter, chunk_size=chunk_size, recurrent=recurrent)
+    core.scalar_transition, core.decay_input = True, 2       # the key covariance decays by e^{sum gk} per segment
     state = None if initial_state is None else (initial_state,)
     x, (hT,) = ssm_scan(core, [q, k, gk], state, sp)
     return x, hT

@@ -23,9 +23,10 @@ CPU) cannot deadlock on autograd's scheduling.
 """
 from __future__ import annotations
 
-from typing import Callable, Optional, Sequence, Tuple
+from typing import Callable, List, Optional, Sequence, Tuple
 
 import torch
+import torch.distributed as dist
 
 Tensor = torch.Tensor
 State = Optional[Tuple[Tensor, ...]]
@@ -123,6 +124,96 @@ def _peer_plan(core, transport, seg_inputs):
     return (tuple(shape), bh) if transport.fits(shape, dtype, bh) else None
 
 
+# -- chain-free sequence parallelism for cores with a scalar state transition ---------------------------------------
+# Gated linear attention, Mamba2's SSD and the key covariance of Gated KalmaNet all update their state as
+# ``h_out = e^{L} h_in + h_local`` with ``L`` the summed log-decay of the segment (one scalar per batch and head).  The
+# states entering the 2n zig-zag chunks then follow from every chunk's ``(h_local, L)`` by a prefix over chunks, so the
+# ranks need not wait for one another: each scans its two segments from a zero state, one all-gather exchanges
+# ``(h_local, L)``, and each scans again from its true incoming states.  Two passes of local work replace a serial chain
+# of 2n links.  The backward pass mirrors it with the state gradients (``d_h_in = e^{L} d_h_out + d_h_local``).
+# A core opts in with ``scalar_transition = True`` and ``decay_input`` (index of the log-decay tensor ``[B, T, H]`` among
+# its inputs, or ``None``); the SP context switches the mode on with ``parallel_scan``.
+def _segment_log_decay(core, seg_inputs, like: Tensor) -> Tensor:
+    idx = getattr(core, "decay_input", None)
+    g = None if idx is None else seg_inputs[idx]
+    if g is None:
+        return like.new_zeros(like.shape[0], like.shape[1])
+    return g.float().sum(dim=1)
+
+
+def _gather_chunks(sp, mine_a: Tensor, mine_b: Tensor) -> List[Tensor]:
+    """All-gathers one tensor per local segment and returns them ordered by global chunk (rank ``r`` owns chunks ``r``
+    and ``2n - 1 - r``)."""
+    n = sp.size
+    payload = torch.stack([mine_a, mine_b]).contiguous()
+    parts = [torch.empty_like(payload) for _ in range(n)]
+    dist.all_gather(parts, payload, group=sp.group)
+    chunks: List[Optional[Tensor]] = [None] * (2 * n)
+    for rr, p in enumerate(parts):
+        chunks[rr], chunks[2 * n - 1 - rr] = p[0], p[1]
+    return chunks
+
+
+def _bcast_from_first(sp, t: Optional[Tensor], like: Tensor) -> Tensor:
+    """The tensor held by SP rank 0 (zeros when it has none) on every rank."""
+    buf = like.new_zeros(like.shape) if (t is None or sp.rank != 0) else t.to(like.dtype).contiguous().clone()
+    dist.broadcast(buf, src=sp.ranks[0], group=sp.group)
+    return buf
+
+
+parallel_scan_calls = 0      # forward passes that took the chain-free form (diagnostics, tests)
+
+
+def _parallel_forward(ctx, core, sp, seg_a, seg_b, state0):
+    global parallel_scan_calls
+    parallel_scan_calls += 1
+    r, n = sp.rank, sp.size
+    with torch.no_grad():
+        _, (la,), _, _ = core.forward(seg_a, None)              # local contributions from a zero state
+        _, (lb,), _, _ = core.forward(seg_b, None)
+        La, Lb = _segment_log_decay(core, seg_a, la), _segment_log_decay(core, seg_b, lb)
+        loc = _gather_chunks(sp, la.float(), lb.float())
+        dec = _gather_chunks(sp, La, Lb)
+        S = _bcast_from_first(sp, None if state0 is None else state0[0], la.float())
+        incoming = []
+        for c in range(2 * n):
+            incoming.append(S)
+            S = torch.exp(dec[c])[..., None, None] * S + loc[c]
+    ca, cb = r, 2 * n - 1 - r
+    out_a, sT_a, saved_a, meta_a = core.forward(seg_a, (incoming[ca].to(la.dtype),))
+    out_b, sT_b, saved_b, meta_b = core.forward(seg_b, (incoming[cb].to(lb.dtype),))
+    ctx.save_for_backward(*saved_a, *saved_b, *[d.contiguous() for d in dec])
+    ctx.counts, ctx.metas = [len(saved_a), len(saved_b)], [meta_a, meta_b]
+    ctx.state_templates = ((S.shape, la.dtype),)
+    ctx.peer = None
+    return (torch.cat([out_a, out_b], dim=1), S.to(la.dtype))
+
+
+def _parallel_backward(ctx, core, sp, saved_all, d_a, d_b, d_state):
+    r, n = sp.rank, sp.size
+    na, nb = ctx.counts
+    saved_a, saved_b, dec = saved_all[:na], saved_all[na:na + nb], saved_all[na + nb:]
+    shape, dtype = ctx.state_templates[0]
+    with torch.no_grad():
+        _, dla = core.backward(saved_a, ctx.metas[0], d_a, None)      # state gradients with nothing coming from later chunks
+        _, dlb = core.backward(saved_b, ctx.metas[1], d_b, None)
+        zero = d_a.new_zeros(shape, dtype=torch.float32)
+        dla = zero if (dla is None or dla[0] is None) else dla[0].float()
+        dlb = zero if (dlb is None or dlb[0] is None) else dlb[0].float()
+        dloc = _gather_chunks(sp, dla, dlb)
+        Dg = _bcast_from_first(sp, None if d_state is None else d_state[0], zero)   # gradient of the final state
+        outgoing: List[Optional[Tensor]] = [None] * (2 * n)
+        for c in reversed(range(2 * n)):
+            outgoing[c] = Dg
+            Dg = torch.exp(dec[c])[..., None, None] * Dg + dloc[c]
+    ca, cb = r, 2 * n - 1 - r
+    d_in_a, _ = core.backward(saved_a, ctx.metas[0], d_a, (outgoing[ca].to(dtype),))
+    d_in_b, _ = core.backward(saved_b, ctx.metas[1], d_b, (outgoing[cb].to(dtype),))
+    d_inputs = [None if ga is None else torch.cat([ga, gb], dim=1) for ga, gb in zip(d_in_a, d_in_b)]
+    d_s0 = ([Dg.to(dtype)] if r == 0 else [None]) if ctx.n_state0 else []
+    return (None, None, None, None, *d_inputs, *d_s0)
+
+
 class _SSMScan(torch.autograd.Function):
     @staticmethod
     def forward(ctx, core: ScanCore, sp, n_inputs: int, want_state: bool, *tensors):
@@ -140,6 +231,9 @@ class _SSMScan(torch.autograd.Function):
         r, n = sp.rank, sp.size
         seg_a, seg_b = zip(*[_split_time(t) for t in inputs])
         tr = sp.transport
+        ctx.parallel = bool(getattr(core, "scalar_transition", False) and getattr(sp, "parallel_scan", False))
+        if ctx.parallel:
+            return _parallel_forward(ctx, core, sp, list(seg_a), list(seg_b), state0)
         ctx.peer = _peer_plan(core, tr, list(seg_a))
         if ctx.peer is not None:
             # in-kernel state chain over peer memory: both launches are queued at once, the kernels wait for
@@ -185,6 +279,8 @@ class _SSMScan(torch.autograd.Function):
         tr = sp.transport
         half = d_out.shape[1] // 2
         d_a, d_b = d_out[:, :half], d_out[:, half:]
+        if ctx.parallel:
+            return _parallel_backward(ctx, core, sp, saved_all, d_a, d_b, d_state)
         saved_a, saved_b = saved_all[:ctx.counts[0]], saved_all[ctx.counts[0]:]
         device = d_out.device
         if ctx.peer is not None:

@@ -19,6 +19,8 @@ SP groups are contiguous blocks of ``sp_size`` global ranks
 """
 from __future__ import annotations
 
+import os
+
 from dataclasses import dataclass, field
 from typing import List, Optional, Sequence, Tuple
 
@@ -124,6 +126,9 @@ class SPContext:
     ranks: List[int]
     transport: StateTransport = field(default=None)
     mode: str = "zigzag"
+    # scan cores with a scalar state transition (GLA, Mamba2 SSD, the GKA covariance) skip the serial state chain:
+    # two local passes and one all-gather instead of 2 * size dependent links (``ops/scan.py``)
+    parallel_scan: bool = field(default_factory=lambda: os.environ.get("HMF_SP_PARALLEL_SCAN", "0") == "1")
 
     def __post_init__(self):
         if self.transport is None:

@@ -180,7 +180,7 @@ def test_expert_parallel_fused_all_to_all_two_gpus():
     run_ranks(_ep_fused_worker, 2, backend="nccl", timeout=240)
 
 
-def _sp_model_worker(rank, world, pattern):
+def _sp_model_worker(rank, world, pattern, parallel_scan=False):
     """A whole hybrid model under SP=2 (peer-memory state chain and K/V exchange) against the single-GPU run."""
     import copy
     from hybrid_model_factory_b200.models.configuration import HybridConfig
@@ -205,6 +205,7 @@ def _sp_model_worker(rank, world, pattern):
     out_ref = ref(ids, labels=labels, labels_shifted=True)
     out_ref.loss.backward()
     sp = init_sp_group(world)
+    sp.parallel_scan = parallel_scan
     assert enable_peer_transport(sp) and enable_peer_kv(sp, 16 << 20)
     set_sequence_parallel_group_recursive(model, sp)
     pos = torch.arange(T, device=dev)[None]
@@ -234,3 +235,9 @@ def _sp_model_worker(rank, world, pattern):
 @pytest.mark.parametrize("pattern", ["*-GDN", "M2-GKA", "SWA-BMF", "BMF"])
 def test_sp_model_two_gpus(pattern):
     run_ranks(_sp_model_worker, 2, pattern, backend="nccl", timeout=300)
+
+
+@needs2
+def test_sp_model_chain_free_scan_two_gpus():
+    """Mamba2 and GKA layers with the two-pass / all-gather form of the state exchange on the GPU kernels."""
+    run_ranks(_sp_model_worker, 2, "M2-GKA", True, backend="nccl", timeout=300)

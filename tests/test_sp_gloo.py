@@ -21,7 +21,7 @@ def _config(pattern):
                         swa_config={"window_size": 16}, torch_dtype="float32")
 
 
-def _sp_worker(rank, world, pattern, seq, tol):
+def _sp_worker(rank, world, pattern, seq, tol, parallel_scan=False):
     torch.manual_seed(0)
     cfg = _config(pattern)
     ref = build_model(cfg)
@@ -36,12 +36,19 @@ def _sp_worker(rank, world, pattern, seq, tol):
     out_ref.loss.backward()
     # sequence-parallel run
     sp = init_sp_group(world)
+    sp.parallel_scan = parallel_scan
     set_sequence_parallel_group_recursive(model, sp)
     pos = torch.arange(seq).expand(2, seq)
     l_ids, l_lab, l_pos = (zigzag_split(t, sp.rank, sp.size) for t in (ids, labels, pos))
     opt = torch.optim.AdamW(model.parameters(), lr=1e-3)
+    from hybrid_model_factory_b200.ops import scan as scan_mod
+    before = scan_mod.parallel_scan_calls
     out = model(l_ids, labels=l_lab, position_ids=l_pos, labels_shifted=True)
     out.loss.backward()
+    if parallel_scan:       # every GLA-type scan of the pattern (GKA: solve + GLA stage, M2: SSD) took the chain-free form
+        assert scan_mod.parallel_scan_calls - before >= 3
+    else:
+        assert scan_mod.parallel_scan_calls == before
     for p in model.parameters():
         if p.grad is None:
             p.grad = torch.zeros_like(p)
@@ -66,3 +73,10 @@ def test_sp2_matches_single_rank(pattern, tol):
 @pytest.mark.slow
 def test_sp4_matches_single_rank():
     run_ranks(_sp_worker, 4, "*-GDN-GKA-M2", 256, 5e-5)
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_chain_free_scan_for_scalar_transition_layers(world):
+    """GKA and Mamba2 layers under the two-pass / all-gather form of sequence parallelism (no serial state chain)
+    equal the single-rank run; the GDN layer in the pattern keeps the chain (its transition is a matrix)."""
+    run_ranks(_sp_worker, world, "GKA-M2-GDN-M2", 256, 5e-5, True)
