@@ -44,6 +44,7 @@ def gated_delta_rule(q: Tensor, k: Tensor, v: Tensor, g: Tensor, beta: Tensor, *
         if not recurrent:
             kw["chunk_size"] = chunk_size
         core = TorchScanCore(fn, n_state=1, state_shape_fn=_qkv_state_shapes, **kw)
+    core.matrix_transition, core.value_input = True, 2       # S_out = A S_in + S_local with A from (k, beta, g) only
     state = None if initial_state is None else (initial_state,)
     o, (sT,) = ssm_scan(core, [q, k, v, g, beta], state, sp)
     return o, sT

@@ -133,12 +133,35 @@ def _peer_plan(core, transport, seg_inputs):
 # of 2n links.  The backward pass mirrors it with the state gradients (``d_h_in = e^{L} d_h_out + d_h_local``).
 # A core opts in with ``scalar_transition = True`` and ``decay_input`` (index of the log-decay tensor ``[B, T, H]`` among
 # its inputs, or ``None``); the SP context switches the mode on with ``parallel_scan``.
+# The delta rule has a matrix transition ``h_out = A h_in + h_local``; a core that sets ``matrix_transition = True`` and
+# ``value_input`` gets the same treatment with ``A`` probed by one more scan (zero values, identity start state), i.e.
+# three passes of local work; worth it only for long chains (``parallel_scan_matrix`` on the SP context).
 def _segment_log_decay(core, seg_inputs, like: Tensor) -> Tensor:
     idx = getattr(core, "decay_input", None)
     g = None if idx is None else seg_inputs[idx]
     if g is None:
         return like.new_zeros(like.shape[0], like.shape[1])
     return g.float().sum(dim=1)
+
+
+def _segment_transition(core, seg_inputs, like: Tensor) -> Tensor:
+    """Matrix transition ``A`` of a segment (``h_out = A h_in + h_local``, ``A [B, H, Dk, Dk]``) for cores that declare
+    ``matrix_transition``: the state reached from the identity when the values are zero (needs ``Dv == Dk``)."""
+    vi = core.value_input
+    zeroed = list(seg_inputs)
+    zeroed[vi] = torch.zeros_like(seg_inputs[vi])
+    B, H, Dk, Dv = like.shape
+    assert Dk == Dv, "the identity-state probe of the transition needs square states"
+    eye = torch.eye(Dk, device=like.device, dtype=like.dtype).expand(B, H, Dk, Dk).contiguous()
+    _, (A,), _, _ = core.forward(zeroed, (eye,))
+    return A.float()
+
+
+def _apply(T: Tensor, S: Tensor, transpose: bool = False) -> Tensor:
+    """Applies a segment transition (scalar log-decay ``[B, H]`` or matrix ``[B, H, Dk, Dk]``) to a state."""
+    if T.dim() == 2:
+        return torch.exp(T)[..., None, None] * S
+    return (T.transpose(-1, -2) if transpose else T) @ S
 
 
 def _gather_chunks(sp, mine_a: Tensor, mine_b: Tensor) -> List[Tensor]:
@@ -171,14 +194,17 @@ def _parallel_forward(ctx, core, sp, seg_a, seg_b, state0):
     with torch.no_grad():
         _, (la,), _, _ = core.forward(seg_a, None)              # local contributions from a zero state
         _, (lb,), _, _ = core.forward(seg_b, None)
-        La, Lb = _segment_log_decay(core, seg_a, la), _segment_log_decay(core, seg_b, lb)
+        if getattr(core, "scalar_transition", False):
+            La, Lb = _segment_log_decay(core, seg_a, la), _segment_log_decay(core, seg_b, lb)
+        else:
+            La, Lb = _segment_transition(core, seg_a, la), _segment_transition(core, seg_b, lb)
         loc = _gather_chunks(sp, la.float(), lb.float())
         dec = _gather_chunks(sp, La, Lb)
         S = _bcast_from_first(sp, None if state0 is None else state0[0], la.float())
         incoming = []
         for c in range(2 * n):
             incoming.append(S)
-            S = torch.exp(dec[c])[..., None, None] * S + loc[c]
+            S = _apply(dec[c], S) + loc[c]
     ca, cb = r, 2 * n - 1 - r
     out_a, sT_a, saved_a, meta_a = core.forward(seg_a, (incoming[ca].to(la.dtype),))
     out_b, sT_b, saved_b, meta_b = core.forward(seg_b, (incoming[cb].to(lb.dtype),))
@@ -205,7 +231,7 @@ def _parallel_backward(ctx, core, sp, saved_all, d_a, d_b, d_state):
         outgoing: List[Optional[Tensor]] = [None] * (2 * n)
         for c in reversed(range(2 * n)):
             outgoing[c] = Dg
-            Dg = torch.exp(dec[c])[..., None, None] * Dg + dloc[c]
+            Dg = _apply(dec[c], Dg, transpose=True) + dloc[c]
     ca, cb = r, 2 * n - 1 - r
     d_in_a, _ = core.backward(saved_a, ctx.metas[0], d_a, (outgoing[ca].to(dtype),))
     d_in_b, _ = core.backward(saved_b, ctx.metas[1], d_b, (outgoing[cb].to(dtype),))
@@ -231,7 +257,9 @@ class _SSMScan(torch.autograd.Function):
         r, n = sp.rank, sp.size
         seg_a, seg_b = zip(*[_split_time(t) for t in inputs])
         tr = sp.transport
-        ctx.parallel = bool(getattr(core, "scalar_transition", False) and getattr(sp, "parallel_scan", False))
+        ctx.parallel = bool(getattr(sp, "parallel_scan", False) and (
+            getattr(core, "scalar_transition", False)
+            or (getattr(core, "matrix_transition", False) and getattr(sp, "parallel_scan_matrix", False))))
         if ctx.parallel:
             return _parallel_forward(ctx, core, sp, list(seg_a), list(seg_b), state0)
         ctx.peer = _peer_plan(core, tr, list(seg_a))

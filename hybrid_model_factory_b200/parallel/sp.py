@@ -128,7 +128,9 @@ class SPContext:
     mode: str = "zigzag"
     # scan cores with a scalar state transition (GLA, Mamba2 SSD, the GKA covariance) skip the serial state chain:
     # two local passes and one all-gather instead of 2 * size dependent links (``ops/scan.py``)
-    parallel_scan: bool = field(default_factory=lambda: os.environ.get("HMF_SP_PARALLEL_SCAN", "0") == "1")
+    parallel_scan: bool = field(default_factory=lambda: os.environ.get("HMF_SP_PARALLEL_SCAN", "0") in ("1", "2"))
+    # also for the delta rule (matrix transition, one extra probing scan per segment): HMF_SP_PARALLEL_SCAN=2
+    parallel_scan_matrix: bool = field(default_factory=lambda: os.environ.get("HMF_SP_PARALLEL_SCAN", "0") == "2")
 
     def __post_init__(self):
         if self.transport is None:

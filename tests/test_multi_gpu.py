@@ -205,7 +205,8 @@ def _sp_model_worker(rank, world, pattern, parallel_scan=False):
     out_ref = ref(ids, labels=labels, labels_shifted=True)
     out_ref.loss.backward()
     sp = init_sp_group(world)
-    sp.parallel_scan = parallel_scan
+    sp.parallel_scan = bool(parallel_scan)
+    sp.parallel_scan_matrix = parallel_scan == "matrix"
     assert enable_peer_transport(sp) and enable_peer_kv(sp, 16 << 20)
     set_sequence_parallel_group_recursive(model, sp)
     pos = torch.arange(T, device=dev)[None]
@@ -241,3 +242,9 @@ def test_sp_model_two_gpus(pattern):
 def test_sp_model_chain_free_scan_two_gpus():
     """Mamba2 and GKA layers with the two-pass / all-gather form of the state exchange on the GPU kernels."""
     run_ranks(_sp_model_worker, 2, "M2-GKA", True, backend="nccl", timeout=300)
+
+
+@needs2
+def test_sp_model_chain_free_delta_rule_two_gpus():
+    """Gated DeltaNet with the matrix-transition form of the chain-free state exchange on the GPU kernels."""
+    run_ranks(_sp_model_worker, 2, "*-GDN", "matrix", backend="nccl", timeout=300)

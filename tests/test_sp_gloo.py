@@ -36,7 +36,8 @@ def _sp_worker(rank, world, pattern, seq, tol, parallel_scan=False):
     out_ref.loss.backward()
     # sequence-parallel run
     sp = init_sp_group(world)
-    sp.parallel_scan = parallel_scan
+    sp.parallel_scan = bool(parallel_scan)
+    sp.parallel_scan_matrix = parallel_scan == "matrix"
     set_sequence_parallel_group_recursive(model, sp)
     pos = torch.arange(seq).expand(2, seq)
     l_ids, l_lab, l_pos = (zigzag_split(t, sp.rank, sp.size) for t in (ids, labels, pos))
@@ -45,7 +46,9 @@ def _sp_worker(rank, world, pattern, seq, tol, parallel_scan=False):
     before = scan_mod.parallel_scan_calls
     out = model(l_ids, labels=l_lab, position_ids=l_pos, labels_shifted=True)
     out.loss.backward()
-    if parallel_scan:       # every GLA-type scan of the pattern (GKA: solve + GLA stage, M2: SSD) took the chain-free form
+    if parallel_scan == "matrix":
+        assert scan_mod.parallel_scan_calls - before >= 2
+    elif parallel_scan:     # every GLA-type scan of the pattern (GKA: solve + GLA stage, M2: SSD) took the chain-free form
         assert scan_mod.parallel_scan_calls - before >= 3
     else:
         assert scan_mod.parallel_scan_calls == before
@@ -80,3 +83,9 @@ def test_chain_free_scan_for_scalar_transition_layers(world):
     """GKA and Mamba2 layers under the two-pass / all-gather form of sequence parallelism (no serial state chain)
     equal the single-rank run; the GDN layer in the pattern keeps the chain (its transition is a matrix)."""
     run_ranks(_sp_worker, world, "GKA-M2-GDN-M2", 256, 5e-5, True)
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_chain_free_scan_for_the_delta_rule(world):
+    """Gated DeltaNet layers with the matrix-transition form (a third local scan probes the segment's transition)."""
+    run_ranks(_sp_worker, world, "GDN-*-GDN", 256, 2e-5, "matrix")
