@@ -117,7 +117,7 @@ def phase_concatenate(tokenized: List[str], tokenized_path: str) -> str:
 def run(data_args: DataArguments, tokenizer_path: Optional[str], stage: str = "pt", sp_size: int = 1,
         num_shards: int = 8, workers: int = 4, seed: int = 42) -> str:
     assert data_args.tokenized_path, "tokenized_path must be set for preprocessing"
-    work = os.path.join(data_args.tokenized_path, "_work")
+    work = os.path.join(data_args.tokenized_path, "stages")      # per-phase outputs (restartable)
     aligned = phase_align(data_args, work, workers)
     shards = phase_shard(aligned, work, num_shards, not data_args.disable_shuffling, seed)
     tokenized = phase_tokenize(shards, work, data_args, tokenizer_path, stage, sp_size, workers)
