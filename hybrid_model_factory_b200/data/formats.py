@@ -260,7 +260,59 @@ TEMPLATES: Dict[str, Template] = {
                        assistant_fmt="{content}<|eot_id|>", add_bos=True, efficient_eos=False),
     "mistral": Template("mistral", system_fmt="{content}\n\n", user_fmt="[INST] {content}[/INST]",
                         assistant_fmt=" {content}", add_bos=True),
+    "ministral": Template("ministral", system_fmt="[SYSTEM_PROMPT]{content}[/SYSTEM_PROMPT]",
+                          user_fmt="[INST]{content}[/INST]", assistant_fmt="{content}", add_bos=True),
+    "qwen3_nothink": Template("qwen3_nothink", system_fmt="<|im_start|>system\n{content}<|im_end|>\n",
+                              user_fmt="<|im_start|>user\n{content}<|im_end|>\n<|im_start|>assistant\n<think>\n\n</think>\n\n",
+                              assistant_fmt="{content}<|im_end|>\n", efficient_eos=False),
+    "llama2": Template("llama2", system_fmt="<<SYS>>\n{content}\n<</SYS>>\n\n", user_fmt="[INST] {content} [/INST]",
+                       assistant_fmt=" {content} ", add_bos=True),
+    "llama4": Template("llama4", system_fmt="<|header_start|>system<|header_end|>\n\n{content}<|eot|>",
+                       user_fmt="<|header_start|>user<|header_end|>\n\n{content}<|eot|>"
+                                "<|header_start|>assistant<|header_end|>\n\n",
+                       assistant_fmt="{content}<|eot|>", add_bos=True, efficient_eos=False),
+    "gemma": Template("gemma", system_fmt="{content}\n\n",
+                      user_fmt="<start_of_turn>user\n{content}<end_of_turn>\n<start_of_turn>model\n",
+                      assistant_fmt="{content}<end_of_turn>\n", add_bos=True, efficient_eos=False),
+    "phi": Template("phi", system_fmt="<|system|>\n{content}<|end|>\n", user_fmt="<|user|>\n{content}<|end|>\n<|assistant|>\n",
+                    assistant_fmt="{content}<|end|>\n", efficient_eos=False),
+    "phi4": Template("phi4", system_fmt="<|im_start|>system<|im_sep|>{content}<|im_end|>",
+                     user_fmt="<|im_start|>user<|im_sep|>{content}<|im_end|><|im_start|>assistant<|im_sep|>",
+                     assistant_fmt="{content}<|im_end|>", efficient_eos=False),
+    "deepseek": Template("deepseek", system_fmt="{content}\n\n", user_fmt="User: {content}\n\nAssistant:",
+                         assistant_fmt=" {content}", add_bos=True),
+    "deepseek3": Template("deepseek3", system_fmt="{content}", user_fmt="<\uff5cUser\uff5c>{content}<\uff5cAssistant\uff5c>",
+                          assistant_fmt="{content}", add_bos=True),
+    "glm4": Template("glm4", system_fmt="<|system|>\n{content}", user_fmt="<|user|>\n{content}<|assistant|>\n",
+                     assistant_fmt="{content}", default_system="", efficient_eos=True),
+    "yi": Template("yi", system_fmt="<|im_start|>system\n{content}<|im_end|>\n",
+                   user_fmt="<|im_start|>user\n{content}<|im_end|>\n<|im_start|>assistant\n",
+                   assistant_fmt="{content}<|im_end|>\n", efficient_eos=False),
+    "zephyr": Template("zephyr", system_fmt="<|system|>\n{content}</s>\n", user_fmt="<|user|>\n{content}</s>\n<|assistant|>\n",
+                       assistant_fmt="{content}</s>\n", default_system="You are a friendly chatbot.", efficient_eos=False),
+    "vicuna": Template("vicuna", system_fmt="{content} ", user_fmt="USER: {content} ASSISTANT:", assistant_fmt="{content}",
+                       default_system="A chat between a curious user and an artificial intelligence assistant. "
+                                      "The assistant gives helpful, detailed, and polite answers to the user's questions."),
+    "alpaca": Template("alpaca", system_fmt="{content}\n\n", user_fmt="### Instruction:\n{content}\n\n### Response:\n",
+                       assistant_fmt="{content}\n\n",
+                       default_system="Below is an instruction that describes a task. "
+                                      "Write a response that appropriately completes the request."),
+    "openchat": Template("openchat", system_fmt="{content}", user_fmt="GPT4 Correct User: {content}<|end_of_turn|>"
+                                                                      "GPT4 Correct Assistant:",
+                         assistant_fmt="{content}<|end_of_turn|>", add_bos=True, efficient_eos=False),
+    "falcon": Template("falcon", system_fmt="{content}\n", user_fmt="User: {content}\nFalcon:", assistant_fmt="{content}\n"),
+    "granite3": Template("granite3", system_fmt="<|start_of_role|>system<|end_of_role|>{content}<|end_of_text|>\n",
+                         user_fmt="<|start_of_role|>user<|end_of_role|>{content}<|end_of_text|>\n"
+                                  "<|start_of_role|>assistant<|end_of_role|>",
+                         assistant_fmt="{content}<|end_of_text|>\n", efficient_eos=False),
 }
+
+
+def register_template(template: Template) -> None:
+    """Adds a user-defined template (the name must be new)."""
+    if template.name in TEMPLATES:
+        raise ValueError(f"template '{template.name}' already exists")
+    TEMPLATES[template.name] = template
 
 
 def get_template(name: Optional[str]) -> Template:

@@ -258,3 +258,27 @@ def test_sharded_preprocess_four_phases(tmp_path):
                                                                          tmp_path / "o"))
     assert SPP.main(["--config", str(y), "--num-shards", "2", "--workers", "2"]) == 0
     assert os.path.exists(tmp_path / "tok_cli" / "dataset.pt")
+
+
+def test_every_chat_template_encodes_a_two_turn_conversation():
+    from hybrid_model_factory_b200.data.formats import TEMPLATES, Template, register_template
+    tok = ByteTokenizer()
+    msgs = [{"role": "user", "content": "first question"}, {"role": "assistant", "content": "first answer"},
+            {"role": "user", "content": "second question"}, {"role": "assistant", "content": "second answer"}]
+    assert len(TEMPLATES) >= 24
+    for name, tpl in TEMPLATES.items():
+        pairs = tpl.encode_multiturn(tok, msgs, "be exact")
+        assert len(pairs) == 2, name
+        text = bytes(t for p, r in pairs for t in p + r if t < 256).decode(errors="ignore")
+        for piece in ("first question", "first answer", "second question", "second answer"):
+            assert piece in text, (name, piece)
+        if name != "empty":
+            assert text.index("be exact") < text.index("first question"), name           # system prompt comes first
+        prompt2 = bytes(t for t in pairs[1][0] if t < 256).decode(errors="ignore")
+        assert "be exact" not in prompt2, name                                            # and only once
+        rows = L.process_supervised([{"messages": msgs, "system": ""}], tok, tpl, 512)
+        lab = [t for t in rows[0]["labels"] if t != -100 and t < 256]
+        assert "first answer" in bytes(lab).decode(errors="ignore") and "question" not in bytes(lab).decode(errors="ignore")
+    register_template(Template("my_format", user_fmt="Q: {content}\\nA:", assistant_fmt=" {content}\\n"))
+    with pytest.raises(ValueError):
+        register_template(Template("qwen3"))
