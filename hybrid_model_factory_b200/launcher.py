@@ -22,6 +22,7 @@ USAGE = """usage: hmf <command> [args]
   train CONFIG.yaml [k=v ...]    run a training stage (pt | sft | hkd | dpo | kto | rm)
   train-multinode CONFIG.yaml    same, expecting NNODES / NODE_RANK / MASTER_ADDR in the environment
   preprocess --config CFG.yaml   tokenise (and SP-split) datasets into `tokenized_path`, sharded and parallel
+  eval CKPT --task T_split ...   multiple-choice benchmark evaluation (few-shot, accuracy per category)
   export CKPT OUT [--dtype D]    re-shard / cast a checkpoint
   serve CKPT [--tp N ...]        OpenAI-compatible server on the native serving engine
   api CKPT                       alias of serve
@@ -90,6 +91,9 @@ def launch(argv: List[str]) -> int:
     if cmd == "preprocess":
         from .data.sharded_preprocess import main as prep_main
         return prep_main(rest)
+    if cmd == "eval":
+        from .train.evaluate import main as eval_main
+        return eval_main(rest)
     if cmd == "export":
         from .utils.export import main as export_main
         return export_main(rest)

@@ -282,3 +282,55 @@ def test_every_chat_template_encodes_a_two_turn_conversation():
     register_template(Template("my_format", user_fmt="Q: {content}\\nA:", assistant_fmt=" {content}\\n"))
     with pytest.raises(ValueError):
         register_template(Template("qwen3"))
+
+
+def test_multiple_choice_evaluator(tmp_path, capsys):
+    from hybrid_model_factory_b200.models.configuration import HybridConfig
+    from hybrid_model_factory_b200.models.modeling_hybrid import build_model
+    from hybrid_model_factory_b200.train import evaluate as E
+    from hybrid_model_factory_b200.utils import checkpoint_io
+    root = tmp_path / "evaluation" / "toy"
+    root.mkdir(parents=True)
+    (root / "mapping.json").write_text(json.dumps({"algebra": {"name": "algebra", "category": "STEM"},
+                                                   "history": {"name": "world history", "category": "Humanities"}}))
+    letters = "ABCD"
+
+    def make(n, off):
+        return [{"question": f"question {i} #{letters[(i + off) % 4]}", "A": "one", "B": "two", "C": "three", "D": "four",
+                 "answer": letters[(i + off) % 4]} for i in range(n)]
+    for subj, off in (("algebra", 0), ("history", 1)):
+        (root / f"{subj}.json").write_text(json.dumps({"train": make(6, off + 2), "test": make(8, off)}))
+
+    class Oracle(torch.nn.Module):
+        """Reads the letter after the last '#' of the prompt: a perfect model for this toy task."""
+        def __init__(self, always=None):
+            super().__init__()
+            self.w = torch.nn.Parameter(torch.zeros(1))
+            self.always = always
+
+        def forward(self, ids, logits_to_keep=1):
+            out = torch.zeros(ids.shape[0], 1, 259)
+            for b, row in enumerate(ids.tolist()):
+                pos = max(i for i, t in enumerate(row) if t == ord("#"))
+                out[b, 0, ord(self.always) if self.always else row[pos + 1]] = 5.0
+            return type("O", (), {"logits": out})()
+    tok, tpl = ByteTokenizer(), get_template("qwen3")
+    args = E.EvaluationArguments(task="toy_test", task_dir=str(tmp_path / "evaluation"), n_shot=3, batch_size=4,
+                                 save_dir=str(tmp_path / "res"))
+    res = E.Evaluator(Oracle(), tok, tpl, args).evaluate()
+    assert res["Average"] == 100.0 and res["STEM"] == 100.0 and res["subject/history"] == 100.0
+    assert json.load(open(tmp_path / "res" / "results.json"))["algebra"]["1"] == "B"
+    assert "Average" in open(tmp_path / "res" / "results.log").read()
+    res_a = E.Evaluator(Oracle(always="A"), tok, tpl, args).evaluate()
+    assert res_a["Average"] == 25.0
+    # few-shot prompt: header once, three solved exemplars, then the open question
+    ev = E.Evaluator(Oracle(), tok, tpl, args)
+    msgs = ev.eval_template.format_example(make(1, 0)[0], make(3, 2), "algebra")
+    assert len(msgs) == 8 and msgs[0]["content"].startswith("The following are multiple choice questions")
+    assert msgs[1]["content"] in letters and msgs[-2]["content"].endswith("Answer:")
+    # a real (untrained) checkpoint through the command line
+    cfg = HybridConfig(**TINY)
+    checkpoint_io.save_pretrained(build_model(cfg), str(tmp_path / "ckpt"))
+    assert E.main([str(tmp_path / "ckpt"), "--task", "toy_test", "--task-dir", str(tmp_path / "evaluation"), "--n-shot", "1",
+                   "--template", "qwen3"]) == 0
+    assert "Average" in capsys.readouterr().out
