@@ -334,3 +334,27 @@ def test_multiple_choice_evaluator(tmp_path, capsys):
     assert E.main([str(tmp_path / "ckpt"), "--task", "toy_test", "--task-dir", str(tmp_path / "evaluation"), "--n-shot", "1",
                    "--template", "qwen3"]) == 0
     assert "Average" in capsys.readouterr().out
+
+
+def test_example_configs_parse():
+    """Every file under examples/ is accepted by the parser it is meant for."""
+    import glob
+    from hybrid_model_factory_b200.models.patterns import is_fused, parse_override_pattern
+    from hybrid_model_factory_b200.priming.hybridize_model import load_config, verify_hybrid_config
+    from hybrid_model_factory_b200.train.workflow import zero_config
+    root = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "examples")
+    stage0 = sorted(glob.glob(os.path.join(root, "priming", "stage0", "*.yaml")))
+    assert len(stage0) >= 4
+    for path in stage0:
+        cfg = load_config(path)
+        verify_hybrid_config(cfg, 36)
+        assert any(is_fused(s) for s in parse_override_pattern(cfg.hybrid_override_pattern).values()), path
+    train = sorted(glob.glob(os.path.join(root, "priming", "stage[12]", "*.yaml")) +
+                   glob.glob(os.path.join(root, "tokenization", "*.yaml")))
+    assert len(train) >= 6
+    for path in train:
+        model_args, data_args, run_args, ft_args, _ = get_train_args([path])
+        assert ft_args.stage in ("pt", "sft", "hkd", "dpo") and data_args.cutoff_len >= 4096, path
+    stages = {os.path.basename(p): zero_config(p) for p in glob.glob(os.path.join(root, "zero", "*.json"))}
+    assert stages["ds_z3_offload_config.json"] == {"zero_stage": 3, "offload_optimizer": True}
+    assert stages["ds_z3_mics_config.json"]["mics_shard_size"] == 8 and stages["ds_z2_config.json"]["zero_stage"] == 2
