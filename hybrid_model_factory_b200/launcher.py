@@ -24,7 +24,7 @@ USAGE = """usage: hmf <command> [args]
   preprocess --config CFG.yaml   tokenise (and SP-split) datasets into `tokenized_path`, sharded and parallel
   eval CKPT --task T_split ...   multiple-choice benchmark evaluation (few-shot, accuracy per category)
   export CKPT OUT [--dtype D]    re-shard / cast a checkpoint
-  serve CKPT [--tp N ...]        OpenAI-compatible server on the native serving engine
+  serve CKPT [--port P ...]      OpenAI-compatible server on the native engine (under torchrun: tensor parallel)
   api CKPT                       alias of serve
   chat CKPT                      interactive chat in the terminal
   bench-serve CKPT|CONFIG ...    serving benchmark (continuous batching workload)

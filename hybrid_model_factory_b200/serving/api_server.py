@@ -19,12 +19,35 @@ from ..utils import checkpoint_io
 from .engine import SamplingParams, ServingEngine
 
 
-class EngineLoop:
-    """Runs ``engine.step()`` in a thread and routes new tokens to per-request asyncio queues."""
+class ControlChannel:
+    """Rank 0 of a tensor-parallel server tells the other ranks what it is about to do: a small object broadcast on a
+    gloo group before every engine step (new requests, stop).  The engine itself is deterministic given the same
+    request stream, so this is all the followers need to stay in lock-step."""
 
-    def __init__(self, engine: ServingEngine):
-        self.engine = engine
+    def __init__(self):
+        import torch.distributed as dist
+        self.dist = dist
+        self.group = dist.new_group(backend="gloo")
+        self.rank = dist.get_rank()
+
+    def broadcast(self, msg=None):
+        box = [msg]
+        self.dist.broadcast_object_list(box, src=0, group=self.group)
+        return box[0]
+
+
+def _params_to_dict(p: SamplingParams) -> dict:
+    return {k: getattr(p, k) for k in ("max_new_tokens", "temperature", "top_k", "eos_token_id", "ignore_eos")}
+
+
+class EngineLoop:
+    """Runs ``engine.step()`` in a thread and routes new tokens to per-request asyncio queues.  With a
+    ``ControlChannel`` (tensor parallelism) every step is announced to the follower ranks first."""
+
+    def __init__(self, engine: ServingEngine, control: Optional[ControlChannel] = None):
+        self.engine, self.control = engine, control
         self.lock = threading.Lock()
+        self.pending: List[tuple] = []
         self.queues: Dict[int, tuple] = {}
         self.wake = threading.Event()
         self.stop = False
@@ -34,16 +57,23 @@ class EngineLoop:
     def submit(self, prompt: List[int], params: SamplingParams, loop) -> tuple:
         q: asyncio.Queue = asyncio.Queue()
         with self.lock:
-            rid = self.engine.add_request(prompt, params)
-            self.queues[rid] = (q, loop)
+            self.pending.append((list(prompt), params, q, loop))
         self.wake.set()
-        return rid, q
+        return None, q
 
     def _run(self):
-        while not self.stop:
+        while True:
             with self.lock:
-                busy = self.engine.has_unfinished()
-                results = self.engine.step() if busy else []
+                new, self.pending = self.pending, []
+            stop = self.stop
+            if self.control is not None:
+                self.control.broadcast({"add": [(p, _params_to_dict(sp)) for p, sp, _, _ in new], "stop": stop})
+            if stop:
+                return
+            for prompt, params, q, loop in new:
+                self.queues[self.engine.add_request(prompt, params)] = (q, loop)
+            busy = self.engine.has_unfinished()
+            results = self.engine.step() if busy else []
             for rid, tok, done in results:
                 entry = self.queues.get(rid)
                 if entry:
@@ -56,11 +86,27 @@ class EngineLoop:
                 self.wake.clear()
 
 
-def create_app(engine: ServingEngine, tokenizer, model_name: str = "hybrid", template: Optional[str] = None):
+def follow(engine: ServingEngine, control: ControlChannel) -> int:
+    """Loop of the tensor-parallel ranks other than 0: replay rank 0's request stream and step with it.  Returns the
+    number of engine steps taken."""
+    steps = 0
+    while True:
+        msg = control.broadcast()
+        if msg["stop"]:
+            return steps
+        for prompt, params in msg["add"]:
+            engine.add_request(prompt, SamplingParams(**params))
+        if engine.has_unfinished():
+            engine.step()
+            steps += 1
+
+
+def create_app(engine: ServingEngine, tokenizer, model_name: str = "hybrid", template: Optional[str] = None,
+               control: Optional[ControlChannel] = None):
     from fastapi import FastAPI
     from fastapi.responses import JSONResponse, StreamingResponse
     app = FastAPI(title="hybrid-model-factory (B200 native) server")
-    loop_runner = EngineLoop(engine)
+    loop_runner = EngineLoop(engine, control)
     tpl = get_template(template)
 
     def params_from(body: dict) -> SamplingParams:
@@ -145,13 +191,38 @@ def main(argv=None) -> int:
     ap.add_argument("--hf-overrides", default=None, help='JSON, e.g. {"gka_overrides": {"num_iter": 10}}')
     args = ap.parse_args(argv)
     overrides = json.loads(args.hf_overrides) if args.hf_overrides else {}
-    device = torch.device("cuda", 0) if torch.cuda.is_available() else torch.device("cpu")
+    import os
+    world, local = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("LOCAL_RANK", "0"))
+    device = torch.device("cuda", local) if torch.cuda.is_available() else torch.device("cpu")
     model = checkpoint_io.from_pretrained(args.model, device=device, **overrides)
+    tp = control = None
+    if world > 1:       # launched by torchrun: tensor parallel over all ranks, rank 0 serves HTTP
+        import torch.distributed as dist
+        from ..parallel.tp import TPContext, shard_model
+        if device.type == "cuda":
+            torch.cuda.set_device(device)
+            dist.init_process_group("nccl", device_id=device)
+        else:
+            dist.init_process_group("gloo")
+        tp = TPContext(dist.group.WORLD)
+        if device.type == "cuda":
+            tp.enable_fused_gemm(max_m=256, max_n=8192)
+        shard_model(model, tp)
+        torch.manual_seed(0)           # stochastic sampling must draw the same numbers on every rank
+        control = ControlChannel()
     engine = ServingEngine(model, max_num_seqs=args.max_num_seqs, max_num_batched_tokens=args.max_num_batched_tokens,
-                           max_model_len=args.max_model_len, enable_prefix_caching=args.enable_prefix_caching)
+                           max_model_len=args.max_model_len, enable_prefix_caching=args.enable_prefix_caching, tp=tp)
+    if control is not None and control.rank != 0:
+        follow(engine, control)
+        return 0
     import uvicorn
-    uvicorn.run(create_app(engine, load_tokenizer(args.model), model_name=args.model, template=args.template),
-                host=args.host, port=args.port)
+    app = create_app(engine, load_tokenizer(args.model), model_name=args.model, template=args.template, control=control)
+    try:
+        uvicorn.run(app, host=args.host, port=args.port)
+    finally:
+        app.state.loop_runner.stop = True      # also releases the follower ranks
+        app.state.loop_runner.wake.set()
+        app.state.loop_runner.thread.join(timeout=5)
     return 0
 
 

@@ -389,3 +389,49 @@ def test_chat_cli_round_trip(tmp_path, monkeypatch, capsys):
     assert chat.main([str(tmp_path / "ckpt"), "--max-new-tokens", "4", "--template", "qwen3"]) == 0
     out = capsys.readouterr().out
     assert out.count("Assistant:") == 2
+
+
+def _tp_server_worker(rank, world):
+    import asyncio
+    import json
+    import torch.distributed as dist
+    from hybrid_model_factory_b200.data.formats import ByteTokenizer
+    from hybrid_model_factory_b200.parallel.tp import TPContext, shard_model
+    from hybrid_model_factory_b200.serving import api_server as S
+    torch.manual_seed(0)
+    cfg = tiny("*-GDN-M2", vocab_size=260)
+    model = build_model(cfg).eval()
+    tok = ByteTokenizer()
+    prompts = ["hello there", "tensor parallel"]
+    want = []
+    for p in prompts:
+        ids = tok.encode(p, add_special_tokens=False)
+        want.append(model.generate(torch.tensor([ids]), max_new_tokens=6)[0, len(ids):].tolist())
+    tp = TPContext(dist.group.WORLD)
+    shard_model(model, tp)
+    control = S.ControlChannel()
+    eng = ServingEngine(model, block_size=4, num_blocks=128, max_num_seqs=4, max_num_batched_tokens=32, max_model_len=128,
+                        tp=tp)
+    if rank != 0:
+        assert S.follow(eng, control) >= 6          # stepped along with rank 0 until it was told to stop
+        return
+    app = S.create_app(eng, tok, model_name="tiny", control=control)
+    routes = {r.path: r.endpoint for r in app.routes if hasattr(r, "endpoint")}
+
+    async def scenario():
+        resps = await asyncio.gather(*[routes["/v1/completions"]({"prompt": p, "max_tokens": 6, "ignore_eos": True})
+                                       for p in prompts])
+        return [json.loads(r.body)["choices"][0]["text"] for r in resps]
+    try:
+        texts = asyncio.run(scenario())
+    finally:
+        app.state.loop_runner.stop = True
+        app.state.loop_runner.wake.set()
+        app.state.loop_runner.thread.join(timeout=10)
+    assert texts == [tok.decode(w) for w in want], (texts, want)
+
+
+def test_tensor_parallel_api_server_gloo():
+    """Rank 0 serves the routes, rank 1 follows the broadcast request stream; outputs equal the unsharded model's."""
+    from dist_utils import run_ranks
+    run_ranks(_tp_server_worker, 2)
