@@ -51,6 +51,7 @@ class EngineLoop:
         self.queues: Dict[int, tuple] = {}
         self.wake = threading.Event()
         self.stop = False
+        self.error: Optional[BaseException] = None
         self.thread = threading.Thread(target=self._run, daemon=True)
         self.thread.start()
 
@@ -62,6 +63,26 @@ class EngineLoop:
         return None, q
 
     def _run(self):
+        try:
+            self._loop()
+        except BaseException as e:      # an engine failure must not leave handlers and follower ranks waiting for ever
+            self.error = e
+            self.stop = True
+            if self.control is not None:
+                try:
+                    self.control.broadcast({"add": [], "stop": True})
+                except Exception:
+                    pass
+            with self.lock:
+                waiting = list(self.queues.values()) + [(q, loop) for _, _, q, loop in self.pending]
+                self.queues.clear()
+                self.pending = []
+            for q, loop in waiting:
+                loop.call_soon_threadsafe(q.put_nowait, (None, True))
+            import logging
+            logging.getLogger(__name__).exception("engine thread stopped: %r", e)
+
+    def _loop(self):
         while True:
             with self.lock:
                 new, self.pending = self.pending, []
@@ -115,6 +136,8 @@ def create_app(engine: ServingEngine, tokenizer, model_name: str = "hybrid", tem
                               ignore_eos=bool(body.get("ignore_eos", False)))
 
     async def run(prompt_ids: List[int], body: dict, chat: bool):
+        if loop_runner.error is not None:
+            return JSONResponse({"error": repr(loop_runner.error)}, status_code=500)
         rid, q = loop_runner.submit(prompt_ids, params_from(body), asyncio.get_running_loop())
         created, cid = int(time.time()), f"cmpl-{uuid.uuid4().hex[:12]}"
         if body.get("stream"):
@@ -122,6 +145,9 @@ def create_app(engine: ServingEngine, tokenizer, model_name: str = "hybrid", tem
                 toks, sent = [], 0          # incremental detokenisation: a character may span several tokens
                 while True:
                     tok, done = await q.get()
+                    if tok is None:         # the engine thread failed
+                        yield "data: " + json.dumps({"error": repr(loop_runner.error)}) + "\n\n"
+                        return
                     toks.append(tok)
                     full = tokenizer.decode(toks)
                     if not done and full.endswith("\ufffd"):
@@ -137,6 +163,8 @@ def create_app(engine: ServingEngine, tokenizer, model_name: str = "hybrid", tem
         toks = []
         while True:
             tok, done = await q.get()
+            if tok is None:                 # the engine thread failed
+                return JSONResponse({"error": repr(loop_runner.error)}, status_code=500)
             toks.append(tok)
             if done:
                 break

@@ -435,3 +435,26 @@ def test_tensor_parallel_api_server_gloo():
     """Rank 0 serves the routes, rank 1 follows the broadcast request stream; outputs equal the unsharded model's."""
     from dist_utils import run_ranks
     run_ranks(_tp_server_worker, 2)
+
+
+def test_api_server_reports_an_engine_failure_instead_of_hanging():
+    import asyncio
+    import json
+    from hybrid_model_factory_b200.data.formats import ByteTokenizer
+    from hybrid_model_factory_b200.serving.api_server import create_app
+    model = build_model(tiny("*-GDN", vocab_size=259)).eval()
+    eng = ServingEngine(model, block_size=4, num_blocks=64, max_num_seqs=2, max_num_batched_tokens=16, max_model_len=64)
+
+    def boom():
+        raise RuntimeError("engine exploded")
+    eng.step = boom
+    app = create_app(eng, ByteTokenizer(), model_name="tiny")
+    routes = {r.path: r.endpoint for r in app.routes if hasattr(r, "endpoint")}
+
+    async def scenario():
+        r1 = await asyncio.wait_for(routes["/v1/completions"]({"prompt": "hi", "max_tokens": 2}), timeout=20)
+        r2 = await asyncio.wait_for(routes["/v1/completions"]({"prompt": "again", "max_tokens": 2}), timeout=20)
+        return r1, r2
+    r1, r2 = asyncio.run(scenario())
+    assert r1.status_code == 500 and "engine exploded" in json.loads(r1.body)["error"]
+    assert r2.status_code == 500
