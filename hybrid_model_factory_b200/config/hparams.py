@@ -6,8 +6,8 @@ keep working (``hparams/model_args.py``, ``data_args.py``, ``training_args.py``,
 from __future__ import annotations
 
 import json
-from dataclasses import asdict, dataclass, field, fields
-from typing import Any, Dict, List, Optional
+from dataclasses import asdict, dataclass, fields
+from typing import Any, Dict, Optional
 
 
 @dataclass

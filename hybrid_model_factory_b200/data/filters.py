@@ -6,7 +6,7 @@ response text of every record and reports how many each one removed.
 from __future__ import annotations
 
 from collections import Counter
-from typing import Callable, Dict, Iterable, List, Sequence, Tuple
+from typing import Callable, Iterable, List, Sequence, Tuple
 
 
 def ngram_repetition_ratio(text: str, n: int = 4) -> float:

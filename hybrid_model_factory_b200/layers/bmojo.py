@@ -8,7 +8,6 @@ Reference: ``layers/bmojo_f/modules.py:31-211``, ``bmojo_attention.py:69-503``,
 """
 from __future__ import annotations
 
-from typing import Optional
 
 import torch
 import torch.nn as nn

@@ -13,7 +13,6 @@ halo of the pre-convolution activations and the recurrence receives its incoming
 """
 from __future__ import annotations
 
-import math
 from dataclasses import asdict, dataclass
 from typing import Optional
 

@@ -9,7 +9,6 @@ Reference: ``layers/mamba/mamba2.py:98-693`` and ``mamba2_config.py:58-122``.
 """
 from __future__ import annotations
 
-import math
 from dataclasses import asdict, dataclass, field
 from typing import Optional
 

@@ -9,7 +9,7 @@ context the experts are sharded over ranks and tokens are exchanged by all-to-al
 """
 from __future__ import annotations
 
-from typing import Optional, Tuple
+from typing import Tuple
 
 import torch
 import torch.nn.functional as F

@@ -14,7 +14,6 @@ Math follows the reference project's layers:
 """
 from __future__ import annotations
 
-import math
 from typing import Optional, Tuple
 
 import torch

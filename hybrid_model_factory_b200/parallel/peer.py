@@ -20,7 +20,7 @@ opposite chain of epoch ``e``, already waited for the reader of epoch ``e``).
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Dict, List, Optional, Tuple
+from typing import Dict, List, Optional
 
 import torch
 import torch.distributed as dist

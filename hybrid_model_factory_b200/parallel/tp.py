@@ -14,7 +14,7 @@ the fused GEMM + reduce over peer memory for the decode-size case, this module f
 """
 from __future__ import annotations
 
-from typing import List, Optional, Sequence
+from typing import Optional, Sequence
 
 import torch
 import torch.distributed as dist

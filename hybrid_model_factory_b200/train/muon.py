@@ -6,7 +6,7 @@ whole matrix).  Reference: the vendored ``third_party/muon/muon.py`` selected by
 """
 from __future__ import annotations
 
-from typing import Iterable, List, Optional
+from typing import List, Optional
 
 import torch
 import torch.distributed as dist

@@ -19,7 +19,7 @@ gets the same behaviour from DeepSpeed ZeRO-3 (+ CPU offload) configs (``example
 """
 from __future__ import annotations
 
-from typing import Dict, Iterable, List, Optional, Sequence
+from typing import Dict, List, Optional, Sequence
 
 import torch
 import torch.distributed as dist
