@@ -24,7 +24,7 @@ USAGE = """usage: hmf <command> [args]
   preprocess --config CFG.yaml   tokenise (and SP-split) datasets into `tokenized_path`, sharded and parallel
   eval CKPT --task T_split ...   multiple-choice benchmark evaluation (few-shot, accuracy per category)
   export CKPT OUT [--dtype D]    re-shard / cast a checkpoint
-  serve CKPT [--port P ...]      OpenAI-compatible server on the native engine (under torchrun: tensor parallel)
+  serve CKPT [--tp N --port P]   OpenAI-compatible server on the native engine (--tp N: tensor parallel over N GPUs)
   api CKPT                       alias of serve
   chat CKPT                      interactive chat in the terminal
   bench-serve CKPT|CONFIG ...    serving benchmark (continuous batching workload)
@@ -55,6 +55,14 @@ def torchrun_command(script_args: List[str]) -> List[str]:
                 "--master-addr", os.environ.get("MASTER_ADDR", "127.0.0.1"),
                 "--master-port", os.environ.get("MASTER_PORT", "29500")]
     return cmd + ["-m", "hybrid_model_factory_b200.launcher", "--worker", "train"] + script_args
+
+
+def serve_command(tp: int, server_args: List[str]) -> List[str]:
+    """torchrun command line of a tensor-parallel server on this node (rank 0 serves HTTP, the others follow)."""
+    return [sys.executable, "-m", "torch.distributed.run", "--nnodes", "1", "--nproc-per-node", str(tp),
+            "--master-addr", os.environ.get("MASTER_ADDR", "127.0.0.1"),
+            "--master-port", os.environ.get("MASTER_PORT", "29500"),
+            "-m", "hybrid_model_factory_b200.serving.api_server"] + list(server_args)
 
 
 def launch(argv: List[str]) -> int:
@@ -98,6 +106,11 @@ def launch(argv: List[str]) -> int:
         from .utils.export import main as export_main
         return export_main(rest)
     if cmd in ("serve", "api"):
+        if "--tp" in rest and "WORLD_SIZE" not in os.environ:       # tensor parallel: one process per GPU under torchrun
+            i = rest.index("--tp")
+            tp, rest = int(rest[i + 1]), rest[:i] + rest[i + 2:]
+            if tp > 1:
+                return subprocess.call(serve_command(tp, rest))
         from .serving.api_server import main as serve_main
         return serve_main(rest)
     if cmd == "chat":

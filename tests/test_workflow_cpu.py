@@ -223,6 +223,9 @@ def test_launcher_commands_and_torchrun_command(tmp_path, monkeypatch, capsys):
     assert el[el.index("--nnodes") + 1] == "1:2" and el[el.index("--rdzv-id") + 1] == "job7"
     assert el[el.index("--max-restarts") + 1] == "3" and el[el.index("--rdzv-endpoint") + 1] == "127.0.0.1:29611"
     monkeypatch.delenv("RDZV_ID")
+    sc = launcher.serve_command(4, ["ckpt", "--port", "8123"])
+    assert sc[sc.index("--nproc-per-node") + 1] == "4" and sc[-3:] == ["ckpt", "--port", "8123"]
+    assert "hybrid_model_factory_b200.serving.api_server" in sc
     # single-process training through the command line entry
     y = tmp_path / "c.yaml"
     y.write_text("model_name_or_path: '%s'\nstage: pt\nsynthetic: true\ncutoff_len: 16\nmax_steps: 1\noutput_dir: %s\n"
