@@ -64,6 +64,8 @@ class EngineLoop:
 
     def _run(self):
         try:
+            if self.engine.device.type == "cuda":       # a new thread starts on device 0
+                torch.cuda.set_device(self.engine.device)
             self._loop()
         except BaseException as e:      # an engine failure must not leave handlers and follower ranks waiting for ever
             self.error = e
@@ -240,6 +242,10 @@ def main(argv=None) -> int:
         control = ControlChannel()
     engine = ServingEngine(model, max_num_seqs=args.max_num_seqs, max_num_batched_tokens=args.max_num_batched_tokens,
                            max_model_len=args.max_model_len, enable_prefix_caching=args.enable_prefix_caching, tp=tp)
+    if device.type == "cuda":
+        # capture the decode graphs here, on the main thread and on every rank at the same time; the serving thread
+        # then only replays them
+        engine.warmup(args.max_model_len)
     if control is not None and control.rank != 0:
         follow(engine, control)
         return 0
