@@ -245,7 +245,7 @@ def main(argv=None) -> int:
     if device.type == "cuda":
         # capture the decode graphs here, on the main thread and on every rank at the same time; the serving thread
         # then only replays them
-        engine.warmup(args.max_model_len)
+        engine.warmup(args.max_model_len, every_length=True)
     if control is not None and control.rank != 0:
         follow(engine, control)
         return 0

@@ -283,14 +283,23 @@ class ServingEngine:
             self._tables[rid] = t
         return t
 
-    def warmup(self, max_len: Optional[int] = None) -> int:
-        """Captures the decode graphs of every batch bucket (short- and long-context split counts) up front."""
+    def warmup(self, max_len: Optional[int] = None, every_length: bool = False) -> int:
+        """Captures the decode graphs of every batch bucket up front: for the shortest and the longest context, or
+        (``every_length``) for every KV split count a context between them can select, so that nothing is captured
+        later (a server replays from a thread other than the one that captured)."""
         if not self._use_graphs:
             return 0
+        longest = max_len or self.max_blocks_per_seq * self.block_size
+        lengths = {1, longest}
+        if every_length:
+            ml = 512
+            while ml < longest:
+                lengths.add(ml)
+                ml *= 2
         n, rows = 0, 1
         while True:
             rows = min(rows, self.sched.max_num_seqs)
-            for ml in {1, max_len or self.max_blocks_per_seq * self.block_size}:
+            for ml in sorted(lengths):
                 key = (rows, self._splits_for(rows, ml))
                 if key not in self._graphs:
                     tables = [[self._pad_block]] * rows if self.state.kv else None
