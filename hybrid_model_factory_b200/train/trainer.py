@@ -58,6 +58,7 @@ class TrainingArguments:
     optimizer_args: dict = field(default_factory=dict)
     zero_stage: int = 2                   # 2: flat AdamW with sharded states / gradients; 3: parameters sharded too
     offload_optimizer: bool = False       # ZeRO-3 only: moments and master weights in pinned host memory
+    offload_checkpoints: bool = False     # checkpointed layer inputs wait in pinned host memory until the backward pass
     mics_shard_size: int = 0              # ZeRO-3 only: shard inside groups of this many ranks, replicate across them
 
     def to_dict(self):
@@ -92,6 +93,9 @@ class Trainer:
         self.dp_size = self.world // sp_size
         if not args.disable_gradient_checkpointing and hasattr(model, "gradient_checkpointing_enable"):
             model.gradient_checkpointing_enable()
+            if args.offload_checkpoints:
+                from ..utils.checkpointing import set_offload
+                set_offload(True)
         params = list(trainable) if trainable is not None else [p for p in model.parameters() if p.requires_grad]
         sdt = None if args.optimizer_state_dtype == "auto" else getattr(torch, args.optimizer_state_dtype)
         if args.zero_stage == 3:

@@ -16,6 +16,26 @@ from typing import Callable, List, Optional
 import torch
 
 _state = threading.local()
+# Offloaded checkpoints: the saved layer inputs wait in pinned host memory between the forward and the backward pass
+# (at 128K tokens one hidden state is 1 GB per layer).  Off by default; `set_offload(True)` or the trainer argument
+# `offload_checkpoints`.  The copies are ordinary stream-ordered `copy_` calls, so they overlap with nothing by
+# themselves; they trade PCIe time for memory.
+_offload = {"enabled": False, "min_bytes": 1 << 20, "force_cpu_copy": False}
+
+
+def set_offload(enabled: bool, min_bytes: int = 1 << 20, force_cpu_copy: bool = False) -> None:
+    """``force_cpu_copy`` also moves CPU tensors through a copy (lets CPU tests exercise the path)."""
+    _offload.update(enabled=bool(enabled), min_bytes=int(min_bytes), force_cpu_copy=bool(force_cpu_copy))
+
+
+def _to_host(t: torch.Tensor):
+    if not _offload["enabled"] or t.numel() * t.element_size() < _offload["min_bytes"]:
+        return None
+    if t.is_cuda:
+        host = torch.empty(t.shape, dtype=t.dtype, device="cpu", pin_memory=True)
+        host.copy_(t, non_blocking=True)
+        return host
+    return t.detach().clone() if _offload["force_cpu_copy"] else None
 
 
 def stash_for_write() -> Optional[List]:
@@ -32,7 +52,12 @@ class _LayerCheckpoint(torch.autograd.Function):
     @staticmethod
     def forward(ctx, fn: Callable, use_stash: bool, *args):
         ctx.fn = fn
-        ctx.save_for_backward(*[a for a in args if isinstance(a, torch.Tensor)])
+        tensors = [a for a in args if isinstance(a, torch.Tensor)]
+        ctx.hosted = [(i, _to_host(t), t.device, t.requires_grad) for i, t in enumerate(tensors)]
+        ctx.hosted = [h for h in ctx.hosted if h[1] is not None]
+        moved = {i for i, _, _, _ in ctx.hosted}
+        # offloaded inputs are replaced by empty placeholders in the autograd-saved list
+        ctx.save_for_backward(*[t.new_empty(0) if i in moved else t for i, t in enumerate(tensors)])
         ctx.arg_is_tensor = [isinstance(a, torch.Tensor) for a in args]
         ctx.non_tensor = [a for a in args if not isinstance(a, torch.Tensor)]
         ctx.stash = [] if use_stash else None
@@ -51,6 +76,9 @@ class _LayerCheckpoint(torch.autograd.Function):
     @staticmethod
     def backward(ctx, *grads):
         tensors = list(ctx.saved_tensors)
+        for i, host, device, _ in ctx.hosted:          # bring the offloaded inputs back
+            tensors[i] = host.to(device, non_blocking=True)
+        ctx.hosted = []
         non_tensor = list(ctx.non_tensor)
         args, leaves = [], []
         for is_t in ctx.arg_is_tensor:

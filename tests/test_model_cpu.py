@@ -96,3 +96,31 @@ def test_layer_checkpoint_matches_plain_backward():
     m2(ids, labels=ids).loss.backward()
     for (n, a), (_, b) in zip(m1.named_parameters(), m2.named_parameters()):
         torch.testing.assert_close(a.grad, b.grad, rtol=1e-5, atol=1e-6, msg=n)
+
+
+def test_offloaded_checkpoints_give_the_same_gradients():
+    """Layer inputs parked in host memory between forward and backward (here: forced copies of CPU tensors)."""
+    import copy
+    from hybrid_model_factory_b200.utils import checkpointing
+    torch.manual_seed(0)
+    cfg = HybridConfig("hybrid_qwen3", vocab_size=128, hidden_size=64, intermediate_size=128, num_hidden_layers=3,
+                       num_attention_heads=4, num_key_value_heads=2, head_dim=16, hybrid_override_pattern="*-GDN-M2")
+    a = build_model(cfg)
+    b = copy.deepcopy(a)
+    ids = torch.randint(0, 128, (2, 24))
+    a.gradient_checkpointing_enable()
+    b.gradient_checkpointing_enable()
+    a.train(), b.train()
+    a(ids, labels=ids).loss.backward()
+    moved = []
+    orig = checkpointing._to_host
+    checkpointing.set_offload(True, min_bytes=0, force_cpu_copy=True)
+    checkpointing._to_host = lambda t: (moved.append(t.numel()) or orig(t))
+    try:
+        b(ids, labels=ids).loss.backward()
+    finally:
+        checkpointing._to_host = orig
+        checkpointing.set_offload(False)
+    assert len(moved) >= 3 and max(moved) == 2 * 24 * 64            # the hidden state of every layer went through a copy
+    for (n, p), q in zip(a.named_parameters(), b.parameters()):
+        assert torch.allclose(p.grad, q.grad, atol=1e-6), n
