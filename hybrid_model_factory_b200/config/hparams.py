@@ -45,6 +45,7 @@ class ModelArguments:
 @dataclass
 class DataArguments:
     dataset: Optional[str] = None                      # comma separated names from dataset_info.json
+    eval_dataset: Optional[str] = None                 # dataset(s) for `do_predict`
     dataset_dir: str = "data"
     tokenized_path: Optional[str] = None
     cutoff_len: int = 2048
@@ -72,6 +73,8 @@ class RunArguments:
     output_dir: str = "output"
     overwrite_output_dir: bool = False
     do_train: bool = True
+    do_predict: bool = False                           # generate over `eval_dataset` (or `dataset`) and score the text
+    predict_with_generate: bool = False                # accepted for compatibility (prediction always generates)
     per_device_train_batch_size: int = 1
     gradient_accumulation_steps: int = 1
     learning_rate: float = 1e-5

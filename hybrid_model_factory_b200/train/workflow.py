@@ -175,6 +175,23 @@ def run_ppo(model, ft_args, run_args, dataset, tokenizer, device, bsz):
     return trainer
 
 
+def run_prediction(model, tokenizer, data_args, run_args, gen_args):
+    """``do_predict``: generate an answer for every sample of ``eval_dataset`` (or ``dataset``), write
+    ``generated_predictions.jsonl`` and the text metrics to ``output_dir`` (single process)."""
+    import copy
+    from .predict import run_predict
+    da = copy.copy(data_args)
+    da.dataset = data_args.eval_dataset or data_args.dataset
+    da.tokenized_path, da.synthetic, da.disable_shuffling = None, False, True      # keep the file order
+    rows = get_dataset(da, tokenizer, stage="unsupervised")
+    rows = [rows[i] for i in range(len(rows))]
+    metrics = run_predict(model.eval(), tokenizer, rows, run_args.output_dir, max_new_tokens=gen_args.max_new_tokens,
+                          temperature=gen_args.temperature if gen_args.do_sample else 0.0, top_k=gen_args.top_k,
+                          max_model_len=data_args.cutoff_len + gen_args.max_new_tokens + 64)
+    info_rank0(logger, "prediction metrics: %s", metrics)
+    return metrics
+
+
 def run_exp(args: Optional[Any] = None) -> Trainer:
     model_args, data_args, run_args, ft_args, _ = get_train_args(args)
     init_distributed(run_args.ddp_timeout)
@@ -191,6 +208,8 @@ def run_exp(args: Optional[Any] = None) -> Trainer:
                 upcast_norms=getattr(model_args, "upcast_layernorm", False),
                 upcast_logits=getattr(model_args, "upcast_lmhead_output", False), gradient_checkpointing=False)
     stage = ft_args.stage
+    if run_args.do_predict and not run_args.do_train:
+        return run_prediction(model, tokenizer, data_args, run_args, _)
     if stage == "hkd" or ft_args.hybrid_learnable_params:
         n = freeze_params_hybrid(model, ft_args.hybrid_learnable_params)
         info_rank0(logger, "trainable parameters: %d", n)

@@ -361,3 +361,27 @@ def test_example_configs_parse():
     stages = {os.path.basename(p): zero_config(p) for p in glob.glob(os.path.join(root, "zero", "*.json"))}
     assert stages["ds_z3_offload_config.json"] == {"zero_stage": 3, "offload_optimizer": True}
     assert stages["ds_z3_mics_config.json"]["mics_shard_size"] == 8 and stages["ds_z2_config.json"]["zero_stage"] == 2
+
+
+def test_text_metrics_and_do_predict(tmp_path):
+    from hybrid_model_factory_b200.train import predict as P
+    a, b = "the cat sat on the mat".split(), "the cat lay on the mat".split()
+    assert P.rouge_n(a, a, 1) == 1.0 and abs(P.rouge_n(a, b, 1) - 5 / 6) < 1e-9
+    assert abs(P.rouge_n(a, b, 2) - 3 / 5) < 1e-9 and abs(P.rouge_l(a, b) - 5 / 6) < 1e-9
+    assert P.bleu4(a, a) == 1.0 and 0 < P.bleu4(a, b) < 1 and P.bleu4(["x"], a) == 0.0
+    assert P.bleu4(a[:3], a) < P.bleu4(a, a)                                 # brevity penalty
+    m = P.text_metrics(["hello world", "abc"], ["hello world", "abd"])
+    assert m["predict_exact_match"] == 50.0 and m["predict_rouge-l"] > 50.0
+    # through the workflow: an untrained tiny model generates for two prompts of a sharegpt file
+    (tmp_path / "dataset_info.json").write_text(json.dumps({"qa": {"file_name": "qa.json", "formatting": "sharegpt"}}))
+    (tmp_path / "qa.json").write_text(json.dumps([
+        {"conversations": [{"from": "human", "value": f"question {i}"}, {"from": "gpt", "value": f"answer {i}"}]}
+        for i in range(2)]))
+    out = str(tmp_path / "pred")
+    metrics = run_exp({"model_name_or_path": json.dumps(TINY), "stage": "sft", "do_train": False, "do_predict": True,
+                       "eval_dataset": "qa", "dataset_dir": str(tmp_path), "template": "qwen3", "cutoff_len": 128,
+                       "max_new_tokens": 5, "do_sample": False, "output_dir": out, "bf16": False, "pure_bf16": False})
+    assert set(metrics) == {"predict_exact_match", "predict_rouge-1", "predict_rouge-2", "predict_rouge-l", "predict_bleu-4"}
+    lines = [json.loads(l) for l in open(os.path.join(out, "generated_predictions.jsonl"))]
+    assert len(lines) == 2 and lines[0]["label"].startswith("answer 0") and "question 0" in lines[0]["prompt"]
+    assert os.path.exists(os.path.join(out, "predict_results.json"))
