@@ -90,6 +90,9 @@ class RunArguments:
     warmup_ratio: float = 0.0
     logging_steps: int = 1
     save_steps: int = 0
+    eval_steps: int = 0                                # with `val_size`: held-out loss every N steps and at the end
+    eval_strategy: str = "steps"                       # accepted for compatibility
+    per_device_eval_batch_size: int = 1
     save_only_model: bool = False
     save_max_shard_size: str = "5GB"
     seed: int = 42

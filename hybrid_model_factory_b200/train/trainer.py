@@ -46,6 +46,7 @@ class TrainingArguments:
     disable_gradient_checkpointing: bool = False
     logging_steps: int = 1
     save_steps: int = 0
+    eval_steps: int = 0                   # evaluate on the held-out batches every N steps (and at the end of training)
     save_only_model: bool = False
     save_max_shard_size: str = "5GB"
     seed: int = 42
@@ -172,6 +173,31 @@ class Trainer:
         self._last_lr = lr
         return total
 
+    # -- evaluation -----------------------------------------------------------------------------
+    @torch.no_grad()
+    def evaluate(self, batches: Iterable[Dict[str, torch.Tensor]]) -> float:
+        """Mean loss over ``batches`` (every rank evaluates its own share; the mean is taken over all ranks)."""
+        was_training = self.model.training
+        self.model.eval()
+        total, n = 0.0, 0
+        for batch in batches:
+            total += float(self.compute_loss(self._to_device(batch)))
+            n += 1
+        self.model.train(was_training)
+        if dist.is_initialized() and self.world > 1:
+            t = torch.tensor([total, float(n)], device=self.device, dtype=torch.float64)
+            dist.all_reduce(t)
+            total, n = float(t[0]), int(t[1])
+        return total / max(n, 1)
+
+    def _maybe_evaluate(self, force: bool = False) -> None:
+        fn = getattr(self, "eval_batches_fn", None)
+        if fn is None:
+            return
+        if force or (self.args.eval_steps and self.global_step % self.args.eval_steps == 0):
+            self.last_eval_loss = self.evaluate(fn())
+            self.log({"eval_loss": self.last_eval_loss})
+
     # -- loop ---------------------------------------------------------------------------------
     def train(self, batches: Iterable[Dict[str, torch.Tensor]]) -> None:
         for batch in batches:
@@ -183,8 +209,11 @@ class Trainer:
                 self.log({"loss": self._last_loss, "lr": self._last_lr})
             for cb in self.callbacks:
                 cb(self)
+            self._maybe_evaluate()
             if self.args.save_steps and self.global_step % self.args.save_steps == 0:
                 self.save_checkpoint(os.path.join(self.args.output_dir, f"checkpoint-{self.global_step}"))
+        if self.args.eval_steps == 0 or self.global_step % max(self.args.eval_steps, 1) != 0:
+            self._maybe_evaluate(force=True)
 
     def log(self, values: dict) -> None:
         elapsed = time.time() - self._t0

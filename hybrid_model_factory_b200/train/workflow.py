@@ -83,7 +83,7 @@ def to_trainer_args(model_args, data_args, run_args, n_batches: Optional[int]) -
         sequence_parallel_size=model_args.sequence_parallel_size, sequence_parallel_mode=model_args.sequence_parallel_mode,
         bf16=run_args.bf16, pure_bf16=run_args.pure_bf16,
         disable_gradient_checkpointing=run_args.disable_gradient_checkpointing, logging_steps=run_args.logging_steps,
-        save_steps=run_args.save_steps, save_only_model=run_args.save_only_model,
+        save_steps=run_args.save_steps, eval_steps=run_args.eval_steps, save_only_model=run_args.save_only_model,
         save_max_shard_size=run_args.save_max_shard_size, seed=run_args.seed,
         resume_from_checkpoint=run_args.resume_from_checkpoint, ddp_timeout=run_args.ddp_timeout,
         **zero_config(run_args.deepspeed))
@@ -257,6 +257,16 @@ def run_exp(args: Optional[Any] = None) -> Trainer:
         from ..parallel.sp import set_sequence_parallel_group_recursive
         set_sequence_parallel_group_recursive(teacher, trainer.sp)
     pad_id = getattr(tokenizer, "pad_token_id", None) or 0
+    if data_args.val_size and hasattr(dataset, "rows"):
+        # hold out the tail of the dataset (whole SP groups): `val_size` is a fraction below 1, a sample count above
+        from ..data.loader import ListDataset
+        groups = len(dataset) // sp
+        n_val = int(data_args.val_size * groups) if data_args.val_size < 1 else int(data_args.val_size)
+        n_val = max(1, min(n_val, groups - 1))
+        held = ListDataset(dataset.rows[(groups - n_val) * sp:groups * sp], dataset.labels_shifted)
+        dataset = ListDataset(dataset.rows[:(groups - n_val) * sp], dataset.labels_shifted)
+        ebs = run_args.per_device_eval_batch_size
+        trainer.eval_batches_fn = lambda: batch_iterator(held, ebs, rank, world, sp, pad_id, pin=device.type == "cuda")
     batches = batch_iterator(dataset, bsz, rank, world, sp, pad_id, start_step=trainer.global_step,
                              pin=device.type == "cuda")
     if run_args.do_train:

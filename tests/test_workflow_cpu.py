@@ -385,3 +385,17 @@ def test_text_metrics_and_do_predict(tmp_path):
     lines = [json.loads(l) for l in open(os.path.join(out, "generated_predictions.jsonl"))]
     assert len(lines) == 2 and lines[0]["label"].startswith("answer 0") and "question 0" in lines[0]["prompt"]
     assert os.path.exists(os.path.join(out, "predict_results.json"))
+
+
+def test_held_out_loss_during_training(tmp_path):
+    (tmp_path / "dataset_info.json").write_text(json.dumps({"docs": {"file_name": "docs.json", "formatting": "text",
+                                                                     "columns": {"prompt": "text"}}}))
+    (tmp_path / "docs.json").write_text(json.dumps([{"text": "abc abc abc " * 30} for _ in range(24)]))
+    out = str(tmp_path / "run")
+    tr = run_exp({"model_name_or_path": json.dumps(TINY), "stage": "pt", "dataset": "docs", "dataset_dir": str(tmp_path),
+                  "cutoff_len": 32, "val_size": 0.1, "eval_steps": 3, "max_steps": 6, "output_dir": out, "bf16": False,
+                  "pure_bf16": False, "learning_rate": 3e-3, "lr_scheduler_type": "constant",
+                  "per_device_train_batch_size": 2, "per_device_eval_batch_size": 2})
+    log = [json.loads(l) for l in open(os.path.join(out, "trainer_log.jsonl"))]
+    evals = [r["eval_loss"] for r in log if "eval_loss" in r]
+    assert len(evals) == 2 and evals[1] < evals[0] and abs(tr.last_eval_loss - evals[1]) < 1e-9
