@@ -458,3 +458,29 @@ def test_api_server_reports_an_engine_failure_instead_of_hanging():
     r1, r2 = asyncio.run(scenario())
     assert r1.status_code == 500 and "engine exploded" in json.loads(r1.body)["error"]
     assert r2.status_code == 500
+
+
+def test_state_shapes_match_the_engine_allocations():
+    """The published per-request state shapes agree with what `ServingState` allocates for each mixer type, and shrink
+    with the tensor-parallel size."""
+    from hybrid_model_factory_b200.serving import state_shapes as SS
+    from hybrid_model_factory_b200.serving.cache import ServingState
+    model = build_model(tiny("*-GDN-M2-GKA")).eval()
+    st = ServingState(model, num_blocks=8, block_size=4, num_slots=2, num_snapshots=0, device=torch.device("cpu"),
+                      dtype=torch.float32)
+    cfg = model.config
+    H, Hkv, D = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+    by_layer = {i: type(l.seq_mixer).__name__ for i, l in enumerate(model.model.layers)}
+    for i, entry in st.ssm.items():
+        name = by_layer[i]
+        rec = next(v for k, v in entry.items() if k in ("state", "recurrent", "h_kv"))
+        assert tuple(rec.shape[1:]) in (SS.gdn_state_shapes(H, H, H, D)["recurrent"][0],
+                                        SS.mamba2_state_shapes(H * D, Hkv * D, D)["ssm"][0]), (name, rec.shape)
+    kv = SS.attention_kv_shape(Hkv, D, 4)
+    k_cache = st.kv[0][0]
+    assert tuple(k_cache.shape[-2:]) == kv["k"][0][1:]
+    full = SS.bytes_per_request(SS.gka_state_shapes(32, 8, 32, 128))
+    half = SS.bytes_per_request(SS.gka_state_shapes(32, 8, 32, 128, tp=2))
+    assert full == 2 * half and SS.gka_state_shapes(32, 8, 32, 128, use_v_conv=False)["conv"][0][1] == 40 * 128
+    with pytest.raises(AssertionError):
+        SS.gdn_state_shapes(32, 8, 32, 128, tp=16)
