@@ -6,10 +6,13 @@ synthetic uniform-random token ids, random-init weights).
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
         --master-port P bench.py --gpus N --steps K --warmup W
 
-Two timed regions of K optimizer steps each, both through ``Trainer.train_step``:
-  * device region: inputs already resident on the GPU, timed with CUDA events (``value``);
-  * end-to-end region: every step copies its inputs from pinned host memory and reads the loss
-    back to the host, timed by the host clock around synchronised boundaries (``e2e``).
+ONE timed region of K optimizer steps through ``Trainer.train_step``, the call a user of the
+framework makes.  Every step copies its inputs from pinned host memory to the device and reads the
+loss back to the host.  The region is bracketed twice: by CUDA events on the launching stream
+(``value``, maximum over ranks) and by the host clock around synchronised boundaries (``e2e``).
+The process keeps to a wall-clock budget (``--time-budget`` seconds, default 780): when the warm-up
+steps show that K steps would not fit, fewer steps are timed and the line says so (``steps`` is the
+number actually timed, ``steps_requested`` what was asked).
 ``--impl reference`` runs (or reports why it cannot run) the unmodified reference project.
 """
 from __future__ import annotations
@@ -24,6 +27,7 @@ import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
+T_START = time.perf_counter()
 
 
 def parse_args():
@@ -35,7 +39,9 @@ def parse_args():
     ap.add_argument("--seq-len", type=int, default=int(os.environ.get("HMF_BENCH_SEQ_LEN", 131072)))
     ap.add_argument("--layers", type=int, default=36)
     ap.add_argument("--pattern", default="*-GDN")
-    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--ref-child", action="store_true", help=argparse.SUPPRESS)
+    ap.add_argument("--time-budget", type=float, default=float(os.environ.get("HMF_BENCH_BUDGET_S", 780)),
+                    help="wall-clock seconds the whole process may take; fewer steps are timed if K would not fit")
     return ap.parse_args()
 
 
@@ -84,8 +90,34 @@ class ClockSampler:
 
 
 def run_reference(args):
+    """Runs the reference arm in a child process per rank, so that a crash inside one of its native dependencies
+    (which ends the process, not a Python exception) still yields the one-line ``unavailable`` report."""
+    rank0 = int(os.environ.get("RANK", "0")) == 0
+    if not args.ref_child:
+        cmd = [sys.executable, os.path.abspath(__file__), "--ref-child"] + sys.argv[1:]
+        proc = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+        line = next((ln for ln in reversed(proc.stdout.splitlines()) if ln.startswith("{")), None)
+        if rank0:
+            if line is not None:
+                print(line, flush=True)
+            else:
+                err = [ln for ln in proc.stderr.splitlines() if "rror" in ln and not ln.startswith("frame")]
+                why = (err[-1] if err else proc.stderr[-300:]).strip()
+                print(json.dumps({"impl": "reference", "n_gpus": args.gpus,
+                                  "unavailable": f"reference process ended with code {proc.returncode}: {why[:500]}"}),
+                      flush=True)
+            sys.stderr.write(proc.stderr[-4000:])
+        return
     from baseline.reference_arm import run as run_ref
-    print(json.dumps(run_ref(args)), flush=True)
+    out = run_ref(args, ClockSampler, T_START)
+    if rank0:
+        print(json.dumps(out), flush=True)
+    try:
+        import torch.distributed as dist
+        if dist.is_initialized():
+            dist.destroy_process_group()
+    except Exception:
+        pass
 
 
 def main():
@@ -142,10 +174,24 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    resident = {k: (v.to(dev) if hasattr(v, "to") else v) for k, v in make_batch(0, False).items()}
-    for _ in range(args.warmup):
-        trainer.train_step(resident)
+    def fit_steps(sec_per_step: float, done_s: float) -> int:
+        """Number of timed steps that fit what is left of the wall-clock budget (same answer on every rank)."""
+        left = args.time_budget - done_s - 20.0                 # 20 s for the report and the teardown
+        n = max(1, min(args.steps, int(left / max(sec_per_step, 1e-6))))
+        t = torch.tensor([n], device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        return int(t)
+
+    from hybrid_model_factory_b200.utils import profiling
+    n_batches = 4                                               # distinct pinned batches, cycled
+    batches = [make_batch(i, True) for i in range(n_batches)]
+    h2d = sum(v.numel() * v.element_size() for v in batches[0].values() if hasattr(v, "numel"))
+    warm_t0 = time.perf_counter()
+    for i in range(args.warmup):
+        float(trainer.train_step(batches[i % n_batches]).item())
     sync()
+    warm_s = (time.perf_counter() - warm_t0) / max(args.warmup, 1)
     transport = "none" if trainer.sp is None else type(trainer.sp.transport).__name__
     if world > 1:
         # a device-side wait of the peer-memory state chain that ran out leaves a status code: fall back to the NCCL
@@ -156,48 +202,42 @@ def main():
             from hybrid_model_factory_b200.parallel.sp import StateTransport
             trainer.sp.transport = StateTransport(trainer.sp.group, trainer.sp.ranks)
             transport = "StateTransport (peer chain reported a timeout during warm-up)"
-            for _ in range(args.warmup):
-                trainer.train_step(resident)
+            for i in range(args.warmup):
+                float(trainer.train_step(batches[i % n_batches]).item())
             sync()
+    steps = fit_steps(warm_s, time.perf_counter() - T_START)
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+    profiling.enable_phases(True)
     launches0 = _lib.launch_count()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     sync()
+    t0 = time.perf_counter()
     ev0.record()
-    for _ in range(args.steps):
-        trainer.train_step(resident)
+    last = 0.0
+    for i in range(steps):
+        last = float(trainer.train_step(batches[i % n_batches]).item())   # H2D of the inputs, D2H of the loss
     ev1.record()
     sync()
+    host_s = time.perf_counter() - t0
     ms = ev0.elapsed_time(ev1)
     launches = _lib.launch_count() - launches0
-    t = torch.tensor([ms], device=dev)
+    t = torch.tensor([ms, host_s], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_per_step = t.item() / args.steps
-
-    e2e = None
-    if not args.no_e2e:
-        batches = [make_batch(i + 1, True) for i in range(args.steps)]
-        h2d = sum(v.numel() * v.element_size() for v in batches[0].values() if hasattr(v, "numel"))
-        sync()
-        t0 = time.perf_counter()
-        last = 0.0
-        for b in batches:
-            last = float(trainer.train_step(b).item())  # D2H read of the loss every step
-        sync()
-        dt = torch.tensor([time.perf_counter() - t0], device=dev)
-        if world > 1:
-            dist.all_reduce(dt, op=dist.ReduceOp.MAX)
-        e2e = {"value": S * args.steps / dt.item(), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
-               "d2h_bytes_per_step": 4, "last_loss": last}
+    ms_per_step = float(t[0]) / steps
+    e2e = {"value": S * steps / float(t[1]), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+           "d2h_bytes_per_step": 4, "last_loss": last,
+           "note": "same steps as `value`; host clock around synchronised boundaries, max over ranks"}
+    phases = {k: round(v["total_ms"] / steps, 3) for k, v in profiling.PHASES.summary().items()}
+    profiling.enable_phases(False)
     clocks = sampler.stop() if rank == 0 else None
     status = _lib.read_status()
     if rank == 0:
         value = S / (ms_per_step / 1e3)
         out = {"metric": "train tok/s (128K ctx, SP 1/2/4/8)", "value": value, "unit": "tokens/s", "n_gpus": world,
-               "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+               "steps": steps, "steps_requested": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
                "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform-random token ids, random-init weights",
                "config": {"model": f"GDN-primed Qwen3-8B ({args.layers} layers, pattern {args.pattern} tiled, hidden 4096, "
                                    "SwiGLU 12288, 32/8 heads x 128, vocab 151936)",
@@ -205,7 +245,7 @@ def main():
                           "optimizer": "AdamW bf16 states, ZeRO-sharded over all ranks, grad clip 1.0",
                           "activation_checkpointing": "per layer", "sp_state_transport": transport,
                           "l2": "working set per step far exceeds the 126 MB L2 (no flush needed)"},
-               "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "kernel_status": list(status),
+               "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "phase_ms_per_step": phases, "kernel_status": list(status),
                "impl": "ours"}
         print(json.dumps(out), flush=True)
     if world > 1:

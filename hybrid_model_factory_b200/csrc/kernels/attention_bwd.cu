@@ -751,6 +751,433 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   }
 }
 
+// ------------------------------------------------------------------------------------
+// Fused backward (D = 128): one kernel, five GEMMs per (key tile, query tile) pair
+// ------------------------------------------------------------------------------------
+// The key-tile owner computes S^T and dP^T once and derives all three gradients from them:
+//     dV += P^T dO,   dK += dS^T Q          (accumulated in tensor memory over the whole loop, as above)
+//     dQ^T(tile) = K^T dS                    (one fresh [128 d x 64 q] product per pair, added to an fp32 dQ buffer
+//                                             in global memory with red.global.add.f32)
+// The packed P^T and dS^T both go back into the S^T columns (P^T in [0,32), dS^T in [32,64)), so that the whole
+// dP^T buffer is free once the softmax threads have read it: the dQ^T product of the same pair is written there.
+// dS^T is also stored in shared memory ([key][query], 128-byte swizzle): the MN-major B operand of the dQ^T MMA,
+// whose A operand is the K tile read MN-major (M = d).  Four drain warps move each dQ^T tile from tensor memory to
+// the global buffer; consecutive lanes hold consecutive d of one query row, so every warp-level reduction is one
+// contiguous 128-byte line.  The fp32 buffer must be zero on entry; a small kernel converts it to bf16 afterwards.
+// Summation order across key tiles is not fixed: use the two-kernel path above when bit-reproducible gradients
+// are required.
+constexpr int FTHR = 512;   // warps 0-3: TMA, S/dP MMA, accumulate MMA, spare; 4-11: softmax; 12-15: dQ drain
+
+template <int D>
+struct SmemFused {
+  static constexpr int KPANEL = KM * 128;
+  static constexpr int QPANEL = QN * 128;
+  static constexpr int K_BYTES = KM * D * 2;
+  static constexpr int Q_BYTES = QN * D * 2;
+  static constexpr int OFF_V = K_BYTES;
+  static constexpr int NST = 4;
+  static constexpr int OFF_Q = 2 * K_BYTES;
+  static constexpr int STAGE = 2 * Q_BYTES;
+  static constexpr int DS_BYTES = KM * QN * 2;                // 16 KB: dS^T [128 keys][64 queries] bf16
+  static constexpr int OFF_DS = OFF_Q + NST * STAGE;
+  static constexpr int OFF_ROW = OFF_DS + 2 * DS_BYTES;       // lse2 / delta / qpos staging: 2 x 3 x 64 x 4
+  static constexpr int OFF_BAR = OFF_ROW + 2 * 3 * QN * 4;
+  static constexpr int TOTAL = OFF_BAR + 256;
+};
+
+template <int RegCount>
+__device__ __forceinline__ void reg_dealloc() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;\n" ::"n"(RegCount));
+}
+template <int RegCount>
+__device__ __forceinline__ void reg_alloc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;\n" ::"n"(RegCount));
+}
+
+template <int D>
+__global__ void __launch_bounds__(FTHR, 1)
+attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
+                      const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                      const Params p, float* __restrict__ dq_acc) {
+  static_assert(D == 128, "the fused backward is written for head dimension 128");
+  using L = SmemFused<D>;
+  constexpr int TMEM_COLS = 512;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint8_t* sK = smem;
+  uint8_t* sV = smem + L::OFF_V;
+  uint8_t* sQ = smem + L::OFF_Q;
+  uint8_t* sDS = smem + L::OFF_DS;
+  float* s_row = reinterpret_cast<float*>(smem + L::OFF_ROW);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
+  constexpr int NST = L::NST;
+  uint64_t* kv_full = bars + 0;
+  uint64_t* q_full = bars + 1;              // [NST]
+  uint64_t* q_empty = bars + 1 + NST;       // [NST]
+  uint64_t* st_full = bars + 1 + 2 * NST;   // [2] S^T / dP^T written by the MMAs
+  uint64_t* pds_full = bars + 3 + 2 * NST;  // [2] P^T / dS^T written by the softmax threads
+  uint64_t* dq_full = bars + 5 + 2 * NST;   // [2] dQ^T tile written by the MMAs (all MMAs of the pair are done)
+  uint64_t* t_free = bars + 7 + 2 * NST;    // [2] dQ^T tile read by the drain warps: the buffer pair is reusable
+  uint64_t* acc_done = bars + 9 + 2 * NST;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10 + 2 * NST);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const WaitCtx ctx{abort_flag, p.status};
+  const int kt = blockIdx.x;
+  const int hkv = blockIdx.y;
+  const int b = blockIdx.z;
+  const int k0 = kt * KM;
+  const int keys_valid = min(KM, p.Tk - k0);
+  const int G = p.Hq / p.Hkv;
+  const int nq_tiles = (p.Tq + QN - 1) / QN;
+
+  QTileIter iter;
+  iter.G = G;
+  iter.nq_tiles = nq_tiles;
+  if (p.q_pos) {
+    iter.i_lo = 0;
+    iter.i_hi = nq_tiles - 1;
+  } else {
+    long long rmin = (long long)k0 + p.lo - p.q_off;
+    long long rmax = (long long)k0 + keys_valid - 1 + (long long)p.hi - 1 - p.q_off;
+    if (rmin < 0) rmin = 0;
+    if (rmax > p.Tq - 1) rmax = p.Tq - 1;
+    iter.i_lo = (int)(rmin / QN);
+    iter.i_hi = (rmax >= rmin) ? (int)(rmax / QN) : iter.i_lo - 1;
+  }
+  const int n_it = iter.count();
+
+  if (threadIdx.x == 0) {
+    if ((smem_u32(smem) & 1023u) != 0) report_error(p.status, kBadArgument, 0xA3);
+    mbar_init(kv_full, 1);
+    for (int s = 0; s < NST; ++s) {
+      mbar_init(&q_full[s], 1);
+      mbar_init(&q_empty[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&st_full[s], 1);
+      mbar_init(&dq_full[s], 1);
+      mbar_init(&t_free[s], 128);
+      mbar_init(&pds_full[s], NSOFT);
+    }
+    mbar_init(acc_done, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  auto tST = [&](int s) -> uint32_t { return tmem_base + (uint32_t)s * 64u; };
+  auto tDPT = [&](int s) -> uint32_t { return tmem_base + 128u + (uint32_t)s * 64u; };   // later: dQ^T of the pair
+  const uint32_t tDV = tmem_base + 256, tDK = tmem_base + 256 + D;
+
+  const int wg = warp >> 2;
+  if (wg == 0) {
+    reg_dealloc<48>();
+    if (warp == 0) {
+      if (lane == 0 && n_it > 0) {
+        mbar_expect_tx(kv_full, 2 * L::K_BYTES);
+#pragma unroll
+        for (int pn = 0; pn < D / 64; ++pn) {
+          tma_load_4d(sK + pn * L::KPANEL, &tmK, kv_full, pn * 64, hkv, k0, b);
+          tma_load_4d(sV + pn * L::KPANEL, &tmV, kv_full, pn * 64, hkv, k0, b);
+        }
+        for (int it = 0; it < n_it; ++it) {
+          const int s = it % NST;
+          int g, i;
+          iter.get(it, g, i);
+          const int h = hkv * G + g;
+          if (it >= NST) mbar_wait(&q_empty[s], ((it / NST) - 1) & 1, ctx, 0x310 + s);
+          mbar_expect_tx(&q_full[s], L::STAGE);
+          uint8_t* dst = sQ + s * L::STAGE;
+#pragma unroll
+          for (int pn = 0; pn < D / 64; ++pn) {
+            tma_load_4d(dst + pn * L::QPANEL, &tmQ, &q_full[s], pn * 64, h, i * QN, b);
+            tma_load_4d(dst + L::Q_BYTES + pn * L::QPANEL, &tmDO, &q_full[s], pn * 64, h, i * QN, b);
+          }
+        }
+      }
+    } else if (warp == 1) {
+      if (lane == 0 && n_it > 0) {
+        constexpr uint32_t idescST = make_idesc_bf16(KM, QN, false, false);
+        const uint32_t aK = smem_u32(sK), aV = smem_u32(sV);
+        mbar_wait(kv_full, 0, ctx, 0x330);
+        for (int it = 0; it < n_it; ++it) {
+          const int s = it & 1, qs = it % NST;
+          if (it >= 2) mbar_wait(&t_free[s], ((it >> 1) - 1) & 1, ctx, 0x370 + s);
+          mbar_wait(&q_full[qs], (it / NST) & 1, ctx, 0x320 + qs);
+          tc_fence_after();
+          const uint32_t aQ = smem_u32(sQ + qs * L::STAGE);
+          const uint32_t aDO = aQ + L::Q_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < D / 16; ++kk) {
+            const uint64_t ad = make_desc_kmajor_sw128(aK + (kk / 4) * L::KPANEL + (kk % 4) * 32);
+            const uint64_t bd = make_desc_kmajor_sw128(aQ + (kk / 4) * L::QPANEL + (kk % 4) * 32);
+            umma_ss(tST(s), ad, bd, idescST, kk > 0 ? 1u : 0u);
+          }
+#pragma unroll
+          for (int kk = 0; kk < D / 16; ++kk) {
+            const uint64_t ad = make_desc_kmajor_sw128(aV + (kk / 4) * L::KPANEL + (kk % 4) * 32);
+            const uint64_t bd = make_desc_kmajor_sw128(aDO + (kk / 4) * L::QPANEL + (kk % 4) * 32);
+            umma_ss(tDPT(s), ad, bd, idescST, kk > 0 ? 1u : 0u);
+          }
+          umma_commit(&st_full[s]);
+        }
+      }
+    } else if (warp == 2) {
+      if (lane == 0 && n_it > 0) {
+        constexpr uint32_t idescAcc = make_idesc_bf16(KM, D, false, true);     // [128 keys x D], B MN-major
+        constexpr uint32_t idescDQ = make_idesc_bf16(D, QN, true, true);       // [D x 64 q], A and B MN-major
+        const uint32_t aK = smem_u32(sK);
+        for (int it = 0; it < n_it; ++it) {
+          const int s = it & 1, qs = it % NST;
+          mbar_wait(&q_full[qs], (it / NST) & 1, ctx, 0x380 + qs);
+          mbar_wait(&pds_full[s], (it >> 1) & 1, ctx, 0x340 + s);
+          tc_fence_after();
+          const uint32_t aQ = smem_u32(sQ + qs * L::STAGE);
+          const uint32_t aDO = aQ + L::Q_BYTES;
+          const uint32_t aDS = smem_u32(sDS + s * L::DS_BYTES);
+#pragma unroll
+          for (int kk = 0; kk < QN / 16; ++kk) {
+            const uint64_t bd = make_desc_mnmajor_sw128(aDO + kk * 2048, L::QPANEL);
+            umma_ts(tDV, tST(s) + kk * 8, bd, idescAcc, (it > 0 || kk > 0) ? 1u : 0u);
+          }
+#pragma unroll
+          for (int kk = 0; kk < QN / 16; ++kk) {
+            const uint64_t bd = make_desc_mnmajor_sw128(aQ + kk * 2048, L::QPANEL);
+            umma_ts(tDK, tST(s) + 32 + kk * 8, bd, idescAcc, (it > 0 || kk > 0) ? 1u : 0u);
+          }
+          umma_commit(&q_empty[qs]);
+          // dQ^T[d, q] = sum_key K[key, d] dS^T[key, q]: 8 steps of 16 keys
+#pragma unroll
+          for (int kk = 0; kk < KM / 16; ++kk) {
+            const uint64_t ad = make_desc_mnmajor_sw128(aK + kk * 2048, L::KPANEL);
+            const uint64_t bd = make_desc_mnmajor_sw128(aDS + kk * 2048, L::DS_BYTES);
+            umma_ss(tDPT(s), ad, bd, idescDQ, kk > 0 ? 1u : 0u);
+          }
+          umma_commit(&dq_full[s]);
+        }
+        umma_commit(acc_done);
+      }
+    }
+  } else if (wg == 3) {
+    // dQ drain: lane = d (quadrant * 32 + lane), 64 columns = the query rows of the tile
+    reg_dealloc<96>();
+    const int quad = warp & 3;
+    const int d = quad * 32 + lane;
+    const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
+    for (int it = 0; it < n_it; ++it) {
+      const int s = it & 1;
+      int g, i;
+      iter.get(it, g, i);
+      const int h = hkv * G + g;
+      const int q0 = i * QN;
+      const bool ok = mbar_wait(&dq_full[s], (it >> 1) & 1, ctx, 0x390 + s);
+      tc_fence_after();
+      float* base = dq_acc + (((size_t)b * p.Tq + q0) * p.Hq + h) * D + d;
+      const size_t rstride = (size_t)p.Hq * D;
+      const int nq = min(QN, p.Tq - q0);
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t v[32];
+        tmem_ld_x32(tDPT(s) + lane_off + half * 32, v);
+        tmem_ld_wait();
+        if (half == 1) {
+          tc_fence_before();
+          mbar_arrive(&t_free[s]);                    // registers hold the tile: the buffers may be overwritten
+        }
+        if (ok) {
+#pragma unroll
+          for (int c = 0; c < 32; ++c) {
+            const int qi = half * 32 + c;
+            if (qi < nq)
+              asm volatile("red.global.add.f32 [%0], %1;" ::"l"(base + (size_t)qi * rstride),
+                           "f"(__uint_as_float(v[c]))
+                           : "memory");
+          }
+        }
+      }
+    }
+  } else {
+    reg_alloc<184>();
+    const int quad = warp & 3;
+    const int part = (warp - 4) >> 2;
+    const int r = quad * 32 + lane;  // key row
+    const int tid = threadIdx.x - 128;  // 0..NSOFT-1
+    const long long kpos = (long long)k0 + r;
+    const bool key_ok = r < keys_valid;
+    const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
+    const int vis_lo = (int)min(kpos + (long long)p.lo, 2147483647ll);
+    const int vis_hi = (int)min(kpos + (long long)p.hi, 2147483647ll);
+    auto load_rows = [&](int it, float& v0, int& v1) {
+      int g, i;
+      iter.get(it, g, i);
+      const int h = hkv * G + g;
+      const int q0 = i * QN;
+      v0 = 0.f;
+      v1 = -(1 << 30);
+      if (tid < QN) {
+        const int qi = q0 + tid;
+        v0 = INFINITY;
+        if (qi < p.Tq) {
+          const float l = p.lse[((size_t)b * p.Hq + h) * p.Tq + qi];
+          v0 = (l == -INFINITY) ? INFINITY : l * kLog2e;
+          v1 = p.q_pos ? p.q_pos[(size_t)b * p.Tq + qi] : qi + p.q_off;
+        }
+      } else if (tid < 2 * QN) {
+        const int qi = q0 + tid - QN;
+        v0 = (qi < p.Tq) ? p.delta[((size_t)b * p.Hq + h) * p.Tq + qi] : 0.f;
+      }
+    };
+    auto store_rows = [&](int it, float v0, int v1) {
+      float* b_lse = s_row + (it & 1) * 3 * QN;
+      if (tid < QN) {
+        b_lse[tid] = v0;
+        reinterpret_cast<int*>(b_lse + 2 * QN)[tid] = v1;
+      } else if (tid < 2 * QN) {
+        b_lse[QN + tid - QN] = v0;
+      }
+    };
+    if (n_it > 0) {
+      float v0;
+      int v1;
+      load_rows(0, v0, v1);
+      store_rows(0, v0, v1);
+    }
+    for (int it = 0; it < n_it; ++it) {
+      const int s = it & 1;
+      int g, i;
+      iter.get(it, g, i);
+      const int q0 = i * QN;
+      float* st_lse = s_row + s * 3 * QN;
+      float* st_del = st_lse + QN;
+      int* st_pos = reinterpret_cast<int*>(st_del + QN);
+      float nv0 = 0.f;
+      int nv1 = 0;
+      if (it + 1 < n_it) load_rows(it + 1, nv0, nv1);
+      const long long pmin = (long long)q0 + p.q_off, pmax = pmin + QN - 1;
+      const bool full = p.q_pos == nullptr && keys_valid == KM && q0 + QN <= p.Tq &&
+                        pmin - ((long long)k0 + KM - 1) >= (long long)p.lo && pmax - (long long)k0 < (long long)p.hi;
+      asm volatile("bar.sync 1, %0;" ::"n"(NSOFT) : "memory");
+      mbar_wait(&st_full[s], (it >> 1) & 1, ctx, 0x350 + s);
+      tc_fence_after();
+      {
+        uint32_t sv[WCOLS], dp[WCOLS], pp[WCOLS / 2], pd[WCOLS / 2];
+        tmem_ld_n<WCOLS>(tST(s) + lane_off + part * WCOLS, sv);
+        tmem_ld_n<WCOLS>(tDPT(s) + lane_off + part * WCOLS, dp);
+        tmem_ld_wait();
+        if (full) {
+#pragma unroll
+          for (int c = 0; c < WCOLS; c += 4) {
+            const float4 l4 = *reinterpret_cast<const float4*>(st_lse + part * WCOLS + c);
+            const float4 d4 = *reinterpret_cast<const float4*>(st_del + part * WCOLS + c);
+            const float p0 = exp2f(fmaf(__uint_as_float(sv[c + 0]), p.scale_log2, -l4.x));
+            const float p1 = exp2f(fmaf(__uint_as_float(sv[c + 1]), p.scale_log2, -l4.y));
+            const float p2 = exp2f(fmaf(__uint_as_float(sv[c + 2]), p.scale_log2, -l4.z));
+            const float p3 = exp2f(fmaf(__uint_as_float(sv[c + 3]), p.scale_log2, -l4.w));
+            pp[(c >> 1) + 0] = pack_bf16x2(p0, p1);
+            pp[(c >> 1) + 1] = pack_bf16x2(p2, p3);
+            pd[(c >> 1) + 0] = pack_bf16x2(p0 * (__uint_as_float(dp[c + 0]) - d4.x) * p.scale,
+                                           p1 * (__uint_as_float(dp[c + 1]) - d4.y) * p.scale);
+            pd[(c >> 1) + 1] = pack_bf16x2(p2 * (__uint_as_float(dp[c + 2]) - d4.z) * p.scale,
+                                           p3 * (__uint_as_float(dp[c + 3]) - d4.w) * p.scale);
+          }
+        } else {
+#pragma unroll
+          for (int c = 0; c < WCOLS; c += 2) {
+            float pr[2], ds[2];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              const int cc = part * WCOLS + c + e;
+              const int pos = st_pos[cc];
+              const bool vis = key_ok && pos >= vis_lo && pos < vis_hi;
+              pr[e] = vis ? exp2f(fmaf(__uint_as_float(sv[c + e]), p.scale_log2, -st_lse[cc])) : 0.f;
+              ds[e] = pr[e] * (__uint_as_float(dp[c + e]) - st_del[cc]) * p.scale;
+            }
+            pp[c >> 1] = pack_bf16x2(pr[0], pr[1]);
+            pd[c >> 1] = pack_bf16x2(ds[0], ds[1]);
+          }
+        }
+        // dS^T row r, query columns [part * WCOLS, +WCOLS): 64 bytes = 4 swizzled 16-byte chunks of the row
+        uint8_t* ds_tile = sDS + s * L::DS_BYTES;
+#pragma unroll
+        for (int ch = 0; ch < WCOLS / 8; ++ch) {
+          uint4 w;
+          w.x = pd[4 * ch + 0]; w.y = pd[4 * ch + 1]; w.z = pd[4 * ch + 2]; w.w = pd[4 * ch + 3];
+          *reinterpret_cast<uint4*>(ds_tile + sw128_offset((uint32_t)r, (uint32_t)(part * WCOLS * 2 + ch * 16))) = w;
+        }
+        fence_async_smem();
+        // all 64 S^T columns of these rows must have been read (by every warpgroup) before the packed values
+        // overwrite them
+        asm volatile("bar.sync 2, %0;" ::"n"(NSOFT) : "memory");
+        tmem_st_n<WCOLS / 2>(tST(s) + lane_off + part * (WCOLS / 2), pp);
+        tmem_st_n<WCOLS / 2>(tST(s) + 32 + lane_off + part * (WCOLS / 2), pd);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(&pds_full[s]);
+      if (it + 1 < n_it) store_rows(it + 1, nv0, nv1);
+    }
+    if (n_it > 0) {
+      mbar_wait(acc_done, 0, ctx, 0x360);
+      tc_fence_after();
+    }
+    {
+      constexpr int PER = NWG / 2;
+      constexpr int OC = D / PER;
+      const int which = part / PER, sub = part % PER;
+      bf16* base = which == 0 ? p.dv : p.dk;
+      const uint32_t tacc = which == 0 ? tDV : tDK;
+      bf16* orow = base + (((size_t)b * p.Tk + k0 + r) * p.Hkv + hkv) * D + sub * OC;
+#pragma unroll
+      for (int ch = 0; ch < OC / 32; ++ch) {
+        uint32_t o[32];
+        if (n_it > 0) {
+          tmem_ld_x32(tacc + lane_off + sub * OC + ch * 32, o);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = 0u;
+        }
+        if (key_ok) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint4 w;
+            w.x = pack_bf16x2(__uint_as_float(o[8 * i + 0]), __uint_as_float(o[8 * i + 1]));
+            w.y = pack_bf16x2(__uint_as_float(o[8 * i + 2]), __uint_as_float(o[8 * i + 3]));
+            w.z = pack_bf16x2(__uint_as_float(o[8 * i + 4]), __uint_as_float(o[8 * i + 5]));
+            w.w = pack_bf16x2(__uint_as_float(o[8 * i + 6]), __uint_as_float(o[8 * i + 7]));
+            reinterpret_cast<uint4*>(orow + ch * 32)[i] = w;
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// dq (bf16) = dq_acc (fp32); n elements, n % 8 == 0
+__global__ void dq_convert_kernel(const float* __restrict__ acc, bf16* __restrict__ dq, long long n8) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n8) return;
+  const float4 a = reinterpret_cast<const float4*>(acc)[2 * i];
+  const float4 c = reinterpret_cast<const float4*>(acc)[2 * i + 1];
+  uint4 w;
+  w.x = pack_bf16x2(a.x, a.y); w.y = pack_bf16x2(a.z, a.w);
+  w.z = pack_bf16x2(c.x, c.y); w.w = pack_bf16x2(c.z, c.w);
+  reinterpret_cast<uint4*>(dq)[i] = w;
+}
+
 static int make_map_bthd(CUtensorMap* m, const void* base, int B, int T, int H, int D, long long sb,
                          long long st, long long sh, int box_rows) {
   uint64_t dims[4] = {(uint64_t)D, (uint64_t)H, (uint64_t)T, (uint64_t)B};
@@ -800,6 +1227,33 @@ static int launch_all(const void* q, const void* k, const void* v, const void* d
   return HMF_OK;
 }
 
+
+static int launch_fused(const void* q, const void* k, const void* v, const void* d_o, const Params& p,
+                        const long long* qs, const long long* ks, const long long* vs, float* dq_acc,
+                        cudaStream_t st) {
+  constexpr int D = 128;
+  CUtensorMap tmQ, tmDO, tmK, tmV;
+  int rc;
+  const long long os[3] = {(long long)p.Tq * p.Hq * D, (long long)p.Hq * D, D};
+  if ((rc = make_map_bthd(&tmQ, q, p.B, p.Tq, p.Hq, D, qs[0], qs[1], qs[2], QN)) != HMF_OK) return rc;
+  if ((rc = make_map_bthd(&tmDO, d_o, p.B, p.Tq, p.Hq, D, os[0], os[1], os[2], QN)) != HMF_OK) return rc;
+  if ((rc = make_map_bthd(&tmK, k, p.B, p.Tk, p.Hkv, D, ks[0], ks[1], ks[2], KM)) != HMF_OK) return rc;
+  if ((rc = make_map_bthd(&tmV, v, p.B, p.Tk, p.Hkv, D, vs[0], vs[1], vs[2], KM)) != HMF_OK) return rc;
+  auto kern = attn_bwd_fused_kernel<D>;
+  static bool configured = false;
+  if (!configured) {
+    HMF_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemFused<D>::TOTAL));
+    configured = true;
+  }
+  dim3 grid((p.Tk + KM - 1) / KM, p.Hkv, p.B);
+  kern<<<grid, FTHR, SmemFused<D>::TOTAL, st>>>(tmQ, tmDO, tmK, tmV, p, dq_acc);
+  HMF_CHECK_CUDA(cudaGetLastError());
+  const long long n8 = (long long)p.B * p.Tq * p.Hq * D / 8;
+  dq_convert_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, st>>>(dq_acc, p.dq, n8);
+  HMF_CHECK_CUDA(cudaGetLastError());
+  return HMF_OK;
+}
+
 }  // namespace attn_bwd
 }  // namespace hmf
 
@@ -838,4 +1292,39 @@ HMF_API int hmf_attention_bwd(const void* q, const void* k, const void* v, const
   const long long qs[3] = {q_sb, q_st, q_sh}, ks[3] = {k_sb, k_st, k_sh}, vs[3] = {v_sb, v_st, v_sh};
   if (D == 64) return launch_all<64>(q, k, v, d_o, p, qs, ks, vs, stream);
   return launch_all<128>(q, k, v, d_o, p, qs, ks, vs, stream);
+}
+
+// Single-kernel variant for D = 128 (five GEMMs per tile pair; dQ is summed with fp32 reductions in global memory, so
+// the order of that sum, and with it the last bits of dq, may differ from run to run).  Same arguments as
+// hmf_attention_bwd plus dq_acc: fp32 scratch [B,Tq,Hq,D] that must be ZERO on entry (it holds dq in fp32 on return).
+HMF_API int hmf_attention_bwd_fused(const void* q, const void* k, const void* v, const void* o, const void* d_o,
+                                    const float* lse, const float* dlse, float* delta, float* dq_acc, void* dq,
+                                    void* dk, void* dv, const int* q_pos, int B, int Tq, int Tk, int Hq, int Hkv,
+                                    int D, long long q_sb, long long q_st, long long q_sh, long long k_sb,
+                                    long long k_st, long long k_sh, long long v_sb, long long v_st, long long v_sh,
+                                    int lo, int hi, int q_off, float scale, cudaStream_t stream) {
+  using namespace hmf;
+  using namespace hmf::attn_bwd;
+  HMF_REQUIRE(q && k && v && o && d_o && lse && delta && dq_acc && dq && dk && dv, "attention_bwd_fused: null tensor");
+  HMF_REQUIRE(D == 128, "attention_bwd_fused: head dim %d unsupported (128)", D);
+  HMF_REQUIRE(Hkv > 0 && Hq % Hkv == 0, "attention_bwd_fused: Hq=%d not a multiple of Hkv=%d", Hq, Hkv);
+  HMF_REQUIRE(lo >= 0 && hi > lo, "attention_bwd_fused: bad window lo=%d hi=%d", lo, hi);
+  {
+    const long long rows = (long long)B * Tq * Hq;
+    const int rpw = 32 / (D / 8);
+    const long long warps = (rows + rpw - 1) / rpw;
+    const long long blocks = (warps + 7) / 8;
+    delta_kernel<<<(unsigned)blocks, 256, 0, stream>>>((const bf16*)o, (const bf16*)d_o, dlse, delta, B, Tq, Hq, D);
+    HMF_CHECK_CUDA(cudaGetLastError());
+  }
+  Params p;
+  p.lse = lse; p.delta = delta; p.q_pos = q_pos;
+  p.dq = (bf16*)dq; p.dk = (bf16*)dk; p.dv = (bf16*)dv;
+  p.B = B; p.Tq = Tq; p.Tk = Tk; p.Hq = Hq; p.Hkv = Hkv;
+  p.lo = lo; p.hi = hi; p.q_off = q_off;
+  p.scale = scale;
+  p.scale_log2 = scale * kLog2e;
+  p.status = status_ptr();
+  const long long qs[3] = {q_sb, q_st, q_sh}, ks[3] = {k_sb, k_st, k_sh}, vs[3] = {v_sb, v_st, v_sh};
+  return launch_fused(q, k, v, d_o, p, qs, ks, vs, dq_acc, stream);
 }

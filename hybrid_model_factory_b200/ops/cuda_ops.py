@@ -8,6 +8,7 @@ training and serving paths are bf16).
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional, Tuple
 
 import torch
@@ -472,8 +473,18 @@ def attention_fwd_raw(q: Tensor, k: Tensor, v: Tensor, scale: float, lo: int, hi
     return o, lse
 
 
-def attention_bwd_raw(q, k, v, o, do, lse, scale, lo, hi, q_off, q_pos=None, dlse=None):
-    """Launches delta + dQ + dK/dV kernels; returns ``(dq, dk, dv)`` (bf16, contiguous)."""
+def deterministic_attention_backward() -> bool:
+    """True when the attention backward must sum dQ in a fixed order (``torch.use_deterministic_algorithms`` or
+    ``HMF_ATTN_BWD_DETERMINISTIC=1``): the two-kernel path, 7 GEMMs per tile pair, no atomics."""
+    return os.environ.get("HMF_ATTN_BWD_DETERMINISTIC", "0") == "1" or torch.are_deterministic_algorithms_enabled()
+
+
+def attention_bwd_raw(q, k, v, o, do, lse, scale, lo, hi, q_off, q_pos=None, dlse=None, deterministic=None):
+    """Gradients of ``attention_fwd_raw``; returns ``(dq, dk, dv)`` (bf16, contiguous).
+
+    Head dimension 128 runs the single fused kernel (S and dP computed once per tile pair, dQ summed into an fp32
+    buffer with global reductions, then converted); head dimension 64, or ``deterministic``, runs the dQ and dK/dV
+    kernels separately."""
     B, Tq, Hq, D = q.shape
     Tk, Hkv = k.shape[1], k.shape[2]
     q = q if _tma_ok(q) else q.contiguous()
@@ -488,6 +499,18 @@ def attention_bwd_raw(q, k, v, o, do, lse, scale, lo, hi, q_off, q_pos=None, dls
         q_pos = q_pos.to(torch.int32).contiguous()
     if dlse is not None:
         dlse = dlse.float().contiguous()
+    if deterministic is None:
+        deterministic = deterministic_attention_backward()
+    if D == 128 and not deterministic:
+        dq_acc = torch.zeros(B, Tq, Hq, D, device=q.device, dtype=torch.float32)
+        _lib.check(_K().hmf_attention_bwd_fused(
+            _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(o), _lib.ptr(do), _lib.ptr(lse), _lib.ptr(dlse),
+            _lib.ptr(delta), _lib.ptr(dq_acc), _lib.ptr(dq), _lib.ptr(dk), _lib.ptr(dv), _lib.ptr(q_pos),
+            c_int(B), c_int(Tq), c_int(Tk), c_int(Hq), c_int(Hkv), c_int(D),
+            *_bthd_strides(q), *_bthd_strides(k), *_bthd_strides(v), c_int(lo), c_int(hi),
+            c_int(q_off), c_float(scale), _st(q)), "attention_bwd_fused")
+        _lib.add_launches(2)
+        return dq, dk, dv
     _lib.check(_K().hmf_attention_bwd(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(o), _lib.ptr(do), _lib.ptr(lse),
                                       _lib.ptr(dlse), _lib.ptr(delta), _lib.ptr(dq), _lib.ptr(dk), _lib.ptr(dv), _lib.ptr(q_pos),
                                       c_int(B), c_int(Tq), c_int(Tk), c_int(Hq), c_int(Hkv), c_int(D),

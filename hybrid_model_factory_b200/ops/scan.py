@@ -28,6 +28,8 @@ from typing import Callable, List, Optional, Sequence, Tuple
 import torch
 import torch.distributed as dist
 
+from ..utils.profiling import phase
+
 Tensor = torch.Tensor
 State = Optional[Tuple[Tensor, ...]]
 
@@ -243,6 +245,16 @@ def _parallel_backward(ctx, core, sp, saved_all, d_a, d_b, d_state):
 class _SSMScan(torch.autograd.Function):
     @staticmethod
     def forward(ctx, core: ScanCore, sp, n_inputs: int, want_state: bool, *tensors):
+        with phase("ssm_scan_fwd"):
+            return _SSMScan._forward(ctx, core, sp, n_inputs, want_state, *tensors)
+
+    @staticmethod
+    def backward(ctx, d_out, *d_state):
+        with phase("ssm_scan_bwd"):
+            return _SSMScan._backward(ctx, d_out, *d_state)
+
+    @staticmethod
+    def _forward(ctx, core: ScanCore, sp, n_inputs: int, want_state: bool, *tensors):
         inputs = list(tensors[:n_inputs])
         state0 = tensors[n_inputs:]
         state0 = tuple(state0) if len(state0) else None
@@ -293,7 +305,7 @@ class _SSMScan(torch.autograd.Function):
         return (out, *[s if s is not None else out.new_zeros(()) for s in sT_b])
 
     @staticmethod
-    def backward(ctx, d_out, *d_state):
+    def _backward(ctx, d_out, *d_state):
         core, sp = ctx.core, ctx.sp
         d_state = tuple(d_state) if len(d_state) else None
         if d_state is not None and all(ds is None for ds in d_state):

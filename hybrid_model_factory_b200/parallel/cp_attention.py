@@ -19,6 +19,7 @@ import torch
 import torch.distributed as dist
 
 from ..ops import functional as F_ops
+from ..utils.profiling import phase
 from .sp import SPContext, zigzag_merge, zigzag_split
 
 Tensor = torch.Tensor
@@ -26,17 +27,19 @@ Tensor = torch.Tensor
 
 def _all_gather_seq(x: Tensor, sp: SPContext) -> Tensor:
     """Gathers ``[B, L_local, ...]`` shards and returns the sequence in global order."""
-    shards = [torch.empty_like(x) for _ in range(sp.size)]
-    dist.all_gather(shards, x.contiguous(), group=sp.group)
-    return zigzag_merge(shards, dim=1)
+    with phase("kv_gather"):
+        shards = [torch.empty_like(x) for _ in range(sp.size)]
+        dist.all_gather(shards, x.contiguous(), group=sp.group)
+        return zigzag_merge(shards, dim=1)
 
 
 def _reduce_scatter_seq(x_full: Tensor, sp: SPContext) -> Tensor:
     """Sums full-sequence tensors over the group and returns this rank's zig-zag shard."""
     if x_full.is_cuda:
-        parts = [zigzag_split(x_full, r, sp.size, dim=1).contiguous() for r in range(sp.size)]
-        out = torch.empty_like(parts[0])
-        dist.reduce_scatter(out, parts, group=sp.group)
+        with phase("dkv_reduce_scatter"):
+            parts = [zigzag_split(x_full, r, sp.size, dim=1).contiguous() for r in range(sp.size)]
+            out = torch.empty_like(parts[0])
+            dist.reduce_scatter(out, parts, group=sp.group)
         return out
     buf = x_full.contiguous()
     dist.all_reduce(buf, group=sp.group)  # gloo has no reduce_scatter

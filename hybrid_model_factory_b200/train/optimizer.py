@@ -25,6 +25,7 @@ import torch
 import torch.distributed as dist
 
 from ..ops import _lib
+from ..utils.profiling import phase
 
 
 class FlatAdamW:
@@ -108,8 +109,9 @@ class FlatAdamW:
         self.step_count += 1
         if self.world > 1:
             gshard = torch.empty(self.shard, device=self.device, dtype=self.grad_dtype)
-            dist.reduce_scatter_tensor(gshard, self.flat_grad, group=self.group) if self.flat_grad.is_cuda else \
-                self._cpu_reduce_scatter(gshard)
+            with phase("zero_grad_reduce_scatter"):
+                dist.reduce_scatter_tensor(gshard, self.flat_grad, group=self.group) if self.flat_grad.is_cuda else \
+                    self._cpu_reduce_scatter(gshard)
         else:
             gshard = self.flat_grad
         pshard = self.flat_param[self._shard_slice]
@@ -143,7 +145,8 @@ class FlatAdamW:
                                   None if self.master is None else self.master[a:b])
         if self.world > 1:
             if self.flat_param.is_cuda:
-                dist.all_gather_into_tensor(self.flat_param, pshard.clone(), group=self.group)
+                with phase("zero_param_all_gather"):
+                    dist.all_gather_into_tensor(self.flat_param, pshard.clone(), group=self.group)
             else:
                 parts = [torch.empty_like(pshard) for _ in range(self.world)]
                 dist.all_gather(parts, pshard.clone(), group=self.group)

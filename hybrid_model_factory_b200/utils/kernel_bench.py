@@ -99,8 +99,11 @@ def bench_attention_bwd(args):
     q, k, v = _qkv(T, H, Hkv, D)
     o, lse = cuda_ops.attention_fwd_raw(q, k, v, D ** -0.5, 0, 2 ** 31 - 1, 0)
     do = torch.randn_like(o)
-    ms = time_fn(lambda: cuda_ops.attention_bwd_raw(q, k, v, o, do, lse, D ** -0.5, 0, 2 ** 31 - 1, 0), flush=False)
-    report(f"attention_bwd causal T={T} H={H}/{Hkv} D={D} (5-GEMM flop count)", ms, flops=10.0 * T * T * H * D / 2)
+    for det, name in ((False, "fused kernel"), (True, "dQ + dK/dV kernels")):
+        ms = time_fn(lambda: cuda_ops.attention_bwd_raw(q, k, v, o, do, lse, D ** -0.5, 0, 2 ** 31 - 1, 0,
+                                                        deterministic=det), flush=False)
+        report(f"attention_bwd {name} causal T={T} H={H}/{Hkv} D={D} (5-GEMM flop count)", ms,
+               flops=10.0 * T * T * H * D / 2)
 
 
 def _gdn_inputs(T, H):

@@ -5,6 +5,9 @@
   bounds a step).
 * ``nvtx_range``: context manager / decorator emitting an NVTX range (no-op on CPU) so kernels group by phase
   in a timeline tool.
+* ``PHASES`` / ``phase(name)``: one process-wide timer that the communication sites of the training step
+  (K/V gather, dK/dV reduce-scatter, gradient reduce-scatter, parameter all-gather, state-chain scans) record
+  into when a benchmark switches it on; disabled it costs one attribute test per site.
 * ``StepBreakdown``: wraps the modules of a model with forward timers to attribute step time to layer types.
 """
 from __future__ import annotations
@@ -62,6 +65,30 @@ class DeviceTimer:
     def reset(self) -> None:
         self._open.clear()
         self._pairs.clear()
+
+
+PHASES = DeviceTimer(enabled=False)
+
+
+def enable_phases(on: bool = True) -> None:
+    PHASES.enabled = bool(on) and torch.cuda.is_available()
+    PHASES.reset()
+
+
+@contextlib.contextmanager
+def phase(name: str):
+    """Times the enclosed stream work under ``name`` in ``PHASES`` (no-op unless ``enable_phases()`` ran)."""
+    if not PHASES.enabled:
+        yield
+        return
+    key = f"{name}#{len(PHASES._pairs[name])}"
+    PHASES.start(key)
+    try:
+        yield
+    finally:
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        PHASES._pairs[name].append((PHASES._open.pop(key), ev))
 
 
 @contextlib.contextmanager

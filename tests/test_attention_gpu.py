@@ -48,6 +48,27 @@ def test_attention_fwd_bwd(B, Tq, Tk, Hq, Hkv, D, window, hollow):
     assert _rel(vs.grad, vr.grad) < 3e-2, "dv"
 
 
+@pytest.mark.parametrize("Tq,Tk,window", [(2048, 2048, None), (700, 1500, 300), (333, 333, None)])
+def test_attention_bwd_fused_matches_two_kernel_path(Tq, Tk, window):
+    """D = 128: the single fused backward kernel (dQ by global fp32 reductions) against the dQ + dK/dV pair."""
+    from hybrid_model_factory_b200.ops import cuda_ops
+    B, Hq, Hkv, D = 2, 8, 2, 128
+    q = torch.randn(B, Tq, Hq, D, device=DEV).bfloat16()
+    k = torch.randn(B, Tk, Hkv, D, device=DEV).bfloat16()
+    v = torch.randn(B, Tk, Hkv, D, device=DEV).bfloat16()
+    hi = 2 ** 31 - 1 if window is None else window
+    q_off = Tk - Tq
+    o, lse = cuda_ops.attention_fwd_raw(q, k, v, D ** -0.5, 0, hi, q_off)
+    do = torch.randn_like(o)
+    a = cuda_ops.attention_bwd_raw(q, k, v, o, do, lse, D ** -0.5, 0, hi, q_off, deterministic=False)
+    b = cuda_ops.attention_bwd_raw(q, k, v, o, do, lse, D ** -0.5, 0, hi, q_off, deterministic=True)
+    torch.cuda.synchronize()
+    from hybrid_model_factory_b200.ops import _lib
+    _lib.assert_status_ok()
+    for x, y, name in zip(a, b, ("dq", "dk", "dv")):
+        assert _rel(x, y) < 1e-2, name
+
+
 def test_attention_strided_qkv_views():
     """q, k, v as column slices of one fused projection output (no copies before the kernel)."""
     B, T, Hq, Hkv, D = 1, 512, 8, 2, 128
