@@ -307,21 +307,44 @@ def collate(rows: Sequence[Dict[str, List[int]]], pad_id: int = 0, pin: bool = F
     return batch
 
 
+def steps_per_epoch(n_rows: int, batch_size: int, world: int = 1, sp_size: int = 1) -> int:
+    """Optimizer steps in one pass over the data: the same number on every rank (a tail that does not fill one batch
+    on every data-parallel replica is dropped)."""
+    dp = max(1, world // sp_size)
+    return (n_rows // sp_size) // (dp * batch_size)
+
+
 def batch_iterator(dataset, batch_size: int, rank: int = 0, world: int = 1, sp_size: int = 1, pad_id: int = 0,
-                   start_step: int = 0, pin: bool = True) -> Iterator[Dict[str, torch.Tensor]]:
-    """Sequential, deterministic batches.  With SP the dataset rows are already interleaved per rank:
-    data-parallel replica ``d`` and SP rank ``r`` read rows ``((step*dp + d)*B + j)*SP + r``; resuming is
-    skipping ``start_step`` batches."""
-    dp = world // sp_size
+                   start_step: int = 0, pin: bool = True, num_epochs: Optional[float] = None, shuffle: bool = False,
+                   seed: int = 0) -> Iterator[Dict[str, torch.Tensor]]:
+    """Deterministic batches, epoch after epoch.  With SP the dataset rows are already interleaved per rank:
+    in step ``s`` of an epoch data-parallel replica ``d`` and SP rank ``r`` read samples ``(s*dp + d)*B + j`` (row
+    ``sample*SP + r``).  Every rank sees the same number of steps per epoch, so no rank runs out of batches before
+    another (ranks that disagreed would issue mismatched collectives).  ``num_epochs`` ends the stream (``None``: it
+    wraps around for as long as the trainer asks, which stops at ``max_steps``); epochs after the first draw the
+    samples in a fresh order when ``shuffle`` is set (reference: the per-epoch sampler seed of its trainer), the first
+    keeps the dataset's own order.  Resuming is skipping ``start_step`` steps."""
+    dp = max(1, world // sp_size)
     d, r = rank // sp_size, rank % sp_size
     n_samples = len(dataset) // sp_size
-    step = start_step
-    while True:
-        first = (step * dp + d) * batch_size
-        if first + batch_size > n_samples:
-            return
-        rows = [dataset[(first + j) * sp_size + r] for j in range(batch_size)]
+    spe = steps_per_epoch(len(dataset), batch_size, world, sp_size)
+    if spe == 0:
+        return
+    total = None if num_epochs is None else int(round(num_epochs * spe))
+    labels_shifted = bool(getattr(dataset, "labels_shifted", False))
+    step, cur_epoch, order = start_step, -1, None
+    while total is None or step < total:
+        epoch, s = divmod(step, spe)
+        if epoch != cur_epoch:
+            cur_epoch = epoch
+            order = None
+            if shuffle and epoch > 0:
+                g = torch.Generator().manual_seed(seed + epoch)
+                order = torch.randperm(n_samples, generator=g).tolist()
+        first = (s * dp + d) * batch_size
+        ids = range(first, first + batch_size)
+        rows = [dataset[(order[i] if order is not None else i) * sp_size + r] for i in ids]
         batch = collate(rows, pad_id, pin)
-        batch["labels_shifted"] = bool(getattr(dataset, "labels_shifted", False))
+        batch["labels_shifted"] = labels_shifted
         yield batch
         step += 1

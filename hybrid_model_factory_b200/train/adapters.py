@@ -21,6 +21,7 @@ class LoRALinear(nn.Module):
         for p in self.base.parameters():
             p.requires_grad_(False)
         self.rank, self.scaling = rank, alpha / rank
+        self.enabled = True               # False: the base layer alone (reference policy of DPO / KTO)
         dev, dt = base.weight.device, base.weight.dtype
         self.lora_A = nn.Parameter(torch.empty(rank, base.in_features, device=dev, dtype=dt))
         self.lora_B = nn.Parameter(torch.zeros(base.out_features, rank, device=dev, dtype=dt))
@@ -35,6 +36,8 @@ class LoRALinear(nn.Module):
         return self.base.bias
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if not self.enabled:
+            return self.base(x)
         return self.base(x) + (x @ self.lora_A.t()) @ self.lora_B.t() * self.scaling
 
     def merged_weight(self) -> torch.Tensor:

@@ -186,12 +186,15 @@ class PPOTrainer:
 
 def reward_model_fn(reward_model, score_row: int = 0) -> Callable:
     """Reward function backed by a model trained by the ``rm`` stage (``train/preference.py``): the score is the
-    projection of the hidden state of the last real token on one row of the output head."""
+    value head applied to the hidden state of the last real token (a model without a value head is scored by one
+    row of its output head)."""
     @torch.no_grad()
     def fn(ids: torch.Tensor, resp_mask: torch.Tensor) -> torch.Tensor:
         h = reward_model.model(ids)[0].float()
         P = ids.shape[1] - resp_mask.shape[1]
         last = P + resp_mask.sum(-1).long().clamp(min=1) - 1
         h_last = h[torch.arange(ids.shape[0], device=ids.device), last]
+        if hasattr(reward_model, "v_head"):
+            return reward_model.v_head(h_last.to(reward_model.v_head.weight.dtype)).squeeze(-1).float()
         return h_last @ reward_model.lm_head.weight[score_row].float()
     return fn

@@ -127,6 +127,7 @@ class Trainer:
                                        max_grad_norm=args.max_grad_norm, group=None, dp_size=self.dp_size,
                                        state_dtype=sdt, master_weights=args.master_weights)
         self.global_step = 0
+        self.status_check_steps = 50
         self.tokens_seen = 0
         self._t0 = time.time()
         self._log_file = None
@@ -173,6 +174,30 @@ class Trainer:
         self._last_lr = lr
         return total
 
+    # -- device-side wait status -----------------------------------------------------------------
+    def check_kernel_status(self, status_reader: Optional[Callable] = None) -> None:
+        """Raises ``KernelError`` on every rank when any rank's kernels recorded a wait that ran out (a late or
+        missing peer in the in-kernel state chain, an mbarrier that never completed).  Such a kernel returns and the
+        step goes on with stale data, so the record must be read: here at logging steps, before every checkpoint
+        and every ``status_check_steps`` steps (one small device-to-host read and, with several ranks, one
+        all-reduce)."""
+        from ..ops import _lib
+        if status_reader is None:
+            if not (torch.cuda.is_available() and self.device.type == "cuda" and _lib.kernels_available()):
+                return
+            status_reader = _lib.read_status
+        code, block, detail, count = status_reader()
+        worst = int(code)
+        if dist.is_initialized() and self.world > 1:
+            t = torch.tensor([worst], device=self.device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            worst = int(t)
+        if worst != 0:
+            raise _lib.KernelError(
+                f"step {self.global_step}: a device-side wait ran out on at least one rank (this rank: code={code} "
+                f"block={block} detail={detail:#x} count={count}); the results of the steps since the last check are "
+                f"not valid.  With sequence parallelism, HMF_SP_PEER=0 selects the NCCL state transport.")
+
     # -- evaluation -----------------------------------------------------------------------------
     @torch.no_grad()
     def evaluate(self, batches: Iterable[Dict[str, torch.Tensor]]) -> float:
@@ -204,7 +229,10 @@ class Trainer:
             if self.global_step >= self.args.max_steps:
                 break
             loss = self.train_step(batch)
-            if self.args.logging_steps and self.global_step % self.args.logging_steps == 0:
+            logging_now = bool(self.args.logging_steps and self.global_step % self.args.logging_steps == 0)
+            if logging_now or self.global_step % self.status_check_steps == 0:
+                self.check_kernel_status()
+            if logging_now:
                 self._last_loss = float(loss.item())
                 self.log({"loss": self._last_loss, "lr": self._last_lr})
             for cb in self.callbacks:
@@ -228,6 +256,7 @@ class Trainer:
     # -- checkpoints --------------------------------------------------------------------------
     def save_checkpoint(self, path: str) -> None:
         from ..utils.checkpoint_io import save_pretrained
+        self.check_kernel_status()          # never write weights that a timed-out wait may have corrupted
         zero3 = hasattr(self.optimizer, "gather_full_state")
         if zero3:                       # every rank takes part in the all-gathers
             self.optimizer.gather_full_state()
@@ -245,15 +274,36 @@ class Trainer:
             dist.barrier()
 
     def load_checkpoint(self, path: str) -> None:
+        """Restores weights, step counters and (when present) this rank's optimizer shard.
+
+        Under ZeRO-3 the parameters are released to empty placeholders: the per-rank optimizer file carries the
+        weight shards, and a model-only checkpoint is loaded into the gathered parameters and re-sliced.  A parameter
+        that the checkpoint does not hold is an error (a LoRA- or OFT-wrapped model resumed as a plain one, or the
+        reverse, would otherwise continue from random weights)."""
         from ..utils.checkpoint_io import load_state_dict_into
-        load_state_dict_into(self.model, path)
+        zero3 = hasattr(self.optimizer, "gather_full_state")
+        opt = os.path.join(path, f"optimizer_rank{self.rank:05d}.pt")
+        has_opt = os.path.exists(opt)
+        if not (zero3 and has_opt):
+            if zero3:
+                self.optimizer.gather_full_state()
+            missing, unexpected = load_state_dict_into(self.model, path)
+            if zero3:
+                self.optimizer.reshard_from_full()
+                self.optimizer.release_all()
+            if missing:
+                raise KeyError(f"{path}: {len(missing)} model parameters are not in the checkpoint "
+                               f"(first: {missing[:6]})")
+            if unexpected and self.rank == 0:
+                import warnings
+                warnings.warn(f"{path}: {len(unexpected)} checkpoint tensors match no model parameter "
+                              f"(first: {unexpected[:6]})")
         st = os.path.join(path, "trainer_state.json")
         if os.path.exists(st):
             with open(st) as f:
                 s = json.load(f)
             self.global_step, self.tokens_seen = int(s["global_step"]), int(s["tokens_seen"])
-        opt = os.path.join(path, f"optimizer_rank{self.rank:05d}.pt")
-        if os.path.exists(opt):
+        if has_opt:
             self.optimizer.load_state_dict(torch.load(opt, map_location=self.device))
 
 

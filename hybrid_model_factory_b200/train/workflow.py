@@ -143,6 +143,11 @@ def run_ppo(model, ft_args, run_args, dataset, tokenizer, device, bsz):
     if not getattr(ft_args, "reward_model", None):
         raise ValueError("`reward_model` is necessary for PPO training")
     rm = checkpoint_io.from_pretrained(ft_args.reward_model, device=device).eval()
+    vh = dict(checkpoint_io.load_state_dict(ft_args.reward_model)).get("v_head.weight")
+    if vh is not None:
+        from .preference import attach_value_head
+        with torch.no_grad():
+            attach_value_head(rm).weight.copy_(vh.to(rm.v_head.weight.dtype))
     ref = checkpoint_io.from_pretrained(ft_args.ref_model, device=device).eval() if getattr(ft_args, "ref_model", None) else None
     cfg = PPOConfig(learning_rate=run_args.learning_rate, ppo_epochs=ft_args.ppo_epochs,
                     ppo_buffer_size=ft_args.ppo_buffer_size, mini_batch_size=run_args.per_device_train_batch_size,
@@ -227,9 +232,19 @@ def run_exp(args: Optional[Any] = None) -> Trainer:
     dataset = get_dataset(data_args, tokenizer, stage=("pt" if stage in ("pt", "hkd") else stage if stage in ("rm", "dpo", "kto") else "sft"), sp_size=sp,
                           vocab_size=model.config.vocab_size, seed=run_args.seed)
     bsz = run_args.per_device_train_batch_size * run_args.gradient_accumulation_steps
+    held = None
+    if data_args.val_size and hasattr(dataset, "rows"):
+        # hold out the tail of the dataset (whole SP groups): `val_size` is a fraction below 1, a sample count above
+        from ..data.loader import ListDataset
+        groups = len(dataset) // sp
+        n_val = int(data_args.val_size * groups) if data_args.val_size < 1 else int(data_args.val_size)
+        n_val = max(1, min(n_val, groups - 1))
+        held = ListDataset(dataset.rows[(groups - n_val) * sp:groups * sp], dataset.labels_shifted)
+        dataset = ListDataset(dataset.rows[:(groups - n_val) * sp], dataset.labels_shifted)
     n_batches = None
     if hasattr(dataset, "__len__") and len(dataset) < (1 << 29):
-        n_batches = (len(dataset) // sp) // (bsz * max(1, world // sp))
+        from ..data.loader import steps_per_epoch
+        n_batches = steps_per_epoch(len(dataset), bsz, world, sp)      # counted after the hold-out split
     targs = to_trainer_args(model_args, data_args, run_args, n_batches)
     if ft_args.use_muon:
         targs.optimizer = "muon"
@@ -248,8 +263,13 @@ def run_exp(args: Optional[Any] = None) -> Trainer:
             loss_fn = lambda m, b: hkd_mse_loss(m, b, ft_args.hybrid_lw_distill_target,  # noqa: E731
                                                 ft_args.hybrid_distill_pre_lm_head)
     elif stage in ("dpo", "kto", "rm"):
-        from .preference import make_preference_loss
-        loss_fn = make_preference_loss(stage, ft_args)
+        from .preference import NEEDS_REFERENCE, ReferencePolicy, attach_value_head, make_preference_loss
+        reference = None
+        if stage == "kto" or (stage == "dpo" and ft_args.pref_loss in NEEDS_REFERENCE):
+            reference = ReferencePolicy.build(model, ft_args, device)     # before training touches the weights
+        if stage == "rm":
+            attach_value_head(model)                                      # before the optimizer collects parameters
+        loss_fn = make_preference_loss(stage, ft_args, reference, getattr(tokenizer, "pad_token_id", None) or 0)
     if stage == "ppo":
         return run_ppo(model, ft_args, run_args, dataset, tokenizer, device, bsz)
     trainer = Trainer(model, targs, device=device, loss_fn=loss_fn)
@@ -257,18 +277,15 @@ def run_exp(args: Optional[Any] = None) -> Trainer:
         from ..parallel.sp import set_sequence_parallel_group_recursive
         set_sequence_parallel_group_recursive(teacher, trainer.sp)
     pad_id = getattr(tokenizer, "pad_token_id", None) or 0
-    if data_args.val_size and hasattr(dataset, "rows"):
-        # hold out the tail of the dataset (whole SP groups): `val_size` is a fraction below 1, a sample count above
-        from ..data.loader import ListDataset
-        groups = len(dataset) // sp
-        n_val = int(data_args.val_size * groups) if data_args.val_size < 1 else int(data_args.val_size)
-        n_val = max(1, min(n_val, groups - 1))
-        held = ListDataset(dataset.rows[(groups - n_val) * sp:groups * sp], dataset.labels_shifted)
-        dataset = ListDataset(dataset.rows[:(groups - n_val) * sp], dataset.labels_shifted)
+    if held is not None:
         ebs = run_args.per_device_eval_batch_size
-        trainer.eval_batches_fn = lambda: batch_iterator(held, ebs, rank, world, sp, pad_id, pin=device.type == "cuda")
+        trainer.eval_batches_fn = lambda: batch_iterator(held, ebs, rank, world, sp, pad_id, pin=device.type == "cuda",
+                                                         num_epochs=1)
+    # the stream wraps around epoch by epoch (fresh order per epoch unless disable_shuffling); the trainer stops at
+    # max_steps, which to_trainer_args derived from num_train_epochs when it was not given
     batches = batch_iterator(dataset, bsz, rank, world, sp, pad_id, start_step=trainer.global_step,
-                             pin=device.type == "cuda")
+                             pin=device.type == "cuda", shuffle=not getattr(data_args, "disable_shuffling", False),
+                             seed=run_args.seed)
     if run_args.do_train:
         trainer.train(batches)
         final = os.path.join(run_args.output_dir, "final")

@@ -291,6 +291,17 @@ class Zero3Engine:
         for u in self.units:
             u.release()
 
+    def reshard_from_full(self) -> None:
+        """After weights were copied into the materialised parameters (``gather_full_state`` + a checkpoint load):
+        re-slices every unit's shard and fp32 master copy from them."""
+        for u in self.units:
+            assert u.full is not None, "reshard_from_full needs gather_full_state() first"
+            lo = u.rank * u.shard_len if u.world > 1 else 0
+            u.shard.copy_(u.full[lo:lo + u.shard_len])
+            st = self.state.get(u.name)
+            if st is not None and st.get("master") is not None:
+                st["master"].copy_(u.shard.detach().float())
+
     def state_dict(self) -> dict:
         return {"step": self.step_count, "rank": self.rank, "world": self.world,
                 "shards": {u.name: u.shard.detach().cpu() for u in self.units},

@@ -168,8 +168,14 @@ def load_state_dict_into(model: torch.nn.Module, path: str, strict: bool = False
     return missing, unexpected
 
 
-def from_pretrained(path: str, dtype: Optional[torch.dtype] = None, device=None, **config_overrides):
-    """Builds the model named by ``config.json`` and loads its weights."""
+def from_pretrained(path: str, dtype: Optional[torch.dtype] = None, device=None, allow_missing: bool = False,
+                    **config_overrides):
+    """Builds the model named by ``config.json`` and loads its weights.
+
+    A parameter of the model that the checkpoint does not hold raises ``KeyError`` unless ``allow_missing`` is set
+    (a converted or adapter-wrapped checkpoint whose names do not match would otherwise leave random weights in
+    place without a sound); checkpoint tensors that the model does not own are reported with a warning.  Both lists
+    are kept in ``model._load_report``."""
     from ..models.configuration import HybridConfig
     from ..models.modeling_hybrid import build_model
     cfg = HybridConfig.from_pretrained(path, **config_overrides)
@@ -179,4 +185,11 @@ def from_pretrained(path: str, dtype: Optional[torch.dtype] = None, device=None,
         model = model.to(device)
     missing, unexpected = load_state_dict_into(model, path)
     model._load_report = {"missing": missing, "unexpected": unexpected}
+    if missing and not allow_missing:
+        raise KeyError(f"{path}: {len(missing)} model parameters are not in the checkpoint (first: {missing[:6]}); "
+                       f"pass allow_missing=True to keep their initial values")
+    if unexpected:
+        import warnings
+        warnings.warn(f"{path}: {len(unexpected)} checkpoint tensors match no model parameter "
+                      f"(first: {unexpected[:6]})", stacklevel=2)
     return model

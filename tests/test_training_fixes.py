@@ -1,0 +1,173 @@
+"""Regression tests of the training stack: reference policy of DPO / KTO, reward scoring at the last real token,
+ZeRO-3 save + resume, epoch wrap-around of the batch stream, loud failure after a recorded device-side timeout."""
+import json
+import math
+import os
+import types
+
+import pytest
+import torch
+
+from hybrid_model_factory_b200.data import loader as L
+from hybrid_model_factory_b200.models.configuration import HybridConfig
+from hybrid_model_factory_b200.models.modeling_hybrid import build_model
+from hybrid_model_factory_b200.train import preference as P
+from hybrid_model_factory_b200.train.trainer import Trainer, TrainingArguments
+from hybrid_model_factory_b200.train.workflow import run_exp
+
+TINY = {"model_type": "hybrid_qwen3", "vocab_size": 259, "hidden_size": 32, "intermediate_size": 64,
+        "num_hidden_layers": 2, "num_attention_heads": 2, "num_key_value_heads": 1, "head_dim": 16,
+        "hybrid_override_pattern": "*-GDN", "torch_dtype": "float32"}
+
+
+def _tiny(seed=0):
+    torch.manual_seed(seed)
+    return build_model(HybridConfig.from_dict(dict(TINY)))
+
+
+def _pref_batch():
+    g = torch.Generator().manual_seed(3)
+    c = torch.randint(5, 250, (2, 12), generator=g)
+    r = torch.randint(5, 250, (2, 12), generator=g)
+    lab = lambda t: torch.cat([torch.full((2, 4), -100), t[:, 4:]], 1)
+    return {"chosen_input_ids": c, "chosen_labels": lab(c), "rejected_input_ids": r, "rejected_labels": lab(r)}
+
+
+def test_dpo_needs_and_uses_a_reference_policy():
+    ft = types.SimpleNamespace(pref_beta=0.5, pref_loss="sigmoid", ref_model=None)
+    model, batch = _tiny(0), _pref_batch()
+    with pytest.raises(ValueError):                       # no reference anywhere: refuse, do not train unanchored
+        P.make_preference_loss("dpo", ft)(model, batch)
+    # reference = frozen copy of the starting policy: first loss is ln 2, and it moves once the policy does
+    ref = P.ReferencePolicy.build(model, ft)
+    loss_fn = P.make_preference_loss("dpo", ft, ref)
+    l0 = loss_fn(model, batch)
+    assert abs(l0.item() - math.log(2)) < 1e-5
+    opt = torch.optim.SGD(model.parameters(), lr=0.5)
+    for _ in range(3):
+        opt.zero_grad()
+        loss_fn(model, batch).backward()
+        opt.step()
+    l1 = loss_fn(model, batch).item()
+    assert l1 < math.log(2) - 1e-3, l1                    # the KL-anchored margin really grows
+    # another reference gives another loss for the same policy
+    other = P.ReferencePolicy(_tiny(7))
+    l2 = P.make_preference_loss("dpo", ft, other)(model, batch).item()
+    assert abs(l2 - l1) > 1e-4
+    # precomputed reference log-probabilities in the batch take precedence
+    b2 = dict(batch, ref_chosen_logps=torch.zeros(2), ref_rejected_logps=torch.zeros(2))
+    assert abs(P.make_preference_loss("dpo", ft)(model, b2).item() - l1) > 1e-6
+
+
+def test_lora_policy_uses_its_base_weights_as_reference():
+    from hybrid_model_factory_b200.train.adapters import LoRALinear, apply_lora
+    ft = types.SimpleNamespace(pref_beta=0.5, pref_loss="sigmoid", ref_model=None)
+    model, batch = _tiny(0), _pref_batch()
+    apply_lora(model, rank=2)
+    ref = P.ReferencePolicy.build(model, ft)
+    assert ref.use_adapter_base and ref.model is None
+    with torch.no_grad():
+        for m in model.modules():
+            if isinstance(m, LoRALinear):
+                m.lora_B.normal_(std=0.2)
+    loss = P.make_preference_loss("dpo", ft, ref)(model, batch).item()
+    assert abs(loss - math.log(2)) > 1e-4                 # adapters moved the policy away from its own base
+    assert all(m.enabled for m in model.modules() if isinstance(m, LoRALinear))
+
+
+def test_kto_and_reward_scoring():
+    ft = types.SimpleNamespace(pref_beta=0.1, pref_loss="sigmoid", ref_model=None)
+    model = _tiny(0)
+    ids = torch.randint(5, 250, (2, 10))
+    batch = {"input_ids": ids, "labels": ids.clone(), "kto_tags": torch.tensor([1, 0])}
+    with pytest.raises(ValueError):
+        P.make_preference_loss("kto", ft)(model, batch)
+    l = P.make_preference_loss("kto", ft, P.ReferencePolicy.build(model, ft))(model, batch)
+    assert abs(l.item() - 0.5) < 1e-5                     # r = 0 against its own copy: sigmoid(0)
+    # the reward is read at the last real token, not at the padded end of the row
+    P.attach_value_head(model)
+    pad = 0
+    a = torch.tensor([[7, 8, 9, 10, 11, pad, pad, pad]])
+    b = torch.tensor([[7, 8, 9, 10, 11, 55, 66, 77]])
+    assert P.last_token_index(a, None, pad).tolist() == [4]
+    sa = P.reward_scores(model, a, None, pad)
+    sb = P.reward_scores(model, b[:, :5], None, pad)
+    assert torch.allclose(sa, sb, atol=1e-5)              # causal model: same prefix, same score
+
+
+def test_zero3_checkpoint_resume(tmp_path):
+    out = str(tmp_path / "z3")
+    (tmp_path / "ds.json").write_text(json.dumps({"zero_optimization": {"stage": 3}}))
+    cfg = {"model_name_or_path": json.dumps(TINY), "stage": "pt", "synthetic": True, "cutoff_len": 32, "max_steps": 2,
+           "save_steps": 2, "output_dir": out, "bf16": False, "pure_bf16": False, "learning_rate": 1e-3,
+           "lr_scheduler_type": "constant", "per_device_train_batch_size": 2, "deepspeed": str(tmp_path / "ds.json")}
+    tr = run_exp(cfg)
+    assert tr.global_step == 2
+    ck = os.path.join(out, "checkpoint-2")
+    tr.optimizer.gather_full_state()
+    want = {k: v.clone() for k, v in tr.model.state_dict().items()}
+    tr.optimizer.release_all()
+    # full resume (optimizer shards present) and model-only resume both restore the weights under ZeRO-3
+    for model_only in (False, True):
+        if model_only:
+            os.remove(os.path.join(ck, "optimizer_rank00000.pt"))
+        tr2 = run_exp(dict(cfg, max_steps=3, resume_from_checkpoint=ck, output_dir=str(tmp_path / f"r{int(model_only)}")))
+        assert tr2.global_step == 3
+    model = _tiny(1)
+    targs = TrainingArguments(output_dir="", zero_stage=3, max_steps=1, logging_steps=0, bf16=False, pure_bf16=False,
+                              resume_from_checkpoint=ck)
+    tr3 = Trainer(model, targs, device=torch.device("cpu"))
+    tr3.optimizer.gather_full_state()
+    for k, v in tr3.model.state_dict().items():
+        assert torch.allclose(v, want[k]), k
+    tr3.optimizer.release_all()
+
+
+def test_resume_refuses_a_checkpoint_that_lacks_model_parameters(tmp_path):
+    from hybrid_model_factory_b200.utils import checkpoint_io
+    model = _tiny(0)
+    sd = {k: v for k, v in model.state_dict().items() if "q_proj" not in k}
+    checkpoint_io.save_state_dict(checkpoint_io.to_hf_names(sd), str(tmp_path))
+    model.config.save_pretrained(str(tmp_path))
+    with pytest.raises(KeyError):
+        checkpoint_io.from_pretrained(str(tmp_path))
+    assert checkpoint_io.from_pretrained(str(tmp_path), allow_missing=True)._load_report["missing"]
+    with pytest.raises(KeyError):
+        Trainer(_tiny(0), TrainingArguments(output_dir="", max_steps=1, logging_steps=0, bf16=False, pure_bf16=False,
+                                            resume_from_checkpoint=str(tmp_path)), device=torch.device("cpu"))
+
+
+def test_batch_stream_wraps_epochs_and_is_rank_uniform():
+    rows = [{"input_ids": [i] * 4, "labels": [i] * 4} for i in range(11)]      # 11 samples: not divisible by dp*B = 4
+    ds = L.ListDataset(rows, False)
+    assert L.steps_per_epoch(len(ds), 2, world=2, sp_size=1) == 2
+    streams = []
+    for rank in range(2):
+        it = L.batch_iterator(ds, 2, rank, 2, 1, pin=False, num_epochs=2, shuffle=True, seed=5)
+        streams.append([b["input_ids"][:, 0].tolist() for b in it])
+    assert len(streams[0]) == len(streams[1]) == 4         # two epochs of two steps on every rank
+    assert streams[0][:2] == [[0, 1], [4, 5]] and streams[1][:2] == [[2, 3], [6, 7]]
+    second = sum(streams[0][2:] + streams[1][2:], [])
+    assert len(set(second)) == 8 and second != [0, 1, 4, 5, 2, 3, 6, 7]          # reshuffled, no repeats
+    # without an epoch limit the stream keeps going (the trainer stops at max_steps); resuming skips steps
+    it = L.batch_iterator(ds, 2, 0, 2, 1, pin=False, start_step=3)
+    assert next(it)["input_ids"][:, 0].tolist() == [4, 5]
+
+
+def test_two_epochs_run_to_the_end_of_the_schedule(tmp_path):
+    (tmp_path / "dataset_info.json").write_text(json.dumps({"d": {"file_name": "d.json", "columns": {"prompt": "text"}}}))
+    (tmp_path / "d.json").write_text(json.dumps([{"text": "lorem ipsum dolor sit amet " * 6} for _ in range(6)]))
+    cfg = {"model_name_or_path": json.dumps(TINY), "stage": "pt", "dataset": "d", "dataset_dir": str(tmp_path),
+           "cutoff_len": 32, "num_train_epochs": 2, "output_dir": str(tmp_path / "run"), "bf16": False, "pure_bf16": False,
+           "learning_rate": 1e-3, "per_device_train_batch_size": 2}
+    tr = run_exp(cfg)
+    assert tr.global_step == tr.args.max_steps and tr.args.max_steps >= 2 and tr.args.max_steps % 2 == 0
+
+
+def test_recorded_timeout_makes_the_trainer_fail_loudly():
+    from hybrid_model_factory_b200.ops._lib import KernelError
+    tr = Trainer(_tiny(0), TrainingArguments(output_dir="", max_steps=1, logging_steps=0, bf16=False, pure_bf16=False),
+                 device=torch.device("cpu"))
+    tr.check_kernel_status(lambda: (0, 0, 0, 0))
+    with pytest.raises(KernelError):
+        tr.check_kernel_status(lambda: (2, 17, 0x350, 1))
