@@ -13,6 +13,7 @@
 // the query-tile CTA and dK/dV by the key-tile CTA (the GQA group sum happens in the accumulator).
 // Masks follow the forward kernel: key visible <=> lo <= q_pos - k_pos < hi.
 #include <math.h>
+#include <stdlib.h>
 
 #include "../common/host.h"
 #include "../common/sm100.cuh"
@@ -34,6 +35,7 @@ struct Params {
   int lo, hi, q_off;
   float scale, scale_log2;
   unsigned int* status;
+  int dq_mode;         // experiment switch of the fused kernel: 0 = reduce, 1 = no dQ output, 2 = plain stores
 };
 
 // ------------------------------------------------------------------------------------
@@ -982,23 +984,34 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       float* base = dq_acc + (((size_t)b * p.Tq + q0) * p.Hq + h) * D + d;
       const size_t rstride = (size_t)p.Hq * D;
       const int nq = min(QN, p.Tq - q0);
+      uint32_t v0[32], v1[32];
+      tmem_ld_x32(tDPT(s) + lane_off, v0);
+      tmem_ld_x32(tDPT(s) + lane_off + 32, v1);
+      tmem_ld_wait();
+      tc_fence_before();
+      // registers hold the tile, the buffers may be overwritten.  Relaxed: a releasing arrive would wait for the
+      // previous tile's 64 global reductions of this thread to be acknowledged by L2 (measured: 2x the kernel time).
+      mbar_arrive_relaxed(&t_free[s]);
+      if (ok && p.dq_mode != 1) {
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        uint32_t v[32];
-        tmem_ld_x32(tDPT(s) + lane_off + half * 32, v);
-        tmem_ld_wait();
-        if (half == 1) {
-          tc_fence_before();
-          mbar_arrive(&t_free[s]);                    // registers hold the tile: the buffers may be overwritten
-        }
-        if (ok) {
-#pragma unroll
-          for (int c = 0; c < 32; ++c) {
-            const int qi = half * 32 + c;
-            if (qi < nq)
-              asm volatile("red.global.add.f32 [%0], %1;" ::"l"(base + (size_t)qi * rstride),
-                           "f"(__uint_as_float(v[c]))
+        for (int c = 0; c < 32; ++c) {
+          if (c < nq) {
+            if (p.dq_mode == 0)
+              asm volatile("red.global.add.f32 [%0], %1;" ::"l"(base + (size_t)c * rstride), "f"(__uint_as_float(v0[c]))
                            : "memory");
+            else
+              base[(size_t)c * rstride] = __uint_as_float(v0[c]);
+          }
+        }
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          if (32 + c < nq) {
+            if (p.dq_mode == 0)
+              asm volatile("red.global.add.f32 [%0], %1;" ::"l"(base + (size_t)(32 + c) * rstride),
+                           "f"(__uint_as_float(v1[c]))
+                           : "memory");
+            else
+              base[(size_t)(32 + c) * rstride] = __uint_as_float(v1[c]);
           }
         }
       }
@@ -1289,6 +1302,7 @@ HMF_API int hmf_attention_bwd(const void* q, const void* k, const void* v, const
   p.scale = scale;
   p.scale_log2 = scale * kLog2e;
   p.status = status_ptr();
+  p.dq_mode = 0;
   const long long qs[3] = {q_sb, q_st, q_sh}, ks[3] = {k_sb, k_st, k_sh}, vs[3] = {v_sb, v_st, v_sh};
   if (D == 64) return launch_all<64>(q, k, v, d_o, p, qs, ks, vs, stream);
   return launch_all<128>(q, k, v, d_o, p, qs, ks, vs, stream);
@@ -1325,6 +1339,10 @@ HMF_API int hmf_attention_bwd_fused(const void* q, const void* k, const void* v,
   p.scale = scale;
   p.scale_log2 = scale * kLog2e;
   p.status = status_ptr();
+  {
+    const char* m = getenv("HMF_ATTN_BWD_DQ_MODE");
+    p.dq_mode = m ? atoi(m) : 0;
+  }
   const long long qs[3] = {q_sb, q_st, q_sh}, ks[3] = {k_sb, k_st, k_sh}, vs[3] = {v_sb, v_st, v_sh};
   return launch_fused(q, k, v, d_o, p, qs, ks, vs, dq_acc, stream);
 }

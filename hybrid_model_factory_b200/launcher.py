@@ -19,6 +19,7 @@ USAGE = """usage: hmf <command> [args]
   prime-init CONFIG.yaml         stage 0: initialise a hybrid model from a Transformer checkpoint
   prime-unfuse CKPT [OUT]        convert a fused stage-1 checkpoint to the standard hybrid layout
   reassemble-vlm TEXT_CKPT VL_CKPT OUT   put a distilled text backbone back into its VL wrapper
+  convert-qwen-gdn SRC OUT [--pattern P] convert a Qwen3-Next / Qwen3.5-MoE checkpoint to the hybrid layout
   train CONFIG.yaml [k=v ...]    run a training stage (pt | sft | hkd | dpo | kto | rm)
   train-multinode CONFIG.yaml    same, expecting NNODES / NODE_RANK / MASTER_ADDR in the environment
   preprocess --config CFG.yaml   tokenise (and SP-split) datasets into `tokenized_path`, sharded and parallel
@@ -85,6 +86,9 @@ def launch(argv: List[str]) -> int:
         from .priming.fused_to_standard import unfuse_checkpoint
         print(unfuse_checkpoint(rest[0], rest[1] if len(rest) > 1 else None))
         return 0
+    if cmd == "convert-qwen-gdn":
+        from .priming.convert_qwen_gdn import main as convert_main
+        return convert_main(rest)
     if cmd == "reassemble-vlm":
         from .priming.reassemble_vlm import reassemble_vlm
         reassemble_vlm(rest[0], rest[1], rest[2])

@@ -171,3 +171,110 @@ def test_recorded_timeout_makes_the_trainer_fail_loudly():
     tr.check_kernel_status(lambda: (0, 0, 0, 0))
     with pytest.raises(KernelError):
         tr.check_kernel_status(lambda: (2, 17, 0x350, 1))
+
+
+# -- Qwen3-Next / Qwen3.5 converters ---------------------------------------------------------------------------
+NEXT_TINY = {"model_type": "qwen3_next_hmf", "vocab_size": 97, "hidden_size": 32, "intermediate_size": 48,
+             "num_hidden_layers": 4, "num_attention_heads": 2, "num_key_value_heads": 1, "head_dim": 16,
+             "linear_num_key_heads": 2, "linear_num_value_heads": 4, "linear_key_head_dim": 8, "linear_value_head_dim": 8,
+             "num_experts": 4, "num_experts_per_tok": 2, "moe_intermediate_size": 16,
+             "shared_expert_intermediate_size": 16, "decoder_sparse_step": 1, "mlp_only_layers": [],
+             "hybrid_override_pattern": "GDN-GDN-GDN-*", "torch_dtype": "float32",
+             "layer_types": ["linear_attention"] * 3 + ["full_attention"]}
+
+
+def _to_source_layout(model, layout: str):
+    """State dict of a tiny hybrid model written the way the released Qwen checkpoints store it."""
+    from hybrid_model_factory_b200.priming import convert_qwen_gdn as cv
+    from hybrid_model_factory_b200.utils import checkpoint_io
+    cfg = model.config
+    Hk, Hv, dk, dv = (cfg.linear_num_key_heads, cfg.linear_num_value_heads, cfg.linear_key_head_dim,
+                      cfg.linear_value_head_dim)
+    prefix = "model.language_model." if layout == "qwen3_5" else "model."
+    out = {}
+    sd = checkpoint_io.to_hf_names(model.state_dict())
+    for name, t in sd.items():
+        if ".gdn." not in name:
+            out[name.replace("model.", prefix, 1) if name.startswith("model.") else name] = t.clone()
+    for i, layer in enumerate(model.model.layers):
+        if layer.symbol != "GDN":
+            continue
+        g = {k: v.clone() for k, v in layer.gdn.state_dict().items()}
+        p = f"{prefix}layers.{i}.linear_attn."
+        if layout == "qwen3_next":
+            out[p + "in_proj_qkvz.weight"] = cv.interleave_qkvz(g["q_proj.weight"], g["k_proj.weight"], g["v_proj.weight"],
+                                                                 g["g_proj.weight"], Hk, Hv, dk, dv)
+            out[p + "in_proj_ba.weight"] = cv.interleave_ba(g["b_proj.weight"], g["gk_proj.weight"], Hk, Hv)
+        else:
+            out[p + "in_proj_qkv.weight"] = torch.cat([g["q_proj.weight"], g["k_proj.weight"], g["v_proj.weight"]])
+            out[p + "in_proj_z.weight"], out[p + "in_proj_b.weight"] = g["g_proj.weight"], g["b_proj.weight"]
+            out[p + "in_proj_a.weight"] = g["gk_proj.weight"]
+        out[p + "conv1d.weight"] = torch.cat([g["q_conv1d.weight"], g["k_conv1d.weight"], g["v_conv1d.weight"]])
+        out[p + "A_log"], out[p + "dt_bias"] = g["A_log"], g["dt_bias"]
+        out[p + "norm.weight"], out[p + "out_proj.weight"] = g["o_norm.weight"], g["o_proj.weight"]
+    out["mtp.layers.0.input_layernorm.weight"] = torch.ones(cfg.hidden_size)        # dropped by the converter
+    if layout == "qwen3_5":
+        out["model.visual.patch_embed.proj.weight"] = torch.ones(4, 4)
+    return out
+
+
+@pytest.mark.parametrize("layout", ["qwen3_next", "qwen3_5"])
+def test_qwen_gdn_checkpoint_converts_and_loads_strictly(tmp_path, layout):
+    from hybrid_model_factory_b200.priming import convert_qwen_gdn as cv
+    from hybrid_model_factory_b200.utils import checkpoint_io
+    torch.manual_seed(0)
+    model = build_model(HybridConfig.from_dict(dict(NEXT_TINY))).eval()
+    src_dir, out_dir = str(tmp_path / "src"), str(tmp_path / "out")
+    os.makedirs(src_dir)
+    checkpoint_io.save_state_dict(_to_source_layout(model, layout), src_dir)
+    src_cfg = dict(NEXT_TINY, model_type="qwen3_next" if layout == "qwen3_next" else "qwen3_5_moe_text")
+    src_cfg.pop("hybrid_override_pattern")
+    if layout == "qwen3_5":
+        src_cfg = {"model_type": "qwen3_5_moe", "text_config": src_cfg}
+    with open(os.path.join(src_dir, "config.json"), "w") as f:
+        json.dump(src_cfg, f)
+    rep = cv.convert_checkpoint(src_dir, out_dir, dtype=torch.float32)
+    assert rep["missing"] == [] and any(k.startswith("mtp.") for k in rep["dropped"])
+    assert rep["layers"][0] == "linear_attention -> GDN" and rep["layers"][3] == "full_attention -> *"
+    loaded = checkpoint_io.from_pretrained(out_dir).eval()           # strict: raises on any missing parameter
+    ids = torch.randint(0, 97, (2, 24))
+    with torch.no_grad():
+        a = model(ids, return_logits=True).logits
+        b = loaded(ids, return_logits=True).logits
+    assert torch.allclose(a, b, atol=1e-5), (a - b).abs().max()
+    keys = set(checkpoint_io.load_state_dict(out_dir))
+    assert "model.layers.0.gdn.q_proj.weight" in keys and not any("seq_mixer" in k or "linear_attn" in k for k in keys)
+
+
+def test_qwen_gdn_to_gka_and_attention_to_ssm_targets(tmp_path):
+    from hybrid_model_factory_b200.priming import convert_qwen_gdn as cv
+    from hybrid_model_factory_b200.utils import checkpoint_io
+    torch.manual_seed(0)
+    # attention -> SSM copies q/k/v/o row for row, so it needs a source whose attention and linear-attention head
+    # layouts coincide (the stage-0 rules raise on a shape mismatch)
+    NEXT_TINY = dict(globals()["NEXT_TINY"], num_key_value_heads=2, head_dim=8, linear_num_value_heads=2)
+    model = build_model(HybridConfig.from_dict(dict(NEXT_TINY))).eval()
+    src_dir, out_dir = str(tmp_path / "src"), str(tmp_path / "out")
+    os.makedirs(src_dir)
+    checkpoint_io.save_state_dict(_to_source_layout(model, "qwen3_next"), src_dir)
+    src_cfg = dict(NEXT_TINY, model_type="qwen3_next")
+    src_cfg.pop("hybrid_override_pattern")
+    with open(os.path.join(src_dir, "config.json"), "w") as f:
+        json.dump(src_cfg, f)
+    rep = cv.convert_checkpoint(src_dir, out_dir, pattern="GDN-GKA-GDN>GKA-GDN", dtype=torch.float32)
+    assert rep["layers"] == {0: "linear_attention -> GDN", 1: "linear_attention -> GKA",
+                             2: "linear_attention -> GDN>GKA", 3: "full_attention -> GDN"}
+    assert all(any(m.startswith(p) for p in rep["fresh"]) for m in rep["missing"]) and rep["missing"]
+    out = checkpoint_io.load_state_dict(out_dir)
+    g0 = model.model.layers[1].gdn.state_dict()
+    assert torch.equal(out["model.layers.1.gka.a_proj.weight"], g0["gk_proj.weight"])
+    assert torch.equal(out["model.layers.1.gka.b_proj.weight"], g0["b_proj.weight"])
+    assert torch.equal(out["model.layers.2.gdn.q_proj.weight"], model.model.layers[2].gdn.q_proj.weight)
+    assert torch.equal(out["model.layers.2.gka.q_proj.weight"], model.model.layers[2].gdn.q_proj.weight)
+    # attention -> GDN: query rows come out of the per-head [q | gate] blocks of the gated attention
+    qg = model.model.layers[3].self_attn.q_proj.weight.view(2, 16, -1)
+    assert torch.allclose(out["model.layers.3.gdn.q_proj.weight"], qg[:, :8].reshape(16, -1))
+    assert cv.main([src_dir, str(tmp_path / "cli"), "--dtype", "float32"]) == 0
+    # a naming mismatch is an error, not a silent random initialisation
+    with pytest.raises(KeyError):
+        cv.load_converted(build_model(HybridConfig.from_dict(dict(NEXT_TINY))), {"model.layers.0.seq_mixer.x": torch.ones(1)}, [])
