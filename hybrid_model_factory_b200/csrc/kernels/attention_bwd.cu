@@ -13,7 +13,6 @@
 // the query-tile CTA and dK/dV by the key-tile CTA (the GQA group sum happens in the accumulator).
 // Masks follow the forward kernel: key visible <=> lo <= q_pos - k_pos < hi.
 #include <math.h>
-#include <stdlib.h>
 
 #include "../common/host.h"
 #include "../common/sm100.cuh"
@@ -35,7 +34,6 @@ struct Params {
   int lo, hi, q_off;
   float scale, scale_log2;
   unsigned int* status;
-  int dq_mode;         // experiment switch of the fused kernel: 0 = reduce, 1 = no dQ output, 2 = plain stores
 };
 
 // ------------------------------------------------------------------------------------
@@ -759,13 +757,15 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 // The key-tile owner computes S^T and dP^T once and derives all three gradients from them:
 //     dV += P^T dO,   dK += dS^T Q          (accumulated in tensor memory over the whole loop, as above)
 //     dQ^T(tile) = K^T dS                    (one fresh [128 d x 64 q] product per pair, added to an fp32 dQ buffer
-//                                             in global memory with red.global.add.f32)
+//                                             in global memory by one tiled TMA reduction per pair)
 // The packed P^T and dS^T both go back into the S^T columns (P^T in [0,32), dS^T in [32,64)), so that the whole
 // dP^T buffer is free once the softmax threads have read it: the dQ^T product of the same pair is written there.
 // dS^T is also stored in shared memory ([key][query], 128-byte swizzle): the MN-major B operand of the dQ^T MMA,
-// whose A operand is the K tile read MN-major (M = d).  Four drain warps move each dQ^T tile from tensor memory to
-// the global buffer; consecutive lanes hold consecutive d of one query row, so every warp-level reduction is one
-// contiguous 128-byte line.  The fp32 buffer must be zero on entry; a small kernel converts it to bf16 afterwards.
+// whose A operand is the K tile read MN-major (M = d).  Four drain warps move each dQ^T tile from tensor memory into
+// the shared-memory stage that held the pair's Q / dO (free by then) as a [64 q][128 d] fp32 tile, and one thread
+// issues cp.reduce.async.bulk.tensor (.add) for it.  (Per-thread red.global.add.f32, 64 per thread and pair, ran the
+// kernel 3x slower: the number of outstanding store requests per SM, not bytes, was the limit.)
+// The fp32 buffer must be zero on entry; a small kernel converts it to bf16 afterwards.
 // Summation order across key tiles is not fixed: use the two-kernel path above when bit-reproducible gradients
 // are required.
 constexpr int FTHR = 512;   // warps 0-3: TMA, S/dP MMA, accumulate MMA, spare; 4-11: softmax; 12-15: dQ drain
@@ -800,7 +800,7 @@ template <int D>
 __global__ void __launch_bounds__(FTHR, 1)
 attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
                       const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
-                      const Params p, float* __restrict__ dq_acc) {
+                      const __grid_constant__ CUtensorMap tmDQ, const Params p) {
   static_assert(D == 128, "the fused backward is written for head dimension 128");
   using L = SmemFused<D>;
   constexpr int TMEM_COLS = 512;
@@ -954,8 +954,8 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             const uint64_t bd = make_desc_mnmajor_sw128(aQ + kk * 2048, L::QPANEL);
             umma_ts(tDK, tST(s) + 32 + kk * 8, bd, idescAcc, (it > 0 || kk > 0) ? 1u : 0u);
           }
-          umma_commit(&q_empty[qs]);
-          // dQ^T[d, q] = sum_key K[key, d] dS^T[key, q]: 8 steps of 16 keys
+          // dQ^T[d, q] = sum_key K[key, d] dS^T[key, q]: 8 steps of 16 keys (the Q / dO stage is released by the drain
+          // warps, which reuse its memory to stage the dQ tile)
 #pragma unroll
           for (int kk = 0; kk < KM / 16; ++kk) {
             const uint64_t ad = make_desc_mnmajor_sw128(aK + kk * 2048, L::KPANEL);
@@ -968,52 +968,41 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       }
     }
   } else if (wg == 3) {
-    // dQ drain: lane = d (quadrant * 32 + lane), 64 columns = the query rows of the tile
+    // dQ drain: lane = d (quadrant * 32 + lane), 64 columns = the query rows of the tile.  The tile goes through the
+    // Q / dO ring stage of the same pair (its 32 KB are exactly one [64 q][128 d] fp32 tile, and every MMA that read
+    // it has completed once dq_full fires) and leaves as ONE tiled reduction per pair.
     reg_dealloc<96>();
     const int quad = warp & 3;
     const int d = quad * 32 + lane;
     const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
     for (int it = 0; it < n_it; ++it) {
-      const int s = it & 1;
+      const int s = it & 1, qs = it % NST;
       int g, i;
       iter.get(it, g, i);
       const int h = hkv * G + g;
       const int q0 = i * QN;
       const bool ok = mbar_wait(&dq_full[s], (it >> 1) & 1, ctx, 0x390 + s);
       tc_fence_after();
-      float* base = dq_acc + (((size_t)b * p.Tq + q0) * p.Hq + h) * D + d;
-      const size_t rstride = (size_t)p.Hq * D;
-      const int nq = min(QN, p.Tq - q0);
       uint32_t v0[32], v1[32];
       tmem_ld_x32(tDPT(s) + lane_off, v0);
       tmem_ld_x32(tDPT(s) + lane_off + 32, v1);
       tmem_ld_wait();
       tc_fence_before();
-      // registers hold the tile, the buffers may be overwritten.  Relaxed: a releasing arrive would wait for the
-      // previous tile's 64 global reductions of this thread to be acknowledged by L2 (measured: 2x the kernel time).
-      mbar_arrive_relaxed(&t_free[s]);
-      if (ok && p.dq_mode != 1) {
+      mbar_arrive_relaxed(&t_free[s]);                // registers hold the tile: the buffer pair may be overwritten
+      float* stg = reinterpret_cast<float*>(sQ + qs * L::STAGE);
 #pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          if (c < nq) {
-            if (p.dq_mode == 0)
-              asm volatile("red.global.add.f32 [%0], %1;" ::"l"(base + (size_t)c * rstride), "f"(__uint_as_float(v0[c]))
-                           : "memory");
-            else
-              base[(size_t)c * rstride] = __uint_as_float(v0[c]);
-          }
-        }
+      for (int c = 0; c < 32; ++c) stg[c * D + d] = __uint_as_float(v0[c]);
 #pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          if (32 + c < nq) {
-            if (p.dq_mode == 0)
-              asm volatile("red.global.add.f32 [%0], %1;" ::"l"(base + (size_t)(32 + c) * rstride),
-                           "f"(__uint_as_float(v1[c]))
-                           : "memory");
-            else
-              base[(size_t)(32 + c) * rstride] = __uint_as_float(v1[c]);
-          }
+      for (int c = 0; c < 32; ++c) stg[(32 + c) * D + d] = __uint_as_float(v1[c]);
+      fence_async_smem();
+      asm volatile("bar.sync 3, 128;" ::: "memory");
+      if (warp == 12 && lane == 0) {
+        if (ok) {
+          tma_reduce_add_4d(&tmDQ, stg, 0, h, q0, b);
+          tma_store_commit();
+          tma_store_wait_read<0>();                   // the stage may be refilled once the reduction has read it
         }
+        mbar_arrive(&q_empty[qs]);
       }
     }
   } else {
@@ -1252,6 +1241,13 @@ static int launch_fused(const void* q, const void* k, const void* v, const void*
   if ((rc = make_map_bthd(&tmDO, d_o, p.B, p.Tq, p.Hq, D, os[0], os[1], os[2], QN)) != HMF_OK) return rc;
   if ((rc = make_map_bthd(&tmK, k, p.B, p.Tk, p.Hkv, D, ks[0], ks[1], ks[2], KM)) != HMF_OK) return rc;
   if ((rc = make_map_bthd(&tmV, v, p.B, p.Tk, p.Hkv, D, vs[0], vs[1], vs[2], KM)) != HMF_OK) return rc;
+  CUtensorMap tmDQ;
+  {
+    uint64_t dims[4] = {(uint64_t)D, (uint64_t)p.Hq, (uint64_t)p.Tq, (uint64_t)p.B};
+    uint64_t strides[4] = {4, (uint64_t)D * 4, (uint64_t)p.Hq * D * 4, (uint64_t)p.Tq * p.Hq * D * 4};
+    uint32_t box[4] = {(uint32_t)D, 1, (uint32_t)QN, 1};
+    if ((rc = make_tensor_map(&tmDQ, dq_acc, 1, 4, dims, strides, box, 0)) != HMF_OK) return rc;
+  }
   auto kern = attn_bwd_fused_kernel<D>;
   static bool configured = false;
   if (!configured) {
@@ -1259,7 +1255,7 @@ static int launch_fused(const void* q, const void* k, const void* v, const void*
     configured = true;
   }
   dim3 grid((p.Tk + KM - 1) / KM, p.Hkv, p.B);
-  kern<<<grid, FTHR, SmemFused<D>::TOTAL, st>>>(tmQ, tmDO, tmK, tmV, p, dq_acc);
+  kern<<<grid, FTHR, SmemFused<D>::TOTAL, st>>>(tmQ, tmDO, tmK, tmV, tmDQ, p);
   HMF_CHECK_CUDA(cudaGetLastError());
   const long long n8 = (long long)p.B * p.Tq * p.Hq * D / 8;
   dq_convert_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, st>>>(dq_acc, p.dq, n8);
@@ -1302,7 +1298,6 @@ HMF_API int hmf_attention_bwd(const void* q, const void* k, const void* v, const
   p.scale = scale;
   p.scale_log2 = scale * kLog2e;
   p.status = status_ptr();
-  p.dq_mode = 0;
   const long long qs[3] = {q_sb, q_st, q_sh}, ks[3] = {k_sb, k_st, k_sh}, vs[3] = {v_sb, v_st, v_sh};
   if (D == 64) return launch_all<64>(q, k, v, d_o, p, qs, ks, vs, stream);
   return launch_all<128>(q, k, v, d_o, p, qs, ks, vs, stream);
@@ -1339,10 +1334,6 @@ HMF_API int hmf_attention_bwd_fused(const void* q, const void* k, const void* v,
   p.scale = scale;
   p.scale_log2 = scale * kLog2e;
   p.status = status_ptr();
-  {
-    const char* m = getenv("HMF_ATTN_BWD_DQ_MODE");
-    p.dq_mode = m ? atoi(m) : 0;
-  }
   const long long qs[3] = {q_sb, q_st, q_sh}, ks[3] = {k_sb, k_st, k_sh}, vs[3] = {v_sb, v_st, v_sh};
   return launch_fused(q, k, v, d_o, p, qs, ks, vs, dq_acc, stream);
 }

@@ -42,6 +42,20 @@ struct Params {
   unsigned int* status;
 };
 
+// Tile order: groups of GROUP_M row tiles are walked column by column, so the CTAs that run at the same time
+// (consecutive tile ids) cover a block of about 16 x 9 tiles and share 16 A panels and 9 B panels through L2,
+// instead of one B panel and 148 A panels (measured before the change: 7.6x the algorithmic DRAM reads at 8192^3).
+constexpr int GROUP_M = 16;
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& m0, int& n0) {
+  const int per_group = GROUP_M * tiles_n;
+  const int g = tile / per_group;
+  const int first_m = g * GROUP_M;
+  const int gsz = min(tiles_m - first_m, GROUP_M);
+  const int r = tile - g * per_group;
+  m0 = (first_m + r % gsz) * BM;
+  n0 = (r / gsz) * BN;
+}
+
 template <bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -94,8 +108,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int s = 0;
       uint32_t ph = 0;
       for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-        const int m0 = (tile % tiles_m) * BM;
-        const int n0 = (tile / tiles_m) * BN;
+        int m0, n0;
+        tile_coords(tile, tiles_m, tiles_n, m0, n0);
         for (int kb = 0; kb < num_kb; ++kb) {
           mbar_wait(&empty[s], ph ^ 1, ctx, 0x100 + s);
           uint8_t* sA = smem + s * STAGE_BYTES;
@@ -154,8 +168,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     int it = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
       const int a = it & 1;
-      const int m0 = (tile % tiles_m) * BM;
-      const int n0 = (tile / tiles_m) * BN;
+      int m0, n0;
+      tile_coords(tile, tiles_m, tiles_n, m0, n0);
       const int row = m0 + q * 32 + lane;
       mbar_wait(&tfull[a], (it >> 1) & 1, ctx, 0x400 + a);
       tc_fence_after();

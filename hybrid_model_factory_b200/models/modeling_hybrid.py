@@ -415,4 +415,9 @@ MODEL_CLASSES = {
 
 
 def build_model(config: HybridConfig) -> HybridForCausalLM:
-    return MODEL_CLASSES.get(config.model_type, HybridForCausalLM)(config)
+    """Builds the model class of ``config.model_type``; every ``nn.Linear`` in it is re-classed to the layer that runs
+    its three GEMMs on the library's tcgen05 kernel (bf16 CUDA tensors; other tensors take ``F.linear``)."""
+    from ..ops.gemm import use_own_linear
+    model = MODEL_CLASSES.get(config.model_type, HybridForCausalLM)(config)
+    use_own_linear(model)
+    return model

@@ -374,12 +374,19 @@ class _LinearCE(torch.autograd.Function):
             n = min(chunk, N - s)
             h = hidden[s:s + n]
             logits = buf[:n, :V]
-            torch.matmul(h, weight.t(), out=logits) if Vp == V else logits.copy_(h @ weight.t())
+            own = V % 8 == 0 and Dm % 8 == 0 and n >= 128 and weight.is_contiguous()
+            if own:
+                gemm(h, weight, out=logits)
+            else:
+                torch.matmul(h, weight.t(), out=logits) if Vp == V else logits.copy_(h @ weight.t())
             _lib.check(_K().hmf_ce_fwd_bwd(_lib.ptr(logits), _lib.ptr(labels[s:s + n]), _lib.ptr(loss),
                                            _lib.ptr(nvalid), c_ll(n), c_int(V), c_ll(Vp), c_ll(ignore_index),
                                            _st(hidden)), "ce_fwd_bwd")
             if need_dh:
-                torch.matmul(logits, weight, out=dh[s:s + n])
+                if own:
+                    gemm(logits, weight, b_mn_major=True, out=dh[s:s + n])
+                else:
+                    torch.matmul(logits, weight, out=dh[s:s + n])
             if need_dw:
                 # dW[V, Dm] += dlogits^T[V, n] @ h[n, Dm]: both operands MN-major for the tcgen05 GEMM
                 if V % 8 == 0 and Dm % 8 == 0:

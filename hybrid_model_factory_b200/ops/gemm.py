@@ -13,8 +13,10 @@ is evaluated with ``torch.matmul`` in fp32 (reference).
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
+import torch.nn.functional as F
 
 from . import _lib
 
@@ -60,3 +62,80 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False, b_mn_maj
         ctypes.c_int(_OUT_MODES[out_mode]), _lib.stream_ptr(a.device))
     _lib.check(rc, "hmf_gemm_bf16")
     return out
+
+
+# ------------------------------------------------------------------------------------------------------
+# nn.Linear on the kernel above
+# ------------------------------------------------------------------------------------------------------
+# Below this many rows (decode steps) a 128-row tile is mostly padding and the weight read dominates: those calls stay
+# on the library GEMV-style kernels.
+MIN_ROWS = 128
+
+
+def _own_linear_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
+    return (x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.dim() == 2
+            and w.shape[0] % 8 == 0 and w.shape[1] % 8 == 0 and w.is_contiguous() and x.shape[-1] == w.shape[1]
+            and x.numel() >= MIN_ROWS * x.shape[-1] and w.data_ptr() % 16 == 0 and _lib.kernels_available()
+            and os.environ.get("HMF_LINEAR", "own") == "own")
+
+
+def _rows(x: torch.Tensor) -> torch.Tensor:
+    """``[..., K] -> [M, K]`` with unit inner stride, a row stride that is a multiple of 8 and a 16-byte aligned
+    base (what a TMA descriptor needs); a copy only if the view does not qualify."""
+    x2 = x.reshape(-1, x.shape[-1])
+    if x2.stride(1) != 1 or x2.stride(0) % 8 != 0 or x2.data_ptr() % 16 != 0:
+        x2 = x2.contiguous()
+    return x2
+
+
+class _Linear(torch.autograd.Function):
+    """``y = x W^T + b`` with all three GEMMs (forward, input gradient, weight gradient) on the tcgen05 kernel; the
+    operands are read in the layout they already have (no transposes)."""
+
+    @staticmethod
+    def forward(ctx, x, w, b):
+        x2 = _rows(x)
+        y = gemm(x2, w, bias=b)
+        ctx.save_for_backward(x2, w)
+        ctx.has_bias, ctx.x_shape = b is not None, x.shape
+        return y.view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w = ctx.saved_tensors
+        dy2 = _rows(dy)
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dy2, w, b_mn_major=True).view(ctx.x_shape)             # [M, N] x [N, K]
+        if ctx.needs_input_grad[1]:
+            dw = gemm(dy2, x2, a_mn_major=True, b_mn_major=True)             # [N, M] x [M, K]
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = dy2.float().sum(0).to(dy.dtype)
+        return dx, dw, db
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor | None = None) -> torch.Tensor:
+    """Drop-in for ``F.linear``: bf16 CUDA operands run on the library's own GEMM (set ``HMF_LINEAR=cublas`` to
+    compare against the vendor library), everything else takes ``F.linear``."""
+    if not _own_linear_ok(x, w):
+        return F.linear(x, w, b)
+    if torch.is_grad_enabled() and (x.requires_grad or w.requires_grad or (b is not None and b.requires_grad)):
+        return _Linear.apply(x, w, b)
+    return gemm(_rows(x), w, bias=b).view(*x.shape[:-1], w.shape[0])
+
+
+class Linear(torch.nn.Linear):
+    """``nn.Linear`` whose forward and backward run on the library's GEMM.  Same parameters, same state-dict keys."""
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return linear(x, self.weight, self.bias)
+
+
+def use_own_linear(model: torch.nn.Module) -> int:
+    """Re-classes every plain ``nn.Linear`` of ``model`` in place (parameters and names untouched); returns how many."""
+    n = 0
+    for m in model.modules():
+        if type(m) is torch.nn.Linear:
+            m.__class__ = Linear
+            n += 1
+    return n
