@@ -76,6 +76,27 @@ def bench_gemm(args):
     b = torch.randn(N, K, device="cuda").bfloat16()
     out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
     report(f"gemm_bf16 {M}^3", time_fn(lambda: gemm(a, b, out=out)), flops=2.0 * M * N * K)
+    report(f"torch.matmul (cuBLAS) {M}^3", time_fn(lambda: torch.matmul(a, b.t(), out=out)), flops=2.0 * M * N * K)
+
+
+def bench_gemm_step(args):
+    """The projection GEMMs of one Qwen3-8B decoder layer at ``--seq`` tokens: forward, input gradient and weight
+    gradient of [hidden 4096 -> 4096], [4096 -> 12288], [12288 -> 4096], [4096 -> 1024], own kernel against cuBLAS."""
+    from ..ops.gemm import gemm
+    T = args.seq
+    for n_out, k_in in ((4096, 4096), (12288, 4096), (4096, 12288), (1024, 4096)):
+        x = torch.randn(T, k_in, device="cuda").bfloat16()
+        w = torch.randn(n_out, k_in, device="cuda").bfloat16()
+        dy = torch.randn(T, n_out, device="cuda").bfloat16()
+        fl = 2.0 * T * n_out * k_in
+        cases = (("fwd  ", lambda: gemm(x, w), lambda: torch.matmul(x, w.t())),
+                 ("dgrad", lambda: gemm(dy, w, b_mn_major=True), lambda: torch.matmul(dy, w)),
+                 ("wgrad", lambda: gemm(dy, x, a_mn_major=True, b_mn_major=True), lambda: torch.matmul(dy.t(), x)))
+        for name, own, lib in cases:
+            a, b = time_fn(own, flush=False), time_fn(lib, flush=False)
+            tf = fl / a / 1e9
+            print(f"gemm {name} T={T} {k_in}->{n_out}: own {a:.3f} ms ({tf:.0f} TFLOP/s)  cuBLAS {b:.3f} ms "
+                  f"({fl / b / 1e9:.0f} TFLOP/s)  own/cuBLAS time {a / b:.2f}", flush=True)
 
 
 def _qkv(T, H, Hkv, D):
@@ -211,7 +232,7 @@ def bench_paged_decode(args):
                bytes_=2.0 * Rn * L * Hkv * D * 2)
 
 
-CASES = {"gka_cheb": bench_gka_cheb, "paged_decode": bench_paged_decode, "gemm": bench_gemm, "attention_fwd": bench_attention_fwd, "attention_bwd": bench_attention_bwd,
+CASES = {"gemm_step": bench_gemm_step, "gka_cheb": bench_gka_cheb, "paged_decode": bench_paged_decode, "gemm": bench_gemm, "attention_fwd": bench_attention_fwd, "attention_bwd": bench_attention_bwd,
          "gdn_fwd": bench_gdn_fwd, "gdn_fwd_bwd": bench_gdn_fwd_bwd, "rmsnorm": bench_rmsnorm, "swiglu": bench_swiglu,
          "conv1d": bench_conv1d}
 

@@ -1,4 +1,5 @@
-"""Multi-GPU paths (one process per GPU, NCCL + peer memory).  Skipped unless at least two GPUs are visible."""
+"""Multi-GPU paths (one process per GPU, NCCL + peer memory) at 2, 4 and 8 ranks; each case is skipped unless that
+many GPUs are visible.  Every device-side wait in these paths is bounded and no case expects a fault."""
 import pytest
 import torch
 import torch.distributed as dist
@@ -6,7 +7,7 @@ import torch.distributed as dist
 from dist_utils import run_ranks
 
 pytestmark = pytest.mark.gpu
-needs2 = pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+WORLDS = [pytest.param(n, marks=pytest.mark.multigpu(n), id=f"{n}gpu") for n in (2, 4, 8)]
 
 
 def _rel(a, b):
@@ -57,10 +58,11 @@ def _sp_gdn_worker(rank, world, use_peer):
     dist.barrier()
 
 
-@needs2
+@pytest.mark.parametrize("world", WORLDS)
 @pytest.mark.parametrize("use_peer", [False, True])
-def test_sp_gdn_state_chain_two_gpus(use_peer):
-    run_ranks(_sp_gdn_worker, 2, use_peer, backend="nccl", timeout=240)
+def test_sp_gdn_state_chain(world, use_peer):
+    """Zig-zag state chain of 2 * world links, forward and backward, against the single-GPU kernel."""
+    run_ranks(_sp_gdn_worker, world, use_peer, backend="nccl", timeout=240)
 
 
 def _tp_worker(rank, world):
@@ -92,7 +94,8 @@ def _tp_worker(rank, world):
     # 2. the TP engine (CUDA graphs + fused GEMM/all-reduce) against the unsharded engine
     torch.manual_seed(0)
     cfg = HybridConfig("hybrid_qwen3", vocab_size=512, hidden_size=512, intermediate_size=1024, num_hidden_layers=4,
-                       num_attention_heads=4, num_key_value_heads=2, head_dim=128, hybrid_override_pattern="*-GDN-M2-*")
+                       num_attention_heads=2 * world, num_key_value_heads=world, head_dim=128,
+                       hybrid_override_pattern="*-GDN-M2-*")
     model = build_model(cfg).to(dev, torch.bfloat16).eval()
     prompts = [torch.randint(0, 512, (n,)).tolist() for n in (70, 200, 33)]
     ref_eng = ServingEngine(model, block_size=64, num_blocks=32, max_num_seqs=4, max_num_batched_tokens=128,
@@ -110,9 +113,9 @@ def _tp_worker(rank, world):
     dist.barrier()
 
 
-@needs2
-def test_tp_fused_gemm_allreduce_and_engine_two_gpus():
-    run_ranks(_tp_worker, 2, backend="nccl", timeout=300)
+@pytest.mark.parametrize("world", WORLDS)
+def test_tp_fused_gemm_allreduce_and_engine(world):
+    run_ranks(_tp_worker, world, backend="nccl", timeout=300)
 
 
 def _cp_worker(rank, world):
@@ -143,9 +146,9 @@ def _cp_worker(rank, world):
     dist.barrier()
 
 
-@needs2
-def test_cp_attention_peer_kv_two_gpus():
-    run_ranks(_cp_worker, 2, backend="nccl", timeout=240)
+@pytest.mark.parametrize("world", WORLDS)
+def test_cp_attention_peer_kv(world):
+    run_ranks(_cp_worker, world, backend="nccl", timeout=240)
 
 
 def _ep_fused_worker(rank, world):
@@ -175,13 +178,13 @@ def _ep_fused_worker(rank, world):
     dist.barrier()
 
 
-@needs2
-def test_expert_parallel_fused_all_to_all_two_gpus():
-    run_ranks(_ep_fused_worker, 2, backend="nccl", timeout=240)
+@pytest.mark.parametrize("world", WORLDS)
+def test_expert_parallel_fused_all_to_all(world):
+    run_ranks(_ep_fused_worker, world, backend="nccl", timeout=240)
 
 
 def _sp_model_worker(rank, world, pattern, parallel_scan=False):
-    """A whole hybrid model under SP=2 (peer-memory state chain and K/V exchange) against the single-GPU run."""
+    """A whole hybrid model under SP = world (peer-memory state chain and K/V exchange) against the single-GPU run."""
     import copy
     from hybrid_model_factory_b200.models.configuration import HybridConfig
     from hybrid_model_factory_b200.models.modeling_hybrid import build_model
@@ -193,12 +196,12 @@ def _sp_model_worker(rank, world, pattern, parallel_scan=False):
     cfg = HybridConfig("hybrid_qwen3", vocab_size=1024, hidden_size=512, intermediate_size=1024,
                        num_hidden_layers=len(pattern.split("-")), num_attention_heads=4, num_key_value_heads=2,
                        head_dim=128, hybrid_override_pattern=pattern, max_position_embeddings=8192,
-                       swa_config={"window_size": 256},
-                       bmojo_config={"window_size": 128, "ssm_mixer": "gdn", "tie_attn_weights": False})
+                       swa_config={"window_size": 128},
+                       bmojo_config={"window_size": 64, "ssm_mixer": "gdn", "tie_attn_weights": False})
     ref = build_model(cfg).to(dev, torch.bfloat16)
     model = copy.deepcopy(ref)
     g = torch.Generator().manual_seed(1)
-    T = 2048
+    T = 512 * world                                            # 256 tokens per zig-zag segment
     ids = torch.randint(0, 1024, (1, T), generator=g).to(dev)
     labels = torch.roll(ids, -1, dims=1)
     labels[:, -1] = -100
@@ -232,20 +235,20 @@ def _sp_model_worker(rank, world, pattern, parallel_scan=False):
     dist.barrier()
 
 
-@needs2
+@pytest.mark.parametrize("world", WORLDS)
 @pytest.mark.parametrize("pattern", ["*-GDN", "M2-GKA", "SWA-BMF", "BMF"])
-def test_sp_model_two_gpus(pattern):
-    run_ranks(_sp_model_worker, 2, pattern, backend="nccl", timeout=300)
+def test_sp_model(world, pattern):
+    run_ranks(_sp_model_worker, world, pattern, backend="nccl", timeout=300)
 
 
-@needs2
-def test_sp_model_chain_free_scan_two_gpus():
+@pytest.mark.parametrize("world", WORLDS)
+def test_sp_model_chain_free_scan(world):
     """Mamba2 and GKA layers with the two-pass / all-gather form of the state exchange on the GPU kernels."""
-    run_ranks(_sp_model_worker, 2, "M2-GKA", True, backend="nccl", timeout=300)
+    run_ranks(_sp_model_worker, world, "M2-GKA", True, backend="nccl", timeout=300)
 
 
-@needs2
-def test_sp_model_chain_free_delta_rule_two_gpus():
+@pytest.mark.parametrize("world", WORLDS)
+def test_sp_model_chain_free_delta_rule(world):
     """Gated DeltaNet with the matrix-transition form of the chain-free state exchange on the GPU kernels."""
-    run_ranks(_sp_model_worker, 2, "*-GDN", "matrix", backend="nccl", timeout=300)
+    run_ranks(_sp_model_worker, world, "*-GDN", "matrix", backend="nccl", timeout=300)
 
