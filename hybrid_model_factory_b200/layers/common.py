@@ -57,27 +57,69 @@ class MLP(nn.Module):
         return self.down_proj(F_ops.swiglu(self.gate_proj(x), self.up_proj(x)))
 
 
+def rope_inverse_frequencies(dim: int, theta: float, scaling: Optional[dict], max_position: int = 0):
+    """``(inv_freq [dim/2], attention_factor)`` for the RoPE variants of the HF configuration format
+    (``rope_scaling`` / ``rope_parameters`` with ``rope_type`` in default | linear | dynamic | yarn | llama3 | longrope;
+    the same formulas as ``transformers.modeling_rope_utils.ROPE_INIT_FUNCTIONS``, which the reference's rotary module
+    dispatches to, ``modeling_hybrid_qwen3.py:121-183``)."""
+    import math
+    scaling = scaling or {}
+    kind = scaling.get("rope_type", scaling.get("type", "default"))
+    factor = float(scaling.get("factor", 1.0))
+    exps = torch.arange(0, dim, 2, dtype=torch.float32) / dim
+    inv = 1.0 / (theta ** exps)
+    att = 1.0
+    if kind == "linear":
+        inv = inv / factor
+    elif kind in ("dynamic", "ntk") and factor > 1.0:
+        inv = 1.0 / ((theta * factor ** (dim / max(dim - 2, 1))) ** exps)
+    elif kind == "llama3":
+        lo = float(scaling.get("low_freq_factor", 1.0))
+        hi = float(scaling.get("high_freq_factor", 4.0))
+        old = float(scaling.get("original_max_position_embeddings", max_position or 8192))
+        wavelen = 2 * math.pi / inv
+        smooth = ((old / wavelen) - lo) / max(hi - lo, 1e-9)
+        mid = (1 - smooth) * inv / factor + smooth * inv
+        inv = torch.where(wavelen > old / lo, inv / factor, torch.where(wavelen < old / hi, inv, mid))
+    elif kind == "yarn":
+        old = float(scaling.get("original_max_position_embeddings", max_position or 4096))
+        beta_fast, beta_slow = float(scaling.get("beta_fast", 32)), float(scaling.get("beta_slow", 1))
+
+        def correction_dim(rotations):
+            return dim * math.log(old / (rotations * 2 * math.pi)) / (2 * math.log(theta))
+        low = max(math.floor(correction_dim(beta_fast)), 0)
+        high = min(math.ceil(correction_dim(beta_slow)), dim - 1)
+        ramp = ((torch.arange(dim // 2, dtype=torch.float32) - low) / max(high - low, 1e-3)).clamp(0, 1)
+        extrapolation = 1 - ramp
+        inv = inv / factor * (1 - extrapolation) + inv * extrapolation
+        att = float(scaling.get("attention_factor") or (0.1 * math.log(factor) + 1.0 if factor > 1 else 1.0))
+    elif kind == "longrope":
+        old = float(scaling.get("original_max_position_embeddings", max_position or 4096))
+        ext = torch.tensor(scaling.get("long_factor" if max_position > old else "short_factor"), dtype=torch.float32)
+        inv = 1.0 / (ext * theta ** exps)
+        f = max(max_position / old, 1.0)
+        att = float(scaling.get("attention_factor") or (math.sqrt(1 + math.log(f) / math.log(old)) if f > 1 else 1.0))
+    elif kind not in ("default", "mrope"):
+        raise ValueError(f"unknown rope_type {kind!r}")
+    return inv, att
+
+
 class RotaryEmbedding(nn.Module):
     """cos/sin tables from explicit position ids (so zig-zag sharded sequences rotate by their
-    true positions).  Supports the default and linear / dynamic-NTK scaling types."""
+    true positions).  Scaling types: default, linear, dynamic-NTK, llama3, yarn, longrope."""
 
     def __init__(self, dim: int, theta: float = 1e6, scaling: Optional[dict] = None, max_position: int = 0):
         super().__init__()
         self.dim, self.theta, self.scaling, self.max_position = dim, theta, scaling or {}, max_position
-        inv = 1.0 / (theta ** (torch.arange(0, dim, 2, dtype=torch.float32) / dim))
-        kind = self.scaling.get("rope_type", self.scaling.get("type", "default"))
-        factor = float(self.scaling.get("factor", 1.0))
-        if kind == "linear":
-            inv = inv / factor
-        elif kind in ("dynamic", "ntk") and factor > 1.0:
-            base = theta * factor ** (dim / max(dim - 2, 1))
-            inv = 1.0 / (base ** (torch.arange(0, dim, 2, dtype=torch.float32) / dim))
+        inv, self.attention_factor = rope_inverse_frequencies(dim, theta, self.scaling, max_position)
         self.register_buffer("inv_freq", inv, persistent=False)
 
     @torch.no_grad()
     def forward(self, position_ids: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
         freqs = position_ids.float()[..., None] * self.inv_freq.float().to(position_ids.device)
         emb = torch.cat([freqs, freqs], dim=-1)
+        if self.attention_factor != 1.0:                      # yarn / longrope scale the rotated vectors
+            return emb.cos() * self.attention_factor, emb.sin() * self.attention_factor
         return emb.cos(), emb.sin()
 
 

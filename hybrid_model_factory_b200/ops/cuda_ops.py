@@ -179,6 +179,15 @@ class _SwiGLU(torch.autograd.Function):
         return dg, du
 
 
+def swiglu_backward(gate: Tensor, up: Tensor, dy: Tensor) -> Tuple[Tensor, Tensor]:
+    """Gradients of ``silu(gate) * up`` with respect to ``gate`` and ``up`` (bf16, one kernel)."""
+    g, u, dy = gate.contiguous(), up.contiguous(), dy.contiguous()
+    dg, du = torch.empty_like(g), torch.empty_like(u)
+    _lib.check(_K().hmf_swiglu_bwd(_lib.ptr(g), _lib.ptr(u), _lib.ptr(dy), _lib.ptr(dg), _lib.ptr(du),
+                                   c_ll(g.numel()), _st(g)), "swiglu_bwd")
+    return dg, du
+
+
 def swiglu(gate: Tensor, up: Tensor) -> Tensor:
     if not _is_bf16(gate, up) or gate.numel() % 8 != 0:
         return R.swiglu(gate, up)

@@ -23,9 +23,17 @@ from . import _lib
 _OUT_MODES = {"bf16": 0, "f32": 1, "f32_accumulate": 2}
 
 
+def _use_pair_kernel(M: int, N: int, pair) -> bool:
+    """The CTA-pair kernel (256 x 256 tiles on two SMs, ``gemm_bf16_2cta.cu``) takes problems with at least one full
+    tile; ``HMF_GEMM_PAIR=0`` keeps everything on the single-CTA kernel."""
+    if pair is not None:
+        return bool(pair)
+    return M >= 256 and N >= 256 and os.environ.get("HMF_GEMM_PAIR", "1") != "0"
+
+
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False, b_mn_major: bool = False,
          bias: torch.Tensor | None = None, out: torch.Tensor | None = None,
-         out_mode: str = "bf16") -> torch.Tensor:
+         out_mode: str = "bf16", pair: bool | None = None) -> torch.Tensor:
     assert a.dim() == 2 and b.dim() == 2
     M, K = (a.shape[1], a.shape[0]) if a_mn_major else a.shape
     N, Kb = (b.shape[1], b.shape[0]) if b_mn_major else b.shape
@@ -53,7 +61,9 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False, b_mn_maj
     assert out.stride(1) == 1
     if bias is not None:
         bias = bias.float().contiguous()
-    rc = _lib.kernels().hmf_gemm_bf16(
+    K_ = _lib.kernels()
+    fn = K_.hmf_gemm_bf16_2cta if _use_pair_kernel(M, N, pair) else K_.hmf_gemm_bf16
+    rc = fn(
         _lib.ptr(a), _lib.ptr(b), _lib.ptr(out), _lib.ptr(bias),
         ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(K),
         ctypes.c_longlong(a.stride(0)), ctypes.c_longlong(b.stride(0)),

@@ -66,7 +66,7 @@ def shard_experts(moe_block, ep: EPContext) -> None:
 def ep_experts_forward(x: Tensor, w_gate_up: Tensor, w_down: Tensor, weights: Tensor, indices: Tensor,
                        ep: EPContext) -> Tensor:
     """``x [T, Dm]`` local tokens, global routing ``indices [T, k]``; ``w_*`` hold this rank's experts only."""
-    from ..ops.moe import grouped_swiglu_experts
+    from ..ops.moe import experts_rows
     T, k = indices.shape
     per = w_gate_up.shape[0]
     flat_e = indices.reshape(-1)
@@ -82,13 +82,9 @@ def ep_experts_forward(x: Tensor, w_gate_up: Tensor, w_down: Tensor, weights: Te
     er = torch.empty(sum(out_splits), dtype=send_e.dtype, device=x.device)
     dist.all_to_all_single(er, (send_e % per).contiguous(), out_splits, in_splits, group=ep.group)
     # local grouped experts
-    order2 = torch.argsort(er, stable=True)
-    counts = torch.bincount(er, minlength=per)
-    y = grouped_swiglu_experts(xr[order2], counts, w_gate_up, w_down)
-    y_unsorted = torch.empty_like(y)
-    y_unsorted[order2] = y
+    y_rows = experts_rows(xr, er, w_gate_up, w_down)        # grouped tcgen05 GEMMs on the GPU
     # combine
-    yb = all_to_all_rows(y_unsorted, out_splits, in_splits, ep.group)
+    yb = all_to_all_rows(y_rows, out_splits, in_splits, ep.group)
     yb = yb * weights.reshape(-1)[order][:, None].to(yb.dtype)
     out = torch.zeros_like(x)
     out.index_add_(0, token_of, yb)

@@ -75,7 +75,8 @@ def bench_gemm(args):
     a = torch.randn(M, K, device="cuda").bfloat16()
     b = torch.randn(N, K, device="cuda").bfloat16()
     out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
-    report(f"gemm_bf16 {M}^3", time_fn(lambda: gemm(a, b, out=out)), flops=2.0 * M * N * K)
+    report(f"gemm_bf16 {M}^3 (one CTA per tile)", time_fn(lambda: gemm(a, b, out=out, pair=False)), flops=2.0 * M * N * K)
+    report(f"gemm_bf16 {M}^3 (CTA pair per tile)", time_fn(lambda: gemm(a, b, out=out, pair=True)), flops=2.0 * M * N * K)
     report(f"torch.matmul (cuBLAS) {M}^3", time_fn(lambda: torch.matmul(a, b.t(), out=out)), flops=2.0 * M * N * K)
 
 
@@ -94,6 +95,10 @@ def bench_gemm_step(args):
                  ("wgrad", lambda: gemm(dy, x, a_mn_major=True, b_mn_major=True), lambda: torch.matmul(dy.t(), x)))
         for name, own, lib in cases:
             a, b = time_fn(own, flush=False), time_fn(lib, flush=False)
+            os.environ["HMF_GEMM_PAIR"] = "0"
+            a1 = time_fn(own, flush=False)
+            os.environ["HMF_GEMM_PAIR"] = "1"
+            name = f"{name} [1-CTA {a1:.3f} ms]"
             tf = fl / a / 1e9
             print(f"gemm {name} T={T} {k_in}->{n_out}: own {a:.3f} ms ({tf:.0f} TFLOP/s)  cuBLAS {b:.3f} ms "
                   f"({fl / b / 1e9:.0f} TFLOP/s)  own/cuBLAS time {a / b:.2f}", flush=True)

@@ -470,3 +470,23 @@ def test_profiling_helpers_are_inert_without_a_gpu():
     model(torch.randint(0, 128, (1, 8)))
     sb.remove()
     assert isinstance(sb.summary(), dict)
+
+
+def test_rope_scaling_variants_match_transformers():
+    """llama3 / yarn / linear inverse frequencies and attention factor against transformers' own init functions."""
+    import types
+    from transformers.modeling_rope_utils import ROPE_INIT_FUNCTIONS
+    from hybrid_model_factory_b200.layers.common import RotaryEmbedding, rope_inverse_frequencies
+    for kind, extra in [("llama3", dict(factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                                        original_max_position_embeddings=8192)),
+                        ("yarn", dict(factor=4.0, original_max_position_embeddings=4096)), ("linear", dict(factor=2.0))]:
+        rs = dict(rope_type=kind, rope_theta=500000.0, **extra)
+        cfg = types.SimpleNamespace(rope_parameters=rs, rope_scaling=rs, rope_theta=500000.0, head_dim=64,
+                                    hidden_size=256, num_attention_heads=4, max_position_embeddings=32768,
+                                    partial_rotary_factor=1.0, standardize_rope_params=lambda: None)
+        inv_ref, att_ref = ROPE_INIT_FUNCTIONS[kind](cfg, "cpu")
+        inv, att = rope_inverse_frequencies(64, 500000.0, rs, 32768)
+        assert torch.allclose(inv, inv_ref, rtol=1e-6, atol=0) and abs(att - att_ref) < 1e-9, kind
+    rot = RotaryEmbedding(64, 500000.0, dict(rope_type="yarn", factor=4.0, original_max_position_embeddings=4096), 32768)
+    cos, sin = rot(torch.arange(8)[None])
+    assert abs(float(cos[0, 0, 0]) - rot.attention_factor) < 1e-6 and rot.attention_factor > 1.0
