@@ -490,3 +490,30 @@ def test_rope_scaling_variants_match_transformers():
     rot = RotaryEmbedding(64, 500000.0, dict(rope_type="yarn", factor=4.0, original_max_position_embeddings=4096), 32768)
     cos, sin = rot(torch.arange(8)[None])
     assert abs(float(cos[0, 0, 0]) - rot.attention_factor) < 1e-6 and rot.attention_factor > 1.0
+
+
+def test_task_heads_sequence_token_and_qa():
+    from hybrid_model_factory_b200.models.heads import build_head_model, last_token_positions
+    cfg = _cfg("*-GDN", pad_token_id=0, num_labels=3)
+    ids = torch.randint(1, 120, (2, 12))
+    ids[0, 8:] = 0                                                  # right padding
+    assert last_token_positions(ids, 0).tolist() == [7, 11]
+    seq = build_head_model(cfg, "sequence_classification")
+    out = seq(ids, labels=torch.tensor([0, 2]))
+    assert out.logits.shape == (2, 3) and out.loss.item() > 0
+    out.loss.backward()
+    assert seq.score.weight.grad.abs().sum() > 0
+    # padding after the last real token does not change the pooled score (causal model)
+    out2 = seq(ids[:1, :8])
+    assert torch.allclose(out.logits[0], out2.logits[0], atol=1e-5)
+    tok = build_head_model(cfg, "token_classification").eval()
+    lab = torch.randint(0, 3, (2, 12))
+    lab[0, 8:] = -100
+    o = tok(ids, labels=lab)
+    assert o.logits.shape == (2, 12, 3) and torch.isfinite(o.loss)
+    qa = build_head_model(cfg, "question_answering")
+    o = qa(ids, start_positions=torch.tensor([1, 40]), end_positions=torch.tensor([3, 5]))
+    assert o.start_logits.shape == (2, 12) and torch.isfinite(o.loss)
+    reg = build_head_model(_cfg("*-GDN", pad_token_id=0, num_labels=1), "sequence_classification")
+    assert reg(ids, labels=torch.tensor([0.5, -1.0])).loss.item() >= 0 and reg.config.problem_type == "regression"
+    assert set(k.split(".")[0] for k in seq.state_dict()) == {"model", "score"}
