@@ -29,14 +29,23 @@ class DatasetAttr:
     split: str = "train"
     num_samples: Optional[int] = None
     ranking: bool = False              # preference data: ``chosen`` / ``rejected`` answers
+    hf_hub_url: Optional[str] = None   # load with ``datasets.load_dataset`` instead of from a local file
+    subset: Optional[str] = None
+    streaming: bool = False
+
+
+PACKAGED_CATALOGUE = os.path.join(os.path.dirname(os.path.abspath(__file__)), "dataset_info.json")
 
 
 def load_dataset_info(dataset_dir: str) -> Dict[str, dict]:
-    path = os.path.join(dataset_dir, "dataset_info.json")
-    if not os.path.exists(path):
-        return {}
-    with open(path) as f:
-        return json.load(f)
+    """The catalogue shipped with the package (well-known instruction, preference and long-context text datasets by
+    hub name), overlaid by ``<dataset_dir>/dataset_info.json`` when the user provides one."""
+    info: Dict[str, dict] = {}
+    for path in (PACKAGED_CATALOGUE, os.path.join(dataset_dir, "dataset_info.json")):
+        if os.path.exists(path):
+            with open(path) as f:
+                info.update(json.load(f))
+    return info
 
 
 def get_dataset_list(names: Optional[str], dataset_dir: str) -> List[DatasetAttr]:
@@ -49,7 +58,8 @@ def get_dataset_list(names: Optional[str], dataset_dir: str) -> List[DatasetAttr
             e = info[name]
             out.append(DatasetAttr(name, e.get("file_name", name), e.get("formatting", "alpaca"),
                                    e.get("columns", {}), e.get("tags", {}), e.get("split", "train"),
-                                   e.get("num_samples"), bool(e.get("ranking", False))))
+                                   e.get("num_samples"), bool(e.get("ranking", False)), e.get("hf_hub_url"),
+                                   e.get("subset"), bool(e.get("streaming", False))))
         elif os.path.exists(os.path.join(dataset_dir, name)) or os.path.exists(name):
             fmt = "text" if name.endswith(".txt") else "alpaca"
             out.append(DatasetAttr(os.path.basename(name), name, fmt))
@@ -59,6 +69,20 @@ def get_dataset_list(names: Optional[str], dataset_dir: str) -> List[DatasetAttr
 
 
 def read_records(attr: DatasetAttr, dataset_dir: str) -> Iterator[dict]:
+    local = attr.file_name if os.path.isabs(attr.file_name) or os.path.exists(attr.file_name) \
+        else os.path.join(dataset_dir, attr.file_name)
+    if attr.hf_hub_url and not os.path.exists(local):
+        try:
+            import datasets
+            ds = datasets.load_dataset(attr.hf_hub_url, attr.subset, split=attr.split, streaming=attr.streaming)
+        except Exception as e:  # noqa: BLE001  (offline machine, missing package, gated dataset)
+            raise RuntimeError(f"dataset '{attr.name}' is a hub dataset ({attr.hf_hub_url}) and could not be loaded: "
+                               f"{type(e).__name__}: {e}; place a local copy under {dataset_dir} and set file_name") from e
+        for i, rec in enumerate(ds):
+            if attr.num_samples is not None and i >= attr.num_samples:
+                break
+            yield rec
+        return
     path = attr.file_name if os.path.isabs(attr.file_name) or os.path.exists(attr.file_name) \
         else os.path.join(dataset_dir, attr.file_name)
     if path.endswith(".jsonl"):
@@ -306,6 +330,11 @@ TEMPLATES: Dict[str, Template] = {
                                   "<|start_of_role|>assistant<|end_of_role|>",
                          assistant_fmt="{content}<|end_of_text|>\n", efficient_eos=False),
 }
+
+
+from .template_zoo import register_all as _register_zoo  # noqa: E402
+
+_register_zoo(TEMPLATES, Template)
 
 
 def register_template(template: Template) -> None:

@@ -297,6 +297,9 @@ def run_exp(args: Optional[Any] = None) -> Trainer:
             merge_oft(model)
         trainer.args.save_only_model = True
         trainer.save_checkpoint(final)
+        if getattr(run_args, "plot_loss", False) and rank == 0:
+            from ..utils.ploting import plot_loss
+            info_rank0(logger, "loss curves: %s", plot_loss(run_args.output_dir))
         if rank == 0:
             for fn in ("tokenizer.json", "tokenizer_config.json", "vocab.json", "merges.txt", "special_tokens_map.json"):
                 src = os.path.join(model_args.model_name_or_path or "", fn)

@@ -517,3 +517,20 @@ def test_task_heads_sequence_token_and_qa():
     reg = build_head_model(_cfg("*-GDN", pad_token_id=0, num_labels=1), "sequence_classification")
     assert reg(ids, labels=torch.tensor([0.5, -1.0])).loss.item() >= 0 and reg.config.problem_type == "regression"
     assert set(k.split(".")[0] for k in seq.state_dict()) == {"model", "score"}
+
+
+def test_packaged_dataset_catalogue_and_template_zoo(tmp_path):
+    from hybrid_model_factory_b200.data import formats
+    info = formats.load_dataset_info(str(tmp_path))                 # no user file: the packaged catalogue alone
+    assert len(info) >= 40 and info["tulu_3_sft"]["formatting"] == "sharegpt"
+    (tmp_path / "dataset_info.json").write_text(json.dumps({"mine": {"file_name": "mine.json"}, "lima": {"file_name": "l.json"}}))
+    info = formats.load_dataset_info(str(tmp_path))
+    assert info["mine"]["file_name"] == "mine.json" and info["lima"] == {"file_name": "l.json"}    # user entry wins
+    attr = formats.get_dataset_list("fineweb_edu", str(tmp_path))[0]
+    assert attr.hf_hub_url == "HuggingFaceFW/fineweb-edu" and attr.streaming and attr.columns == {"prompt": "text"}
+    with pytest.raises(RuntimeError, match="hub dataset"):          # no network here: a clear message, not a crash
+        next(formats.read_records(attr, str(tmp_path)))
+    assert len(formats.TEMPLATES) >= 100
+    t = formats.get_template("cohere")
+    pairs = t.encode_multiturn(formats.ByteTokenizer(), [{"role": "user", "content": "hi"}, {"role": "assistant", "content": "yo"}])
+    assert bytes(pairs[0][0][-len("<|CHATBOT_TOKEN|>"):]).decode() == "<|CHATBOT_TOKEN|>"

@@ -278,3 +278,14 @@ def test_qwen_gdn_to_gka_and_attention_to_ssm_targets(tmp_path):
     # a naming mismatch is an error, not a silent random initialisation
     with pytest.raises(KeyError):
         cv.load_converted(build_model(HybridConfig.from_dict(dict(NEXT_TINY))), {"model.layers.0.seq_mixer.x": torch.ones(1)}, [])
+
+
+def test_plot_loss_writes_curves(tmp_path):
+    from hybrid_model_factory_b200.utils.ploting import plot_loss, smooth
+    cfg = {"model_name_or_path": json.dumps(TINY), "stage": "pt", "synthetic": True, "cutoff_len": 32, "max_steps": 5,
+           "output_dir": str(tmp_path / "run"), "bf16": False, "pure_bf16": False, "learning_rate": 1e-3,
+           "per_device_train_batch_size": 2, "plot_loss": True}
+    run_exp(cfg)
+    files = [f for f in os.listdir(tmp_path / "run") if f.startswith("training_loss")]
+    assert files and os.path.getsize(tmp_path / "run" / files[0]) > 200
+    assert len(smooth([3.0, 2.0, 1.0])) == 3 and plot_loss(str(tmp_path / "nothing")) == []
