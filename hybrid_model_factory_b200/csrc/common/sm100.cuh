@@ -246,6 +246,16 @@ __device__ __forceinline__ void umma_ss_pair(uint32_t tmem_d, uint64_t adesc, ui
       "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// Same for 8-bit floating-point operands (kind::f8f6f4; K = 32 per instruction).
+__device__ __forceinline__ void umma_ss_pair_f8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                                uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 // Arrive on the mbarrier at this offset in BOTH CTAs of the pair once every earlier tcgen05.mma of this thread is done.
 __device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
   asm volatile(
@@ -377,6 +387,11 @@ __host__ __device__ constexpr uint32_t make_idesc_bf16(int M, int N, bool a_mn_m
          | (1u << 10)                    // B format bf16
          | ((a_mn_major ? 1u : 0u) << 15) | ((b_mn_major ? 1u : 0u) << 16) |
          ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+// kind::f8f6f4 with 8-bit float inputs and fp32 accumulation; format 0 = e4m3, 1 = e5m2; both operands K-major.
+__host__ __device__ constexpr uint32_t make_idesc_f8(int M, int N, int a_fmt, int b_fmt) {
+  return (1u << 4) | ((uint32_t)a_fmt << 7) | ((uint32_t)b_fmt << 10) | ((uint32_t)(N >> 3) << 17) |
+         ((uint32_t)(M >> 4) << 24);
 }
 // Same, tf32 inputs (32-bit operands in shared memory, K = 8 per instruction).
 __host__ __device__ constexpr uint32_t make_idesc_tf32(int M, int N, bool a_mn_major,

@@ -45,6 +45,9 @@ struct Params {
   long long ldc;
   int out_mode;
   unsigned int* status;
+  const float* scale_a;   // fp8 form: per-row scales of A [M] and of B [N]; C = (A_q B_q^T) * scale_a[m] * scale_b[n]
+  const float* scale_b;
+  int fmt_a, fmt_b;       // fp8 form: 0 = e4m3, 1 = e5m2
 };
 
 __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& m0, int& n0) {
@@ -57,7 +60,9 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
   n0 = (r / gsz) * BN;
 }
 
-template <bool A_MN, bool B_MN>
+// FP8 = true: both operands are 8-bit floats, K-major, 128 elements (one 128-byte swizzled row) per k-block, and the
+// epilogue applies the row scales of the two operands (row-wise scaled float8 training).
+template <bool A_MN, bool B_MN, bool FP8 = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                       const Params p) {
@@ -107,7 +112,8 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   const int tiles_m = (p.M + 2 * BM - 1) / (2 * BM);
   const int tiles_n = (p.N + BN - 1) / BN;
   const int num_tiles = tiles_m * tiles_n;
-  const int num_kb = (p.K + BK - 1) / BK;
+  constexpr int BKE = FP8 ? 2 * BK : BK;      // elements per k-block (a 128-byte row either way)
+  const int num_kb = (p.K + BKE - 1) / BKE;
   const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
 
   if (warp == 0) {
@@ -125,14 +131,14 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
           uint8_t* sB = sA + A_BYTES;
           if (leader) mbar_expect_tx(&full[s], 2 * STAGE_BYTES);   // bytes of both CTAs land on the leader's barrier
           if (!A_MN) {
-            tma_load_2d_pair(sA, &tmA, &full[s], kb * BK, m0);
+            tma_load_2d_pair(sA, &tmA, &full[s], kb * BKE, m0);
           } else {
 #pragma unroll
             for (int pn = 0; pn < BM / 64; ++pn)
               tma_load_2d_pair(sA + pn * PANEL_BYTES, &tmA, &full[s], m0 + pn * 64, kb * BK);
           }
           if (!B_MN) {
-            tma_load_2d_pair(sB, &tmB, &full[s], kb * BK, nb);
+            tma_load_2d_pair(sB, &tmB, &full[s], kb * BKE, nb);
           } else {
 #pragma unroll
             for (int pn = 0; pn < BNH / 64; ++pn)
@@ -144,7 +150,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     }
   } else if (warp == 1) {
     if (lane == 0 && leader) {
-      constexpr uint32_t idesc = make_idesc_bf16(2 * BM, BN, A_MN, B_MN);
+      const uint32_t idesc = FP8 ? make_idesc_f8(2 * BM, BN, p.fmt_a, p.fmt_b) : make_idesc_bf16(2 * BM, BN, A_MN, B_MN);
       int s = 0;
       uint32_t ph = 0;
       int it = 0;
@@ -164,7 +170,8 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                                      : make_desc_kmajor_sw128(sA + k * 32);
             const uint64_t bd = B_MN ? make_desc_mnmajor_sw128(sB + k * 2048, PANEL_BYTES)
                                      : make_desc_kmajor_sw128(sB + k * 32);
-            umma_ss_pair(d, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
+            if (FP8) umma_ss_pair_f8(d, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
+            else umma_ss_pair(d, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
           }
           umma_commit_pair(&empty[s]);        // both CTAs may refill the stage
           if (++s == STAGES) { s = 0; ph ^= 1; }
@@ -180,6 +187,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       int m0, n0;
       tile_coords(tile, tiles_m, tiles_n, m0, n0);
       const int row = m0 + rank * BM + q * 32 + lane;
+      const float sa = (FP8 && row < p.M) ? p.scale_a[row] : 1.f;
       mbar_wait(&tfull[a], (it >> 1) & 1, ctx, 0x800 + a);
       tc_fence_after();
       const uint32_t tbase = tmem_base + a * BN + ((uint32_t)(q * 32) << 16);
@@ -193,6 +201,10 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
           float v[32];
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+          if (FP8) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] *= sa * (col0 + j < p.N ? p.scale_b[col0 + j] : 0.f);
+          }
           if (p.bias != nullptr) {
 #pragma unroll
             for (int j = 0; j < 32; ++j)
@@ -252,9 +264,9 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   }
 }
 
-template <bool A_MN, bool B_MN>
+template <bool A_MN, bool B_MN, bool FP8 = false>
 static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const Params& p, cudaStream_t stream) {
-  auto kern = gemm_bf16_2cta_kernel<A_MN, B_MN>;
+  auto kern = gemm_bf16_2cta_kernel<A_MN, B_MN, FP8>;
   static bool configured = false;
   if (!configured) {
     HMF_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
@@ -288,9 +300,41 @@ HMF_API int hmf_gemm_bf16_2cta(const void* A, const void* B, void* C, const floa
   if (rc != HMF_OK) return rc;
   rc = !b_mn_major ? make_map_2d_bf16(&tmB, B, N, K, ldb, BNH, BK) : make_map_2d_bf16(&tmB, B, K, N, ldb, BK, 64);
   if (rc != HMF_OK) return rc;
-  Params p{C, bias, M, N, K, ldc, out_mode, status_ptr()};
+  Params p{C, bias, M, N, K, ldc, out_mode, status_ptr(), nullptr, nullptr, 0, 0};
   if (!a_mn_major && !b_mn_major) return launch<false, false>(tmA, tmB, p, stream);
   if (!a_mn_major && b_mn_major) return launch<false, true>(tmA, tmB, p, stream);
   if (a_mn_major && !b_mn_major) return launch<true, false>(tmA, tmB, p, stream);
   return launch<true, true>(tmA, tmB, p, stream);
+}
+
+
+// Row-wise scaled float8 GEMM: C[M,N] = (A_q[M,K] . B_q[N,K]^T) * scale_a[m] * scale_b[n] (+ bias), A_q / B_q 8-bit
+// floats (fmt 0 = e4m3, 1 = e5m2) stored K-major with row strides lda / ldb in bytes = elements, fp32 accumulation.
+// Requirements: 16-byte aligned pointers, lda / ldb multiples of 16.
+HMF_API int hmf_gemm_fp8_2cta(const void* A, const void* B, void* C, const float* scale_a, const float* scale_b,
+                              const float* bias, int M, int N, int K, long long lda, long long ldb, long long ldc,
+                              int fmt_a, int fmt_b, int out_mode, cudaStream_t stream) {
+  using namespace hmf;
+  using namespace hmf::gemm2;
+  HMF_REQUIRE(A && B && C && scale_a && scale_b, "fp8 gemm: null operand");
+  HMF_REQUIRE(M > 0 && N > 0 && K > 0, "fp8 gemm: empty problem %d x %d x %d", M, N, K);
+  HMF_REQUIRE(lda % 16 == 0 && ldb % 16 == 0, "fp8 gemm: lda=%lld ldb=%lld must be multiples of 16", lda, ldb);
+  HMF_REQUIRE(fmt_a >= 0 && fmt_a <= 1 && fmt_b >= 0 && fmt_b <= 1, "fp8 gemm: formats must be 0 (e4m3) or 1 (e5m2)");
+  HMF_REQUIRE(out_mode >= 0 && out_mode <= 1, "fp8 gemm: out_mode %d", out_mode);
+  CUtensorMap tmA, tmB;
+  int rc;
+  {
+    uint64_t dims[2] = {(uint64_t)K, (uint64_t)M};
+    uint64_t strides[2] = {1, (uint64_t)lda};
+    uint32_t box[2] = {2 * BK, BM};
+    if ((rc = make_tensor_map(&tmA, A, 2, 2, dims, strides, box, 3)) != HMF_OK) return rc;
+  }
+  {
+    uint64_t dims[2] = {(uint64_t)K, (uint64_t)N};
+    uint64_t strides[2] = {1, (uint64_t)ldb};
+    uint32_t box[2] = {2 * BK, BNH};
+    if ((rc = make_tensor_map(&tmB, B, 2, 2, dims, strides, box, 3)) != HMF_OK) return rc;
+  }
+  Params p{C, bias, M, N, K, ldc, out_mode, status_ptr(), scale_a, scale_b, fmt_a, fmt_b};
+  return launch<false, false, true>(tmA, tmB, p, stream);
 }

@@ -229,6 +229,9 @@ def run_exp(args: Optional[Any] = None) -> Trainer:
     elif ft_args.finetuning_type == "freeze":
         from .adapters import freeze_all_but_last
         info_rank0(logger, "trainable parameters: %d", freeze_all_but_last(model, ft_args.freeze_trainable_layers))
+    if getattr(run_args, "fp8", False):
+        from ..ops.fp8 import use_fp8_linear
+        info_rank0(logger, "fp8: %d linear layers run their GEMMs in row-wise scaled float8", use_fp8_linear(model))
     dataset = get_dataset(data_args, tokenizer, stage=("pt" if stage in ("pt", "hkd") else stage if stage in ("rm", "dpo", "kto") else "sft"), sp_size=sp,
                           vocab_size=model.config.vocab_size, seed=run_args.seed)
     bsz = run_args.per_device_train_batch_size * run_args.gradient_accumulation_steps
