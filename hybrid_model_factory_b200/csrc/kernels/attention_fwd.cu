@@ -12,8 +12,8 @@
 //   warps 2-5 : softmax, one query row per thread (no shuffles): tcgen05.ld S, mask, running max with
 //               lazy rescaling of O (only when the max grows by more than 2^8), exp2, bf16 P stored back
 //               over S by tcgen05.st; final O / l and LSE written straight to global memory.
-// Tensor-memory map (256 columns): S0 [0,64) S1 [64,128) O [128,128+D).  P_j aliases the first 32
-// columns of S_j.
+// Tensor-memory map (256 columns; 512 at D = 256): S0 [0,64) S1 [64,128) O [128,128+D).  P_j aliases the first
+// 32 columns of S_j.  At D = 256 (Qwen3-Next gated attention) the tiles take 192 KB, so one CTA runs per SM.
 #include <float.h>
 #include <math.h>
 
@@ -370,7 +370,7 @@ HMF_API int hmf_attention_fwd(const void* q, const void* k, const void* v, void*
   using namespace hmf;
   using namespace hmf::attn;
   HMF_REQUIRE(q && k && v && o, "attention: null tensor");
-  HMF_REQUIRE(D == 64 || D == 128, "attention: head dim %d unsupported (64, 128)", D);
+  HMF_REQUIRE(D == 64 || D == 128 || D == 256, "attention: head dim %d unsupported (64, 128, 256)", D);
   HMF_REQUIRE(Hkv > 0 && Hq % Hkv == 0, "attention: Hq=%d not a multiple of Hkv=%d", Hq, Hkv);
   HMF_REQUIRE(B > 0 && Tq > 0 && Tk > 0, "attention: empty problem");
   HMF_REQUIRE(lo >= 0 && hi > lo, "attention: bad window lo=%d hi=%d", lo, hi);
@@ -391,6 +391,7 @@ HMF_API int hmf_attention_fwd(const void* q, const void* k, const void* v, void*
   p.status = status_ptr();
   p.src_maps = nullptr; p.src_flags = nullptr; p.n_chunks = 0; p.chunk_len = 0; p.epoch = 0;
   if (D == 64) return launch<64>(tmQ, tmK, tmV, p, stream);
+  if (D == 256) return launch<256>(tmQ, tmK, tmV, p, stream);   // one CTA per SM: 192 KB of tiles, 384 TMEM columns
   return launch<128>(tmQ, tmK, tmV, p, stream);
 }
 

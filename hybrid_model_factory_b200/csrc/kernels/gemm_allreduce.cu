@@ -12,6 +12,14 @@
 //      plain peer loads, adds them in rank order (every rank gets bit-identical results) and stores y.
 // The transfer of a tile overlaps the GEMM of the other tiles; no separate collective kernel is launched.
 //
+// Two more forms share the kernel:
+//   * reduce-scatter (mode 1): the 128-column tiles are owned in contiguous blocks of N / (128 world) tiles per rank; a
+//     CTA raises its tile's flag on the owner only, and only the owner's CTA reduces, into y_shard [M, N / world];
+//   * all-gather -> GEMM (x_maps != null): the activations are sharded over the ranks along K ([M, Ks] each, in
+//     symmetric buffers); the TMA producer fetches every k-block of x from its owner's buffer (plain, non-multicast
+//     TMA over NVLink) after that rank's publication flag has been seen, so y = concat_r(x_r) . W^T needs no separate
+//     all-gather.  There is no cross-rank sum in this form (the reduction runs over this rank's own partial).
+//
 // Epochs come from device memory (`sync[0]`, advanced by the last CTA of each launch), so the kernel can be
 // replayed from a CUDA graph.  Partials are double-buffered by epoch parity: a rank can only be one launch
 // ahead of the slowest peer because it needs that peer's flags to finish a launch.
@@ -46,6 +54,12 @@ struct Params {
   unsigned int* status;
   long long part_stride;            // elements between the two parity buffers
   int M, N, Ks, Mpad, rank, world, tmem_cols, splits;
+  int mode;                         // 0 all-reduce, 1 reduce-scatter
+  int ldy, tiles_per_rank;          // reduce-scatter: row stride of y_shard, tiles owned by each rank
+  const CUtensorMap* x_maps;        // all-gather form: [ag_world] maps of the ranks' x shards (global memory)
+  const unsigned int* x_flags;      // x_flags[r] >= x_epoch once rank r has published its shard
+  unsigned int x_epoch;
+  int ag_world, ag_ks;              // ranks and K per rank of the gathered activations
 };
 
 // Rank-ordered sum of every (rank, split) partial of one tile.  Remote loads take microseconds, so they go out in
@@ -53,16 +67,17 @@ struct Params {
 // so every rank gets the same bits.
 template <int CU>
 __device__ __forceinline__ void reduce_tile(const Params& p, int et, int chunks, int ksp, int n0, unsigned parity,
-                                            size_t split_elems) {
+                                            size_t split_elems, int y_col0) {
   const int total = p.world * p.splits;
   for (int c0 = et; c0 < chunks; c0 += 128 * CU) {
     float acc[CU][8];
-    size_t off[CU];
+    size_t off[CU], yoff[CU];
 #pragma unroll
     for (int q = 0; q < CU; ++q) {
       const int c = c0 + q * 128;
       const int m = ksp + (c / (BN / 8)) * p.splits, cc = (c % (BN / 8)) * 8;
       off[q] = (size_t)m * p.N + n0 + cc;
+      yoff[q] = (size_t)m * p.ldy + (n0 - y_col0) + cc;
 #pragma unroll
       for (int j = 0; j < 8; ++j) acc[q][j] = 0.f;
     }
@@ -106,7 +121,7 @@ __device__ __forceinline__ void reduce_tile(const Params& p, int et, int chunks,
         o.y = pack_bf16x2(acc[q][2], acc[q][3]);
         o.z = pack_bf16x2(acc[q][4], acc[q][5]);
         o.w = pack_bf16x2(acc[q][6], acc[q][7]);
-        *reinterpret_cast<uint4*>(p.y + off[q]) = o;
+        *reinterpret_cast<uint4*>(p.y + yoff[q]) = o;
       }
     }
   }
@@ -154,12 +169,23 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
   if (warp == 0) {
     if (lane == 0) {
       const uint32_t bytes = A_BYTES + (uint32_t)p.Mpad * BK * 2;
+      unsigned int x_seen = 0u;
       for (int i = 0; i < k_steps; ++i) {
         const int s = i % STAGES;
         if (i >= STAGES) mbar_wait(&empty[s], ((i / STAGES) - 1) & 1, ctx, 0x10 + s);
         mbar_expect_tx(&full[s], bytes);
         tma_load_2d(smem + OFF_A + s * A_BYTES, &tmW, &full[s], (kb0 + i) * BK, n0);
-        tma_load_2d(smem + OFF_B + s * B_BYTES, &tmX, &full[s], (kb0 + i) * BK, 0);
+        if (p.x_maps == nullptr) {
+          tma_load_2d(smem + OFF_B + s * B_BYTES, &tmX, &full[s], (kb0 + i) * BK, 0);
+        } else {
+          const int kg = (kb0 + i) * BK;                 // column of the gathered activations
+          const int src = kg / p.ag_ks;
+          if (!((x_seen >> src) & 1u)) {
+            wait_flag_sys(p.x_flags + src, p.x_epoch, kPeerWaitNs, p.status, 0x50 + src);
+            x_seen |= 1u << src;
+          }
+          tma_load_2d(smem + OFF_B + s * B_BYTES, p.x_maps + src, &full[s], kg - src * p.ag_ks, 0);
+        }
       }
     }
   } else if (warp == 1) {
@@ -198,9 +224,11 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
     }
     // the CTA barrier orders every thread's partial stores before the (cumulative) system-scope release stores
     asm volatile("bar.sync 1, 128;" ::: "memory");
-    if (et < p.world)
+    const int owner = p.mode == 1 ? tile / p.tiles_per_rank : -1;     // reduce-scatter: the rank that owns the tile
+    if (et < p.world && (owner < 0 || et == owner))
       st_release_sys(p.flags[et] + (size_t)tile * FLAGS_PER_TILE + p.rank * p.splits + ksp, epoch);
-    if (et < p.world * p.splits)
+    const bool reduce_here = owner < 0 || owner == p.rank;
+    if (reduce_here && et < p.world * p.splits)
       wait_flag_sys(p.flags[p.rank] + (size_t)tile * FLAGS_PER_TILE + et, epoch, kPeerWaitNs, p.status, 0x40 + et);
     asm volatile("bar.sync 1, 128;" ::: "memory");
     // this CTA reduces the rows m = ksp, ksp + splits, ... of the tile: rows x 16 chunks of 8 columns, summed over
@@ -209,8 +237,11 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
     const int chunks = rows * (BN / 8);
     // few chunks per thread (many K splits): two at a time; a whole 64-row tile per CTA (8 ranks, no splits): four, so
     // the tile takes two rounds of remote latency instead of four
-    if (chunks > 256) reduce_tile<4>(p, et, chunks, ksp, n0, parity, split_elems);
-    else reduce_tile<2>(p, et, chunks, ksp, n0, parity, split_elems);
+    const int y_col0 = p.mode == 1 ? p.rank * p.tiles_per_rank * BN : 0;
+    if (reduce_here) {
+      if (chunks > 256) reduce_tile<4>(p, et, chunks, ksp, n0, parity, split_elems, y_col0);
+      else reduce_tile<2>(p, et, chunks, ksp, n0, parity, split_elems, y_col0);
+    }
   }
 
   tc_fence_before();
@@ -237,33 +268,46 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
 using namespace hmf;
 using namespace hmf::gar;
 
-// x [M, Ks] bf16 (row stride ldx), w [N, Ks] bf16 (row stride ldw), y [M, N] bf16.
-// part_ptrs / flag_ptrs: `world` device addresses (this process' mappings of every rank's buffers);
-// sync: two zero-initialised uint32 on this device, shared by every launch that uses the same buffers.
-// flag arrays hold max_tiles * 32 words; partial buffers 2 * part_stride elements with part_stride >= splits * M * N.
-HMF_API int hmf_gemm_allreduce(const void* x, const void* w, void* y, int M, int N, int Ks, long long ldx,
-                               long long ldw, const unsigned long long* part_ptrs,
-                               const unsigned long long* flag_ptrs, unsigned int* sync, long long part_stride,
-                               int max_tiles, int rank, int world, int splits, cudaStream_t st) {
-  HMF_REQUIRE(splits >= 1 && splits <= MAX_SPLIT && Ks % (splits * BK) == 0,
-              "gemm_allreduce: %d K splits do not divide Ks=%d into multiples of 64", splits, Ks);
-  HMF_REQUIRE(M >= 1 && M <= MAX_M, "gemm_allreduce: M=%d out of range (1..%d)", M, MAX_M);
-  HMF_REQUIRE(N % BN == 0 && Ks % BK == 0 && Ks > 0, "gemm_allreduce: N=%d must be a multiple of 128, Ks=%d of 64", N, Ks);
-  HMF_REQUIRE(world >= 1 && world <= MAX_WORLD && rank >= 0 && rank < world, "gemm_allreduce: bad rank %d / world %d",
-              rank, world);
-  HMF_REQUIRE(N / BN <= max_tiles, "gemm_allreduce: %d tiles exceed the flag array (%d)", N / BN, max_tiles);
-  HMF_REQUIRE((long long)M * N * splits <= part_stride, "gemm_allreduce: partial buffer too small");
+static int launch_tp(const void* x, const void* w, void* y, int M, int N, int Ks, long long ldx, long long ldw,
+                     const unsigned long long* part_ptrs, const unsigned long long* flag_ptrs, unsigned int* sync,
+                     long long part_stride, int max_tiles, int rank, int world, int splits, int mode,
+                     const unsigned long long* x_ptrs, void* maps_dev, const unsigned int* x_flags,
+                     unsigned int x_epoch, int ag_world, cudaStream_t st) {
+  const int Ktot = x_ptrs ? Ks * ag_world : Ks;
+  HMF_REQUIRE(splits >= 1 && splits <= MAX_SPLIT && Ktot % (splits * BK) == 0,
+              "tp gemm: %d K splits do not divide K=%d into multiples of 64", splits, Ktot);
+  HMF_REQUIRE(M >= 1 && M <= MAX_M, "tp gemm: M=%d out of range (1..%d)", M, MAX_M);
+  HMF_REQUIRE(N % BN == 0 && Ks % BK == 0 && Ks > 0, "tp gemm: N=%d must be a multiple of 128, Ks=%d of 64", N, Ks);
+  HMF_REQUIRE(world >= 1 && world <= MAX_WORLD && rank >= 0 && rank < world, "tp gemm: bad rank %d / world %d", rank, world);
+  HMF_REQUIRE(N / BN <= max_tiles, "tp gemm: %d tiles exceed the flag array (%d)", N / BN, max_tiles);
+  HMF_REQUIRE((long long)M * N * splits <= part_stride, "tp gemm: partial buffer too small");
+  HMF_REQUIRE(mode == 0 || (N / BN) % world == 0, "tp gemm: reduce-scatter needs N / 128 = %d tiles divisible by %d ranks",
+              N / BN, world);
   CUtensorMap tmW, tmX;
   int rc;
   const int Mpad = (M + 15) / 16 * 16;
-  if ((rc = make_map_2d_bf16(&tmW, w, N, Ks, ldw, BN, BK)) != HMF_OK) return rc;
-  if ((rc = make_map_2d_bf16(&tmX, x, M, Ks, ldx, Mpad, BK)) != HMF_OK) return rc;
+  if ((rc = make_map_2d_bf16(&tmW, w, N, Ktot, ldw, BN, BK)) != HMF_OK) return rc;
+  Params p;
+  p.x_maps = nullptr; p.x_flags = nullptr; p.x_epoch = 0; p.ag_world = 1; p.ag_ks = Ks;
+  if (x_ptrs == nullptr) {
+    if ((rc = make_map_2d_bf16(&tmX, x, M, Ks, ldx, Mpad, BK)) != HMF_OK) return rc;
+  } else {
+    HMF_REQUIRE(maps_dev && x_flags && ag_world >= 1 && ag_world <= MAX_WORLD, "tp gemm: bad all-gather arguments");
+    HMF_REQUIRE(((uintptr_t)maps_dev & 63) == 0, "tp gemm: descriptor scratch must be 64-byte aligned");
+    CUtensorMap host_maps[MAX_WORLD];
+    for (int r = 0; r < ag_world; ++r)
+      if ((rc = make_map_2d_bf16(&host_maps[r], reinterpret_cast<const void*>(x_ptrs[r]), M, Ks, ldx, Mpad, BK)) != HMF_OK)
+        return rc;
+    HMF_CHECK_CUDA(cudaMemcpyAsync(maps_dev, host_maps, sizeof(CUtensorMap) * ag_world, cudaMemcpyHostToDevice, st));
+    tmX = host_maps[0];
+    p.x_maps = reinterpret_cast<const CUtensorMap*>(maps_dev);
+    p.x_flags = x_flags; p.x_epoch = x_epoch; p.ag_world = ag_world;
+  }
   static bool configured = false;
   if (!configured) {
     HMF_CHECK_CUDA(cudaFuncSetAttribute(gemm_allreduce_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
     configured = true;
   }
-  Params p;
   p.y = (bf16*)y;
   for (int r = 0; r < MAX_WORLD; ++r) {
     p.part[r] = r < world ? reinterpret_cast<bf16*>(part_ptrs[r]) : nullptr;
@@ -272,11 +316,50 @@ HMF_API int hmf_gemm_allreduce(const void* x, const void* w, void* y, int M, int
   p.sync = sync;
   p.status = status_ptr();
   p.part_stride = part_stride;
-  p.M = M; p.N = N; p.Ks = Ks; p.Mpad = Mpad; p.rank = rank; p.world = world; p.splits = splits;
+  p.M = M; p.N = N; p.Ks = Ktot; p.Mpad = Mpad; p.rank = rank; p.world = world; p.splits = splits;
+  p.mode = mode;
+  p.tiles_per_rank = mode == 1 ? (N / BN) / world : N / BN;
+  p.ldy = mode == 1 ? N / world : N;
   int cols = 32;
   while (cols < Mpad) cols *= 2;
   p.tmem_cols = cols;
   gemm_allreduce_kernel<<<(N / BN) * splits, 192, SMEM_BYTES, st>>>(tmW, tmX, p);
   HMF_CHECK_CUDA(cudaGetLastError());
   return HMF_OK;
+}
+
+// x [M, Ks] bf16 (row stride ldx), w [N, Ks] bf16 (row stride ldw), y [M, N] bf16.
+// part_ptrs / flag_ptrs: `world` device addresses (this process' mappings of every rank's buffers);
+// sync: two zero-initialised uint32 on this device, shared by every launch that uses the same buffers.
+// flag arrays hold max_tiles * 32 words; partial buffers 2 * part_stride elements with part_stride >= splits * M * N.
+HMF_API int hmf_gemm_allreduce(const void* x, const void* w, void* y, int M, int N, int Ks, long long ldx,
+                               long long ldw, const unsigned long long* part_ptrs,
+                               const unsigned long long* flag_ptrs, unsigned int* sync, long long part_stride,
+                               int max_tiles, int rank, int world, int splits, cudaStream_t st) {
+  return launch_tp(x, w, y, M, N, Ks, ldx, ldw, part_ptrs, flag_ptrs, sync, part_stride, max_tiles, rank, world, splits,
+                   0, nullptr, nullptr, nullptr, 0, 1, st);
+}
+
+// Row-parallel GEMM fused with a reduce-scatter over the output columns: y_shard [M, N / world] holds columns
+// [rank * N / world, (rank + 1) * N / world) of sum_r x_r W_r^T.  Other arguments as hmf_gemm_allreduce.
+HMF_API int hmf_gemm_reduce_scatter(const void* x, const void* w, void* y_shard, int M, int N, int Ks, long long ldx,
+                                    long long ldw, const unsigned long long* part_ptrs,
+                                    const unsigned long long* flag_ptrs, unsigned int* sync, long long part_stride,
+                                    int max_tiles, int rank, int world, int splits, cudaStream_t st) {
+  return launch_tp(x, w, y_shard, M, N, Ks, ldx, ldw, part_ptrs, flag_ptrs, sync, part_stride, max_tiles, rank, world,
+                   splits, 1, nullptr, nullptr, nullptr, 0, 1, st);
+}
+
+// All-gather fused into a column-parallel GEMM: y [M, N] = concat_r(x_r) [M, ag_world * Ks] . w [N, ag_world * Ks]^T,
+// where x_r [M, Ks] (row stride ldx) is rank r's shard at x_ptrs[r] (this process' mapping of the symmetric buffers)
+// and x_flags[r] >= x_epoch (local flags) says that shard is complete.  maps_dev: ag_world * 128 bytes of 64-byte
+// aligned device scratch, untouched until the kernel has finished.  part / flag / sync buffers: LOCAL ones (world 1).
+HMF_API int hmf_allgather_gemm(const unsigned long long* x_ptrs, void* maps_dev, const unsigned int* x_flags,
+                               unsigned int x_epoch, int ag_world, const void* w, void* y, int M, int N, int Ks,
+                               long long ldx, long long ldw, const unsigned long long* part_ptrs,
+                               const unsigned long long* flag_ptrs, unsigned int* sync, long long part_stride,
+                               int max_tiles, int splits, cudaStream_t st) {
+  HMF_REQUIRE(x_ptrs != nullptr, "allgather_gemm: null shard table");
+  return launch_tp(nullptr, w, y, M, N, Ks, ldx, ldw, part_ptrs, flag_ptrs, sync, part_stride, max_tiles, 0, 1, splits,
+                   0, x_ptrs, maps_dev, x_flags, x_epoch, ag_world, st);
 }

@@ -489,6 +489,50 @@ def attention_fwd_raw(q: Tensor, k: Tensor, v: Tensor, scale: float, lo: int, hi
     return o, lse
 
 
+_warned = set()
+
+
+def warn_once(msg: str) -> None:
+    """One warning per distinct message when a bf16 CUDA tensor leaves the kernel path (orders of magnitude slower)."""
+    if msg not in _warned:
+        _warned.add(msg)
+        import warnings
+        warnings.warn(msg, stacklevel=3)
+
+
+def _attention_bwd_blocked(q, k, v, o, do, lse, scale, lo, hi, q_off, q_pos=None, dlse=None, block: int = 1024):
+    """Attention backward for head dimensions without a backward kernel (256): recomputes the probabilities from the
+    saved log-sum-exp one block of query rows at a time (memory O(block x Tk) per head) with library matrix products."""
+    B, Tq, Hq, D = q.shape
+    Tk, Hkv = k.shape[1], k.shape[2]
+    G = Hq // Hkv
+    dq = torch.empty_like(q)
+    dk = torch.zeros(B, Tk, Hkv, D, device=q.device, dtype=torch.float32)
+    dv = torch.zeros_like(dk)
+    delta = (o.float() * do.float()).sum(-1)                              # [B, Tq, Hq]
+    if dlse is not None:
+        delta = delta - dlse.transpose(1, 2)
+    kpos = torch.arange(Tk, device=q.device)
+    kf, vf = k.float(), v.float()
+    for s in range(0, Tq, block):
+        e = min(Tq, s + block)
+        pos = (q_pos[:, s:e].long() if q_pos is not None else (torch.arange(s, e, device=q.device) + q_off)[None].expand(B, -1))
+        diff = pos[:, :, None] - kpos[None, None, :]
+        vis = (diff >= lo) & (diff < hi)                                  # [B, n, Tk]
+        qb = q[:, s:e].float().view(B, e - s, Hkv, G, D)
+        dob = do[:, s:e].float().view(B, e - s, Hkv, G, D)
+        sc = torch.einsum("bnhgd,bkhd->bhgnk", qb, kf) * scale
+        lse_b = lse[:, :, s:e].view(B, Hkv, G, e - s)
+        p = torch.exp(sc - lse_b[..., None]).masked_fill(~vis[:, None, None], 0.0)
+        p = torch.nan_to_num(p, nan=0.0)
+        dp = torch.einsum("bnhgd,bkhd->bhgnk", dob, vf)
+        ds = p * (dp - delta[:, s:e].view(B, e - s, Hkv, G).permute(0, 2, 3, 1)[..., None]) * scale
+        dq[:, s:e] = torch.einsum("bhgnk,bkhd->bnhgd", ds, kf).reshape(B, e - s, Hq, D).to(q.dtype)
+        dk += torch.einsum("bhgnk,bnhgd->bkhd", ds, qb)
+        dv += torch.einsum("bhgnk,bnhgd->bkhd", p, dob)
+    return dq, dk.to(k.dtype), dv.to(v.dtype)
+
+
 def deterministic_attention_backward() -> bool:
     """True when the attention backward must sum dQ in a fixed order (``torch.use_deterministic_algorithms`` or
     ``HMF_ATTN_BWD_DETERMINISTIC=1``): the two-kernel path, 7 GEMMs per tile pair, no atomics."""
@@ -503,6 +547,10 @@ def attention_bwd_raw(q, k, v, o, do, lse, scale, lo, hi, q_off, q_pos=None, dls
     kernels separately."""
     B, Tq, Hq, D = q.shape
     Tk, Hkv = k.shape[1], k.shape[2]
+    if D not in (64, 128):
+        warn_once(f"attention backward: head dimension {D} has a forward kernel only; the gradients are computed "
+                  "block by block with library matrix products")
+        return _attention_bwd_blocked(q, k, v, o, do, lse, scale, lo, hi, q_off, q_pos, dlse)
     q = q if _tma_ok(q) else q.contiguous()
     k = k if _tma_ok(k) else k.contiguous()
     v = v if _tma_ok(v) else v.contiguous()
@@ -591,7 +639,9 @@ def attention(q, k, v, *, scale=None, causal=True, window=None, hollow=None, q_p
     """Softmax attention on the tcgen05 kernels.  ``q_pos`` / ``k_pos`` follow the reference contract;
     keys must sit at contiguous positions, queries either contiguous or ascending (query-sparse)."""
     D = q.shape[-1]
-    if not _is_bf16(q, k, v) or D not in (64, 128):
+    if not _is_bf16(q, k, v) or D not in (64, 128, 256):
+        if q.is_cuda and q.dtype == BF16:
+            warn_once(f"attention: head dimension {D} has no kernel; evaluating the PyTorch formulation on the GPU")
         return R.attention(q, k, v, scale=scale, causal=causal, window=window, hollow=hollow, q_pos=q_pos,
                            k_pos=k_pos, return_lse=return_lse)
     Tq, Tk = q.shape[1], k.shape[1]
@@ -600,6 +650,7 @@ def attention(q, k, v, *, scale=None, causal=True, window=None, hollow=None, q_p
     k_off = _contiguous_positions(k_pos, Tk)
     if k_off is None:
         # keys at irregular positions (B'MOJO halo with padded negatives): shift is not expressible
+        warn_once("attention: keys at irregular positions; evaluating the PyTorch formulation on the GPU")
         return R.attention(q, k, v, scale=scale, causal=causal, window=window, hollow=hollow, q_pos=q_pos,
                            k_pos=k_pos, return_lse=return_lse)
     qp = None

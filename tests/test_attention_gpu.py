@@ -22,6 +22,8 @@ CASES = [
     (1, 700, 700, 2, 2, 128, None, 64),
     (1, 1000, 1000, 4, 1, 64, 129, None),
     (1, 2048, 2048, 4, 1, 128, None, None),
+    (2, 1500, 1500, 4, 2, 256, None, None),       # Qwen3-Next head dimension: forward kernel, blocked backward
+    (1, 640, 900, 2, 1, 256, 200, None),
 ]
 
 

@@ -118,6 +118,40 @@ def test_tp_fused_gemm_allreduce_and_engine(world):
     run_ranks(_tp_worker, world, backend="nccl", timeout=300)
 
 
+def _tp_rs_ag_worker(rank, world):
+    """GEMM -> reduce-scatter and all-gather -> GEMM in one kernel each, against NCCL collectives around F.linear."""
+    import torch.nn.functional as F
+    from hybrid_model_factory_b200.ops import _lib
+    from hybrid_model_factory_b200.ops.fused_comm import PeerAllGatherGemm, PeerGemmAllReduce
+    dev = torch.device("cuda", rank)
+    rs = PeerGemmAllReduce(dist.group.WORLD, max_m=256, max_n=4096, device=dev)
+    ag = PeerAllGatherGemm(dist.group.WORLD, max_m=256, max_ks=1024, max_n=4096, device=dev)
+    g = torch.Generator().manual_seed(10 + rank)
+    for it, (M, N, Ks) in enumerate(((5, 128 * world, 128), (64, 1024 * world, 512), (200, 256 * world, 320), (33, 512 * world, 64))):
+        x = torch.randn(M, Ks, generator=g).bfloat16().to(dev)
+        w = (torch.randn(N, Ks, generator=g) * 0.05).bfloat16().to(dev)
+        y = rs.reduce_scatter(x, w)
+        full = F.linear(x, w).float()
+        dist.all_reduce(full)
+        ref = full[:, rank * (N // world):(rank + 1) * (N // world)]
+        assert y.shape == ref.shape and (y.float() - ref).abs().max() < 3e-2 * full.abs().max() + 1e-2, ("rs", it)
+        # all-gather -> GEMM: every rank holds Ks columns of the activations and a weight over all world * Ks columns
+        wa = (torch.randn(N // world, Ks * world, generator=torch.Generator().manual_seed(77 + it)) * 0.05).bfloat16().to(dev)
+        ya = ag(x, wa)
+        xs = [torch.empty_like(x) for _ in range(world)]
+        dist.all_gather(xs, x)
+        refa = F.linear(torch.cat(xs, dim=1), wa).float()
+        assert (ya.float() - refa).abs().max() < 3e-2 * refa.abs().max() + 1e-2, ("ag", it)
+    torch.cuda.synchronize()
+    _lib.assert_status_ok()
+    dist.barrier()
+
+
+@pytest.mark.parametrize("world", WORLDS)
+def test_tp_gemm_reduce_scatter_and_allgather_gemm(world):
+    run_ranks(_tp_rs_ag_worker, world, backend="nccl", timeout=240)
+
+
 def _cp_worker(rank, world):
     from hybrid_model_factory_b200.ops import _lib
     from hybrid_model_factory_b200.parallel.cp_attention import cp_attention
