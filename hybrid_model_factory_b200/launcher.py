@@ -93,6 +93,12 @@ def launch(argv: List[str]) -> int:
         from .priming.reassemble_vlm import reassemble_vlm
         reassemble_vlm(rest[0], rest[1], rest[2])
         return 0
+    if cmd in ("train", "train-multinode") and os.environ.get("USE_RAY", "0") == "1":
+        # Ray placement-group launch: one actor per GPU (RAY_NUM_WORKERS, default: every GPU of the cluster)
+        from .launcher_ray import launch as ray_launch
+        n = int(os.environ.get("RAY_NUM_WORKERS", "0")) or max(1, _visible_gpus())
+        ray_launch(rest, n, os.environ.get("MASTER_ADDR"), int(os.environ["MASTER_PORT"]) if "MASTER_PORT" in os.environ else None)
+        return 0
     if cmd in ("train", "train-multinode"):
         multi = (_visible_gpus() > 1 or os.environ.get("FORCE_TORCHRUN", "0") == "1" or cmd == "train-multinode")
         if multi and "WORLD_SIZE" not in os.environ:

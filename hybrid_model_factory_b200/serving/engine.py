@@ -40,6 +40,9 @@ class SamplingParams:
     max_new_tokens: int = 16
     temperature: float = 0.0
     top_k: int = 0
+    top_p: float = 1.0
+    min_p: float = 0.0
+    repetition_penalty: float = 1.0
     eos_token_id: Optional[int] = None
     ignore_eos: bool = True
 
@@ -54,6 +57,71 @@ class RequestState:
     first_token_time: Optional[float] = None
     finish_time: Optional[float] = None
     finished: bool = False
+
+
+def sample_tokens(logits: torch.Tensor, params: List[SamplingParams], histories=None,
+                  generator: Optional[torch.Generator] = None) -> List[int]:
+    """One token per row of ``logits [rows, V]``: temperature, top-k, top-p, min-p and repetition penalty
+    (``histories[row]`` = token ids seen so far) for the whole batch in one kernel (``csrc/kernels/sampler.cu``) on
+    the GPU, the same procedure in PyTorch elsewhere.  Rows with ``temperature <= 0`` take the arg-max."""
+    rows, V = logits.shape
+    pen = [p.repetition_penalty for p in params]
+    use_kernel = logits.is_cuda and _lib.kernels_available() and logits.dtype in (torch.bfloat16, torch.float32)
+    if histories is not None and any(x != 1.0 for x in pen):
+        logits = logits.clone()
+        n_max = max(1, max(len(h) for h in histories))
+        ids = torch.zeros(rows, n_max, dtype=torch.long)
+        for r, h in enumerate(histories):
+            ids[r, :len(h)] = torch.as_tensor(list(h), dtype=torch.long)
+        n_ids = torch.tensor([len(h) for h in histories], dtype=torch.int32)
+        if use_kernel:
+            ids, n_ids = ids.to(logits.device), n_ids.to(logits.device)
+            pt = torch.tensor(pen, dtype=torch.float32, device=logits.device)
+            lg = logits if logits.stride(1) == 1 else logits.contiguous()
+            _lib.check(_lib.kernels().hmf_repetition_penalty(_lib.ptr(lg), c_int(int(lg.dtype == torch.bfloat16)),
+                                                             c_ll(lg.stride(0)), c_int(rows), _lib.ptr(ids), c_int(n_max),
+                                                             _lib.ptr(n_ids), _lib.ptr(pt), _lib.stream_ptr(lg.device)),
+                       "repetition_penalty")
+            logits = lg
+        else:
+            for r, h in enumerate(histories):
+                if pen[r] != 1.0 and len(h):
+                    idx = torch.as_tensor(sorted(set(h)), dtype=torch.long, device=logits.device)
+                    v = logits[r, idx].float()
+                    logits[r, idx] = torch.where(v > 0, v / pen[r], v * pen[r]).to(logits.dtype)
+    u = torch.rand(rows, generator=generator)
+    if use_kernel:
+        par = torch.tensor([[p.temperature, p.top_p, p.min_p, float(u[i])] for i, p in enumerate(params)],
+                           dtype=torch.float32, device=logits.device)
+        topk = torch.tensor([p.top_k for p in params], dtype=torch.int32, device=logits.device)
+        out = torch.empty(rows, dtype=torch.long, device=logits.device)
+        lg = logits if logits.stride(1) == 1 else logits.contiguous()
+        _lib.check(_lib.kernels().hmf_sample(_lib.ptr(lg), c_int(int(lg.dtype == torch.bfloat16)), c_ll(lg.stride(0)),
+                                             c_int(rows), c_int(V), _lib.ptr(par), _lib.ptr(topk), _lib.ptr(out),
+                                             _lib.stream_ptr(lg.device)), "sample")
+        return out.tolist()
+    out = []
+    for r, (row, p) in enumerate(zip(logits.float(), params)):
+        if p.temperature <= 0:
+            out.append(int(row.argmax()))
+            continue
+        pr = torch.exp((row - row.max()) / p.temperature)
+        keep = torch.ones_like(pr, dtype=torch.bool)
+        if p.top_k and p.top_k < V:
+            keep &= pr >= torch.topk(pr, p.top_k).values[-1]
+        if p.min_p > 0:
+            keep &= pr >= p.min_p
+        if 0 < p.top_p < 1:
+            srt, order = torch.sort(torch.where(keep, pr, torch.zeros_like(pr)), descending=True)
+            cum = torch.cumsum(srt, 0)
+            n_keep = int((cum < p.top_p * cum[-1]).sum()) + 1
+            mask = torch.zeros_like(keep)
+            mask[order[:n_keep]] = True
+            keep &= mask
+        pr = torch.where(keep, pr, torch.zeros_like(pr))
+        cdf = torch.cumsum(pr, 0)
+        out.append(int(torch.searchsorted(cdf, u[r].to(cdf.device) * cdf[-1], right=True).clamp(max=V - 1)))
+    return out
 
 
 class ServingEngine:
@@ -135,7 +203,9 @@ class ServingEngine:
         t0 = time.perf_counter()
         if decodes:
             logits = self._decode_forward(decodes)
-            toks = self._sample(logits, [self.requests[s.req_id].params for s in decodes])
+            reqs = [self.requests[s.req_id] for s in decodes]
+            hist = [r.prompt + r.output for r in reqs] if any(r.params.repetition_penalty != 1.0 for r in reqs) else None
+            toks = self._sample(logits, [r.params for r in reqs], hist)
             if self._timed_replay:      # the sampled ids were read back, so the replay has finished
                 self.stats["decode_gpu_s"] += self._events[0].elapsed_time(self._events[1]) * 1e-3
                 self._timed_replay = False
@@ -160,7 +230,8 @@ class ServingEngine:
                 if snap >= 0:
                     self.state.copy_slot(s.slot, snap)
             if end >= len(req.prompt) + len(req.output):
-                tok = self._sample(logits[-1:], [req.params])[0]
+                hist = [req.prompt + req.output] if req.params.repetition_penalty != 1.0 else None
+                tok = self._sample(logits[-1:], [req.params], hist)[0]
                 results.append(self._emit(s.req_id, int(tok)))
         if prefills:
             self.stats["prefill_s"] += time.perf_counter() - t0
@@ -188,7 +259,7 @@ class ServingEngine:
         return (rid, tok, done)
 
     # -- sampling ------------------------------------------------------------------------------
-    def _sample(self, logits: torch.Tensor, params: List[SamplingParams]) -> List[int]:
+    def _sample(self, logits: torch.Tensor, params: List[SamplingParams], histories=None) -> List[int]:
         if all(p.temperature <= 0 for p in params):
             if self._cuda and logits.is_cuda:
                 ids = torch.empty(logits.shape[0], dtype=torch.long, device=logits.device)
@@ -200,17 +271,7 @@ class ServingEngine:
                     ids = lg.float().argmax(-1)
                 return ids.tolist()
             return logits.float().argmax(-1).tolist()
-        out = []
-        for row, p in zip(logits.float(), params):
-            if p.temperature <= 0:
-                out.append(int(row.argmax()))
-                continue
-            row = row / p.temperature
-            if p.top_k:
-                kth = torch.topk(row, p.top_k).values[-1]
-                row = row.masked_fill(row < kth, float("-inf"))
-            out.append(int(torch.multinomial(torch.softmax(row, -1), 1)))
-        return out
+        return sample_tokens(logits, params, histories)
 
     # -- prefill (per request chunk) -------------------------------------------------------------
     def _prefill_forward(self, s: ScheduledSeq, tokens: List[int]) -> torch.Tensor:

@@ -534,3 +534,73 @@ def test_packaged_dataset_catalogue_and_template_zoo(tmp_path):
     t = formats.get_template("cohere")
     pairs = t.encode_multiturn(formats.ByteTokenizer(), [{"role": "user", "content": "hi"}, {"role": "assistant", "content": "yo"}])
     assert bytes(pairs[0][0][-len("<|CHATBOT_TOKEN|>"):]).decode() == "<|CHATBOT_TOKEN|>"
+
+
+def test_ray_launcher_plans_ranks_and_runs_workers(monkeypatch, tmp_path):
+    """The Ray launch against a small in-process stand-in for the ``ray`` package: placement group of one GPU bundle
+    per worker, rank order by node, rendezvous variables per rank, results gathered on the driver."""
+    import sys
+    import types
+    from hybrid_model_factory_b200 import launcher_ray as LR
+    assert LR.order_bundles(["b", "a", "b", "a"], "a") == [1, 3, 0, 2]
+    assert LR.order_bundles(["x", "x"], None) == [0, 1]
+    env = LR.worker_env(3, 8, "10.0.0.1", 2345, {"HMF_X": "1"})
+    assert env["RANK"] == "3" and env["WORLD_SIZE"] == "8" and env["MASTER_PORT"] == "2345" and env["HMF_X"] == "1"
+
+    started, state = [], {"init": False}
+
+    class _Ref:
+        def __init__(self, v):
+            self.v = v
+
+    class _Method:
+        def __init__(self, fn):
+            self.fn = fn
+
+        def remote(self, *a, **k):
+            return _Ref(self.fn(*a, **k))
+
+    class _Handle:
+        def __init__(self, cls, opts, args):
+            self.opts, self.env = opts, args[0]
+            started.append(self)
+            self.node = ["n0", "n1"][opts["scheduling_strategy"].placement_group_bundle_index % 2]
+            self.node_ip = _Method(lambda: self.node)
+            self.train = _Method(lambda cfg: {"global_step": 7, "rank": int(self.env["RANK"])})
+
+    class _Remote:
+        def __init__(self, cls):
+            self.cls, self.opts = cls, {}
+
+        def options(self, **kw):
+            r = _Remote(self.cls)
+            r.opts = kw
+            return r
+
+        def remote(self, *args):
+            return _Handle(self.cls, self.opts, args)
+
+    ray = types.ModuleType("ray")
+    ray.is_initialized = lambda: state["init"]
+    ray.init = lambda **kw: state.__setitem__("init", True)
+    ray.shutdown = lambda: state.__setitem__("init", False)
+    ray.cluster_resources = lambda: {"GPU": 4}
+    ray.remote = lambda cls: _Remote(cls)
+    ray.get = lambda x: [r.v for r in x] if isinstance(x, list) else x.v
+    ray.kill = lambda h: None
+    util = types.ModuleType("ray.util")
+    pgm = types.ModuleType("ray.util.placement_group")
+    pgm.placement_group = lambda bundles, strategy="PACK": types.SimpleNamespace(bundles=bundles, strategy=strategy, ready=lambda: _Ref(True))
+    ssm = types.ModuleType("ray.util.scheduling_strategies")
+    ssm.PlacementGroupSchedulingStrategy = lambda placement_group, placement_group_bundle_index: types.SimpleNamespace(
+        placement_group=placement_group, placement_group_bundle_index=placement_group_bundle_index)
+    for name, mod in {"ray": ray, "ray.util": util, "ray.util.placement_group": pgm, "ray.util.scheduling_strategies": ssm}.items():
+        monkeypatch.setitem(sys.modules, name, mod)
+    out = LR.launch({"stage": "pt"}, 4, master_port=4321)
+    assert sorted(o["rank"] for o in out) == [0, 1, 2, 3] and not state["init"]
+    workers = started[4:]                                   # the first four actors were placement probes
+    assert [w.env["RANK"] for w in workers] == ["0", "1", "2", "3"]
+    assert [w.node for w in workers] == ["n0", "n0", "n1", "n1"]          # ranks on one node are consecutive
+    assert all(w.env["MASTER_ADDR"] == "n0" and w.env["MASTER_PORT"] == "4321" for w in workers)
+    with pytest.raises(ValueError):
+        LR.launch({}, 8)

@@ -484,3 +484,42 @@ def test_state_shapes_match_the_engine_allocations():
     assert full == 2 * half and SS.gka_state_shapes(32, 8, 32, 128, use_v_conv=False)["conv"][0][1] == 40 * 128
     with pytest.raises(AssertionError):
         SS.gdn_state_shapes(32, 8, 32, 128, tp=16)
+
+
+@pytest.mark.parametrize("device", ["cpu", pytest.param("cuda", marks=pytest.mark.gpu)])
+def test_sampler_filters(device):
+    """Temperature / top-k / top-p / min-p / repetition penalty: the sampled token always lies in the kept set, greedy
+    rows return the arg-max, and the empirical distribution follows the renormalised probabilities (the PyTorch
+    procedure on the CPU, the sampling kernel on the GPU)."""
+    from hybrid_model_factory_b200.serving.engine import SamplingParams, sample_tokens
+    devs = [device]
+    g = torch.Generator().manual_seed(0)
+    V = 1000
+    base = torch.randn(V, generator=g) * 3
+    for dev in devs:
+        logits = base.repeat(64, 1).to(dev)
+        top5 = set(torch.topk(base, 5).indices.tolist())
+        toks = sample_tokens(logits, [SamplingParams(temperature=1.0, top_k=5)] * 64, generator=g)
+        assert set(toks) <= top5 and len(set(toks)) > 1
+        assert sample_tokens(logits[:3], [SamplingParams(temperature=0.0)] * 3) == [int(base.argmax())] * 3
+        # nucleus: the smallest prefix of the sorted probabilities that reaches top_p
+        pr = torch.softmax(base, 0)
+        srt, order = torch.sort(pr, descending=True)
+        n_keep = int((torch.cumsum(srt, 0) < 0.6).sum()) + 1
+        toks = sample_tokens(logits, [SamplingParams(temperature=1.0, top_p=0.6)] * 64, generator=g)
+        assert set(toks) <= set(order[:n_keep + 1].tolist())
+        toks = sample_tokens(logits, [SamplingParams(temperature=1.0, min_p=0.5)] * 64, generator=g)
+        assert all(pr[t] >= 0.5 * pr.max() - 1e-6 for t in toks)
+        # repetition penalty pushes the arg-max away from a token already produced
+        best = int(base.argmax())
+        boosted = base.clone()
+        boosted[best] = boosted.abs().max() + 0.1
+        second = int(torch.topk(boosted, 2).indices[1])
+        out = sample_tokens(boosted[None].to(dev), [SamplingParams(temperature=0.0, repetition_penalty=50.0)], [[best, best]])
+        assert out == [second]
+    # distribution check on the widest device available
+    dev = devs[-1]
+    small = torch.tensor([[2.0, 1.0, 0.0, -1.0]]).repeat(4000, 1).to(dev)
+    toks = torch.tensor(sample_tokens(small, [SamplingParams(temperature=1.0)] * 4000, generator=g))
+    freq = torch.bincount(toks, minlength=4).float() / 4000
+    assert (freq - torch.softmax(small[0].float().cpu(), 0)).abs().max() < 0.03
