@@ -72,11 +72,14 @@ sample_kernel(const T* __restrict__ logits, long long ld_row, int V, const float
   for (int i = threadIdx.x; i < V; i += THREADS) mx = fmaxf(mx, ld(l, i));
   mx = block_max(mx, red);
   if (!(temp > 0.f)) {
+    if (threadIdx.x == 0) winner = V;
+    __syncthreads();
     int best = V;
     for (int i = threadIdx.x; i < V; i += THREADS)
       if (ld(l, i) == mx) best = min(best, i);
-    best = -(int)block_max((float)(-best), red);                      // indices below 2^24 are exact in fp32
-    if (threadIdx.x == 0) out[row] = best;
+    if (best < V) atomicMin(&winner, best);
+    __syncthreads();
+    if (threadIdx.x == 0) out[row] = winner < V ? winner : 0;
     return;
   }
   const float inv_t = 1.f / temp;

@@ -260,7 +260,7 @@ def get_dataset(data_args: DataArguments, tokenizer, stage: str = "pt", sp_size:
         else:
             rows = process_supervised(examples, tokenizer, template, data_args.cutoff_len, data_args.train_on_prompt,
                                       data_args.mask_history)
-            if data_args.packing:
+            if data_args.packing or data_args.neat_packing:
                 rows = pack_supervised(rows, data_args.cutoff_len, pad_id)
         parts.append(rows)
     probs = [float(x) for x in data_args.interleave_probs.split(",")] if data_args.interleave_probs else None
@@ -272,6 +272,7 @@ def get_dataset(data_args: DataArguments, tokenizer, stage: str = "pt", sp_size:
         rows = preprocess_sp_dataset(rows, sp_size, data_args.cutoff_len, pad_id)
         shifted = True
     ds = ListDataset(rows, shifted)
+    ds.neat_packing = bool(getattr(data_args, "neat_packing", False)) and sp_size == 1
     if data_args.tokenized_path:
         ds.save(data_args.tokenized_path)
     return ds
@@ -346,5 +347,10 @@ def batch_iterator(dataset, batch_size: int, rank: int = 0, world: int = 1, sp_s
         rows = [dataset[(order[i] if order is not None else i) * sp_size + r] for i in ids]
         batch = collate(rows, pad_id, pin)
         batch["labels_shifted"] = labels_shifted
+        if getattr(dataset, "neat_packing", False) and batch_size == 1 and "position_ids" in rows[0]:
+            # packed samples must not attend to one another: sample boundaries are where the position ids restart
+            from .collator import indices_from_position_ids, segment_boundaries
+            seg = indices_from_position_ids(rows[0]["position_ids"], len(rows[0]["position_ids"]))
+            batch["cu_seqlens"] = segment_boundaries(torch.tensor([seg]))
         yield batch
         step += 1

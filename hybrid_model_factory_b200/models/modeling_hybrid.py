@@ -158,8 +158,23 @@ class DecoderLayer(nn.Module):
         h = self.input_layernorm(hidden_states)
         if self.symbol == "L2A":        # the router reads the residual stream after the local attention
             kwargs = dict(kwargs, residual=residual)
-        h, _, _ = self.seq_mixer(h, position_embeddings=position_embeddings, position_ids=position_ids,
-                                 past_key_values=past_key_values, use_cache=use_cache, **kwargs)
+        cu = kwargs.pop("cu_seqlens", None)
+        if cu is not None and len(cu) > 2:
+            # packed samples (batch of one row): the mixer runs once per sample on its slice, so neither attention
+            # nor recurrent state crosses a sample boundary
+            parts = []
+            for a, b in zip(cu[:-1], cu[1:]):
+                pe = None if position_embeddings is None else tuple(t[:, a:b] for t in position_embeddings)
+                kw = dict(kwargs)
+                if "residual" in kw:
+                    kw["residual"] = kw["residual"][:, a:b]
+                parts.append(self.seq_mixer(h[:, a:b], position_embeddings=pe,
+                                            position_ids=None if position_ids is None else position_ids[:, a:b],
+                                            past_key_values=None, use_cache=False, **kw)[0])
+            h = torch.cat(parts, dim=1)
+        else:
+            h, _, _ = self.seq_mixer(h, position_embeddings=position_embeddings, position_ids=position_ids,
+                                     past_key_values=past_key_values, use_cache=use_cache, **kwargs)
         norm = self.post_attention_layernorm
         if not torch.is_grad_enabled() and h.is_cuda and h.dtype == torch.bfloat16 and not norm.zero_centered:
             normed, residual = F_ops.fused_add_rms_norm(h, residual, norm.weight, norm.variance_epsilon)   # one pass
@@ -257,8 +272,20 @@ class HybridModel(nn.Module):
 
     def forward(self, input_ids=None, position_ids=None, past_key_values=None, use_cache=False, inputs_embeds=None,
                 **kwargs):
+        """``cu_seqlens`` (keyword): boundaries ``[0, e_1, ..., T]`` of the samples packed into the (single) row, or a
+        list with one such list per row when the batch has one row; every sequence mixer then treats the samples
+        independently (``data/collator.py``)."""
         h = self.embed_tokens(input_ids) if inputs_embeds is None else inputs_embeds
         B, T = h.shape[0], h.shape[1]
+        cu = kwargs.get("cu_seqlens")
+        if cu is not None:
+            if len(cu) and isinstance(cu[0], (list, tuple)):
+                if B != 1 and any(len(c) > 2 for c in cu):
+                    raise ValueError("packed samples (cu_seqlens) need a batch of one row; collate rows one by one")
+                cu = list(cu[0])
+            kwargs["cu_seqlens"] = [int(c) for c in cu]
+            if self.gradient_checkpointing and self.training and len(cu) > 2:
+                raise ValueError("cu_seqlens with activation checkpointing is not supported; disable one of the two")
         if position_ids is None:
             off = past_key_values.seqlen_offset if past_key_values is not None else 0
             position_ids = torch.arange(off, off + T, device=h.device).expand(B, T)

@@ -144,8 +144,9 @@ class Trainer:
     def compute_loss(self, batch: Dict[str, torch.Tensor]) -> torch.Tensor:
         if self.loss_fn is not None:
             return self.loss_fn(self.model, batch)
+        extra = {"cu_seqlens": batch["cu_seqlens"]} if batch.get("cu_seqlens") is not None else {}
         out = self.model(input_ids=batch["input_ids"], labels=batch["labels"], position_ids=batch.get("position_ids"),
-                         labels_shifted=bool(batch.get("labels_shifted", self.sp is not None)))
+                         labels_shifted=bool(batch.get("labels_shifted", self.sp is not None)), **extra)
         return out.loss
 
     def train_step(self, batch: Dict[str, torch.Tensor]) -> torch.Tensor:
@@ -162,6 +163,8 @@ class Trainer:
         for i in range(0, bsz, micro):
             mb = {k: (v[i:i + micro] if isinstance(v, torch.Tensor) and v.dim() > 0 and v.shape[0] == bsz else v)
                   for k, v in dev.items()}
+            if isinstance(mb.get("cu_seqlens"), list) and micro == 1 and len(mb["cu_seqlens"]) == bsz:
+                mb["cu_seqlens"] = [mb["cu_seqlens"][i]]
             loss = self.compute_loss(mb) * (micro / bsz)
             loss.backward()
             total = loss.detach() if total is None else total + loss.detach()

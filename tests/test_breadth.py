@@ -604,3 +604,28 @@ def test_ray_launcher_plans_ranks_and_runs_workers(monkeypatch, tmp_path):
     assert all(w.env["MASTER_ADDR"] == "n0" and w.env["MASTER_PORT"] == "4321" for w in workers)
     with pytest.raises(ValueError):
         LR.launch({}, 8)
+
+
+def test_packed_sequences_do_not_see_each_other():
+    """cu_seqlens from the packed-sequence collator: logits of a packed row equal the logits of every sample run alone
+    (attention and recurrent layers), and the 4-D mask is block diagonal and causal."""
+    from hybrid_model_factory_b200.data.collator import (PackedSequenceCollator, prepare_4d_attention_mask,
+                                                         segment_boundaries)
+    m = prepare_4d_attention_mask(torch.tensor([[1, 1, 2, 2, 2, 0]]))
+    ok = (m[0, 0] == 0)
+    assert ok[1, 0] and not ok[2, 1] and ok[4, 2] and not ok[0, 1] and not ok[5, 5] and not ok[5, 0]
+    assert segment_boundaries(torch.tensor([[1, 1, 2, 2, 2, 0]])) == [[0, 2, 5, 6]]
+    torch.manual_seed(0)
+    model = build_model(_cfg("*-GDN-GKA-M2", num_hidden_layers=4)).eval()
+    a, b = torch.randint(1, 120, (9,)).tolist(), torch.randint(1, 120, (14,)).tolist()
+    row = {"input_ids": a + b, "labels": a + b, "position_ids": list(range(9)) + list(range(14))}
+    batch = PackedSequenceCollator(pad_id=0, with_4d_mask=True)([row])
+    assert batch["cu_seqlens"] == [[0, 9, 23, 24]] and batch["attention_mask_4d"].shape == (1, 1, 24, 24)
+    with torch.no_grad():
+        packed = model(batch["input_ids"], position_ids=batch["position_ids"], cu_seqlens=batch["cu_seqlens"],
+                       return_logits=True).logits
+        la = model(torch.tensor([a]), return_logits=True).logits
+        lb = model(torch.tensor([b]), return_logits=True).logits
+        mixed = model(batch["input_ids"], position_ids=batch["position_ids"], return_logits=True).logits
+    assert torch.allclose(packed[0, :9], la[0], atol=2e-4) and torch.allclose(packed[0, 9:23], lb[0], atol=2e-4)
+    assert not torch.allclose(mixed[0, 9:23], lb[0], atol=1e-3)          # without boundaries sample b sees sample a
