@@ -29,12 +29,45 @@ def _qkv_state_shapes(inputs):
     return [((q.shape[0], q.shape[2], q.shape[3], v.shape[3]), torch.float32)]
 
 
+KERNEL_DIM = 128     # key / value width the chunk kernels are written for
+
+
+def _pad_to_kernel_width(q: Tensor, k: Tensor, v: Tensor, initial_state: Optional[Tensor], scale: Optional[float]):
+    """The chunk kernels work on 128-wide keys and values.  Narrower heads (Mamba2 with head_dim 64 and d_state 128,
+    small test models) are zero-padded to that width instead of leaving the tensor cores: zero key columns add nothing
+    to any score or state row, zero value columns produce zero outputs, so the result is the same and only the value
+    side does up to 2x the arithmetic.  Returns the padded tensors, the scale of the unpadded problem and ``(Dk, Dv)``
+    (``None`` when nothing was padded)."""
+    Dk, Dv = q.shape[-1], v.shape[-1]
+    if not (q.is_cuda and q.dtype == torch.bfloat16) or (Dk == KERNEL_DIM and Dv == KERNEL_DIM) \
+            or Dk > KERNEL_DIM or Dv > KERNEL_DIM:
+        return q, k, v, initial_state, scale, None
+    import torch.nn.functional as F
+    scale = Dk ** -0.5 if scale is None else scale
+    q = F.pad(q, (0, KERNEL_DIM - Dk))
+    k = F.pad(k, (0, KERNEL_DIM - Dk))
+    v = F.pad(v, (0, KERNEL_DIM - Dv))
+    if initial_state is not None:
+        initial_state = F.pad(initial_state, (0, KERNEL_DIM - Dv, 0, KERNEL_DIM - Dk))
+    return q, k, v, initial_state, scale, (Dk, Dv)
+
+
+def _unpad(o: Tensor, sT: Tensor, dims):
+    if dims is None:
+        return o, sT
+    Dk, Dv = dims
+    return o[..., :Dv], (sT[..., :Dk, :Dv] if sT is not None and sT.dim() >= 2 else sT)
+
+
 # -- Gated DeltaNet ------------------------------------------------------------------------
 def gated_delta_rule(q: Tensor, k: Tensor, v: Tensor, g: Tensor, beta: Tensor, *, scale: Optional[float] = None,
                      initial_state: Optional[Tensor] = None, sp=None, chunk_size: int = 64,
                      use_qk_l2norm: bool = True, recurrent: bool = False) -> Tuple[Tensor, Tensor]:
     """Gated delta rule over ``q,k [B,T,H,Dk]``, ``v [B,T,H,Dv]``, ``g,beta [B,T,H]``.
     Returns ``(o [B,T,H,Dv], final_state [B,H,Dk,Dv] fp32)``."""
+    dims = None
+    if _lib.use_cuda_kernels(q, k, v) and not recurrent:
+        q, k, v, initial_state, scale, dims = _pad_to_kernel_width(q, k, v, initial_state, scale)
     if _lib.use_cuda_kernels(q, k, v):
         from . import cuda_ops
         core = cuda_ops.GDNCore(scale=scale, chunk_size=chunk_size, use_qk_l2norm=use_qk_l2norm, recurrent=recurrent)
@@ -47,7 +80,7 @@ def gated_delta_rule(q: Tensor, k: Tensor, v: Tensor, g: Tensor, beta: Tensor, *
     core.matrix_transition, core.value_input = True, 2       # S_out = A S_in + S_local with A from (k, beta, g) only
     state = None if initial_state is None else (initial_state,)
     o, (sT,) = ssm_scan(core, [q, k, v, g, beta], state, sp)
-    return o, sT
+    return _unpad(o, sT, dims)
 
 
 # -- plain gated linear attention ------------------------------------------------------------
@@ -60,7 +93,9 @@ def _gla_ref(q, k, v, g, beta=None, initial_state=None, scale=None, chunk_size=6
 def simple_gla(q: Tensor, k: Tensor, v: Tensor, g: Tensor, *, scale: Optional[float] = None,
                initial_state: Optional[Tensor] = None, sp=None, chunk_size: int = 64, recurrent: bool = False):
     """``S_t = e^{g_t} S_{t-1} + k_t v_t^T``, ``o_t = S_t^T q_t * scale``.  State ``[B,H,Dk,Dv]`` fp32."""
-    core = None
+    core, dims = None, None
+    if _lib.use_cuda_kernels(q, k, v) and not recurrent:
+        q, k, v, initial_state, scale, dims = _pad_to_kernel_width(q, k, v, initial_state, scale)
     if _lib.use_cuda_kernels(q, k, v) and not recurrent:
         from . import gdn_cuda
         if gdn_cuda.available():
@@ -71,7 +106,7 @@ def simple_gla(q: Tensor, k: Tensor, v: Tensor, g: Tensor, *, scale: Optional[fl
     core.scalar_transition, core.decay_input = True, 3       # S_out = e^{sum g} S_in + S_local: chain-free SP possible
     state = None if initial_state is None else (initial_state,)
     o, (sT,) = ssm_scan(core, [q, k, v, g, None], state, sp)
-    return o, sT
+    return _unpad(o, sT, dims)
 
 
 # -- Gated KalmaNet --------------------------------------------------------------------------

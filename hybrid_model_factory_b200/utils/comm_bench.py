@@ -117,6 +117,40 @@ def bench_gemm_ar():
         report(f"gemm+all-reduce M={M} N={N} K={K}/{n}", fused, base, 2.0 * M * N * Ks, (n - 1) * M * N * 2.0)
 
 
+def bench_gemm_rs_ag():
+    """GEMM -> reduce-scatter and all-gather -> GEMM (one kernel each) against F.linear + NCCL collectives."""
+    from ..ops.fused_comm import PeerAllGatherGemm, PeerGemmAllReduce
+    n, rank = dist.get_world_size(), dist.get_rank()
+    rs = PeerGemmAllReduce(dist.group.WORLD, max_m=256, max_n=4096)
+    ag = PeerAllGatherGemm(dist.group.WORLD, max_m=256, max_ks=4096, max_n=12288)
+    for M, N, K in ((64, 4096, 4096), (64, 4096, 12288), (256, 4096, 4096)):
+        Ks = K // n
+        x = torch.randn(M, Ks, device="cuda").bfloat16()
+        w = (torch.randn(N, Ks, device="cuda") * 0.02).bfloat16()
+        out = torch.empty(M, N // n, device="cuda", dtype=torch.bfloat16)
+
+        def nccl_rs():
+            y = F.linear(x, w)
+            dist.reduce_scatter_tensor(out, y.view(M, n, N // n).transpose(0, 1).contiguous())
+            return out
+        fused = timed_graph(lambda: rs.reduce_scatter(x, w))
+        base = timed_graph(nccl_rs)
+        # every rank reads the other ranks' bf16 partials of its own N / n columns once
+        report(f"gemm+reduce-scatter M={M} N={N} K={K}/{n}", fused, base, 2.0 * M * N * Ks, (n - 1) * M * (N // n) * 2.0)
+    for M, N, K in ((64, 12288, 4096), (64, 4096, 4096), (256, 12288, 4096)):
+        Ks, Nl = K // n, N // n
+        xs = torch.randn(M, Ks, device="cuda").bfloat16()
+        w = (torch.randn(Nl, K, device="cuda") * 0.02).bfloat16()
+        gathered = torch.empty(n, M, Ks, device="cuda", dtype=torch.bfloat16)
+
+        def nccl_ag():
+            dist.all_gather_into_tensor(gathered, xs)
+            return F.linear(gathered.permute(1, 0, 2).reshape(M, K), w)
+        fused = timed(lambda: ag(xs, w), iters=20, flush=False)
+        base = timed(nccl_ag, iters=20, flush=False)
+        report(f"all-gather+gemm M={M} N={N}/{n} K={K}", fused, base, 2.0 * M * Nl * K, (n - 1) * M * Ks * 2.0)
+
+
 def bench_cp_attn():
     from ..parallel.cp_attention import cp_attention
     from ..parallel.peer import enable_peer_kv
@@ -159,7 +193,7 @@ def bench_moe():
     report(f"MoE layer E={E} top-{k} T={T} Dm={Dm} F={Fi}, EP={n}", fused, base, flops, link)
 
 
-CASES = {"gemm_ar": bench_gemm_ar, "cp_attn": bench_cp_attn, "moe": bench_moe}
+CASES = {"gemm_ar": bench_gemm_ar, "gemm_rs_ag": bench_gemm_rs_ag, "cp_attn": bench_cp_attn, "moe": bench_moe}
 
 
 # -- one GPU: every "peer" address is one of this GPU's own buffers ---------------------------------------------------

@@ -104,6 +104,34 @@ def test_ssd_matches_reference():
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("P,N,H,G", [(64, 128, 8, 2), (128, 64, 4, 4), (32, 64, 4, 1)])
+def test_ssd_narrow_heads_forward_backward(P, N, H, G):
+    """Mamba2 shapes whose head_dim / d_state are not 128 (e.g. 64 heads x 64 with d_state 128 in groups): padded to
+    the kernel width, forward and backward against the fp32 chunked formulation."""
+    from hybrid_model_factory_b200.ops import _lib
+    B, T = 2, 520
+    x = torch.randn(B, T, H, P, device=DEV).bfloat16()
+    dt = torch.rand(B, T, H, device=DEV) * 0.3
+    A = -torch.rand(H, device=DEV)
+    Bm = (torch.randn(B, T, G, N, device=DEV) * 0.3).bfloat16()
+    Cm = (torch.randn(B, T, G, N, device=DEV) * 0.3).bfloat16()
+    h0 = torch.randn(B, H, P, N, device=DEV) * 0.1
+    xs, dts, Bs, Cs, hs = (t.clone().requires_grad_(True) for t in (x, dt, Bm, Cm, h0))
+    xr, dtr, Br, Cr, hr = (t.float().clone().requires_grad_(True) for t in (x, dt, Bm, Cm, h0))
+    before = _lib.launch_count()
+    y, s = mixers.ssd(xs, dts, A, Bs, Cs, None, initial_state=hs)
+    assert _lib.launch_count() > before, "the padded problem must run on the kernels"
+    yr, sr = R.ssd_chunk(xr, dtr, A, Br, Cr, None, initial_state=hr, chunk_size=64)
+    assert y.shape == (B, T, H, P) and s.shape == (B, H, P, N)
+    assert _rel(y, yr) < 3e-2 and _rel(s, sr) < 3e-2
+    dy, ds = torch.randn_like(yr), torch.randn_like(sr) * 0.1
+    torch.autograd.backward([y.float(), s], [dy, ds])
+    torch.autograd.backward([yr, sr], [dy, ds])
+    for a, b, name in ((xs, xr, "dx"), (dts, dtr, "ddt"), (Bs, Br, "dB"), (Cs, Cr, "dC"), (hs, hr, "dh0")):
+        assert _rel(a.grad, b.grad) < 6e-2, (name, _rel(a.grad, b.grad))
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("T,with_state,with_gate", [(256, False, True), (200, True, True), (128, True, False)])
 def test_gka_chebyshev_kernel_matches_fp32_formulation(T, with_state, with_gate):
     """The one-kernel Chebyshev solve (bf16 operands, fp32 accumulation) against the batched fp32 PyTorch solve."""
