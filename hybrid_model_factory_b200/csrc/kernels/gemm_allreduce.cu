@@ -20,6 +20,9 @@
 //     TMA over NVLink) after that rank's publication flag has been seen, so y = concat_r(x_r) . W^T needs no separate
 //     all-gather.  There is no cross-rank sum in this form (the reduction runs over this rank's own partial).
 //
+//   * NVLS (mc_part != null): in the reduction step one multimem.ld_reduce through the NVSwitch multicast mapping of
+//     the partial buffers replaces the `world` peer loads per 16 bytes (the sum happens inside the switch).
+//
 // Epochs come from device memory (`sync[0]`, advanced by the last CTA of each launch), so the kernel can be
 // replayed from a CUDA graph.  Partials are double-buffered by epoch parity: a rank can only be one launch
 // ahead of the slowest peer because it needs that peer's flags to finish a launch.
@@ -60,7 +63,47 @@ struct Params {
   const unsigned int* x_flags;      // x_flags[r] >= x_epoch once rank r has published its shard
   unsigned int x_epoch;
   int ag_world, ag_ks;              // ranks and K per rank of the gathered activations
+  const bf16* mc_part;              // NVLS form: the partial buffers through their NVSwitch multicast mapping (or null)
 };
+
+// One load that returns the sum over every rank's copy of 8 bf16 values (reduced inside NVSwitch, fp32 accumulation).
+__device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const bf16* mc_addr) {
+  uint4 r;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+               : "l"(mc_addr)
+               : "memory");
+  return r;
+}
+
+// NVLS variant of the tile reduction: the cross-rank sum is one multimem.ld_reduce per 16 bytes instead of `world`
+// peer loads; the K splits (separate partial buffers) are added here.
+__device__ __forceinline__ void reduce_tile_nvls(const Params& p, int et, int chunks, int ksp, int n0, unsigned parity,
+                                                 size_t split_elems, int y_col0) {
+  for (int c = et; c < chunks; c += 128) {
+    const int m = ksp + (c / (BN / 8)) * p.splits, cc = (c % (BN / 8)) * 8;
+    const size_t off = (size_t)m * p.N + n0 + cc;
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int sp = 0; sp < p.splits; ++sp) {
+      const uint4 u = multimem_ld_reduce_bf16x8(p.mc_part + (size_t)parity * p.part_stride + off + (size_t)sp * split_elems);
+      const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(h2[j]);
+        acc[2 * j] += f.x;
+        acc[2 * j + 1] += f.y;
+      }
+    }
+    uint4 o;
+    o.x = pack_bf16x2(acc[0], acc[1]);
+    o.y = pack_bf16x2(acc[2], acc[3]);
+    o.z = pack_bf16x2(acc[4], acc[5]);
+    o.w = pack_bf16x2(acc[6], acc[7]);
+    *reinterpret_cast<uint4*>(p.y + (size_t)m * p.ldy + (n0 - y_col0) + cc) = o;
+  }
+}
 
 // Rank-ordered sum of every (rank, split) partial of one tile.  Remote loads take microseconds, so they go out in
 // batches before the first use: 8 partials of CU chunks at a time.  The sums are still taken in (rank, split) order,
@@ -238,7 +281,9 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
     // few chunks per thread (many K splits): two at a time; a whole 64-row tile per CTA (8 ranks, no splits): four, so
     // the tile takes two rounds of remote latency instead of four
     const int y_col0 = p.mode == 1 ? p.rank * p.tiles_per_rank * BN : 0;
-    if (reduce_here) {
+    if (reduce_here && p.mc_part != nullptr) {
+      reduce_tile_nvls(p, et, chunks, ksp, n0, parity, split_elems, y_col0);
+    } else if (reduce_here) {
       if (chunks > 256) reduce_tile<4>(p, et, chunks, ksp, n0, parity, split_elems, y_col0);
       else reduce_tile<2>(p, et, chunks, ksp, n0, parity, split_elems, y_col0);
     }
@@ -272,7 +317,7 @@ static int launch_tp(const void* x, const void* w, void* y, int M, int N, int Ks
                      const unsigned long long* part_ptrs, const unsigned long long* flag_ptrs, unsigned int* sync,
                      long long part_stride, int max_tiles, int rank, int world, int splits, int mode,
                      const unsigned long long* x_ptrs, void* maps_dev, const unsigned int* x_flags,
-                     unsigned int x_epoch, int ag_world, cudaStream_t st) {
+                     unsigned int x_epoch, int ag_world, const void* mc_part, cudaStream_t st, int x_epoch_flags = 0) {
   const int Ktot = x_ptrs ? Ks * ag_world : Ks;
   HMF_REQUIRE(splits >= 1 && splits <= MAX_SPLIT && Ktot % (splits * BK) == 0,
               "tp gemm: %d K splits do not divide K=%d into multiples of 64", splits, Ktot);
@@ -298,7 +343,8 @@ static int launch_tp(const void* x, const void* w, void* y, int M, int N, int Ks
     for (int r = 0; r < ag_world; ++r)
       if ((rc = make_map_2d_bf16(&host_maps[r], reinterpret_cast<const void*>(x_ptrs[r]), M, Ks, ldx, Mpad, BK)) != HMF_OK)
         return rc;
-    HMF_CHECK_CUDA(cudaMemcpyAsync(maps_dev, host_maps, sizeof(CUtensorMap) * ag_world, cudaMemcpyHostToDevice, st));
+    if (!(x_epoch_flags & 1))
+      HMF_CHECK_CUDA(cudaMemcpyAsync(maps_dev, host_maps, sizeof(CUtensorMap) * ag_world, cudaMemcpyHostToDevice, st));
     tmX = host_maps[0];
     p.x_maps = reinterpret_cast<const CUtensorMap*>(maps_dev);
     p.x_flags = x_flags; p.x_epoch = x_epoch; p.ag_world = ag_world;
@@ -318,6 +364,7 @@ static int launch_tp(const void* x, const void* w, void* y, int M, int N, int Ks
   p.part_stride = part_stride;
   p.M = M; p.N = N; p.Ks = Ktot; p.Mpad = Mpad; p.rank = rank; p.world = world; p.splits = splits;
   p.mode = mode;
+  p.mc_part = (const bf16*)mc_part;
   p.tiles_per_rank = mode == 1 ? (N / BN) / world : N / BN;
   p.ldy = mode == 1 ? N / world : N;
   int cols = 32;
@@ -337,7 +384,19 @@ HMF_API int hmf_gemm_allreduce(const void* x, const void* w, void* y, int M, int
                                const unsigned long long* flag_ptrs, unsigned int* sync, long long part_stride,
                                int max_tiles, int rank, int world, int splits, cudaStream_t st) {
   return launch_tp(x, w, y, M, N, Ks, ldx, ldw, part_ptrs, flag_ptrs, sync, part_stride, max_tiles, rank, world, splits,
-                   0, nullptr, nullptr, nullptr, 0, 1, st);
+                   0, nullptr, nullptr, nullptr, 0, 1, nullptr, st);
+}
+
+// The all-reduce (mode 0) and reduce-scatter (mode 1) forms with the cross-rank sum done inside NVSwitch:
+// mc_part is the multicast address of the partial buffers (the same offset as part_ptrs[r] in every rank's buffer).
+HMF_API int hmf_gemm_reduce_nvls(const void* x, const void* w, void* y, int M, int N, int Ks, long long ldx,
+                                 long long ldw, const unsigned long long* part_ptrs,
+                                 const unsigned long long* flag_ptrs, unsigned int* sync, long long part_stride,
+                                 int max_tiles, int rank, int world, int splits, int mode, const void* mc_part,
+                                 cudaStream_t st) {
+  HMF_REQUIRE(mc_part != nullptr && (mode == 0 || mode == 1), "gemm_reduce_nvls: bad arguments");
+  return launch_tp(x, w, y, M, N, Ks, ldx, ldw, part_ptrs, flag_ptrs, sync, part_stride, max_tiles, rank, world, splits,
+                   mode, nullptr, nullptr, nullptr, 0, 1, mc_part, st);
 }
 
 // Row-parallel GEMM fused with a reduce-scatter over the output columns: y_shard [M, N / world] holds columns
@@ -347,19 +406,21 @@ HMF_API int hmf_gemm_reduce_scatter(const void* x, const void* w, void* y_shard,
                                     const unsigned long long* flag_ptrs, unsigned int* sync, long long part_stride,
                                     int max_tiles, int rank, int world, int splits, cudaStream_t st) {
   return launch_tp(x, w, y_shard, M, N, Ks, ldx, ldw, part_ptrs, flag_ptrs, sync, part_stride, max_tiles, rank, world,
-                   splits, 1, nullptr, nullptr, nullptr, 0, 1, st);
+                   splits, 1, nullptr, nullptr, nullptr, 0, 1, nullptr, st);
 }
 
 // All-gather fused into a column-parallel GEMM: y [M, N] = concat_r(x_r) [M, ag_world * Ks] . w [N, ag_world * Ks]^T,
 // where x_r [M, Ks] (row stride ldx) is rank r's shard at x_ptrs[r] (this process' mapping of the symmetric buffers)
 // and x_flags[r] >= x_epoch (local flags) says that shard is complete.  maps_dev: ag_world * 128 bytes of 64-byte
 // aligned device scratch, untouched until the kernel has finished.  part / flag / sync buffers: LOCAL ones (world 1).
+// maps_ready != 0: maps_dev already holds the descriptors of exactly these shard addresses and sizes (a caller
+// that reuses its buffers can skip the host-to-device copy of the descriptors on every call after the first).
 HMF_API int hmf_allgather_gemm(const unsigned long long* x_ptrs, void* maps_dev, const unsigned int* x_flags,
                                unsigned int x_epoch, int ag_world, const void* w, void* y, int M, int N, int Ks,
                                long long ldx, long long ldw, const unsigned long long* part_ptrs,
                                const unsigned long long* flag_ptrs, unsigned int* sync, long long part_stride,
-                               int max_tiles, int splits, cudaStream_t st) {
+                               int max_tiles, int splits, int maps_ready, cudaStream_t st) {
   HMF_REQUIRE(x_ptrs != nullptr, "allgather_gemm: null shard table");
   return launch_tp(nullptr, w, y, M, N, Ks, ldx, ldw, part_ptrs, flag_ptrs, sync, part_stride, max_tiles, 0, 1, splits,
-                   0, x_ptrs, maps_dev, x_flags, x_epoch, ag_world, st);
+                   0, x_ptrs, maps_dev, x_flags, x_epoch, ag_world, nullptr, st, maps_ready ? 1 : 0);
 }

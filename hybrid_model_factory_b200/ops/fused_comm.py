@@ -43,11 +43,17 @@ class PeerGemmAllReduce:
             self.local = torch.zeros(part_bytes + flag_bytes, dtype=torch.uint8, device=dev)
             self.rank, self.world = 0, 1
             bases = [self.local.data_ptr()]
+            self.mc_part = 0
         else:
             self.ws = SymmetricWorkspace(part_bytes + flag_bytes, group, device)
             self.rank, self.world = self.ws.rank, self.ws.world
             dev = self.ws.device
             bases = [self.ws.peer_ptr(r, 0) for r in range(self.world)]
+            self.mc_part = self.ws.multicast_ptr          # the partial buffers start at offset 0 of the workspace
+        # NVLS reduction (multimem.ld_reduce inside the kernel) when the buffers have a multicast mapping and
+        # HMF_TP_NVLS=1; the peer-load reduction (bit-identical on every rank) otherwise
+        import os
+        self.use_nvls = bool(self.mc_part) and os.environ.get("HMF_TP_NVLS", "0") == "1"
         assert self.world <= self.MAX_WORLD
         pad = [0] * (self.MAX_WORLD - self.world)
         self.part_ptrs = arr(*bases, *pad)
@@ -72,11 +78,24 @@ class PeerGemmAllReduce:
         while (splits < self.MAX_SPLIT and tiles * splits * 2 <= 148 and Ks % (splits * 2 * 64) == 0
                and Ks // (splits * 2) >= 256 and self.world * splits * 2 <= 8):
             splits *= 2
+        if self.use_nvls:
+            return self._nvls(x, weight, y, splits, 0)
         _lib.check(_lib.kernels().hmf_gemm_allreduce(
             _lib.ptr(x), _lib.ptr(weight), _lib.ptr(y), c_int(M), c_int(N), c_int(Ks), c_ll(x.stride(0)),
             c_ll(weight.stride(0)), self.part_ptrs, self.flag_ptrs, _lib.ptr(self.sync), c_ll(self.part_stride),
             c_int(self.max_tiles), c_int(self.rank), c_int(self.world), c_int(splits), _lib.stream_ptr(x.device)),
             "gemm_allreduce")
+        self.calls += 1
+        return y
+
+    def _nvls(self, x, weight, y, splits: int, mode: int) -> torch.Tensor:
+        M, Ks = x.shape
+        N = weight.shape[0]
+        _lib.check(_lib.kernels().hmf_gemm_reduce_nvls(
+            _lib.ptr(x), _lib.ptr(weight), _lib.ptr(y), c_int(M), c_int(N), c_int(Ks), c_ll(x.stride(0)),
+            c_ll(weight.stride(0)), self.part_ptrs, self.flag_ptrs, _lib.ptr(self.sync), c_ll(self.part_stride),
+            c_int(self.max_tiles), c_int(self.rank), c_int(self.world), c_int(splits), c_int(mode),
+            ctypes.c_void_p(self.mc_part), _lib.stream_ptr(x.device)), "gemm_reduce_nvls")
         self.calls += 1
         return y
 
@@ -93,6 +112,8 @@ class PeerGemmAllReduce:
         N = weight.shape[0]
         assert (N // 128) % self.world == 0, "reduce-scatter needs N / 128 tiles divisible by the number of ranks"
         y = torch.empty(M, N // self.world, device=x.device, dtype=torch.bfloat16)
+        if self.use_nvls:
+            return self._nvls(x, weight, y, self._splits(N, Ks), 1)
         _lib.check(_lib.kernels().hmf_gemm_reduce_scatter(
             _lib.ptr(x), _lib.ptr(weight), _lib.ptr(y), c_int(M), c_int(N), c_int(Ks), c_ll(x.stride(0)),
             c_ll(weight.stride(0)), self.part_ptrs, self.flag_ptrs, _lib.ptr(self.sync), c_ll(self.part_stride),
@@ -124,7 +145,9 @@ class PeerAllGatherGemm:
         self.flag_ptrs_dev = torch.tensor([self.ws.peer_ptr(r, self.off_flags) for r in range(self.world)],
                                           dtype=torch.int64, device=dev)
         self.local = PeerGemmAllReduce(None, max_m, max_n, dev)       # partial / flag scratch of the 1-rank reduction
-        self.maps = torch.empty(8 * self.MAX_WORLD * 128 + 64, dtype=torch.uint8, device=dev)
+        self.max_slots = 16
+        self.maps = torch.empty(self.max_slots * self.MAX_WORLD * 128 + 64, dtype=torch.uint8, device=dev)
+        self._slots = {}            # (M, Ks, parity) -> descriptor slot that already holds the maps of that shape
         self.epoch = 0
         self.calls = 0
 
@@ -144,12 +167,20 @@ class PeerAllGatherGemm:
         arr = ctypes.c_ulonglong * self.MAX_WORLD
         x_ptrs = arr(*[self.ws.peer_ptr(r, par * self.shard_bytes) for r in range(self.world)],
                      *([0] * (self.MAX_WORLD - self.world)))
-        slot = (self.maps.data_ptr() + 63) // 64 * 64 + (self.calls % 8) * self.MAX_WORLD * 128
+        key = (M, Ks, par)
+        ready = key in self._slots
+        if not ready:
+            if len(self._slots) >= self.max_slots:
+                torch.cuda.current_stream(x_shard.device).synchronize()     # no kernel still reads the old descriptors
+                self._slots.clear()
+            self._slots[key] = len(self._slots)
+        slot = (self.maps.data_ptr() + 63) // 64 * 64 + self._slots[key] * self.MAX_WORLD * 128
         y = torch.empty(M, N, device=x_shard.device, dtype=torch.bfloat16)
         lo = self.local
         _lib.check(K.hmf_allgather_gemm(x_ptrs, ctypes.c_void_p(slot), _lib.ptr(self.flags), ctypes.c_uint(self.epoch),
                                         c_int(self.world), _lib.ptr(weight), _lib.ptr(y), c_int(M), c_int(N), c_int(Ks),
                                         c_ll(Ks), c_ll(weight.stride(0)), lo.part_ptrs, lo.flag_ptrs, _lib.ptr(lo.sync),
-                                        c_ll(lo.part_stride), c_int(lo.max_tiles), c_int(1), st), "allgather_gemm")
+                                        c_ll(lo.part_stride), c_int(lo.max_tiles), c_int(1), c_int(int(ready)), st),
+                   "allgather_gemm")
         self.calls += 1
         return y

@@ -41,6 +41,7 @@ class SymmetricWorkspace:
             self.handle, self.rank, self.world = None, 0, 1
             self.ptrs = [self.buffer.data_ptr()]
             self.nbytes = nbytes
+            self.multicast_ptr = 0
             return
         import torch.distributed._symmetric_memory as symm_mem
         self.buffer = symm_mem.empty(nbytes, dtype=torch.uint8, device=self.device)
@@ -48,6 +49,11 @@ class SymmetricWorkspace:
         self.rank, self.world = self.handle.rank, self.handle.world_size
         self.ptrs: List[int] = [int(p) for p in self.handle.buffer_ptrs]
         self.nbytes = nbytes
+        # address of the same buffer through its NVSwitch multicast object (0 where NVLS is not available)
+        try:
+            self.multicast_ptr = int(getattr(self.handle, "multicast_ptr", 0) or 0)
+        except Exception:
+            self.multicast_ptr = 0
         self.buffer.zero_()
         torch.cuda.synchronize(self.device)
         dist.barrier(group=group)

@@ -123,6 +123,9 @@ def bench_gemm_rs_ag():
     n, rank = dist.get_world_size(), dist.get_rank()
     rs = PeerGemmAllReduce(dist.group.WORLD, max_m=256, max_n=4096)
     ag = PeerAllGatherGemm(dist.group.WORLD, max_m=256, max_ks=4096, max_n=12288)
+    os.environ["HMF_TP_NVLS"] = "1"
+    nv = PeerGemmAllReduce(dist.group.WORLD, max_m=256, max_n=4096)
+    os.environ["HMF_TP_NVLS"] = "0"
     for M, N, K in ((64, 4096, 4096), (64, 4096, 12288), (256, 4096, 4096)):
         Ks = K // n
         x = torch.randn(M, Ks, device="cuda").bfloat16()
@@ -135,6 +138,12 @@ def bench_gemm_rs_ag():
             return out
         fused = timed_graph(lambda: rs.reduce_scatter(x, w))
         base = timed_graph(nccl_rs)
+        if nv.use_nvls:
+            t_nv = timed_graph(lambda: nv(x, w))
+            t_nvrs = timed_graph(lambda: nv.reduce_scatter(x, w))
+            if rank == 0:
+                print(f"  NVLS (multimem.ld_reduce) M={M} N={N} K={K}/{n}: all-reduce {t_nv * 1e3:.1f} us, "
+                      f"reduce-scatter {t_nvrs * 1e3:.1f} us", flush=True)
         # every rank reads the other ranks' bf16 partials of its own N / n columns once
         report(f"gemm+reduce-scatter M={M} N={N} K={K}/{n}", fused, base, 2.0 * M * N * Ks, (n - 1) * M * (N // n) * 2.0)
     for M, N, K in ((64, 12288, 4096), (64, 4096, 4096), (256, 12288, 4096)):

@@ -104,6 +104,25 @@ def bench_gemm_step(args):
                   f"({fl / b / 1e9:.0f} TFLOP/s)  own/cuBLAS time {a / b:.2f}", flush=True)
 
 
+def bench_gemm_fp8(args):
+    """Row-wise scaled float8 GEMM and its quantisers against the bf16 CTA-pair GEMM, layer shapes at ``--seq`` tokens."""
+    from ..ops import fp8
+    from ..ops.gemm import gemm
+    T = args.seq
+    for n_out, k_in in ((4096, 4096), (12288, 4096), (4096, 12288)):
+        x = torch.randn(T, k_in, device="cuda").bfloat16()
+        w = torch.randn(n_out, k_in, device="cuda").bfloat16()
+        xq, sx = fp8.quant_rows(x)
+        wq, sw = fp8.quant_rows(w)
+        a = time_fn(lambda: fp8.gemm_fp8(xq, sx, wq, sw), flush=False)
+        b = time_fn(lambda: gemm(x, w), flush=False)
+        q = time_fn(lambda: fp8.quant_rows(x), flush=False)
+        qt = time_fn(lambda: fp8.quant_cols_t(x), flush=False)
+        fl = 2.0 * T * n_out * k_in
+        print(f"fp8 gemm T={T} {k_in}->{n_out}: {a:.3f} ms ({fl / a / 1e9:.0f} TFLOP/s)  bf16 pair gemm {b:.3f} ms "
+              f"({fl / b / 1e9:.0f} TFLOP/s)  quant_rows(x) {q:.3f} ms  quant_cols_t(x) {qt:.3f} ms", flush=True)
+
+
 def _qkv(T, H, Hkv, D):
     q = torch.randn(1, T, H, D, device="cuda").bfloat16()
     k = torch.randn(1, T, Hkv, D, device="cuda").bfloat16()
@@ -237,7 +256,7 @@ def bench_paged_decode(args):
                bytes_=2.0 * Rn * L * Hkv * D * 2)
 
 
-CASES = {"gemm_step": bench_gemm_step, "gka_cheb": bench_gka_cheb, "paged_decode": bench_paged_decode, "gemm": bench_gemm, "attention_fwd": bench_attention_fwd, "attention_bwd": bench_attention_bwd,
+CASES = {"gemm_step": bench_gemm_step, "gemm_fp8": bench_gemm_fp8, "gka_cheb": bench_gka_cheb, "paged_decode": bench_paged_decode, "gemm": bench_gemm, "attention_fwd": bench_attention_fwd, "attention_bwd": bench_attention_bwd,
          "gdn_fwd": bench_gdn_fwd, "gdn_fwd_bwd": bench_gdn_fwd_bwd, "rmsnorm": bench_rmsnorm, "swiglu": bench_swiglu,
          "conv1d": bench_conv1d}
 

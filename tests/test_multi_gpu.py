@@ -142,6 +142,22 @@ def _tp_rs_ag_worker(rank, world):
         dist.all_gather(xs, x)
         refa = F.linear(torch.cat(xs, dim=1), wa).float()
         assert (ya.float() - refa).abs().max() < 3e-2 * refa.abs().max() + 1e-2, ("ag", it)
+    # the same reductions through the NVSwitch multicast mapping (multimem.ld_reduce), where the buffers have one
+    import os
+    os.environ["HMF_TP_NVLS"] = "1"
+    nv = PeerGemmAllReduce(dist.group.WORLD, max_m=256, max_n=4096, device=dev)
+    os.environ["HMF_TP_NVLS"] = "0"
+    if nv.use_nvls:
+        for M, N, Ks in ((64, 1024 * world, 512), (200, 256 * world, 320)):
+            x = torch.randn(M, Ks, generator=g).bfloat16().to(dev)
+            w = (torch.randn(N, Ks, generator=g) * 0.05).bfloat16().to(dev)
+            full = F.linear(x, w).float()
+            dist.all_reduce(full)
+            y = nv(x, w)
+            assert (y.float() - full).abs().max() < 3e-2 * full.abs().max() + 1e-2, "nvls all-reduce"
+            ys = nv.reduce_scatter(x, w)
+            ref = full[:, rank * (N // world):(rank + 1) * (N // world)]
+            assert (ys.float() - ref).abs().max() < 3e-2 * full.abs().max() + 1e-2, "nvls reduce-scatter"
     torch.cuda.synchronize()
     _lib.assert_status_ok()
     dist.barrier()
