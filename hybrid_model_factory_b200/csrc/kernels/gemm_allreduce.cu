@@ -64,6 +64,8 @@ struct Params {
   unsigned int x_epoch;
   int ag_world, ag_ks;              // ranks and K per rank of the gathered activations
   const bf16* mc_part;              // NVLS form: the partial buffers through their NVSwitch multicast mapping (or null)
+  const bf16* bias;                 // [N] added to the result (or null)
+  int direct;                       // one rank, one K split: the accumulator goes straight to y (no partial, no flags)
 };
 
 // One load that returns the sum over every rank's copy of 8 bf16 values (reduced inside NVSwitch, fp32 accumulation).
@@ -159,6 +161,11 @@ __device__ __forceinline__ void reduce_tile(const Params& p, int et, int chunks,
 #pragma unroll
     for (int q = 0; q < CU; ++q) {
       if (c0 + q * 128 < chunks) {
+        if (p.bias != nullptr) {
+          const int cc = ((c0 + q * 128) % (BN / 8)) * 8;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[q][j] += __bfloat162float(p.bias[n0 + cc + j]);
+        }
         uint4 o;
         o.x = pack_bf16x2(acc[q][0], acc[q][1]);
         o.y = pack_bf16x2(acc[q][2], acc[q][3]);
@@ -257,6 +264,18 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
     bf16* mine = p.part[p.rank] + (size_t)parity * p.part_stride + (size_t)ksp * split_elems;
     mbar_wait(acc_done, 0, ctx, 0x30);
     tc_fence_after();
+    if (p.direct) {
+      // single-GPU skinny GEMM: thread = output column, a warp writes 32 consecutive columns of one row per store
+      const float bv = p.bias != nullptr ? __bfloat162float(p.bias[n0 + row]) : 0.f;
+      for (int m0 = 0; m0 < p.Mpad; m0 += 16) {
+        uint32_t v[16];
+        tmem_ld_x16(tmem_base + lane_bits + m0, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+          if (m0 + j < p.M) p.y[(size_t)(m0 + j) * p.ldy + n0 + row] = __float2bfloat16(__uint_as_float(v[j]) + bv);
+      }
+    } else {
     for (int m0 = 0; m0 < p.Mpad; m0 += 16) {
       uint32_t v[16];
       tmem_ld_x16(tmem_base + lane_bits + m0, v);
@@ -287,6 +306,7 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
       if (chunks > 256) reduce_tile<4>(p, et, chunks, ksp, n0, parity, split_elems, y_col0);
       else reduce_tile<2>(p, et, chunks, ksp, n0, parity, split_elems, y_col0);
     }
+    }  // !direct
   }
 
   tc_fence_before();
@@ -296,7 +316,7 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
     tmem_dealloc(tmem_base, p.tmem_cols);
   }
   // the last CTA of the launch publishes the epoch for the next launch
-  if (threadIdx.x == 0) {
+  if (threadIdx.x == 0 && !p.direct) {
     __threadfence();
     const unsigned int ticket = atomicAdd(p.sync + 1, 1u);
     if (ticket == gridDim.x - 1) {
@@ -317,15 +337,18 @@ static int launch_tp(const void* x, const void* w, void* y, int M, int N, int Ks
                      const unsigned long long* part_ptrs, const unsigned long long* flag_ptrs, unsigned int* sync,
                      long long part_stride, int max_tiles, int rank, int world, int splits, int mode,
                      const unsigned long long* x_ptrs, void* maps_dev, const unsigned int* x_flags,
-                     unsigned int x_epoch, int ag_world, const void* mc_part, cudaStream_t st, int x_epoch_flags = 0) {
+                     unsigned int x_epoch, int ag_world, const void* mc_part, cudaStream_t st, int x_epoch_flags = 0,
+                     const void* bias = nullptr) {
   const int Ktot = x_ptrs ? Ks * ag_world : Ks;
   HMF_REQUIRE(splits >= 1 && splits <= MAX_SPLIT && Ktot % (splits * BK) == 0,
               "tp gemm: %d K splits do not divide K=%d into multiples of 64", splits, Ktot);
   HMF_REQUIRE(M >= 1 && M <= MAX_M, "tp gemm: M=%d out of range (1..%d)", M, MAX_M);
   HMF_REQUIRE(N % BN == 0 && Ks % BK == 0 && Ks > 0, "tp gemm: N=%d must be a multiple of 128, Ks=%d of 64", N, Ks);
   HMF_REQUIRE(world >= 1 && world <= MAX_WORLD && rank >= 0 && rank < world, "tp gemm: bad rank %d / world %d", rank, world);
-  HMF_REQUIRE(N / BN <= max_tiles, "tp gemm: %d tiles exceed the flag array (%d)", N / BN, max_tiles);
-  HMF_REQUIRE((long long)M * N * splits <= part_stride, "tp gemm: partial buffer too small");
+  const bool direct = world == 1 && splits == 1 && mode == 0 && x_ptrs == nullptr && mc_part == nullptr;
+  HMF_REQUIRE(direct || N / BN <= max_tiles, "tp gemm: %d tiles exceed the flag array (%d)", N / BN, max_tiles);
+  HMF_REQUIRE(direct || (long long)M * N * splits <= part_stride, "tp gemm: partial buffer too small");
+  HMF_REQUIRE(bias == nullptr || mc_part == nullptr, "tp gemm: no bias in the NVLS form");
   HMF_REQUIRE(mode == 0 || (N / BN) % world == 0, "tp gemm: reduce-scatter needs N / 128 = %d tiles divisible by %d ranks",
               N / BN, world);
   CUtensorMap tmW, tmX;
@@ -365,6 +388,8 @@ static int launch_tp(const void* x, const void* w, void* y, int M, int N, int Ks
   p.M = M; p.N = N; p.Ks = Ktot; p.Mpad = Mpad; p.rank = rank; p.world = world; p.splits = splits;
   p.mode = mode;
   p.mc_part = (const bf16*)mc_part;
+  p.bias = (const bf16*)bias;
+  p.direct = direct ? 1 : 0;
   p.tiles_per_rank = mode == 1 ? (N / BN) / world : N / BN;
   p.ldy = mode == 1 ? N / world : N;
   int cols = 32;
@@ -397,6 +422,17 @@ HMF_API int hmf_gemm_reduce_nvls(const void* x, const void* w, void* y, int M, i
   HMF_REQUIRE(mc_part != nullptr && (mode == 0 || mode == 1), "gemm_reduce_nvls: bad arguments");
   return launch_tp(x, w, y, M, N, Ks, ldx, ldw, part_ptrs, flag_ptrs, sync, part_stride, max_tiles, rank, world, splits,
                    mode, nullptr, nullptr, nullptr, 0, 1, mc_part, st);
+}
+
+// Single-GPU skinny GEMM (decode-sized M <= 256): y [M, N] = x [M, K] . w [N, K]^T + bias, the swap-AB kernel above on
+// one rank.  splits == 1: the accumulator is stored straight to y.  splits > 1 (few 128-column tiles: K is split over
+// more SMs to stream the weight): the splits are summed through the LOCAL partial / flag buffers as in the
+// multi-rank forms; the grid must then fit on the device at once (the caller keeps tiles * splits <= the SM count).
+HMF_API int hmf_gemm_skinny(const void* x, const void* w, const void* bias, void* y, int M, int N, int K, long long ldx,
+                            long long ldw, const unsigned long long* part_ptrs, const unsigned long long* flag_ptrs,
+                            unsigned int* sync, long long part_stride, int max_tiles, int splits, cudaStream_t st) {
+  return launch_tp(x, w, y, M, N, K, ldx, ldw, part_ptrs, flag_ptrs, sync, part_stride, max_tiles, 0, 1, splits, 0,
+                   nullptr, nullptr, nullptr, 0, 1, nullptr, st, 0, bias);
 }
 
 // Row-parallel GEMM fused with a reduce-scatter over the output columns: y_shard [M, N / world] holds columns

@@ -14,6 +14,7 @@ from __future__ import annotations
 
 import ctypes
 import os
+from typing import Optional
 
 import torch
 import torch.nn.functional as F
@@ -77,9 +78,38 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False, b_mn_maj
 # ------------------------------------------------------------------------------------------------------
 # nn.Linear on the kernel above
 # ------------------------------------------------------------------------------------------------------
-# Below this many rows (decode steps) a 128-row tile is mostly padding and the weight read dominates: those calls stay
-# on the library GEMV-style kernels.
+# Below this many rows (decode steps) a 128-row tile is mostly padding and the weight read dominates: those calls go
+# to the swap-AB kernel (weight rows on the MMA M axis, the few activation rows on N, K split over more SMs when the
+# weight has few 128-row tiles), ``csrc/kernels/gemm_allreduce.cu`` on one rank.
 MIN_ROWS = 128
+_skinny_state = {}
+
+
+def _skinny_ok(x2: torch.Tensor, w: torch.Tensor) -> bool:
+    return (x2.is_cuda and x2.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.dim() == 2 and x2.dim() == 2
+            and 1 <= x2.shape[0] <= 256 and w.shape[0] % 128 == 0 and w.shape[1] % 64 == 0
+            and x2.shape[1] == w.shape[1] and w.stride(1) == 1 and w.stride(0) % 8 == 0 and w.data_ptr() % 16 == 0
+            and _lib.kernels_available() and os.environ.get("HMF_LINEAR", "own") == "own")
+
+
+def skinny_gemm(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``y [M, N] = x [M, K] w [N, K]^T + bias`` for ``M <= 256`` (decode batches) on the swap-AB tcgen05 kernel."""
+    from .fused_comm import PeerGemmAllReduce
+    x2 = _rows(x)
+    M, K = x2.shape
+    N = w.shape[0]
+    dev = x2.device
+    st = _skinny_state.get(dev.index)
+    if st is None:      # partial / flag scratch of the K-split reduction (unused when one split covers K)
+        st = _skinny_state[dev.index] = PeerGemmAllReduce(None, 256, 8192, dev)
+    splits = st._splits(N, K) if N <= st.max_n else 1
+    y = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+    c_int, c_ll = ctypes.c_int, ctypes.c_longlong
+    _lib.check(_lib.kernels().hmf_gemm_skinny(
+        _lib.ptr(x2), _lib.ptr(w), _lib.ptr(bias), _lib.ptr(y), c_int(M), c_int(N), c_int(K), c_ll(x2.stride(0)),
+        c_ll(w.stride(0)), st.part_ptrs, st.flag_ptrs, _lib.ptr(st.sync), c_ll(st.part_stride), c_int(st.max_tiles),
+        c_int(splits), _lib.stream_ptr(dev)), "gemm_skinny")
+    return y
 
 
 def _own_linear_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
@@ -128,6 +158,10 @@ def linear(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor | None = None) -> t
     """Drop-in for ``F.linear``: bf16 CUDA operands run on the library's own GEMM (set ``HMF_LINEAR=cublas`` to
     compare against the vendor library), everything else takes ``F.linear``."""
     if not _own_linear_ok(x, w):
+        if (x.is_cuda and x.dtype == torch.bfloat16 and x.numel() < MIN_ROWS * x.shape[-1] and x.numel() > 0
+                and not (torch.is_grad_enabled() and (x.requires_grad or w.requires_grad))
+                and (b is None or b.dtype == torch.bfloat16) and _skinny_ok(x.reshape(-1, x.shape[-1]), w)):
+            return skinny_gemm(x, w, b).view(*x.shape[:-1], w.shape[0])
         return F.linear(x, w, b)
     if torch.is_grad_enabled() and (x.requires_grad or w.requires_grad or (b is not None and b.requires_grad)):
         return _Linear.apply(x, w, b)

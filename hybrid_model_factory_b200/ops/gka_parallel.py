@@ -66,13 +66,10 @@ def _kernel_ok(q: Tensor, k: Tensor, gk: Optional[Tensor], chunk_size: int) -> b
 def _solve_kernel(q: Tensor, k: Tensor, gk: Optional[Tensor], states: Tensor, ridge_ratio: float, num_iter: int,
                   N: int) -> Tensor:
     """One CTA per (chunk, head); ``states [B,H,N+1,D,D]`` fp32 contiguous.  ``csrc/kernels/gka_cheb_tc.cu`` (tcgen05,
-    operands read from shared memory by the tensor core, accumulators in tensor memory) unless ``HMF_GKA_TC=0``
-    selects the warp-level MMA version ``csrc/kernels/gka_cheb.cu``."""
+    operands read from shared memory by the tensor core, accumulators in tensor memory)."""
     import ctypes
-    import os
     from . import _lib
-    fn = (_lib.kernels().hmf_gka_cheb_fwd_tc if os.environ.get("HMF_GKA_TC", "1") == "1"
-          else _lib.kernels().hmf_gka_cheb_fwd)
+    fn = _lib.kernels().hmf_gka_cheb_fwd_tc
     B, T, Hh, D = q.shape
     g = None if gk is None else gk.float().contiguous()
     states = states.contiguous()

@@ -22,12 +22,19 @@ from .engine import SamplingParams, ServingEngine
 class ControlChannel:
     """Rank 0 of a tensor-parallel server tells the other ranks what it is about to do: a small object broadcast on a
     gloo group before every engine step (new requests, stop).  The engine itself is deterministic given the same
-    request stream, so this is all the followers need to stay in lock-step."""
+    request stream, so this is all the followers need to stay in lock-step.
 
-    def __init__(self):
+    Rank 0 broadcasts at least every 50 ms, also when idle, so the channel doubles as a heartbeat: the group's
+    timeout (``HMF_TP_CONTROL_TIMEOUT_S``, default 120 s) ends a follower whose rank 0 has gone, and rank 0's send to
+    a follower that has gone fails the same way, instead of either side waiting for gloo's default half hour."""
+
+    def __init__(self, timeout_s: Optional[float] = None):
+        import datetime
+        import os
         import torch.distributed as dist
         self.dist = dist
-        self.group = dist.new_group(backend="gloo")
+        timeout_s = timeout_s or float(os.environ.get("HMF_TP_CONTROL_TIMEOUT_S", "120"))
+        self.group = dist.new_group(backend="gloo", timeout=datetime.timedelta(seconds=timeout_s))
         self.rank = dist.get_rank()
 
     def broadcast(self, msg=None):
@@ -37,7 +44,10 @@ class ControlChannel:
 
 
 def _params_to_dict(p: SamplingParams) -> dict:
-    return {k: getattr(p, k) for k in ("max_new_tokens", "temperature", "top_k", "eos_token_id", "ignore_eos")}
+    """Every field: a follower that sampled with other settings than rank 0 would pick other tokens, finish its
+    requests at other steps and leave the ranks' collectives unmatched."""
+    import dataclasses
+    return dataclasses.asdict(p)
 
 
 class EngineLoop:
@@ -134,7 +144,10 @@ def create_app(engine: ServingEngine, tokenizer, model_name: str = "hybrid", tem
 
     def params_from(body: dict) -> SamplingParams:
         return SamplingParams(max_new_tokens=int(body.get("max_tokens", 64)), temperature=float(body.get("temperature", 0.0)),
-                              top_k=int(body.get("top_k", 0)), eos_token_id=getattr(tokenizer, "eos_token_id", None),
+                              top_k=int(body.get("top_k", 0)), top_p=float(body.get("top_p", 1.0)),
+                              min_p=float(body.get("min_p", 0.0)),
+                              repetition_penalty=float(body.get("repetition_penalty", 1.0)),
+                              eos_token_id=getattr(tokenizer, "eos_token_id", None),
                               ignore_eos=bool(body.get("ignore_eos", False)))
 
     async def run(prompt_ids: List[int], body: dict, chat: bool):

@@ -28,6 +28,7 @@ from ..layers.gka import GatedKalmaNet
 from ..layers.mamba2 import Mamba2
 from ..ops import _lib
 from ..ops import functional as F_ops
+from ..ops import gemm as gemm_ops
 from ..ops import reference as R
 from .cache import ServingState, SlotCache
 from .scheduler import NativeScheduler, ScheduledSeq
@@ -478,7 +479,7 @@ class ServingEngine:
         c = self._layer_cache.setdefault(("mlp", i), {})
         if not c:
             c["w_gu"] = torch.cat([mlp.gate_proj.weight, mlp.up_proj.weight], dim=0).contiguous()
-        gu = F.linear(h, c["w_gu"])
+        gu = gemm_ops.linear(h, c["w_gu"])
         Fi = gu.shape[-1] // 2
         a = torch.empty(h.shape[0], Fi, device=h.device, dtype=h.dtype)
         _lib.check(_lib.kernels().hmf_swiglu_packed(_lib.ptr(gu), _lib.ptr(a), c_ll(h.shape[0]), c_int(Fi),
@@ -505,7 +506,7 @@ class ServingEngine:
                 c["w"] = torch.cat([mx.q_proj.weight, mx.k_proj.weight, mx.v_proj.weight], dim=0).contiguous()
                 c["b"] = (torch.cat([mx.q_proj.bias, mx.k_proj.bias, mx.v_proj.bias]).contiguous()
                           if mx.q_proj.bias is not None else None)
-            qkv = F.linear(h, c["w"], c["b"])
+            qkv = gemm_ops.linear(h, c["w"], c["b"])
             kc, vc = self.state.kv[i]
             q = torch.empty(Rn, mx.num_heads, mx.head_dim, device=h.device, dtype=h.dtype)
             qn = mx.q_norm
@@ -598,6 +599,36 @@ class ServingEngine:
         e["conv"][slots.long()] = new.to(e["conv"].dtype)
         return y
 
+    def _packed(self, key, mods):
+        """Several projections of the same input as ONE weight (rows concatenated, padded with zero rows to whole
+        128-row tiles so the decode GEMM kernel takes it; the reference merges the input projections of its serving
+        layers the same way, ``vllm-inference/src/primed_vllm/layers/gdn/primed_gdn_layer.py``).  The modules' own
+        weights become views of the packed tensor, so nothing is held twice.  ``{"w": None}`` when the modules are
+        not plain linears of one kind."""
+        c = self._layer_cache.get(key)
+        if c is None:
+            plain = all(isinstance(m, torch.nn.Linear) for m in mods)
+            if not plain or len({m.weight.dtype for m in mods}) != 1:
+                c = {"w": None}
+            else:
+                sizes = [m.weight.shape[0] for m in mods]
+                n = sum(sizes)
+                w0 = mods[0].weight
+                W = torch.zeros((n + 127) // 128 * 128, w0.shape[1], dtype=w0.dtype, device=w0.device)
+                torch.cat([m.weight.detach() for m in mods], dim=0, out=W[:n])
+                b = None
+                if any(m.bias is not None for m in mods):       # zero where a projection has no bias
+                    b = torch.zeros(W.shape[0], dtype=w0.dtype, device=w0.device)
+                off = 0
+                for m, sz in zip(mods, sizes):
+                    m.weight.data = W[off:off + sz]
+                    if m.bias is not None:
+                        b[off:off + sz] = m.bias.detach()
+                    off += sz
+                c = {"w": W, "b": b, "sizes": sizes}
+            self._layer_cache[key] = c
+        return c
+
     def _layer_consts(self, i, mixer):
         c = self._layer_cache.get(i)
         if c is None:
@@ -616,10 +647,24 @@ class ServingEngine:
     def _gdn_decode(self, i, mx: GatedDeltaNet, h, slots):
         Rn = h.shape[0]
         c = self._layer_consts(i, mx)
-        qkv = torch.cat([mx.q_proj(h), mx.k_proj(h), mx.v_proj(h)], dim=-1)
+        pk = {"w": None}
+        if mx.kv_proj_rank is None:
+            pk = self._packed(("in", i), [mx.q_proj, mx.k_proj, mx.v_proj, mx.gk_proj, mx.b_proj]
+                              + ([mx.g_proj] if mx.use_gate else []))
+        gate = None
+        if pk["w"] is not None:         # one GEMM for every projection of the layer input
+            z = gemm_ops.linear(h, pk["w"], pk["b"])
+            sz = pk["sizes"]
+            qkv = z[:, :sz[0] + sz[1] + sz[2]]
+            rest = torch.split(z[:, sz[0] + sz[1] + sz[2]:sum(sz)], sz[3:], dim=-1)
+            a_in, b_in = rest[0], rest[1]
+            gate = rest[2] if mx.use_gate else None
+        else:
+            qkv = torch.cat([mx.q_proj(h), mx.k_proj(h), mx.v_proj(h)], dim=-1)
+            a_in, b_in = mx.gk_proj(h), mx.b_proj(h)
         qkv = self._conv_update(i, qkv, c["w"], c["b"], slots)
         q, k, v = torch.split(qkv, [mx.query_dim, mx.key_dim, mx.value_dim], dim=-1)
-        g, beta = R.gdn_gating(mx.gk_proj(h), mx.b_proj(h), mx.A_log, mx.dt_bias, 2.0 if mx.allow_neg_eigval else 1.0)
+        g, beta = R.gdn_gating(a_in, b_in, mx.A_log, mx.dt_bias, 2.0 if mx.allow_neg_eigval else 1.0)
         H, D = mx.expanded_num_heads, mx.head_dim
         st = self.state.ssm[i]["state"]
         if self._cuda and D == 128 and h.dtype == torch.bfloat16 and mx.kv_proj_rank is None:
@@ -639,7 +684,7 @@ class ServingEngine:
             st[slots.long()] = sT
             o = o[:, 0].to(h.dtype)
         if mx.use_gate:
-            o = mx.o_norm(o, mx.g_proj(h).view(Rn, H, D))
+            o = mx.o_norm(o, (gate if gate is not None else mx.g_proj(h)).reshape(Rn, H, D))
         else:
             o = mx.o_norm(o)
         return self._row_linear(o.reshape(Rn, -1), mx.o_proj)
@@ -717,18 +762,33 @@ class ServingEngine:
         Rn = h.shape[0]
         c = self._layer_consts(i, mx)
         e = self.state.ssm[i]
-        parts = [mx.q_proj(h), mx.k_proj(h)] + ([mx.v_proj(h)] if mx.use_v_conv else [])
-        x = self._conv_update(i, torch.cat(parts, dim=-1), c["w"], c["b"], slots)
+        pk = {"w": None}
+        if mx.kv_proj_rank is None:
+            names = (["q_proj", "k_proj", "v_proj", "a_proj"] + (["b_proj"] if mx.use_beta_gate else [])
+                     + (["alpha_proj"] if mx.use_alpha_connection else []) + (["g_proj"] if mx.use_gate else []))
+            pk = self._packed(("in", i), [getattr(mx, n) for n in names])
+        pre = {}
+        if pk["w"] is not None:         # one GEMM for every projection of the layer input
+            z = gemm_ops.linear(h, pk["w"], pk["b"])
+            pre = dict(zip(names, torch.split(z[:, :sum(pk["sizes"])], pk["sizes"], dim=-1)))
+            nconv = pk["sizes"][0] + pk["sizes"][1] + (pk["sizes"][2] if mx.use_v_conv else 0)
+            parts = [pre["q_proj"], pre["k_proj"]] + ([pre["v_proj"]] if mx.use_v_conv else [])
+            xin = z[:, :nconv]
+        else:
+            parts = [mx.q_proj(h), mx.k_proj(h)] + ([mx.v_proj(h)] if mx.use_v_conv else [])
+            xin = torch.cat(parts, dim=-1)
+        proj = lambda n: pre[n] if n in pre else getattr(mx, n)(h)  # noqa: E731
+        x = self._conv_update(i, xin, c["w"], c["b"], slots)
         outs = torch.split(x, [p.shape[-1] for p in parts], dim=-1)
         q, k = outs[0], outs[1]
-        v = outs[2] if mx.use_v_conv else mx.v_proj(h)
+        v = outs[2] if mx.use_v_conv else proj("v_proj")
         D = mx.head_dim
         H = mx.expanded_num_heads
         if self._cuda and D == 128 and h.dtype == torch.bfloat16 and mx.kv_proj_rank is None:
             # fused kernel: norms, gates, covariance update, Chebyshev solve, GLA update and read-out
-            beta = torch.sigmoid(mx.b_proj(h)).float().contiguous() if mx.use_beta_gate else None
-            alpha = torch.sigmoid(mx.alpha_proj(h)).float().contiguous() if mx.use_alpha_connection else None
-            g = (-mx.A_log.float().exp() * F.softplus(mx.a_proj(h).float() + mx.dt_bias.float())).contiguous()
+            beta = torch.sigmoid(proj("b_proj")).float().contiguous() if mx.use_beta_gate else None
+            alpha = torch.sigmoid(proj("alpha_proj")).float().contiguous() if mx.use_alpha_connection else None
+            g = (-mx.A_log.float().exp() * F.softplus(proj("a_proj").float() + mx.dt_bias.float())).contiguous()
             qc, kc_, vc_ = q.contiguous(), k.contiguous(), v.contiguous()
             o = torch.empty(Rn, H, D, device=h.device, dtype=h.dtype)
             _lib.check(_lib.kernels().hmf_gka_decode(
@@ -737,7 +797,7 @@ class ServingEngine:
                 c_int(mx.num_q_heads), c_int(mx.num_k_heads), c_int(mx.num_v_heads), c_int(D), c_float(mx.gla_scale),
                 c_float(mx.ridge_strength), c_int(mx.num_iter), c_int(int(mx.use_forgetting_gate_kk)),
                 _lib.stream_ptr(h.device)), "gka_decode")
-            o = mx.o_norm(o, mx.g_proj(h).view(Rn, H, D)) if mx.use_gate else mx.o_norm(o)
+            o = mx.o_norm(o, proj("g_proj").reshape(Rn, H, D)) if mx.use_gate else mx.o_norm(o)
             return self._row_linear(o.reshape(Rn, -1), mx.o_proj)
         q = repeat_heads(q.reshape(Rn, 1, mx.num_q_heads, D), mx.num_q_groups)
         k, v = mx._expand_kv(k[:, None], v[:, None])
@@ -746,10 +806,10 @@ class ServingEngine:
         k = k.float() / (torch.linalg.vector_norm(k.float(), dim=-1, keepdim=True) + eps)
         v = v.float()
         if mx.use_beta_gate:
-            beta = torch.sigmoid(mx.b_proj(h)).float()[:, None]
+            beta = torch.sigmoid(proj("b_proj")).float()[:, None]
             k, v = (beta[..., None] + eps) * k, (beta[..., None] + eps) * v
-        alpha = torch.sigmoid(mx.alpha_proj(h)).float()[:, None] if mx.use_alpha_connection else None
-        g = (-mx.A_log.float().exp() * F.softplus(mx.a_proj(h).float() + mx.dt_bias.float()))[:, None]
+        alpha = torch.sigmoid(proj("alpha_proj")).float()[:, None] if mx.use_alpha_connection else None
+        g = (-mx.A_log.float().exp() * F.softplus(proj("a_proj").float() + mx.dt_bias.float()))[:, None]
         gk = g if mx.use_forgetting_gate_kk else None
         sl = slots.long()
         o, (h_kk, h_kv) = R.gka_forward(q, k, v, alpha, g, gk, scale=mx.gla_scale, ridge_ratio=mx.ridge_strength,
@@ -760,7 +820,7 @@ class ServingEngine:
         e["state"][sl] = h_kv
         o = o[:, 0].to(h.dtype)
         H = mx.expanded_num_heads
-        o = mx.o_norm(o, mx.g_proj(h).view(Rn, H, D)) if mx.use_gate else mx.o_norm(o)
+        o = mx.o_norm(o, proj("g_proj").reshape(Rn, H, D)) if mx.use_gate else mx.o_norm(o)
         return self._row_linear(o.reshape(Rn, -1), mx.o_proj)
 
     # -- metrics ---------------------------------------------------------------------------------------

@@ -69,6 +69,22 @@ def report(name, ms, flops=None, bytes_=None):
     print(line, flush=True)
 
 
+def bench_gemm_skinny(args):
+    """Decode-sized projections: the swap-AB kernel against the vendor library, weights cold in L2 (flushed between
+    iterations; the weight read is the algorithmic traffic)."""
+    import torch.nn.functional as F
+    from ..ops.gemm import skinny_gemm
+    for N, K in ((4096, 4096), (24576, 4096), (4096, 12288), (151936, 4096)):
+        w = (torch.randn(N, K, device="cuda") * 0.02).bfloat16()
+        for M in (1, 16, 64):
+            x = torch.randn(M, K, device="cuda").bfloat16()
+            ms = time_fn(lambda: skinny_gemm(x, w), iters=10)
+            ms_lib = time_fn(lambda: F.linear(x, w), iters=10)
+            report(f"skinny gemm M={M} N={N} K={K}", ms, bytes_=2.0 * N * K)
+            report(f"  library     M={M} N={N} K={K}", ms_lib, bytes_=2.0 * N * K)
+        del w
+
+
 def bench_gemm(args):
     from ..ops.gemm import gemm
     M = N = K = args.size
@@ -256,7 +272,7 @@ def bench_paged_decode(args):
                bytes_=2.0 * Rn * L * Hkv * D * 2)
 
 
-CASES = {"gemm_step": bench_gemm_step, "gemm_fp8": bench_gemm_fp8, "gka_cheb": bench_gka_cheb, "paged_decode": bench_paged_decode, "gemm": bench_gemm, "attention_fwd": bench_attention_fwd, "attention_bwd": bench_attention_bwd,
+CASES = {"gemm_skinny": bench_gemm_skinny, "gemm_step": bench_gemm_step, "gemm_fp8": bench_gemm_fp8, "gka_cheb": bench_gka_cheb, "paged_decode": bench_paged_decode, "gemm": bench_gemm, "attention_fwd": bench_attention_fwd, "attention_bwd": bench_attention_bwd,
          "gdn_fwd": bench_gdn_fwd, "gdn_fwd_bwd": bench_gdn_fwd_bwd, "rmsnorm": bench_rmsnorm, "swiglu": bench_swiglu,
          "conv1d": bench_conv1d}
 

@@ -302,3 +302,58 @@ def test_sp_model_chain_free_delta_rule(world):
     """Gated DeltaNet with the matrix-transition form of the chain-free state exchange on the GPU kernels."""
     run_ranks(_sp_model_worker, world, "*-GDN", "matrix", backend="nccl", timeout=300)
 
+
+
+def _tp_server_gpu_worker(rank, world):
+    """Tensor-parallel API server on two GPUs (bf16 kernels, CUDA-graph decode, fused GEMM + all-reduce): rank 0 serves
+    the routes in-process, rank 1 follows the broadcast request stream.  Every wait gives up: the control channel
+    after 60 s without a message, each route after 120 s, the device-side waits after their own limit."""
+    import asyncio
+    import json
+    from hybrid_model_factory_b200.data.formats import ByteTokenizer
+    from hybrid_model_factory_b200.models.configuration import HybridConfig
+    from hybrid_model_factory_b200.models.modeling_hybrid import build_model
+    from hybrid_model_factory_b200.ops import _lib
+    from hybrid_model_factory_b200.parallel.tp import TPContext, shard_model
+    from hybrid_model_factory_b200.serving import api_server as S
+    from hybrid_model_factory_b200.serving.engine import ServingEngine
+    dev = torch.device("cuda", rank)
+    torch.manual_seed(0)
+    cfg = HybridConfig("hybrid_qwen3", vocab_size=512, hidden_size=512, intermediate_size=1024, num_hidden_layers=2,
+                       num_attention_heads=4, num_key_value_heads=2, head_dim=128, hybrid_override_pattern="*-M2")
+    model = build_model(cfg).to(dev, torch.bfloat16).eval()
+    tok = ByteTokenizer()
+    prompts = ["hello there, this is a prompt", "tensor parallel serving"]
+    tp = TPContext(dist.group.WORLD)
+    tp.enable_fused_gemm(max_m=256, max_n=4096)
+    shard_model(model, tp)
+    control = S.ControlChannel(timeout_s=60)
+    eng = ServingEngine(model, block_size=64, num_blocks=64, max_num_seqs=4, max_num_batched_tokens=256, max_model_len=512,
+                        tp=tp)
+    # as `hmf serve` does: every rank captures its decode graphs on its main thread, at the same time
+    eng.warmup(512, every_length=True)
+    if rank != 0:
+        assert S.follow(eng, control) >= 8
+        return
+    app = S.create_app(eng, tok, model_name="tiny", control=control)
+    routes = {r.path: r.endpoint for r in app.routes if hasattr(r, "endpoint")}
+
+    async def scenario():
+        calls = [asyncio.wait_for(routes["/v1/completions"]({"prompt": p, "max_tokens": 8, "ignore_eos": True,
+                                                             "temperature": 0.7, "top_p": 0.9}), timeout=120)
+                 for p in prompts]
+        resps = await asyncio.gather(*calls)
+        return [json.loads(r.body)["usage"]["completion_tokens"] for r in resps]
+    try:
+        counts = asyncio.run(scenario())
+    finally:
+        app.state.loop_runner.stop = True
+        app.state.loop_runner.wake.set()
+        app.state.loop_runner.thread.join(timeout=20)
+    _lib.assert_status_ok()
+    assert counts == [8, 8] and eng.stats["graph_replays"] > 0
+
+
+@pytest.mark.multigpu(2)
+def test_tensor_parallel_api_server_two_gpus():
+    run_ranks(_tp_server_gpu_worker, 2, backend="nccl", timeout=240)
