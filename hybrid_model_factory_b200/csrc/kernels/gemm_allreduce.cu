@@ -36,14 +36,14 @@ using bf16 = __nv_bfloat16;
 
 constexpr int BN = 128;          // output columns (weight rows) per CTA = MMA M
 constexpr int BK = 64;           // K per stage (one 128-byte swizzle atom)
-constexpr int STAGES = 4;
+constexpr int MAX_STAGES = 8;
 constexpr int A_BYTES = BN * BK * 2;             // 16 KB
 constexpr int MAX_M = 256;
-constexpr int B_BYTES = MAX_M * BK * 2;          // 32 KB (only Mpad rows are filled)
-constexpr int OFF_A = 0;
-constexpr int OFF_B = STAGES * A_BYTES;
-constexpr int OFF_BAR = OFF_B + STAGES * B_BYTES;
-constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
+// Shared memory per CTA: `stages` x (A tile 16 KB + B tile Mpad x 128 B rounded up to 1 KB) + barriers.  The ring is
+// sized by the launch: few activation rows leave room for a deeper ring AND a second CTA on the SM, whose prologue
+// and epilogue then overlap the other CTA's weight stream.
+constexpr int BAR_BYTES = 256;
+__host__ __device__ inline int b_stage_bytes(int Mpad) { return (Mpad * BK * 2 + 1023) / 1024 * 1024; }
 constexpr int MAX_WORLD = 8;
 constexpr int MAX_SPLIT = 4;
 constexpr int FLAGS_PER_TILE = MAX_WORLD * MAX_SPLIT;
@@ -66,6 +66,7 @@ struct Params {
   const bf16* mc_part;              // NVLS form: the partial buffers through their NVSwitch multicast mapping (or null)
   const bf16* bias;                 // [N] added to the result (or null)
   int direct;                       // one rank, one K split: the accumulator goes straight to y (no partial, no flags)
+  int stages, b_bytes;              // depth of the shared-memory ring, bytes of one B stage
 };
 
 // One load that returns the sum over every rank's copy of 8 bf16 values (reduced inside NVSwitch, fp32 accumulation).
@@ -177,15 +178,20 @@ __device__ __forceinline__ void reduce_tile(const Params& p, int et, int chunks,
   }
 }
 
-__global__ void __launch_bounds__(192, 1)
+// PAIR: two CTAs per SM (the single-GPU skinny GEMM: short ring, small reduction); otherwise one CTA per SM with
+// the full register budget for the batched remote loads of the cross-rank reduction.
+template <bool PAIR>
+__global__ void __launch_bounds__(192, PAIR ? 2 : 1)
 gemm_allreduce_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const Params p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int STAGES = p.stages, B_BYTES = p.b_bytes;
+  const int OFF_A = 0, OFF_B = STAGES * A_BYTES, OFF_BAR = OFF_B + STAGES * B_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
-  uint64_t* full = bars;                 // [STAGES]
-  uint64_t* empty = bars + STAGES;       // [STAGES]
-  uint64_t* acc_done = bars + 2 * STAGES;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 1);
+  uint64_t* full = bars;                 // [MAX_STAGES]
+  uint64_t* empty = bars + MAX_STAGES;   // [MAX_STAGES]
+  uint64_t* acc_done = bars + 2 * MAX_STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * MAX_STAGES + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const WaitCtx ctx{abort_flag, p.status};
@@ -303,8 +309,8 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
     if (reduce_here && p.mc_part != nullptr) {
       reduce_tile_nvls(p, et, chunks, ksp, n0, parity, split_elems, y_col0);
     } else if (reduce_here) {
-      if (chunks > 256) reduce_tile<4>(p, et, chunks, ksp, n0, parity, split_elems, y_col0);
-      else reduce_tile<2>(p, et, chunks, ksp, n0, parity, split_elems, y_col0);
+      if (!PAIR && chunks > 256) reduce_tile<4>(p, et, chunks, ksp, n0, parity, split_elems, y_col0);
+      else reduce_tile<PAIR ? 1 : 2>(p, et, chunks, ksp, n0, parity, split_elems, y_col0);
     }
     }  // !direct
   }
@@ -372,9 +378,19 @@ static int launch_tp(const void* x, const void* w, void* y, int M, int N, int Ks
     p.x_maps = reinterpret_cast<const CUtensorMap*>(maps_dev);
     p.x_flags = x_flags; p.x_epoch = x_epoch; p.ag_world = ag_world;
   }
+  // ring depth: as many stages as fit in half an SM's shared memory (two CTAs per SM), at least 3; a launch with many
+  // activation rows takes the whole SM with 4 stages
+  const int bst = b_stage_bytes(Mpad);
+  int stages = (100 * 1024 - BAR_BYTES - 1024) / (A_BYTES + bst);
+  if (stages > MAX_STAGES) stages = MAX_STAGES;
+  const bool pair = world == 1 && x_ptrs == nullptr && stages >= 3;
+  if (!pair) stages = 4;
+  const int smem_bytes = stages * (A_BYTES + bst) + BAR_BYTES + 1024;
   static bool configured = false;
   if (!configured) {
-    HMF_CHECK_CUDA(cudaFuncSetAttribute(gemm_allreduce_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    const int most = 4 * (A_BYTES + b_stage_bytes(MAX_M)) + BAR_BYTES + 1024;
+    HMF_CHECK_CUDA(cudaFuncSetAttribute(gemm_allreduce_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, most));
+    HMF_CHECK_CUDA(cudaFuncSetAttribute(gemm_allreduce_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, most));
     configured = true;
   }
   p.y = (bf16*)y;
@@ -390,12 +406,15 @@ static int launch_tp(const void* x, const void* w, void* y, int M, int N, int Ks
   p.mc_part = (const bf16*)mc_part;
   p.bias = (const bf16*)bias;
   p.direct = direct ? 1 : 0;
+  p.stages = stages;
+  p.b_bytes = bst;
   p.tiles_per_rank = mode == 1 ? (N / BN) / world : N / BN;
   p.ldy = mode == 1 ? N / world : N;
   int cols = 32;
   while (cols < Mpad) cols *= 2;
   p.tmem_cols = cols;
-  gemm_allreduce_kernel<<<(N / BN) * splits, 192, SMEM_BYTES, st>>>(tmW, tmX, p);
+  if (pair) gemm_allreduce_kernel<true><<<(N / BN) * splits, 192, smem_bytes, st>>>(tmW, tmX, p);
+  else gemm_allreduce_kernel<false><<<(N / BN) * splits, 192, smem_bytes, st>>>(tmW, tmX, p);
   HMF_CHECK_CUDA(cudaGetLastError());
   return HMF_OK;
 }

@@ -258,6 +258,9 @@ class HybridModel(nn.Module):
         self.rotary_emb = RotaryEmbedding(rot_dim, config.rope_theta, config.rope_scaling,
                                           config.max_position_embeddings)
         self.gradient_checkpointing = False
+        # indices of layers that keep their activations although checkpointing is on (they fit in memory: see
+        # `Trainer.plan_recompute`); every rank of a sequence-parallel group must hold the same set
+        self.checkpoint_skip = frozenset()
         self.sequence_parallel_group = None
 
     @staticmethod
@@ -292,17 +295,17 @@ class HybridModel(nn.Module):
         pos_emb = self.rotary_emb(position_ids)
         pos_emb = (pos_emb[0].to(h.dtype), pos_emb[1].to(h.dtype))
         router_logits = []
-        for layer in self.layers:
+        for li, layer in enumerate(self.layers):
             if isinstance(layer, FusedDecoderLayer):
                 h = layer(h, h, position_embeddings=pos_emb, position_ids=position_ids)[0]
                 continue
-            if self.gradient_checkpointing and self.training:
+            if self.gradient_checkpointing and self.training and li not in self.checkpoint_skip:
                 if layer.is_moe:
                     h, rl = layer_checkpoint(lambda a, c, s_, p_, _d, layer=layer: layer(a, (c, s_), p_, None, False),
-                                             h, pos_emb[0], pos_emb[1], position_ids, self._ckpt_anchor(h))
+                                             h, pos_emb[0], pos_emb[1], position_ids, self._ckpt_anchor(h), key=li)
                 else:
                     (h,) = layer_checkpoint(lambda a, c, s_, p_, _d, layer=layer: layer(a, (c, s_), p_, None, False)[0],
-                                            h, pos_emb[0], pos_emb[1], position_ids, self._ckpt_anchor(h))
+                                            h, pos_emb[0], pos_emb[1], position_ids, self._ckpt_anchor(h), key=li)
                     rl = None
             else:
                 h, rl = layer(h, position_embeddings=pos_emb, position_ids=position_ids,

@@ -61,6 +61,9 @@ class TrainingArguments:
     offload_optimizer: bool = False       # ZeRO-3 only: moments and master weights in pinned host memory
     offload_checkpoints: bool = False     # checkpointed layer inputs wait in pinned host memory until the backward pass
     mics_shard_size: int = 0              # ZeRO-3 only: shard inside groups of this many ranks, replicate across them
+    recompute_budget: str = "auto"        # auto: after the first step, layers whose activations fit in the free device
+    #                                       memory stop being checkpointed (no second forward for them); off: every
+    #                                       layer stays checkpointed; a number: fraction of the device memory to fill
 
     def to_dict(self):
         return asdict(self)
@@ -127,6 +130,8 @@ class Trainer:
                                        max_grad_norm=args.max_grad_norm, group=None, dp_size=self.dp_size,
                                        state_dtype=sdt, master_weights=args.master_weights)
         self.global_step = 0
+        self._recompute_planned = False
+        self.unchecked_layers: list = []
         self.status_check_steps = 50
         self.tokens_seen = 0
         self._t0 = time.time()
@@ -149,8 +154,50 @@ class Trainer:
                          labels_shifted=bool(batch.get("labels_shifted", self.sp is not None)), **extra)
         return out.loss
 
+    # -- which layers need no second forward ---------------------------------------------------------
+    def _core_with_layers(self):
+        for m in self.model.modules():
+            if hasattr(m, "checkpoint_skip") and hasattr(m, "layers"):
+                return m
+        return None
+
+    def _probe_wanted(self) -> bool:
+        core = self._core_with_layers()
+        return (not self._recompute_planned and str(self.args.recompute_budget) != "off" and core is not None
+                and getattr(core, "gradient_checkpointing", False) and self.device.type == "cuda"
+                and not self.args.offload_checkpoints)
+
+    def plan_recompute(self, sizes: dict, total_bytes: int, peak_bytes: int) -> list:
+        """Chooses the layers that run WITHOUT activation checkpointing from now on.  ``sizes``: bytes each layer's
+        autograd graph held during the first (fully checkpointed) step; ``peak_bytes``: that step's peak of live
+        memory.  The activations of the chosen layers must fit in what the step left free, with a margin for the
+        allocator's fragmentation; sharding over more ranks frees memory, so more layers qualify and the step loses
+        their second forward.  Every rank takes the same decision (smallest budget, largest sizes): a layer that one
+        rank re-runs and another does not would issue its collectives a different number of times."""
+        from ..utils.checkpointing import choose_unchecked_layers
+        frac = 0.90 if str(self.args.recompute_budget) == "auto" else float(self.args.recompute_budget)
+        budget = (frac * total_bytes - peak_bytes) * 0.8
+        keys = sorted(sizes)
+        if dist.is_initialized() and self.world > 1 and keys:
+            t = torch.tensor([-budget] + [float(sizes[k]) for k in keys], device=self.device, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            budget = -float(t[0])
+            sizes = {k: float(v) for k, v in zip(keys, t[1:].tolist())}
+        chosen = choose_unchecked_layers(sizes, budget)
+        core = self._core_with_layers()
+        if core is not None:
+            core.checkpoint_skip = frozenset(chosen)
+        self.unchecked_layers = chosen
+        self._recompute_planned = True
+        return chosen
+
     def train_step(self, batch: Dict[str, torch.Tensor]) -> torch.Tensor:
         self.model.train()
+        probing = self._probe_wanted()
+        if probing:
+            from ..utils import checkpointing
+            torch.cuda.reset_peak_memory_stats(self.device)
+            checkpointing.start_probe()
         ga = max(1, self.args.gradient_accumulation_steps)
         self.optimizer.zero_grad()
         dev = self._to_device(batch)
@@ -171,6 +218,11 @@ class Trainer:
         lr = get_lr(self.args.lr_scheduler_type, self.global_step, self.args.learning_rate, self.args.warmup_steps,
                     self.args.max_steps)
         self.optimizer.step(lr)
+        if probing:
+            sizes = checkpointing.stop_probe()
+            if self.plan_recompute(sizes, torch.cuda.mem_get_info(self.device)[1],
+                                   torch.cuda.max_memory_allocated(self.device)):
+                torch.cuda.empty_cache()        # the cached blocks were shaped by the fully checkpointed step
         self.global_step += 1
         self.tokens_seen += sum(int(v.numel()) for k, v in dev.items()
                                 if isinstance(v, torch.Tensor) and k.endswith("input_ids")) * self.world

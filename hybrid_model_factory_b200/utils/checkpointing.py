@@ -38,6 +38,28 @@ def _to_host(t: torch.Tensor):
     return t.detach().clone() if _offload["force_cpu_copy"] else None
 
 
+# Probe of what a layer's autograd graph holds: while on, the re-run of a checkpointed layer (the only time its graph
+# exists) records the growth of the allocator's live bytes under the layer's key.  The trainer uses the figures to
+# decide which layers fit in memory WITHOUT checkpointing (`train/trainer.py::Trainer.plan_recompute`).
+_probe = {"on": False, "sizes": {}, "mem_fn": None}
+
+
+def start_probe(mem_fn: Optional[Callable[[], int]] = None) -> None:
+    """``mem_fn`` returns the live bytes (default: ``torch.cuda.memory_allocated`` of the current device)."""
+    _probe.update(on=True, sizes={}, mem_fn=mem_fn)
+
+
+def stop_probe() -> dict:
+    _probe["on"] = False
+    return dict(_probe["sizes"])
+
+
+def _live_bytes() -> int:
+    if _probe["mem_fn"] is not None:
+        return int(_probe["mem_fn"]())
+    return int(torch.cuda.memory_allocated()) if torch.cuda.is_available() else 0
+
+
 def stash_for_write() -> Optional[List]:
     """List to append to while inside the first (graph-free) run of a checkpointed layer."""
     return getattr(_state, "write", None)
@@ -50,8 +72,9 @@ def stash_for_read() -> Optional[List]:
 
 class _LayerCheckpoint(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, fn: Callable, use_stash: bool, *args):
+    def forward(ctx, fn: Callable, use_stash: bool, key, *args):
         ctx.fn = fn
+        ctx.key = key
         tensors = [a for a in args if isinstance(a, torch.Tensor)]
         ctx.hosted = [(i, _to_host(t), t.device, t.requires_grad) for i, t in enumerate(tensors)]
         ctx.hosted = [h for h in ctx.hosted if h[1] is not None]
@@ -93,11 +116,15 @@ class _LayerCheckpoint(torch.autograd.Function):
                 args.append(non_tensor.pop(0))
         prev = getattr(_state, "read", None)
         _state.read = ctx.stash
+        probing = _probe["on"] and ctx.key is not None
+        before = _live_bytes() if probing else 0
         try:
             with torch.enable_grad():
                 out = ctx.fn(*args)
         finally:
             _state.read = prev
+        if probing:
+            _probe["sizes"][ctx.key] = max(_probe["sizes"].get(ctx.key, 0), _live_bytes() - before)
         outs = (out,) if isinstance(out, torch.Tensor) else tuple(out)
         pairs = [(o, g) for o, g, is_t in zip(outs, grads, ctx.out_is_tensor)
                  if is_t and o.requires_grad and g is not None]
@@ -112,10 +139,23 @@ class _LayerCheckpoint(torch.autograd.Function):
                 res.append(leaf.grad if leaf.requires_grad else None)
             else:
                 res.append(None)
-        return (None, None, *res)
+        return (None, None, None, *res)
 
 
-def layer_checkpoint(fn: Callable, *args, use_stash: bool = True):
-    """Checkpointed call of ``fn(*args)`` (tensor and non-tensor positional arguments)."""
-    out = _LayerCheckpoint.apply(fn, use_stash, *args)
+def layer_checkpoint(fn: Callable, *args, use_stash: bool = True, key=None):
+    """Checkpointed call of ``fn(*args)`` (tensor and non-tensor positional arguments).  ``key`` names the layer for the
+    activation-size probe."""
+    out = _LayerCheckpoint.apply(fn, use_stash, key, *args)
     return out
+
+
+def choose_unchecked_layers(sizes: dict, budget: float) -> List:
+    """Layers (keys of ``sizes``: bytes their graphs hold) to run without checkpointing so that the sum stays within
+    ``budget`` bytes: taken from the last layer backwards (their activations are the first to be freed again), skipping
+    what does not fit."""
+    chosen = []
+    for k in sorted(sizes, reverse=True):
+        if 0 < sizes[k] <= budget:
+            chosen.append(k)
+            budget -= sizes[k]
+    return sorted(chosen)

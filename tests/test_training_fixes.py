@@ -289,3 +289,44 @@ def test_plot_loss_writes_curves(tmp_path):
     files = [f for f in os.listdir(tmp_path / "run") if f.startswith("training_loss")]
     assert files and os.path.getsize(tmp_path / "run" / files[0]) > 200
     assert len(smooth([3.0, 2.0, 1.0])) == 3 and plot_loss(str(tmp_path / "nothing")) == []
+
+
+def test_recompute_plan_keeps_layers_that_fit(tmp_path):
+    """The activation probe records what each checkpointed layer's graph holds; the plan un-checkpoints layers from the
+    last one backwards while they fit, and the un-checkpointed model gives the same loss and gradients."""
+    import torch
+    from hybrid_model_factory_b200.models.configuration import HybridConfig
+    from hybrid_model_factory_b200.models.modeling_hybrid import build_model
+    from hybrid_model_factory_b200.train.trainer import Trainer, TrainingArguments
+    from hybrid_model_factory_b200.utils import checkpointing
+    torch.manual_seed(0)
+    cfg = HybridConfig("hybrid_qwen3", vocab_size=64, hidden_size=32, intermediate_size=64, num_hidden_layers=4,
+                       num_attention_heads=2, num_key_value_heads=1, head_dim=16, hybrid_override_pattern="*-GDN-*-M2")
+    model = build_model(cfg)
+    tr = Trainer(model, TrainingArguments(output_dir="", learning_rate=0.0, max_steps=4, logging_steps=0,
+                                          pure_bf16=False, bf16=False), device=torch.device("cpu"))
+    ids = torch.randint(0, 64, (2, 24))
+    batch = {"input_ids": ids, "labels": ids.clone()}
+    live = {"n": 0}
+
+    def fake_mem():            # every call reports 100 more bytes: each layer "holds" 100 bytes
+        live["n"] += 100
+        return live["n"]
+    checkpointing.start_probe(fake_mem)
+    model.train()
+    model(input_ids=ids, labels=ids).loss.backward()
+    sizes = checkpointing.stop_probe()
+    assert sorted(sizes) == [0, 1, 2, 3] and all(v == 100 for v in sizes.values())
+    g_ref = {n: p.grad.clone() for n, p in model.named_parameters() if p.grad is not None}
+    # room for two and a half layers: total 1000, peak 600 -> (0.9 * 1000 - 600) * 0.8 = 240
+    assert tr.plan_recompute(sizes, 1000, 600) == [2, 3]
+    assert model.model.checkpoint_skip == frozenset({2, 3})
+    model.zero_grad()
+    loss2 = model(input_ids=ids, labels=ids).loss
+    loss2.backward()
+    for n, p in model.named_parameters():
+        if n in g_ref:
+            assert torch.allclose(p.grad, g_ref[n], atol=1e-6), n
+    # a layer larger than the rest of the budget is passed over, smaller earlier ones still go in
+    assert checkpointing.choose_unchecked_layers({0: 50, 1: 500, 2: 100}, 160) == [0, 2]
+    assert tr.train_step(batch) is not None
