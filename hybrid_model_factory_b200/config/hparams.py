@@ -157,6 +157,11 @@ class FinetuningArguments:
     lora_rank: int = 8
     lora_alpha: Optional[int] = None
     lora_target: str = "all"
+    use_rslora: bool = False                   # scale alpha / sqrt(rank)
+    use_dora: bool = False                     # weight-decomposed LoRA (trainable row magnitudes)
+    pissa_init: bool = False                   # adapters start as the principal singular directions of the weight
+    pissa_iter: int = 16                       # power iterations of the randomised SVD (0: exact SVD)
+    shift_attn: bool = False                   # LongLoRA shifted sparse attention while training (groups of 1/4 length)
     freeze_trainable_layers: int = 2
     include_effective_tokens_per_second: bool = False
 

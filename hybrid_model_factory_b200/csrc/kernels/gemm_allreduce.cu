@@ -344,14 +344,16 @@ static int launch_tp(const void* x, const void* w, void* y, int M, int N, int Ks
                      long long part_stride, int max_tiles, int rank, int world, int splits, int mode,
                      const unsigned long long* x_ptrs, void* maps_dev, const unsigned int* x_flags,
                      unsigned int x_epoch, int ag_world, const void* mc_part, cudaStream_t st, int x_epoch_flags = 0,
-                     const void* bias = nullptr) {
+                     const void* bias = nullptr, bool allow_direct = false) {
   const int Ktot = x_ptrs ? Ks * ag_world : Ks;
   HMF_REQUIRE(splits >= 1 && splits <= MAX_SPLIT && Ktot % (splits * BK) == 0,
               "tp gemm: %d K splits do not divide K=%d into multiples of 64", splits, Ktot);
   HMF_REQUIRE(M >= 1 && M <= MAX_M, "tp gemm: M=%d out of range (1..%d)", M, MAX_M);
   HMF_REQUIRE(N % BN == 0 && Ks % BK == 0 && Ks > 0, "tp gemm: N=%d must be a multiple of 128, Ks=%d of 64", N, Ks);
   HMF_REQUIRE(world >= 1 && world <= MAX_WORLD && rank >= 0 && rank < world, "tp gemm: bad rank %d / world %d", rank, world);
-  const bool direct = world == 1 && splits == 1 && mode == 0 && x_ptrs == nullptr && mc_part == nullptr;
+  // only the plain single-GPU GEMM skips the partial / flag protocol; the tensor-parallel entry points keep it on one
+  // rank too (that is how the protocol is tested without peers)
+  const bool direct = allow_direct && world == 1 && splits == 1 && mode == 0 && x_ptrs == nullptr && mc_part == nullptr;
   HMF_REQUIRE(direct || N / BN <= max_tiles, "tp gemm: %d tiles exceed the flag array (%d)", N / BN, max_tiles);
   HMF_REQUIRE(direct || (long long)M * N * splits <= part_stride, "tp gemm: partial buffer too small");
   HMF_REQUIRE(bias == nullptr || mc_part == nullptr, "tp gemm: no bias in the NVLS form");
@@ -451,7 +453,7 @@ HMF_API int hmf_gemm_skinny(const void* x, const void* w, const void* bias, void
                             long long ldw, const unsigned long long* part_ptrs, const unsigned long long* flag_ptrs,
                             unsigned int* sync, long long part_stride, int max_tiles, int splits, cudaStream_t st) {
   return launch_tp(x, w, y, M, N, K, ldx, ldw, part_ptrs, flag_ptrs, sync, part_stride, max_tiles, 0, 1, splits, 0,
-                   nullptr, nullptr, nullptr, 0, 1, nullptr, st, 0, bias);
+                   nullptr, nullptr, nullptr, 0, 1, nullptr, st, 0, bias, true);
 }
 
 // Row-parallel GEMM fused with a reduce-scatter over the output columns: y_shard [M, N / world] holds columns

@@ -91,7 +91,17 @@ class Attention(nn.Module):
         else:
             if past_key_values is not None:
                 k, v = past_key_values.update_attention(self.layer_idx, k, v, window=self.sliding_window)
-            o = F_ops.attention(q, k, v, scale=self.scaling, causal=True, window=self.sliding_window)
+            ratio = getattr(self, "shift_group_ratio", None)
+            group = int(T * ratio) if (ratio and self.training and past_key_values is None) else 0
+            if group >= 2 and T % group == 0 and q.shape[2] % 2 == 0:
+                # LongLoRA: attention inside groups of `group` tokens, half of the heads on the half-shifted sequence
+                from ..layers.common import repeat_heads
+                from ..train.adapters import shift_attention
+                rep = q.shape[2] // k.shape[2]
+                o = shift_attention(q, repeat_heads(k, rep), repeat_heads(v, rep), group,
+                                    lambda a, b, c: F_ops.attention(a, b, c, scale=self.scaling, causal=True))
+            else:
+                o = F_ops.attention(q, k, v, scale=self.scaling, causal=True, window=self.sliding_window)
         o = o.reshape(B, T, -1)
         if gate is not None:
             o = o * torch.sigmoid(gate)

@@ -287,8 +287,6 @@ class HybridModel(nn.Module):
                     raise ValueError("packed samples (cu_seqlens) need a batch of one row; collate rows one by one")
                 cu = list(cu[0])
             kwargs["cu_seqlens"] = [int(c) for c in cu]
-            if self.gradient_checkpointing and self.training and len(cu) > 2:
-                raise ValueError("cu_seqlens with activation checkpointing is not supported; disable one of the two")
         if position_ids is None:
             off = past_key_values.seqlen_offset if past_key_values is not None else 0
             position_ids = torch.arange(off, off + T, device=h.device).expand(B, T)
@@ -300,12 +298,15 @@ class HybridModel(nn.Module):
                 h = layer(h, h, position_embeddings=pos_emb, position_ids=position_ids)[0]
                 continue
             if self.gradient_checkpointing and self.training and li not in self.checkpoint_skip:
+                pk = {"cu_seqlens": kwargs["cu_seqlens"]} if kwargs.get("cu_seqlens") is not None else {}
                 if layer.is_moe:
-                    h, rl = layer_checkpoint(lambda a, c, s_, p_, _d, layer=layer: layer(a, (c, s_), p_, None, False),
-                                             h, pos_emb[0], pos_emb[1], position_ids, self._ckpt_anchor(h), key=li)
+                    h, rl = layer_checkpoint(
+                        lambda a, c, s_, p_, _d, layer=layer, pk=pk: layer(a, (c, s_), p_, None, False, **pk),
+                        h, pos_emb[0], pos_emb[1], position_ids, self._ckpt_anchor(h), key=li)
                 else:
-                    (h,) = layer_checkpoint(lambda a, c, s_, p_, _d, layer=layer: layer(a, (c, s_), p_, None, False)[0],
-                                            h, pos_emb[0], pos_emb[1], position_ids, self._ckpt_anchor(h), key=li)
+                    (h,) = layer_checkpoint(
+                        lambda a, c, s_, p_, _d, layer=layer, pk=pk: layer(a, (c, s_), p_, None, False, **pk)[0],
+                        h, pos_emb[0], pos_emb[1], position_ids, self._ckpt_anchor(h), key=li)
                     rl = None
             else:
                 h, rl = layer(h, position_embeddings=pos_emb, position_ids=position_ids,

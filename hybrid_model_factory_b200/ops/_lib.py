@@ -108,7 +108,22 @@ def stream_ptr(device=None) -> ctypes.c_void_p:
 
 
 def ptr(t: torch.Tensor | None) -> ctypes.c_void_p:
-    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+    """Device address of ``t`` for a kernel argument.  The kernels read and write 16 bytes at a time, so a tensor of 16
+    bytes or more must start on a 16-byte boundary; a view that does not (a column slice of a one-row matrix counts as
+    contiguous and keeps its odd offset) is refused here, on the host, instead of faulting on the device."""
+    if t is None:
+        return ctypes.c_void_p(0)
+    p = t.data_ptr()
+    if (p & 15) and t.is_cuda and t.numel() * t.element_size() >= 16:
+        raise ValueError(f"tensor of shape {tuple(t.shape)} ({t.dtype}) starts at {p:#x}, not on a 16-byte boundary: "
+                         "clone the view before handing it to a kernel")
+    return ctypes.c_void_p(p)
+
+
+def aligned(t: torch.Tensor) -> torch.Tensor:
+    """``t`` made contiguous, and copied when its first element is not on a 16-byte boundary."""
+    t = t.contiguous()
+    return t.clone() if (t.data_ptr() & 15) else t
 
 
 def check(rc: int, what: str) -> None:

@@ -122,7 +122,7 @@ class _GatedNorm(torch.autograd.Function):
     def forward(ctx, x, gate, weight, eps, mode):
         shape = x.shape
         D = shape[-1]
-        x2, g2 = x.reshape(-1, D).contiguous(), gate.reshape(-1, D).contiguous()
+        x2, g2 = _lib.aligned(x.reshape(-1, D)), _lib.aligned(gate.reshape(-1, D))
         w = weight.contiguous()
         w_rows = 1 if w.dim() == 1 else w.shape[0]
         N = x2.shape[0]

@@ -603,29 +603,32 @@ class ServingEngine:
         """Several projections of the same input as ONE weight (rows concatenated, padded with zero rows to whole
         128-row tiles so the decode GEMM kernel takes it; the reference merges the input projections of its serving
         layers the same way, ``vllm-inference/src/primed_vllm/layers/gdn/primed_gdn_layer.py``).  The modules' own
-        weights become views of the packed tensor, so nothing is held twice.  ``{"w": None}`` when the modules are
-        not plain linears of one kind."""
+        weights become views of the packed tensor, so nothing is held twice.  Every projection starts at a multiple of
+        8 output columns: with one decoding request the slices of the product are handed to kernels as they are, and
+        those read 16 bytes at a time.  ``{"w": None}`` when the modules are not plain linears of one kind."""
         c = self._layer_cache.get(key)
         if c is None:
             plain = all(isinstance(m, torch.nn.Linear) for m in mods)
-            if not plain or len({m.weight.dtype for m in mods}) != 1:
+            if (not plain or len({m.weight.dtype for m in mods}) != 1
+                    or any(m.weight.shape[0] % 8 for m in mods[:3])):      # q, k, v are read as one contiguous block
                 c = {"w": None}
             else:
                 sizes = [m.weight.shape[0] for m in mods]
-                n = sum(sizes)
+                offs, n = [], 0
+                for sz in sizes:
+                    offs.append(n)
+                    n += (sz + 7) // 8 * 8
                 w0 = mods[0].weight
                 W = torch.zeros((n + 127) // 128 * 128, w0.shape[1], dtype=w0.dtype, device=w0.device)
-                torch.cat([m.weight.detach() for m in mods], dim=0, out=W[:n])
                 b = None
                 if any(m.bias is not None for m in mods):       # zero where a projection has no bias
                     b = torch.zeros(W.shape[0], dtype=w0.dtype, device=w0.device)
-                off = 0
-                for m, sz in zip(mods, sizes):
+                for m, sz, off in zip(mods, sizes, offs):
+                    W[off:off + sz].copy_(m.weight.detach())
                     m.weight.data = W[off:off + sz]
                     if m.bias is not None:
                         b[off:off + sz] = m.bias.detach()
-                    off += sz
-                c = {"w": W, "b": b, "sizes": sizes}
+                c = {"w": W, "b": b, "sizes": sizes, "offs": offs}
             self._layer_cache[key] = c
         return c
 
@@ -654,11 +657,11 @@ class ServingEngine:
         gate = None
         if pk["w"] is not None:         # one GEMM for every projection of the layer input
             z = gemm_ops.linear(h, pk["w"], pk["b"])
-            sz = pk["sizes"]
-            qkv = z[:, :sz[0] + sz[1] + sz[2]]
-            rest = torch.split(z[:, sz[0] + sz[1] + sz[2]:sum(sz)], sz[3:], dim=-1)
-            a_in, b_in = rest[0], rest[1]
-            gate = rest[2] if mx.use_gate else None
+            sz, of = pk["sizes"], pk["offs"]
+            part = [z[:, o:o + n_] for o, n_ in zip(of, sz)]
+            qkv = z[:, :sz[0] + sz[1] + sz[2]]          # q, k, v are multiples of 8 wide: no padding between them
+            a_in, b_in = part[3], part[4]
+            gate = part[5] if mx.use_gate else None
         else:
             qkv = torch.cat([mx.q_proj(h), mx.k_proj(h), mx.v_proj(h)], dim=-1)
             a_in, b_in = mx.gk_proj(h), mx.b_proj(h)
@@ -770,7 +773,7 @@ class ServingEngine:
         pre = {}
         if pk["w"] is not None:         # one GEMM for every projection of the layer input
             z = gemm_ops.linear(h, pk["w"], pk["b"])
-            pre = dict(zip(names, torch.split(z[:, :sum(pk["sizes"])], pk["sizes"], dim=-1)))
+            pre = {n_: z[:, o:o + sz_] for n_, o, sz_ in zip(names, pk["offs"], pk["sizes"])}
             nconv = pk["sizes"][0] + pk["sizes"][1] + (pk["sizes"][2] if mx.use_v_conv else 0)
             parts = [pre["q_proj"], pre["k_proj"]] + ([pre["v_proj"]] if mx.use_v_conv else [])
             xin = z[:, :nconv]

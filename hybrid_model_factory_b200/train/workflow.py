@@ -220,8 +220,18 @@ def run_exp(args: Optional[Any] = None) -> Trainer:
         info_rank0(logger, "trainable parameters: %d", n)
     if ft_args.finetuning_type == "lora":
         from .adapters import apply_lora
-        wrapped = apply_lora(model, ft_args.lora_rank, ft_args.lora_alpha, ft_args.lora_target)
+        wrapped = apply_lora(model, ft_args.lora_rank, ft_args.lora_alpha, ft_args.lora_target,
+                             use_rslora=ft_args.use_rslora, use_dora=ft_args.use_dora, pissa_init=ft_args.pissa_init,
+                             pissa_iter=ft_args.pissa_iter)
         info_rank0(logger, "LoRA adapters on %d linear layers", len(wrapped))
+    if getattr(ft_args, "shift_attn", False):
+        from ..layers.attention import Attention
+        n_shift = 0
+        for m in model.modules():
+            if isinstance(m, Attention) and m.sliding_window is None:
+                m.shift_group_ratio = 0.25
+                n_shift += 1
+        info_rank0(logger, "shifted sparse attention on %d attention layers", n_shift)
     elif ft_args.finetuning_type == "oft":
         from .patcher import add_oft
         wrapped = add_oft(model, tuple(t.strip() for t in ft_args.lora_target.split(",")), ft_args.oft_block_size)

@@ -629,3 +629,72 @@ def test_packed_sequences_do_not_see_each_other():
         mixed = model(batch["input_ids"], position_ids=batch["position_ids"], return_logits=True).logits
     assert torch.allclose(packed[0, :9], la[0], atol=2e-4) and torch.allclose(packed[0, 9:23], lb[0], atol=2e-4)
     assert not torch.allclose(mixed[0, 9:23], lb[0], atol=1e-3)          # without boundaries sample b sees sample a
+
+
+def test_lora_variants_dora_pissa_rslora():
+    import math
+    from hybrid_model_factory_b200.train.adapters import LoRALinear, apply_lora, merge_lora
+    torch.manual_seed(0)
+    base = torch.nn.Linear(24, 16, bias=False)
+    w0 = base.weight.detach().clone()
+    x = torch.randn(5, 24)
+    # PiSSA: same function at initialisation, but the adapter now carries the principal directions
+    pl = LoRALinear(torch.nn.Linear(24, 16, bias=False), 4, 8.0, pissa=True)
+    pl.base.weight.data.add_(0)       # (initialised from its own random weight)
+    full = pl.merged_weight()
+    U, S, Vh = torch.linalg.svd(full, full_matrices=False)
+    resid = pl.base.weight
+    assert torch.linalg.matrix_norm(resid, 2) <= S[4] * 1.001 + 1e-5          # top-4 directions moved to the adapter
+    # randomised variant agrees on the function too
+    lin = torch.nn.Linear(24, 16, bias=False)
+    y0 = lin(x)
+    pr = LoRALinear(lin, 4, 8.0, pissa=True, pissa_iters=8)
+    assert torch.allclose(pr(x), y0, atol=1e-4)
+    # DoRA: identical output at initialisation, magnitude and adapters train, merge reproduces the forward
+    base.weight.data.copy_(w0)
+    dl = LoRALinear(base, 4, 8.0, use_dora=True)
+    assert torch.allclose(dl(x), x @ w0.t(), atol=1e-5)
+    with torch.no_grad():
+        dl.lora_B.normal_(0, 0.1)
+        dl.magnitude.mul_(1.5)
+    y = dl(x)
+    y.sum().backward()
+    assert dl.magnitude.grad is not None and dl.lora_A.grad is not None and base.weight.grad is None
+    assert torch.allclose(x @ dl.merged_weight().t(), y, atol=1e-5)
+    assert torch.allclose(dl.merged_weight().norm(dim=1), dl.magnitude, atol=1e-5)
+    # rank-stabilised scaling
+    assert LoRALinear(torch.nn.Linear(8, 8), 16, 32.0, use_rslora=True).scaling == 32.0 / math.sqrt(16)
+    # through the model: wrap, perturb, merge -> plain linears with the same function
+    model = build_model(_cfg("*-GDN")).eval()
+    ids = torch.randint(0, 64, (1, 12))
+    wrapped = apply_lora(model, rank=2, use_dora=True, pissa_init=True, pissa_iter=0)
+    assert wrapped
+    ref = model(input_ids=ids).logits
+    assert merge_lora(model) == len(wrapped)
+    assert torch.allclose(model(input_ids=ids).logits, ref, atol=2e-4)
+
+
+def test_longlora_shift_attention():
+    from hybrid_model_factory_b200.ops import reference as R
+    from hybrid_model_factory_b200.train.adapters import shift_attention
+    torch.manual_seed(0)
+    B, T, H, D, G = 2, 16, 4, 8, 8
+    q, k, v = (torch.randn(B, T, H, D) for _ in range(3))
+    o = shift_attention(q, k, v, G, lambda a, b, c: R.attention(a, b, c, scale=D ** -0.5, causal=True))
+    # heads of the first half: plain causal attention inside each group of 8 tokens
+    for g0 in (0, 8):
+        exp = R.attention(q[:, g0:g0 + G, :2], k[:, g0:g0 + G, :2], v[:, g0:g0 + G, :2], scale=D ** -0.5, causal=True)
+        assert torch.allclose(o[:, g0:g0 + G, :2], exp, atol=1e-5)
+    # heads of the second half: groups start half a group later (tokens 4..11 form one group)
+    exp = R.attention(q[:, 4:12, 2:], k[:, 4:12, 2:], v[:, 4:12, 2:], scale=D ** -0.5, causal=True)
+    assert torch.allclose(o[:, 4:12, 2:], exp, atol=1e-5)
+    # wired into the attention layer while training
+    model = build_model(_cfg("*-*")).train()
+    for m in model.modules():
+        if type(m).__name__ == "Attention":
+            m.shift_group_ratio = 0.25
+    ids = torch.randint(0, 64, (1, 16))
+    a = model(input_ids=ids).logits
+    model.eval()
+    b = model(input_ids=ids).logits
+    assert a.shape == b.shape and not torch.allclose(a, b)        # grouped attention in training, full attention in eval
