@@ -248,6 +248,8 @@ def main():
                               "activations instead (they fit in the memory left free after the first step)"),
                           "sp_state_transport": transport,
                           "l2": "working set per step far exceeds the 126 MB L2 (no flush needed)"},
+               "memory_gib": {"peak_allocated": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1),
+                              "peak_reserved": round(torch.cuda.max_memory_reserved() / 2 ** 30, 1)},
                "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "phase_ms_per_step": phases, "kernel_status": list(status),
                "impl": "ours"}
         print(json.dumps(out), flush=True)

@@ -67,6 +67,7 @@ struct Params {
   const bf16* bias;                 // [N] added to the result (or null)
   int direct;                       // one rank, one K split: the accumulator goes straight to y (no partial, no flags)
   int stages, b_bytes;              // depth of the shared-memory ring, bytes of one B stage
+  int part_f32;                     // single-GPU K splits: the partials stay fp32 (the buffers hold half as many)
 };
 
 // One load that returns the sum over every rank's copy of 8 bf16 values (reduced inside NVSwitch, fp32 accumulation).
@@ -105,6 +106,33 @@ __device__ __forceinline__ void reduce_tile_nvls(const Params& p, int et, int ch
     o.z = pack_bf16x2(acc[4], acc[5]);
     o.w = pack_bf16x2(acc[6], acc[7]);
     *reinterpret_cast<uint4*>(p.y + (size_t)m * p.ldy + (n0 - y_col0) + cc) = o;
+  }
+}
+
+// Single-GPU K splits: fp32 partials of this GPU, summed in split order (no rounding before the final conversion).
+__device__ __forceinline__ void reduce_tile_f32(const Params& p, int et, int chunks, int ksp, int n0, unsigned parity,
+                                                size_t split_elems) {
+  const float* base = reinterpret_cast<const float*>(p.part[0]) + (size_t)parity * (p.part_stride / 2);
+  for (int c = et; c < chunks; c += 128) {
+    const int m = ksp + (c / (BN / 8)) * p.splits, cc = (c % (BN / 8)) * 8;
+    const size_t off = (size_t)m * p.N + n0 + cc;
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = p.bias != nullptr ? __bfloat162float(p.bias[n0 + cc + j]) : 0.f;
+    for (int sp = 0; sp < p.splits; ++sp) {
+      const float* src = base + off + (size_t)sp * split_elems;
+      float4 a, b;
+      asm volatile("ld.volatile.global.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(a.x), "=f"(a.y), "=f"(a.z), "=f"(a.w) : "l"(src));
+      asm volatile("ld.volatile.global.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(b.x), "=f"(b.y), "=f"(b.z), "=f"(b.w) : "l"(src + 4));
+      acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
+      acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
+    }
+    uint4 o;
+    o.x = pack_bf16x2(acc[0], acc[1]);
+    o.y = pack_bf16x2(acc[2], acc[3]);
+    o.z = pack_bf16x2(acc[4], acc[5]);
+    o.w = pack_bf16x2(acc[6], acc[7]);
+    *reinterpret_cast<uint4*>(p.y + (size_t)m * p.ldy + n0 + cc) = o;
   }
 }
 
@@ -282,13 +310,18 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
           if (m0 + j < p.M) p.y[(size_t)(m0 + j) * p.ldy + n0 + row] = __float2bfloat16(__uint_as_float(v[j]) + bv);
       }
     } else {
+    float* mine_f = reinterpret_cast<float*>(p.part[p.rank]) + (size_t)parity * (p.part_stride / 2) +
+                    (size_t)ksp * split_elems;
     for (int m0 = 0; m0 < p.Mpad; m0 += 16) {
       uint32_t v[16];
       tmem_ld_x16(tmem_base + lane_bits + m0, v);
       tmem_ld_wait();
 #pragma unroll
       for (int j = 0; j < 16; ++j)
-        if (m0 + j < p.M) mine[(size_t)(m0 + j) * p.N + n0 + row] = __float2bfloat16(__uint_as_float(v[j]));
+        if (m0 + j < p.M) {
+          if (p.part_f32) mine_f[(size_t)(m0 + j) * p.N + n0 + row] = __uint_as_float(v[j]);
+          else mine[(size_t)(m0 + j) * p.N + n0 + row] = __float2bfloat16(__uint_as_float(v[j]));
+        }
     }
     // the CTA barrier orders every thread's partial stores before the (cumulative) system-scope release stores
     asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -306,7 +339,9 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
     // few chunks per thread (many K splits): two at a time; a whole 64-row tile per CTA (8 ranks, no splits): four, so
     // the tile takes two rounds of remote latency instead of four
     const int y_col0 = p.mode == 1 ? p.rank * p.tiles_per_rank * BN : 0;
-    if (reduce_here && p.mc_part != nullptr) {
+    if (reduce_here && p.part_f32) {
+      reduce_tile_f32(p, et, chunks, ksp, n0, parity, split_elems);
+    } else if (reduce_here && p.mc_part != nullptr) {
       reduce_tile_nvls(p, et, chunks, ksp, n0, parity, split_elems, y_col0);
     } else if (reduce_here) {
       if (!PAIR && chunks > 256) reduce_tile<4>(p, et, chunks, ksp, n0, parity, split_elems, y_col0);
@@ -355,7 +390,9 @@ static int launch_tp(const void* x, const void* w, void* y, int M, int N, int Ks
   // rank too (that is how the protocol is tested without peers)
   const bool direct = allow_direct && world == 1 && splits == 1 && mode == 0 && x_ptrs == nullptr && mc_part == nullptr;
   HMF_REQUIRE(direct || N / BN <= max_tiles, "tp gemm: %d tiles exceed the flag array (%d)", N / BN, max_tiles);
-  HMF_REQUIRE(direct || (long long)M * N * splits <= part_stride, "tp gemm: partial buffer too small");
+  const bool part_f32 = allow_direct && !direct && world == 1 && mode == 0 && x_ptrs == nullptr && mc_part == nullptr;
+  HMF_REQUIRE(direct || (long long)M * N * splits * (part_f32 ? 2 : 1) <= part_stride,
+              "tp gemm: partial buffer too small");
   HMF_REQUIRE(bias == nullptr || mc_part == nullptr, "tp gemm: no bias in the NVLS form");
   HMF_REQUIRE(mode == 0 || (N / BN) % world == 0, "tp gemm: reduce-scatter needs N / 128 = %d tiles divisible by %d ranks",
               N / BN, world);
@@ -409,6 +446,7 @@ static int launch_tp(const void* x, const void* w, void* y, int M, int N, int Ks
   p.bias = (const bf16*)bias;
   p.direct = direct ? 1 : 0;
   p.stages = stages;
+  p.part_f32 = part_f32 ? 1 : 0;
   p.b_bytes = bst;
   p.tiles_per_rank = mode == 1 ? (N / BN) / world : N / BN;
   p.ldy = mode == 1 ? N / world : N;

@@ -78,12 +78,16 @@ class SparseMoeBlock(nn.Module):
             self.shared_expert = None
         self.expert_parallel_group = None
         self.fused_ep = None            # parallel.ep_fused.FusedExpertParallel (grouped GEMM kernels, inference)
+        self.eplb_plan = None           # parallel.eplb.EPLBPlan: replicated hot experts, routing on physical slots
 
     def forward(self, x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
         shape = x.shape
         flat = x.reshape(-1, shape[-1])
         logits = self.gate(flat)
         weights, indices = moe_ops.router(logits, self.top_k, self.norm_topk_prob)
+        if self.eplb_plan is not None:
+            from ..parallel.eplb import remap
+            indices = remap(indices, self.eplb_plan)
         out = moe_ops.experts_forward(flat, self.experts.gate_up_proj, self.experts.down_proj, weights.to(flat.dtype),
                                       indices, ep=self.expert_parallel_group, fused=self.fused_ep)
         if self.shared_expert is not None:

@@ -101,8 +101,8 @@ def skinny_gemm(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] =
     dev = x2.device
     st = _skinny_state.get(dev.index)
     if st is None:      # partial / flag scratch of the K-split reduction (unused when one split covers K)
-        st = _skinny_state[dev.index] = PeerGemmAllReduce(None, 256, 8192, dev)
-    splits = st._splits(N, K) if N <= st.max_n else 1
+        st = _skinny_state[dev.index] = PeerGemmAllReduce(None, 256, 16384, dev)     # fp32 partials: half the capacity
+    splits = st._splits(N, K) if N <= st.max_n // 2 else 1
     y = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
     c_int, c_ll = ctypes.c_int, ctypes.c_longlong
     _lib.check(_lib.kernels().hmf_gemm_skinny(

@@ -242,6 +242,13 @@ def run_exp(args: Optional[Any] = None) -> Trainer:
     if getattr(run_args, "fp8", False):
         from ..ops.fp8 import use_fp8_linear
         info_rank0(logger, "fp8: %d linear layers run their GEMMs in row-wise scaled float8", use_fp8_linear(model))
+    if not data_args.template and stage not in ("pt", "hkd"):
+        # no template given: the one the model family speaks (`data/model_registry.py`), else the plain default
+        from ..data.model_registry import template_for_model
+        guess = template_for_model(getattr(model_args, "model_name_or_path", None))
+        if guess:
+            data_args.template = guess
+            info_rank0(logger, "template '%s' chosen from the model name", guess)
     dataset = get_dataset(data_args, tokenizer, stage=("pt" if stage in ("pt", "hkd") else stage if stage in ("rm", "dpo", "kto") else "sft"), sp_size=sp,
                           vocab_size=model.config.vocab_size, seed=run_args.seed)
     bsz = run_args.per_device_train_batch_size * run_args.gradient_accumulation_steps

@@ -698,3 +698,17 @@ def test_longlora_shift_attention():
     model.eval()
     b = model(input_ids=ids).logits
     assert a.shape == b.shape and not torch.allclose(a, b)        # grouped attention in training, full attention in eval
+
+
+def test_model_name_selects_its_chat_template():
+    from hybrid_model_factory_b200.data import template_zoo  # noqa: F401  (registers the zoo)
+    from hybrid_model_factory_b200.data.formats import TEMPLATES
+    from hybrid_model_factory_b200.data.model_registry import families, template_for_model as t
+    assert t("Qwen/Qwen3-8B") == "qwen3" and t("/ckpt/Qwen2.5-7B-Instruct") == "qwen"
+    assert t("Qwen/Qwen3-Next-80B-A3B-Instruct") == "qwen3_next" and t("Qwen3-VL-8B") == "qwen3_vl"
+    assert t("meta-llama/Llama-3.1-8B-Instruct") == "llama3" and t("Llama-2-7b-chat-hf") == "llama2"
+    assert t("mistralai/Ministral-3-8B-Instruct") == "ministral" and t("Mistral-7B-Instruct-v0.3") == "mistral"
+    assert t("deepseek-ai/DeepSeek-R1-Distill-Qwen-7B") == "deepseekr1"
+    assert t("Qwen3-8B-Base") == "default" and t("some-unknown-model") is None and t(None) is None
+    missing = [f for f in families() if f not in TEMPLATES]
+    assert not missing, missing

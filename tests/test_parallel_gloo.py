@@ -54,6 +54,45 @@ def test_expert_parallel_matches_local_experts():
     run_ranks(_ep_worker, 2)
 
 
+def _eplb_worker(rank, world):
+    """Skewed routing: the hot expert is replicated, the ranks' loads even out, the output does not change."""
+    from hybrid_model_factory_b200.parallel.ep import EPContext
+    from hybrid_model_factory_b200.parallel.eplb import balance, shard_experts_balanced
+    torch.manual_seed(0)
+    ref = SparseMoeBlock(_moe_cfg())
+    blk = copy.deepcopy(ref)
+    g = torch.Generator().manual_seed(20 + rank)
+    x = torch.randn(9, 32, generator=g)
+    out_ref, _ = ref(x)
+    plan = balance(torch.tensor([100.0, 5.0, 5.0, 10.0]), num_physical=6, num_ranks=world)
+    shard_experts_balanced(blk, EPContext.from_group(None), plan)
+    assert blk.experts.gate_up_proj.shape[0] == 3
+    out, _ = blk(x)
+    assert torch.allclose(out, out_ref, atol=1e-5)
+
+
+def test_expert_load_balancer():
+    from hybrid_model_factory_b200.parallel.eplb import LoadTracker, balance, identity_plan, remap
+    load = torch.tensor([100.0, 5.0, 5.0, 10.0, 40.0, 0.0, 20.0, 20.0])
+    plan = balance(load, num_physical=12, num_ranks=4)
+    assert plan.replicas.sum() == 12 and plan.replicas[0] >= 3 and plan.replicas[5] == 1
+    assert sorted(plan.phys2log.tolist()) == sorted(sum(([e] * int(r) for e, r in enumerate(plan.replicas)), []))
+    before = identity_plan(8, 4).rank_load(load)
+    after = plan.rank_load(load)
+    assert after.max() < 0.6 * before.max() and abs(after.sum() - load.sum()) < 1e-6
+    idx = torch.randint(0, 8, (64, 2))
+    phys = remap(idx, plan)
+    assert torch.equal(plan.phys2log[phys], idx)                       # every physical id serves the routed expert
+    hot = phys[idx == 0]
+    assert len(set(hot.tolist())) == int(plan.replicas[0])             # all replicas of the hot expert are used
+    tr = LoadTracker(2, 8)
+    tr.update(0, idx)
+    tr.update(1, torch.zeros(10, 2, dtype=torch.long))
+    plans = tr.plans(12, 4)
+    assert plans[1].replicas[0] == 5                                   # all spare slots go to the only busy expert
+    run_ranks(_eplb_worker, 2)
+
+
 def _ulysses_worker(rank, world):
     from hybrid_model_factory_b200.ops import reference as R
     from hybrid_model_factory_b200.parallel.sp import init_sp_group, zigzag_split
