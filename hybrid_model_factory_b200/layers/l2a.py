@@ -40,9 +40,26 @@ class L2AAttention(nn.Module):
         self.global_norm = RMSNorm(config.hidden_size, config.rms_norm_eps)
         self.router = nn.Linear(config.hidden_size, 1, bias=False)
         self.sequence_parallel_group = None
+        # training step, set by the L2A loss before every forward: the leakage coin is a function of (layer, step), so
+        # the first run and the re-run of a checkpointed layer, and all ranks of a sequence-parallel group, agree on it
+        self.leak_step: Optional[int] = None
         self.last_soft_sq: Optional[torch.Tensor] = None
         self.last_tokens = 0
         self.last_routed_fraction = 0.0
+
+    def _leak_coin(self, sp) -> float:
+        """Uniform number in [0, 1) deciding "dense attention for all tokens this step"."""
+        if self.leak_step is not None:
+            g = torch.Generator().manual_seed(1_000_003 * (self.layer_idx + 1) + int(self.leak_step))
+            return float(torch.rand((), generator=g))
+        coin = torch.rand(())
+        if sp is not None:                         # no step was announced: rank 0 of the group decides for all
+            import torch.distributed as dist
+            dev = self.router.weight.device
+            t = coin.to(dev if dev.type == "cuda" else "cpu")
+            dist.broadcast(t, src=sp.ranks[0], group=sp.group)
+            coin = t.cpu()
+        return float(coin)
 
     def forward(self, hidden_states, residual=None, position_embeddings=None, past_key_values=None, position_ids=None,
                 **kwargs):
@@ -53,23 +70,45 @@ class L2AAttention(nn.Module):
         soft = torch.sigmoid(self.router(h2).float() / self.temperature)        # [B, T, 1]
         hard = (soft > self.threshold).float()
         mask = hard + soft - soft.detach()
-        self.last_soft_sq, self.last_tokens = (soft ** 2).sum(), B * T
+        sp = self.sequence_parallel_group
+        sp_on = sp is not None and sp.size > 1
+        # under sequence parallelism the ranks' regularisers add up (their gradients are summed): each holds its share
+        self.last_soft_sq, self.last_tokens = (soft ** 2).sum(), B * T * (sp.size if sp_on else 1)
         self.last_routed_fraction = float(hard.mean())
         ga = self.global_attn
         q, k, v, _ = ga._qkv(h2, position_embeddings)
-        leak = self.training and self.leak_prob > 0 and float(torch.rand(())) < self.leak_prob
-        if leak:
+        leak = self.training and self.leak_prob > 0 and self._leak_coin(sp if sp_on else None) < self.leak_prob
+        if leak and sp_on:
+            from ..parallel.cp_attention import cp_attention
+            o = cp_attention(q, k, v, sp, scale=ga.scaling)
+        elif leak:
             o = F_ops.attention(q, k, v, scale=ga.scaling, causal=True)
         else:
+            if sp_on:
+                # the selected local queries attend the whole (gathered) sequence at their global positions; the
+                # gradients of K / V are reduce-scattered back to their owners by the gather's backward
+                from ..parallel.cp_attention import gather_seq
+                from ..parallel.sp import zigzag_positions
+                k, v = gather_seq(k, sp), gather_seq(v, sp)
+                gpos = zigzag_positions(T * sp.size, sp.rank, sp.size, device=q.device)
+            else:
+                gpos = None
             o = torch.zeros_like(q)
             for b in range(B):                                   # rows differ per sample: compact each one
                 idx = torch.nonzero(hard[b, :, 0], as_tuple=False)[:, 0]
                 if idx.numel() == 0:
                     continue
-                ob = F_ops.qsparse_attention(q[b:b + 1, idx], k[b:b + 1], v[b:b + 1], idx[None], scale=ga.scaling)
+                pos = idx if gpos is None else gpos[idx]
+                ob = F_ops.qsparse_attention(q[b:b + 1, idx], k[b:b + 1], v[b:b + 1], pos[None], scale=ga.scaling)
                 o[b, idx] = ob[0].to(o.dtype)
         o = (o * mask[..., None].to(o.dtype)).reshape(B, T, -1)
         return s + ga.o_proj(o), None, past_key_values
+
+
+def set_l2a_step(model: nn.Module, step: int) -> None:
+    for m in model.modules():
+        if isinstance(m, L2AAttention):
+            m.leak_step = int(step)
 
 
 def l2a_regulariser(model: nn.Module) -> torch.Tensor:

@@ -46,6 +46,24 @@ def _reduce_scatter_seq(x_full: Tensor, sp: SPContext) -> Tensor:
     return zigzag_split(buf, sp.rank, sp.size, dim=1)
 
 
+class _GatherSeq(torch.autograd.Function):
+    """Differentiable all-gather along the sequence: shards in, the whole sequence in global order out; the gradient
+    is summed over the group (fp32) and every rank gets back its shard's part."""
+
+    @staticmethod
+    def forward(ctx, x: Tensor, sp: SPContext):
+        ctx.sp, ctx.dtype = sp, x.dtype
+        return _all_gather_seq(x, sp)
+
+    @staticmethod
+    def backward(ctx, g: Tensor):
+        return _reduce_scatter_seq(g.float(), ctx.sp).to(ctx.dtype), None
+
+
+def gather_seq(x: Tensor, sp: SPContext) -> Tensor:
+    return _GatherSeq.apply(x, sp)
+
+
 class _CPAttention(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q: Tensor, k: Tensor, v: Tensor, sp: SPContext, scale: Optional[float], window: Optional[int]):

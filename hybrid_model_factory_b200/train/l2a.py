@@ -4,7 +4,7 @@ from __future__ import annotations
 
 import math
 
-from ..layers.l2a import l2a_regulariser, router_sparsity
+from ..layers.l2a import l2a_regulariser, router_sparsity, set_l2a_step
 
 
 def lambda_schedule(step: int, lambda_reg: float, warmup_steps: int, total_steps: int, kind: str = "linear") -> float:
@@ -27,6 +27,7 @@ class L2ALoss:
         self.last_sparsity = {}
 
     def __call__(self, model, batch):
+        set_l2a_step(model, self.step)
         out = model(input_ids=batch["input_ids"], labels=batch["labels"], position_ids=batch.get("position_ids"),
                     labels_shifted=bool(batch.get("labels_shifted", False)))
         lam = lambda_schedule(self.step, self.lambda_reg, self.args.warmup_steps, self.args.max_steps, self.scheduler)

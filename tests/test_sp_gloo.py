@@ -18,13 +18,19 @@ def _config(pattern):
                         num_attention_heads=4, num_key_value_heads=2, head_dim=32, rope_theta=1e6,
                         hybrid_override_pattern=pattern, max_position_embeddings=4096,
                         bmojo_config={"window_size": 8, "ssm_mixer": "gdn", "tie_attn_weights": False},
-                        swa_config={"window_size": 16}, torch_dtype="float32")
+                        swa_config={"window_size": 16}, l2a_config={"sliding_window": 16, "leak_prob": 0.5},
+                        torch_dtype="float32")
 
 
 def _sp_worker(rank, world, pattern, seq, tol, parallel_scan=False):
     torch.manual_seed(0)
     cfg = _config(pattern)
     ref = build_model(cfg)
+    if "L2A" in pattern:        # layer 0 takes the routed (query-sparse) branch at this step, layer 1 the dense one
+        from hybrid_model_factory_b200.layers.l2a import L2AAttention, set_l2a_step
+        set_l2a_step(ref, 1)
+        coins = [m._leak_coin(None) < 0.5 for m in ref.modules() if isinstance(m, L2AAttention)]
+        assert coins == [False, True], coins
     model = copy.deepcopy(ref)
     g = torch.Generator().manual_seed(1)
     ids = torch.randint(0, 1024, (2, seq), generator=g)
@@ -68,7 +74,8 @@ def _sp_worker(rank, world, pattern, seq, tol, parallel_scan=False):
         assert (p - q).abs().max().item() < 2.1e-3, n
 
 
-@pytest.mark.parametrize("pattern,tol", [("*-GDN-*-GDN", 1e-5), ("GKA-*-M2-SWA", 5e-5), ("BMF-GDN", 5e-5)])
+@pytest.mark.parametrize("pattern,tol", [("*-GDN-*-GDN", 1e-5), ("GKA-*-M2-SWA", 5e-5), ("BMF-GDN", 5e-5),
+                                         ("L2A-L2A", 5e-5)])
 def test_sp2_matches_single_rank(pattern, tol):
     run_ranks(_sp_worker, 2, pattern, 256, tol)
 
