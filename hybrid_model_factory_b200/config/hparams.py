@@ -161,6 +161,9 @@ class FinetuningArguments:
     use_dora: bool = False                     # weight-decomposed LoRA (trainable row magnitudes)
     pissa_init: bool = False                   # adapters start as the principal singular directions of the weight
     pissa_iter: int = 16                       # power iterations of the randomised SVD (0: exact SVD)
+    use_dft_loss: bool = False                 # SFT: token losses scaled by the target's (detached) probability
+    use_eaft_loss: bool = False                # SFT: token losses scaled by the top-20 entropy ** eaft_alpha
+    eaft_alpha: float = 1.0
     shift_attn: bool = False                   # LongLoRA shifted sparse attention while training (groups of 1/4 length)
     freeze_trainable_layers: int = 2
     include_effective_tokens_per_second: bool = False

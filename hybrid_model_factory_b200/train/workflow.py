@@ -290,6 +290,9 @@ def run_exp(args: Optional[Any] = None) -> Trainer:
         if stage == "rm":
             attach_value_head(model)                                      # before the optimizer collects parameters
         loss_fn = make_preference_loss(stage, ft_args, reference, getattr(tokenizer, "pad_token_id", None) or 0)
+    if stage == "sft" and (ft_args.use_dft_loss or ft_args.use_eaft_loss):
+        from .losses import make_weighted_sft_loss
+        loss_fn = make_weighted_sft_loss("dft" if ft_args.use_dft_loss else "eaft", ft_args.eaft_alpha)
     if stage == "ppo":
         return run_ppo(model, ft_args, run_args, dataset, tokenizer, device, bsz)
     trainer = Trainer(model, targs, device=device, loss_fn=loss_fn)

@@ -145,7 +145,13 @@ def iter_tensors(path: str) -> Iterator[Tuple[str, torch.Tensor]]:
 
 
 def load_state_dict(path: str) -> Dict[str, torch.Tensor]:
-    return from_hf_names(dict(iter_tensors(path)))
+    """All tensors of a checkpoint directory under this package's names; matrices stored as group-wise quantised
+    integers (``hmf export --quantize``) are dequantised to bf16 on the way in."""
+    state = dict(iter_tensors(path))
+    if any(k.endswith(".qweight") for k in state):
+        from .export import dequantize_state
+        state = dequantize_state(state)
+    return from_hf_names(state)
 
 
 def load_state_dict_into(model: torch.nn.Module, path: str, strict: bool = False) -> Tuple[List[str], List[str]]:

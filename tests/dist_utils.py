@@ -20,10 +20,17 @@ def _entry(rank, world, port, fn, args, errq, backend="gloo"):
     os.environ["RANK"], os.environ["WORLD_SIZE"] = str(rank), str(world)
     os.environ["LOCAL_RANK"] = str(rank)
     torch.set_num_threads(2)
+    dump_after = float(os.environ.get("HMF_TEST_DUMP_AFTER_S", "0"))
+    if dump_after > 0:          # a rank still running by then prints every thread's stack (shows where it waits)
+        import faulthandler
+        faulthandler.dump_traceback_later(dump_after, exit=False)
     try:
         if backend == "nccl":
             torch.cuda.set_device(rank)
-            dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+            import datetime
+            # a rank that failed never joins the others' next collective: let that collective give up in minutes
+            dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank),
+                                    timeout=datetime.timedelta(seconds=180))
         else:
             dist.init_process_group("gloo", rank=rank, world_size=world)
         fn(rank, world, *args)
@@ -50,6 +57,7 @@ def run_ranks(fn, world: int, *args, timeout: float = 300.0, backend: str = "glo
     errors = []
     while not errq.empty():
         errors.append(errq.get())
-    assert not alive, f"{len(alive)} rank(s) timed out"
+    # a rank that failed leaves the others waiting in their next collective: show its error with the timeout
+    assert not alive, f"{len(alive)} rank(s) timed out" + "".join(f"\n[rank {r}]\n{tb}" for r, tb in errors)
     assert not errors, "\n".join(f"[rank {r}]\n{tb}" for r, tb in errors)
     assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]

@@ -712,3 +712,35 @@ def test_model_name_selects_its_chat_template():
     assert t("Qwen3-8B-Base") == "default" and t("some-unknown-model") is None and t(None) is None
     missing = [f for f in families() if f not in TEMPLATES]
     assert not missing, missing
+
+
+def test_export_merges_adapters_quantises_and_writes_modelfile(tmp_path):
+    from hybrid_model_factory_b200.train.adapters import apply_lora
+    from hybrid_model_factory_b200.utils import checkpoint_io
+    from hybrid_model_factory_b200.utils.export import dequantize_state, export, quantize_state
+    torch.manual_seed(0)
+    model = build_model(_cfg("*-GDN", hidden_size=128, intermediate_size=512)).eval()
+    apply_lora(model, rank=4, alpha=8, use_dora=True)
+    for n, p in model.named_parameters():
+        if n.endswith("lora_B"):
+            torch.nn.init.normal_(p, std=0.05)
+    ids = torch.randint(0, 128, (1, 10))
+    ref = model(input_ids=ids).logits
+    src, merged, q8 = tmp_path / "src", tmp_path / "merged", tmp_path / "q8"
+    checkpoint_io.save_pretrained(model, str(src))
+    export(str(src), str(merged), merge_lora=True, lora_alpha=8, ollama=True, template="qwen")
+    plain = checkpoint_io.from_pretrained(str(merged), dtype=torch.float32).eval()     # strict load: ordinary layout
+    assert torch.allclose(plain(input_ids=ids).logits, ref, atol=1e-4)
+    mf = (merged / "Modelfile").read_text()
+    assert mf.startswith("FROM .") and "{{ .Prompt }}" in mf
+    # int8 / int4 group-wise round trip on a state dict, then through a checkpoint directory
+    w = {"a.weight": torch.randn(512, 256), "small.weight": torch.randn(4, 4)}
+    for bits, tol in ((8, 0.02), (4, 0.2)):
+        q = quantize_state(w, bits, 128)
+        assert "a.weight.qweight" in q and "small.weight" in q and q["a.weight.qweight"].dtype == torch.int8
+        back = dequantize_state(q, torch.float32)
+        assert (back["a.weight"] - w["a.weight"]).abs().max() < tol * w["a.weight"].abs().max()
+    export(str(merged), str(q8), quantize="int8")
+    quant = checkpoint_io.from_pretrained(str(q8), dtype=torch.float32).eval()
+    err = (quant(input_ids=ids).logits - ref).abs().max() / ref.abs().max()
+    assert err < 0.05

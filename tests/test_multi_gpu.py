@@ -356,4 +356,4 @@ def _tp_server_gpu_worker(rank, world):
 
 @pytest.mark.multigpu(2)
 def test_tensor_parallel_api_server_two_gpus():
-    run_ranks(_tp_server_gpu_worker, 2, backend="nccl", timeout=240)
+    run_ranks(_tp_server_gpu_worker, 2, backend="nccl", timeout=150)

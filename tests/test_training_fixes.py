@@ -330,3 +330,35 @@ def test_recompute_plan_keeps_layers_that_fit(tmp_path):
     # a layer larger than the rest of the budget is passed over, smaller earlier ones still go in
     assert checkpointing.choose_unchecked_layers({0: 50, 1: 500, 2: 100}, 160) == [0, 2]
     assert tr.train_step(batch) is not None
+
+
+def test_dft_and_eaft_losses_match_their_definitions():
+    import torch
+    import torch.nn.functional as F
+    from hybrid_model_factory_b200.models.configuration import HybridConfig
+    from hybrid_model_factory_b200.models.modeling_hybrid import build_model
+    from hybrid_model_factory_b200.train.losses import make_weighted_sft_loss
+    torch.manual_seed(0)
+    cfg = HybridConfig("hybrid_qwen3", vocab_size=50, hidden_size=32, intermediate_size=64, num_hidden_layers=2,
+                       num_attention_heads=2, num_key_value_heads=1, head_dim=16, hybrid_override_pattern="*-GDN")
+    model = build_model(cfg)
+    ids = torch.randint(0, 50, (2, 20))
+    labels = ids.clone()
+    labels[:, :5] = -100
+    logits = model(input_ids=ids).logits.float()[:, :-1].reshape(-1, 50)
+    y = labels[:, 1:].reshape(-1)
+    ce = F.cross_entropy(logits, y, ignore_index=-100, reduction="none")[y != -100]
+    lg = logits[y != -100]
+    dft = (ce * torch.exp(-ce).detach()).mean()
+    top = torch.topk(lg, 20, dim=-1).values
+    lp = top - torch.logsumexp(top, -1, keepdim=True)
+    ent = -(lp.exp() * lp).sum(-1)
+    eaft = (ce * torch.pow(ent / 3.0, 2.0).detach()).mean()
+    batch = {"input_ids": ids, "labels": labels}
+    got_dft = make_weighted_sft_loss("dft", chunk=7)(model, batch)
+    got_eaft = make_weighted_sft_loss("eaft", 2.0, chunk=7)(model, batch)
+    assert torch.allclose(got_dft, dft, atol=1e-5) and torch.allclose(got_eaft, eaft, atol=1e-5)
+    # gradients flow through the cross entropy only (the weights are constants)
+    g1 = torch.autograd.grad(got_dft, model.lm_head.weight)[0]
+    g2 = torch.autograd.grad(dft, model.lm_head.weight)[0]
+    assert torch.allclose(g1, g2, atol=1e-6)
