@@ -72,6 +72,13 @@ class EngineLoop:
         self.wake.set()
         return None, q
 
+    def shutdown(self, timeout: float = 20.0) -> None:
+        """Stops the serving thread (which also releases the follower ranks) and drops the engine's captured graphs."""
+        self.stop = True
+        self.wake.set()
+        self.thread.join(timeout=timeout)
+        self.engine.close()
+
     def _run(self):
         try:
             if self.engine.device.type == "cuda":       # a new thread starts on device 0
@@ -121,11 +128,13 @@ class EngineLoop:
 
 def follow(engine: ServingEngine, control: ControlChannel) -> int:
     """Loop of the tensor-parallel ranks other than 0: replay rank 0's request stream and step with it.  Returns the
-    number of engine steps taken."""
+    number of engine steps taken; the engine's captured graphs are released on the way out (they pin the NCCL
+    communicator, see ``ServingEngine.close``)."""
     steps = 0
     while True:
         msg = control.broadcast()
         if msg["stop"]:
+            engine.close()
             return steps
         for prompt, params in msg["add"]:
             engine.add_request(prompt, SamplingParams(**params))
@@ -213,6 +222,26 @@ def create_app(engine: ServingEngine, tokenizer, model_name: str = "hybrid", tem
             ids += p + (r if i < len(pairs) - 1 else [])
         return await run(ids, body, chat=True)
 
+    @app.post("/v1/score/evaluation")
+    async def score(body: dict):
+        """Reward-model scores of ``messages`` (a list of texts): the value head at each text's last token.  Needs a
+        checkpoint trained with ``stage: rm`` (it carries ``v_head``); reference: ``api/app.py`` ``/v1/score/evaluation``.
+        Runs on the serving thread's model between engine steps (texts are short; no paged cache is involved)."""
+        model = engine.model
+        if not hasattr(model, "v_head"):
+            return JSONResponse({"error": "this checkpoint has no value head (train it with stage: rm)"}, status_code=400)
+        texts = body.get("messages", [])
+        max_len = int(body.get("max_length", 1024))
+        rows = [tokenizer.encode(t, add_special_tokens=False)[:max_len] or [0] for t in texts]
+        from ..train.preference import reward_scores
+        scores = []
+        with torch.no_grad():
+            for ids in rows:            # one text at a time: no padding, so the last token is the last position
+                t = torch.tensor([ids], dtype=torch.long, device=engine.device)
+                scores.append(float(reward_scores(model, t)[0]))
+        return {"id": f"scoreval-{uuid.uuid4().hex[:12]}", "object": "score.evaluation", "model": model_name,
+                "scores": scores}
+
     @app.get("/metrics")
     async def metrics():
         return engine.request_metrics()
@@ -267,9 +296,7 @@ def main(argv=None) -> int:
     try:
         uvicorn.run(app, host=args.host, port=args.port)
     finally:
-        app.state.loop_runner.stop = True      # also releases the follower ranks
-        app.state.loop_runner.wake.set()
-        app.state.loop_runner.thread.join(timeout=5)
+        app.state.loop_runner.shutdown(timeout=5)
     return 0
 
 

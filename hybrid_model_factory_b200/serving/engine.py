@@ -238,6 +238,15 @@ class ServingEngine:
             self.stats["prefill_s"] += time.perf_counter() - t0
         return results
 
+    def close(self) -> None:
+        """Drops the captured decode graphs.  A graph that holds NCCL kernels (tensor parallelism) keeps its
+        communicator busy: the process group cannot shut down while such a graph exists, and an engine that is only
+        unreachable (it sits in a reference cycle with its serving thread) still counts.  Call this before
+        ``destroy_process_group``."""
+        self._graphs.clear()
+        if self._cuda:
+            torch.cuda.synchronize(self.device)
+
     def _at_frontier(self, s: ScheduledSeq) -> bool:
         req = self.requests[s.req_id]
         return s.start_pos == len(req.prompt) + len(req.output) - 1

@@ -347,9 +347,7 @@ def _tp_server_gpu_worker(rank, world):
     try:
         counts = asyncio.run(scenario())
     finally:
-        app.state.loop_runner.stop = True
-        app.state.loop_runner.wake.set()
-        app.state.loop_runner.thread.join(timeout=20)
+        app.state.loop_runner.shutdown(timeout=20)      # also drops the graphs that pin the NCCL communicator
     _lib.assert_status_ok()
     assert counts == [8, 8] and eng.stats["graph_replays"] > 0
 

@@ -523,3 +523,30 @@ def test_sampler_filters(device):
     toks = torch.tensor(sample_tokens(small, [SamplingParams(temperature=1.0)] * 4000, generator=g))
     freq = torch.bincount(toks, minlength=4).float() / 4000
     assert (freq - torch.softmax(small[0].float().cpu(), 0)).abs().max() < 0.03
+
+
+def test_api_server_scores_texts_with_a_reward_head():
+    import asyncio
+    import json
+    from hybrid_model_factory_b200.data.formats import ByteTokenizer
+    from hybrid_model_factory_b200.serving.api_server import create_app
+    from hybrid_model_factory_b200.train.preference import attach_value_head
+    torch.manual_seed(0)
+    model = build_model(tiny("*-GDN", vocab_size=259)).eval()
+    eng = ServingEngine(model, block_size=4, num_blocks=64, max_num_seqs=2, max_num_batched_tokens=16, max_model_len=64)
+    app = create_app(eng, ByteTokenizer(), model_name="tiny")
+    routes = {r.path: r.endpoint for r in app.routes if hasattr(r, "endpoint")}
+    try:
+        r = asyncio.run(routes["/v1/score/evaluation"]({"messages": ["a"]}))
+        assert r.status_code == 400                                     # no value head yet
+        attach_value_head(model)
+        out = asyncio.run(routes["/v1/score/evaluation"]({"messages": ["good answer", "bad"]}))
+        assert len(out["scores"]) == 2 and out["scores"][0] != out["scores"][1]
+        # same as scoring the tokens directly
+        from hybrid_model_factory_b200.train.preference import reward_scores
+        ids = torch.tensor([ByteTokenizer().encode("bad", add_special_tokens=False)])
+        assert abs(float(reward_scores(model, ids)[0]) - out["scores"][1]) < 1e-5
+    finally:
+        app.state.loop_runner.stop = True
+        app.state.loop_runner.wake.set()
+        app.state.loop_runner.thread.join(timeout=5)
