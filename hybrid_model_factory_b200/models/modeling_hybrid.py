@@ -163,18 +163,21 @@ class DecoderLayer(nn.Module):
         if self.symbol == "L2A":        # the router reads the residual stream after the local attention
             kwargs = dict(kwargs, residual=residual)
         cu = kwargs.pop("cu_seqlens", None)
-        if cu is not None and len(cu) > 2:
+        caches = kwargs.pop("sample_caches", None)
+        if cu is not None and (len(cu) > 2 or caches is not None):
             # packed samples (batch of one row): the mixer runs once per sample on its slice, so neither attention
-            # nor recurrent state crosses a sample boundary
+            # nor recurrent state crosses a sample boundary.  `sample_caches` (serving: the prefill pieces of several
+            # requests in one forward) gives every sample its own cache
             parts = []
-            for a, b in zip(cu[:-1], cu[1:]):
+            for j, (a, b) in enumerate(zip(cu[:-1], cu[1:])):
                 pe = None if position_embeddings is None else tuple(t[:, a:b] for t in position_embeddings)
                 kw = dict(kwargs)
                 if "residual" in kw:
                     kw["residual"] = kw["residual"][:, a:b]
+                pkv = None if caches is None else caches[j]
                 parts.append(self.seq_mixer(h[:, a:b], position_embeddings=pe,
                                             position_ids=None if position_ids is None else position_ids[:, a:b],
-                                            past_key_values=None, use_cache=False, **kw)[0])
+                                            past_key_values=pkv, use_cache=pkv is not None, **kw)[0])
             h = torch.cat(parts, dim=1)
         else:
             h, _, _ = self.seq_mixer(h, position_embeddings=position_embeddings, position_ids=position_ids,
@@ -319,6 +322,9 @@ class HybridModel(nn.Module):
                 router_logits.append(rl)
         if past_key_values is not None:
             past_key_values.update_offset(T)
+        if kwargs.get("sample_caches") is not None:
+            for c, a, b in zip(kwargs["sample_caches"], kwargs["cu_seqlens"][:-1], kwargs["cu_seqlens"][1:]):
+                c.update_offset(b - a)
         return self.norm(h), router_logits
 
 

@@ -153,10 +153,11 @@ class ServingEngine:
         self._cuda = self.device.type == "cuda" and _lib.kernels_available()
         self._layer_cache: Dict[int, dict] = {}
         self.max_blocks_per_seq = (max_model_len + block_size - 1) // block_size
-        self.stats = {"steps": 0, "decode_tokens": 0, "prefill_tokens": 0, "graph_replays": 0, "decode_steps": 0,
+        self.stats = {"steps": 0, "decode_tokens": 0, "prefill_tokens": 0, "graph_replays": 0, "decode_steps": 0, "packed_prefills": 0,
                       "decode_s": 0.0, "prefill_s": 0.0, "decode_gpu_s": 0.0}
         has_moe = any(hasattr(l.mlp, "experts") for l in model.model.layers)
         # B'MOJO-F layers decode request by request through the layer itself (bounded window state per request)
+        self.packed_prefill = True      # several requests' prefill pieces of one step share a forward
         self._use_graphs = bool(use_cuda_graphs and self._cuda and not has_moe and not self.state.bmojo_layers)
         self._graphs: Dict[tuple, dict] = {}
         self._tables: Dict[int, torch.Tensor] = {}
@@ -217,12 +218,24 @@ class ServingEngine:
             self.stats["decode_steps"] += 1
             self.stats["decode_s"] += time.perf_counter() - t0
         t0 = time.perf_counter()
-        for s in prefills:
+        packed = None
+        if len(prefills) > 1 and self.packed_prefill and not self.state.bmojo_layers:
+            # the pieces of several requests as ONE row with sample boundaries: embeddings, norms, MLPs and the
+            # vocabulary projection run once for all of them, every mixer once per piece with that request's cache
+            for s in prefills:
+                if s.restore_from >= 0:
+                    self.state.copy_slot(s.restore_from, s.slot)
+            packed = self._prefill_forward_packed(prefills)
+            self.stats["packed_prefills"] += 1
+        for i, s in enumerate(prefills):
             req = self.requests[s.req_id]
             tokens = (req.prompt + req.output)[s.start_pos:s.start_pos + s.num_tokens]
-            if s.restore_from >= 0:
-                self.state.copy_slot(s.restore_from, s.slot)
-            logits = self._prefill_forward(s, tokens)
+            if packed is not None:
+                logits = packed[i:i + 1]
+            else:
+                if s.restore_from >= 0:
+                    self.state.copy_slot(s.restore_from, s.slot)
+                logits = self._prefill_forward(s, tokens)
             self.sched.advance(s.req_id, s.num_tokens)
             self.stats["prefill_tokens"] += s.num_tokens
             end = s.start_pos + s.num_tokens
@@ -293,6 +306,22 @@ class ServingEngine:
         cache = SlotCache(self.state, s.slot, self.sched.block_table(s.req_id), s.start_pos, side)
         h, _ = self.model.model(ids, position_ids=pos, past_key_values=cache, use_cache=True)
         return self._logits(h[0, -1:])
+
+    def _prefill_forward_packed(self, pieces: List[ScheduledSeq]) -> torch.Tensor:
+        """One forward for the prefill pieces of several requests; returns the logits at each piece's last token."""
+        toks, pos, cu, caches = [], [], [0], []
+        for s in pieces:
+            req = self.requests[s.req_id]
+            t = (req.prompt + req.output)[s.start_pos:s.start_pos + s.num_tokens]
+            toks += t
+            pos += list(range(s.start_pos, s.start_pos + len(t)))
+            cu.append(len(toks))
+            caches.append(SlotCache(self.state, s.slot, self.sched.block_table(s.req_id), s.start_pos, None))
+        ids = torch.tensor([toks], dtype=torch.long, device=self.device)
+        pid = torch.tensor([pos], dtype=torch.long, device=self.device)
+        h, _ = self.model.model(ids, position_ids=pid, cu_seqlens=cu, sample_caches=caches)
+        last = torch.tensor([c - 1 for c in cu[1:]], dtype=torch.long, device=self.device)
+        return self._logits(h[0, last])
 
     def _logits(self, h: torch.Tensor) -> torch.Tensor:
         logits = self.model.lm_head(h)

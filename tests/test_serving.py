@@ -550,3 +550,21 @@ def test_api_server_scores_texts_with_a_reward_head():
         app.state.loop_runner.stop = True
         app.state.loop_runner.wake.set()
         app.state.loop_runner.thread.join(timeout=5)
+
+
+@pytest.mark.parametrize("pattern", ["*-GDN", "M2-GKA", "SWA-*"])
+def test_packed_prefill_of_several_requests_matches_one_by_one(pattern):
+    """Several requests' prefill pieces share one forward (one row with sample boundaries, one cache per sample); the
+    generated tokens equal those of request-by-request prefill, also when pieces continue a chunked prompt."""
+    torch.manual_seed(0)
+    model = build_model(tiny(pattern, vocab_size=259)).eval()
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(0, 259, (n,), generator=g).tolist() for n in (9, 23, 5, 14)]
+    outs = []
+    for packed in (False, True):
+        eng = ServingEngine(model, block_size=4, num_blocks=128, max_num_seqs=4, max_num_batched_tokens=24,
+                            max_model_len=64)
+        eng.packed_prefill = packed
+        outs.append(eng.generate(prompts, SamplingParams(max_new_tokens=5)))
+        assert (eng.stats["packed_prefills"] > 0) == packed
+    assert outs[0] == outs[1]
