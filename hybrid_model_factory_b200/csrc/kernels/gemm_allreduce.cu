@@ -68,6 +68,7 @@ struct Params {
   int direct;                       // one rank, one K split: the accumulator goes straight to y (no partial, no flags)
   int stages, b_bytes;              // depth of the shared-memory ring, bytes of one B stage
   int part_f32;                     // single-GPU K splits: the partials stay fp32 (the buffers hold half as many)
+  int cluster_split;                // single-GPU K splits as one thread-block cluster: partials meet in shared memory
 };
 
 // One load that returns the sum over every rank's copy of 8 bf16 values (reduced inside NVSwitch, fp32 accumulation).
@@ -298,7 +299,19 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
     bf16* mine = p.part[p.rank] + (size_t)parity * p.part_stride + (size_t)ksp * split_elems;
     mbar_wait(acc_done, 0, ctx, 0x30);
     tc_fence_after();
-    if (p.direct) {
+    if (p.cluster_split) {
+      // the K splits of a tile are the CTAs of one cluster: the fp32 partial goes to this CTA's shared memory (the
+      // ring is idle once the accumulator is complete) and is summed below, after a cluster barrier, through
+      // distributed shared memory -- no global scratch, no flags, no polling
+      float* stg = reinterpret_cast<float*>(smem);
+      for (int m0 = 0; m0 < p.Mpad; m0 += 16) {
+        uint32_t v[16];
+        tmem_ld_x16(tmem_base + lane_bits + m0, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) stg[(m0 + j) * BN + row] = __uint_as_float(v[j]);
+      }
+    } else if (p.direct) {
       // single-GPU skinny GEMM: thread = output column, a warp writes 32 consecutive columns of one row per store
       const float bv = p.bias != nullptr ? __bfloat162float(p.bias[n0 + row]) : 0.f;
       for (int m0 = 0; m0 < p.Mpad; m0 += 16) {
@@ -350,6 +363,33 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
     }  // !direct
   }
 
+  if (p.cluster_split) {
+    tc_fence_before();
+    __syncthreads();
+    cluster_arrive();                 // release: every CTA's partial is in its shared memory
+    cluster_wait();
+    if (warp >= 2) {
+      // CTA `ksp` sums the rows ksp, ksp + splits, ...; thread = output column, so every remote read is one
+      // contiguous 128-byte line per warp
+      const int col = (warp & 3) * 32 + lane;
+      const uint32_t local = smem_u32(smem);
+      const float bv = p.bias != nullptr ? __bfloat162float(p.bias[n0 + col]) : 0.f;
+      uint32_t remote[MAX_SPLIT];
+      for (int sp = 0; sp < p.splits; ++sp)
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote[sp]) : "r"(local), "r"(sp));
+      for (int m = ksp; m < p.M; m += p.splits) {
+        float acc = bv;
+        for (int sp = 0; sp < p.splits; ++sp) {
+          float v;
+          asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote[sp] + (uint32_t)(m * BN + col) * 4u));
+          acc += v;
+        }
+        p.y[(size_t)m * p.ldy + n0 + col] = __float2bfloat16(acc);
+      }
+    }
+    cluster_arrive();                 // nobody leaves while a peer may still read its shared memory
+    cluster_wait();
+  }
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -357,7 +397,7 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
     tmem_dealloc(tmem_base, p.tmem_cols);
   }
   // the last CTA of the launch publishes the epoch for the next launch
-  if (threadIdx.x == 0 && !p.direct) {
+  if (threadIdx.x == 0 && !p.direct && !p.cluster_split) {
     __threadfence();
     const unsigned int ticket = atomicAdd(p.sync + 1, 1u);
     if (ticket == gridDim.x - 1) {
@@ -447,13 +487,30 @@ static int launch_tp(const void* x, const void* w, void* y, int M, int N, int Ks
   p.direct = direct ? 1 : 0;
   p.stages = stages;
   p.part_f32 = part_f32 ? 1 : 0;
+  // the cluster form needs the fp32 tile (Mpad x 128 x 4 bytes) to fit in the ring of the two-CTAs-per-SM variant
+  const bool cluster_split = part_f32 && pair && splits > 1 && Mpad * BN * 4 <= stages * (A_BYTES + bst);
+  p.cluster_split = cluster_split ? 1 : 0;
   p.b_bytes = bst;
   p.tiles_per_rank = mode == 1 ? (N / BN) / world : N / BN;
   p.ldy = mode == 1 ? N / world : N;
   int cols = 32;
   while (cols < Mpad) cols *= 2;
   p.tmem_cols = cols;
-  if (pair) gemm_allreduce_kernel<true><<<(N / BN) * splits, 192, smem_bytes, st>>>(tmW, tmX, p);
+  if (cluster_split) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((N / BN) * splits);
+    cfg.blockDim = dim3(192);
+    cfg.dynamicSmemBytes = smem_bytes;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = splits;        // consecutive CTAs = the K splits of one tile
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    HMF_CHECK_CUDA(cudaLaunchKernelEx(&cfg, gemm_allreduce_kernel<true>, tmW, tmX, p));
+  } else if (pair) gemm_allreduce_kernel<true><<<(N / BN) * splits, 192, smem_bytes, st>>>(tmW, tmX, p);
   else gemm_allreduce_kernel<false><<<(N / BN) * splits, 192, smem_bytes, st>>>(tmW, tmX, p);
   HMF_CHECK_CUDA(cudaGetLastError());
   return HMF_OK;

@@ -13,6 +13,8 @@ contract of the fused one.
 """
 from __future__ import annotations
 
+import os
+
 from typing import Optional
 
 import torch
@@ -117,8 +119,12 @@ class _CPAttention(torch.autograd.Function):
             dk_full[:, :dk.shape[1]] += dk.float()
             dv_full[:, :dv.shape[1]] += dv.float()
         ctx.graphs = None
-        dk = _reduce_scatter_seq(dk_full, sp).to(ks0.dtype)
-        dv = _reduce_scatter_seq(dv_full, sp).to(vs0.dtype)
+        # this rank's two contributions were summed in fp32; the sum over ranks travels in the gradient's own dtype
+        # (half the bytes of an fp32 reduce-scatter; the result is stored in that dtype anyway) unless
+        # HMF_CP_DKV_FP32=1
+        wire = torch.float32 if os.environ.get("HMF_CP_DKV_FP32", "0") == "1" else ks0.dtype
+        dk = _reduce_scatter_seq(dk_full.to(wire), sp).to(ks0.dtype)
+        dv = _reduce_scatter_seq(dv_full.to(wire), sp).to(vs0.dtype)
         return torch.cat(dqs, dim=1), dk, dv, None, None, None
 
 
