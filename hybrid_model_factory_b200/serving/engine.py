@@ -158,6 +158,7 @@ class ServingEngine:
         has_moe = any(hasattr(l.mlp, "experts") for l in model.model.layers)
         # B'MOJO-F layers decode request by request through the layer itself (bounded window state per request)
         self.packed_prefill = True      # several requests' prefill pieces of one step share a forward
+        self.status_check_steps = 64    # tensor parallelism: how often the kernels' wait-status block is read
         self._use_graphs = bool(use_cuda_graphs and self._cuda and not has_moe and not self.state.bmojo_layers)
         self._graphs: Dict[tuple, dict] = {}
         self._tables: Dict[int, torch.Tensor] = {}
@@ -249,7 +250,21 @@ class ServingEngine:
                 results.append(self._emit(s.req_id, int(tok)))
         if prefills:
             self.stats["prefill_s"] += time.perf_counter() - t0
+        if (self.tp is not None and self.tp.size > 1 and self._cuda
+                and self.stats["steps"] % self.status_check_steps == 0):
+            self.check_kernel_status()
         return results
+
+    def check_kernel_status(self, status_reader=None) -> None:
+        """Raises ``KernelError`` when a device-side wait ran out since the last check (a late or missing peer in a
+        fused GEMM + reduction): such a kernel returns and the step goes on with partial sums, so the tokens produced
+        since then are not valid.  Read every ``status_check_steps`` steps of a tensor-parallel engine (one small
+        device-to-host read)."""
+        code, block, detail, count = (status_reader or _lib.read_status)()
+        if code != 0:
+            raise _lib.KernelError(
+                f"engine step {self.stats['steps']}: a device-side wait ran out (code={code} block={block} "
+                f"detail={detail:#x} count={count}); HMF_TP_FUSED=0 selects the NCCL reductions")
 
     def close(self) -> None:
         """Drops the captured decode graphs.  A graph that holds NCCL kernels (tensor parallelism) keeps its

@@ -568,3 +568,13 @@ def test_packed_prefill_of_several_requests_matches_one_by_one(pattern):
         outs.append(eng.generate(prompts, SamplingParams(max_new_tokens=5)))
         assert (eng.stats["packed_prefills"] > 0) == packed
     assert outs[0] == outs[1]
+
+
+def test_engine_raises_on_a_recorded_device_wait_timeout():
+    """A tensor-parallel engine reads the kernels' status block; a recorded timeout must end the run loudly."""
+    from hybrid_model_factory_b200.ops import _lib
+    model = build_model(tiny("*-GDN", vocab_size=259)).eval()
+    eng = ServingEngine(model, block_size=4, num_blocks=64, max_num_seqs=2, max_num_batched_tokens=16, max_model_len=64)
+    eng.check_kernel_status(lambda: (0, 0, 0, 0))
+    with pytest.raises(_lib.KernelError, match="wait ran out"):
+        eng.check_kernel_status(lambda: (3, 17, 0x40, 2))
