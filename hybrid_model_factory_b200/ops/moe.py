@@ -42,7 +42,9 @@ def padded_layout(flat_expert: Tensor, num_experts: int):
     R = (A + TILE - 1) // TILE * TILE + TILE * E
     order = torch.argsort(flat_expert, stable=True)
     sorted_e = flat_expert[order]
-    counts = torch.bincount(flat_expert, minlength=E)
+    # (not torch.bincount: on the GPU it reads the largest value back to the host to size its result)
+    counts = torch.zeros(E, dtype=torch.long, device=flat_expert.device).scatter_add_(
+        0, flat_expert.long(), torch.ones_like(flat_expert, dtype=torch.long))
     padded = (counts + TILE - 1) // TILE * TILE
     pad_end = torch.cumsum(padded, 0)
     pad_start = pad_end - padded

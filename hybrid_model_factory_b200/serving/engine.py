@@ -159,7 +159,10 @@ class ServingEngine:
         # B'MOJO-F layers decode request by request through the layer itself (bounded window state per request)
         self.packed_prefill = True      # several requests' prefill pieces of one step share a forward
         self.status_check_steps = 64    # tensor parallelism: how often the kernels' wait-status block is read
-        self._use_graphs = bool(use_cuda_graphs and self._cuda and not has_moe and not self.state.bmojo_layers)
+        # MoE layers: the bf16 expert path sorts and pads its rows on the device with static shapes (`ops/moe.py`), so
+        # the decode step stays capturable; other dtypes take a per-expert loop with a host read and run eagerly
+        moe_ok = not has_moe or next(model.parameters()).dtype == torch.bfloat16
+        self._use_graphs = bool(use_cuda_graphs and self._cuda and moe_ok and not self.state.bmojo_layers)
         self._graphs: Dict[tuple, dict] = {}
         self._tables: Dict[int, torch.Tensor] = {}
         self._timed_replay = False

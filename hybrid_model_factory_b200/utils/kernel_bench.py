@@ -74,9 +74,14 @@ def bench_gemm_skinny(args):
     iterations; the weight read is the algorithmic traffic)."""
     import torch.nn.functional as F
     from ..ops.gemm import skinny_gemm
-    for N, K in ((4096, 4096), (24576, 4096), (4096, 12288), (151936, 4096)):
+    shapes = ((4096, 4096), (24576, 4096), (4096, 12288), (151936, 4096))
+    rows = (1, 16, 64)
+    if args.skinny_shape:                  # "N,K,M": one case (profiler captures)
+        n, k, m = (int(v) for v in args.skinny_shape.split(","))
+        shapes, rows = ((n, k),), (m,)
+    for N, K in shapes:
         w = (torch.randn(N, K, device="cuda") * 0.02).bfloat16()
-        for M in (1, 16, 64):
+        for M in rows:
             x = torch.randn(M, K, device="cuda").bfloat16()
             ms = time_fn(lambda: skinny_gemm(x, w), iters=10)
             ms_lib = time_fn(lambda: F.linear(x, w), iters=10)
@@ -285,6 +290,7 @@ def main(argv=None):
     ap.add_argument("--kv-heads", type=int, default=8)
     ap.add_argument("--size", type=int, default=8192)
     ap.add_argument("--batch", type=int, default=64)
+    ap.add_argument("--skinny-shape", default=None, help="gemm_skinny: N,K,M of a single case")
     args = ap.parse_args(argv)
     names = list(CASES) if args.case == "all" else [args.case]
     for n in names:
