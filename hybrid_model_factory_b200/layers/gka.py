@@ -166,13 +166,9 @@ class GatedKalmaNet(nn.Module):
             new_conv = (cq, ck, cv)
         q = repeat_heads(q.reshape(B, T, self.num_q_heads, self.head_dim), self.num_q_groups)
         k, v = self._expand_kv(k, v)
-        eps = 1e-6
-        q = (q.float() / (torch.linalg.vector_norm(q.float(), dim=-1, keepdim=True) + eps)).to(q.dtype)
-        k = (k.float() / (torch.linalg.vector_norm(k.float(), dim=-1, keepdim=True) + eps)).to(k.dtype)
-        if self.use_beta_gate:
-            beta = torch.sigmoid(self.b_proj(hidden_states))
-            k = ((beta[..., None] + eps) * k).to(k.dtype)
-            v = ((beta[..., None] + eps) * v).to(v.dtype)
+        # unit-norm q and k, beta gate on k and v: one pass over the three tensors (`ops/cuda_ops.py::gka_prepare`)
+        beta = torch.sigmoid(self.b_proj(hidden_states)) if self.use_beta_gate else None
+        q, k, v = F_ops.gka_prepare(q, k, v, beta, 1e-6)
         alpha = torch.sigmoid(self.alpha_proj(hidden_states)) if self.use_alpha_connection else None
         if self.use_forgetting_gate:
             g = -self.A_log.float().exp() * torch.nn.functional.softplus(

@@ -290,6 +290,53 @@ def heads_norm_rope(x: Tensor, n_plain: int, n_b: int, n_c: int, wb: Optional[Te
 # ----------------------------------------------------------------------------------------
 # gating (tiny [T, H] tensors: plain PyTorch elementwise math)
 # ----------------------------------------------------------------------------------------
+class _GKAPrepare(torch.autograd.Function):
+    """q / k normalisation and beta scaling of Gated KalmaNet in one kernel each way (``csrc/kernels/gka_prep.cu``)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, beta, eps):
+        D = q.shape[-1]
+        q2, k2, v2 = (_lib.aligned(t.reshape(-1, D)) for t in (q, k, v))
+        N = q2.shape[0]
+        bt = None if beta is None else beta.reshape(-1).float().contiguous()
+        qn, kn, vn = (torch.empty(N, D, device=q.device, dtype=BF16) for _ in range(3))
+        nq = torch.empty(N, device=q.device, dtype=torch.float32)
+        nk = torch.empty_like(nq)
+        _lib.check(_K().hmf_gka_prep_fwd(_lib.ptr(q2), _lib.ptr(k2), _lib.ptr(v2), _lib.ptr(bt), _lib.ptr(qn), _lib.ptr(kn),
+                                         _lib.ptr(vn), _lib.ptr(nq), _lib.ptr(nk), c_ll(N), c_int(D), c_ll(q2.stride(0)),
+                                         c_ll(k2.stride(0)), c_ll(v2.stride(0)), c_float(eps), _st(q)), "gka_prep_fwd")
+        ctx.save_for_backward(q2, k2, v2, bt, nq, nk)
+        ctx.eps, ctx.shapes, ctx.beta_meta = eps, (q.shape, k.shape, v.shape), None if beta is None else (beta.shape, beta.dtype)
+        return qn.view(q.shape), kn.view(k.shape), vn.view(v.shape)
+
+    @staticmethod
+    def backward(ctx, gq, gk, gv):
+        q2, k2, v2, bt, nq, nk = ctx.saved_tensors
+        N, D = q2.shape
+        gq2, gk2, gv2 = (_lib.aligned(g.reshape(-1, D).to(BF16)) for g in (gq, gk, gv))
+        dq, dk, dv = (torch.empty(N, D, device=q2.device, dtype=BF16) for _ in range(3))
+        dbeta = torch.empty(N, device=q2.device, dtype=torch.float32) if bt is not None else None
+        _lib.check(_K().hmf_gka_prep_bwd(_lib.ptr(q2), _lib.ptr(k2), _lib.ptr(v2), _lib.ptr(bt), _lib.ptr(nq), _lib.ptr(nk),
+                                         _lib.ptr(gq2), _lib.ptr(gk2), _lib.ptr(gv2), _lib.ptr(dq), _lib.ptr(dk),
+                                         _lib.ptr(dv), _lib.ptr(dbeta), c_ll(N), c_int(D), c_ll(q2.stride(0)),
+                                         c_ll(k2.stride(0)), c_ll(v2.stride(0)), c_float(ctx.eps), _st(q2)),
+                   "gka_prep_bwd")
+        sq, sk, sv = ctx.shapes
+        db = None
+        if ctx.beta_meta is not None:
+            db = dbeta.view(ctx.beta_meta[0]).to(ctx.beta_meta[1])
+        return dq.view(sq), dk.view(sk), dv.view(sv), db, None
+
+
+def gka_prepare(q, k, v, beta=None, eps=1e-6):
+    """``(q / (|q| + eps), (beta + eps) k / (|k| + eps), (beta + eps) v)``; bf16 CUDA tensors with a head dimension that
+    is a multiple of 8 up to 256 take the fused kernels, everything else the PyTorch formulation."""
+    D = q.shape[-1]
+    if not (_is_bf16(q, k, v) and D % 8 == 0 and D <= 256 and q.shape == k.shape == v.shape):
+        return R.gka_prepare(q, k, v, beta, eps)
+    return _apply(_GKAPrepare, q, k, v, beta, eps)
+
+
 def gdn_gating(a, b, A_log, dt_bias, beta_scale=1.0):
     return R.gdn_gating(a, b, A_log, dt_bias, beta_scale)
 

@@ -64,6 +64,14 @@ def l2_norm(x: Tensor, eps: float = 1e-6) -> Tensor:
     return R.l2_norm(x, eps)
 
 
+def gka_prepare(q: Tensor, k: Tensor, v: Tensor, beta: Optional[Tensor] = None, eps: float = 1e-6):
+    """Gated KalmaNet inputs: unit-norm ``q``, ``k`` scaled by ``beta + eps`` after normalisation, ``v`` scaled by
+    ``beta + eps`` (one fused kernel each way on the GPU)."""
+    if _cuda(q, k, v):
+        return _ck().gka_prepare(q, k, v, beta, eps)
+    return R.gka_prepare(q, k, v, beta, eps)
+
+
 def gdn_gating(a: Tensor, b: Tensor, A_log: Tensor, dt_bias: Tensor, beta_scale: float = 1.0) -> Tuple[Tensor, Tensor]:
     if _cuda(a, b):
         return _ck().gdn_gating(a, b, A_log, dt_bias, beta_scale)

@@ -90,6 +90,19 @@ def softplus(x: Tensor) -> Tensor:
     return F.softplus(x.float())
 
 
+def gka_prepare(q: Tensor, k: Tensor, v: Tensor, beta: Optional[Tensor] = None, eps: float = 1e-6):
+    """Gated KalmaNet input preparation: ``q / (|q| + eps)``, ``(beta + eps) k / (|k| + eps)``, ``(beta + eps) v`` with
+    the norms over the last dimension and ``beta [...]`` one value per row (``None``: factor 1).  fp32 math, results in
+    the input dtype."""
+    qf, kf, vf = q.float(), k.float(), v.float()
+    qn = qf / (torch.linalg.vector_norm(qf, dim=-1, keepdim=True) + eps)
+    kn = kf / (torch.linalg.vector_norm(kf, dim=-1, keepdim=True) + eps)
+    if beta is not None:
+        c = beta.float()[..., None] + eps
+        kn, vf = c * kn, c * vf
+    return qn.to(q.dtype), kn.to(k.dtype), vf.to(v.dtype)
+
+
 def gdn_gating(a: Tensor, b: Tensor, A_log: Tensor, dt_bias: Tensor, beta_scale: float = 1.0) -> Tuple[Tensor, Tensor]:
     """``g = -exp(A_log) * softplus(a + dt_bias)`` (fp32), ``beta = sigmoid(b) * beta_scale``."""
     g = -torch.exp(A_log.float()) * F.softplus(a.float() + dt_bias.float())

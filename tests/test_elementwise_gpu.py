@@ -249,3 +249,33 @@ def test_device_timer_and_step_breakdown_on_gpu():
     assert {"Attention", "GatedDeltaNetLayer", "MLP"} <= set(s) and s["MLP"]["calls"] == 2
     total = t.summary()["forward"]["total_ms"]
     assert total > 0 and sum(v["total_ms"] for v in s.values()) <= total * 1.05
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("D,with_beta", [(128, True), (64, True), (256, False), (128, False)])
+def test_gka_prepare_matches_reference(D, with_beta):
+    """Fused q / k normalisation + beta scaling against the fp32 PyTorch formulation, values and gradients."""
+    from hybrid_model_factory_b200.ops import _lib, cuda_ops
+    from hybrid_model_factory_b200.ops import reference as R
+    torch.manual_seed(D)
+    B, T, H = 2, 300, 4
+    q, k, v = (torch.randn(B, T, H, D, device="cuda").bfloat16().requires_grad_(True) for _ in range(3))
+    beta = torch.rand(B, T, H, device="cuda").bfloat16().requires_grad_(True) if with_beta else None
+    before = _lib.launch_count()
+    outs = cuda_ops.gka_prepare(q, k, v, beta, 1e-6)
+    gs = [torch.randn_like(o) for o in outs]
+    torch.autograd.backward(outs, gs)
+    assert _lib.launch_count() - before == 2
+    got = [q.grad, k.grad, v.grad] + ([beta.grad] if with_beta else [])
+    qf, kf, vf = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    bf = beta.detach().float().requires_grad_(True) if with_beta else None
+    refs = R.gka_prepare(qf, kf, vf, bf, 1e-6)
+    torch.autograd.backward(refs, [g.float() for g in gs])
+    want = [qf.grad, kf.grad, vf.grad] + ([bf.grad] if with_beta else [])
+    for o, r in zip(outs, refs):
+        assert (o.float() - r).abs().max() < 2e-2 * r.abs().max() + 1e-3
+    for g, w in zip(got, want):
+        rel = (g.float() - w).norm() / (w.norm() + 1e-12)
+        assert rel < 2e-2, float(rel)
+    torch.cuda.synchronize()
+    _lib.assert_status_ok()
