@@ -64,7 +64,10 @@ class L2AAttention(nn.Module):
     def forward(self, hidden_states, residual=None, position_embeddings=None, past_key_values=None, position_ids=None,
                 **kwargs):
         B, T, _ = hidden_states.shape
-        s, _, _ = self.local(hidden_states, position_embeddings=position_embeddings, position_ids=position_ids)
+        # generation: the local stream keeps its window of K / V under this layer's index, the global stream keeps all
+        # of its K / V under a key of its own; only the routed tokens ever read the global cache
+        s, _, _ = self.local(hidden_states, position_embeddings=position_embeddings, position_ids=position_ids,
+                             past_key_values=past_key_values)
         base = hidden_states if residual is None else residual
         h2 = self.global_norm(base + s)
         soft = torch.sigmoid(self.router(h2).float() / self.temperature)        # [B, T, 1]
@@ -77,6 +80,10 @@ class L2AAttention(nn.Module):
         self.last_routed_fraction = float(hard.mean())
         ga = self.global_attn
         q, k, v, _ = ga._qkv(h2, position_embeddings)
+        offset = 0
+        if past_key_values is not None and hasattr(past_key_values, "attention"):
+            k, v = past_key_values.update_attention(("l2a_global", self.layer_idx), k, v)
+            offset = k.shape[1] - T                 # tokens already in the cache: the new queries come after them
         leak = self.training and self.leak_prob > 0 and self._leak_coin(sp if sp_on else None) < self.leak_prob
         if leak and sp_on:
             from ..parallel.cp_attention import cp_attention
@@ -98,7 +105,7 @@ class L2AAttention(nn.Module):
                 idx = torch.nonzero(hard[b, :, 0], as_tuple=False)[:, 0]
                 if idx.numel() == 0:
                     continue
-                pos = idx if gpos is None else gpos[idx]
+                pos = idx + offset if gpos is None else gpos[idx]
                 ob = F_ops.qsparse_attention(q[b:b + 1, idx], k[b:b + 1], v[b:b + 1], pos[None], scale=ga.scaling)
                 o[b, idx] = ob[0].to(o.dtype)
         o = (o * mask[..., None].to(o.dtype)).reshape(B, T, -1)

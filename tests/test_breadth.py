@@ -744,3 +744,24 @@ def test_export_merges_adapters_quantises_and_writes_modelfile(tmp_path):
     quant = checkpoint_io.from_pretrained(str(q8), dtype=torch.float32).eval()
     err = (quant(input_ids=ids).logits - ref).abs().max() / ref.abs().max()
     assert err < 0.05
+
+
+def test_l2a_generation_with_cache_matches_full_forward():
+    """L2A keeps two caches per layer (window K/V of the local stream, all K/V of the global stream); decoding token by
+    token gives the logits of one forward over the whole sequence."""
+    from hybrid_model_factory_b200.models.cache import HybridCache
+    torch.manual_seed(0)
+    model = build_model(_cfg("L2A-GDN-L2A", l2a_config={"sliding_window": 6, "leak_prob": 0.0,
+                                                        "sigmoid_threshold": 0.45})).eval()
+    ids = torch.randint(0, 128, (1, 20))
+    with torch.no_grad():
+        full = model(input_ids=ids).logits
+        cache = HybridCache()
+        out = model(input_ids=ids[:, :11], past_key_values=cache, use_cache=True)
+        steps = [out.logits[:, -1]]
+        for t in range(11, 20):
+            out = model(input_ids=ids[:, t:t + 1], past_key_values=cache, use_cache=True)
+            steps.append(out.logits[:, -1])
+    got = torch.stack(steps, dim=1)
+    assert torch.allclose(got, full[:, 10:], atol=2e-4), float((got - full[:, 10:]).abs().max())
+    assert ("l2a_global", 0) in cache.attention and cache.attention[0][0].shape[1] <= 6
