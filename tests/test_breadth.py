@@ -765,3 +765,61 @@ def test_l2a_generation_with_cache_matches_full_forward():
     got = torch.stack(steps, dim=1)
     assert torch.allclose(got, full[:, 10:], atol=2e-4), float((got - full[:, 10:]).abs().max())
     assert ("l2a_global", 0) in cache.attention and cache.attention[0][0].shape[1] <= 6
+
+
+def test_vendor_multimodal_plugins_expand_placeholders():
+    from PIL import Image
+    from hybrid_model_factory_b200.data.mm_plugin import get_mm_plugin
+    from hybrid_model_factory_b200.data.mm_plugin_zoo import InternVLPlugin, TowerConfig, select_best_resolution
+    wide, square = Image.new("RGB", (640, 320), (200, 10, 10)), Image.new("RGB", (100, 100))
+    msgs = [{"role": "user", "content": "look <image> and <image>"}, {"role": "assistant", "content": "ok"}]
+    count = lambda out, tok: out[0]["content"].count(tok)  # noqa: E731
+    # llava: fixed 24 x 24 = 576 tokens per image
+    p = get_mm_plugin("llava", image_token="<im>")
+    assert count(p.process_messages(msgs, [wide, square]), "<im>") == 2 * 576
+    assert p.get_mm_inputs([wide, square])["pixel_values"].shape == (2, 3, 336, 336)
+    # llava-next: base + un-padded tiles + a newline token per row; a 2:1 image picks the 336 x 672 canvas
+    p = get_mm_plugin("llava_next", image_token="<im>")
+    assert select_best_resolution((320, 640), TowerConfig().grid_pinpoints) == (336, 672)
+    assert p._counts(320, 640, TowerConfig()) == 576 + 24 * 48 + 24
+    mm = p.get_mm_inputs([wide, square])
+    assert mm["pixel_values"].shape[:2] == (2, 3) and mm["image_sizes"].tolist() == [[320, 640], [100, 100]]
+    # pixtral: rows of patches separated by breaks, one end marker per image
+    p = get_mm_plugin("pixtral", image_token="[IMG]")
+    out = p.process_messages(msgs, [wide, square])
+    assert count(out, "[IMG_END]") == 2 and count(out, "[IMG]") == 40 * 20 + 7 * 7
+    assert count(out, "[IMG_BREAK]") == 19 + 6
+    # intern-vl: the 2:1 image is cut into a 2 x 1 ... grid of 448-pixel tiles plus a thumbnail, 256 tokens each
+    a, b = InternVLPlugin.tile_grid(320, 640, TowerConfig(image_size=448))
+    assert a == 2 * b
+    p = get_mm_plugin("intern_vl", image_token="<ctx>")
+    out = p.process_messages(msgs, [wide, square])
+    mm = p.get_mm_inputs([wide, square])
+    assert count(out, "<ctx>") == 256 * int(mm["image_num_patches"].sum()) and count(out, "<img>") == 2
+    assert mm["pixel_values"].shape[0] == int(mm["image_num_patches"].sum())
+    # gemma3: 256 soft tokens between the markers
+    p = get_mm_plugin("gemma3", image_token="<soft>")
+    out = p.process_messages(msgs, [wide, square])
+    assert count(out, "<soft>") == 512 and count(out, "<start_of_image>") == 2
+    # paligemma: placeholders vanish from the text, image tokens lead the ids and carry no loss
+    class Tok:
+        def convert_tokens_to_ids(self, t):
+            return 99
+    p = get_mm_plugin("paligemma", image_token="<image>")
+    out = p.process_messages(msgs, [wide, square])
+    assert "<image>" not in out[0]["content"]
+    ids, labels = p.process_token_ids([1, 2, 3], [1, 2, 3], [wide], tokenizer=Tok())
+    assert ids[:256] == [99] * 256 and labels[:256] == [-100] * 256 and ids[256:] == [1, 2, 3]
+    # mllama: one token per image and a mask that lets each token see the images before it
+    p = get_mm_plugin("mllama", image_token="<|image|>")
+    assert count(p.process_messages(msgs, [wide, square]), "<|image|>") == 2
+    mask = p.get_mm_inputs([wide], batch_ids=[[5, 7, 8, 7, 9]], image_token_id=7)["cross_attention_mask"]
+    assert mask[0, :, 0].tolist() == [0, 1, 1, 1, 1] and mask[0, :, 1].tolist() == [0, 0, 0, 1, 1]
+    # video-llava and glm4v
+    p = get_mm_plugin("video_llava", image_token="<im>", video_token="<vid>")
+    vm = [{"role": "user", "content": "<video> what happens?"}]
+    assert p.process_messages(vm, [], [[square] * 20])[0]["content"].count("<vid>") == 8 * 257
+    assert p.get_mm_inputs([], [[square] * 20])["pixel_values_videos"].shape == (1, 8, 3, 224, 224)
+    p = get_mm_plugin("glm4v", image_token="<|image|>", video_token="<|video|>")
+    out = p.process_messages(msgs, [wide, square])
+    assert count(out, "<|begin_of_image|>") == 2 and count(out, "<|image|>") > 2
