@@ -156,6 +156,7 @@ def create_app(engine: ServingEngine, tokenizer, model_name: str = "hybrid", tem
                               top_k=int(body.get("top_k", 0)), top_p=float(body.get("top_p", 1.0)),
                               min_p=float(body.get("min_p", 0.0)),
                               repetition_penalty=float(body.get("repetition_penalty", 1.0)),
+                              speculative_tokens=int(body.get("speculative_tokens", 0)),
                               eos_token_id=getattr(tokenizer, "eos_token_id", None),
                               ignore_eos=bool(body.get("ignore_eos", False)))
 

@@ -44,6 +44,8 @@ class SamplingParams:
     top_p: float = 1.0
     min_p: float = 0.0
     repetition_penalty: float = 1.0
+    speculative_tokens: int = 0       # greedy requests: up to this many drafted tokens are verified per step (drafts
+    #                                   come from the request's own text: the continuation of its latest repeated n-gram)
     eos_token_id: Optional[int] = None
     ignore_eos: bool = True
 
@@ -141,9 +143,13 @@ class ServingEngine:
             num_blocks = self._plan_blocks(n_attn, block_size, max_num_seqs, max_model_len, gpu_memory_utilization)
         snapshots = max_num_seqs if (enable_prefix_caching and has_ssm) else 0
         # one extra block and one extra slot absorb the padding rows of a bucketed (graph-captured) decode batch
-        self.state = ServingState(model, num_blocks + 1, block_size, max_num_seqs, snapshots + 1, self.device,
+        # ... and one more slot holds the recurrent state of a request while its drafted tokens are verified
+        self.state = ServingState(model, num_blocks + 1, block_size, max_num_seqs, snapshots + 2, self.device,
                                   dtype=next(model.parameters()).dtype)
         self._pad_block, self._pad_slot = num_blocks, max_num_seqs + snapshots
+        self._spec_slot = max_num_seqs + snapshots + 1
+        self.spec_ngram = (4, 2)          # longest / shortest n-gram looked up for a draft
+        self.spec_window = 4096           # how far back the lookup goes
         self.sched = NativeScheduler(num_blocks, block_size, max_num_seqs, max_num_seqs, max_num_batched_tokens,
                                      enable_prefix_caching, snapshots, require_snapshot=has_ssm,
                                      whole_prompts=whole_prompts)
@@ -154,6 +160,7 @@ class ServingEngine:
         self._layer_cache: Dict[int, dict] = {}
         self.max_blocks_per_seq = (max_model_len + block_size - 1) // block_size
         self.stats = {"steps": 0, "decode_tokens": 0, "prefill_tokens": 0, "graph_replays": 0, "decode_steps": 0, "packed_prefills": 0,
+                      "spec_steps": 0, "spec_drafted": 0, "spec_accepted": 0,
                       "decode_s": 0.0, "prefill_s": 0.0, "decode_gpu_s": 0.0}
         has_moe = any(hasattr(l.mlp, "experts") for l in model.model.layers)
         # B'MOJO-F layers decode request by request through the layer itself (bounded window state per request)
@@ -206,6 +213,22 @@ class ServingEngine:
         decodes = [s for s in batch if s.is_decode and self._at_frontier(s)]
         prefills = [s for s in batch if s not in decodes]
         results = []
+        # speculative decoding: requests with a usable draft are verified one by one (several tokens per step); the
+        # others share the batched decode step below
+        plain = []
+        for s in decodes:
+            toks = self._speculate(s)
+            if toks is None:
+                plain.append(s)
+                continue
+            for t in toks:
+                self.sched.advance(s.req_id, 1)
+                res = self._emit(s.req_id, int(t))
+                results.append(res)
+                self.stats["decode_tokens"] += 1
+                if res[2]:
+                    break
+        decodes = plain
         t0 = time.perf_counter()
         if decodes:
             logits = self._decode_forward(decodes)
@@ -268,6 +291,64 @@ class ServingEngine:
             raise _lib.KernelError(
                 f"engine step {self.stats['steps']}: a device-side wait ran out (code={code} block={block} "
                 f"detail={detail:#x} count={count}); HMF_TP_FUSED=0 selects the NCCL reductions")
+
+    # -- speculative decoding ----------------------------------------------------------------------
+    def _draft(self, seq: List[int], k: int) -> List[int]:
+        """Continuation of the latest earlier occurrence of the sequence's last n tokens (longest n first)."""
+        hi, lo = self.spec_ngram
+        start = max(0, len(seq) - self.spec_window)
+        for n in range(min(hi, len(seq) - 1), lo - 1, -1):
+            tail = seq[-n:]
+            for i in range(len(seq) - n - 1, start - 1, -1):
+                if seq[i:i + n] == tail:
+                    return seq[i + n:i + n + k]
+        return []
+
+    def _speculate(self, s: ScheduledSeq) -> Optional[List[int]]:
+        """Verifies drafted tokens for one decoding request; returns the tokens to emit (accepted drafts + the model's
+        own next token) or ``None`` when the request takes the ordinary decode step.
+
+        The drafts are run as one piece of ``1 + k`` tokens, exactly like a prefill continuation; the greedy targets of
+        all positions come out of that one forward.  Attention needs no undo (cache entries after the accepted prefix
+        are overwritten later).  The recurrent state does: it is copied to a spare slot first, and when a draft is
+        rejected it is restored and advanced again over the accepted prefix only, which is what starting from the state
+        "after ``num_accepted`` tokens" means for a recurrence (reference: ``num_accepted_tokens`` in
+        ``vllm-inference/src/primed_vllm/layers/gdn/ops/fused_recurrent_gqa.py:24-154``)."""
+        req = self.requests[s.req_id]
+        p = req.params
+        if p.speculative_tokens <= 0 or p.temperature > 0 or p.repetition_penalty != 1.0 or self.state.bmojo_layers:
+            return None
+        seq = req.prompt + req.output
+        capacity = len(self.sched.block_table(s.req_id)) * self.block_size
+        k = min(p.speculative_tokens, capacity - 1 - s.start_pos, p.max_new_tokens - len(req.output) - 1)
+        drafts = self._draft(seq, k) if k > 0 else []
+        if not drafts:
+            return None
+        has_state = bool(self.state.ssm)
+        if has_state:
+            self.state.copy_slot(s.slot, self._spec_slot)
+        tokens = [seq[s.start_pos]] + drafts
+        logits = self._piece_logits(s, tokens)
+        targets = self._sample(logits, [p] * len(tokens))
+        n_acc = 0
+        while n_acc < len(drafts) and drafts[n_acc] == targets[n_acc]:
+            n_acc += 1
+        if n_acc < len(drafts) and has_state:
+            self.state.copy_slot(self._spec_slot, s.slot)
+            self._piece_logits(s, tokens[:n_acc + 1], want_logits=False)
+        self.stats["spec_steps"] += 1
+        self.stats["spec_drafted"] += len(drafts)
+        self.stats["spec_accepted"] += n_acc
+        return targets[:n_acc + 1]
+
+    def _piece_logits(self, s: ScheduledSeq, tokens: List[int], want_logits: bool = True):
+        """Runs ``tokens`` at positions ``s.start_pos ..`` through the model with the request's caches; logits of every
+        position."""
+        ids = torch.tensor([tokens], dtype=torch.long, device=self.device)
+        pos = torch.arange(s.start_pos, s.start_pos + len(tokens), device=self.device)[None]
+        cache = SlotCache(self.state, s.slot, self.sched.block_table(s.req_id), s.start_pos, None)
+        h, _ = self.model.model(ids, position_ids=pos, past_key_values=cache, use_cache=True)
+        return self._logits(h[0]) if want_logits else None
 
     def close(self) -> None:
         """Drops the captured decode graphs.  A graph that holds NCCL kernels (tensor parallelism) keeps its

@@ -598,3 +598,48 @@ def test_engine_raises_on_a_recorded_device_wait_timeout():
     eng.check_kernel_status(lambda: (0, 0, 0, 0))
     with pytest.raises(_lib.KernelError, match="wait ran out"):
         eng.check_kernel_status(lambda: (3, 17, 0x40, 2))
+
+
+@pytest.mark.parametrize("pattern", ["*-GDN", "M2-GKA-*", "*-*"])
+def test_speculative_decoding_is_exact(pattern):
+    """Drafts from the request's own n-grams, verified in one forward; rejected drafts roll the recurrent state back.
+    The tokens equal plain greedy decoding whatever is accepted."""
+    torch.manual_seed(0)
+    model = build_model(tiny(pattern, vocab_size=24)).eval()         # a small vocabulary makes repeats (and drafts) common
+    g = torch.Generator().manual_seed(5)
+    base = torch.randint(0, 24, (6,), generator=g).tolist()
+    prompts = [base * 3, torch.randint(0, 24, (17,), generator=g).tolist(), (base[:3] * 5)[:13]]
+    outs, stats = [], []
+    for k in (0, 4):
+        eng = ServingEngine(model, block_size=8, num_blocks=64, max_num_seqs=4, max_num_batched_tokens=64,
+                            max_model_len=128)
+        outs.append(eng.generate(prompts, SamplingParams(max_new_tokens=24, speculative_tokens=k)))
+        stats.append(dict(eng.stats))
+    assert outs[0] == outs[1]
+    assert stats[0]["spec_steps"] == 0 and stats[1]["spec_steps"] > 0 and stats[1]["spec_drafted"] > 0
+    assert all(len(o) == 24 for o in outs[1])
+    assert stats[1]["steps"] <= stats[0]["steps"]
+
+
+@pytest.mark.gpu
+def test_speculative_decoding_on_gpu_kernels():
+    """bf16 kernels: the verify forward (prefill kernels) and the decode step (decode kernels) round differently, so the
+    two runs may part at a near-tie; they must agree on almost all tokens and drafts must get accepted."""
+    torch.manual_seed(0)
+    cfg = tiny("*-GDN-M2-*", hidden_size=512, intermediate_size=1024, num_attention_heads=4, num_key_value_heads=2,
+               head_dim=128, vocab_size=64)
+    model = build_model(cfg).to("cuda", torch.bfloat16).eval()
+    g = torch.Generator().manual_seed(5)
+    base = torch.randint(0, 64, (8,), generator=g).tolist()
+    prompts = [base * 6, torch.randint(0, 64, (70,), generator=g).tolist(), (base[:4] * 20)[:75]]
+    outs, stats = [], []
+    for k in (0, 4):
+        eng = ServingEngine(model, block_size=64, num_blocks=32, max_num_seqs=4, max_num_batched_tokens=256,
+                            max_model_len=512)
+        outs.append(eng.generate(prompts, SamplingParams(max_new_tokens=32, speculative_tokens=k)))
+        stats.append(dict(eng.stats))
+    from hybrid_model_factory_b200.ops import _lib
+    _lib.assert_status_ok()
+    agree = sum(a == b for x, y in zip(*outs) for a, b in zip(x, y))
+    assert stats[1]["spec_steps"] > 0 and all(len(o) == 32 for o in outs[1])
+    assert all(x[0] == y[0] for x, y in zip(*outs)) and agree >= 0.7 * 96, (agree, outs)
