@@ -100,6 +100,7 @@ class RunArguments:
     pure_bf16: bool = True
     fp8: bool = False
     disable_gradient_checkpointing: bool = False
+    recompute_budget: str = "auto"             # auto | off | fraction of the device memory that un-checkpointed layers may fill
     deepspeed: Optional[str] = None                    # accepted; ZeRO stage is read from the JSON ("zero_optimization.stage")
     ddp_timeout: int = 180000000
     report_to: str = "none"

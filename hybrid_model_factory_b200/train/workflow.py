@@ -82,7 +82,8 @@ def to_trainer_args(model_args, data_args, run_args, n_batches: Optional[int]) -
         gradient_accumulation_steps=run_args.gradient_accumulation_steps,
         sequence_parallel_size=model_args.sequence_parallel_size, sequence_parallel_mode=model_args.sequence_parallel_mode,
         bf16=run_args.bf16, pure_bf16=run_args.pure_bf16,
-        disable_gradient_checkpointing=run_args.disable_gradient_checkpointing, logging_steps=run_args.logging_steps,
+        disable_gradient_checkpointing=run_args.disable_gradient_checkpointing,
+        recompute_budget=str(run_args.recompute_budget), logging_steps=run_args.logging_steps,
         save_steps=run_args.save_steps, eval_steps=run_args.eval_steps, save_only_model=run_args.save_only_model,
         save_max_shard_size=run_args.save_max_shard_size, seed=run_args.seed,
         resume_from_checkpoint=run_args.resume_from_checkpoint, ddp_timeout=run_args.ddp_timeout,
