@@ -15,7 +15,7 @@ import torch.nn as nn
 from ..ops import functional as F_ops
 from ..parallel.cp_attention import cp_attention
 from ..parallel.sp import halo_exchange
-from .common import RMSNorm
+from .common import RMSNorm, input_proj, output_proj
 
 
 class Attention(nn.Module):
@@ -44,17 +44,19 @@ class Attention(nn.Module):
         else:
             self.q_norm = self.k_norm = None
 
-    def _qkv(self, hidden_states, position_embeddings):
+    INPUT_PROJECTIONS, OUTPUT_PROJECTION = ("q_proj", "k_proj", "v_proj"), "o_proj"
+
+    def _qkv(self, hidden_states, position_embeddings, kw=None):
         B, T, _ = hidden_states.shape
-        q = self.q_proj(hidden_states)
+        q = input_proj(self, "q_proj", hidden_states, kw)
         gate = None
         if self.gated:
             q = q.view(B, T, self.num_heads, 2 * self.head_dim)
             q, gate = q[..., : self.head_dim], q[..., self.head_dim:].reshape(B, T, -1)
         else:
             q = q.view(B, T, self.num_heads, self.head_dim)
-        k = self.k_proj(hidden_states).view(B, T, self.num_kv_heads, self.head_dim)
-        v = self.v_proj(hidden_states).view(B, T, self.num_kv_heads, self.head_dim)
+        k = input_proj(self, "k_proj", hidden_states, kw).view(B, T, self.num_kv_heads, self.head_dim)
+        v = input_proj(self, "v_proj", hidden_states, kw).view(B, T, self.num_kv_heads, self.head_dim)
         if not self.gated and q.is_cuda and (self.q_norm is not None or position_embeddings is not None):
             from ..ops import cuda_ops
             if cuda_ops.heads_norm_rope_ok(q, self.head_dim, position_embeddings):
@@ -78,7 +80,7 @@ class Attention(nn.Module):
     def forward(self, hidden_states: torch.Tensor, position_embeddings=None, past_key_values=None,
                 position_ids: Optional[torch.Tensor] = None, **kwargs) -> Tuple[torch.Tensor, None, object]:
         B, T, _ = hidden_states.shape
-        q, k, v, gate = self._qkv(hidden_states, position_embeddings)
+        q, k, v, gate = self._qkv(hidden_states, position_embeddings, kwargs)
         sp = self.sequence_parallel_group
         if sp is not None and sp.size > 1:
             if getattr(sp, "mode", "zigzag") == "ulysses":
@@ -105,7 +107,7 @@ class Attention(nn.Module):
         o = o.reshape(B, T, -1)
         if gate is not None:
             o = o * torch.sigmoid(gate)
-        return self.o_proj(o), None, past_key_values
+        return output_proj(self, "o_proj", o, kwargs), None, past_key_values
 
     def _swa_sp(self, q, k, v, sp):
         """Sliding-window attention under zig-zag SP: each segment needs the ``window-1`` keys

@@ -166,6 +166,24 @@ class ShortConvolution(nn.Module):
         return res, None
 
 
+def input_proj(module: nn.Module, name: str, x: torch.Tensor, kw: Optional[dict]) -> torch.Tensor:
+    """Projection ``name`` of a mixer applied to the layer input ``x``, or its precomputed result when the caller
+    (a packed prefill: ``models/modeling_hybrid.py::DecoderLayer``) already applied it to the whole packed row and
+    passes this sample's slice in ``kw["pre_proj"]``."""
+    pre = None if kw is None else kw.get("pre_proj")
+    if pre is not None and name in pre:
+        return pre[name]
+    return getattr(module, name)(x)
+
+
+def output_proj(module: nn.Module, name: str, y: torch.Tensor, kw: Optional[dict]) -> torch.Tensor:
+    """Output projection of a mixer, left to the caller when ``kw["defer_out_proj"]`` is set (one GEMM over the
+    packed row instead of one per sample)."""
+    if kw is not None and kw.get("defer_out_proj"):
+        return y
+    return getattr(module, name)(y)
+
+
 def repeat_heads(x: torch.Tensor, n_rep: int) -> torch.Tensor:
     """``[B, T, H, D] -> [B, T, H*n_rep, D]`` with each head repeated consecutively."""
     if n_rep == 1:

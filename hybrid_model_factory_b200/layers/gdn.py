@@ -22,7 +22,7 @@ import torch.nn as nn
 from ..ops import functional as F_ops
 from ..ops import mixers
 from ..parallel.sp import merge_segments, segments_with_halo
-from .common import GatedRMSNorm, LinearLowRank, RMSNorm, ShortConvolution, init_dt_bias, repeat_heads
+from .common import GatedRMSNorm, LinearLowRank, RMSNorm, ShortConvolution, init_dt_bias, input_proj, output_proj, repeat_heads
 
 
 @dataclass
@@ -143,11 +143,13 @@ class GatedDeltaNet(nn.Module):
             k_res, v_res = repeat_heads(kh, self.num_k_groups), repeat_heads(vh, self.num_v_groups)
         return k_res + self.proj_k(k).view(B, T, H, D), v_res + self.proj_v(v).view(B, T, H, D)
 
+    INPUT_PROJECTIONS, OUTPUT_PROJECTION = ("q_proj", "k_proj", "v_proj", "gk_proj", "b_proj", "g_proj"), "o_proj"
+
     def forward(self, hidden_states: torch.Tensor, past_key_values=None, use_cache: bool = False, **kwargs):
         sp = self.sequence_parallel_group
         B, T, _ = hidden_states.shape
         last = past_key_values.get_ssm(self.layer_idx) if past_key_values is not None else None
-        q, k, v = self.q_proj(hidden_states), self.k_proj(hidden_states), self.v_proj(hidden_states)
+        q, k, v = (input_proj(self, n, hidden_states, kwargs) for n in ("q_proj", "k_proj", "v_proj"))
         new_conv = None
         if self.use_short_conv:
             if sp is not None and sp.size > 1:
@@ -169,7 +171,8 @@ class GatedDeltaNet(nn.Module):
         q = q.reshape(B, T, self.num_q_heads, self.head_dim)
         k, v = self._expand_kv(k, v)
         q = repeat_heads(q, self.num_q_groups)
-        g, beta = F_ops.gdn_gating(self.gk_proj(hidden_states), self.b_proj(hidden_states), self.A_log, self.dt_bias,
+        g, beta = F_ops.gdn_gating(input_proj(self, "gk_proj", hidden_states, kwargs),
+                                   input_proj(self, "b_proj", hidden_states, kwargs), self.A_log, self.dt_bias,
                                    2.0 if self.allow_neg_eigval else 1.0)
         state0 = last["recurrent_state"] if last is not None else None
         o, state = mixers.gated_delta_rule(q, k, v, g, beta, initial_state=state0, sp=sp, chunk_size=self.chunk_size,
@@ -185,11 +188,11 @@ class GatedDeltaNet(nn.Module):
             extra = {} if transition is None else {"transition": transition}
             past_key_values.update_ssm(self.layer_idx, recurrent_state=state, conv_state=new_conv, offset=T, **extra)
         if self.use_gate:
-            gate = self.g_proj(hidden_states).view(B, T, self.expanded_num_heads, self.head_dim)
+            gate = input_proj(self, "g_proj", hidden_states, kwargs).view(B, T, self.expanded_num_heads, self.head_dim)
             o = self.o_norm(o.to(hidden_states.dtype), gate)
         else:
             o = self.o_norm(o.to(hidden_states.dtype))
-        return self.o_proj(o.reshape(B, T, self.expanded_dim)), None, past_key_values
+        return output_proj(self, "o_proj", o.reshape(B, T, self.expanded_dim), kwargs), None, past_key_values
 
 
 class GatedDeltaNetLayer(GatedDeltaNet):

@@ -19,7 +19,7 @@ import torch.nn as nn
 from ..ops import functional as F_ops
 from ..ops import mixers
 from ..parallel.sp import merge_segments, segments_with_halo
-from .common import GatedRMSNorm, LinearLowRank, RMSNorm, ShortConvolution, init_dt_bias, repeat_heads
+from .common import GatedRMSNorm, LinearLowRank, RMSNorm, ShortConvolution, init_dt_bias, input_proj, output_proj, repeat_heads
 
 
 @dataclass
@@ -137,11 +137,14 @@ class GatedKalmaNet(nn.Module):
 
     _expand_kv = None  # assigned below (shared with GatedDeltaNet)
 
+    INPUT_PROJECTIONS = ("q_proj", "k_proj", "v_proj", "a_proj", "b_proj", "alpha_proj", "g_proj")
+    OUTPUT_PROJECTION = "o_proj"
+
     def forward(self, hidden_states: torch.Tensor, past_key_values=None, use_cache: bool = False, **kwargs):
         sp = self.sequence_parallel_group
         B, T, _ = hidden_states.shape
         last = past_key_values.get_ssm(self.layer_idx) if past_key_values is not None else None
-        q, k, v = self.q_proj(hidden_states), self.k_proj(hidden_states), self.v_proj(hidden_states)
+        q, k, v = (input_proj(self, n, hidden_states, kwargs) for n in ("q_proj", "k_proj", "v_proj"))
         new_conv = None
         if sp is not None and sp.size > 1:
             parts, convs = [q, k], [self.q_conv1d, self.k_conv1d]
@@ -167,12 +170,13 @@ class GatedKalmaNet(nn.Module):
         q = repeat_heads(q.reshape(B, T, self.num_q_heads, self.head_dim), self.num_q_groups)
         k, v = self._expand_kv(k, v)
         # unit-norm q and k, beta gate on k and v: one pass over the three tensors (`ops/cuda_ops.py::gka_prepare`)
-        beta = torch.sigmoid(self.b_proj(hidden_states)) if self.use_beta_gate else None
+        beta = torch.sigmoid(input_proj(self, "b_proj", hidden_states, kwargs)) if self.use_beta_gate else None
         q, k, v = F_ops.gka_prepare(q, k, v, beta, 1e-6)
-        alpha = torch.sigmoid(self.alpha_proj(hidden_states)) if self.use_alpha_connection else None
+        alpha = (torch.sigmoid(input_proj(self, "alpha_proj", hidden_states, kwargs))
+                 if self.use_alpha_connection else None)
         if self.use_forgetting_gate:
             g = -self.A_log.float().exp() * torch.nn.functional.softplus(
-                self.a_proj(hidden_states).float() + self.dt_bias.float())
+                input_proj(self, "a_proj", hidden_states, kwargs).float() + self.dt_bias.float())
         else:
             g = torch.zeros(B, T, self.expanded_num_heads, device=q.device, dtype=torch.float32)
         gk = g if (self.use_forgetting_gate and self.use_forgetting_gate_kk) else None
@@ -184,11 +188,11 @@ class GatedKalmaNet(nn.Module):
         if past_key_values is not None:
             past_key_values.update_ssm(self.layer_idx, recurrent_state=state, conv_state=new_conv, offset=T)
         if self.use_gate:
-            gate = self.g_proj(hidden_states).view(B, T, self.expanded_num_heads, self.head_dim)
+            gate = input_proj(self, "g_proj", hidden_states, kwargs).view(B, T, self.expanded_num_heads, self.head_dim)
             o = self.o_norm(o.to(hidden_states.dtype), gate)
         else:
             o = self.o_norm(o.to(hidden_states.dtype))
-        return self.o_proj(o.reshape(B, T, self.expanded_dim)), None, past_key_values
+        return output_proj(self, "o_proj", o.reshape(B, T, self.expanded_dim), kwargs), None, past_key_values
 
 
 from .gdn import GatedDeltaNet as _GDN  # noqa: E402

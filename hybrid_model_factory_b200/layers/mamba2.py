@@ -19,7 +19,7 @@ import torch.nn.functional as F
 from ..ops import functional as F_ops
 from ..ops import mixers
 from ..parallel.sp import merge_segments, segments_with_halo
-from .common import GatedRMSNorm, RMSNorm, init_dt_bias, repeat_heads
+from .common import GatedRMSNorm, RMSNorm, init_dt_bias, input_proj, output_proj, repeat_heads
 
 
 @dataclass
@@ -113,12 +113,14 @@ class Mamba2(nn.Module):
             Bm, Cm = F_ops.apply_rope(Bm, cos, sin), F_ops.apply_rope(Cm, cos, sin)
         return torch.cat([x, Bm.reshape(Bsz, T, -1), Cm.reshape(Bsz, T, -1)], dim=-1)
 
+    INPUT_PROJECTIONS, OUTPUT_PROJECTION = ("in_proj",), "out_proj"
+
     def forward(self, hidden_states: torch.Tensor, past_key_values=None, position_embeddings=None,
                 use_cache: bool = False, **kwargs):
         sp = self.sequence_parallel_group
         Bsz, T, _ = hidden_states.shape
         last = past_key_values.get_ssm(self.layer_idx) if past_key_values is not None else None
-        zxbcdt = self.in_proj(hidden_states)
+        zxbcdt = input_proj(self, "in_proj", hidden_states, kwargs)
         if zxbcdt.shape[-1] != self.in_proj_valid:
             zxbcdt = zxbcdt[..., :self.in_proj_valid]
         z, xBC, dt = torch.split(zxbcdt, [self.d_inner, self.conv_dim, self.nheads], dim=-1)
@@ -155,7 +157,7 @@ class Mamba2(nn.Module):
         zg = z.reshape(Bsz, T, self.nheads, self.headdim)
         wn = self.norm.weight.view(self.nheads, self.headdim)
         y = F_ops.gated_rms_norm(y, zg, wn, self.norm.eps, norm_before_gate=False)
-        return self.out_proj(y.reshape(Bsz, T, self.d_inner)), None, past_key_values
+        return output_proj(self, "out_proj", y.reshape(Bsz, T, self.d_inner), kwargs), None, past_key_values
 
 
 class Mamba2Layer(Mamba2):

@@ -169,16 +169,35 @@ class DecoderLayer(nn.Module):
             # nor recurrent state crosses a sample boundary.  `sample_caches` (serving: the prefill pieces of several
             # requests in one forward) gives every sample its own cache
             parts = []
+            mixer = self.seq_mixer
+            # inference: the projections that read the layer input run ONCE on the packed row (one GEMM each instead of
+            # one per sample), and so does the output projection afterwards; the samples only differ in the mixer core
+            pre_all, out_name = {}, None
+            if caches is not None and not torch.is_grad_enabled() and hasattr(mixer, "INPUT_PROJECTIONS"):
+                for n in mixer.INPUT_PROJECTIONS:
+                    m = getattr(mixer, n, None)
+                    if isinstance(m, nn.Linear):
+                        pre_all[n] = m(h)
+                # (a mixer with forward hooks -- tensor parallelism sums its partial outputs there -- must return its
+                # finished output, so its output projection stays inside)
+                if isinstance(getattr(mixer, mixer.OUTPUT_PROJECTION, None), nn.Linear) and not mixer._forward_hooks:
+                    out_name = mixer.OUTPUT_PROJECTION
             for j, (a, b) in enumerate(zip(cu[:-1], cu[1:])):
                 pe = None if position_embeddings is None else tuple(t[:, a:b] for t in position_embeddings)
                 kw = dict(kwargs)
                 if "residual" in kw:
                     kw["residual"] = kw["residual"][:, a:b]
+                if pre_all:
+                    kw["pre_proj"] = {n: y[:, a:b] for n, y in pre_all.items()}
+                if out_name:
+                    kw["defer_out_proj"] = True
                 pkv = None if caches is None else caches[j]
-                parts.append(self.seq_mixer(h[:, a:b], position_embeddings=pe,
-                                            position_ids=None if position_ids is None else position_ids[:, a:b],
-                                            past_key_values=pkv, use_cache=pkv is not None, **kw)[0])
+                parts.append(mixer(h[:, a:b], position_embeddings=pe,
+                                   position_ids=None if position_ids is None else position_ids[:, a:b],
+                                   past_key_values=pkv, use_cache=pkv is not None, **kw)[0])
             h = torch.cat(parts, dim=1)
+            if out_name:
+                h = getattr(mixer, out_name)(h)
         else:
             h, _, _ = self.seq_mixer(h, position_embeddings=position_embeddings, position_ids=position_ids,
                                      past_key_values=past_key_values, use_cache=use_cache, **kwargs)
