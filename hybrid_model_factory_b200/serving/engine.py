@@ -832,7 +832,9 @@ class ServingEngine:
     def _mamba_decode(self, i, mx: Mamba2, h, cos, sin, slots):
         Rn = h.shape[0]
         c = self._layer_consts(i, mx)
-        zx = mx.in_proj(h)
+        # the projection's rows padded to whole 128-row tiles, so the decode GEMM kernel takes it
+        pk = self._packed(("in", i), [mx.in_proj]) if (self._cuda and h.dtype == torch.bfloat16) else {"w": None}
+        zx = gemm_ops.linear(h, pk["w"], pk["b"]) if pk["w"] is not None else mx.in_proj(h)
         z, xBC, dt = torch.split(zx if zx.shape[-1] == mx.in_proj_valid else zx[:, :mx.in_proj_valid],
                                  [mx.d_inner, mx.conv_dim, mx.nheads], dim=-1)
         rope = mx.use_pos_emb and cos is not None
