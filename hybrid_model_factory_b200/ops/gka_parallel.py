@@ -17,6 +17,49 @@ import torch
 Tensor = torch.Tensor
 
 
+def _prefix_kernel(U: Tensor, gl: Tensor, h0: Optional[Tensor]) -> Tensor:
+    """``states[n + 1] = e^{gl[n]} states[n] + U[n]`` from ``states[0] = h0`` (zeros when ``None``): ``U [B,H,N,E]``,
+    ``gl [B,H,N]``, all fp32 and contiguous -> ``[B,H,N+1,E]``.  One bandwidth-bound pass of the decayed prefix-sum
+    kernel (``csrc/kernels/gdn_scan.cu::gla_segment_prefix_kernel``)."""
+    import ctypes
+    from . import _lib
+    B, Hh, N, E = U.shape
+    states = torch.empty(B, Hh, N + 1, E, device=U.device, dtype=torch.float32)
+    ll = ctypes.c_longlong
+    _lib.check(_lib.kernels().hmf_gla_segment_prefix(
+        _lib.ptr(U), _lib.ptr(gl), _lib.ptr(h0), _lib.ptr(states), ctypes.c_void_p(states.data_ptr() + N * E * 4),
+        ctypes.c_int(N), ctypes.c_int(B * Hh), ctypes.c_int(1), ctypes.c_int(E), ll(E), ll(N * E), ll(1), ll(N),
+        ll(E), ll((N + 1) * E), ll((N + 1) * E), _lib.stream_ptr(U.device)), "gla_segment_prefix")
+    return states
+
+
+class _DecayedPrefix(torch.autograd.Function):
+    """Differentiable form of :func:`_prefix_kernel`.  The gradient obeys the same recurrence run backwards
+    (``R[n] = dS[n] + e^{gl[n]} R[n + 1]``), so the backward pass is the same kernel on the flipped sequence:
+    ``dU[n] = R[n + 1]``, ``dgl[n] = e^{gl[n]} <R[n + 1], S[n]>``, ``dh0 = R[0]``.  Replaces a ``[N + 1, N]`` weight
+    product whose cost grows with the square of the number of chunks (2048 chunks at 128K tokens)."""
+
+    @staticmethod
+    def forward(ctx, U, gl, h0):
+        U, gl = U.float().contiguous(), gl.float().contiguous()
+        h0c = None if h0 is None else h0.float().contiguous()
+        states = _prefix_kernel(U, gl, h0c)
+        ctx.save_for_backward(states, gl)
+        ctx.has_h0 = h0 is not None
+        return states
+
+    @staticmethod
+    def backward(ctx, dS):
+        states, gl = ctx.saved_tensors
+        N = gl.shape[-1]
+        dS = dS.float()
+        Q = _prefix_kernel(dS[:, :, :N].flip(2).contiguous(), gl.flip(-1).contiguous(), dS[:, :, N].contiguous())
+        Rv = Q.flip(2)                                              # R[0 .. N]
+        dU = Rv[:, :, 1:]
+        dgl = torch.exp(gl) * (dU * states[:, :, :N]).sum(-1)
+        return dU, dgl, (Rv[:, :, 0] if ctx.has_h0 else None)
+
+
 def chunk_states(k: Tensor, G: Tensor, H0: Optional[Tensor]) -> Tensor:
     """``k [B,H,N,C,D]``, inclusive in-chunk cumulative gates ``G [B,H,N,C]`` -> states ``[B,H,N+1,D,D]``
     (state at the start of chunk ``n``; index ``N`` is the final state)."""
@@ -24,21 +67,19 @@ def chunk_states(k: Tensor, G: Tensor, H0: Optional[Tensor]) -> Tensor:
     Glast = G[..., -1]                                            # [B,H,N]
     kdec = k * torch.exp(Glast[..., None] - G)[..., None]
     U = kdec.transpose(-1, -2) @ k                                # [B,H,N,D,D] contribution of chunk m at its end
-    if k.is_cuda and not torch.is_grad_enabled() and B * Hh <= 65535:
-        # no graph to record: one pass of the decayed prefix-sum kernel instead of the [N+1, N] weight product
-        import ctypes
+    if k.is_cuda and B * Hh <= 65535:
+        # one pass of the decayed prefix-sum kernel (and one more, backwards, for the gradient) instead of the
+        # [N+1, N] weight product
         from . import _lib
         if _lib.use_cuda_kernels(k):
-            U = U.contiguous()
-            gl = Glast.float().contiguous()
-            h0 = None if H0 is None else H0.float().contiguous()
-            states = torch.empty(B, Hh, N + 1, D, D, device=k.device, dtype=torch.float32)
-            E, ll = D * D, ctypes.c_longlong
-            _lib.check(_lib.kernels().hmf_gla_segment_prefix(
-                _lib.ptr(U), _lib.ptr(gl), _lib.ptr(h0), _lib.ptr(states), ctypes.c_void_p(states.data_ptr() + N * E * 4),
-                ctypes.c_int(N), ctypes.c_int(B * Hh), ctypes.c_int(1), ctypes.c_int(E), ll(E), ll(N * E), ll(1), ll(N),
-                ll(E), ll((N + 1) * E), ll((N + 1) * E), _lib.stream_ptr(k.device)), "gla_segment_prefix")
-            return states
+            h0 = None if H0 is None else H0.reshape(B, Hh, D * D)
+            Uf = U.reshape(B, Hh, N, D * D)
+            if torch.is_grad_enabled() and (Uf.requires_grad or Glast.requires_grad or (h0 is not None and h0.requires_grad)):
+                states = _DecayedPrefix.apply(Uf, Glast, h0)
+            else:
+                states = _prefix_kernel(Uf.float().contiguous(), Glast.float().contiguous(),
+                                        None if h0 is None else h0.float().contiguous())
+            return states.view(B, Hh, N + 1, D, D)
     tot = torch.cumsum(Glast, dim=-1)                             # log decay up to the end of chunk m
     tot0 = torch.cat([torch.zeros_like(tot[..., :1]), tot], dim=-1)          # [B,H,N+1]: up to the start of chunk n
     # state_n = e^{tot0_n} H0 + sum_{m<n} e^{tot0_n - tot_m} U_m

@@ -223,3 +223,33 @@ def test_gla_segment_parallel_inference_scan_matches_sequential(T, H, with_state
     torch.cuda.synchronize()
     assert (o_seg.float() - o_ref.float()).abs().max() < 2e-2 * o_ref.float().abs().max() + 1e-2
     assert (h_seg - h_ref).abs().max() < 2e-2 * h_ref.abs().max() + 1e-2
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("with_h0", [False, True])
+def test_gka_chunk_states_prefix_kernel_with_gradients(with_h0):
+    """Chunk-start states of the key covariance: the decayed prefix-sum kernel (forward, and backward on the flipped
+    sequence) against the quadratic weight-product formulation on the CPU in fp64."""
+    from hybrid_model_factory_b200.ops import _lib
+    from hybrid_model_factory_b200.ops.gka_parallel import chunk_states
+    torch.manual_seed(3)
+    B, H, N, C, D = 1, 3, 9, 16, 32
+    k = (torch.randn(B, H, N, C, D) * 0.3)
+    G = torch.cumsum(-torch.rand(B, H, N, C) * 0.1, dim=-1)
+    H0 = torch.randn(B, H, D, D) * 0.2 if with_h0 else None
+    leaves_ref = [t.double().requires_grad_(True) if t is not None else None for t in (k, G, H0)]
+    ref = chunk_states(*leaves_ref)                      # CPU: the weight-product formulation
+    w = torch.randn_like(ref)
+    (ref * w).sum().backward()
+    leaves = [t.cuda().requires_grad_(True) if t is not None else None for t in (k, G, H0)]
+    before = _lib.launch_count()
+    out = chunk_states(*leaves)
+    (out * w.cuda().float()).sum().backward()
+    assert _lib.launch_count() - before == 2             # one prefix pass each way
+    assert (out.double().cpu() - ref).abs().max() < 1e-4 * ref.abs().max() + 1e-5
+    for a, b in zip(leaves, leaves_ref):
+        if a is not None:
+            err = (a.grad.double().cpu() - b.grad).norm() / (b.grad.norm() + 1e-12)
+            assert err < 1e-4, float(err)
+    torch.cuda.synchronize()
+    _lib.assert_status_ok()
