@@ -93,6 +93,10 @@ def launch(argv: List[str]) -> int:
         from .priming.reassemble_vlm import reassemble_vlm
         reassemble_vlm(rest[0], rest[1], rest[2])
         return 0
+    if cmd == "train" and os.environ.get("USE_V1", "0") == "1":
+        # the second-generation stack (data engine, resumable batch generator, token-weighted trainer)
+        from .v1.launcher import main as v1_main
+        return v1_main(rest)
     if cmd in ("train", "train-multinode") and os.environ.get("USE_RAY", "0") == "1":
         # Ray placement-group launch: one actor per GPU (RAY_NUM_WORKERS, default: every GPU of the cluster)
         from .launcher_ray import launch as ray_launch

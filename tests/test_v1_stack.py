@@ -107,3 +107,27 @@ def test_v1_trainer_token_weighting_and_resume(tmp_path):
     assert abs(la - lb) < 1e-5
     ta.fit()
     assert ta.global_step == 3
+
+
+def test_v1_launcher_runs_from_yaml(tmp_path):
+    """``USE_V1=1 hmf train cfg.yaml``: loads a checkpoint, trains two steps on a dataset description, saves a model
+    that loads again."""
+    from hybrid_model_factory_b200.utils import checkpoint_io
+    from hybrid_model_factory_b200.v1.launcher import main
+    torch.manual_seed(0)
+    cfg = HybridConfig("hybrid_qwen3", vocab_size=259, hidden_size=32, intermediate_size=64, num_hidden_layers=2,
+                       num_attention_heads=2, num_key_value_heads=1, head_dim=16, hybrid_override_pattern="*-GDN")
+    checkpoint_io.save_pretrained(build_model(cfg), str(tmp_path / "model"))
+    _engine(tmp_path)                                            # writes mix.yaml and its data files
+    out = tmp_path / "out"
+    (tmp_path / "run.yaml").write_text(
+        f"model: {tmp_path / 'model'}\ntrain_dataset: {tmp_path / 'mix.yaml'}\noutput_dir: {out}\n"
+        "micro_batch_size: 2\nglobal_batch_size: 4\nmax_steps: 2\nbf16: false\ncutoff_len: 48\n"
+        "batching_strategy: padding_free\nlearning_rate: 1.0e-3\n")
+    assert main([str(tmp_path / "run.yaml"), "lr_scheduler=constant"]) == 0
+    again = checkpoint_io.from_pretrained(str(out), dtype=torch.float32)
+    assert again.config.num_hidden_layers == 2
+    import pytest
+    with pytest.raises(ValueError, match="unknown configuration keys"):
+        (tmp_path / "bad.yaml").write_text(f"model: {tmp_path / 'model'}\ntrain_dataset: x\nno_such_key: 1\n")
+        main([str(tmp_path / "bad.yaml")])
