@@ -144,8 +144,9 @@ class ServingEngine:
         snapshots = max_num_seqs if (enable_prefix_caching and has_ssm) else 0
         # one extra block and one extra slot absorb the padding rows of a bucketed (graph-captured) decode batch
         # ... and one more slot holds the recurrent state of a request while its drafted tokens are verified
-        self.state = ServingState(model, num_blocks + 1, block_size, max_num_seqs, snapshots + 2, self.device,
-                                  dtype=next(model.parameters()).dtype)
+        self._spec_slots = min(max_num_seqs, 8)       # requests whose drafts are verified in the same step
+        self.state = ServingState(model, num_blocks + 1, block_size, max_num_seqs, snapshots + 1 + self._spec_slots,
+                                  self.device, dtype=next(model.parameters()).dtype)
         self._pad_block, self._pad_slot = num_blocks, max_num_seqs + snapshots
         self._spec_slot = max_num_seqs + snapshots + 1
         self.spec_ngram = (4, 2)          # longest / shortest n-gram looked up for a draft
@@ -213,14 +214,10 @@ class ServingEngine:
         decodes = [s for s in batch if s.is_decode and self._at_frontier(s)]
         prefills = [s for s in batch if s not in decodes]
         results = []
-        # speculative decoding: requests with a usable draft are verified one by one (several tokens per step); the
-        # others share the batched decode step below
-        plain = []
-        for s in decodes:
-            toks = self._speculate(s)
-            if toks is None:
-                plain.append(s)
-                continue
+        # speculative decoding: the requests with a usable draft are verified together in one packed forward (several
+        # tokens each); the others share the batched decode step below
+        decodes, verified = self._speculate(decodes)
+        for s, toks in verified:
             for t in toks:
                 self.sched.advance(s.req_id, 1)
                 res = self._emit(s.req_id, int(t))
@@ -228,7 +225,6 @@ class ServingEngine:
                 self.stats["decode_tokens"] += 1
                 if res[2]:
                     break
-        decodes = plain
         t0 = time.perf_counter()
         if decodes:
             logits = self._decode_forward(decodes)
@@ -304,51 +300,72 @@ class ServingEngine:
                     return seq[i + n:i + n + k]
         return []
 
-    def _speculate(self, s: ScheduledSeq) -> Optional[List[int]]:
-        """Verifies drafted tokens for one decoding request; returns the tokens to emit (accepted drafts + the model's
-        own next token) or ``None`` when the request takes the ordinary decode step.
+    def _speculate(self, decodes: List[ScheduledSeq]):
+        """Verifies drafted tokens for the decoding requests that have some.  Returns ``(plain, verified)``: the
+        requests left to the ordinary decode step, and ``(request, tokens to emit)`` pairs (accepted drafts + the
+        model's own next token).
 
-        The drafts are run as one piece of ``1 + k`` tokens, exactly like a prefill continuation; the greedy targets of
-        all positions come out of that one forward.  Attention needs no undo (cache entries after the accepted prefix
-        are overwritten later).  The recurrent state does: it is copied to a spare slot first, and when a draft is
-        rejected it is restored and advanced again over the accepted prefix only, which is what starting from the state
-        "after ``num_accepted`` tokens" means for a recurrence (reference: ``num_accepted_tokens`` in
+        Each request's drafts run as one piece of ``1 + k`` tokens, exactly like a prefill continuation, all pieces of
+        the step packed into one forward; the greedy targets of every position come out of it.  Attention needs no undo
+        (cache entries after the accepted prefix are overwritten later).  The recurrent state does: it is copied to a
+        spare slot first, and after a rejection it is restored and advanced again over the accepted prefix only (one
+        more packed forward for all rejected requests), which is what starting from the state "after ``num_accepted``
+        tokens" means for a recurrence (reference: ``num_accepted_tokens`` in
         ``vllm-inference/src/primed_vllm/layers/gdn/ops/fused_recurrent_gqa.py:24-154``)."""
-        req = self.requests[s.req_id]
-        p = req.params
-        if p.speculative_tokens <= 0 or p.temperature > 0 or p.repetition_penalty != 1.0 or self.state.bmojo_layers:
-            return None
-        seq = req.prompt + req.output
-        capacity = len(self.sched.block_table(s.req_id)) * self.block_size
-        k = min(p.speculative_tokens, capacity - 1 - s.start_pos, p.max_new_tokens - len(req.output) - 1)
-        drafts = self._draft(seq, k) if k > 0 else []
-        if not drafts:
-            return None
+        plain, cand = [], []
+        for s in decodes:
+            req = self.requests[s.req_id]
+            p = req.params
+            drafts: List[int] = []
+            if (p.speculative_tokens > 0 and p.temperature <= 0 and p.repetition_penalty == 1.0
+                    and not self.state.bmojo_layers and len(cand) < self._spec_slots):
+                seq = req.prompt + req.output
+                capacity = len(self.sched.block_table(s.req_id)) * self.block_size
+                k = min(p.speculative_tokens, capacity - 1 - s.start_pos, p.max_new_tokens - len(req.output) - 1)
+                drafts = self._draft(seq, k) if k > 0 else []
+            if drafts:
+                cand.append((s, [(req.prompt + req.output)[s.start_pos]] + drafts))
+            else:
+                plain.append(s)
+        if not cand:
+            return plain, []
         has_state = bool(self.state.ssm)
         if has_state:
-            self.state.copy_slot(s.slot, self._spec_slot)
-        tokens = [seq[s.start_pos]] + drafts
-        logits = self._piece_logits(s, tokens)
-        targets = self._sample(logits, [p] * len(tokens))
-        n_acc = 0
-        while n_acc < len(drafts) and drafts[n_acc] == targets[n_acc]:
-            n_acc += 1
-        if n_acc < len(drafts) and has_state:
-            self.state.copy_slot(self._spec_slot, s.slot)
-            self._piece_logits(s, tokens[:n_acc + 1], want_logits=False)
+            for j, (s, _) in enumerate(cand):
+                self.state.copy_slot(s.slot, self._spec_slot + j)
+        logits, cu = self._pieces_forward(cand)
+        params = [self.requests[s.req_id].params for s, toks in cand for _ in toks]
+        targets = self._sample(logits, params)
+        verified, redo = [], []
+        for j, (s, toks) in enumerate(cand):
+            mine, drafts = targets[cu[j]:cu[j + 1]], toks[1:]
+            n_acc = 0
+            while n_acc < len(drafts) and drafts[n_acc] == mine[n_acc]:
+                n_acc += 1
+            if n_acc < len(drafts) and has_state:
+                self.state.copy_slot(self._spec_slot + j, s.slot)
+                redo.append((s, toks[:n_acc + 1]))
+            self.stats["spec_drafted"] += len(drafts)
+            self.stats["spec_accepted"] += n_acc
+            verified.append((s, mine[:n_acc + 1]))
+        if redo:
+            self._pieces_forward(redo, want_logits=False)
         self.stats["spec_steps"] += 1
-        self.stats["spec_drafted"] += len(drafts)
-        self.stats["spec_accepted"] += n_acc
-        return targets[:n_acc + 1]
+        return plain, verified
 
-    def _piece_logits(self, s: ScheduledSeq, tokens: List[int], want_logits: bool = True):
-        """Runs ``tokens`` at positions ``s.start_pos ..`` through the model with the request's caches; logits of every
-        position."""
-        ids = torch.tensor([tokens], dtype=torch.long, device=self.device)
-        pos = torch.arange(s.start_pos, s.start_pos + len(tokens), device=self.device)[None]
-        cache = SlotCache(self.state, s.slot, self.sched.block_table(s.req_id), s.start_pos, None)
-        h, _ = self.model.model(ids, position_ids=pos, past_key_values=cache, use_cache=True)
-        return self._logits(h[0]) if want_logits else None
+    def _pieces_forward(self, items, want_logits: bool = True):
+        """One packed forward over ``(request, tokens)`` pieces, each continuing its request at ``start_pos`` with the
+        request's caches.  Returns ``(logits of every position, piece boundaries)``."""
+        toks, pos, cu, caches = [], [], [0], []
+        for s, t in items:
+            toks += t
+            pos += list(range(s.start_pos, s.start_pos + len(t)))
+            cu.append(len(toks))
+            caches.append(SlotCache(self.state, s.slot, self.sched.block_table(s.req_id), s.start_pos, None))
+        ids = torch.tensor([toks], dtype=torch.long, device=self.device)
+        pid = torch.tensor([pos], dtype=torch.long, device=self.device)
+        h, _ = self.model.model(ids, position_ids=pid, cu_seqlens=cu, sample_caches=caches)
+        return (self._logits(h[0]) if want_logits else None), cu
 
     def close(self) -> None:
         """Drops the captured decode graphs.  A graph that holds NCCL kernels (tensor parallelism) keeps its
