@@ -22,9 +22,11 @@ USAGE = """usage: hmf <command> [args]
   convert-qwen-gdn SRC OUT [--pattern P] convert a Qwen3-Next / Qwen3.5-MoE checkpoint to the hybrid layout
   train CONFIG.yaml [k=v ...]    run a training stage (pt | sft | hkd | dpo | kto | rm)
   train-multinode CONFIG.yaml    same, expecting NNODES / NODE_RANK / MASTER_ADDR in the environment
+                                 (USE_RAY=1: Ray actors instead of torchrun; USE_V1=1: the second-generation SFT stack)
   preprocess --config CFG.yaml   tokenise (and SP-split) datasets into `tokenized_path`, sharded and parallel
   eval CKPT --task T_split ...   multiple-choice benchmark evaluation (few-shot, accuracy per category)
-  export CKPT OUT [--dtype D]    re-shard / cast a checkpoint
+  export CKPT OUT [--dtype D] [--merge-lora] [--quantize int8|int4] [--ollama]
+                                 re-shard / cast a checkpoint, fold adapters in, quantise, write an Ollama Modelfile
   serve CKPT [--tp N --port P]   OpenAI-compatible server on the native engine (--tp N: tensor parallel over N GPUs)
   api CKPT                       alias of serve
   chat CKPT                      interactive chat in the terminal
