@@ -80,6 +80,59 @@ __global__ void rms_norm_fwd_kernel(const bf16* __restrict__ x, const bf16* __re
   }
 }
 
+// Few rows (decode steps): one 256-thread block per row, the row held in registers between the sum and the scaling
+// (D <= 8192), so a row costs one read and one write and its latency is spread over eight warps.
+__global__ void __launch_bounds__(256)
+rms_norm_fwd_rows_kernel(const bf16* __restrict__ x, const bf16* __restrict__ res, const bf16* __restrict__ w,
+                         bf16* __restrict__ y, bf16* __restrict__ res_out, float* __restrict__ rstd_out, int D,
+                         float eps, int zero_centered) {
+  __shared__ float s_part[8];
+  const long long row = blockIdx.x;
+  const int t = threadIdx.x;
+  float f[4][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const int c = (u * 256 + t) * 8;
+    if (c < D) {
+      load8(x + row * D + c, f[u]);
+      if (res != nullptr) {
+        float r[8];
+        load8(res + row * D + c, r);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[u][i] = __bfloat162float(__float2bfloat16(f[u][i] + r[i]));
+        store8(res_out + row * D + c, f[u]);
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss += f[u][i] * f[u][i];
+    }
+  }
+  ss = warp_sum(ss);
+  if ((t & 31) == 0) s_part[t >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) tot += s_part[i];
+  const float rstd = rsqrtf(tot / D + eps);
+  if (t == 0 && rstd_out) rstd_out[row] = rstd;
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const int c = (u * 256 + t) * 8;
+    if (c < D) {
+      if (w) {
+        float g[8];
+        load8(w + c, g);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[u][i] = f[u][i] * rstd * (zero_centered ? 1.f + g[i] : g[i]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[u][i] *= rstd;
+      }
+      store8(y + row * D + c, f[u]);
+    }
+  }
+}
+
 // backward, input gradient: dx = rstd * (w dy - xhat * mean(w dy xhat)); one warp per row.
 __global__ void rms_norm_bwd_dx_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w,
                                        const bf16* __restrict__ dy, const float* __restrict__ rstd,
@@ -761,6 +814,12 @@ HMF_API int hmf_rms_norm_fwd(const void* x, const void* res, const void* w, void
                              cudaStream_t st) {
   HMF_REQUIRE(D % 8 == 0 && D > 0, "rms_norm: D=%d must be a positive multiple of 8", D);
   if (N == 0) return HMF_OK;
+  if (N <= 1024 && D >= 1024 && D <= 8192) {          // too few rows to fill the GPU with one warp each
+    rms_norm_fwd_rows_kernel<<<(unsigned)N, 256, 0, st>>>((const bf16*)x, (const bf16*)res, (const bf16*)w, (bf16*)y,
+                                                         (bf16*)res_out, rstd, D, eps, zero_centered);
+    HMF_CHECK_CUDA(cudaGetLastError());
+    return HMF_OK;
+  }
   const int warps = 8;
   const long long blocks = (N + warps - 1) / warps;
   rms_norm_fwd_kernel<<<(unsigned)blocks, warps * 32, 0, st>>>((const bf16*)x, (const bf16*)res,

@@ -263,7 +263,7 @@ def bench_paged_decode(args):
     lens = torch.full((Rn,), L, dtype=torch.int32, device="cuda")
     q = torch.randn(Rn, H, D, device="cuda", dtype=torch.bfloat16)
     o = torch.empty_like(q)
-    for splits in (1, 2, 4, 8):
+    for splits in (1, 2, 4, 8, 16):
         po = torch.empty(Rn, H, splits, D, device="cuda", dtype=torch.float32)
         pml = torch.empty(Rn, H, splits, 2, device="cuda", dtype=torch.float32)
 

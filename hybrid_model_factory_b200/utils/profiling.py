@@ -82,6 +82,9 @@ def phase(name: str):
         yield
         return
     key = f"{name}#{len(PHASES._pairs[name])}"
+    if key in PHASES._open:         # the same phase entered again inside itself (a scan whose backward runs another
+        yield                       # scan): the outer interval already covers it
+        return
     PHASES.start(key)
     try:
         yield

@@ -29,7 +29,7 @@ def _grad_pair(fn_cuda, fn_ref, inputs, names):
         _close(a.grad, b.grad, rtol=3e-2, atol=3e-2 * max(1.0, b.grad.abs().max().item()) * 0.5, name=f"d{n}")
 
 
-@pytest.mark.parametrize("N,D,zc", [(1000, 4096, False), (4096 * 4, 128, False), (513, 2048, True)])
+@pytest.mark.parametrize("N,D,zc", [(1000, 4096, False), (4096 * 4, 128, False), (513, 2048, True), (2100, 4096, True), (3, 8192, False)])
 def test_rms_norm(N, D, zc):
     x = torch.randn(N, D, device=DEV).bfloat16()
     w = (torch.randn(D, device=DEV) * 0.1 + (0 if zc else 1)).bfloat16()
