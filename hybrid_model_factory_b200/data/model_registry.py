@@ -50,7 +50,7 @@ _COMPILED = [(re.compile(p), t) for p, t in _RULES]
 def template_for_model(name_or_path: Optional[str], base_model: bool = False) -> Optional[str]:
     """Template of the family ``name_or_path`` belongs to, or ``None`` when no family matches.  ``base_model``:
     pretrained (non-chat) checkpoints are fine-tuned with the plain ``default`` template."""
-    if not name_or_path:
+    if not name_or_path or name_or_path.lstrip().startswith("{"):      # nothing, or an inline JSON configuration
         return None
     name = os.path.basename(os.path.normpath(name_or_path)).lower()
     if base_model or re.search(r"(^|[-_])base($|[-_])", name):

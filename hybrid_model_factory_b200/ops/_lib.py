@@ -108,13 +108,15 @@ def stream_ptr(device=None) -> ctypes.c_void_p:
 
 
 def ptr(t: torch.Tensor | None) -> ctypes.c_void_p:
-    """Device address of ``t`` for a kernel argument.  The kernels read and write 16 bytes at a time, so a tensor of 16
-    bytes or more must start on a 16-byte boundary; a view that does not (a column slice of a one-row matrix counts as
-    contiguous and keeps its odd offset) is refused here, on the host, instead of faulting on the device."""
+    """Device address of ``t`` for a kernel argument.  The kernels read and write 8- and 16-bit data 16 bytes at a
+    time, so such a tensor of 16 bytes or more must start on a 16-byte boundary; a view that does not (a column slice
+    of a one-row matrix counts as contiguous and keeps its odd offset) is refused here, on the host, instead of
+    faulting on the device.  Index, label and fp32 side inputs are read element by element and only need their natural
+    alignment, which every view has."""
     if t is None:
         return ctypes.c_void_p(0)
     p = t.data_ptr()
-    if (p & 15) and t.is_cuda and t.numel() * t.element_size() >= 16:
+    if (p & 15) and t.is_cuda and t.element_size() <= 2 and t.numel() * t.element_size() >= 16:
         raise ValueError(f"tensor of shape {tuple(t.shape)} ({t.dtype}) starts at {p:#x}, not on a 16-byte boundary: "
                          "clone the view before handing it to a kernel")
     return ctypes.c_void_p(p)

@@ -54,9 +54,12 @@ class FlatAdamW:
         no_decay = [p for p in self.params if getattr(p, "_no_weight_decay", False) or p.dim() < 2]
         self.params = decay + no_decay
         align = 128 * self.world
-        n_decay = sum(p.numel() for p in decay)
+        # every parameter starts on a 16-byte boundary of the flat buffers (8 elements also covers fp32): the kernels
+        # read weights 16 bytes at a time, and a [4]-element gate vector must not shift what follows it
+        pad8 = lambda n: (n + 7) // 8 * 8  # noqa: E731
+        n_decay = sum(pad8(p.numel()) for p in decay)
         self.n_decay = (n_decay + align - 1) // align * align
-        n_rest = sum(p.numel() for p in no_decay)
+        n_rest = sum(pad8(p.numel()) for p in no_decay)
         self.n_total = self.n_decay + (n_rest + align - 1) // align * align
         self.flat_param = torch.zeros(self.n_total, device=self.device, dtype=self.dtype)
         self.flat_grad = torch.zeros(self.n_total, device=self.device, dtype=self.grad_dtype)
@@ -69,7 +72,7 @@ class FlatAdamW:
             p.data = self.flat_param[off:off + n].view(p.shape)
             p.grad = self.flat_grad[off:off + n].view(p.shape) if self.grad_dtype == self.dtype else None
             p._flat_offset = off
-            off += n
+            off += pad8(n)
         self.shard = self.n_total // self.world
         lo = self.rank * self.shard
         self._shard_slice = slice(lo, lo + self.shard)

@@ -60,15 +60,17 @@ class _Unit:
         self.params = [self.params[i] for i in order]
         self.shapes = [self.shapes[i] for i in order]
         self.numels = [self.numels[i] for i in order]
-        self.n_decay = sum(n for p, n in zip(self.params, self.numels) if not self._no_decay(p))
-        n = sum(self.numels)
+        # every parameter starts on a 16-byte boundary of the flat buffer (the kernels read weights 16 bytes at a time)
+        self.slots = [(k + 7) // 8 * 8 for k in self.numels]
+        self.n_decay = sum(n for p, n in zip(self.params, self.slots) if not self._no_decay(p))
+        n = sum(self.slots)
         self.n_pad = (n + align * world - 1) // (align * world) * (align * world)
         self.shard_len = self.n_pad // world
         full = torch.zeros(self.n_pad, device=self.device, dtype=self.dtype)
         off = 0
-        for p, k in zip(self.params, self.numels):
+        for p, k, slot in zip(self.params, self.numels, self.slots):
             full[off:off + k].copy_(p.data.reshape(-1))
-            off += k
+            off += slot
         self.shard = full[rank * self.shard_len:(rank + 1) * self.shard_len].clone()
         self.grad_shard: Optional[torch.Tensor] = None
         self.full: Optional[torch.Tensor] = None
@@ -92,9 +94,9 @@ class _Unit:
         else:
             self.full.copy_(self.shard)
         off = 0
-        for p, k, shp in zip(self.params, self.numels, self.shapes):
+        for p, k, shp, slot in zip(self.params, self.numels, self.shapes, self.slots):
             p.data = self.full[off:off + k].view(shp)
-            off += k
+            off += slot
 
     def release(self) -> None:
         self.full = None
@@ -114,11 +116,11 @@ class _Unit:
         """All parameters of the unit have their gradient: flatten, reduce-scatter, free."""
         flat = torch.zeros(self.n_pad, device=self.device, dtype=self.dtype)
         off = 0
-        for p, k in zip(self.params, self.numels):
+        for p, k, slot in zip(self.params, self.numels, self.slots):
             if p.grad is not None:
                 flat[off:off + k].copy_(p.grad.reshape(-1))
                 p.grad = None
-            off += k
+            off += slot
         if self.world > 1:
             out = torch.empty(self.shard_len, device=self.device, dtype=self.dtype)
             _reduce_scatter_flat(out, flat, self.rank, self.group)
