@@ -404,3 +404,32 @@ def _zero3_gpu_worker(rank, world, offload):
 @pytest.mark.parametrize("offload", [False, True], ids=["device_state", "host_state"])
 def test_zero3_over_nccl(world, offload):
     run_ranks(_zero3_gpu_worker, world, offload, backend="nccl", timeout=240)
+
+
+def _sp_workflow_gpu_worker(rank, world, out_dir):
+    """`hmf train` under sequence parallelism on GPUs, bf16 kernels, peer-memory state chain, ZeRO-sharded AdamW."""
+    import json
+    import os
+    from hybrid_model_factory_b200.ops import _lib
+    from hybrid_model_factory_b200.train.workflow import run_exp
+    small = {"model_type": "hybrid_qwen3", "vocab_size": 512, "hidden_size": 512, "intermediate_size": 1024,
+             "num_hidden_layers": 4, "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 128,
+             "hybrid_override_pattern": "*-GDN-M2-GKA", "torch_dtype": "bfloat16"}
+    cfg = {"model_name_or_path": json.dumps(small), "stage": "pt", "synthetic": True, "cutoff_len": 2048, "max_steps": 3,
+           "output_dir": os.path.join(out_dir, "sp"), "bf16": True, "pure_bf16": True, "learning_rate": 1e-3,
+           "lr_scheduler_type": "constant", "per_device_train_batch_size": 1, "sequence_parallel_size": world,
+           "logging_steps": 1, "save_steps": 2, "seed": 7}
+    tr = run_exp(cfg)
+    torch.cuda.synchronize()
+    _lib.assert_status_ok()
+    assert tr.global_step == 3 and tr.sp.size == world
+    if rank == 0:
+        log = [json.loads(l)["loss"] for l in open(os.path.join(out_dir, "sp", "trainer_log.jsonl"))]
+        assert len(log) == 3 and all(l == l and l < 20 for l in log), log
+        assert os.path.exists(os.path.join(out_dir, "sp", "checkpoint-2", "model.safetensors"))
+    dist.barrier()
+
+
+@pytest.mark.parametrize("world", WORLDS[:2])
+def test_training_workflow_under_sequence_parallelism(world, tmp_path):
+    run_ranks(_sp_workflow_gpu_worker, world, str(tmp_path), backend="nccl", timeout=240)

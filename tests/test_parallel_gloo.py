@@ -198,3 +198,38 @@ def test_zero3_matches_single_process_adamw(offload, checkpointing):
 def test_zero3_mics_shards_inside_groups_of_two():
     """Four ranks, parameters sharded over pairs and replicated across the two pairs (MiCS)."""
     run_ranks(_zero3_worker, 4, False, True, 2)
+
+
+def _sp_workflow_worker(rank, world, out_dir, ref_losses):
+    """`hmf train` with sequence_parallel_size = world: every rank takes its zig-zag share of each sample; the logged
+    losses equal the single-process run of the same configuration."""
+    import json
+    import os
+    from hybrid_model_factory_b200.train.workflow import run_exp
+    tiny = {"model_type": "hybrid_qwen3", "vocab_size": 259, "hidden_size": 32, "intermediate_size": 64,
+            "num_hidden_layers": 3, "num_attention_heads": 2, "num_key_value_heads": 1, "head_dim": 16,
+            "hybrid_override_pattern": "*-GDN-M2", "torch_dtype": "float32"}
+    cfg = {"model_name_or_path": json.dumps(tiny), "stage": "pt", "synthetic": True, "cutoff_len": 64, "max_steps": 3,
+           "output_dir": os.path.join(out_dir, "sp"), "bf16": False, "pure_bf16": False, "learning_rate": 1e-3,
+           "lr_scheduler_type": "constant", "per_device_train_batch_size": 1, "sequence_parallel_size": world,
+           "logging_steps": 1, "seed": 7}
+    tr = run_exp(cfg)
+    assert tr.global_step == 3 and tr.sp is not None and tr.sp.size == world
+    if rank == 0:
+        log = [json.loads(l)["loss"] for l in open(os.path.join(out_dir, "sp", "trainer_log.jsonl"))]
+        assert all(abs(a - b) < 2e-3 for a, b in zip(log, ref_losses)), (log, ref_losses)
+
+
+def test_training_workflow_under_sequence_parallelism(tmp_path):
+    import json
+    import os
+    from hybrid_model_factory_b200.train.workflow import run_exp
+    tiny = {"model_type": "hybrid_qwen3", "vocab_size": 259, "hidden_size": 32, "intermediate_size": 64,
+            "num_hidden_layers": 3, "num_attention_heads": 2, "num_key_value_heads": 1, "head_dim": 16,
+            "hybrid_override_pattern": "*-GDN-M2", "torch_dtype": "float32"}
+    cfg = {"model_name_or_path": json.dumps(tiny), "stage": "pt", "synthetic": True, "cutoff_len": 64, "max_steps": 3,
+           "output_dir": str(tmp_path / "one"), "bf16": False, "pure_bf16": False, "learning_rate": 1e-3,
+           "lr_scheduler_type": "constant", "per_device_train_batch_size": 1, "logging_steps": 1, "seed": 7}
+    run_exp(cfg)
+    ref = [json.loads(l)["loss"] for l in open(os.path.join(str(tmp_path / "one"), "trainer_log.jsonl"))]
+    run_ranks(_sp_workflow_worker, 2, str(tmp_path), ref)
