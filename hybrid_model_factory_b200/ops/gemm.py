@@ -102,7 +102,13 @@ def skinny_gemm(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] =
     st = _skinny_state.get(dev.index)
     if st is None:      # partial / flag scratch of the K-split reduction (unused when one split covers K)
         st = _skinny_state[dev.index] = PeerGemmAllReduce(None, 256, 16384, dev)     # fp32 partials: half the capacity
-    splits = st._splits(N, K) if N <= st.max_n // 2 else 1
+    # K splits put more CTAs on the weight stream when the weight has few 128-row tiles; two CTAs fit on an SM, so
+    # up to 296 are resident at once.  The splits of a tile form one cluster and meet in shared memory.
+    splits, tiles = 1, N // 128
+    if N <= st.max_n // 2:
+        while (splits < st.MAX_SPLIT and tiles * splits * 2 <= 296 and K % (splits * 2 * 64) == 0
+               and K // (splits * 2) >= 256):
+            splits *= 2
     y = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
     c_int, c_ll = ctypes.c_int, ctypes.c_longlong
     _lib.check(_lib.kernels().hmf_gemm_skinny(

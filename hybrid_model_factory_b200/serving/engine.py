@@ -60,6 +60,8 @@ class RequestState:
     first_token_time: Optional[float] = None
     finish_time: Optional[float] = None
     finished: bool = False
+    ngram_index: dict = field(default_factory=dict)     # speculative decoding: n-gram -> end of its latest occurrence
+    ngram_upto: int = 0
 
 
 def sample_tokens(logits: torch.Tensor, params: List[SamplingParams], histories=None,
@@ -150,7 +152,6 @@ class ServingEngine:
         self._pad_block, self._pad_slot = num_blocks, max_num_seqs + snapshots
         self._spec_slot = max_num_seqs + snapshots + 1
         self.spec_ngram = (4, 2)          # longest / shortest n-gram looked up for a draft
-        self.spec_window = 4096           # how far back the lookup goes
         self.sched = NativeScheduler(num_blocks, block_size, max_num_seqs, max_num_seqs, max_num_batched_tokens,
                                      enable_prefix_caching, snapshots, require_snapshot=has_ssm,
                                      whole_prompts=whole_prompts)
@@ -292,15 +293,20 @@ class ServingEngine:
                 f"detail={detail:#x} count={count}); HMF_TP_FUSED=0 selects the NCCL reductions")
 
     # -- speculative decoding ----------------------------------------------------------------------
-    def _draft(self, seq: List[int], k: int) -> List[int]:
-        """Continuation of the latest earlier occurrence of the sequence's last n tokens (longest n first)."""
+    def _draft(self, req: "RequestState", seq: List[int], k: int) -> List[int]:
+        """Continuation of the latest earlier occurrence of the sequence's last n tokens (longest n first).  The
+        request keeps an index ``n-gram -> end of its latest occurrence`` that grows with the sequence, so a lookup
+        costs a few dictionary reads whatever the context length."""
         hi, lo = self.spec_ngram
-        start = max(0, len(seq) - self.spec_window)
+        index, upto = req.ngram_index, req.ngram_upto
+        for e in range(max(upto, lo), len(seq)):              # n-grams that end before the last token
+            for n in range(lo, min(hi, e) + 1):
+                index[tuple(seq[e - n:e])] = e
+        req.ngram_upto = len(seq)
         for n in range(min(hi, len(seq) - 1), lo - 1, -1):
-            tail = seq[-n:]
-            for i in range(len(seq) - n - 1, start - 1, -1):
-                if seq[i:i + n] == tail:
-                    return seq[i + n:i + n + k]
+            e = index.get(tuple(seq[-n:]))
+            if e is not None:
+                return seq[e:e + k]
         return []
 
     def _speculate(self, decodes: List[ScheduledSeq]):
@@ -325,7 +331,7 @@ class ServingEngine:
                 seq = req.prompt + req.output
                 capacity = len(self.sched.block_table(s.req_id)) * self.block_size
                 k = min(p.speculative_tokens, capacity - 1 - s.start_pos, p.max_new_tokens - len(req.output) - 1)
-                drafts = self._draft(seq, k) if k > 0 else []
+                drafts = self._draft(req, seq, k) if k > 0 else []
             if drafts:
                 cand.append((s, [(req.prompt + req.output)[s.start_pos]] + drafts))
             else:

@@ -74,7 +74,7 @@ def bench_gemm_skinny(args):
     iterations; the weight read is the algorithmic traffic)."""
     import torch.nn.functional as F
     from ..ops.gemm import skinny_gemm
-    shapes = ((4096, 4096), (24576, 4096), (4096, 12288), (151936, 4096))
+    shapes = ((4096, 4096), (6144, 4096), (10368, 4096), (24576, 4096), (4096, 12288), (151936, 4096))
     rows = (1, 16, 64)
     if args.skinny_shape:                  # "N,K,M": one case (profiler captures)
         n, k, m = (int(v) for v in args.skinny_shape.split(","))
