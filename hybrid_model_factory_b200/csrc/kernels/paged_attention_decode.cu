@@ -54,6 +54,8 @@ __device__ __forceinline__ void named_bar_sync(int id, int count) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
 }
 
+constexpr int kMinSplitTiles = 16;     // 2048 cached tokens per KV split at least
+
 __global__ void __launch_bounds__(192, 1)
 paged_attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                             const Params p) {
@@ -80,9 +82,12 @@ paged_attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
   const int lo = p.window > 0 ? max(0, L - p.window) : 0;
   const int tile_first = lo / TT;
   const int tiles_total = (L + TT - 1) / TT - tile_first;
-  const int per = (tiles_total + nsp - 1) / nsp;
+  // a row uses as many of the launch's KV splits as it has pieces of kMinSplitTiles tiles: long rows are cut finer
+  // than short ones, so the CTAs of a batch with mixed context lengths carry similar amounts of work
+  const int nsp_r = max(1, min(nsp, (tiles_total + kMinSplitTiles - 1) / kMinSplitTiles));
+  const int per = (tiles_total + nsp_r - 1) / nsp_r;
   const int t_begin = tile_first + sp * per;
-  const int n_tiles = max(0, min(per, tile_first + tiles_total - t_begin));
+  const int n_tiles = sp < nsp_r ? max(0, min(per, tile_first + tiles_total - t_begin)) : 0;
 
   if (n_tiles == 0) {   // CTA-uniform: nothing to do for this split
     if (threadIdx.x < G) {

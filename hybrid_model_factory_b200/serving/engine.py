@@ -544,7 +544,9 @@ class ServingEngine:
         while sp < 64 and ctas * sp < 148 and sp * 256 < max_len:
             sp *= 2
         if sp == 1 and max_len >= 4096:
-            sp = 2          # long contexts: two splits balance rows of unequal length better (4.76 against 4.52 TB/s)
+            # long contexts: two splits balance rows of unequal length better (17.2 against 17.75 ms per decode step of
+            # the serving workload; four splits, with the kernel's one-split-per-2048-tokens rule, gave 17.4 ms)
+            sp = 2
         return sp
 
     def _decode_inputs(self, rows: int, mb: int) -> dict:
