@@ -16,9 +16,11 @@ namespace gka_prep {
 
 using bf16 = __nv_bfloat16;
 
-__device__ __forceinline__ float warp_sum_f(float v) {
+// sum over the `group` consecutive lanes that share a row (group = 8, 16 or 32)
+__device__ __forceinline__ float group_sum_f(float v, int group) {
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  for (int o = 16; o > 0; o >>= 1)
+    if (o < group) v += __shfl_xor_sync(0xffffffffu, v, o);
   return v;
 }
 
@@ -47,11 +49,11 @@ __global__ void __launch_bounds__(256)
 fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const bf16* __restrict__ v,
            const float* __restrict__ beta, bf16* __restrict__ qn, bf16* __restrict__ kn, bf16* __restrict__ vn,
            float* __restrict__ nq, float* __restrict__ nk, long long N, int D, long long sq, long long sk,
-           long long sv, float eps) {
-  const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31, c = lane * 8;
-  if (row >= N) return;
-  const bool on = c < D;
+           long long sv, float eps, int group) {
+  // `group` lanes per row: a warp covers 32 / group rows, so narrow heads still use every lane
+  const int lane = threadIdx.x & 31, sub = lane % group, c = sub * 8;
+  const long long row = ((long long)blockIdx.x * 8 + (threadIdx.x >> 5)) * (32 / group) + lane / group;
+  const bool on = row < N && c < D;
   float a[8], b[8], d[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) a[i] = b[i] = d[i] = 0.f;
@@ -66,7 +68,8 @@ fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const bf16* _
     s1 = fmaf(a[i], a[i], s1);
     s2 = fmaf(b[i], b[i], s2);
   }
-  const float n1 = sqrtf(warp_sum_f(s1)), n2 = sqrtf(warp_sum_f(s2));
+  const float n1 = sqrtf(group_sum_f(s1, group)), n2 = sqrtf(group_sum_f(s2, group));
+  if (row >= N) return;
   const float cf = beta ? beta[row] + eps : 1.f;
   const float r1 = 1.f / (n1 + eps), r2 = cf / (n2 + eps);
 #pragma unroll
@@ -80,7 +83,7 @@ fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const bf16* _
     st8(kn + row * D + c, b);
     st8(vn + row * D + c, d);
   }
-  if (lane == 0) {
+  if (sub == 0) {
     nq[row] = n1;
     nk[row] = n2;
   }
@@ -91,11 +94,10 @@ bwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const bf16* _
            const float* __restrict__ beta, const float* __restrict__ nq, const float* __restrict__ nk,
            const bf16* __restrict__ gq, const bf16* __restrict__ gk, const bf16* __restrict__ gv,
            bf16* __restrict__ dq, bf16* __restrict__ dk, bf16* __restrict__ dv, float* __restrict__ dbeta,
-           long long N, int D, long long sq, long long sk, long long sv, float eps) {
-  const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31, c = lane * 8;
-  if (row >= N) return;
-  const bool on = c < D;
+           long long N, int D, long long sq, long long sk, long long sv, float eps, int group) {
+  const int lane = threadIdx.x & 31, sub = lane % group, c = sub * 8;
+  const long long row = ((long long)blockIdx.x * 8 + (threadIdx.x >> 5)) * (32 / group) + lane / group;
+  const bool on = row < N && c < D;
   float a[8], b[8], d[8], ga[8], gb[8], gd[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) a[i] = b[i] = d[i] = ga[i] = gb[i] = gd[i] = 0.f;
@@ -114,9 +116,10 @@ bwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const bf16* _
     dot_k = fmaf(gb[i], b[i], dot_k);
     dot_v = fmaf(gd[i], d[i], dot_v);
   }
-  dot_q = warp_sum_f(dot_q);
-  dot_k = warp_sum_f(dot_k);
-  dot_v = warp_sum_f(dot_v);
+  dot_q = group_sum_f(dot_q, group);
+  dot_k = group_sum_f(dot_k, group);
+  dot_v = group_sum_f(dot_v, group);
+  if (row >= N) return;
   const float n1 = nq[row], n2 = nk[row];
   const float cf = beta ? beta[row] + eps : 1.f;
   const float r1 = 1.f / (n1 + eps), r2 = 1.f / (n2 + eps);
@@ -134,7 +137,7 @@ bwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const bf16* _
     st8(dk + row * D + c, b);
     st8(dv + row * D + c, d);
   }
-  if (dbeta && lane == 0) dbeta[row] = dot_k * r2 + dot_v;
+  if (dbeta && sub == 0) dbeta[row] = dot_k * r2 + dot_v;
 }
 
 }  // namespace gka_prep
@@ -150,9 +153,11 @@ HMF_API int hmf_gka_prep_fwd(const void* q, const void* k, const void* v, const 
   HMF_REQUIRE(D % 8 == 0 && D > 0 && D <= 256, "gka_prep: head dimension %d unsupported (multiple of 8 up to 256)", D);
   HMF_REQUIRE(sq % 8 == 0 && sk % 8 == 0 && sv % 8 == 0, "gka_prep: row strides must be multiples of 8 elements");
   if (N == 0) return HMF_OK;
-  gka_prep::fwd_kernel<<<(unsigned)((N + 7) / 8), 256, 0, st>>>(
+  const int group = D <= 64 ? 8 : (D <= 128 ? 16 : 32);
+  const long long rows_per_block = 8 * (32 / group);
+  gka_prep::fwd_kernel<<<(unsigned)((N + rows_per_block - 1) / rows_per_block), 256, 0, st>>>(
       (const gka_prep::bf16*)q, (const gka_prep::bf16*)k, (const gka_prep::bf16*)v, beta, (gka_prep::bf16*)qn,
-      (gka_prep::bf16*)kn, (gka_prep::bf16*)vn, nq, nk, N, D, sq, sk, sv, eps);
+      (gka_prep::bf16*)kn, (gka_prep::bf16*)vn, nq, nk, N, D, sq, sk, sv, eps, group);
   HMF_CHECK_CUDA(cudaGetLastError());
   return HMF_OK;
 }
@@ -165,10 +170,12 @@ HMF_API int hmf_gka_prep_bwd(const void* q, const void* k, const void* v, const 
   HMF_REQUIRE(D % 8 == 0 && D > 0 && D <= 256, "gka_prep: head dimension %d unsupported (multiple of 8 up to 256)", D);
   HMF_REQUIRE(sq % 8 == 0 && sk % 8 == 0 && sv % 8 == 0, "gka_prep: row strides must be multiples of 8 elements");
   if (N == 0) return HMF_OK;
-  gka_prep::bwd_kernel<<<(unsigned)((N + 7) / 8), 256, 0, st>>>(
+  const int group = D <= 64 ? 8 : (D <= 128 ? 16 : 32);
+  const long long rows_per_block = 8 * (32 / group);
+  gka_prep::bwd_kernel<<<(unsigned)((N + rows_per_block - 1) / rows_per_block), 256, 0, st>>>(
       (const gka_prep::bf16*)q, (const gka_prep::bf16*)k, (const gka_prep::bf16*)v, beta, nq, nk,
       (const gka_prep::bf16*)gq, (const gka_prep::bf16*)gk, (const gka_prep::bf16*)gv, (gka_prep::bf16*)dq,
-      (gka_prep::bf16*)dk, (gka_prep::bf16*)dv, dbeta, N, D, sq, sk, sv, eps);
+      (gka_prep::bf16*)dk, (gka_prep::bf16*)dv, dbeta, N, D, sq, sk, sv, eps, group);
   HMF_CHECK_CUDA(cudaGetLastError());
   return HMF_OK;
 }

@@ -90,6 +90,25 @@ def bench_gemm_skinny(args):
         del w
 
 
+def bench_gka_prep(args):
+    """GKA input preparation (q / k normalisation, beta gate): fused kernels against the eager formulation."""
+    from ..ops import cuda_ops
+    from ..ops import reference as R
+    T, H, D = args.seq, args.heads, 128
+    q, k, v = (torch.randn(1, T, H, D, device="cuda").bfloat16() for _ in range(3))
+    beta = torch.rand(1, T, H, device="cuda").bfloat16()
+    nbytes = 6.0 * T * H * D * 2
+    ms = time_fn(lambda: cuda_ops.gka_prepare(q, k, v, beta, 1e-6), iters=10)
+    report(f"gka_prepare kernel T={T} H={H} D={D}", ms, bytes_=nbytes)
+    ms = time_fn(lambda: R.gka_prepare(q, k, v, beta, 1e-6), iters=5)
+    report(f"gka_prepare eager PyTorch T={T} H={H} D={D}", ms, bytes_=nbytes)
+    qg, kg, vg = (t.clone().requires_grad_(True) for t in (q, k, v))
+    outs = cuda_ops.gka_prepare(qg, kg, vg, beta, 1e-6)
+    gs = [torch.randn_like(o) for o in outs]
+    ms = time_fn(lambda: torch.autograd.grad(outs, (qg, kg, vg), gs, retain_graph=True), iters=10)
+    report(f"gka_prepare backward kernel T={T} H={H} D={D}", ms, bytes_=9.0 * T * H * D * 2)
+
+
 def bench_gemm(args):
     from ..ops.gemm import gemm
     M = N = K = args.size
@@ -277,7 +296,7 @@ def bench_paged_decode(args):
                bytes_=2.0 * Rn * L * Hkv * D * 2)
 
 
-CASES = {"gemm_skinny": bench_gemm_skinny, "gemm_step": bench_gemm_step, "gemm_fp8": bench_gemm_fp8, "gka_cheb": bench_gka_cheb, "paged_decode": bench_paged_decode, "gemm": bench_gemm, "attention_fwd": bench_attention_fwd, "attention_bwd": bench_attention_bwd,
+CASES = {"gka_prep": bench_gka_prep, "gemm_skinny": bench_gemm_skinny, "gemm_step": bench_gemm_step, "gemm_fp8": bench_gemm_fp8, "gka_cheb": bench_gka_cheb, "paged_decode": bench_paged_decode, "gemm": bench_gemm, "attention_fwd": bench_attention_fwd, "attention_bwd": bench_attention_bwd,
          "gdn_fwd": bench_gdn_fwd, "gdn_fwd_bwd": bench_gdn_fwd_bwd, "rmsnorm": bench_rmsnorm, "swiglu": bench_swiglu,
          "conv1d": bench_conv1d}
 
