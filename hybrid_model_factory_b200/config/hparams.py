@@ -162,6 +162,9 @@ class FinetuningArguments:
     use_dora: bool = False                     # weight-decomposed LoRA (trainable row magnitudes)
     pissa_init: bool = False                   # adapters start as the principal singular directions of the weight
     pissa_iter: int = 16                       # power iterations of the randomised SVD (0: exact SVD)
+    freeze_vision_tower: bool = True           # vision-language models: which parts train
+    freeze_multi_modal_projector: bool = True
+    freeze_language_model: bool = False
     use_dft_loss: bool = False                 # SFT: token losses scaled by the target's (detached) probability
     use_eaft_loss: bool = False                # SFT: token losses scaled by the top-20 entropy ** eaft_alpha
     eaft_alpha: float = 1.0

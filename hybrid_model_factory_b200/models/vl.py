@@ -76,3 +76,29 @@ class HybridVLForConditionalGeneration(nn.Module):
         emb = self.merge_embeddings(input_ids, pixel_values, image_grid_thw, image_embeds)
         return self.language_model(None, inputs_embeds=emb, labels=labels,
                                    position_ids=collapse_mrope_position_ids(position_ids), **kw)
+
+
+def apply_vl_freezing(model: nn.Module, freeze_vision_tower: bool = True, freeze_multi_modal_projector: bool = True,
+                      freeze_language_model: bool = False) -> dict:
+    """Which parts of a vision-language model train: the vision tower, the projector that maps its features into the
+    language model's space (``visual.merger`` in the Qwen2-VL family, else a module named ``*projector*``) and the
+    language model.  Returns the trainable parameter count per part.  Reference: ``model/model_utils/visual.py``
+    (``freeze_vision_tower`` / ``freeze_multi_modal_projector`` / ``freeze_language_model``)."""
+    visual = getattr(model, "visual", None)
+    counts = {"vision_tower": 0, "projector": 0, "language_model": 0}
+    proj_ids = set()
+    if visual is not None:
+        for name, mod in visual.named_modules():
+            if name == "merger" or "projector" in name.split(".")[-1]:
+                proj_ids |= {id(p) for p in mod.parameters()}
+        for p in visual.parameters():
+            part = "projector" if id(p) in proj_ids else "vision_tower"
+            p.requires_grad_(not (freeze_multi_modal_projector if part == "projector" else freeze_vision_tower))
+            counts[part] += p.numel() if p.requires_grad else 0
+    lm = getattr(model, "language_model", None)
+    if lm is not None:
+        for p in lm.parameters():
+            if freeze_language_model:
+                p.requires_grad_(False)
+            counts["language_model"] += p.numel() if p.requires_grad else 0
+    return counts

@@ -240,6 +240,11 @@ def run_exp(args: Optional[Any] = None) -> Trainer:
     elif ft_args.finetuning_type == "freeze":
         from .adapters import freeze_all_but_last
         info_rank0(logger, "trainable parameters: %d", freeze_all_but_last(model, ft_args.freeze_trainable_layers))
+    if hasattr(model, "visual") and hasattr(model, "language_model"):
+        from ..models.vl import apply_vl_freezing
+        counts = apply_vl_freezing(model, ft_args.freeze_vision_tower, ft_args.freeze_multi_modal_projector,
+                                   ft_args.freeze_language_model)
+        info_rank0(logger, "vision-language model, trainable parameters per part: %s", counts)
     if getattr(run_args, "fp8", False):
         from ..ops.fp8 import use_fp8_linear
         info_rank0(logger, "fp8: %d linear layers run their GEMMs in row-wise scaled float8", use_fp8_linear(model))

@@ -823,3 +823,28 @@ def test_vendor_multimodal_plugins_expand_placeholders():
     p = get_mm_plugin("glm4v", image_token="<|image|>", video_token="<|video|>")
     out = p.process_messages(msgs, [wide, square])
     assert count(out, "<|begin_of_image|>") == 2 and count(out, "<|image|>") > 2
+
+
+def test_vision_language_freezing_options():
+    from hybrid_model_factory_b200.models.vl import HybridVLForConditionalGeneration, apply_vl_freezing
+
+    class Tower(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.blocks = torch.nn.Linear(12, 16)
+            self.merger = torch.nn.Linear(16, 64)
+
+        def forward(self, px, grid_thw=None):
+            return self.merger(self.blocks(px))
+    model = HybridVLForConditionalGeneration(_cfg("*-GDN"), vision_tower=Tower(), image_token_id=5)
+    c = apply_vl_freezing(model)                                               # defaults: only the language model trains
+    assert c["vision_tower"] == 0 and c["projector"] == 0 and c["language_model"] > 0
+    c = apply_vl_freezing(model, freeze_multi_modal_projector=False, freeze_language_model=True)
+    assert c == {"vision_tower": 0, "projector": 16 * 64 + 64, "language_model": 0}
+    assert model.visual.merger.weight.requires_grad and not model.visual.blocks.weight.requires_grad
+    c = apply_vl_freezing(model, freeze_vision_tower=False)
+    assert c["vision_tower"] == 12 * 16 + 16 and c["projector"] == 0
+    ids = torch.tensor([[1, 5, 5, 2, 3]])
+    out = model(ids, labels=ids, pixel_values=torch.randn(2, 12))
+    out.loss.backward()
+    assert model.visual.blocks.weight.grad is not None and model.visual.merger.weight.grad is None
