@@ -19,6 +19,8 @@ from typing import Any, Dict, Iterator, List, Optional, Sequence
 
 import torch
 
+from .plugin import BatchingStrategy
+
 IGNORE_INDEX = -100
 
 
@@ -85,8 +87,9 @@ class BatchGenerator(Iterator):
     def __init__(self, dataset, renderer, micro_batch_size: int = 1, global_batch_size: Optional[int] = None,
                  strategy: str = "normal", token_budget: int = 0, dp_rank: int = 0, dp_size: int = 1, seed: int = 0,
                  pad_id: int = 0, shuffle: bool = True):
-        if strategy not in ("normal", "padding_free", "dynamic"):
-            raise ValueError(f"unknown batching strategy '{strategy}'")
+        if strategy not in ("normal", "padding_free", "dynamic") and not BatchingStrategy.has(strategy):
+            raise ValueError(f"unknown batching strategy '{strategy}' (built in: normal, padding_free, dynamic; "
+                             f"registered: {', '.join(BatchingStrategy.names()) or 'none'})")
         if strategy == "dynamic" and token_budget <= 0:
             raise ValueError("the dynamic strategy needs token_budget > 0")
         self.dataset, self.renderer = dataset, renderer
@@ -158,6 +161,8 @@ class BatchGenerator(Iterator):
         groups = [rows[i * self.micro_batch_size:(i + 1) * self.micro_batch_size] for i in range(self.num_micro_batch)]
         if self.strategy == "padding_free":
             return [packed_collate(g) for g in groups]
+        if self.strategy != "normal":
+            return BatchingStrategy(self.strategy)(rows, self)
         return [pad_collate(g, self.pad_id) for g in groups]
 
     @staticmethod

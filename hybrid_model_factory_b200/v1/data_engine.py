@@ -14,6 +14,8 @@ from typing import Any, Dict, List, Sequence, Tuple, Union
 
 import torch
 
+from .plugin import DataConverter
+
 
 def _read_records(path: str) -> List[dict]:
     if os.path.isdir(path):
@@ -62,7 +64,8 @@ def convert_pair(rec: dict) -> dict:
     return {"chosen_messages": mk(rec["chosen"]), "rejected_messages": mk(rec["rejected"])}
 
 
-CONVERTERS = {"alpaca": convert_alpaca, "sharegpt": convert_sharegpt, "pair": convert_pair}
+for _name, _fn in (("alpaca", convert_alpaca), ("sharegpt", convert_sharegpt), ("pair", convert_pair)):
+    DataConverter(_name).register(replace=True)(_fn)
 
 
 def adjust_data_index(index: List[Tuple[str, int]], size=None, weight=None) -> List[Tuple[str, int]]:
@@ -118,7 +121,7 @@ class DataEngine(torch.utils.data.Dataset):
 
     def _convert(self, raw: dict, name: str) -> dict:
         conv = self.dataset_infos[name].get("converter")
-        out = CONVERTERS[conv](raw) if conv else dict(raw)
+        out = DataConverter(conv)(raw) if conv else dict(raw)
         out["_dataset_name"] = name
         return out
 

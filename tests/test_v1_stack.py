@@ -131,3 +131,54 @@ def test_v1_launcher_runs_from_yaml(tmp_path):
     with pytest.raises(ValueError, match="unknown configuration keys"):
         (tmp_path / "bad.yaml").write_text(f"model: {tmp_path / 'model'}\ntrain_dataset: x\nno_such_key: 1\n")
         main([str(tmp_path / "bad.yaml")])
+
+
+def test_plugins_register_by_name_and_serve_the_data_engine(tmp_path):
+    """A plugin family keeps functions by name; a user converter and a user batching strategy are found by the data
+    engine and the batch generator through their names."""
+    import pytest
+    from hybrid_model_factory_b200.v1 import BatchingStrategy, DataConverter, Plugin
+
+    class Greeter(Plugin):
+        def twice(self, who):
+            return self(who) + " " + self["again"](who)
+
+    @Greeter("hello").register()
+    def _hello(who):
+        return f"hello {who}"
+
+    @Greeter("hello").register("again")
+    def _again(who):
+        return f"again {who}"
+
+    assert Greeter("hello")("x") == "hello x" and Greeter("hello").again("x") == "again x"
+    assert Greeter("hello").twice("y") == "hello y again y"
+    assert Greeter.names() == ["hello"] and "hello" not in DataConverter.names()   # tables are per family
+    with pytest.raises(ValueError, match="already has"):
+        Greeter("hello").register()(_hello)
+    with pytest.raises(KeyError, match="no '__call__'"):
+        Greeter("nobody")("x")
+    with pytest.raises(ValueError, match="needs a name"):
+        Greeter().register()
+
+    @DataConverter("question_answer").register(replace=True)
+    def _qa(rec):
+        return {"messages": [{"role": "user", "content": rec["q"], "loss_weight": 0.0},
+                             {"role": "assistant", "content": rec["a"], "loss_weight": 1.0}]}
+
+    (tmp_path / "qa.jsonl").write_text("\n".join(json.dumps({"q": f"q{i}", "a": f"a{i}"}) for i in range(8)))
+    (tmp_path / "qa.yaml").write_text("qa:\n  path: qa.jsonl\n  converter: question_answer\n")
+    eng = DataEngine(str(tmp_path / "qa.yaml"))
+    assert len(eng) == 8 and eng[3]["messages"][1]["content"] == "a3"
+
+    @BatchingStrategy("one_row_each").register(replace=True)
+    def _one_each(rows, gen):
+        from hybrid_model_factory_b200.v1.batching import packed_collate
+        return [packed_collate([r]) for r in rows]
+
+    rnd = Renderer(ByteTokenizer(), "default", cutoff_len=64)
+    gen = BatchGenerator(eng, rnd, micro_batch_size=2, global_batch_size=4, strategy="one_row_each", shuffle=False)
+    step = next(gen)
+    assert len(step) == 4 and all(len(mb["cu_seqlens"]) == 2 for mb in step)
+    with pytest.raises(ValueError, match="unknown batching strategy"):
+        BatchGenerator(eng, rnd, strategy="no_such_strategy")
