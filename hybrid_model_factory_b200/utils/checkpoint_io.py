@@ -145,9 +145,18 @@ def iter_tensors(path: str) -> Iterator[Tuple[str, torch.Tensor]]:
 
 
 def load_state_dict(path: str) -> Dict[str, torch.Tensor]:
-    """All tensors of a checkpoint directory under this package's names; matrices stored as group-wise quantised
-    integers (``hmf export --quantize``) are dequantised to bf16 on the way in."""
+    """All tensors of a checkpoint directory under this package's names; matrices stored as quantised integers (this
+    package's group-wise format of ``hmf export --quantize int8|int4``, or the GPTQ / AWQ layouts) are expanded to
+    bf16 on the way in."""
     state = dict(iter_tensors(path))
+    if any(k.endswith(".qzeros") for k in state):
+        from .quant_loaders import expand_quantized_state
+        quant_cfg = None
+        cfg_path = os.path.join(path, "config.json")
+        if os.path.exists(cfg_path):
+            with open(cfg_path) as f:
+                quant_cfg = json.load(f).get("quantization_config")
+        state = expand_quantized_state(state, quant_cfg)
     if any(k.endswith(".qweight") for k in state):
         from .export import dequantize_state
         state = dequantize_state(state)

@@ -65,6 +65,24 @@ def quantize_state(state: dict, bits: int = 8, group_size: int = 128, min_numel:
     return out
 
 
+def interchange_quantize_state(state: dict, method: str, bits: int = 4, group_size: int = 128,
+                               min_numel: int = 1 << 16) -> dict:
+    """Round-to-nearest 4-bit weights in the GPTQ or AWQ tensor layout (``<layer>.qweight / .qzeros / .scales``), for
+    the ``.weight`` of every 2-D matrix that :func:`quantize_state` would take and whose outputs divide by 8."""
+    from .quant_loaders import pack_awq, pack_gptq
+    pack = pack_gptq if method == "gptq" else pack_awq
+    out = {}
+    for k, v in state.items():
+        if not (k.endswith(".weight") and v.dim() == 2 and v.is_floating_point() and v.numel() >= min_numel
+                and v.shape[1] % group_size == 0 and v.shape[0] % 8 == 0 and "embed" not in k and "lm_head" not in k
+                and "norm" not in k):
+            out[k] = v
+            continue
+        for suffix, t in pack(v, bits, group_size).items():
+            out[k[:-len("weight")] + suffix] = t.contiguous()
+    return out
+
+
 def dequantize_state(state: dict, dtype: torch.dtype = torch.bfloat16) -> dict:
     """Inverse of :func:`quantize_state` (tensors without the quantised triple pass through)."""
     out = {}
@@ -113,16 +131,25 @@ def export(src: str, dst: str, dtype: str = None, max_shard_size="5GB", merge_lo
     if dtype:
         dt = DTYPES[dtype]
         state = {k: (v.to(dt) if v.is_floating_point() else v) for k, v in state.items()}
-    if quantize:
+    if quantize in ("gptq", "awq"):
+        state = interchange_quantize_state(state, quantize, 4, group_size)
+    elif quantize:
         state = quantize_state(state, 4 if quantize == "int4" else 8, group_size)
     checkpoint_io.save_state_dict(state, dst, max_shard_size)
     for name in os.listdir(src):
         if name.endswith((".json", ".txt", ".model", ".jinja")) and not name.endswith("index.json"):
             shutil.copy(os.path.join(src, name), os.path.join(dst, name))
-    if dtype and os.path.exists(os.path.join(dst, "config.json")):
+    if (dtype or quantize in ("gptq", "awq")) and os.path.exists(os.path.join(dst, "config.json")):
         with open(os.path.join(dst, "config.json")) as f:
             cfg = json.load(f)
-        cfg["torch_dtype"] = str(DTYPES[dtype]).replace("torch.", "")
+        if dtype:
+            cfg["torch_dtype"] = str(DTYPES[dtype]).replace("torch.", "")
+        if quantize == "gptq":
+            cfg["quantization_config"] = {"quant_method": "gptq", "bits": 4, "group_size": group_size,
+                                          "desc_act": False, "sym": False, "checkpoint_format": "gptq"}
+        elif quantize == "awq":
+            cfg["quantization_config"] = {"quant_method": "awq", "bits": 4, "group_size": group_size,
+                                          "zero_point": True, "version": "gemm"}
         with open(os.path.join(dst, "config.json"), "w") as f:
             json.dump(cfg, f, indent=2)
     if ollama:
@@ -139,7 +166,7 @@ def main(argv=None) -> int:
     ap.add_argument("--merge-lora", action="store_true")
     ap.add_argument("--lora-alpha", type=float, default=None)
     ap.add_argument("--use-rslora", action="store_true")
-    ap.add_argument("--quantize", default=None, choices=["int8", "int4"])
+    ap.add_argument("--quantize", default=None, choices=["int8", "int4", "gptq", "awq"])
     ap.add_argument("--group-size", type=int, default=128)
     ap.add_argument("--ollama", action="store_true")
     ap.add_argument("--template", default=None)

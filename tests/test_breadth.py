@@ -848,3 +848,65 @@ def test_vision_language_freezing_options():
     out = model(ids, labels=ids, pixel_values=torch.randn(2, 12))
     out.loss.backward()
     assert model.visual.blocks.weight.grad is not None and model.visual.merger.weight.grad is None
+
+
+def test_gptq_and_awq_checkpoints_expand_on_load(tmp_path):
+    """GPTQ packs inputs into words (zeros stored minus one, optional ``g_idx``), AWQ packs outputs in its interleaved
+    order: both are unpacked with plain integer arithmetic here and compared against the hand-built integers; a model
+    exported in either layout loads through the ordinary path and stays close to the original."""
+    from hybrid_model_factory_b200.utils import checkpoint_io
+    from hybrid_model_factory_b200.utils.export import export
+    from hybrid_model_factory_b200.utils.quant_loaders import (AWQ_ORDER, dequantize_awq, dequantize_gptq, detect_method,
+                                                               expand_quantized_state, pack_awq, pack_gptq)
+    torch.manual_seed(0)
+    n_in, n_out, group = 64, 16, 32
+    q = torch.randint(0, 16, (n_in, n_out))
+    z = torch.randint(1, 16, (n_in // group, n_out))
+    s = (torch.rand(n_in // group, n_out) * 0.1 + 0.01).half()
+    g = torch.arange(n_in) // group
+    want = ((q - z[g]).float() * s.float()[g]).t()
+    # GPTQ by hand: word r of column o holds inputs 8r .. 8r+7, low nibble first; zeros minus one, packed over outputs
+    qw = torch.zeros(n_in // 8, n_out, dtype=torch.int64)
+    for i in range(n_in):
+        qw[i // 8] |= q[i] << (4 * (i % 8))
+    qz = torch.zeros(n_in // group, n_out // 8, dtype=torch.int64)
+    for o in range(n_out):
+        qz[:, o // 8] |= (z[:, o] - 1) << (4 * (o % 8))
+    to32 = lambda t: torch.where(t >= 2 ** 31, t - 2 ** 32, t).to(torch.int32)  # noqa: E731
+    got = dequantize_gptq(to32(qw), to32(qz), s, None, 4, torch.float32)
+    assert torch.equal(got, want)
+    perm = torch.randperm(n_in)                                   # act-order: rows visit the groups in any order
+    got = dequantize_gptq(to32(qw), to32(qz), s, g[perm].int(), 4, torch.float32)
+    assert torch.equal(got, ((q - z[g[perm]]).float() * s.float()[g[perm]]).t())
+    # AWQ by hand: nibble i of word c holds output 8c + AWQ_ORDER[i]
+    aw = torch.zeros(n_in, n_out // 8, dtype=torch.int64)
+    az = torch.zeros(n_in // group, n_out // 8, dtype=torch.int64)
+    for c in range(n_out // 8):
+        for i, col in enumerate(AWQ_ORDER):
+            aw[:, c] |= q[:, 8 * c + col] << (4 * i)
+            az[:, c] |= z[:, 8 * c + col] << (4 * i)
+    assert torch.equal(dequantize_awq(to32(aw), to32(az), s, 4, group, torch.float32), want)
+    # the packers invert the readers, and the state-level pass names the method from the shapes
+    w = torch.randn(48, 128)
+    for pack, name in ((pack_gptq, "gptq"), (pack_awq, "awq")):
+        st = {f"l.{k}": v for k, v in pack(w, 4, 32).items()}
+        st["l.bias"] = torch.zeros(48)
+        assert detect_method(st) == name
+        back = expand_quantized_state(st, dtype=torch.float32)
+        assert set(back) == {"l.weight", "l.bias"}
+        assert (back["l.weight"] - w).abs().max() < (w.max() - w.min()) / 15 * 0.51 + 1e-2
+    # a whole model through `hmf export --quantize gptq|awq` and back
+    model = build_model(_cfg("*-GDN", hidden_size=128, intermediate_size=512)).eval()
+    ids = torch.randint(0, 128, (1, 10))
+    ref = model(input_ids=ids).logits
+    checkpoint_io.save_pretrained(model, str(tmp_path / "src"))
+    for method in ("gptq", "awq"):
+        dst = tmp_path / method
+        export(str(tmp_path / "src"), str(dst), quantize=method, group_size=64)
+        names = [n for n, _ in checkpoint_io.iter_tensors(str(dst))]
+        assert any(n.endswith(".qzeros") for n in names)
+        import json as _json
+        assert _json.load(open(dst / "config.json"))["quantization_config"]["quant_method"] == method
+        again = checkpoint_io.from_pretrained(str(dst), dtype=torch.float32).eval()
+        err = (again(input_ids=ids).logits - ref).abs().max() / ref.abs().max()
+        assert err < 0.25, (method, float(err))
