@@ -168,6 +168,8 @@ class FinetuningArguments:
     use_dft_loss: bool = False                 # SFT: token losses scaled by the target's (detached) probability
     use_eaft_loss: bool = False                # SFT: token losses scaled by the top-20 entropy ** eaft_alpha
     eaft_alpha: float = 1.0
+    mixture_of_depths: Optional[str] = None    # "convert": add token routers to every second layer; "load": checkpoint has them
+    mod_capacity: float = 0.125                # fraction of a row's tokens a routed layer processes while training
     shift_attn: bool = False                   # LongLoRA shifted sparse attention while training (groups of 1/4 length)
     freeze_trainable_layers: int = 2
     include_effective_tokens_per_second: bool = False

@@ -412,6 +412,11 @@ class HybridForCausalLM(nn.Module):
                 out.aux_loss = load_balancing_loss(router_logits, self.config.num_experts,
                                                    self.config.num_experts_per_tok).to(out.loss.device)
                 out.loss = out.loss + self.config.router_aux_loss_coef * out.aux_loss
+            if getattr(self.config, "mixture_of_depths", None) and self.training:
+                from .mod import mod_aux_loss
+                aux = mod_aux_loss(self)            # (terms of checkpointed layers carry no graph and are left out)
+                if aux is not None:
+                    out.loss = out.loss + float(getattr(self.config, "mod_aux_loss_coef", 0.01)) * aux
         want_logits = return_logits if return_logits is not None else labels is None
         if want_logits:
             hk = h if not logits_to_keep else h[:, -logits_to_keep:]
@@ -479,5 +484,9 @@ def build_model(config: HybridConfig) -> HybridForCausalLM:
     its three GEMMs on the library's tcgen05 kernel (bf16 CUDA tensors; other tensors take ``F.linear``)."""
     from ..ops.gemm import use_own_linear
     model = MODEL_CLASSES.get(config.model_type, HybridForCausalLM)(config)
+    mod = getattr(config, "mixture_of_depths", None)
+    if isinstance(mod, dict):                       # a checkpoint saved with routed layers: same routers, then load
+        from .mod import apply_mixture_of_depths
+        apply_mixture_of_depths(model, **mod)
     use_own_linear(model)
     return model

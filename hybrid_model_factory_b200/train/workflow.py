@@ -225,6 +225,10 @@ def run_exp(args: Optional[Any] = None) -> Trainer:
                              use_rslora=ft_args.use_rslora, use_dora=ft_args.use_dora, pissa_init=ft_args.pissa_init,
                              pissa_iter=ft_args.pissa_iter)
         info_rank0(logger, "LoRA adapters on %d linear layers", len(wrapped))
+    if getattr(ft_args, "mixture_of_depths", None) == "convert":
+        from ..models.mod import apply_mixture_of_depths
+        routed = apply_mixture_of_depths(model, capacity=ft_args.mod_capacity)
+        info_rank0(logger, "mixture-of-depths routers on layers %s (capacity %.3f)", routed, ft_args.mod_capacity)
     if getattr(ft_args, "shift_attn", False):
         from ..layers.attention import Attention
         n_shift = 0

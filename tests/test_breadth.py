@@ -910,3 +910,52 @@ def test_gptq_and_awq_checkpoints_expand_on_load(tmp_path):
         again = checkpoint_io.from_pretrained(str(dst), dtype=torch.float32).eval()
         err = (again(input_ids=ids).logits - ref).abs().max() / ref.abs().max()
         assert err < 0.25, (method, float(err))
+
+
+def test_mixture_of_depths_routes_tokens_and_decodes_causally(tmp_path):
+    """Routed layers process the picked tokens only (the rest keep their residual stream), the router trains through
+    its gate and its top-k prediction loss, decoding with a cache follows the same causal rule as a full forward in
+    eval mode, and a saved model comes back with its routers."""
+    from hybrid_model_factory_b200.models.cache import HybridCache
+    from hybrid_model_factory_b200.models.mod import apply_mixture_of_depths, mod_aux_loss
+    from hybrid_model_factory_b200.utils import checkpoint_io
+    torch.manual_seed(0)
+    model = build_model(_cfg("*-GDN-*-GDN"))
+    assert apply_mixture_of_depths(model, capacity=0.25) == [1, 3]
+    ids = torch.randint(0, 128, (2, 16))
+    model.train()
+    out = model(input_ids=ids, labels=ids)
+    out.loss.backward()
+    assert mod_aux_loss(model) is not None
+    for i in (1, 3):
+        assert model.model.layers[i].mod_router.weight.grad.abs().sum() > 0
+    # one routed layer by hand, eval rule: tokens with a positive score are processed as a subsequence of their own
+    model.eval()
+    layer = model.model.layers[1]
+    x = torch.randn(1, 12, model.config.hidden_size)
+    with torch.no_grad():
+        scores = torch.nn.functional.linear(x, layer.mod_router.weight).squeeze(-1)
+        keep = (scores > 0)[0]
+        assert 0 < int(keep.sum()) < 12
+        got, _ = layer(x)
+        sub, _ = layer._mod_inner(x[:, keep])
+        want = x.clone()
+        want[:, keep] += (sub - x[:, keep]) * torch.sigmoid(scores[:, keep]).unsqueeze(-1)
+    assert torch.allclose(got, want, atol=1e-5)
+    assert torch.equal(got[:, ~keep], x[:, ~keep])
+    # full forward == prefill + token-by-token decode
+    one = ids[:1]
+    with torch.no_grad():
+        full = model(input_ids=one).logits
+        cache = HybridCache()
+        o = model(input_ids=one[:, :9], past_key_values=cache, use_cache=True)
+        steps = [o.logits[:, -1]]
+        for t in range(9, 16):
+            steps.append(model(input_ids=one[:, t:t + 1], past_key_values=cache, use_cache=True).logits[:, -1])
+    assert torch.allclose(torch.stack(steps, 1), full[:, 8:], atol=2e-4)
+    # the routers travel with the checkpoint
+    checkpoint_io.save_pretrained(model, str(tmp_path / "m"))
+    again = checkpoint_io.from_pretrained(str(tmp_path / "m"), dtype=torch.float32).eval()
+    assert hasattr(again.model.layers[3], "mod_router")
+    with torch.no_grad():
+        assert torch.allclose(again(input_ids=one).logits, full, atol=1e-5)
