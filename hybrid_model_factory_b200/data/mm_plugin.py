@@ -253,7 +253,7 @@ def register_mm_plugin(name: str, plugin_class: type) -> None:
 def get_mm_plugin(name: str, image_token: Optional[str] = None, video_token: Optional[str] = None,
                   audio_token: Optional[str] = None, **kw) -> BasePlugin:
     if name not in PLUGINS:
-        from . import mm_plugin_zoo  # noqa: F401  (registers the plugins of the other model families)
+        from . import mm_plugin_audio, mm_plugin_zoo  # noqa: F401  (register the other families' plugins)
     if name not in PLUGINS:
         raise ValueError(f"multimodal plugin `{name}` not found")
     return PLUGINS[name](image_token, video_token, audio_token, **kw)

@@ -959,3 +959,60 @@ def test_mixture_of_depths_routes_tokens_and_decodes_causally(tmp_path):
     assert hasattr(again.model.layers[3], "mod_router")
     with torch.no_grad():
         assert torch.allclose(again(input_ids=one).logits, full, atol=1e-5)
+
+
+def test_audio_plugins_log_mel_and_token_expansion(tmp_path):
+    """A one-second tone: 100 valid frames of 3000, 25 audio tokens, the energy sits in the mel band of the tone; the
+    features equal the ``transformers`` Whisper extractor's; ``.wav`` files are read and resampled; the omni plugin
+    handles an image and an audio clip in one message."""
+    import math
+    import wave
+    import numpy as np
+    from PIL import Image
+    from hybrid_model_factory_b200.data.mm_plugin import get_mm_plugin
+    from hybrid_model_factory_b200.data.mm_plugin_audio import (AudioFrontendConfig, audio_token_count, load_audio,
+                                                               log_mel, mel_filterbank)
+    cfg = AudioFrontendConfig()
+    t = torch.arange(16000) / 16000.0
+    tone = 0.5 * torch.sin(2 * math.pi * 440.0 * t)
+    feats, mask = log_mel(tone, cfg)
+    assert feats.shape == (128, 3000) and int(mask.sum()) == 100 and audio_token_count(100) == 25
+    fb = mel_filterbank(128, 400, 16000)
+    assert fb.shape == (128, 201) and fb.min() >= 0
+    band = int(feats[:, :100].mean(1).argmax())
+    centre_hz = float((fb[band] * torch.linspace(0, 8000, 201)).sum() / fb[band].sum())
+    assert abs(centre_hz - 440.0) < 40.0
+    try:
+        from transformers import WhisperFeatureExtractor
+        theirs = WhisperFeatureExtractor(feature_size=128)(tone.numpy(), sampling_rate=16000, return_tensors="pt",
+                                                           return_attention_mask=True)
+        assert torch.allclose(feats, theirs["input_features"][0], atol=2e-3)
+        assert torch.equal(mask, theirs["attention_mask"][0].long())
+    except ImportError:
+        pass
+    # 8 kHz 16-bit stereo file -> mono 16 kHz
+    path = str(tmp_path / "a.wav")
+    pcm = (np.stack([tone[::2].numpy(), tone[::2].numpy()], 1) * 32767).astype("<i2")
+    with wave.open(path, "wb") as f:
+        f.setnchannels(2), f.setsampwidth(2), f.setframerate(8000)
+        f.writeframes(pcm.tobytes())
+    wav = load_audio(path, 16000)
+    assert wav.numel() == 16000 and (wav - tone).abs().mean() < 0.02
+    assert load_audio({"array": tone.numpy(), "sampling_rate": 16000}, 16000).shape == (16000,)
+    # text expansion
+    plug = get_mm_plugin("qwen2_audio", audio_token="<|AUDIO|>")
+    msgs = [{"role": "user", "content": "listen: <audio> and <audio>"}, {"role": "assistant", "content": "ok"}]
+    out = plug.process_messages(msgs, audios=[path, (tone[:8000], 16000)])
+    assert out[0]["content"] == ("listen: <|audio_bos|>" + "<|AUDIO|>" * 25 + "<|audio_eos|> and <|audio_bos|>"
+                                 + "<|AUDIO|>" * audio_token_count(50) + "<|audio_eos|>")
+    mm = plug.get_mm_inputs(audios=[path, (tone[:8000], 16000)])
+    assert mm["input_features"].shape == (2, 128, 3000) and mm["feature_attention_mask"].sum(-1).tolist() == [100, 50]
+    import pytest
+    with pytest.raises(ValueError, match="placeholders"):
+        plug.process_messages(msgs, audios=[path])
+    omni = get_mm_plugin("qwen2_omni", image_token="<|IMAGE|>", video_token="<|VIDEO|>", audio_token="<|AUDIO|>")
+    img = Image.fromarray((np.random.rand(56, 84, 3) * 255).astype("uint8"))
+    both = omni.process_messages([{"role": "user", "content": "<image> then <audio>"}], images=[img], audios=[path])
+    assert both[0]["content"].count("<|IMAGE|>") == 6 and both[0]["content"].count("<|AUDIO|>") == 25
+    mm = omni.get_mm_inputs(images=[img], audios=[path])
+    assert set(mm) >= {"pixel_values", "image_grid_thw", "input_features", "feature_attention_mask"}
