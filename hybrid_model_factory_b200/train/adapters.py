@@ -143,3 +143,19 @@ def shift_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, group: in
         return x.reshape(B * (T // group), group, H, D)
     o = attend(fold(q), fold(k), fold(v)).reshape(B, T, H, D)
     return torch.cat([o[:, :, :half], torch.roll(o[:, :, half:], group // 2, dims=1)], dim=2)
+
+
+def add_neftune(model: nn.Module, alpha: float = 5.0):
+    """Noisy embeddings for instruction tuning: while the model is in training mode, uniform noise in
+    ``[-s, s]`` with ``s = alpha / sqrt(tokens x width)`` is added to the output of the input embedding; evaluation
+    and generation are untouched.  Returns the hook handle (``handle.remove()`` switches it off).
+    Reference: the ``neftune_noise_alpha`` training argument inherited from the Hugging Face trainer."""
+    emb = model.get_input_embeddings() if hasattr(model, "get_input_embeddings") else model.model.embed_tokens
+
+    def hook(module, inputs, output):
+        if not module.training:
+            return output
+        scale = alpha / (output.shape[-2] * output.shape[-1]) ** 0.5
+        return output + torch.empty_like(output).uniform_(-scale, scale)
+
+    return emb.register_forward_hook(hook)

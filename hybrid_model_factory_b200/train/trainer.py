@@ -290,13 +290,16 @@ class Trainer:
             if logging_now:
                 self._last_loss = float(loss.item())
                 self.log({"loss": self._last_loss, "lr": self._last_lr})
-            for cb in self.callbacks:
-                cb(self)
             self._maybe_evaluate()
             if self.args.save_steps and self.global_step % self.args.save_steps == 0:
                 self.save_checkpoint(os.path.join(self.args.output_dir, f"checkpoint-{self.global_step}"))
+            for cb in self.callbacks:           # after the save, so that a callback finds this step's checkpoint
+                cb(self)
         if self.args.eval_steps == 0 or self.global_step % max(self.args.eval_steps, 1) != 0:
             self._maybe_evaluate(force=True)
+        for cb in self.callbacks:
+            if hasattr(cb, "on_train_end"):
+                cb.on_train_end(self)
 
     def log(self, values: dict) -> None:
         elapsed = time.time() - self._t0

@@ -136,6 +136,24 @@ def select_optimizer(ft_args, default: str = "adamw"):
     return default, {}
 
 
+def build_callbacks(run_args, model_args=None) -> list:
+    """Callbacks of a run: stop on a non-finite loss; ``report_to`` tensorboard (own event-file writer), wandb or
+    swanlab (when importable); the base tokenizer's files re-copied into every checkpoint."""
+    from .callbacks import EarlyStopCallback, PreserveTokenizerConfigCallback, ReporterCallback
+    cbs = [EarlyStopCallback()]
+    targets = {t.strip() for t in str(getattr(run_args, "report_to", "none") or "none").split(",")}
+    if targets & {"tensorboard", "all"}:
+        from ..utils.tensorboard_writer import TensorBoardCallback
+        cbs.append(TensorBoardCallback(run_args.output_dir))
+    for backend in ("wandb", "swanlab"):
+        if targets & {backend, "all"}:
+            cbs.append(ReporterCallback(backend=backend))
+    src = getattr(model_args, "model_name_or_path", None)
+    if src and os.path.isdir(src):
+        cbs.append(PreserveTokenizerConfigCallback(src))
+    return cbs
+
+
 def run_ppo(model, ft_args, run_args, dataset, tokenizer, device, bsz):
     """PPO stage: prompts come from the dataset's ``input_ids`` (truncated to ``cutoff``), scores from the reward model
     of ``ft_args.reward_model`` (a checkpoint of the ``rm`` stage), the KL reference from ``ft_args.ref_model`` or the
@@ -305,7 +323,12 @@ def run_exp(args: Optional[Any] = None) -> Trainer:
         loss_fn = make_weighted_sft_loss("dft" if ft_args.use_dft_loss else "eaft", ft_args.eaft_alpha)
     if stage == "ppo":
         return run_ppo(model, ft_args, run_args, dataset, tokenizer, device, bsz)
-    trainer = Trainer(model, targs, device=device, loss_fn=loss_fn)
+    trainer = Trainer(model, targs, device=device, loss_fn=loss_fn, callbacks=build_callbacks(run_args, model_args))
+    if getattr(ft_args, "neftune_noise_alpha", 0.0):
+        from .adapters import add_neftune
+        add_neftune(model, ft_args.neftune_noise_alpha)
+        info_rank0(logger, "NEFTune: uniform noise of scale %.1f / sqrt(tokens x width) on the embeddings while training",
+                   ft_args.neftune_noise_alpha)
     if teacher is not None:
         from ..parallel.sp import set_sequence_parallel_group_recursive
         set_sequence_parallel_group_recursive(teacher, trainer.sp)

@@ -124,7 +124,7 @@ def _tp_rs_ag_worker(rank, world):
     from hybrid_model_factory_b200.ops import _lib
     from hybrid_model_factory_b200.ops.fused_comm import PeerAllGatherGemm, PeerGemmAllReduce
     dev = torch.device("cuda", rank)
-    rs = PeerGemmAllReduce(dist.group.WORLD, max_m=256, max_n=4096, device=dev)
+    rs = PeerGemmAllReduce(dist.group.WORLD, max_m=256, max_n=max(4096, 1024 * world), device=dev)
     ag = PeerAllGatherGemm(dist.group.WORLD, max_m=256, max_ks=1024, max_n=4096, device=dev)
     g = torch.Generator().manual_seed(10 + rank)
     for it, (M, N, Ks) in enumerate(((5, 128 * world, 128), (64, 1024 * world, 512), (200, 256 * world, 320), (33, 512 * world, 64))):
@@ -145,7 +145,7 @@ def _tp_rs_ag_worker(rank, world):
     # the same reductions through the NVSwitch multicast mapping (multimem.ld_reduce), where the buffers have one
     import os
     os.environ["HMF_TP_NVLS"] = "1"
-    nv = PeerGemmAllReduce(dist.group.WORLD, max_m=256, max_n=4096, device=dev)
+    nv = PeerGemmAllReduce(dist.group.WORLD, max_m=256, max_n=max(4096, 1024 * world), device=dev)
     os.environ["HMF_TP_NVLS"] = "0"
     if nv.use_nvls:
         for M, N, Ks in ((64, 1024 * world, 512), (200, 256 * world, 320)):

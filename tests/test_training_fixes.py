@@ -362,3 +362,47 @@ def test_dft_and_eaft_losses_match_their_definitions():
     g1 = torch.autograd.grad(got_dft, model.lm_head.weight)[0]
     g2 = torch.autograd.grad(dft, model.lm_head.weight)[0]
     assert torch.allclose(g1, g2, atol=1e-6)
+
+
+def test_tensorboard_event_file_neftune_and_callbacks(tmp_path):
+    """The event writer's records carry valid checksums and read back; CRC-32C matches its published check value;
+    ``report_to: tensorboard`` puts a callback on the run; NEFTune perturbs embeddings in training mode only."""
+    from hybrid_model_factory_b200.train.adapters import add_neftune
+    from hybrid_model_factory_b200.train.workflow import build_callbacks
+    from hybrid_model_factory_b200.utils.tensorboard_writer import (EventWriter, TensorBoardCallback, crc32c,
+                                                                    read_scalars)
+    assert crc32c(b"123456789") == 0xE3069283
+    w = EventWriter(str(tmp_path / "runs"))
+    for step in range(3):
+        w.add_scalars({"train/loss": 2.0 - 0.5 * step, "train/learning_rate": 1e-4}, step)
+    w.close()
+    got = list(read_scalars(w.path))
+    assert len(got) == 6 and got[0] == ("train/loss", 2.0, 0) and got[4][0] == "train/loss" and got[4][2] == 2
+    assert abs(got[5][1] - 1e-4) < 1e-9
+    raw = bytearray(open(w.path, "rb").read())
+    raw[-6] ^= 0xFF                                              # a flipped payload byte is caught
+    open(w.path, "wb").write(bytes(raw))
+    import pytest
+    with pytest.raises(ValueError, match="checksum"):
+        list(read_scalars(w.path))
+
+    class Args:
+        report_to, output_dir = "tensorboard", str(tmp_path)
+    cbs = build_callbacks(Args())
+    assert any(isinstance(c, TensorBoardCallback) for c in cbs)
+
+    torch.manual_seed(0)
+    cfg = HybridConfig("hybrid_qwen3", vocab_size=64, hidden_size=32, intermediate_size=64, num_hidden_layers=2,
+                       num_attention_heads=2, num_key_value_heads=1, head_dim=16, hybrid_override_pattern="*-GDN")
+    model = build_model(cfg)
+    ids = torch.randint(0, 64, (1, 8))
+    model.eval()
+    clean = model.model.embed_tokens(ids)
+    handle = add_neftune(model, alpha=5.0)
+    assert torch.equal(model.model.embed_tokens(ids), clean)
+    model.train()
+    noisy = model.model.embed_tokens(ids)
+    bound = 5.0 / (8 * 32) ** 0.5
+    assert 0 < (noisy - clean).abs().max() <= bound + 1e-6
+    handle.remove()
+    assert torch.equal(model.model.embed_tokens(ids), clean)
