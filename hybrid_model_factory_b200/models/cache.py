@@ -75,15 +75,24 @@ class HybridCache:
     def update_offset(self, n: int) -> None:
         self.seqlen_offset += n
 
-    def copy(self) -> "HybridCache":
+    def copy(self, share_attention: bool = False) -> "HybridCache":
         new = HybridCache(self.cache_aprods)
         clone = lambda t: t.clone() if isinstance(t, torch.Tensor) else (  # noqa: E731
             tuple(clone(x) for x in t) if isinstance(t, tuple) else _copy.copy(t))
-        new.attention = {i: (k.clone(), v.clone()) for i, (k, v) in self.attention.items()}
+        if share_attention:
+            new.attention = dict(self.attention)
+        else:
+            new.attention = {i: (k.clone(), v.clone()) for i, (k, v) in self.attention.items()}
         new.ssm = {i: {n: clone(s) for n, s in e.items()} for i, e in self.ssm.items()}
         new.bmojo = {i: {n: clone(s) for n, s in e.items()} for i, e in self.bmojo.items()}
         new.seqlen_offset = self.seqlen_offset
+        new.cache_transitions = self.cache_transitions
         return new
+
+    def snapshot(self) -> "HybridCache":
+        """A cache that stays at this position while the original moves on.  Attention keys / values are replaced, not
+        written in place, when tokens are appended, so they are shared; the (small) recurrent entries are cloned."""
+        return self.copy(share_attention=True)
 
     def clear(self) -> None:
         self.attention.clear()

@@ -261,6 +261,9 @@ def main(argv=None) -> int:
     ap.add_argument("--max-model-len", type=int, default=32768)
     ap.add_argument("--enable-prefix-caching", action="store_true")
     ap.add_argument("--template", default=None)
+    ap.add_argument("--draft-model", default=None,
+                    help="checkpoint of a small model with the same vocabulary: proposes tokens for requests that set "
+                         "speculative_tokens, where their own n-grams offer none")
     ap.add_argument("--hf-overrides", default=None, help='JSON, e.g. {"gka_overrides": {"num_iter": 10}}')
     args = ap.parse_args(argv)
     overrides = json.loads(args.hf_overrides) if args.hf_overrides else {}
@@ -283,8 +286,10 @@ def main(argv=None) -> int:
         shard_model(model, tp)
         torch.manual_seed(0)           # stochastic sampling must draw the same numbers on every rank
         control = ControlChannel()
+    draft = checkpoint_io.from_pretrained(args.draft_model, device=device) if args.draft_model else None
     engine = ServingEngine(model, max_num_seqs=args.max_num_seqs, max_num_batched_tokens=args.max_num_batched_tokens,
-                           max_model_len=args.max_model_len, enable_prefix_caching=args.enable_prefix_caching, tp=tp)
+                           max_model_len=args.max_model_len, enable_prefix_caching=args.enable_prefix_caching, tp=tp,
+                           draft_model=draft)
     if device.type == "cuda":
         # capture the decode graphs here, on the main thread and on every rank at the same time; the serving thread
         # then only replays them

@@ -17,7 +17,7 @@ import ctypes
 import itertools
 import time
 from dataclasses import dataclass, field
-from typing import Dict, List, Optional, Sequence
+from typing import Any, Dict, List, Optional, Sequence
 
 import torch
 import torch.nn.functional as F
@@ -62,6 +62,8 @@ class RequestState:
     finished: bool = False
     ngram_index: dict = field(default_factory=dict)     # speculative decoding: n-gram -> end of its latest occurrence
     ngram_upto: int = 0
+    draft_cache: Any = None                             # draft model: its cache over the first `draft_upto` tokens
+    draft_upto: int = 0
 
 
 def sample_tokens(logits: torch.Tensor, params: List[SamplingParams], histories=None,
@@ -133,8 +135,11 @@ class ServingEngine:
     def __init__(self, model, *, block_size: int = 64, num_blocks: Optional[int] = None, max_num_seqs: int = 64,
                  max_num_batched_tokens: int = 8192, enable_prefix_caching: bool = False, max_model_len: int = 32768,
                  gpu_memory_utilization: float = 0.85, tp=None, use_cuda_graphs: bool = True,
-                 whole_prompts: bool = True):
+                 whole_prompts: bool = True, draft_model=None):
         self.model = model.eval()
+        # speculative decoding: a small model of the same vocabulary proposes tokens where the request's own n-grams
+        # offer none (it runs with the plain per-request cache of `models/cache.py`, not the paged one)
+        self.draft_model = None if draft_model is None else draft_model.eval()
         self.cfg = model.config
         self.device = next(model.parameters()).device
         self.tp = tp
@@ -162,7 +167,7 @@ class ServingEngine:
         self._layer_cache: Dict[int, dict] = {}
         self.max_blocks_per_seq = (max_model_len + block_size - 1) // block_size
         self.stats = {"steps": 0, "decode_tokens": 0, "prefill_tokens": 0, "graph_replays": 0, "decode_steps": 0, "packed_prefills": 0,
-                      "spec_steps": 0, "spec_drafted": 0, "spec_accepted": 0,
+                      "spec_steps": 0, "spec_drafted": 0, "spec_accepted": 0, "spec_model_drafts": 0,
                       "decode_s": 0.0, "prefill_s": 0.0, "decode_gpu_s": 0.0}
         has_moe = any(hasattr(l.mlp, "experts") for l in model.model.layers)
         # B'MOJO-F layers decode request by request through the layer itself (bounded window state per request)
@@ -307,7 +312,32 @@ class ServingEngine:
             e = index.get(tuple(seq[-n:]))
             if e is not None:
                 return seq[e:e + k]
+        if self.draft_model is not None:
+            return self._draft_with_model(req, seq, k)
         return []
+
+    @torch.no_grad()
+    def _draft_with_model(self, req: "RequestState", seq: List[int], k: int) -> List[int]:
+        """``k`` greedy tokens of the draft model after ``seq``.  The draft's cache is kept at the verified prefix: it
+        first reads the tokens verified since its last turn, a snapshot is taken, the drafts are generated, and the
+        snapshot becomes the request's cache again (the next turn reads whatever part of the drafts was accepted)."""
+        from ..models.cache import HybridCache
+        cache = req.draft_cache if req.draft_cache is not None else HybridCache()
+        dev = next(self.draft_model.parameters()).device
+        if len(seq) - 1 > req.draft_upto:
+            ids = torch.tensor([seq[req.draft_upto:len(seq) - 1]], dtype=torch.long, device=dev)
+            self.draft_model(input_ids=ids, past_key_values=cache, use_cache=True, logits_to_keep=1)
+            req.draft_upto = len(seq) - 1
+        keep = cache.snapshot()
+        tok, out = seq[-1], []
+        for _ in range(k):
+            ids = torch.tensor([[tok]], dtype=torch.long, device=dev)
+            logits = self.draft_model(input_ids=ids, past_key_values=cache, use_cache=True).logits[0, -1]
+            tok = int(logits.argmax())
+            out.append(tok)
+        req.draft_cache = keep
+        self.stats["spec_model_drafts"] += 1
+        return out
 
     def _speculate(self, decodes: List[ScheduledSeq]):
         """Verifies drafted tokens for the decoding requests that have some.  Returns ``(plain, verified)``: the

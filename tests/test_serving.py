@@ -643,3 +643,28 @@ def test_speculative_decoding_on_gpu_kernels():
     agree = sum(a == b for x, y in zip(*outs) for a, b in zip(x, y))
     assert stats[1]["spec_steps"] > 0 and all(len(o) == 32 for o in outs[1])
     assert all(x[0] == y[0] for x, y in zip(*outs)) and agree >= 0.7 * 96, (agree, outs)
+
+
+def test_speculative_decoding_with_a_draft_model():
+    """A draft model proposes tokens where the n-gram index has none.  With the target's own weights as the draft every
+    proposal is accepted and the steps shrink; with an unrelated draft most are rejected; the tokens are those of plain
+    greedy decoding either way."""
+    import copy
+    torch.manual_seed(0)
+    model = build_model(tiny("*-GDN-M2", vocab_size=64)).eval()
+    twin = copy.deepcopy(model)
+    torch.manual_seed(1)
+    other = build_model(tiny("GDN-*", vocab_size=64, num_hidden_layers=2)).eval()
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(0, 64, (n,), generator=g).tolist() for n in (9, 17, 12)]
+    runs = {}
+    for name, draft, k in (("plain", None, 0), ("twin", twin, 3), ("other", other, 3)):
+        eng = ServingEngine(model, block_size=8, num_blocks=64, max_num_seqs=4, max_num_batched_tokens=64,
+                            max_model_len=128, draft_model=draft)
+        eng.spec_ngram = (64, 63)                                   # no n-gram of that length exists: drafts come from the model
+        runs[name] = (eng.generate(prompts, SamplingParams(max_new_tokens=20, speculative_tokens=k)), dict(eng.stats))
+    assert runs["twin"][0] == runs["plain"][0] and runs["other"][0] == runs["plain"][0]
+    st = runs["twin"][1]
+    assert st["spec_model_drafts"] > 0 and st["spec_accepted"] == st["spec_drafted"] > 0
+    assert st["steps"] < runs["plain"][1]["steps"]
+    assert runs["other"][1]["spec_accepted"] < runs["other"][1]["spec_drafted"]
