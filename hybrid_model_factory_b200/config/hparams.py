@@ -170,6 +170,8 @@ class FinetuningArguments:
     eaft_alpha: float = 1.0
     mixture_of_depths: Optional[str] = None    # "convert": add token routers to every second layer; "load": checkpoint has them
     mod_capacity: float = 0.125                # fraction of a row's tokens a routed layer processes while training
+    quantization_bit: Optional[int] = None     # lora: 4 or 8, the adapted layers' frozen base weights are held as codes (QLoRA)
+    quantization_type: str = "nf4"             # 4-bit levels: nf4 (normal-quantile table) or int
     neftune_noise_alpha: float = 0.0           # > 0: noisy embeddings while training (scale alpha / sqrt(tokens x width))
     shift_attn: bool = False                   # LongLoRA shifted sparse attention while training (groups of 1/4 length)
     freeze_trainable_layers: int = 2

@@ -106,7 +106,10 @@ def merge_lora(model: nn.Module) -> int:
         for child_name, child in list(parent.named_children()):
             if isinstance(child, LoRALinear):
                 with torch.no_grad():
-                    child.base.weight.copy_(child.merged_weight())
+                    merged = child.merged_weight()
+                    if hasattr(child.base, "to_linear"):          # quantised base: back to an ordinary layer
+                        child.base = child.base.to_linear()
+                    child.base.weight.copy_(merged)
                 setattr(parent, child_name, child.base)
                 n += 1
     return n

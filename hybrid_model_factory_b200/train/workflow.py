@@ -243,6 +243,11 @@ def run_exp(args: Optional[Any] = None) -> Trainer:
                              use_rslora=ft_args.use_rslora, use_dora=ft_args.use_dora, pissa_init=ft_args.pissa_init,
                              pissa_iter=ft_args.pissa_iter)
         info_rank0(logger, "LoRA adapters on %d linear layers", len(wrapped))
+        if getattr(ft_args, "quantization_bit", None):
+            from .qlora import quantize_adapter_bases, quantized_bytes
+            qn = quantize_adapter_bases(model, int(ft_args.quantization_bit), ft_args.quantization_type)
+            info_rank0(logger, "%d adapted layers keep their base weight as %d-bit codes (%.2f GB)", len(qn),
+                       int(ft_args.quantization_bit), quantized_bytes(model) / 1e9)
     if getattr(ft_args, "mixture_of_depths", None) == "convert":
         from ..models.mod import apply_mixture_of_depths
         routed = apply_mixture_of_depths(model, capacity=ft_args.mod_capacity)

@@ -1016,3 +1016,47 @@ def test_audio_plugins_log_mel_and_token_expansion(tmp_path):
     assert both[0]["content"].count("<|IMAGE|>") == 6 and both[0]["content"].count("<|AUDIO|>") == 25
     mm = omni.get_mm_inputs(images=[img], audios=[path])
     assert set(mm) >= {"pixel_values", "image_grid_thw", "input_features", "feature_attention_mask"}
+
+
+def test_qlora_quantised_base_trains_adapters_only():
+    """4-bit normal-quantile and 8-bit integer codes reproduce the weight within their step sizes; the product's
+    gradient reaches the input and the adapters, never the base; merging returns ordinary layers."""
+    from hybrid_model_factory_b200.train.adapters import apply_lora, merge_lora
+    from hybrid_model_factory_b200.train.qlora import (NF4_LEVELS, QuantizedLinear, quantize_adapter_bases,
+                                                       quantized_bytes)
+    torch.manual_seed(0)
+    lin = torch.nn.Linear(128, 48, bias=True)
+    w = lin.weight.detach()
+    q4 = QuantizedLinear(lin, 4, "nf4", 64)
+    assert q4.qweight.shape == (48, 64) and q4.qweight.dtype == torch.uint8 and q4.scales.shape == (48, 2)
+    gap = max(b - a for a, b in zip(NF4_LEVELS[:-1], NF4_LEVELS[1:]))
+    absmax = w.reshape(48, 2, 64).abs().amax(-1, keepdim=True)
+    err = (q4.weight - w).reshape(48, 2, 64).abs()
+    assert (err <= absmax * (gap / 2 + 0.01)).all()             # nearest level (+ bf16 rounding of the scale)
+    q8 = QuantizedLinear(lin, 8)
+    assert (q8.weight - w).abs().max() <= absmax.max() / 127 * 0.51 + absmax.max() * 0.005
+    x = torch.randn(5, 128, requires_grad=True)
+    y = q4(x)
+    ref = torch.nn.functional.linear(x, q4.weight, lin.bias)
+    assert torch.allclose(y, ref, atol=1e-5)
+    y.sum().backward()
+    assert torch.allclose(x.grad, torch.ones(5, 48) @ q4.weight, atol=1e-5)
+    assert not any(p.requires_grad for p in q4.parameters())
+    # through a model
+    model = build_model(_cfg("*-GDN", hidden_size=128, intermediate_size=256))
+    dense = sum(p.numel() * 4 for n, p in model.named_parameters() if "proj" in n and "lm_head" not in n)
+    wrapped = apply_lora(model, rank=4)
+    done = quantize_adapter_bases(model, 4)
+    assert set(done) == set(wrapped) and quantized_bytes(model) < dense / 6
+    ids = torch.randint(0, 128, (2, 10))
+    model.train()
+    model(input_ids=ids, labels=ids).loss.backward()
+    trainable = [n for n, p in model.named_parameters() if p.requires_grad]
+    assert trainable and all("lora_" in n for n in trainable)
+    assert all(p.grad is not None for n, p in model.named_parameters() if n.endswith("lora_B"))
+    model.eval()
+    with torch.no_grad():
+        before = model(input_ids=ids).logits
+        assert merge_lora(model) == len(wrapped)
+        assert not any(isinstance(m, QuantizedLinear) for m in model.modules())
+        assert torch.allclose(model(input_ids=ids).logits, before, atol=1e-4)

@@ -145,6 +145,9 @@ def test_preference_feedback_and_tool_data_processing(tmp_path):
     {"use_adam_mini": True},
     {"finetuning_type": "oft", "lora_target": "q_proj,o_proj", "oft_block_size": 16},
     {"deepspeed": "z3"},
+    {"finetuning_type": "lora", "lora_rank": 4, "quantization_bit": 4, "neftune_noise_alpha": 5.0,
+     "report_to": "tensorboard", "logging_steps": 1},
+    {"mixture_of_depths": "convert", "mod_capacity": 0.5},
 ])
 def test_training_options_run_end_to_end(tmp_path, extra):
     """`hmf train` configurations beyond the default optimizer: each runs a few steps, lowers the loss and saves a
@@ -166,6 +169,14 @@ def test_training_options_run_end_to_end(tmp_path, extra):
     model = checkpoint_io.from_pretrained(os.path.join(out, "final"))
     assert all(p.numel() > 0 and torch.isfinite(p).all() for p in model.parameters())
     assert not any("oft" in n or "lora" in n for n, _ in model.named_parameters())
+    assert not any("qweight" in n for n in model.state_dict())
+    if extra.get("report_to") == "tensorboard":
+        from hybrid_model_factory_b200.utils.tensorboard_writer import read_scalars
+        runs = os.path.join(out, "runs")
+        scalars = list(read_scalars(os.path.join(runs, os.listdir(runs)[0])))
+        assert sum(t == "train/loss" for t, _, _ in scalars) == 6
+    if extra.get("mixture_of_depths"):
+        assert hasattr(model.model.layers[1], "mod_router")
 
 
 def test_dpo_stage_on_a_ranking_dataset(tmp_path):
