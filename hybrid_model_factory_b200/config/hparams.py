@@ -170,6 +170,8 @@ class FinetuningArguments:
     eaft_alpha: float = 1.0
     mixture_of_depths: Optional[str] = None    # "convert": add token routers to every second layer; "load": checkpoint has them
     mod_capacity: float = 0.125                # fraction of a row's tokens a routed layer processes while training
+    lambda_reg: float = 0.0                    # L2A models: weight of the router sparsity term (0: plain language-model loss)
+    lambda_reg_scheduler: str = "linear"       # linear | cosine | constant ramp of lambda after warm-up
     quantization_bit: Optional[int] = None     # lora: 4 or 8, the adapted layers' frozen base weights are held as codes (QLoRA)
     quantization_type: str = "nf4"             # 4-bit levels: nf4 (normal-quantile table) or int
     neftune_noise_alpha: float = 0.0           # > 0: noisy embeddings while training (scale alpha / sqrt(tokens x width))

@@ -16,7 +16,7 @@ VERSION = "0.1.0"
 
 USAGE = """usage: hmf <command> [args]
 
-  prime-init CONFIG.yaml         stage 0: initialise a hybrid model from a Transformer checkpoint
+  prime-init CONFIG.yaml         stage 0: initialise a hybrid (or L2A) model from a Transformer checkpoint
   prime-unfuse CKPT [OUT]        convert a fused stage-1 checkpoint to the standard hybrid layout
   reassemble-vlm TEXT_CKPT VL_CKPT OUT   put a distilled text backbone back into its VL wrapper
   convert-qwen-gdn SRC OUT [--pattern P] convert a Qwen3-Next / Qwen3.5-MoE checkpoint to the hybrid layout
@@ -25,9 +25,10 @@ USAGE = """usage: hmf <command> [args]
                                  (USE_RAY=1: Ray actors instead of torchrun; USE_V1=1: the second-generation SFT stack)
   preprocess --config CFG.yaml   tokenise (and SP-split) datasets into `tokenized_path`, sharded and parallel
   eval CKPT --task T_split ...   multiple-choice benchmark evaluation (few-shot, accuracy per category)
-  export CKPT OUT [--dtype D] [--merge-lora] [--quantize int8|int4] [--ollama]
+  export CKPT OUT [--dtype D] [--merge-lora] [--quantize int8|int4|gptq|awq] [--ollama]
                                  re-shard / cast a checkpoint, fold adapters in, quantise, write an Ollama Modelfile
-  serve CKPT [--tp N --port P]   OpenAI-compatible server on the native engine (--tp N: tensor parallel over N GPUs)
+  serve CKPT [--tp N --port P] [--draft-model D]
+                                 OpenAI-compatible server on the native engine (--tp N: tensor parallel over N GPUs)
   api CKPT                       alias of serve
   chat CKPT                      interactive chat in the terminal
   bench-serve CKPT|CONFIG ...    serving benchmark (continuous batching workload)

@@ -71,7 +71,7 @@ class L2AAttention(nn.Module):
         base = hidden_states if residual is None else residual
         h2 = self.global_norm(base + s)
         soft = torch.sigmoid(self.router(h2).float() / self.temperature)        # [B, T, 1]
-        hard = (soft > self.threshold).float()
+        hard = (soft >= self.threshold).float()             # a zero router (stage 0) sends every token to global attention
         mask = hard + soft - soft.detach()
         sp = self.sequence_parallel_group
         sp_on = sp is not None and sp.size > 1

@@ -136,5 +136,8 @@ def init_mixer(symbol: str, attn: AttentionWeights, mixer, layer_idx: int) -> No
         init_mixer(sub, attn, mixer.ssm_mixer, layer_idx)
     elif symbol == "*":
         attention_like_init(attn, mixer, layer_idx)
+    elif symbol == "L2A":
+        attention_like_init(attn, mixer.local, layer_idx)
+        attention_like_init(attn, mixer.global_attn, layer_idx)
     else:
         raise ValueError(f"no stage-0 initialisation rule for layer symbol '{symbol}'")

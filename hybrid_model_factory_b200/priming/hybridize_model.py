@@ -52,6 +52,7 @@ class HybridizationConfig:
     mamba2: Optional[dict] = None
     gka: Optional[dict] = None
     gdn: Optional[dict] = None
+    l2a: Optional[dict] = None           # sliding_window, sigmoid_threshold, temperature, leak_prob, router_zero_init
     extra: dict = field(default_factory=dict)
 
 
@@ -96,6 +97,14 @@ def add_hybrid_configs(base: HybridConfig, cfg: HybridizationConfig) -> Dict[str
         if not cfg.swa or "window_size" not in cfg.swa:
             raise ValueError("pattern uses SWA layers but the config has no `swa.window_size`")
         out["swa_config"] = {"window_size": int(cfg.swa["window_size"])}
+    if "L2A" in symbols:
+        l2a = dict(cfg.l2a or {})
+        if "sliding_window" not in l2a:
+            raise ValueError("pattern uses L2A layers but the config has no `l2a.sliding_window`")
+        out["l2a_config"] = {"sliding_window": int(l2a["sliding_window"]),
+                             "sigmoid_threshold": float(l2a.get("sigmoid_threshold", 0.5)),
+                             "temperature": float(l2a.get("temperature", 0.1)),
+                             "leak_prob": float(l2a.get("leak_prob", 0.1))}
     return out
 
 
@@ -135,6 +144,15 @@ def hybridize_state(base_cfg: HybridConfig, base_state: Dict[str, torch.Tensor],
                     init_mixer("GKA", attn, layer.seq_mixer, i)
                     continue
                 init_mixer(unfuse_symbol(sym), attn, layer.seq_mixer, i)
+            elif sym == "L2A":
+                # both streams start as the attention they replace, the second norm as the layer's input norm, and
+                # the router at zero (or random): the model then departs from the Transformer only by the window
+                init_mixer("L2A", attn, layer.seq_mixer, i)
+                norm = base_state.get(f"model.layers.{i}.input_layernorm.weight")
+                if norm is not None:
+                    layer.seq_mixer.global_norm.weight.data.copy_(norm.to(layer.seq_mixer.global_norm.weight.dtype))
+                if (cfg.l2a or {}).get("router_zero_init", True):
+                    layer.seq_mixer.router.weight.data.zero_()
             else:
                 init_mixer(sym, attn, layer.seq_mixer, i)
     model = model.to(_DTYPES[cfg.dtype])

@@ -148,6 +148,17 @@ def main(argv=None) -> int:
     ap.add_argument("--batch-size", type=int, default=4)
     ap.add_argument("--seed", type=int, default=42)
     ap.add_argument("--save-dir", default=None)
+    ap.add_argument("--config", default=None, help="YAML file whose keys (task, task_dir, n_shot, ...) replace the defaults")
+    pre, _ = ap.parse_known_args(argv)
+    if pre.config:
+        import yaml
+        with open(pre.config) as f:
+            given = yaml.safe_load(f) or {}
+        known = {act.dest for act in ap._actions}
+        bad = sorted(k for k in given if k not in known)
+        if bad:
+            raise ValueError(f"{pre.config}: unknown keys {bad}")
+        ap.set_defaults(**given)
     a = ap.parse_args(argv)
     device = torch.device("cuda", 0) if torch.cuda.is_available() else torch.device("cpu")
     model = checkpoint_io.from_pretrained(a.model, device=device)

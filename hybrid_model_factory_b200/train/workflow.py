@@ -326,6 +326,13 @@ def run_exp(args: Optional[Any] = None) -> Trainer:
     if stage == "sft" and (ft_args.use_dft_loss or ft_args.use_eaft_loss):
         from .losses import make_weighted_sft_loss
         loss_fn = make_weighted_sft_loss("dft" if ft_args.use_dft_loss else "eaft", ft_args.eaft_alpha)
+    if stage in ("pt", "sft") and loss_fn is None and getattr(ft_args, "lambda_reg", 0.0) > 0:
+        from ..layers.l2a import L2AAttention
+        if any(isinstance(m, L2AAttention) for m in model.modules()):
+            from .l2a import L2ALoss
+            loss_fn = L2ALoss(targs, ft_args.lambda_reg, ft_args.lambda_reg_scheduler)
+            info_rank0(logger, "L2A objective: language-model loss + lambda(step) x router sparsity term, lambda up to "
+                       "%.3g (%s ramp after warm-up)", ft_args.lambda_reg, ft_args.lambda_reg_scheduler)
     if stage == "ppo":
         return run_ppo(model, ft_args, run_args, dataset, tokenizer, device, bsz)
     trainer = Trainer(model, targs, device=device, loss_fn=loss_fn, callbacks=build_callbacks(run_args, model_args))

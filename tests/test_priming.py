@@ -75,3 +75,33 @@ def test_fused_then_unfuse(tmp_path):
                                fused.state_dict()["model.layers.1.gdn.g_proj.weight"])
     out = unfuse_checkpoint(cfg.output_dir)
     assert out.endswith("_unfused") and os.path.exists(os.path.join(out, "config.json"))
+
+
+def test_stage0_builds_an_l2a_model_and_trains_with_the_sparsity_term(tmp_path):
+    """L2A construction: both attention streams and the second norm start from the layer they replace, the router at
+    zero (every token takes global attention); ``hmf train`` with ``lambda_reg`` adds the router sparsity term."""
+    from hybrid_model_factory_b200.train.workflow import run_exp
+    base, d = _base(tmp_path)
+    cfg = load_config({"base_model_name_or_path": d, "hybrid_override_pattern": "L2A-L2A-*-L2A",
+                       "output_dir": str(tmp_path / "l2a"), "dtype": "float32",
+                       "l2a": {"sliding_window": 8, "temperature": 0.1, "leak_prob": 0.0}})
+    model, _ = hybridize_model(cfg)
+    sd, bsd = model.state_dict(), base.state_dict()
+    for name in ("q_proj", "k_proj", "v_proj", "o_proj", "q_norm", "k_norm"):
+        src = bsd[f"model.layers.1.self_attn.{name}.weight"]
+        torch.testing.assert_close(sd[f"model.layers.1.l2a.local.{name}.weight"], src)
+        torch.testing.assert_close(sd[f"model.layers.1.l2a.global_attn.{name}.weight"], src)
+    torch.testing.assert_close(sd["model.layers.3.l2a.global_norm.weight"], bsd["model.layers.3.input_layernorm.weight"])
+    assert sd["model.layers.0.l2a.router.weight"].abs().sum() == 0
+    assert model.config.l2a_config["sliding_window"] == 8
+    model.eval()
+    model(torch.randint(0, 128, (1, 24)))
+    assert all(model.model.layers[i].l2a.last_routed_fraction == 1.0 for i in (0, 1, 3))
+    out = str(tmp_path / "run")
+    tr = run_exp({"model_name_or_path": cfg.output_dir, "stage": "pt", "synthetic": True, "cutoff_len": 32,
+                  "max_steps": 4, "warmup_steps": 1, "output_dir": out, "bf16": False, "pure_bf16": False,
+                  "learning_rate": 1e-3, "lr_scheduler_type": "constant", "per_device_train_batch_size": 2,
+                  "lambda_reg": 0.5, "lambda_reg_scheduler": "constant", "hybrid_learnable_params": "l2a,norm"})
+    from hybrid_model_factory_b200.train.l2a import L2ALoss
+    assert isinstance(tr.loss_fn, L2ALoss) and tr.loss_fn.step >= 4 and tr.loss_fn.last_sparsity
+    assert tr.model.model.layers[0].l2a.router.weight.abs().sum() > 0          # the router has started to move

@@ -348,6 +348,13 @@ def test_multiple_choice_evaluator(tmp_path, capsys):
     assert E.main([str(tmp_path / "ckpt"), "--task", "toy_test", "--task-dir", str(tmp_path / "evaluation"), "--n-shot", "1",
                    "--template", "qwen3"]) == 0
     assert "Average" in capsys.readouterr().out
+    # the same through a YAML file; an unknown key is refused
+    (tmp_path / "eval.yaml").write_text(f"task: toy_test\ntask_dir: {tmp_path / 'evaluation'}\nn_shot: 1\ntemplate: qwen3\n")
+    assert E.main([str(tmp_path / "ckpt"), "--config", str(tmp_path / "eval.yaml")]) == 0
+    assert "Average" in capsys.readouterr().out
+    (tmp_path / "bad.yaml").write_text("task: toy_test\nshots: 1\n")
+    with pytest.raises(ValueError, match="unknown keys"):
+        E.main([str(tmp_path / "ckpt"), "--config", str(tmp_path / "bad.yaml")])
 
 
 def test_example_configs_parse():
@@ -369,6 +376,16 @@ def test_example_configs_parse():
     for path in train:
         model_args, data_args, run_args, ft_args, _ = get_train_args([path])
         assert ft_args.stage in ("pt", "sft", "hkd", "dpo") and data_args.cutoff_len >= 4096, path
+    # the L2A research example: construction pattern of 36 routed layers, training with the sparsity term
+    l2a = load_config(os.path.join(root, "research", "L2A", "construct_qwen3_8b.yaml"))
+    verify_hybrid_config(l2a, 36)
+    assert set(parse_override_pattern(l2a.hybrid_override_pattern).values()) == {"L2A"} and l2a.l2a["sliding_window"] == 4095
+    _, data_args, _, ft_args, _ = get_train_args([os.path.join(root, "research", "L2A", "train_l2a_qwen3_8b.yaml")])
+    assert ft_args.lambda_reg == 1e-8 and data_args.cutoff_len == 131072
+    pipeline = open(os.path.join(root, "training", "8xB200", "run_pipeline.sh")).read()
+    for rel in ("priming/stage0/qwen3_8b_gdn.yaml", "priming/stage1/hqwen3_8b_gdn.yaml",
+                "priming/stage2/hqwen3_8b_gdn_long_ctx.yaml", "tokenization/pretraining_sp.yaml"):
+        assert os.path.basename(rel) in pipeline and os.path.exists(os.path.join(root, rel)), rel
     stages = {os.path.basename(p): zero_config(p) for p in glob.glob(os.path.join(root, "zero", "*.json"))}
     assert stages["ds_z3_offload_config.json"] == {"zero_stage": 3, "offload_optimizer": True}
     assert stages["ds_z3_mics_config.json"]["mics_shard_size"] == 8 and stages["ds_z2_config.json"]["zero_stage"] == 2
