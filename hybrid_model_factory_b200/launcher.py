@@ -18,6 +18,8 @@ USAGE = """usage: hmf <command> [args]
 
   prime-init CONFIG.yaml         stage 0: initialise a hybrid (or L2A) model from a Transformer checkpoint
   prime-unfuse CKPT [OUT]        convert a fused stage-1 checkpoint to the standard hybrid layout
+  select-layers rank CSV --M N | variants SRC DST   which layers to replace: ranking from per-layer benchmark
+                                 scores, or one sliding-window variant of the checkpoint per layer
   reassemble-vlm TEXT_CKPT VL_CKPT OUT   put a distilled text backbone back into its VL wrapper
   convert-qwen-gdn SRC OUT [--pattern P] convert a Qwen3-Next / Qwen3.5-MoE checkpoint to the hybrid layout
   train CONFIG.yaml [k=v ...]    run a training stage (pt | sft | hkd | dpo | kto | rm)
@@ -92,6 +94,9 @@ def launch(argv: List[str]) -> int:
     if cmd == "convert-qwen-gdn":
         from .priming.convert_qwen_gdn import main as convert_main
         return convert_main(rest)
+    if cmd == "select-layers":
+        from .priming.layer_selection import main as select_main
+        return select_main(rest)
     if cmd == "reassemble-vlm":
         from .priming.reassemble_vlm import reassemble_vlm
         reassemble_vlm(rest[0], rest[1], rest[2])

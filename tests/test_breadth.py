@@ -100,6 +100,25 @@ def test_callbacks_and_layer_selection(tmp_path):
     assert len(variants) == 2
     cfg = json.load(open(os.path.join(variants[1], "config.json")))
     assert cfg["hybrid_override_pattern"] == "*-GDN-SWA" and os.path.islink(os.path.join(variants[1], "model.safetensors"))
+    # a plain Transformer checkpoint has no pattern: attention everywhere
+    plain = tmp_path / "plain"
+    plain.mkdir()
+    (plain / "config.json").write_text(json.dumps({"model_type": "qwen3", "num_hidden_layers": 3}))
+    pv = layer_selection.create_swa_variants(str(plain), str(tmp_path / "pv"))
+    assert [json.load(open(os.path.join(d, "config.json")))["hybrid_override_pattern"] for d in pv] == \
+        ["SWA-*-*", "*-SWA-*", "*-*-SWA"]
+    # ranking from per-variant benchmark scores (one column per task, row -1 = unmodified model)
+    multi = tmp_path / "tasks.csv"
+    multi.write_text("layer_num,helmet_a,helmet_b,other\n-1,0.9,0.8,0.5\n0,0.2,0.2,0.9\n1,0.9,0.7,0.1\n2,0.5,0.5,0.1\n3,0.8,0.8,0.3\n")
+    sel, ranked, base_mean = layer_selection.select_layers(str(multi), 2, task_filter="helmet")
+    assert sel == [1, 3] and ranked[0][0] in (1, 3) and abs(base_mean - 0.85) < 1e-9
+    assert layer_selection.select_layers(str(multi), 1)[0] == [3]                       # mean over all three tasks
+    import io
+    from contextlib import redirect_stdout
+    buf = io.StringIO()
+    with redirect_stdout(buf):
+        assert layer_selection.main(["rank", str(multi), "--M", "2", "--task-filter", "helmet", "--num-layers", "4"]) == 0
+    assert "*-GDN-*-GDN" in buf.getvalue() and "drop:" in buf.getvalue()
 
 
 def test_vl_wrapper_merges_image_features_and_collapses_mrope():
