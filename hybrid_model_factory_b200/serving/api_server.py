@@ -43,6 +43,12 @@ class ControlChannel:
         return box[0]
 
 
+def _params_from_dict(d: dict) -> SamplingParams:
+    d = dict(d)
+    d["stop_token_ids"] = tuple(d.get("stop_token_ids") or ())
+    return SamplingParams(**d)
+
+
 def _params_to_dict(p: SamplingParams) -> dict:
     """Every field: a follower that sampled with other settings than rank 0 would pick other tokens, finish its
     requests at other steps and leave the ranks' collectives unmatched."""
@@ -59,6 +65,8 @@ class EngineLoop:
         self.lock = threading.Lock()
         self.pending: List[tuple] = []
         self.queues: Dict[int, tuple] = {}
+        self.rid_of: Dict[int, int] = {}          # id(queue) -> request id, once the serving thread has admitted it
+        self.aborts: List[int] = []               # id(queue) of requests to end before the next step
         self.wake = threading.Event()
         self.stop = False
         self.error: Optional[BaseException] = None
@@ -71,6 +79,12 @@ class EngineLoop:
             self.pending.append((list(prompt), params, q, loop))
         self.wake.set()
         return None, q
+
+    def abort(self, q) -> None:
+        """Ends the request that feeds ``q`` before the next engine step (all tensor-parallel ranks with it)."""
+        with self.lock:
+            self.aborts.append(id(q))
+        self.wake.set()
 
     def shutdown(self, timeout: float = 20.0) -> None:
         """Stops the serving thread (which also releases the follower ranks) and drops the engine's captured graphs."""
@@ -105,22 +119,36 @@ class EngineLoop:
         while True:
             with self.lock:
                 new, self.pending = self.pending, []
+                wanted, self.aborts = self.aborts, []
+            # a request aborted before it was admitted is simply not added
+            new = [n for n in new if id(n[2]) not in wanted]
+            abort_rids = [self.rid_of[k] for k in wanted if k in self.rid_of]
             stop = self.stop
             if self.control is not None:
-                self.control.broadcast({"add": [(p, _params_to_dict(sp)) for p, sp, _, _ in new], "stop": stop})
+                self.control.broadcast({"add": [(p, _params_to_dict(sp)) for p, sp, _, _ in new], "stop": stop,
+                                        "abort": abort_rids})
             if stop:
                 return
+            for rid in abort_rids:
+                self.engine.abort(rid)
+                entry = self.queues.pop(rid, None)
+                if entry:
+                    self.rid_of.pop(id(entry[0]), None)
             for prompt, params, q, loop in new:
-                self.queues[self.engine.add_request(prompt, params)] = (q, loop)
+                rid = self.engine.add_request(prompt, params)
+                self.queues[rid] = (q, loop)
+                self.rid_of[id(q)] = rid
             busy = self.engine.has_unfinished()
             results = self.engine.step() if busy else []
             for rid, tok, done in results:
                 entry = self.queues.get(rid)
                 if entry:
                     q, loop = entry
-                    loop.call_soon_threadsafe(q.put_nowait, (tok, done))
+                    reason = self.engine.requests[rid].finish_reason if done else None
+                    loop.call_soon_threadsafe(q.put_nowait, (tok, reason or done))
                     if done:
                         self.queues.pop(rid, None)
+                        self.rid_of.pop(id(q), None)
             if not busy:
                 self.wake.wait(timeout=0.05)
                 self.wake.clear()
@@ -136,8 +164,10 @@ def follow(engine: ServingEngine, control: ControlChannel) -> int:
         if msg["stop"]:
             engine.close()
             return steps
+        for rid in msg.get("abort", ()):
+            engine.abort(rid)
         for prompt, params in msg["add"]:
-            engine.add_request(prompt, SamplingParams(**params))
+            engine.add_request(prompt, _params_from_dict(params))
         if engine.has_unfinished():
             engine.step()
             steps += 1
@@ -158,48 +188,92 @@ def create_app(engine: ServingEngine, tokenizer, model_name: str = "hybrid", tem
                               repetition_penalty=float(body.get("repetition_penalty", 1.0)),
                               speculative_tokens=int(body.get("speculative_tokens", 0)),
                               eos_token_id=getattr(tokenizer, "eos_token_id", None),
-                              ignore_eos=bool(body.get("ignore_eos", False)))
+                              ignore_eos=bool(body.get("ignore_eos", False)),
+                              stop_token_ids=tuple(int(t) for t in body.get("stop_token_ids") or ()))
+
+    def stops_of(body: dict) -> List[str]:
+        stop = body.get("stop") or []
+        return [s for s in ([stop] if isinstance(stop, str) else list(stop)) if s]
+
+    class Choice:
+        """One generated sequence: collects tokens from its queue, cuts the text at the first stop string (and has
+        the engine drop the request then), and holds back text that may still turn into a stop string."""
+
+        def __init__(self, index: int, q, stops: List[str]):
+            self.index, self.q, self.stops = index, q, stops
+            self.toks: List[int] = []
+            self.text, self.sent, self.reason, self.failed = "", 0, None, False
+            self.hold = max((len(s) for s in stops), default=1) - 1
+
+        async def advance(self) -> str:
+            """Waits for the next token; returns the text that may be shown now ('' if none yet)."""
+            tok, done = await self.q.get()
+            if tok is None:
+                self.failed, self.reason = True, "error"
+                return ""
+            self.toks.append(tok)
+            full = tokenizer.decode(self.toks)
+            cut = min((full.find(s) for s in self.stops if s in full), default=-1)
+            if cut >= 0:
+                self.text, self.reason = full[:cut], "stop"
+                if not done:
+                    loop_runner.abort(self.q)
+            elif done:
+                self.text, self.reason = full, (done if isinstance(done, str) else "length")
+            elif full.endswith("\ufffd"):
+                return ""                   # incomplete multi-byte character: wait for the rest
+            else:
+                self.text = full
+            upto = len(self.text) if self.reason else max(self.sent, len(self.text) - self.hold)
+            out, self.sent = self.text[self.sent:upto], upto
+            return out
 
     async def run(prompt_ids: List[int], body: dict, chat: bool):
         if loop_runner.error is not None:
             return JSONResponse({"error": repr(loop_runner.error)}, status_code=500)
-        rid, q = loop_runner.submit(prompt_ids, params_from(body), asyncio.get_running_loop())
+        n = max(1, int(body.get("n", 1)))
+        ev_loop = asyncio.get_running_loop()
+        choices = [Choice(i, loop_runner.submit(prompt_ids, params_from(body), ev_loop)[1], stops_of(body))
+                   for i in range(n)]
         created, cid = int(time.time()), f"cmpl-{uuid.uuid4().hex[:12]}"
+
+        async def drain(c: Choice, sink=None):
+            while c.reason is None:
+                piece = await c.advance()
+                if sink is not None and (piece or c.reason):
+                    await sink.put((c, piece))
+
         if body.get("stream"):
             async def gen():
-                toks, sent = [], 0          # incremental detokenisation: a character may span several tokens
-                while True:
-                    tok, done = await q.get()
-                    if tok is None:         # the engine thread failed
+                sink: asyncio.Queue = asyncio.Queue()
+                tasks = [asyncio.ensure_future(drain(c, sink)) for c in choices]
+                live = n
+                while live:
+                    c, piece = await sink.get()
+                    if c.failed:
                         yield "data: " + json.dumps({"error": repr(loop_runner.error)}) + "\n\n"
+                        for t in tasks:
+                            t.cancel()
                         return
-                    toks.append(tok)
-                    full = tokenizer.decode(toks)
-                    if not done and full.endswith("\ufffd"):
-                        continue            # incomplete multi-byte character: wait for the rest
-                    text, sent = full[sent:], len(full)
-                    delta = {"delta": {"content": text}} if chat else {"text": text}
+                    delta = {"delta": {"content": piece}} if chat else {"text": piece}
                     yield "data: " + json.dumps({"id": cid, "created": created, "model": model_name,
-                                                 "choices": [{"index": 0, **delta, "finish_reason": "length" if done else None}]}) + "\n\n"
-                    if done:
-                        yield "data: [DONE]\n\n"
-                        return
+                                                 "choices": [{"index": c.index, **delta, "finish_reason": c.reason}]}) + "\n\n"
+                    live -= c.reason is not None
+                yield "data: [DONE]\n\n"
             return StreamingResponse(gen(), media_type="text/event-stream")
-        toks = []
-        while True:
-            tok, done = await q.get()
-            if tok is None:                 # the engine thread failed
-                return JSONResponse({"error": repr(loop_runner.error)}, status_code=500)
-            toks.append(tok)
-            if done:
-                break
-        text = tokenizer.decode(toks)
-        choice = {"index": 0, "finish_reason": "length"}
-        choice.update({"message": {"role": "assistant", "content": text}} if chat else {"text": text})
+        await asyncio.gather(*[drain(c) for c in choices])
+        if any(c.failed for c in choices):
+            return JSONResponse({"error": repr(loop_runner.error)}, status_code=500)
+        out = []
+        for c in choices:
+            item = {"index": c.index, "finish_reason": c.reason}
+            item.update({"message": {"role": "assistant", "content": c.text}} if chat else {"text": c.text})
+            out.append(item)
+        done_toks = sum(len(c.toks) for c in choices)
         return JSONResponse({"id": cid, "object": "chat.completion" if chat else "text_completion", "created": created,
-                             "model": model_name, "choices": [choice],
-                             "usage": {"prompt_tokens": len(prompt_ids), "completion_tokens": len(toks),
-                                       "total_tokens": len(prompt_ids) + len(toks)}})
+                             "model": model_name, "choices": out,
+                             "usage": {"prompt_tokens": len(prompt_ids), "completion_tokens": done_toks,
+                                       "total_tokens": len(prompt_ids) + done_toks}})
 
     @app.get("/v1/models")
     async def models():

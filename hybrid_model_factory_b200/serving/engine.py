@@ -48,6 +48,7 @@ class SamplingParams:
     #                                   come from the request's own text: the continuation of its latest repeated n-gram)
     eos_token_id: Optional[int] = None
     ignore_eos: bool = True
+    stop_token_ids: tuple = ()        # generation ends after any of these tokens (the token is part of the output)
 
 
 @dataclass
@@ -60,6 +61,7 @@ class RequestState:
     first_token_time: Optional[float] = None
     finish_time: Optional[float] = None
     finished: bool = False
+    finish_reason: Optional[str] = None                 # "length" | "stop" (end-of-sequence or stop token) | "abort"
     ngram_index: dict = field(default_factory=dict)     # speculative decoding: n-gram -> end of its latest occurrence
     ngram_upto: int = 0
     draft_cache: Any = None                             # draft model: its cache over the first `draft_upto` tokens
@@ -427,14 +429,29 @@ class ServingEngine:
         req.output.append(tok)
         self.sched.append_token(rid, tok)
         p = req.params
-        done = len(req.output) >= p.max_new_tokens or (not p.ignore_eos and p.eos_token_id is not None
-                                                       and tok == p.eos_token_id)
+        stopped = (not p.ignore_eos and p.eos_token_id is not None and tok == p.eos_token_id) or \
+            (bool(p.stop_token_ids) and tok in p.stop_token_ids)
+        done = stopped or len(req.output) >= p.max_new_tokens
         if done:
-            req.finished, req.finish_time = True, now
-            self.sched.finish(rid)
-            self._tables.pop(rid, None)
-            self.state.side.pop(rid, None)
+            self._retire(req, "stop" if stopped else "length", now)
         return (rid, tok, done)
+
+    def _retire(self, req: "RequestState", reason: str, now: float) -> None:
+        req.finished, req.finish_time, req.finish_reason = True, now, reason
+        req.draft_cache = None
+        self.sched.finish(req.req_id)
+        self._tables.pop(req.req_id, None)
+        self.state.side.pop(req.req_id, None)
+
+    def abort(self, req_id: int) -> bool:
+        """Ends a request between steps (a stop string seen by the caller, a client that went away): its blocks and
+        state slot are free for the next step.  Under tensor parallelism every rank has to abort the same request
+        before the same step (the API server sends it through the control channel).  Returns whether it was live."""
+        req = self.requests.get(req_id)
+        if req is None or req.finished:
+            return False
+        self._retire(req, "abort", time.perf_counter())
+        return True
 
     # -- sampling ------------------------------------------------------------------------------
     def _sample(self, logits: torch.Tensor, params: List[SamplingParams], histories=None) -> List[int]:

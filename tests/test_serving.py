@@ -379,6 +379,36 @@ def test_openai_compatible_server_routes():
         assert "".join(json.loads(c[6:])["choices"][0]["text"] for c in chunks[:-1]) == tok.decode(want[:3])
         m = await routes["/metrics"]()
         assert m["output_tokens"] >= 11
+        # stop strings: the text ends before the first one, the request is dropped early, the reason says so
+        long = json.loads((await routes["/v1/completions"]({"prompt": prompt, "max_tokens": 12, "ignore_eos": True})).body)
+        text = long["choices"][0]["text"]
+        assert long["choices"][0]["finish_reason"] == "length" and len(text) >= 6
+        stop = text[3:5]
+        cut = json.loads((await routes["/v1/completions"]({"prompt": prompt, "max_tokens": 12, "ignore_eos": True,
+                                                           "stop": stop})).body)
+        assert cut["choices"][0]["text"] == text[:text.find(stop)] and cut["choices"][0]["finish_reason"] == "stop"
+        assert cut["usage"]["completion_tokens"] < 12
+        for _ in range(50):                                        # the serving thread retires it before its next step
+            if not eng.has_unfinished():
+                break
+            await asyncio.sleep(0.02)
+        assert not eng.has_unfinished()
+        assert [r.finish_reason for r in eng.requests.values()][-1] == "abort"
+        # a streamed answer never shows text that turns out to be (the start of) a stop string
+        stream = await routes["/v1/completions"]({"prompt": prompt, "max_tokens": 12, "stream": True, "ignore_eos": True,
+                                                  "stop": [stop]})
+        chunks = [json.loads(c[6:]) for c in [c async for c in stream.body_iterator][:-1]]
+        assert "".join(c["choices"][0]["text"] for c in chunks) == text[:text.find(stop)]
+        assert chunks[-1]["choices"][0]["finish_reason"] == "stop"
+        # stop tokens end a request inside the engine; n > 1 returns that many choices
+        third = tok.encode(text, add_special_tokens=False)[2]
+        st = json.loads((await routes["/v1/completions"]({"prompt": prompt, "max_tokens": 12, "ignore_eos": True,
+                                                          "stop_token_ids": [third]})).body)
+        assert st["choices"][0]["finish_reason"] == "stop" and st["usage"]["completion_tokens"] <= 3
+        many = json.loads((await routes["/v1/completions"]({"prompt": prompt, "max_tokens": 4, "n": 3,
+                                                            "ignore_eos": True})).body)
+        assert [c["index"] for c in many["choices"]] == [0, 1, 2] and many["usage"]["completion_tokens"] == 12
+        assert len({c["text"] for c in many["choices"]}) == 1                      # greedy: identical
     try:
         asyncio.run(scenario())
     finally:
