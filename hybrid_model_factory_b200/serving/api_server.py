@@ -67,6 +67,7 @@ class EngineLoop:
         self.queues: Dict[int, tuple] = {}
         self.rid_of: Dict[int, int] = {}          # id(queue) -> request id, once the serving thread has admitted it
         self.aborts: List[int] = []               # id(queue) of requests to end before the next step
+        self.sent: Dict[int, int] = {}            # request id -> log-probability entries handed out so far
         self.wake = threading.Event()
         self.stop = False
         self.error: Optional[BaseException] = None
@@ -111,7 +112,7 @@ class EngineLoop:
                 self.queues.clear()
                 self.pending = []
             for q, loop in waiting:
-                loop.call_soon_threadsafe(q.put_nowait, (None, True))
+                loop.call_soon_threadsafe(q.put_nowait, (None, True, None))
             import logging
             logging.getLogger(__name__).exception("engine thread stopped: %r", e)
 
@@ -144,11 +145,17 @@ class EngineLoop:
                 entry = self.queues.get(rid)
                 if entry:
                     q, loop = entry
-                    reason = self.engine.requests[rid].finish_reason if done else None
-                    loop.call_soon_threadsafe(q.put_nowait, (tok, reason or done))
+                    req = self.engine.requests[rid]
+                    reason = req.finish_reason if done else None
+                    lp = None
+                    if req.params.logprobs > 0:                 # the entry of this token: results arrive in order
+                        k = self.sent.get(rid, 0)
+                        lp, self.sent[rid] = req.logprobs[k] if k < len(req.logprobs) else None, k + 1
+                    loop.call_soon_threadsafe(q.put_nowait, (tok, reason or done, lp))
                     if done:
                         self.queues.pop(rid, None)
                         self.rid_of.pop(id(q), None)
+                        self.sent.pop(rid, None)
             if not busy:
                 self.wake.wait(timeout=0.05)
                 self.wake.clear()
@@ -189,7 +196,27 @@ def create_app(engine: ServingEngine, tokenizer, model_name: str = "hybrid", tem
                               speculative_tokens=int(body.get("speculative_tokens", 0)),
                               eos_token_id=getattr(tokenizer, "eos_token_id", None),
                               ignore_eos=bool(body.get("ignore_eos", False)),
-                              stop_token_ids=tuple(int(t) for t in body.get("stop_token_ids") or ()))
+                              stop_token_ids=tuple(int(t) for t in body.get("stop_token_ids") or ()),
+                              logprobs=logprobs_wanted(body))
+
+    def logprobs_wanted(body: dict) -> int:
+        """Completions: ``logprobs: k``.  Chat: ``logprobs: true`` with ``top_logprobs: k``."""
+        lp = body.get("logprobs")
+        if lp is True:
+            return max(1, int(body.get("top_logprobs") or 1))
+        return int(lp or 0)
+
+    def logprobs_json(c, chat: bool):
+        if not c.lps:
+            return None
+        word = lambda t: tokenizer.decode([t])  # noqa: E731
+        if chat:
+            return {"content": [{"token": word(t), "logprob": lp, "top_logprobs": [{"token": word(i), "logprob": v}
+                                                                                   for i, v in top]}
+                                for t, (lp, top) in c.lps]}
+        return {"tokens": [word(t) for t, _ in c.lps], "token_logprobs": [lp for _, (lp, _) in c.lps],
+                # (tokens that decode to the same string share a key: the likeliest one keeps it)
+                "top_logprobs": [{word(i): v for i, v in reversed(top)} for _, (_, top) in c.lps]}
 
     def stops_of(body: dict) -> List[str]:
         stop = body.get("stop") or []
@@ -203,11 +230,14 @@ def create_app(engine: ServingEngine, tokenizer, model_name: str = "hybrid", tem
             self.index, self.q, self.stops = index, q, stops
             self.toks: List[int] = []
             self.text, self.sent, self.reason, self.failed = "", 0, None, False
+            self.lps: List[tuple] = []                 # (token, (logprob, [(token, logprob)])) when asked for
             self.hold = max((len(s) for s in stops), default=1) - 1
 
         async def advance(self) -> str:
             """Waits for the next token; returns the text that may be shown now ('' if none yet)."""
-            tok, done = await self.q.get()
+            tok, done, lp = await self.q.get()
+            if lp is not None:
+                self.lps.append((tok, lp))
             if tok is None:
                 self.failed, self.reason = True, "error"
                 return ""
@@ -266,7 +296,7 @@ def create_app(engine: ServingEngine, tokenizer, model_name: str = "hybrid", tem
             return JSONResponse({"error": repr(loop_runner.error)}, status_code=500)
         out = []
         for c in choices:
-            item = {"index": c.index, "finish_reason": c.reason}
+            item = {"index": c.index, "finish_reason": c.reason, "logprobs": logprobs_json(c, chat)}
             item.update({"message": {"role": "assistant", "content": c.text}} if chat else {"text": c.text})
             out.append(item)
         done_toks = sum(len(c.toks) for c in choices)

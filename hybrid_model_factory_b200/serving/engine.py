@@ -49,6 +49,7 @@ class SamplingParams:
     eos_token_id: Optional[int] = None
     ignore_eos: bool = True
     stop_token_ids: tuple = ()        # generation ends after any of these tokens (the token is part of the output)
+    logprobs: int = 0                 # > 0: keep the log-probability of every emitted token and of the k likeliest ones
 
 
 @dataclass
@@ -62,6 +63,7 @@ class RequestState:
     finish_time: Optional[float] = None
     finished: bool = False
     finish_reason: Optional[str] = None                 # "length" | "stop" (end-of-sequence or stop token) | "abort"
+    logprobs: List[tuple] = field(default_factory=list)  # per emitted token: (its logprob, [(token, logprob)] of the top k)
     ngram_index: dict = field(default_factory=dict)     # speculative decoding: n-gram -> end of its latest occurrence
     ngram_upto: int = 0
     draft_cache: Any = None                             # draft model: its cache over the first `draft_upto` tokens
@@ -245,8 +247,9 @@ class ServingEngine:
             if self._timed_replay:      # the sampled ids were read back, so the replay has finished
                 self.stats["decode_gpu_s"] += self._events[0].elapsed_time(self._events[1]) * 1e-3
                 self._timed_replay = False
-            for s, t in zip(decodes, toks):
+            for row, (s, t) in enumerate(zip(decodes, toks)):
                 self.sched.advance(s.req_id, 1)
+                self._note_logprobs(s.req_id, logits[row], int(t))
                 results.append(self._emit(s.req_id, int(t)))
             self.stats["decode_tokens"] += len(decodes)
             self.stats["decode_steps"] += 1
@@ -280,6 +283,7 @@ class ServingEngine:
             if end >= len(req.prompt) + len(req.output):
                 hist = [req.prompt + req.output] if req.params.repetition_penalty != 1.0 else None
                 tok = self._sample(logits[-1:], [req.params], hist)[0]
+                self._note_logprobs(s.req_id, logits[-1], int(tok))
                 results.append(self._emit(s.req_id, int(tok)))
         if prefills:
             self.stats["prefill_s"] += time.perf_counter() - t0
@@ -388,6 +392,8 @@ class ServingEngine:
                 redo.append((s, toks[:n_acc + 1]))
             self.stats["spec_drafted"] += len(drafts)
             self.stats["spec_accepted"] += n_acc
+            for i in range(n_acc + 1):
+                self._note_logprobs(s.req_id, logits[cu[j] + i], int(mine[i]))
             verified.append((s, mine[:n_acc + 1]))
         if redo:
             self._pieces_forward(redo, want_logits=False)
@@ -436,9 +442,21 @@ class ServingEngine:
             self._retire(req, "stop" if stopped else "length", now)
         return (rid, tok, done)
 
+    def _note_logprobs(self, rid: int, row: torch.Tensor, tok: int) -> None:
+        """Log-probabilities of the model's distribution (before temperature / penalties) for a token about to be
+        emitted, when the request asked for them."""
+        req = self.requests[rid]
+        k = req.params.logprobs
+        if k <= 0:
+            return
+        lp = torch.log_softmax(row.float(), dim=-1)
+        top = lp.topk(min(k, lp.numel()))
+        req.logprobs.append((float(lp[tok]), list(zip(top.indices.tolist(), top.values.tolist()))))
+
     def _retire(self, req: "RequestState", reason: str, now: float) -> None:
         req.finished, req.finish_time, req.finish_reason = True, now, reason
         req.draft_cache = None
+        del req.logprobs[len(req.output):]          # (a verify step may have scored tokens past the end)
         self.sched.finish(req.req_id)
         self._tables.pop(req.req_id, None)
         self.state.side.pop(req.req_id, None)

@@ -409,6 +409,18 @@ def test_openai_compatible_server_routes():
                                                             "ignore_eos": True})).body)
         assert [c["index"] for c in many["choices"]] == [0, 1, 2] and many["usage"]["completion_tokens"] == 12
         assert len({c["text"] for c in many["choices"]}) == 1                      # greedy: identical
+        # log-probabilities: the greedy token is the likeliest one, values are those of the model's own distribution
+        lp = json.loads((await routes["/v1/completions"]({"prompt": prompt, "max_tokens": 4, "ignore_eos": True,
+                                                          "logprobs": 3})).body)["choices"][0]["logprobs"]
+        assert len(lp["tokens"]) == 4 and all(1 <= len(t) <= 3 for t in lp["top_logprobs"])    # (bytes may decode alike)
+        assert all(abs(max(t.values()) - v) < 1e-6 for t, v in zip(lp["top_logprobs"], lp["token_logprobs"]))
+        with torch.no_grad():
+            ref_lp = torch.log_softmax(model(input_ids=torch.tensor([ids])).logits[0, -1].float(), -1).max()
+        assert abs(float(ref_lp) - lp["token_logprobs"][0]) < 1e-4
+        clp = json.loads((await routes["/v1/chat/completions"]({"messages": [{"role": "user", "content": "hi"}],
+                                                                "max_tokens": 2, "ignore_eos": True, "logprobs": True,
+                                                                "top_logprobs": 2})).body)["choices"][0]["logprobs"]
+        assert len(clp["content"]) == 2 and len(clp["content"][0]["top_logprobs"]) == 2
     try:
         asyncio.run(scenario())
     finally:
