@@ -234,6 +234,29 @@ class Template:
                                                                              else __import__("json").dumps(tools))
         return out, system
 
+    def extract_tool_calls(self, text: str):
+        """``(remaining text, [{"name": ..., "arguments": {...}}, ...])``: the blocks of an answer that have the shape
+        of ``function_fmt`` and hold a JSON object with a ``name``; anything else stays text."""
+        import json as _json
+        import re
+        head, _, tail = self.function_fmt.partition("{content}")
+        head, tail = head.strip(), tail.strip()
+        if not head or not tail:
+            return text, []
+        calls, rest, pos = [], [], 0
+        for m in re.finditer(re.escape(head) + r"\s*(.*?)\s*" + re.escape(tail), text, flags=re.S):
+            try:
+                obj = _json.loads(m.group(1))
+            except ValueError:
+                continue
+            if not isinstance(obj, dict) or "name" not in obj:
+                continue
+            calls.append({"name": obj["name"], "arguments": obj.get("arguments", obj.get("parameters", {}))})
+            rest.append(text[pos:m.start()])
+            pos = m.end()
+        rest.append(text[pos:])
+        return "".join(rest).strip() if calls else text, calls
+
     def encode_multiturn(self, tokenizer, messages: Sequence[dict], system: str = "") -> List[Tuple[List[int], List[int]]]:
         """Returns ``[(prompt_ids, response_ids), ...]`` per user/assistant exchange."""
         pairs = []

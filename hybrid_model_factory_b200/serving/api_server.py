@@ -316,16 +316,56 @@ def create_app(engine: ServingEngine, tokenizer, model_name: str = "hybrid", tem
             prompt if isinstance(prompt, str) else prompt[0], add_special_tokens=False)
         return await run(list(ids), body, chat=False)
 
+    def chat_turns(msgs: List[dict]) -> List[dict]:
+        """OpenAI chat messages -> the template's roles: ``tool`` results become observations, assistant turns that
+        carry ``tool_calls`` become function turns (a JSON list of ``{name, arguments}``)."""
+        turns = []
+        for m in msgs:
+            if m["role"] == "system":
+                continue
+            if m["role"] == "tool":
+                turns.append({"role": "observation", "content": m.get("content") or ""})
+            elif m["role"] == "assistant" and m.get("tool_calls"):
+                calls = []
+                for c in m["tool_calls"]:
+                    fn = c.get("function", c)
+                    args = fn.get("arguments", {})
+                    calls.append({"name": fn["name"], "arguments": json.loads(args) if isinstance(args, str) else args})
+                turns.append({"role": "function", "content": json.dumps(calls, ensure_ascii=False)})
+            else:
+                content = m.get("content") or ""
+                if isinstance(content, list):           # content parts: the text ones
+                    content = "".join(p.get("text", "") for p in content if p.get("type", "text") == "text")
+                turns.append({"role": m["role"], "content": content})
+        return turns
+
     @app.post("/v1/chat/completions")
     async def chat(body: dict):
         msgs = body.get("messages", [])
         system = next((m["content"] for m in msgs if m["role"] == "system"), "")
-        turns = [m for m in msgs if m["role"] != "system"] + [{"role": "assistant", "content": ""}]
-        pairs = tpl.encode_multiturn(tokenizer, turns, system)
+        turns = chat_turns(msgs)
+        tools = body.get("tools") or []
+        if tools or any(t["role"] in ("function", "observation") for t in turns):
+            turns, system = tpl.normalise(turns, system, json.dumps([t.get("function", t) for t in tools],
+                                                                    ensure_ascii=False) if tools else "")
+        pairs = tpl.encode_multiturn(tokenizer, turns + [{"role": "assistant", "content": ""}], system)
         ids: List[int] = []
         for i, (p, r) in enumerate(pairs):
             ids += p + (r if i < len(pairs) - 1 else [])
-        return await run(ids, body, chat=True)
+        resp = await run(ids, body, chat=True)
+        if tools and not body.get("stream") and getattr(resp, "status_code", 200) == 200:
+            data = json.loads(resp.body)                # answers that call tools: structured calls instead of text
+            for choice in data["choices"]:
+                text, calls = tpl.extract_tool_calls(choice["message"]["content"])
+                if calls:
+                    choice["message"]["content"] = text or None
+                    choice["message"]["tool_calls"] = [
+                        {"id": f"call_{uuid.uuid4().hex[:16]}", "type": "function",
+                         "function": {"name": c["name"], "arguments": json.dumps(c["arguments"], ensure_ascii=False)}}
+                        for c in calls]
+                    choice["finish_reason"] = "tool_calls"
+            return JSONResponse(data)
+        return resp
 
     @app.post("/v1/score/evaluation")
     async def score(body: dict):

@@ -427,6 +427,62 @@ def test_openai_compatible_server_routes():
         app.state.loop_runner.stop = True          # ends the engine thread
 
 
+def test_chat_route_formats_tools_and_returns_structured_calls():
+    """``tools`` are written into the system prompt in the template's format, earlier tool traffic becomes function /
+    observation turns, and an answer holding a call block comes back as ``tool_calls``."""
+    import asyncio
+    import json
+    from hybrid_model_factory_b200.data.formats import ByteTokenizer, get_template
+    from hybrid_model_factory_b200.serving import api_server
+    tpl = get_template("qwen3")
+    text, calls = tpl.extract_tool_calls('Let me look.\n<tool_call>\n{"name": "weather", "arguments": {"city": "Oslo"}}\n'
+                                         '</tool_call>\n<tool_call>\n{"name": "time", "arguments": {}}\n</tool_call>')
+    assert text == "Let me look." and [c["name"] for c in calls] == ["weather", "time"] and calls[0]["arguments"] == {"city": "Oslo"}
+    assert tpl.extract_tool_calls("<tool_call>\nnot json\n</tool_call>") == ("<tool_call>\nnot json\n</tool_call>", [])
+    torch.manual_seed(0)
+    model = build_model(tiny("*-GDN", vocab_size=259)).eval()
+    eng = ServingEngine(model, block_size=8, num_blocks=256, max_num_seqs=2, max_num_batched_tokens=1024, max_model_len=1024)
+    tok = ByteTokenizer()
+    app = api_server.create_app(eng, tok, model_name="tiny", template="qwen3")
+    routes = {r.path: r.endpoint for r in app.routes if hasattr(r, "endpoint")}
+    seen = {}
+    real_submit = app.state.loop_runner.submit
+
+    def spy(prompt, params, loop):
+        seen["prompt"] = tok.decode(prompt)
+        return real_submit(prompt, params, loop)
+    app.state.loop_runner.submit = spy
+    answer = '<tool_call>\n{"name": "weather", "arguments": {"city": "Oslo"}}\n</tool_call>'
+    real_decode = tok.decode
+    tools = [{"type": "function", "function": {"name": "weather", "parameters": {"type": "object"}}}]
+    msgs = [{"role": "user", "content": "weather in Bergen?"},
+            {"role": "assistant", "content": None, "tool_calls": [{"id": "c1", "type": "function", "function": {
+                "name": "weather", "arguments": "{\"city\": \"Bergen\"}"}}]},
+            {"role": "tool", "tool_call_id": "c1", "content": "rain"},
+            {"role": "user", "content": "and Oslo?"}]
+
+    async def scenario():
+        tok.decode = lambda ids: answer if len(ids) <= 4 else real_decode(ids)     # the "model" answers with a call
+        try:
+            resp = await routes["/v1/chat/completions"]({"messages": msgs, "tools": tools, "max_tokens": 4,
+                                                         "ignore_eos": True})
+        finally:
+            tok.decode = real_decode
+        return json.loads(resp.body)
+    try:
+        body = asyncio.run(scenario())
+    finally:
+        app.state.loop_runner.stop = True
+    prompt = seen["prompt"]
+    assert "# Tools" in prompt and '"name": "weather"' in prompt
+    assert '<tool_call>\n{"name": "weather", "arguments": {"city": "Bergen"}}\n</tool_call>' in prompt
+    assert "<tool_response>\nrain\n</tool_response>" in prompt and prompt.rstrip().endswith("<|im_start|>assistant")
+    choice = body["choices"][0]
+    assert choice["finish_reason"] == "tool_calls" and choice["message"]["content"] is None
+    call = choice["message"]["tool_calls"][0]
+    assert call["function"]["name"] == "weather" and json.loads(call["function"]["arguments"]) == {"city": "Oslo"}
+
+
 def test_plugin_registry_targets_resolve_to_the_native_models():
     import importlib
     from hybrid_model_factory_b200.serving import vllm_plugin
