@@ -414,7 +414,7 @@ def main(argv=None) -> int:
     import os
     world, local = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("LOCAL_RANK", "0"))
     device = torch.device("cuda", local) if torch.cuda.is_available() else torch.device("cpu")
-    model = checkpoint_io.from_pretrained(args.model, device=device, **overrides)
+    model = checkpoint_io.from_pretrained(args.model, device=device, init="meta", **overrides)
     tp = control = None
     if world > 1:       # launched by torchrun: tensor parallel over all ranks, rank 0 serves HTTP
         import torch.distributed as dist
@@ -430,7 +430,7 @@ def main(argv=None) -> int:
         shard_model(model, tp)
         torch.manual_seed(0)           # stochastic sampling must draw the same numbers on every rank
         control = ControlChannel()
-    draft = checkpoint_io.from_pretrained(args.draft_model, device=device) if args.draft_model else None
+    draft = checkpoint_io.from_pretrained(args.draft_model, device=device, init="meta") if args.draft_model else None
     engine = ServingEngine(model, max_num_seqs=args.max_num_seqs, max_num_batched_tokens=args.max_num_batched_tokens,
                            max_model_len=args.max_model_len, enable_prefix_caching=args.enable_prefix_caching, tp=tp,
                            draft_model=draft)

@@ -83,7 +83,7 @@ def main(argv=None) -> int:
         if os.environ.get("HMF_TP_FUSED", "1") == "1":
             tp.enable_fused_gemm(max_m=256, max_n=8192)
     if args.model:
-        model = checkpoint_io.from_pretrained(args.model, device=dev)
+        model = checkpoint_io.from_pretrained(args.model, device=dev, init="meta")
     else:
         cfg = qwen3_8b_config(args.pattern, num_hidden_layers=args.layers)
         torch.set_default_dtype(torch.bfloat16)

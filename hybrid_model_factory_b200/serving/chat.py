@@ -18,7 +18,7 @@ def main(argv=None) -> int:
     ap.add_argument("--temperature", type=float, default=0.0)
     args = ap.parse_args(argv)
     device = torch.device("cuda", 0) if torch.cuda.is_available() else torch.device("cpu")
-    model = checkpoint_io.from_pretrained(args.model, device=device)
+    model = checkpoint_io.from_pretrained(args.model, device=device, init="meta")
     tok, tpl = load_tokenizer(args.model), get_template(args.template)
     engine = ServingEngine(model, max_num_seqs=1, max_model_len=8192)
     history = []

@@ -161,7 +161,7 @@ def main(argv=None) -> int:
         ap.set_defaults(**given)
     a = ap.parse_args(argv)
     device = torch.device("cuda", 0) if torch.cuda.is_available() else torch.device("cpu")
-    model = checkpoint_io.from_pretrained(a.model, device=device)
+    model = checkpoint_io.from_pretrained(a.model, device=device, init="meta")
     ev = Evaluator(model, load_tokenizer(a.model), get_template(a.template),
                    EvaluationArguments(a.task, a.task_dir, a.batch_size, a.seed, a.lang, a.n_shot, a.save_dir))
     res = ev.evaluate()

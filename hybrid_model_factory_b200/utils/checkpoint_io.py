@@ -184,20 +184,34 @@ def load_state_dict_into(model: torch.nn.Module, path: str, strict: bool = False
 
 
 def from_pretrained(path: str, dtype: Optional[torch.dtype] = None, device=None, allow_missing: bool = False,
-                    **config_overrides):
+                    init: str = "default", **config_overrides):
     """Builds the model named by ``config.json`` and loads its weights.
 
     A parameter of the model that the checkpoint does not hold raises ``KeyError`` unless ``allow_missing`` is set
     (a converted or adapter-wrapped checkpoint whose names do not match would otherwise leave random weights in
     place without a sound); checkpoint tensors that the model does not own are reported with a warning.  Both lists
-    are kept in ``model._load_report``."""
+    are kept in ``model._load_report``.
+
+    ``init="meta"`` builds the module tree without storage, allocates it directly in the target dtype on the target
+    device and fills it from the checkpoint: no random initialisation and no fp32 copy in host memory (an 8B model
+    otherwise passes through 32 GB of it).  Every parameter must then come from the checkpoint."""
     from ..models.configuration import HybridConfig
     from ..models.modeling_hybrid import build_model
     cfg = HybridConfig.from_pretrained(path, **config_overrides)
     dt = dtype or getattr(torch, str(cfg.torch_dtype).replace("torch.", ""), torch.bfloat16)
-    model = build_model(cfg).to(dt)
-    if device is not None:
-        model = model.to(device)
+    if init == "meta":
+        with torch.device("meta"):
+            model = build_model(cfg).to(dt)
+        model = model.to_empty(device=device if device is not None else "cpu")
+        if getattr(cfg, "tie_word_embeddings", False) and hasattr(model, "lm_head"):
+            model.lm_head.weight = model.get_input_embeddings().weight       # allocation un-ties shared parameters
+        allow_missing = False
+    elif init == "default":
+        model = build_model(cfg).to(dt)
+        if device is not None:
+            model = model.to(device)
+    else:
+        raise ValueError(f"init must be 'default' or 'meta', not {init!r}")
     missing, unexpected = load_state_dict_into(model, path)
     model._load_report = {"missing": missing, "unexpected": unexpected}
     if missing and not allow_missing:

@@ -6,6 +6,7 @@ weighted by valid tokens over micro-batches and data-parallel ranks.  Counterpar
 (``train/optimizer.py``, ``train/zero3.py``) instead of FSDP2."""
 from .batching import BatchGenerator, StatefulBuffer  # noqa: F401
 from .data_engine import DataEngine  # noqa: F401
+from .model_engine import InitPlugin, KernelPlugin, ModelEngine, PeftPlugin, register_kernel  # noqa: F401
 from .plugin import BatchingStrategy, DataConverter, Plugin  # noqa: F401
 from .rendering import Renderer  # noqa: F401
 from .trainer import SFTTrainerV1, V1TrainingArguments  # noqa: F401

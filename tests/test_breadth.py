@@ -1079,3 +1079,37 @@ def test_qlora_quantised_base_trains_adapters_only():
         assert merge_lora(model) == len(wrapped)
         assert not any(isinstance(m, QuantizedLinear) for m in model.modules())
         assert torch.allclose(model(input_ids=ids).logits, before, atol=1e-4)
+
+
+@pytest.mark.parametrize("pattern", ["*-GDN-GKA-M2", "SWA-BMF-L2A-*"])
+def test_meta_device_loading_matches_default_loading(tmp_path, pattern):
+    """A model built without storage and filled from the checkpoint computes what the ordinarily loaded one does (every
+    tensor the forward pass needs is a parameter or is recomputed: rotary frequencies stay fp32 under a bf16 cast), tied
+    embeddings stay tied, and an incomplete checkpoint is refused."""
+    from hybrid_model_factory_b200.layers.common import RotaryEmbedding
+    from hybrid_model_factory_b200.utils import checkpoint_io
+    torch.manual_seed(0)
+    extra = {"l2a_config": {"sliding_window": 6, "leak_prob": 0.0}} if "L2A" in pattern else {}
+    model = build_model(_cfg(pattern, tie_word_embeddings=True, **extra)).eval()
+    model.lm_head.weight = model.model.embed_tokens.weight
+    checkpoint_io.save_pretrained(model, str(tmp_path / "m"))
+    ids = torch.randint(0, 128, (1, 14))
+    a = checkpoint_io.from_pretrained(str(tmp_path / "m"), dtype=torch.float32).eval()
+    b = checkpoint_io.from_pretrained(str(tmp_path / "m"), dtype=torch.float32, init="meta").eval()
+    with torch.no_grad():
+        assert torch.allclose(a(input_ids=ids).logits, b(input_ids=ids).logits, atol=1e-5)
+    assert b.lm_head.weight is b.model.embed_tokens.weight
+    assert not any(p.is_meta for p in b.parameters()) and not any(t.is_meta for t in b.buffers())
+    half = checkpoint_io.from_pretrained(str(tmp_path / "m"), dtype=torch.bfloat16, init="meta")
+    rot = [m for m in half.modules() if isinstance(m, RotaryEmbedding)]
+    assert rot and all(m.inv_freq.dtype == torch.float32 for m in rot)
+    ref_inv = RotaryEmbedding(rot[0].dim, rot[0].theta, rot[0].scaling, rot[0].max_position).inv_freq
+    assert torch.equal(rot[0].inv_freq, ref_inv)
+    # drop one tensor from the checkpoint: meta loading cannot invent it
+    from safetensors.torch import load_file, save_file
+    f = next(p for p in (tmp_path / "m").iterdir() if p.suffix == ".safetensors")
+    sd = load_file(str(f))
+    sd.pop(next(k for k in sd if k.endswith("mlp.up_proj.weight")))
+    save_file(sd, str(f))
+    with pytest.raises(KeyError, match="not in the checkpoint"):
+        checkpoint_io.from_pretrained(str(tmp_path / "m"), dtype=torch.float32, init="meta", allow_missing=True)

@@ -182,3 +182,48 @@ def test_plugins_register_by_name_and_serve_the_data_engine(tmp_path):
     assert len(step) == 4 and all(len(mb["cu_seqlens"]) == 2 for mb in step)
     with pytest.raises(ValueError, match="unknown batching strategy"):
         BatchGenerator(eng, rnd, strategy="no_such_strategy")
+
+
+def test_model_engine_plugins_and_launcher_sections(tmp_path):
+    """Init / peft / kernel plugins: meta loading equals default loading, LoRA leaves only adapters trainable, an unknown
+    kernel name is refused, and a YAML with the three sections trains and saves a model in the ordinary layout."""
+    import pytest
+    from hybrid_model_factory_b200.utils import checkpoint_io
+    from hybrid_model_factory_b200.v1 import ModelEngine, register_kernel
+    from hybrid_model_factory_b200.v1.launcher import main
+    torch.manual_seed(0)
+    cfg = HybridConfig("hybrid_qwen3", vocab_size=259, hidden_size=32, intermediate_size=64, num_hidden_layers=2,
+                       num_attention_heads=2, num_key_value_heads=1, head_dim=16, hybrid_override_pattern="*-GDN")
+    checkpoint_io.save_pretrained(build_model(cfg), str(tmp_path / "model"))
+    ids = torch.randint(0, 259, (1, 9))
+    a = ModelEngine(str(tmp_path / "model"), dtype=torch.float32, is_train=False)
+    b = ModelEngine(str(tmp_path / "model"), dtype=torch.float32, is_train=False, init_config={"name": "init_on_meta"})
+    c = ModelEngine(str(tmp_path / "model"), dtype=torch.float32, is_train=False, init_config={"name": "init_on_rank0"})
+    with torch.no_grad():
+        ref = a.model(input_ids=ids).logits
+        assert torch.allclose(b.model(input_ids=ids).logits, ref, atol=1e-6)
+        assert torch.allclose(c.model(input_ids=ids).logits, ref, atol=1e-6)
+    seen = []
+
+    @register_kernel("count_layers")
+    def _count(model):
+        seen.append(len(model.model.layers))
+        return len(model.model.layers)
+    lora = ModelEngine(str(tmp_path / "model"), dtype=torch.float32, peft_config={"name": "lora", "rank": 2},
+                       kernel_config={"name": "auto", "include_kernels": ["own_linear", "count_layers"]})
+    names = [n for n, p in lora.model.named_parameters() if p.requires_grad]
+    assert names and all("lora_" in n for n in names) and lora.trainable_parameters() < 4000
+    assert seen == [2] and lora.model.applied_kernels["count_layers"] == 2
+    frozen = ModelEngine(str(tmp_path / "model"), dtype=torch.float32, peft_config={"name": "freeze", "trainable_layers": 1})
+    assert 0 < frozen.trainable_parameters() < sum(p.numel() for p in frozen.model.parameters())
+    with pytest.raises(ValueError, match="unknown kernels"):
+        ModelEngine(str(tmp_path / "model"), dtype=torch.float32, kernel_config={"include_kernels": ["no_such"]})
+    _engine(tmp_path)
+    out = tmp_path / "out"
+    (tmp_path / "run.yaml").write_text(
+        f"model: {tmp_path / 'model'}\ntrain_dataset: {tmp_path / 'mix.yaml'}\noutput_dir: {out}\n"
+        "micro_batch_size: 2\nglobal_batch_size: 4\nmax_steps: 2\nbf16: false\ncutoff_len: 48\nlearning_rate: 1.0e-3\n"
+        "init_config:\n  name: init_on_meta\npeft_config:\n  name: lora\n  rank: 2\nkernel_config:\n  name: auto\n")
+    assert main([str(tmp_path / "run.yaml"), "lr_scheduler=constant"]) == 0
+    again = checkpoint_io.from_pretrained(str(out), dtype=torch.float32)          # strict: no adapter tensors left
+    assert not any("lora" in n for n, _ in again.named_parameters())
