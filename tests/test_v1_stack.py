@@ -227,3 +227,28 @@ def test_model_engine_plugins_and_launcher_sections(tmp_path):
     assert main([str(tmp_path / "run.yaml"), "lr_scheduler=constant"]) == 0
     again = checkpoint_io.from_pretrained(str(out), dtype=torch.float32)          # strict: no adapter tensors left
     assert not any("lora" in n for n, _ in again.named_parameters())
+
+
+def test_v1_sampler_streams_and_answers_a_dataset(tmp_path):
+    import asyncio
+    from hybrid_model_factory_b200.utils import checkpoint_io
+    from hybrid_model_factory_b200.v1 import ModelEngine
+    from hybrid_model_factory_b200.v1.sampler import Sampler
+    torch.manual_seed(0)
+    cfg = HybridConfig("hybrid_qwen3", vocab_size=259, hidden_size=32, intermediate_size=64, num_hidden_layers=2,
+                       num_attention_heads=2, num_key_value_heads=1, head_dim=16, hybrid_override_pattern="*-GDN")
+    checkpoint_io.save_pretrained(build_model(cfg), str(tmp_path / "model"))
+    me = ModelEngine(str(tmp_path / "model"), dtype=torch.float32, is_train=False, init_config={"name": "init_on_meta"})
+    s = Sampler(me, max_new_tokens=6, max_num_seqs=4, max_model_len=256, block_size=8, num_blocks=64)
+    s.params["ignore_eos"] = True
+    msgs = [{"role": "user", "content": "hello there"}]
+    whole = s.chat(msgs)
+
+    async def collect():
+        return [p async for p in s.generate(msgs)]
+    pieces = asyncio.run(collect())
+    assert "".join(pieces) == whole and len(pieces) >= 1
+    rows = [{"messages": [{"role": "user", "content": "a"}, {"role": "assistant", "content": "gold"}]},
+            {"messages": [{"role": "user", "content": "hello there"}]}]
+    out = s.batch_infer(rows)
+    assert out[0]["label"] == "gold" and out[1]["label"] is None and out[1]["prediction"] == whole
