@@ -1113,3 +1113,16 @@ def test_meta_device_loading_matches_default_loading(tmp_path, pattern):
     save_file(sd, str(f))
     with pytest.raises(KeyError, match="not in the checkpoint"):
         checkpoint_io.from_pretrained(str(tmp_path / "m"), dtype=torch.float32, init="meta", allow_missing=True)
+
+
+def test_gptq_awq_unpacking_agrees_with_an_independent_packer():
+    """The integer layouts, checked against the reference packers of an installed serving library (skipped without it)."""
+    quant_utils = pytest.importorskip("vllm.model_executor.layers.quantization.utils.quant_utils")
+    from hybrid_model_factory_b200.utils.quant_loaders import _awq_natural, _unpack
+    torch.manual_seed(0)
+    k, n = 64, 32
+    q = torch.randint(0, 16, (k, n), dtype=torch.int32)
+    assert torch.equal(_unpack(quant_utils.gptq_pack(q, 4, k, n), 4, dim=0), q)
+    assert torch.equal(_awq_natural(_unpack(quant_utils.awq_pack(q, 4, k, n), 4, dim=1), 4), q)
+    q8 = torch.randint(0, 256, (k, n), dtype=torch.int32)
+    assert torch.equal(_unpack(quant_utils.gptq_pack(q8, 8, k, n), 8, dim=0), q8)
