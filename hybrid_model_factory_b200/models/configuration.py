@@ -82,8 +82,11 @@ class HybridConfig:
             # composite (VL) configs keep the language-model fields in text_config
             values.update(kwargs["text_config"])
         values.update(kwargs)
+        if "num_local_experts" in kwargs and "num_experts" not in kwargs:      # newer serialisations name it so
+            values["num_experts"] = kwargs["num_local_experts"]
         for k, v in values.items():
             setattr(self, k, v)
+        self._sync_rope(prefer_parameters="rope_theta" not in kwargs and "rope_scaling" not in kwargs)
         if self.head_dim is None:
             self.head_dim = self.hidden_size // self.num_attention_heads
         if self.num_key_value_heads is None:
@@ -94,10 +97,55 @@ class HybridConfig:
         if len(pat) != self.num_hidden_layers:
             raise ValueError(f"hybrid_override_pattern has {len(pat)} entries but num_hidden_layers="
                              f"{self.num_hidden_layers}")
-        if self.layer_types is None:
+        if getattr(self, "native_window_layers", None) is None:
+            self.native_window_layers = self._native_window_layers(pat)
+        plain = isinstance(self.layer_types, (list, tuple)) and \
+            set(self.layer_types) <= {"full_attention", "sliding_attention"}
+        if self.layer_types is None or (plain and "hybrid_override_pattern" not in kwargs):
+            # (a plain Transformer's list: its sliding layers are now in native_window_layers, the symbols are all `*`)
             self.layer_types = pattern_to_layer_types(self.hybrid_override_pattern)
         if self.mlp_only_layers is None:
             self.mlp_only_layers = []
+
+    def _native_window_layers(self, pat) -> List[int]:
+        """Attention layers (symbol ``*``) that the base architecture runs with its own ``sliding_window``: where the
+        checkpoint's ``layer_types`` say ``sliding_attention``; for older configs without that list, every layer of
+        a Mistral-family model, and the layers from ``max_window_layers`` on of a Qwen model with
+        ``use_sliding_window``."""
+        if not getattr(self, "sliding_window", None):
+            return []
+        n = self.num_hidden_layers
+        types = self.layer_types
+        if isinstance(types, (list, tuple)) and len(types) == n and set(types) <= {"full_attention", "sliding_attention"}:
+            chosen = [i for i, t in enumerate(types) if t == "sliding_attention"]
+        elif "ministral" in self.model_type:
+            chosen = list(range(n))
+        elif getattr(self, "use_sliding_window", False):
+            chosen = list(range(int(getattr(self, "max_window_layers", 0) or 0), n))
+        else:
+            chosen = []
+        return [i for i in chosen if pat[i] == "*"]
+
+    def _sync_rope(self, prefer_parameters: bool) -> None:
+        """Newer checkpoints describe the rotary embedding in one ``rope_parameters`` dict (``rope_theta``,
+        ``rope_type`` and the scaling fields, optionally ``partial_rotary_factor``), older ones in ``rope_theta`` +
+        ``rope_scaling``.  The model reads the older pair; this keeps the two views equal, taking the dict as the
+        source when ``prefer_parameters`` (a config file that holds it) and the pair otherwise (explicit overrides)."""
+        rp = getattr(self, "rope_parameters", None)
+        if isinstance(rp, dict) and rp and prefer_parameters:
+            if rp.get("rope_theta") is not None:
+                self.rope_theta = float(rp["rope_theta"])
+            kind = rp.get("rope_type", rp.get("type", "default"))
+            rest = {k: v for k, v in rp.items() if k not in ("rope_theta", "partial_rotary_factor")}
+            self.rope_scaling = rest if kind not in (None, "default") else None
+            if rp.get("partial_rotary_factor") is not None and hasattr(self, "partial_rotary_factor"):
+                self.partial_rotary_factor = float(rp["partial_rotary_factor"])
+        if isinstance(rp, dict) and rp:
+            new = dict(self.rope_scaling or {"rope_type": "default"})
+            new["rope_theta"] = self.rope_theta
+            if rp.get("partial_rotary_factor") is not None:
+                new["partial_rotary_factor"] = getattr(self, "partial_rotary_factor", rp["partial_rotary_factor"])
+            self.rope_parameters = new
 
     # -- helpers ----------------------------------------------------------------------
     @property
@@ -163,6 +211,11 @@ class HybridConfig:
                 target[parts[-1]] = value
             else:
                 setattr(target, parts[-1], value)
+        keys = list(overrides or {})
+        if any(k.startswith("rope_parameters") for k in keys):
+            self._sync_rope(prefer_parameters=True)
+        elif any(k.split(".")[0] in ("rope_theta", "rope_scaling") for k in keys):
+            self._sync_rope(prefer_parameters=False)
 
     def __repr__(self):
         return f"HybridConfig({self.model_type}, layers={self.num_hidden_layers}, hidden={self.hidden_size}, " \

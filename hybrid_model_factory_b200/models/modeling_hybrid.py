@@ -112,9 +112,17 @@ def load_balancing_loss(router_logits: List[torch.Tensor], num_experts: int, top
 # ----------------------------------------------------------------------------------------
 # decoder layers
 # ----------------------------------------------------------------------------------------
+def _native_window(config: HybridConfig, layer_idx: int):
+    """Window of an attention layer that the *base* architecture itself runs as sliding-window attention (its weights
+    stay under ``self_attn``); ``HybridConfig`` works out which layers those are."""
+    window = getattr(config, "sliding_window", None)
+    return int(window) if window and layer_idx in (getattr(config, "native_window_layers", None) or ()) else None
+
+
 def _make_mixer(symbol: str, config: HybridConfig, layer_idx: int) -> nn.Module:
     if symbol == "*":
-        return Attention(config, layer_idx, gated=bool(config.gated_attention))
+        return Attention(config, layer_idx, gated=bool(config.gated_attention),
+                         sliding_window=_native_window(config, layer_idx))
     if symbol == "SWA":
         return SlidingWindowAttention(config, layer_idx)
     if symbol == "M2":

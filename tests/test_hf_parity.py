@@ -1,0 +1,64 @@
+"""Checkpoints written by the Hugging Face implementations of the base architectures load into this package's models
+and give the same logits (fp32, CPU, tiny random models).  Covers the config dialects of recent ``transformers``
+(``rope_parameters``, ``num_local_experts``, ``layer_types`` with native sliding-window layers) and every rotary scaling
+rule the base families use."""
+import pytest
+import torch
+
+from hybrid_model_factory_b200.utils import checkpoint_io
+
+T = pytest.importorskip("transformers")
+
+COMMON = dict(vocab_size=160, hidden_size=64, intermediate_size=128, num_hidden_layers=3, num_attention_heads=4,
+              num_key_value_heads=2, max_position_embeddings=512)
+
+CASES = {
+    "qwen3": ("Qwen3Config", "Qwen3ForCausalLM", dict(head_dim=16, rope_theta=10000.0)),
+    "qwen3_tied": ("Qwen3Config", "Qwen3ForCausalLM", dict(head_dim=16, tie_word_embeddings=True)),
+    "qwen3_yarn": ("Qwen3Config", "Qwen3ForCausalLM", dict(head_dim=16, rope_parameters={
+        "rope_type": "yarn", "rope_theta": 10000.0, "factor": 4.0, "original_max_position_embeddings": 128})),
+    "qwen3_native_sliding_layers": ("Qwen3Config", "Qwen3ForCausalLM", dict(
+        head_dim=16, sliding_window=8, use_sliding_window=True, max_window_layers=1,
+        layer_types=["full_attention", "sliding_attention", "sliding_attention"])),
+    "qwen2": ("Qwen2Config", "Qwen2ForCausalLM", dict(rope_theta=20000.0)),
+    "qwen2_window_switched_off": ("Qwen2Config", "Qwen2ForCausalLM", dict(sliding_window=8, use_sliding_window=False)),
+    "llama3_rope": ("LlamaConfig", "LlamaForCausalLM", dict(rope_parameters={
+        "rope_type": "llama3", "rope_theta": 50000.0, "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+        "original_max_position_embeddings": 64})),
+    "mistral_sliding": ("MistralConfig", "MistralForCausalLM", dict(head_dim=16, sliding_window=8)),
+    "qwen3_moe": ("Qwen3MoeConfig", "Qwen3MoeForCausalLM", dict(
+        head_dim=16, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=32, decoder_sparse_step=1,
+        norm_topk_prob=True, mlp_only_layers=[])),
+    "qwen3_moe_mixed_dense": ("Qwen3MoeConfig", "Qwen3MoeForCausalLM", dict(
+        head_dim=16, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=32, decoder_sparse_step=2,
+        norm_topk_prob=False, mlp_only_layers=[])),
+}
+
+
+@pytest.mark.parametrize("name", sorted(CASES))
+def test_logits_equal_the_hugging_face_model(tmp_path, name):
+    cfg_name, model_name, extra = CASES[name]
+    if not hasattr(T, cfg_name) or not hasattr(T, model_name):
+        pytest.skip(f"this transformers has no {model_name}")
+    torch.manual_seed(0)
+    try:
+        hf = getattr(T, model_name)(getattr(T, cfg_name)(**COMMON, **extra)).eval()
+    except TypeError as e:                      # a config dialect this transformers version does not speak
+        pytest.skip(str(e))
+    hf.save_pretrained(str(tmp_path / "hf"), safe_serialization=True)
+    own = checkpoint_io.from_pretrained(str(tmp_path / "hf"), dtype=torch.float32).eval()      # strict: every tensor used
+    assert not own._load_report["unexpected"]
+    ids = torch.randint(0, COMMON["vocab_size"], (2, 40))
+    with torch.no_grad():
+        want, got = hf(input_ids=ids).logits, own(input_ids=ids).logits
+    assert torch.allclose(got, want, atol=2e-5), float((got - want).abs().max())
+    # the checkpoint written by this package reloads to the same function (native windows, rotary settings kept)
+    checkpoint_io.save_pretrained(own, str(tmp_path / "own"))
+    again = checkpoint_io.from_pretrained(str(tmp_path / "own"), dtype=torch.float32, init="meta").eval()
+    with torch.no_grad():
+        assert torch.allclose(again(input_ids=ids).logits, want, atol=2e-5)
+    # and decoding with the cache follows the same function (windowed layers included)
+    with torch.no_grad():
+        gen = own.generate(ids[:1, :20], max_new_tokens=4)
+        ref = hf.generate(ids[:1, :20], max_new_tokens=4, do_sample=False)
+    assert gen[0, 20:].tolist() == ref[0, 20:24].tolist()
