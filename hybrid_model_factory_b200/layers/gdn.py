@@ -62,7 +62,9 @@ def construct_gdn_config(config, user: Optional[dict] = None) -> GDNConfig:
         base = dict(hidden_size=config.hidden_size, head_dim=config.linear_key_head_dim,
                     num_q_heads=config.linear_num_key_heads, num_k_heads=config.linear_num_key_heads,
                     num_v_heads=config.linear_num_value_heads,
-                    conv_size=getattr(config, "linear_conv_kernel_dim", 4))
+                    conv_size=getattr(config, "linear_conv_kernel_dim", 4),
+                    # released Gated-DeltaNet checkpoints norm their head outputs with the model's own epsilon
+                    norm_eps=float(getattr(config, "rms_norm_eps", 1e-6)))
     else:
         nh = config.num_attention_heads
         base = dict(hidden_size=config.hidden_size,

@@ -62,3 +62,38 @@ def test_logits_equal_the_hugging_face_model(tmp_path, name):
         gen = own.generate(ids[:1, :20], max_new_tokens=4)
         ref = hf.generate(ids[:1, :20], max_new_tokens=4, do_sample=False)
     assert gen[0, 20:].tolist() == ref[0, 20:24].tolist()
+
+
+def test_converted_qwen3_next_equals_the_hugging_face_model(tmp_path):
+    """A Qwen3-Next checkpoint (Gated DeltaNet layers with fewer key than value heads, gated attention with partial
+    rotary embedding, zero-centred norms, experts + shared expert) through ``hmf convert-qwen-gdn``: same logits, same
+    greedy continuation with the recurrent cache."""
+    if not hasattr(T, "Qwen3NextForCausalLM"):
+        pytest.skip("this transformers has no Qwen3-Next")
+    from hybrid_model_factory_b200.priming.convert_qwen_gdn import convert_checkpoint
+    torch.manual_seed(0)
+    cfg = T.Qwen3NextConfig(
+        vocab_size=160, hidden_size=64, intermediate_size=128, num_hidden_layers=4, num_attention_heads=4,
+        num_key_value_heads=2, head_dim=16, max_position_embeddings=512, linear_num_key_heads=2,
+        linear_num_value_heads=4, linear_key_head_dim=16, linear_value_head_dim=16, linear_conv_kernel_dim=4,
+        num_experts=4, num_experts_per_tok=2, moe_intermediate_size=32, shared_expert_intermediate_size=32,
+        decoder_sparse_step=1, norm_topk_prob=True, full_attention_interval=4, partial_rotary_factor=0.25,
+        mlp_only_layers=[])
+    hf = T.Qwen3NextForCausalLM(cfg).eval()
+    with torch.no_grad():                       # norms, biases and decay parameters away from their initial values
+        for _, p in hf.named_parameters():
+            if p.dim() == 1:
+                p.add_(torch.randn_like(p) * 0.1)
+    hf.save_pretrained(str(tmp_path / "hf"), safe_serialization=True)
+    report = convert_checkpoint(str(tmp_path / "hf"), str(tmp_path / "own"), None, False, torch.float32)
+    assert not report["dropped"] and not report["missing"]
+    own = checkpoint_io.from_pretrained(str(tmp_path / "own"), dtype=torch.float32).eval()
+    assert own.config.hybrid_override_pattern == "GDN-GDN-GDN-*"
+    ids = torch.randint(0, 160, (2, 40))
+    with torch.no_grad():
+        want, got = hf(input_ids=ids).logits, own(input_ids=ids).logits
+    assert torch.allclose(got, want, atol=2e-5), float((got - want).abs().max())
+    with torch.no_grad():
+        gen = own.generate(ids[:1, :24], max_new_tokens=5)
+        ref = hf.generate(ids[:1, :24], max_new_tokens=5, do_sample=False)
+    assert gen[0, 24:].tolist() == ref[0, 24:29].tolist()
