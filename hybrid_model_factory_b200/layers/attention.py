@@ -81,6 +81,13 @@ class Attention(nn.Module):
                 position_ids: Optional[torch.Tensor] = None, **kwargs) -> Tuple[torch.Tensor, None, object]:
         B, T, _ = hidden_states.shape
         q, k, v, gate = self._qkv(hidden_states, position_embeddings, kwargs)
+        beta = (getattr(self.config, "rope_scaling", None) or {}).get("llama_4_scaling_beta")
+        if beta and position_ids is not None:
+            # queries far beyond the original context get a logarithmically growing temperature (Ministral 3):
+            # 1 + beta * log(1 + floor(position / original_max_position_embeddings)), which is 1 inside that context
+            old = float(self.config.rope_scaling.get("original_max_position_embeddings") or 0) or float("inf")
+            scale = 1.0 + float(beta) * torch.log1p(torch.floor(position_ids.to(torch.float32) / old))
+            q = q * scale.reshape(scale.shape[0], T, 1, 1).to(q.dtype)
         sp = self.sequence_parallel_group
         if sp is not None and sp.size > 1:
             if getattr(sp, "mode", "zigzag") == "ulysses":

@@ -87,12 +87,22 @@ def rope_inverse_frequencies(dim: int, theta: float, scaling: Optional[dict], ma
 
         def correction_dim(rotations):
             return dim * math.log(old / (rotations * 2 * math.pi)) / (2 * math.log(theta))
-        low = max(math.floor(correction_dim(beta_fast)), 0)
-        high = min(math.ceil(correction_dim(beta_slow)), dim - 1)
+        low, high = correction_dim(beta_fast), correction_dim(beta_slow)
+        if scaling.get("truncate", True):
+            low, high = math.floor(low), math.ceil(high)
+        low, high = max(low, 0), min(high, dim - 1)
         ramp = ((torch.arange(dim // 2, dtype=torch.float32) - low) / max(high - low, 1e-3)).clamp(0, 1)
         extrapolation = 1 - ramp
         inv = inv / factor * (1 - extrapolation) + inv * extrapolation
-        att = float(scaling.get("attention_factor") or (0.1 * math.log(factor) + 1.0 if factor > 1 else 1.0))
+
+        def mscale(weight=1.0):
+            return 1.0 if factor <= 1 else 0.1 * weight * math.log(factor) + 1.0
+        if scaling.get("attention_factor"):
+            att = float(scaling["attention_factor"])
+        elif scaling.get("mscale") and scaling.get("mscale_all_dim"):      # ratio of the two magnitude corrections
+            att = mscale(float(scaling["mscale"])) / mscale(float(scaling["mscale_all_dim"]))
+        else:
+            att = mscale()
     elif kind == "longrope":
         old = float(scaling.get("original_max_position_embeddings", max_position or 4096))
         ext = torch.tensor(scaling.get("long_factor" if max_position > old else "short_factor"), dtype=torch.float32)

@@ -763,6 +763,11 @@ class ServingEngine:
             if mx.q_norm is not None:
                 q, k = mx.q_norm(q), mx.k_norm(k)
             q, k = F_ops.apply_rope(q, cos, sin)[:, 0], F_ops.apply_rope(k, cos, sin)[:, 0]
+        beta = (getattr(mx.config, "rope_scaling", None) or {}).get("llama_4_scaling_beta")
+        if beta:        # query temperature beyond the original context (see ``Attention.forward``); position = length - 1
+            old = float(mx.config.rope_scaling.get("original_max_position_embeddings") or 0) or float("inf")
+            pos = meta["lens"].to(torch.float32) - 1.0
+            q = q * (1.0 + float(beta) * torch.log1p(torch.floor(pos / old))).view(Rn, 1, 1).to(q.dtype)
         kc, vc = self.state.kv[i]
         window = mx.sliding_window or 0
         if self._cuda and mx.head_dim == 128 and q.dtype == torch.bfloat16:

@@ -97,3 +97,28 @@ def test_converted_qwen3_next_equals_the_hugging_face_model(tmp_path):
         gen = own.generate(ids[:1, :24], max_new_tokens=5)
         ref = hf.generate(ids[:1, :24], max_new_tokens=5, do_sample=False)
     assert gen[0, 24:].tolist() == ref[0, 24:29].tolist()
+
+
+def test_ministral3_long_context_temperature_in_model_and_engine(tmp_path):
+    """Ministral 3: YaRN with equal magnitude corrections (attention factor 1) and a query temperature that grows past
+    the original context.  A tiny original context makes both matter; the forward pass equals Hugging Face's, and the
+    serving engine's decode path generates what the model's own generation does."""
+    if not hasattr(T, "Ministral3ForCausalLM"):
+        pytest.skip("this transformers has no Ministral 3")
+    from hybrid_model_factory_b200.serving.engine import SamplingParams, ServingEngine
+    torch.manual_seed(0)
+    cfg = T.Ministral3Config(**COMMON, head_dim=16, sliding_window=None, rope_parameters={
+        "rope_type": "yarn", "rope_theta": 1e6, "factor": 16.0, "original_max_position_embeddings": 16,
+        "beta_fast": 32.0, "beta_slow": 1.0, "mscale_all_dim": 1.0, "mscale": 1.0, "llama_4_scaling_beta": 0.1})
+    hf = T.Ministral3ForCausalLM(cfg).eval()
+    hf.save_pretrained(str(tmp_path / "hf"), safe_serialization=True)
+    own = checkpoint_io.from_pretrained(str(tmp_path / "hf"), dtype=torch.float32).eval()
+    ids = torch.randint(0, COMMON["vocab_size"], (2, 60))
+    with torch.no_grad():
+        want, got = hf(input_ids=ids).logits, own(input_ids=ids).logits
+    assert torch.allclose(got, want, atol=2e-5), float((got - want).abs().max())
+    prompt = ids[0, :40].tolist()
+    with torch.no_grad():
+        ref = hf.generate(ids[:1, :40], max_new_tokens=6, do_sample=False)[0, 40:].tolist()
+    eng = ServingEngine(own, block_size=8, num_blocks=32, max_num_seqs=2, max_num_batched_tokens=64, max_model_len=128)
+    assert eng.generate([prompt], SamplingParams(max_new_tokens=6))[0] == ref
