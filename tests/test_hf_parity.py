@@ -122,3 +122,59 @@ def test_ministral3_long_context_temperature_in_model_and_engine(tmp_path):
         ref = hf.generate(ids[:1, :40], max_new_tokens=6, do_sample=False)[0, 40:].tolist()
     eng = ServingEngine(own, block_size=8, num_blocks=32, max_num_seqs=2, max_num_batched_tokens=64, max_model_len=128)
     assert eng.generate([prompt], SamplingParams(max_new_tokens=6))[0] == ref
+
+
+def test_image_sizing_and_patch_layout_agree_with_transformers():
+    """The pixel-budget resize, the any-resolution canvas choice, the LLaVA-NeXT token count and the Qwen2-VL patch
+    layout against the ``transformers`` processors (each part skipped when that processor is not importable)."""
+    import random
+    import numpy as np
+    from PIL import Image
+    from hybrid_model_factory_b200.data.mm_plugin import get_mm_plugin, smart_resize
+    from hybrid_model_factory_b200.data.mm_plugin_zoo import LlavaNextPlugin, TowerConfig, select_best_resolution
+    random.seed(0)
+    checked = 0
+    try:
+        from transformers.models.qwen2_vl.image_processing_qwen2_vl import smart_resize as hf_resize
+        for _ in range(500):
+            h, w = random.randint(28, 3000), random.randint(28, 3000)
+            if max(h, w) / min(h, w) <= 200:
+                assert tuple(smart_resize(h, w, 28, 56 * 56, 28 * 28 * 1280)) == tuple(hf_resize(h, w, 28, 56 * 56, 28 * 28 * 1280))
+        checked += 1
+    except ImportError:
+        pass
+    pins = [(336, 672), (672, 336), (672, 672), (1008, 336), (336, 1008)]
+    try:
+        from transformers.image_processing_utils import select_best_resolution as hf_best
+        for _ in range(500):
+            size = (random.randint(50, 2000), random.randint(50, 2000))
+            assert tuple(select_best_resolution(size, pins)) == tuple(hf_best(size, pins))
+        checked += 1
+    except ImportError:
+        pass
+    try:
+        from transformers import LlavaNextProcessor
+        proc = LlavaNextProcessor.__new__(LlavaNextProcessor)
+        proc.patch_size, proc.num_additional_image_tokens, proc.vision_feature_select_strategy = 14, 0, "default"
+        proc.image_processor = type("IP", (), {"image_grid_pinpoints": [list(p) for p in pins],
+                                               "size": {"shortest_edge": 336}, "crop_size": {"height": 336, "width": 336}})()
+        plug, tower = LlavaNextPlugin("<image>", None, None), TowerConfig()
+        for _ in range(300):
+            h, w = random.randint(40, 2500), random.randint(40, 2500)
+            assert plug._counts(h, w, tower) == proc._get_number_of_features(h, w, 336, 336), (h, w)
+        checked += 1
+    except (ImportError, AttributeError):
+        pass
+    try:
+        from transformers.models.qwen2_vl.image_processing_qwen2_vl import Qwen2VLImageProcessor
+        img = Image.fromarray((np.random.default_rng(0).random((173, 311, 3)) * 255).astype("uint8"))
+        mine = get_mm_plugin("qwen2_vl", image_token="<|image_pad|>", video_token="<|video_pad|>").get_mm_inputs(images=[img])
+        theirs = Qwen2VLImageProcessor()(images=[img], return_tensors="pt")
+        assert mine["image_grid_thw"].tolist() == theirs["image_grid_thw"].tolist()
+        assert mine["pixel_values"].shape == theirs["pixel_values"].shape
+        assert float((mine["pixel_values"] - theirs["pixel_values"]).abs().max()) < 0.05        # one 8-bit level of the resize
+        checked += 1
+    except ImportError:
+        pass
+    if not checked:
+        pytest.skip("no transformers processor to compare with")
