@@ -205,9 +205,11 @@ class PixtralPlugin(LlavaPlugin):
     break_token, end_token = "[IMG_BREAK]", "[IMG_END]"
 
     def _grid(self, img, cfg: TowerConfig) -> Tuple[int, int]:
-        ratio = max(img.height / cfg.image_size, img.width / cfg.image_size, 1.0)
-        h, w = math.ceil(img.height / ratio), math.ceil(img.width / ratio)
-        return max(1, math.ceil(h / cfg.patch_size)), max(1, math.ceil(w / cfg.patch_size))
+        ratio = max(img.height / cfg.image_size, img.width / cfg.image_size)
+        h, w = img.height, img.width
+        if ratio > 1:                  # rounded down, so that the longest side never exceeds the limit
+            h, w = int(math.floor(h / ratio)), int(math.floor(w / ratio))
+        return max(1, (h - 1) // cfg.patch_size + 1), max(1, (w - 1) // cfg.patch_size + 1)
 
     def _image_block(self, img, cfg: TowerConfig) -> str:
         gh, gw = self._grid(img, cfg)

@@ -176,5 +176,29 @@ def test_image_sizing_and_patch_layout_agree_with_transformers():
         checked += 1
     except ImportError:
         pass
+    try:
+        from types import SimpleNamespace
+        from transformers.models.pixtral.image_processing_pixtral import get_resize_output_image_size
+        from hybrid_model_factory_b200.data.mm_plugin_zoo import PixtralPlugin
+        pix, pcfg = PixtralPlugin("[IMG]", None, None), TowerConfig(image_size=1024, patch_size=16)
+        for _ in range(500):
+            h, w = random.randint(8, 4000), random.randint(8, 4000)
+            want = get_resize_output_image_size(np.zeros((h, w, 3), dtype=np.uint8), size=(1024, 1024),
+                                                patch_size=(16, 16), input_data_format="channels_last")
+            gh, gw = pix._grid(SimpleNamespace(height=h, width=w), pcfg)
+            assert (gh * 16, gw * 16) == tuple(want), (h, w)
+        checked += 1
+    except ImportError:
+        pass
+    try:
+        from transformers.models.got_ocr2.image_processing_got_ocr2 import get_optimal_tiled_canvas
+        from hybrid_model_factory_b200.data.mm_plugin_zoo import InternVLPlugin
+        icfg = TowerConfig(image_size=448)
+        for _ in range(500):
+            h, w = random.randint(30, 4000), random.randint(30, 4000)
+            assert tuple(InternVLPlugin.tile_grid(h, w, icfg)) == tuple(get_optimal_tiled_canvas((h, w), (448, 448), 1, 12))
+        checked += 1
+    except ImportError:
+        pass
     if not checked:
         pytest.skip("no transformers processor to compare with")
