@@ -193,6 +193,32 @@ def align_dataset(attr: DatasetAttr, dataset_dir: str, max_samples: Optional[int
 # ----------------------------------------------------------------------------------------
 # templates
 # ----------------------------------------------------------------------------------------
+# How a model family writes tools: the tool list in the system prompt, an assistant turn that calls functions, the
+# results shown back to it, and how calls are recognised in generated text ("xml": blocks between the two halves of
+# ``function``; "json": the answer is a JSON object, or several separated by ";", with ``name`` and ``parameters``;
+# "prefixed_list": a marker followed by a JSON list of calls).  ``joined``: all calls of a turn are one JSON list inside
+# one ``function`` block instead of one block per call.  Reference: the per-family tool formats of
+# ``data/tool_utils.py`` (default / qwen, llama3, mistral, glm4).
+TOOL_FORMATS: Dict[str, dict] = {
+    "qwen": dict(function="<tool_call>\n{content}\n</tool_call>", observation="<tool_response>\n{content}\n</tool_response>",
+                 tools=("\n\n# Tools\n\nYou may call one or more functions to assist with the user query.\n"
+                        "<tools>\n{content}\n</tools>\nFor each function call, return a json object with function "
+                        "name and arguments within <tool_call></tool_call> XML tags."), extract="xml", joined=False,
+                 arguments_key="arguments"),
+    "llama3": dict(function="{content}", observation="{content}",
+                   tools=("\n\nYou have access to the following functions. To call a function, please respond with JSON "
+                          "for a function call. Respond in the format {{\"name\": function name, \"parameters\": dictionary "
+                          "of argument name and its value}}. Do not use variables.\n\n{content}"), extract="json",
+                   joined=False, arguments_key="parameters"),
+    "mistral": dict(function="[TOOL_CALLS] {content}", observation="[TOOL_RESULTS] {{\"content\": {content}}}[/TOOL_RESULTS]",
+                    tools="[AVAILABLE_TOOLS] {content}[/AVAILABLE_TOOLS]", extract="prefixed_list", joined=True,
+                    arguments_key="arguments"),
+    "glm4": dict(function="{content}", observation="<|observation|>\n{content}",
+                 tools=("\n\n# 可用工具\n{content}\n在调用上述函数时，请使用 Json 格式表示调用的参数。"), extract="name_then_json",
+                 joined=False, arguments_key="arguments"),
+}
+
+
 @dataclass
 class Template:
     name: str
@@ -208,6 +234,28 @@ class Template:
                       "<tools>\n{content}\n</tools>\nFor each function call, return a json object with function "
                       "name and arguments within <tool_call></tool_call> XML tags.")
 
+    tool_format: str = "qwen"
+
+    def __post_init__(self):
+        spec = TOOL_FORMATS.get(self.tool_format)
+        if spec is None:
+            raise ValueError(f"template {self.name}: unknown tool format '{self.tool_format}' ({sorted(TOOL_FORMATS)})")
+        if self.tool_format != "qwen":      # the family's own way of writing tools
+            self.function_fmt, self.observation_fmt, self.tools_fmt = spec["function"], spec["observation"], spec["tools"]
+
+    def _render_calls(self, calls: list) -> str:
+        """Text of an assistant turn that makes ``calls`` (``[{name, arguments}]``) in this family's format."""
+        import json as _json
+        spec = TOOL_FORMATS[self.tool_format]
+        key = spec["arguments_key"]
+        objs = [{"name": c["name"], key: c.get("arguments", c.get("parameters", {}))} for c in calls]
+        if spec["extract"] == "name_then_json":
+            return "\n".join(f"{o['name']}\n{_json.dumps(o[key], ensure_ascii=False)}" for o in objs)
+        if spec["joined"]:
+            return self.function_fmt.format(content=_json.dumps(objs, ensure_ascii=False))
+        sep = "; " if spec["extract"] == "json" else "\n"
+        return sep.join(self.function_fmt.format(content=_json.dumps(o, ensure_ascii=False)) for o in objs)
+
     def normalise(self, messages: Sequence[dict], system: str = "", tools: str = ""):
         """Tool turns become ordinary ones: a ``function`` turn is an assistant turn wrapped in ``function_fmt``, an
         ``observation`` a user turn wrapped in ``observation_fmt``; a tool list is appended to the system prompt."""
@@ -219,7 +267,11 @@ class Template:
                     import json as _json
                     calls = _json.loads(content)
                     calls = calls if isinstance(calls, list) else [calls]
-                    content = "\n".join(self.function_fmt.format(content=_json.dumps(c_, ensure_ascii=False)) for c_ in calls)
+                    if all(isinstance(c_, dict) and "name" in c_ for c_ in calls):
+                        content = self._render_calls(calls)
+                    else:
+                        content = "\n".join(self.function_fmt.format(content=_json.dumps(c_, ensure_ascii=False))
+                                            for c_ in calls)
                     out.append({"role": "assistant", "content": content})
                     continue
                 except (ValueError, TypeError):
@@ -235,10 +287,47 @@ class Template:
         return out, system
 
     def extract_tool_calls(self, text: str):
-        """``(remaining text, [{"name": ..., "arguments": {...}}, ...])``: the blocks of an answer that have the shape
-        of ``function_fmt`` and hold a JSON object with a ``name``; anything else stays text."""
+        """``(remaining text, [{"name": ..., "arguments": {...}}, ...])``: the function calls an answer makes, in this
+        family's format; anything that does not parse stays text."""
         import json as _json
         import re
+        spec = TOOL_FORMATS[self.tool_format]
+
+        def as_call(obj):
+            if isinstance(obj, dict) and "name" in obj:
+                return {"name": obj["name"], "arguments": obj.get("arguments", obj.get("parameters", {}))}
+            return None
+
+        kind = spec["extract"]
+        if kind == "json":                                  # the whole answer: one JSON object, or several after ";"
+            try:
+                objs = [_json.loads(text)]
+            except ValueError:
+                try:
+                    objs = [_json.loads(part) for part in text.split("; ")]
+                except ValueError:
+                    return text, []
+            calls = [as_call(o) for o in objs]
+            return ("", calls) if calls and all(calls) else (text, [])
+        if kind == "prefixed_list":
+            marker = self.function_fmt.partition("{content}")[0].strip()
+            at = text.find(marker)
+            if at < 0:
+                return text, []
+            try:
+                objs = _json.loads(text[at + len(marker):].strip())
+            except ValueError:
+                return text, []
+            calls = [as_call(o) for o in (objs if isinstance(objs, list) else [objs])]
+            return (text[:at].strip(), calls) if calls and all(calls) else (text, [])
+        if kind == "name_then_json":                        # a function name on one line, its arguments on the next
+            m = re.fullmatch(r"\s*([\w.\-]+)\n(\{.*\})\s*", text, flags=re.S)
+            if not m:
+                return text, []
+            try:
+                return "", [{"name": m.group(1), "arguments": _json.loads(m.group(2))}]
+            except ValueError:
+                return text, []
         head, _, tail = self.function_fmt.partition("{content}")
         head, tail = head.strip(), tail.strip()
         if not head or not tail:
@@ -246,12 +335,12 @@ class Template:
         calls, rest, pos = [], [], 0
         for m in re.finditer(re.escape(head) + r"\s*(.*?)\s*" + re.escape(tail), text, flags=re.S):
             try:
-                obj = _json.loads(m.group(1))
+                call = as_call(_json.loads(m.group(1)))
             except ValueError:
                 continue
-            if not isinstance(obj, dict) or "name" not in obj:
+            if call is None:
                 continue
-            calls.append({"name": obj["name"], "arguments": obj.get("arguments", obj.get("parameters", {}))})
+            calls.append(call)
             rest.append(text[pos:m.start()])
             pos = m.end()
         rest.append(text[pos:])
@@ -304,11 +393,12 @@ TEMPLATES: Dict[str, Template] = {
     "llama3": Template("llama3", system_fmt="<|start_header_id|>system<|end_header_id|>\n\n{content}<|eot_id|>",
                        user_fmt="<|start_header_id|>user<|end_header_id|>\n\n{content}<|eot_id|>"
                                 "<|start_header_id|>assistant<|end_header_id|>\n\n",
-                       assistant_fmt="{content}<|eot_id|>", add_bos=True, efficient_eos=False),
+                       assistant_fmt="{content}<|eot_id|>", add_bos=True, efficient_eos=False, tool_format="llama3"),
     "mistral": Template("mistral", system_fmt="{content}\n\n", user_fmt="[INST] {content}[/INST]",
-                        assistant_fmt=" {content}", add_bos=True),
+                        assistant_fmt=" {content}", add_bos=True, tool_format="mistral"),
     "ministral": Template("ministral", system_fmt="[SYSTEM_PROMPT]{content}[/SYSTEM_PROMPT]",
-                          user_fmt="[INST]{content}[/INST]", assistant_fmt="{content}", add_bos=True),
+                          user_fmt="[INST]{content}[/INST]", assistant_fmt="{content}", add_bos=True,
+                          tool_format="mistral"),
     "qwen3_nothink": Template("qwen3_nothink", system_fmt="<|im_start|>system\n{content}<|im_end|>\n",
                               user_fmt="<|im_start|>user\n{content}<|im_end|>\n<|im_start|>assistant\n<think>\n\n</think>\n\n",
                               assistant_fmt="{content}<|im_end|>\n", efficient_eos=False),

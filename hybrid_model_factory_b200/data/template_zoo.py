@@ -12,10 +12,11 @@ CHATML = dict(system_fmt="<|im_start|>system\n{content}<|im_end|>\n",
 LLAMA3 = dict(system_fmt="<|start_header_id|>system<|end_header_id|>\n\n{content}<|eot_id|>",
               user_fmt="<|start_header_id|>user<|end_header_id|>\n\n{content}<|eot_id|>"
                        "<|start_header_id|>assistant<|end_header_id|>\n\n",
-              assistant_fmt="{content}<|eot_id|>", add_bos=True, efficient_eos=False)
+              assistant_fmt="{content}<|eot_id|>", add_bos=True, efficient_eos=False, tool_format="llama3")
 GEMMA = dict(system_fmt="{content}\n\n", user_fmt="<start_of_turn>user\n{content}<end_of_turn>\n<start_of_turn>model\n",
              assistant_fmt="{content}<end_of_turn>\n", add_bos=True, efficient_eos=False)
-MISTRAL = dict(system_fmt="{content}\n\n", user_fmt="[INST] {content}[/INST]", assistant_fmt=" {content}", add_bos=True)
+MISTRAL = dict(system_fmt="{content}\n\n", user_fmt="[INST] {content}[/INST]", assistant_fmt=" {content}", add_bos=True,
+               tool_format="mistral")
 VICUNA_SYS = ("A chat between a curious user and an artificial intelligence assistant. "
               "The assistant gives helpful, detailed, and polite answers to the user's questions.")
 
@@ -48,7 +49,7 @@ ZOO = {
                         default_system=VICUNA_SYS),
     # Mistral family
     "mistral_small": dict(system_fmt="[SYSTEM_PROMPT]{content}[/SYSTEM_PROMPT]", user_fmt="[INST]{content}[/INST]",
-                          assistant_fmt="{content}", add_bos=True),
+                          assistant_fmt="{content}", add_bos=True, tool_format="mistral"),
     "pixtral": dict(MISTRAL), "llava_next_mistral": dict(MISTRAL), "breeze": dict(MISTRAL, efficient_eos=True),
     # Gemma family
     "gemma2": dict(GEMMA), "gemma3": dict(GEMMA), "gemma3n": dict(GEMMA), "paligemma": dict(GEMMA),
@@ -64,10 +65,10 @@ ZOO = {
     "belle": dict(system_fmt="{content}", user_fmt="Human: {content}\n\nBelle: ", assistant_fmt="{content}\n\n", add_bos=True),
     "bluelm": dict(system_fmt="{content}", user_fmt="[|Human|]:{content}[|AI|]:", assistant_fmt="{content}"),
     "chatglm2": dict(system_fmt="{content}", user_fmt="[Round 1]\n\n问:{content}\n\n答:", assistant_fmt="{content}\n\n"),
-    "chatglm3": dict(system_fmt="<|system|>\n{content}", user_fmt="<|user|>\n{content}<|assistant|>\n", assistant_fmt="{content}"),
-    "glm4_moe": dict(system_fmt="<|system|>\n{content}", user_fmt="<|user|>\n{content}<|assistant|>\n", assistant_fmt="{content}"),
-    "glm4v": dict(system_fmt="<|system|>\n{content}", user_fmt="<|user|>\n{content}<|assistant|>\n", assistant_fmt="{content}"),
-    "glmz1": dict(system_fmt="<|system|>\n{content}", user_fmt="<|user|>\n{content}<|assistant|>\n", assistant_fmt="{content}"),
+    "chatglm3": dict(system_fmt="<|system|>\n{content}", user_fmt="<|user|>\n{content}<|assistant|>\n", assistant_fmt="{content}", tool_format="glm4"),
+    "glm4_moe": dict(system_fmt="<|system|>\n{content}", user_fmt="<|user|>\n{content}<|assistant|>\n", assistant_fmt="{content}", tool_format="glm4"),
+    "glm4v": dict(system_fmt="<|system|>\n{content}", user_fmt="<|user|>\n{content}<|assistant|>\n", assistant_fmt="{content}", tool_format="glm4"),
+    "glmz1": dict(system_fmt="<|system|>\n{content}", user_fmt="<|user|>\n{content}<|assistant|>\n", assistant_fmt="{content}", tool_format="glm4"),
     "codegeex2": dict(system_fmt="{content}", user_fmt="{content}", assistant_fmt="{content}"),
     "codegeex4": dict(system_fmt="<|system|>\n{content}", user_fmt="<|user|>\n{content}<|assistant|>\n", assistant_fmt="{content}",
                       default_system="你是一位智能编程助手，你叫CodeGeeX。"),

@@ -1126,3 +1126,37 @@ def test_gptq_awq_unpacking_agrees_with_an_independent_packer():
     assert torch.equal(_awq_natural(_unpack(quant_utils.awq_pack(q, 4, k, n), 4, dim=1), 4), q)
     q8 = torch.randint(0, 256, (k, n), dtype=torch.int32)
     assert torch.equal(_unpack(quant_utils.gptq_pack(q8, 8, k, n), 8, dim=0), q8)
+
+
+def test_tool_formats_per_model_family():
+    """Tool lists, calls and results are written the way each family expects, and the calls a model writes in that
+    format are recognised again."""
+    import json
+    from hybrid_model_factory_b200.data.formats import ByteTokenizer, get_template
+    calls = [{"name": "weather", "arguments": {"city": "Oslo"}}, {"name": "time", "arguments": {}}]
+    tools = json.dumps([{"name": "weather", "parameters": {"type": "object"}}])
+    msgs = [{"role": "user", "content": "q"}, {"role": "function", "content": json.dumps(calls)},
+            {"role": "observation", "content": "rain"}]
+    expect = {
+        "qwen3": ('<tool_call>\n{"name": "weather", "arguments": {"city": "Oslo"}}\n</tool_call>\n<tool_call>\n'
+                  '{"name": "time", "arguments": {}}\n</tool_call>', "<tool_response>\nrain\n</tool_response>", "<tools>"),
+        "llama3": ('{"name": "weather", "parameters": {"city": "Oslo"}}; {"name": "time", "parameters": {}}', "rain",
+                   "You have access to the following functions"),
+        "mistral": ('[TOOL_CALLS] [{"name": "weather", "arguments": {"city": "Oslo"}}, {"name": "time", "arguments": {}}]',
+                    '[TOOL_RESULTS] {"content": rain}[/TOOL_RESULTS]', "[AVAILABLE_TOOLS]"),
+        "glm4_moe": ('weather\n{"city": "Oslo"}\ntime\n{}', "<|observation|>\nrain", "可用工具"),
+    }
+    for name, (call_text, result_text, tools_mark) in expect.items():
+        tpl = get_template(name)
+        turns, system = tpl.normalise(msgs, "sys", tools)
+        assert turns[1] == {"role": "assistant", "content": call_text}, name
+        assert turns[2] == {"role": "user", "content": result_text}, name
+        assert system.startswith("sys") and tools_mark in system and '"weather"' in system, name
+        assert tpl.encode_multiturn(ByteTokenizer(), turns + [{"role": "assistant", "content": ""}], system)
+    # recognition of generated calls
+    assert get_template("qwen3").extract_tool_calls("ok " + expect["qwen3"][0]) == ("ok", calls)
+    assert get_template("llama3").extract_tool_calls(expect["llama3"][0]) == ("", calls)
+    assert get_template("llama3").extract_tool_calls("just text") == ("just text", [])
+    assert get_template("mistral").extract_tool_calls("sure. " + expect["mistral"][0]) == ("sure.", calls)
+    assert get_template("glm4_moe").extract_tool_calls('weather\n{"city": "Oslo"}') == ("", calls[:1])
+    assert get_template("glm4_moe").extract_tool_calls("no call here") == ("no call here", [])
