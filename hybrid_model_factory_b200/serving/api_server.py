@@ -278,18 +278,25 @@ def create_app(engine: ServingEngine, tokenizer, model_name: str = "hybrid", tem
                 sink: asyncio.Queue = asyncio.Queue()
                 tasks = [asyncio.ensure_future(drain(c, sink)) for c in choices]
                 live = n
-                while live:
-                    c, piece = await sink.get()
-                    if c.failed:
-                        yield "data: " + json.dumps({"error": repr(loop_runner.error)}) + "\n\n"
-                        for t in tasks:
-                            t.cancel()
-                        return
-                    delta = {"delta": {"content": piece}} if chat else {"text": piece}
-                    yield "data: " + json.dumps({"id": cid, "created": created, "model": model_name,
-                                                 "choices": [{"index": c.index, **delta, "finish_reason": c.reason}]}) + "\n\n"
-                    live -= c.reason is not None
-                yield "data: [DONE]\n\n"
+                try:
+                    while live:
+                        c, piece = await sink.get()
+                        if c.failed:
+                            yield "data: " + json.dumps({"error": repr(loop_runner.error)}) + "\n\n"
+                            return
+                        delta = {"delta": {"content": piece}} if chat else {"text": piece}
+                        yield "data: " + json.dumps({"id": cid, "created": created, "model": model_name,
+                                                     "choices": [{"index": c.index, **delta,
+                                                                  "finish_reason": c.reason}]}) + "\n\n"
+                        live -= c.reason is not None
+                    yield "data: [DONE]\n\n"
+                finally:
+                    # a client that went away (the generator is closed early) must not keep its requests decoding
+                    for t in tasks:
+                        t.cancel()
+                    for c in choices:
+                        if c.reason is None:
+                            loop_runner.abort(c.q)
             return StreamingResponse(gen(), media_type="text/event-stream")
         await asyncio.gather(*[drain(c) for c in choices])
         if any(c.failed for c in choices):

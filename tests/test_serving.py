@@ -400,6 +400,17 @@ def test_openai_compatible_server_routes():
         chunks = [json.loads(c[6:]) for c in [c async for c in stream.body_iterator][:-1]]
         assert "".join(c["choices"][0]["text"] for c in chunks) == text[:text.find(stop)]
         assert chunks[-1]["choices"][0]["finish_reason"] == "stop"
+        # a client that stops reading: closing the stream drops the request inside the engine
+        stream = await routes["/v1/completions"]({"prompt": prompt, "max_tokens": 40, "stream": True, "ignore_eos": True})
+        it = stream.body_iterator
+        await it.__anext__()
+        await it.aclose()
+        for _ in range(100):
+            if not eng.has_unfinished():
+                break
+            await asyncio.sleep(0.02)
+        last = list(eng.requests.values())[-1]
+        assert last.finish_reason == "abort" and len(last.output) < 40
         # stop tokens end a request inside the engine; n > 1 returns that many choices
         third = tok.encode(text, add_special_tokens=False)[2]
         st = json.loads((await routes["/v1/completions"]({"prompt": prompt, "max_tokens": 12, "ignore_eos": True,
