@@ -202,3 +202,30 @@ def test_image_sizing_and_patch_layout_agree_with_transformers():
         pass
     if not checked:
         pytest.skip("no transformers processor to compare with")
+
+
+@pytest.mark.parametrize("name", ["qwen3", "qwen3_moe", "mistral_sliding"])
+def test_loss_and_gradients_equal_the_hugging_face_model(tmp_path, name):
+    """Same next-token loss and the same gradients (fused linear + cross-entropy, attention / MoE backward of this
+    package's reference ops against autograd through the Hugging Face modules)."""
+    cfg_name, model_name, extra = CASES[name]
+    if not hasattr(T, model_name):
+        pytest.skip(f"this transformers has no {model_name}")
+    torch.manual_seed(0)
+    hf = getattr(T, model_name)(getattr(T, cfg_name)(**COMMON, **extra)).train()
+    hf.save_pretrained(str(tmp_path / "hf"), safe_serialization=True)
+    own = checkpoint_io.from_pretrained(str(tmp_path / "hf"), dtype=torch.float32).train()
+    ids = torch.randint(0, COMMON["vocab_size"], (2, 24))
+    own.config.router_aux_loss_coef = 0.0   # the language-model loss alone (the routers' balancing term is an extra)
+    loss_hf = hf(input_ids=ids, labels=ids).loss
+    loss_own = own(input_ids=ids, labels=ids).loss
+    assert abs(float(loss_hf) - float(loss_own)) < 1e-5
+    loss_hf.backward()
+    loss_own.backward()
+    theirs = dict(hf.named_parameters())
+    checked = 0
+    for n, p in own.named_parameters():
+        if n in theirs and p.grad is not None and theirs[n].grad is not None:
+            assert torch.allclose(p.grad, theirs[n].grad, atol=2e-5), (n, float((p.grad - theirs[n].grad).abs().max()))
+            checked += 1
+    assert checked >= 20
