@@ -272,3 +272,40 @@ def test_converted_qwen3_next_gradients_equal_the_hugging_face_model(tmp_path):
         assert torch.allclose(g_own.dt_bias.grad, g_hf.dt_bias.grad, atol=3e-5)
         assert torch.allclose(g_own.o_proj.weight.grad, g_hf.out_proj.weight.grad, atol=3e-5)
         assert torch.allclose(g_own.o_norm.weight.grad, g_hf.norm.weight.grad, atol=3e-5)
+
+
+def test_serving_engine_generates_what_hugging_face_generates(tmp_path):
+    """Continuous batching, paged attention cache, recurrent-state slots, chunked prefill and speculative decoding of
+    the serving engine on a converted Qwen3-Next checkpoint: three prompts of different lengths come out token for
+    token as Hugging Face ``generate`` produces them one by one."""
+    if not hasattr(T, "Qwen3NextForCausalLM"):
+        pytest.skip("this transformers has no Qwen3-Next")
+    from hybrid_model_factory_b200.priming.convert_qwen_gdn import convert_checkpoint
+    from hybrid_model_factory_b200.serving.engine import SamplingParams, ServingEngine
+    torch.manual_seed(0)
+    cfg = T.Qwen3NextConfig(
+        vocab_size=160, hidden_size=64, intermediate_size=128, num_hidden_layers=4, num_attention_heads=4,
+        num_key_value_heads=2, head_dim=16, max_position_embeddings=512, linear_num_key_heads=2,
+        linear_num_value_heads=4, linear_key_head_dim=16, linear_value_head_dim=16, linear_conv_kernel_dim=4,
+        num_experts=4, num_experts_per_tok=2, moe_intermediate_size=32, shared_expert_intermediate_size=32,
+        decoder_sparse_step=1, norm_topk_prob=True, full_attention_interval=4, partial_rotary_factor=0.25,
+        mlp_only_layers=[])
+    hf = T.Qwen3NextForCausalLM(cfg).eval()
+    with torch.no_grad():
+        for _, p in hf.named_parameters():
+            if p.dim() == 1:
+                p.add_(torch.randn_like(p) * 0.1)
+    hf.save_pretrained(str(tmp_path / "hf"), safe_serialization=True)
+    convert_checkpoint(str(tmp_path / "hf"), str(tmp_path / "own"), None, False, torch.float32)
+    own = checkpoint_io.from_pretrained(str(tmp_path / "own"), dtype=torch.float32, init="meta").eval()
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(0, 160, (n,), generator=g).tolist() for n in (37, 9, 21)]
+    want = []
+    with torch.no_grad():
+        for p in prompts:
+            want.append(hf.generate(torch.tensor([p]), max_new_tokens=8, do_sample=False)[0, len(p):].tolist())
+    for kwargs, spec in (({"max_num_batched_tokens": 64}, 0), ({"max_num_batched_tokens": 16, "whole_prompts": False}, 0),
+                         ({"max_num_batched_tokens": 64}, 3)):
+        eng = ServingEngine(own, block_size=8, num_blocks=64, max_num_seqs=4, max_model_len=128, **kwargs)
+        got = eng.generate(prompts, SamplingParams(max_new_tokens=8, speculative_tokens=spec))
+        assert got == want, (kwargs, spec)
