@@ -25,6 +25,10 @@ CASES = {
     "llama3_rope": ("LlamaConfig", "LlamaForCausalLM", dict(rope_parameters={
         "rope_type": "llama3", "rope_theta": 50000.0, "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
         "original_max_position_embeddings": 64})),
+    "llama_with_biases": ("LlamaConfig", "LlamaForCausalLM", dict(attention_bias=True, mlp_bias=True, rope_theta=10000.0)),
+    "llama_linear_rope": ("LlamaConfig", "LlamaForCausalLM", dict(rope_parameters={
+        "rope_type": "linear", "rope_theta": 10000.0, "factor": 2.0})),
+    "qwen3_attention_bias": ("Qwen3Config", "Qwen3ForCausalLM", dict(head_dim=16, attention_bias=True)),
     "mistral_sliding": ("MistralConfig", "MistralForCausalLM", dict(head_dim=16, sliding_window=8)),
     "qwen3_moe": ("Qwen3MoeConfig", "Qwen3MoeForCausalLM", dict(
         head_dim=16, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=32, decoder_sparse_step=1,
@@ -42,7 +46,7 @@ def test_logits_equal_the_hugging_face_model(tmp_path, name):
         pytest.skip(f"this transformers has no {model_name}")
     torch.manual_seed(0)
     try:
-        hf = getattr(T, model_name)(getattr(T, cfg_name)(**COMMON, **extra)).eval()
+        hf = getattr(T, model_name)(getattr(T, cfg_name)(**{**COMMON, **extra})).eval()
     except TypeError as e:                      # a config dialect this transformers version does not speak
         pytest.skip(str(e))
     hf.save_pretrained(str(tmp_path / "hf"), safe_serialization=True)
@@ -212,7 +216,7 @@ def test_loss_and_gradients_equal_the_hugging_face_model(tmp_path, name):
     if not hasattr(T, model_name):
         pytest.skip(f"this transformers has no {model_name}")
     torch.manual_seed(0)
-    hf = getattr(T, model_name)(getattr(T, cfg_name)(**COMMON, **extra)).train()
+    hf = getattr(T, model_name)(getattr(T, cfg_name)(**{**COMMON, **extra})).train()
     hf.save_pretrained(str(tmp_path / "hf"), safe_serialization=True)
     own = checkpoint_io.from_pretrained(str(tmp_path / "hf"), dtype=torch.float32).train()
     ids = torch.randint(0, COMMON["vocab_size"], (2, 24))
